@@ -1,0 +1,99 @@
+"""Seeded synthetic models: random-init weights quantized to GGUF blocks.
+
+No model file, tokenizer or dataset is involved: every benchmark configuration
+uses seeded N(0, 0.02) weights, then Q4_0 / Q4_K quantization, and random token
+ids.  Tensor names follow the GGUF names the reference engine looks up
+(adam/models/engine.py:2895-2921).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Union
+
+import numpy as np
+
+from . import gguf_blocks as gb
+from .config import ModelConfig
+
+
+@dataclass
+class QTensor:
+    """A 2-D weight kept as raw GGUF blocks, row-major ``[rows, cols]``."""
+    ggml_type: int
+    rows: int
+    cols: int
+    raw: np.ndarray            # uint8, rows * cols/block * block_bytes
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    @property
+    def nbytes(self) -> int:
+        return int(self.raw.size)
+
+
+Tensor = Union[QTensor, np.ndarray]
+
+LAYER_MATS = ("attn_q", "attn_k", "attn_v", "attn_output", "ffn_gate", "ffn_up", "ffn_down")
+LAYER_NORMS = ("attn_norm", "post_attention_norm", "ffn_norm", "post_ffw_norm")
+
+
+def mat_shapes(cfg: ModelConfig) -> Dict[str, tuple]:
+    q_dim = cfg.n_head * cfg.head_dim
+    k_dim = cfg.n_head_kv * cfg.head_dim_kv
+    return {
+        "attn_q": (q_dim, cfg.n_embd), "attn_k": (k_dim, cfg.n_embd), "attn_v": (k_dim, cfg.n_embd),
+        "attn_output": (cfg.n_embd, q_dim),
+        "ffn_gate": (cfg.n_ff, cfg.n_embd), "ffn_up": (cfg.n_ff, cfg.n_embd),
+        "ffn_down": (cfg.n_embd, cfg.n_ff),
+    }
+
+
+def _quantize(w: np.ndarray, ggml_type: int) -> QTensor:
+    raw = gb.quantize_q4_0(w) if ggml_type == gb.GGML_TYPE_Q4_0 else gb.quantize_q4_k(w)
+    return QTensor(ggml_type, w.shape[0], w.shape[1], np.ascontiguousarray(raw).reshape(-1))
+
+
+def build_model(cfg: ModelConfig, ggml_type: int = gb.GGML_TYPE_Q4_0, seed: int = 0,
+                tied: bool = True, norm_noise: float = 0.1, qk_norm: bool = True,
+                post_norms: bool = True) -> Dict[str, Tensor]:
+    """Random-init model on the host: N(0, 0.02) matrices quantized to
+    ``ggml_type``, norm weights ``1 + norm_noise * N(0,1)``."""
+    rng = np.random.default_rng(seed)
+
+    def mat(rows, cols):
+        w = rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02)
+        return _quantize(w, ggml_type)
+
+    def norm(n):
+        return (np.float32(1) + np.float32(norm_noise) * rng.standard_normal(n, dtype=np.float32)).astype(np.float32)
+
+    t: Dict[str, Tensor] = {}
+    t["token_embd.weight"] = mat(cfg.n_vocab, cfg.n_embd)
+    if not tied:
+        t["output.weight"] = mat(cfg.n_vocab, cfg.n_embd)
+    t["output_norm.weight"] = norm(cfg.n_embd)
+    shapes = mat_shapes(cfg)
+    for L in range(cfg.n_layer):
+        p = f"blk.{L}"
+        for n in LAYER_NORMS:
+            if n.startswith("post_") and not post_norms:
+                continue
+            t[f"{p}.{n}.weight"] = norm(cfg.n_embd)
+        if qk_norm:
+            t[f"{p}.attn_q_norm.weight"] = norm(cfg.head_dim)
+            t[f"{p}.attn_k_norm.weight"] = norm(cfg.head_dim_kv)
+        for n in LAYER_MATS:
+            t[f"{p}.{n}.weight"] = mat(*shapes[n])
+    return t
+
+
+def model_weight_elems(cfg: ModelConfig, tied: bool = True) -> int:
+    """Number of quantized weights one decoded token reads."""
+    per_layer = sum(r * c for r, c in mat_shapes(cfg).values())
+    return cfg.n_layer * per_layer + cfg.n_vocab * cfg.n_embd
+
+
+def random_prompt(n_vocab: int, n: int, seed: int = 1) -> np.ndarray:
+    return np.random.default_rng(seed).integers(0, n_vocab, size=n, dtype=np.int64).astype(np.int32)
