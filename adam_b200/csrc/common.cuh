@@ -1,0 +1,141 @@
+// Shared declarations of libadam_b200: global context, maps, loc handles, and
+// small device helpers.  One context per process, single-threaded callers, as
+// in the reference runtime (adamah-MAIN/adamah/adamah.c:510-644).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/adam_b200.h"
+
+namespace ab {
+
+constexpr uint32_t MAX_MAPS    = 64;      // reference: MAX_MAPS 16 (adamah.c:30)
+constexpr uint32_t MAX_HANDLES = 1u << 16; // reference: MAX_RES 2048 (adamah.c:31)
+
+// Bits a kernel may OR into the device error word instead of faulting.
+constexpr uint32_t DEVERR_OOB_MAP   = 1u;   // a loc pointed outside its map
+constexpr uint32_t DEVERR_WAIT      = 2u;   // a bounded device-side wait ran out
+constexpr uint32_t DEVERR_BAD_TOKEN = 4u;   // token id outside the vocabulary
+
+struct Map {
+    bool     used;
+    uint32_t dtype;        // ADAMAH_DTYPE_*
+    uint32_t word_size;    // bytes per element for F32 maps
+    uint32_t pack_size;    // elements per pack (locs address packs)
+    uint32_t n_packs;
+    uint32_t group_size;   // Q4 map: elements per (scale, zero) pair
+    uint64_t n_elems;      // pack_size * n_packs
+    void*    buf;          // F32: float[n]; Q4: uint32[ceil(n/8)];
+                           // GGUF_Q4_K: raw 144-byte superblocks;
+                           // GGUF_Q4_0: quant plane (uint4 per block) then scale plane (half per block)
+    size_t   bytes;
+    float*   qparams;      // Q4 map: interleaved [scale, zero] per group
+    uint32_t n_groups;
+    uint4*   q40_qs;       // GGUF_Q4_0 planes (inside buf)
+    __half*  q40_d;
+};
+
+struct Handle {
+    void*     dev;
+    uint32_t  nbytes;
+    bool      used;
+    uint32_t* shadow;      // host copy of what the host uploaded (NULL for device-produced data)
+};
+
+struct Context {
+    bool         inited;
+    int          device;
+    int          sm_count;
+    size_t       total_mem;
+    cudaStream_t stream;
+    Map          maps[MAX_MAPS];
+    Handle*      handles;       // [MAX_HANDLES], index = handle id
+    uint32_t     handle_cursor;
+    uint32_t     active_dtype;
+    int          batch_depth;
+    int          fusion_enabled;
+    int          sched_mode;
+    uint64_t     ticket;
+    uint64_t     launches;      // kernels launched (graph nodes counted one by one)
+    uint64_t     submits;       // stream synchronisations that closed a batch
+    uint64_t     flushes;
+    uint32_t*    dev_err;       // device error word
+};
+
+extern Context g;
+
+int  fail(int code, const char* fmt, ...);          // records text, returns code
+bool ready();                                       // context initialised?
+Map* get_map(uint32_t id);                          // NULL (+ error text) if absent
+bool handle_ok(uint32_t h, uint32_t min_bytes);     // exists and holds >= min_bytes
+inline uint32_t* hlocs(uint32_t h) { return (uint32_t*)g.handles[h].dev; }
+inline float*    hdata(uint32_t h) { return (float*)g.handles[h].dev; }
+// First word of a loc handle (the base of single-base ops).  Served from the host
+// copy kept at upload time; device-produced handles cost one small read-back.
+bool hfirst(uint32_t h, uint32_t* out);
+uint32_t handle_alloc(uint32_t n_bytes);            // 0 on failure
+int  check_launch(const char* what);                // cudaGetLastError -> status
+inline void count_launch(uint64_t n = 1) { g.launches += n; }
+void end_of_op();                                   // sync when not inside a batch
+
+// ---- device helpers --------------------------------------------------------
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a whole CTA (blockDim.x a multiple of 32, at most 1024).  `red` is
+// shared scratch of at least 33 floats.  Every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();                 // protect `red` from a previous use
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = (lane < nw) ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = (lane < nw) ? red[lane] : -3.402823466e+38f;
+        t = warp_max(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// tanh-approximated GELU exactly as the reference's numpy decoder writes it
+// (tests/diagnostics/diag_inference.py:941-943).
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float k = 0.7978845608028654f;        // float32(sqrt(2/pi))
+    float x3 = x * x * x;
+    float inner = k * (x + 0.044715f * x3);
+    return 0.5f * x * (1.0f + tanhf(inner));
+}
+__device__ __forceinline__ float silu_clip(float x) {
+    float c = fminf(fmaxf(x, -80.f), 80.f);     // diag_inference.py:945-946
+    return x * (1.0f / (1.0f + expf(-c)));
+}
+
+}  // namespace ab

@@ -1,0 +1,735 @@
+// Context, maps, loc handles and host<->device I/O of libadam_b200.
+//
+// CUDA counterpart of the reference's native runtime for the parts the decode
+// path needs (adamah-MAIN/adamah/adamah.c): typed maps (:2698-2824), host
+// scatter/gather (:3087-3371, :3374), loc-handle pool (:3570-3663), batching
+// (:1629-1721) and the scheduling counters (:282-346).  A map is a cudaMalloc'd
+// array, a loc handle a small device array, a batch a section of one in-order
+// stream closed by a single synchronisation.
+#include "common.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+namespace ab {
+
+Context g = {};
+static char g_err[512] = "no error";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    if (getenv("ADAMAH_DEBUG")) fprintf(stderr, "[adam_b200] error %d: %s\n", code, g_err);
+    return code;
+}
+
+bool ready() {
+    if (!g.inited) { fail(ADAMAH_ERR_INVALID, "backend not initialised (call adamah_init)"); return false; }
+    return true;
+}
+
+Map* get_map(uint32_t id) {
+    if (!ready()) return nullptr;
+    if (id >= MAX_MAPS || !g.maps[id].used) { fail(ADAMAH_ERR_NOT_FOUND, "map %u does not exist", id); return nullptr; }
+    return &g.maps[id];
+}
+
+bool handle_ok(uint32_t h, uint32_t min_bytes) {
+    if (h == 0 || h >= MAX_HANDLES || !g.handles[h].used) { fail(ADAMAH_ERR_NOT_FOUND, "loc handle %u does not exist", h); return false; }
+    if (g.handles[h].nbytes < min_bytes) {
+        fail(ADAMAH_ERR_INVALID, "loc handle %u holds %u bytes, op needs %u", h, g.handles[h].nbytes, min_bytes);
+        return false;
+    }
+    return true;
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(ADAMAH_ERR_BACKEND, "%s: %s", what, cudaGetErrorString(e));
+    return ADAMAH_OK;
+}
+
+void end_of_op() {
+    if (g.batch_depth == 0) { cudaStreamSynchronize(g.stream); g.submits++; }
+}
+
+static int cuda_fail(cudaError_t e, const char* what) {
+    return fail(e == cudaErrorMemoryAllocation ? ADAMAH_ERR_MEMORY : ADAMAH_ERR_BACKEND, "%s: %s", what, cudaGetErrorString(e));
+}
+#define CU(x) do { cudaError_t e__ = (x); if (e__ != cudaSuccess) return cuda_fail(e__, #x); } while (0)
+
+// ---- kernels ---------------------------------------------------------------
+
+__global__ void k_scatter_f32(float* __restrict__ map, uint64_t n_elems, const uint32_t* __restrict__ locs, uint32_t start_pack,
+                              const float* __restrict__ data, uint32_t n_locs, uint32_t pack, uint32_t* err) {
+    uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= (uint64_t)n_locs * pack) return;
+    uint32_t li = (uint32_t)(tid / pack), ei = (uint32_t)(tid % pack);
+    uint64_t dst = (uint64_t)(locs ? locs[li] : start_pack + li) * pack + ei;
+    if (dst >= n_elems) { atomicOr(err, DEVERR_OOB_MAP); return; }
+    map[dst] = data[tid];
+}
+
+__global__ void k_gather_f32(const float* __restrict__ map, uint64_t n_elems, const uint32_t* __restrict__ locs,
+                             float* __restrict__ out, uint32_t n_locs, uint32_t pack, uint32_t* err) {
+    uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= (uint64_t)n_locs * pack) return;
+    uint32_t li = (uint32_t)(tid / pack), ei = (uint32_t)(tid % pack);
+    uint64_t src = (uint64_t)locs[li] * pack + ei;
+    if (src >= n_elems) { atomicOr(err, DEVERR_OOB_MAP); out[tid] = 0.f; return; }
+    out[tid] = map[src];
+}
+
+// float32 -> Q4 map: q = clamp(round((v - zero)/max(scale,1e-10)), 0, 15), ties to
+// even (adamah-MAIN/adamah/shaders/src/q4/map_scatter.comp; tests/test_q4_roundtrip.py:47-63).
+__global__ void k_scatter_q4map(uint32_t* __restrict__ words, uint64_t n_elems, const float* __restrict__ qp, uint32_t group,
+                                const uint32_t* __restrict__ locs, uint32_t start_pack, const float* __restrict__ data,
+                                uint32_t n_locs, uint32_t pack, uint32_t* err) {
+    uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= (uint64_t)n_locs * pack) return;
+    uint32_t li = (uint32_t)(tid / pack), ei = (uint32_t)(tid % pack);
+    uint64_t e = (uint64_t)(locs ? locs[li] : start_pack + li) * pack + ei;
+    if (e >= n_elems) { atomicOr(err, DEVERR_OOB_MAP); return; }
+    uint64_t grp = e / group;
+    float scale = qp[grp * 2], zero = qp[grp * 2 + 1];
+    float qf = __fdiv_rn(__fsub_rn(data[tid], zero), fmaxf(scale, 1e-10f));
+    float q = fminf(fmaxf(rintf(qf), 0.f), 15.f);
+    if (!(qf == qf)) q = 0.f;
+    uint32_t qi = (uint32_t)q, sh = (uint32_t)(e & 7) * 4;
+    atomicAnd(&words[e >> 3], ~(0xFu << sh));
+    atomicOr(&words[e >> 3], qi << sh);
+}
+
+__global__ void k_gather_q4map(const uint32_t* __restrict__ words, uint64_t n_elems, const float* __restrict__ qp, uint32_t group,
+                               const uint32_t* __restrict__ locs, float* __restrict__ out, uint32_t n_locs, uint32_t pack, uint32_t* err) {
+    uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (tid >= (uint64_t)n_locs * pack) return;
+    uint32_t li = (uint32_t)(tid / pack), ei = (uint32_t)(tid % pack);
+    uint64_t e = (uint64_t)locs[li] * pack + ei;
+    if (e >= n_elems) { atomicOr(err, DEVERR_OOB_MAP); out[tid] = 0.f; return; }
+    uint32_t raw = (words[e >> 3] >> ((uint32_t)(e & 7) * 4)) & 0xFu;
+    uint64_t grp = e / group;
+    out[tid] = __fadd_rn(__fmul_rn((float)raw, qp[grp * 2]), qp[grp * 2 + 1]);
+}
+
+__global__ void k_interleave_qparams(float* __restrict__ qp, const float* __restrict__ s, const float* __restrict__ z, uint32_t n) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) { qp[2 * i] = s[i]; qp[2 * i + 1] = z[i]; }
+}
+
+// Raw 18-byte Q4_0 blocks -> quant plane (one uint4 per block) + scale plane.
+__global__ void k_repack_q4_0(const uint16_t* __restrict__ raw, uint4* __restrict__ qs, __half* __restrict__ d, uint64_t n_blocks) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_blocks) return;
+    const uint16_t* b = raw + i * 9;
+    uint16_t h[9];
+#pragma unroll
+    for (int k = 0; k < 9; ++k) h[k] = b[k];
+    d[i] = __ushort_as_half(h[0]);
+    uint4 q;
+    q.x = h[1] | ((uint32_t)h[2] << 16);
+    q.y = h[3] | ((uint32_t)h[4] << 16);
+    q.z = h[5] | ((uint32_t)h[6] << 16);
+    q.w = h[7] | ((uint32_t)h[8] << 16);
+    qs[i] = q;
+}
+
+// Bit-exact block decode (one rounding per product / difference; no FMA).
+__global__ void k_dequant_q4_0(const uint4* __restrict__ qs, const __half* __restrict__ d, uint64_t first_block,
+                               float* __restrict__ out, uint64_t n_blocks) {
+    uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    uint64_t blk = t >> 4;
+    uint32_t j = (uint32_t)(t & 15);
+    if (blk >= n_blocks) return;
+    const uint8_t* q = (const uint8_t*)(qs + first_block + blk);
+    float s = __half2float(d[first_block + blk]);
+    uint32_t byte = q[j];
+    out[blk * 32 + j]      = __fmul_rn((float)(int)(byte & 15) - 8.f, s);
+    out[blk * 32 + 16 + j] = __fmul_rn((float)(int)(byte >> 4) - 8.f, s);
+}
+
+__device__ __forceinline__ void q4k_scale_min(const uint8_t* rs, int j, int& sc, int& mn) {
+    if (j < 4) { sc = rs[j] & 63; mn = rs[j + 4] & 63; }
+    else       { sc = (rs[j + 4] & 0x0F) | ((rs[j - 4] >> 6) << 4); mn = (rs[j + 4] >> 4) | ((rs[j] >> 6) << 4); }
+}
+
+__global__ void k_dequant_q4_k(const uint8_t* __restrict__ raw, uint64_t first_sb, float* __restrict__ out, uint64_t n_sb) {
+    uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one thread per quant byte
+    uint64_t sb = t >> 7;
+    uint32_t b = (uint32_t)(t & 127);
+    if (sb >= n_sb) return;
+    const uint8_t* blk = raw + (first_sb + sb) * 144;
+    float d  = __half2float(__ushort_as_half(*(const uint16_t*)(blk)));
+    float dm = __half2float(__ushort_as_half(*(const uint16_t*)(blk + 2)));
+    int grp = b >> 5, j = b & 31, sc0, m0, sc1, m1;
+    q4k_scale_min(blk + 4, 2 * grp, sc0, m0);
+    q4k_scale_min(blk + 4, 2 * grp + 1, sc1, m1);
+    uint32_t byte = blk[16 + b];
+    float* o = out + sb * 256 + grp * 64;
+    o[j]      = __fsub_rn(__fmul_rn((float)(byte & 15), __fmul_rn(d, (float)sc0)), __fmul_rn(dm, (float)m0));
+    o[32 + j] = __fsub_rn(__fmul_rn((float)(byte >> 4), __fmul_rn(d, (float)sc1)), __fmul_rn(dm, (float)m1));
+}
+
+// ggml Q4_0 rule, one thread per block of 32 (see adam_b200/gguf_blocks.py).
+__global__ void k_quantize_q4_0(const float* __restrict__ w, uint64_t n_blocks, uint16_t* __restrict__ raw) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_blocks) return;
+    const float4* src = (const float4*)(w + i * 32);
+    float v[32];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { float4 f = src[k]; v[4*k] = f.x; v[4*k+1] = f.y; v[4*k+2] = f.z; v[4*k+3] = f.w; }
+    float amax = -1.f, vmax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) { float a = fabsf(v[k]); if (a > amax) { amax = a; vmax = v[k]; } }
+    float d = __fdiv_rn(vmax, -8.f);
+    float id = (d == 0.f) ? 0.f : __fdiv_rn(1.f, d);
+    uint32_t q[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        float t = truncf(__fadd_rn(__fmul_rn(v[k], id), 8.5f));
+        q[k] = (uint32_t)fminf(fmaxf(t, 0.f), 15.f);
+    }
+    uint16_t* o = raw + i * 9;
+    o[0] = __half_as_ushort(__float2half_rn(d));
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        uint32_t b0 = q[2*k] | (q[2*k + 16] << 4), b1 = q[2*k + 1] | (q[2*k + 17] << 4);
+        o[1 + k] = (uint16_t)(b0 | (b1 << 8));
+    }
+}
+
+static inline unsigned blocks_for(uint64_t n, unsigned t) { return (unsigned)((n + t - 1) / t); }
+
+}  // namespace ab
+
+using namespace ab;
+
+// ---- context ---------------------------------------------------------------
+
+extern "C" int adamah_init_ex(uint64_t, uint64_t) {
+    if (g.inited) return ADAMAH_OK;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) return fail(ADAMAH_ERR_BACKEND, "no CUDA device: %s", cudaGetErrorString(e));
+    int dev = 0;
+    if (const char* s = getenv("ADAM_B200_DEVICE")) dev = atoi(s);
+    else if (const char* s2 = getenv("LOCAL_RANK")) dev = atoi(s2) % n;
+    CU(cudaSetDevice(dev));
+    cudaDeviceProp p;
+    CU(cudaGetDeviceProperties(&p, dev));
+    memset(&g, 0, sizeof g);
+    g.device = dev;
+    g.sm_count = p.multiProcessorCount;
+    g.total_mem = p.totalGlobalMem;
+    CU(cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking));
+    g.handles = (Handle*)calloc(MAX_HANDLES, sizeof(Handle));
+    if (!g.handles) return fail(ADAMAH_ERR_MEMORY, "out of host memory");
+    CU(cudaMalloc(&g.dev_err, sizeof(uint32_t)));
+    CU(cudaMemset(g.dev_err, 0, sizeof(uint32_t)));
+    g.handle_cursor = 1;
+    g.active_dtype = ADAMAH_DTYPE_F32;
+    g.sched_mode = 2;
+    g.inited = true;
+    return ADAMAH_OK;
+}
+extern "C" int adamah_init(void) { return adamah_init_ex(0, 0); }
+
+namespace ab { void decoder_destroy_all(); void plans_clear_all(); }
+
+extern "C" void adamah_shutdown(void) {
+    if (!g.inited) return;
+    cudaSetDevice(g.device);
+    cudaStreamSynchronize(g.stream);
+    decoder_destroy_all();
+    plans_clear_all();
+    for (uint32_t i = 0; i < MAX_MAPS; ++i) if (g.maps[i].used) { cudaFree(g.maps[i].buf); cudaFree(g.maps[i].qparams); }
+    for (uint32_t i = 0; i < MAX_HANDLES; ++i) if (g.handles[i].used) { cudaFree(g.handles[i].dev); free(g.handles[i].shadow); }
+    free(g.handles);
+    cudaFree(g.dev_err);
+    cudaStreamDestroy(g.stream);
+    memset(&g, 0, sizeof g);
+}
+
+extern "C" void adamah_sync(void) { if (g.inited) cudaStreamSynchronize(g.stream); }
+extern "C" void adamah_synchronize(uint64_t) { adamah_sync(); }
+extern "C" void adamah_synchronize_all(void) { adamah_sync(); }
+
+extern "C" const char* adam_b200_last_error(void) { return g_err; }
+extern "C" int adam_b200_device_info(int* device, int* sm_count, uint64_t* total_mem) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    if (device) *device = g.device;
+    if (sm_count) *sm_count = g.sm_count;
+    if (total_mem) *total_mem = g.total_mem;
+    return ADAMAH_OK;
+}
+extern "C" uint64_t adam_b200_kernel_launches(void) { return g.launches; }
+// Reads and clears the device error word (bits: 1 = a loc fell outside its map,
+// 2 = a bounded device wait ran out, 4 = bad token id).
+extern "C" uint32_t adam_b200_device_error(void) {
+    if (!g.inited) return 0;
+    uint32_t v = 0;
+    cudaMemcpyAsync(&v, g.dev_err, 4, cudaMemcpyDeviceToHost, g.stream);
+    cudaStreamSynchronize(g.stream);
+    if (v) cudaMemsetAsync(g.dev_err, 0, 4, g.stream);
+    return v;
+}
+
+extern "C" int adamah_set_dtype(uint32_t dtype) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    if (dtype != ADAMAH_DTYPE_F32 && dtype != ADAMAH_DTYPE_Q4 && dtype != ADAMAH_DTYPE_GGUF_Q4_0 && dtype != ADAMAH_DTYPE_GGUF_Q4_K)
+        return fail(ADAMAH_ERR_INVALID, "dtype %u is not on the decode path (f32, q4 and GGUF block maps only)", dtype);
+    g.active_dtype = dtype;
+    return ADAMAH_OK;
+}
+extern "C" uint32_t adamah_get_dtype(void) { return g.active_dtype; }
+
+// ---- maps ------------------------------------------------------------------
+
+extern "C" int map_destroy(uint32_t id) {
+    Map* m = get_map(id);
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    cudaStreamSynchronize(g.stream);
+    cudaFree(m->buf);
+    cudaFree(m->qparams);
+    memset(m, 0, sizeof *m);
+    return ADAMAH_OK;
+}
+
+extern "C" int map_init_dtype(uint32_t id, uint32_t dtype, uint32_t pack_size, uint32_t n_packs, uint32_t group_size) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    if (id >= MAX_MAPS) return fail(ADAMAH_ERR_INVALID, "map id %u out of range (max %u)", id, MAX_MAPS - 1);
+    if (pack_size == 0 || n_packs == 0) return fail(ADAMAH_ERR_INVALID, "map %u: empty shape", id);
+    if (g.maps[id].used) map_destroy(id);
+    Map m = {};
+    m.dtype = dtype; m.pack_size = pack_size; m.n_packs = n_packs;
+    m.n_elems = (uint64_t)pack_size * n_packs;
+    m.word_size = 4;
+    switch (dtype) {
+    case ADAMAH_DTYPE_F32: m.bytes = m.n_elems * 4; break;
+    case ADAMAH_DTYPE_Q4:
+        if (group_size == 0) group_size = 32;
+        m.group_size = group_size;
+        m.bytes = (m.n_elems + 7) / 8 * 4;
+        m.n_groups = (uint32_t)((m.n_elems + group_size - 1) / group_size);
+        break;
+    case ADAMAH_DTYPE_GGUF_Q4_0:
+        if (m.n_elems % 32) return fail(ADAMAH_ERR_INVALID, "Q4_0 map size must be a multiple of 32");
+        m.bytes = m.n_elems / 32 * 18; break;
+    case ADAMAH_DTYPE_GGUF_Q4_K:
+        if (m.n_elems % 256) return fail(ADAMAH_ERR_INVALID, "Q4_K map size must be a multiple of 256");
+        m.bytes = m.n_elems / 256 * 144; break;
+    default: return fail(ADAMAH_ERR_INVALID, "dtype %u is not on the decode path", dtype);
+    }
+    size_t alloc = (m.bytes + 255) & ~(size_t)255;
+    CU(cudaMalloc(&m.buf, alloc));
+    CU(cudaMemsetAsync(m.buf, 0, alloc, g.stream));
+    if (dtype == ADAMAH_DTYPE_Q4) {
+        CU(cudaMalloc((void**)&m.qparams, (size_t)m.n_groups * 8));
+        CU(cudaMemsetAsync(m.qparams, 0, (size_t)m.n_groups * 8, g.stream));
+    }
+    if (dtype == ADAMAH_DTYPE_GGUF_Q4_0) {
+        m.q40_qs = (uint4*)m.buf;
+        m.q40_d = (__half*)((char*)m.buf + m.n_elems / 32 * 16);
+    }
+    m.used = true;
+    g.maps[id] = m;
+    CU(cudaStreamSynchronize(g.stream));
+    return ADAMAH_OK;
+}
+
+extern "C" int map_init(uint32_t id, uint32_t word_size, uint32_t pack_size, uint32_t n_packs) {
+    if (word_size != 0 && word_size != 4 && g.active_dtype == ADAMAH_DTYPE_F32)
+        return fail(ADAMAH_ERR_INVALID, "word_size %u unsupported (float32 maps only)", word_size);
+    return map_init_dtype(id, g.active_dtype, pack_size, n_packs, 32);
+}
+
+extern "C" uint32_t map_size(uint32_t id) { Map* m = get_map(id); return m ? m->n_packs : 0; }
+extern "C" uint32_t map_get_dtype(uint32_t id) { Map* m = get_map(id); return m ? m->dtype : 0xFFFFFFFFu; }
+
+extern "C" int map_set_qparams(uint32_t id, const float* scales, const float* zeros, uint32_t n_groups) {
+    Map* m = get_map(id);
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (m->dtype != ADAMAH_DTYPE_Q4) return fail(ADAMAH_ERR_INVALID, "map %u is not a Q4 map", id);
+    if (!scales || !zeros || n_groups == 0 || n_groups > m->n_groups) return fail(ADAMAH_ERR_INVALID, "map_set_qparams: bad group count %u (map has %u)", n_groups, m->n_groups);
+    float* tmp = nullptr;
+    CU(cudaMallocAsync((void**)&tmp, (size_t)n_groups * 8, g.stream));
+    CU(cudaMemcpyAsync(tmp, scales, (size_t)n_groups * 4, cudaMemcpyHostToDevice, g.stream));
+    CU(cudaMemcpyAsync(tmp + n_groups, zeros, (size_t)n_groups * 4, cudaMemcpyHostToDevice, g.stream));
+    k_interleave_qparams<<<blocks_for(n_groups, 256), 256, 0, g.stream>>>(m->qparams, tmp, tmp + n_groups, n_groups);
+    count_launch();
+    CU(cudaFreeAsync(tmp, g.stream));
+    end_of_op();
+    return check_launch("map_set_qparams");
+}
+
+namespace ab { bool capturing(); }
+#define NO_CAPTURE(name) if (capturing()) return fail(ADAMAH_ERR_INVALID, name ": host I/O is not allowed while a graph is being captured")
+
+static int scatter_impl(uint32_t id, const uint32_t* locs, uint32_t start_pack, const void* data, uint32_t n_locs) {
+    Map* m = get_map(id);
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    NO_CAPTURE("map_scatter");
+    if (n_locs == 0) return ADAMAH_OK;
+    if (!data) return fail(ADAMAH_ERR_INVALID, "scatter: null data");
+    if (m->dtype != ADAMAH_DTYPE_F32 && m->dtype != ADAMAH_DTYPE_Q4)
+        return fail(ADAMAH_ERR_INVALID, "scatter: map %u holds GGUF blocks; use map_upload_gguf_blocks", id);
+    uint64_t n = (uint64_t)n_locs * m->pack_size;
+    if (!locs && (uint64_t)start_pack + n_locs > m->n_packs) return fail(ADAMAH_ERR_INVALID, "scatter: range beyond map %u", id);
+    if (!locs && m->dtype == ADAMAH_DTYPE_F32) {      // contiguous float copy needs no kernel
+        CU(cudaMemcpyAsync((float*)m->buf + (uint64_t)start_pack * m->pack_size, data, n * 4, cudaMemcpyHostToDevice, g.stream));
+        end_of_op();
+        return ADAMAH_OK;
+    }
+    float* d_data = nullptr; uint32_t* d_locs = nullptr;
+    CU(cudaMallocAsync((void**)&d_data, n * 4, g.stream));
+    CU(cudaMemcpyAsync(d_data, data, n * 4, cudaMemcpyHostToDevice, g.stream));
+    if (locs) {
+        CU(cudaMallocAsync((void**)&d_locs, (size_t)n_locs * 4, g.stream));
+        CU(cudaMemcpyAsync(d_locs, locs, (size_t)n_locs * 4, cudaMemcpyHostToDevice, g.stream));
+    }
+    if (m->dtype == ADAMAH_DTYPE_F32)
+        k_scatter_f32<<<blocks_for(n, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, d_locs, start_pack, d_data, n_locs, m->pack_size, g.dev_err);
+    else
+        k_scatter_q4map<<<blocks_for(n, 256), 256, 0, g.stream>>>((uint32_t*)m->buf, m->n_elems, m->qparams, m->group_size, d_locs, start_pack, d_data, n_locs, m->pack_size, g.dev_err);
+    count_launch();
+    CU(cudaFreeAsync(d_data, g.stream));
+    if (d_locs) CU(cudaFreeAsync(d_locs, g.stream));
+    end_of_op();
+    return check_launch("map_scatter");
+}
+
+extern "C" int map_scatter(uint32_t id, const uint32_t* locs, const void* data, uint32_t n_locs) {
+    if (!locs && n_locs) return fail(ADAMAH_ERR_INVALID, "map_scatter: null locs");
+    return scatter_impl(id, locs, 0, data, n_locs);
+}
+extern "C" int map_scatter_contiguous(uint32_t id, uint32_t start_pack, const void* data, uint32_t n_locs) {
+    return scatter_impl(id, nullptr, start_pack, data, n_locs);
+}
+
+extern "C" int map_scatter_q4_packed_contiguous(uint32_t id, uint32_t start_pack, const void* packed, uint32_t n_locs) {
+    Map* m = get_map(id);
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (m->dtype != ADAMAH_DTYPE_Q4 || m->pack_size != 1) return fail(ADAMAH_ERR_INVALID, "map %u is not a Q4 map with pack_size 1", id);
+    if ((start_pack & 1) || (n_locs & 1)) return fail(ADAMAH_ERR_INVALID, "packed Q4 scatter needs an even start and count");
+    if ((uint64_t)start_pack + n_locs > m->n_elems) return fail(ADAMAH_ERR_INVALID, "packed Q4 scatter beyond map %u", id);
+    if (n_locs == 0) return ADAMAH_OK;
+    CU(cudaMemcpyAsync((uint8_t*)m->buf + start_pack / 2, packed, n_locs / 2, cudaMemcpyHostToDevice, g.stream));
+    end_of_op();
+    return ADAMAH_OK;
+}
+
+extern "C" int map_gather(uint32_t id, const uint32_t* locs, void* out, uint32_t n_locs) {
+    Map* m = get_map(id);
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (n_locs == 0) return ADAMAH_OK;
+    NO_CAPTURE("map_gather");
+    if (!locs || !out) return fail(ADAMAH_ERR_INVALID, "map_gather: null pointer");
+    if (m->dtype != ADAMAH_DTYPE_F32 && m->dtype != ADAMAH_DTYPE_Q4)
+        return fail(ADAMAH_ERR_INVALID, "gather: map %u holds GGUF blocks; use map_dequant_gguf", id);
+    uint64_t n = (uint64_t)n_locs * m->pack_size;
+    float* d_out = nullptr; uint32_t* d_locs = nullptr;
+    CU(cudaMallocAsync((void**)&d_out, n * 4, g.stream));
+    CU(cudaMallocAsync((void**)&d_locs, (size_t)n_locs * 4, g.stream));
+    CU(cudaMemcpyAsync(d_locs, locs, (size_t)n_locs * 4, cudaMemcpyHostToDevice, g.stream));
+    if (m->dtype == ADAMAH_DTYPE_F32)
+        k_gather_f32<<<blocks_for(n, 256), 256, 0, g.stream>>>((const float*)m->buf, m->n_elems, d_locs, d_out, n_locs, m->pack_size, g.dev_err);
+    else
+        k_gather_q4map<<<blocks_for(n, 256), 256, 0, g.stream>>>((const uint32_t*)m->buf, m->n_elems, m->qparams, m->group_size, d_locs, d_out, n_locs, m->pack_size, g.dev_err);
+    count_launch();
+    CU(cudaMemcpyAsync(out, d_out, n * 4, cudaMemcpyDeviceToHost, g.stream));
+    CU(cudaFreeAsync(d_out, g.stream));
+    CU(cudaFreeAsync(d_locs, g.stream));
+    CU(cudaStreamSynchronize(g.stream));      // the caller reads `out` on return
+    return check_launch("map_gather");
+}
+
+// ---- loc handles -----------------------------------------------------------
+
+namespace ab {
+uint32_t handle_alloc(uint32_t n_bytes) {
+    for (uint32_t k = 0; k < MAX_HANDLES - 1; ++k) {
+        uint32_t h = g.handle_cursor;
+        g.handle_cursor = (g.handle_cursor + 1 >= MAX_HANDLES) ? 1 : g.handle_cursor + 1;
+        if (!g.handles[h].used) {
+            void* p = nullptr;
+            size_t alloc = ((size_t)n_bytes + 15) & ~(size_t)15;
+            if (cudaMalloc(&p, alloc) != cudaSuccess) { fail(ADAMAH_ERR_MEMORY, "out of device memory for a loc handle"); return 0; }
+            g.handles[h].dev = p; g.handles[h].nbytes = n_bytes; g.handles[h].used = true; g.handles[h].shadow = nullptr;
+            return h;
+        }
+    }
+    fail(ADAMAH_ERR_MEMORY, "loc-handle table full");
+    return 0;
+}
+
+bool hfirst(uint32_t h, uint32_t* out) {
+    if (!handle_ok(h, 4)) return false;
+    if (g.handles[h].shadow) { *out = g.handles[h].shadow[0]; return true; }
+    if (cudaMemcpyAsync(out, g.handles[h].dev, 4, cudaMemcpyDeviceToHost, g.stream) != cudaSuccess ||
+        cudaStreamSynchronize(g.stream) != cudaSuccess) { fail(ADAMAH_ERR_BACKEND, "cannot read loc handle %u", h); return false; }
+    return true;
+}
+}
+
+extern "C" uint64_t map_upload_dev(uint32_t handle, const void* data, uint32_t n_bytes) {
+    if (!ready() || !data || n_bytes == 0) { fail(ADAMAH_ERR_INVALID, "map_upload_dev: bad arguments"); return 0; }
+    if (handle == 0) {
+        handle = handle_alloc(n_bytes);
+        if (!handle) return 0;
+    } else {
+        if (!handle_ok(handle, 0)) return 0;
+        if (g.handles[handle].nbytes != n_bytes) {          // adamah.c:3601-3608: same size required
+            fail(ADAMAH_ERR_INVALID, "map_upload_dev: handle %u holds %u bytes, got %u", handle, g.handles[handle].nbytes, n_bytes);
+            return 0;
+        }
+    }
+    if (cudaMemcpyAsync(g.handles[handle].dev, data, n_bytes, cudaMemcpyHostToDevice, g.stream) != cudaSuccess) {
+        fail(ADAMAH_ERR_BACKEND, "map_upload_dev: copy failed");
+        return 0;
+    }
+    if (!g.handles[handle].shadow) g.handles[handle].shadow = (uint32_t*)malloc(((size_t)n_bytes + 3) & ~(size_t)3);
+    if (g.handles[handle].shadow) memcpy(g.handles[handle].shadow, data, n_bytes);
+    end_of_op();
+    return (uint64_t)handle | (++g.ticket << 32);
+}
+
+extern "C" int map_download_dev(uint32_t handle, void* out, uint32_t n_bytes) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    if (!out) return fail(ADAMAH_ERR_INVALID, "map_download_dev: null pointer");
+    if (!handle_ok(handle, n_bytes)) return ADAMAH_ERR_NOT_FOUND;
+    CU(cudaMemcpyAsync(out, g.handles[handle].dev, n_bytes, cudaMemcpyDeviceToHost, g.stream));
+    CU(cudaStreamSynchronize(g.stream));
+    return ADAMAH_OK;
+}
+
+// Free a loc handle (extension; the reference evicts instead).
+extern "C" int adam_b200_handle_free(uint32_t handle) {
+    if (!ready() || !handle_ok(handle, 0)) return ADAMAH_ERR_NOT_FOUND;
+    cudaStreamSynchronize(g.stream);
+    cudaFree(g.handles[handle].dev);
+    free(g.handles[handle].shadow);
+    g.handles[handle] = Handle{};
+    return ADAMAH_OK;
+}
+
+extern "C" uint64_t map_gather_dev(uint32_t id, uint32_t locs_h, uint32_t n_locs) {
+    Map* m = get_map(id);
+    if (!m || n_locs == 0) return 0;
+    if (m->dtype != ADAMAH_DTYPE_F32 && m->dtype != ADAMAH_DTYPE_Q4) { fail(ADAMAH_ERR_INVALID, "map_gather_dev: unsupported map type"); return 0; }
+    if (!handle_ok(locs_h, n_locs * 4)) return 0;
+    uint64_t n = (uint64_t)n_locs * m->pack_size;
+    uint32_t dst = handle_alloc((uint32_t)(n * 4));
+    if (!dst) return 0;
+    if (m->dtype == ADAMAH_DTYPE_F32)
+        k_gather_f32<<<blocks_for(n, 256), 256, 0, g.stream>>>((const float*)m->buf, m->n_elems, hlocs(locs_h), hdata(dst), n_locs, m->pack_size, g.dev_err);
+    else
+        k_gather_q4map<<<blocks_for(n, 256), 256, 0, g.stream>>>((const uint32_t*)m->buf, m->n_elems, m->qparams, m->group_size, hlocs(locs_h), hdata(dst), n_locs, m->pack_size, g.dev_err);
+    count_launch();
+    if (check_launch("map_gather_dev") != ADAMAH_OK) return 0;
+    end_of_op();
+    return (uint64_t)dst | (++g.ticket << 32);
+}
+
+extern "C" uint64_t map_scatter_dev(uint32_t id, uint32_t locs_h, uint32_t n_locs, uint32_t src_h) {
+    Map* m = get_map(id);
+    if (!m || n_locs == 0) return 0;
+    if (m->dtype != ADAMAH_DTYPE_F32 && m->dtype != ADAMAH_DTYPE_Q4) { fail(ADAMAH_ERR_INVALID, "map_scatter_dev: unsupported map type"); return 0; }
+    uint64_t n = (uint64_t)n_locs * m->pack_size;
+    if (!handle_ok(locs_h, n_locs * 4) || !handle_ok(src_h, (uint32_t)(n * 4))) return 0;
+    if (m->dtype == ADAMAH_DTYPE_F32)
+        k_scatter_f32<<<blocks_for(n, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(locs_h), 0, hdata(src_h), n_locs, m->pack_size, g.dev_err);
+    else
+        k_scatter_q4map<<<blocks_for(n, 256), 256, 0, g.stream>>>((uint32_t*)m->buf, m->n_elems, m->qparams, m->group_size, hlocs(locs_h), 0, hdata(src_h), n_locs, m->pack_size, g.dev_err);
+    count_launch();
+    if (check_launch("map_scatter_dev") != ADAMAH_OK) return 0;
+    end_of_op();
+    return ++g.ticket;
+}
+
+// ---- batching, fusion state, counters --------------------------------------
+
+extern "C" void batch_begin(void) { if (g.inited) g.batch_depth++; }
+extern "C" void batch_end(void) {
+    if (!g.inited || g.batch_depth == 0) return;
+    if (--g.batch_depth == 0) { cudaStreamSynchronize(g.stream); g.submits++; }
+}
+
+extern "C" void adamah_fusion_enable(int e) { g.fusion_enabled = e ? 1 : 0; }
+extern "C" int  adamah_fusion_is_enabled(void) { return g.fusion_enabled; }
+extern "C" int  adamah_fusion_flush(void) { g.flushes++; return ADAMAH_OK; }
+extern "C" void adamah_fusion_set_scheduler_mode(int m) { if (m >= 0 && m <= 2) g.sched_mode = m; }
+extern "C" int  adamah_fusion_get_scheduler_mode(void) { return g.sched_mode; }
+extern "C" int  adamah_register_loc_span(uint32_t h, uint32_t map_id, uint32_t, uint32_t) {
+    if (!ready() || !handle_ok(h, 0) || !get_map(map_id)) return ADAMAH_ERR_NOT_FOUND;
+    return ADAMAH_OK;
+}
+extern "C" int  adamah_register_row_base_span(uint32_t h, uint32_t map_id, uint32_t, uint32_t, uint32_t, uint32_t) {
+    if (!ready() || !handle_ok(h, 0) || !get_map(map_id)) return ADAMAH_ERR_NOT_FOUND;
+    return ADAMAH_OK;
+}
+extern "C" int  adamah_clear_loc_alias_meta(uint32_t) { return ADAMAH_OK; }
+
+extern "C" void adamah_stats_reset(void) { g.launches = g.submits = g.flushes = 0; }
+extern "C" void adamah_stats_get(uint64_t* dispatch, uint64_t* submit, uint64_t* barrier, uint64_t* flush,
+                                 uint64_t* ds_upd, uint64_t* ds_hit, uint64_t* ds_miss, uint64_t* alias, uint64_t* mode) {
+    if (dispatch) *dispatch = g.launches;
+    if (submit) *submit = g.submits;
+    if (barrier) *barrier = 0;           // an in-order stream needs no explicit barriers
+    if (flush) *flush = g.flushes;
+    if (ds_upd) *ds_upd = 0;
+    if (ds_hit) *ds_hit = 0;
+    if (ds_miss) *ds_miss = 0;
+    if (alias) *alias = 0;
+    if (mode) *mode = (uint64_t)g.sched_mode;
+}
+
+// ---- GGUF block maps -------------------------------------------------------
+
+extern "C" int map_upload_gguf_blocks(uint32_t id, uint32_t ggml_type, uint64_t elem_off, const void* raw, uint64_t n_bytes) {
+    Map* m = get_map(id);
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (!raw || n_bytes == 0) return fail(ADAMAH_ERR_INVALID, "map_upload_gguf_blocks: empty input");
+    if (ggml_type == 2 && m->dtype == ADAMAH_DTYPE_GGUF_Q4_0) {
+        if (elem_off % 32 || n_bytes % 18) return fail(ADAMAH_ERR_INVALID, "Q4_0 upload must cover whole 18-byte blocks");
+        uint64_t nb = n_bytes / 18, b0 = elem_off / 32;
+        if (elem_off + nb * 32 > m->n_elems) return fail(ADAMAH_ERR_INVALID, "Q4_0 upload beyond map %u", id);
+        cudaPointerAttributes at;
+        bool on_dev = cudaPointerGetAttributes(&at, raw) == cudaSuccess && at.type == cudaMemoryTypeDevice;
+        cudaGetLastError();
+        const uint16_t* src = (const uint16_t*)raw;
+        void* tmp = nullptr;
+        if (!on_dev) {
+            CU(cudaMallocAsync(&tmp, n_bytes, g.stream));
+            CU(cudaMemcpyAsync(tmp, raw, n_bytes, cudaMemcpyHostToDevice, g.stream));
+            src = (const uint16_t*)tmp;
+        } else if ((uintptr_t)raw & 1) return fail(ADAMAH_ERR_INVALID, "device Q4_0 source must be 2-byte aligned");
+        k_repack_q4_0<<<blocks_for(nb, 256), 256, 0, g.stream>>>(src, m->q40_qs + b0, m->q40_d + b0, nb);
+        count_launch();
+        if (tmp) CU(cudaFreeAsync(tmp, g.stream));
+        CU(cudaStreamSynchronize(g.stream));
+        return check_launch("map_upload_gguf_blocks");
+    }
+    if (ggml_type == 12 && m->dtype == ADAMAH_DTYPE_GGUF_Q4_K) {
+        if (elem_off % 256 || n_bytes % 144) return fail(ADAMAH_ERR_INVALID, "Q4_K upload must cover whole 144-byte superblocks");
+        uint64_t nsb = n_bytes / 144;
+        if (elem_off + nsb * 256 > m->n_elems) return fail(ADAMAH_ERR_INVALID, "Q4_K upload beyond map %u", id);
+        CU(cudaMemcpyAsync((uint8_t*)m->buf + elem_off / 256 * 144, raw, n_bytes, cudaMemcpyDefault, g.stream));
+        CU(cudaStreamSynchronize(g.stream));
+        return ADAMAH_OK;
+    }
+    return fail(ADAMAH_ERR_INVALID, "ggml type %u does not match the storage of map %u", ggml_type, id);
+}
+
+extern "C" int map_dequant_gguf(uint32_t id, uint64_t elem_off, float* out, uint64_t n_elems) {
+    Map* m = get_map(id);
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (!out || n_elems == 0) return fail(ADAMAH_ERR_INVALID, "map_dequant_gguf: empty output");
+    if (elem_off + n_elems > m->n_elems) return fail(ADAMAH_ERR_INVALID, "map_dequant_gguf: range beyond map %u", id);
+    float* tmp = nullptr;
+    if (m->dtype == ADAMAH_DTYPE_GGUF_Q4_0) {
+        if (elem_off % 32 || n_elems % 32) return fail(ADAMAH_ERR_INVALID, "Q4_0 decode must cover whole blocks");
+        CU(cudaMallocAsync((void**)&tmp, n_elems * 4, g.stream));
+        k_dequant_q4_0<<<blocks_for(n_elems / 2, 256), 256, 0, g.stream>>>(m->q40_qs, m->q40_d, elem_off / 32, tmp, n_elems / 32);
+    } else if (m->dtype == ADAMAH_DTYPE_GGUF_Q4_K) {
+        if (elem_off % 256 || n_elems % 256) return fail(ADAMAH_ERR_INVALID, "Q4_K decode must cover whole superblocks");
+        CU(cudaMallocAsync((void**)&tmp, n_elems * 4, g.stream));
+        k_dequant_q4_k<<<blocks_for(n_elems / 2, 256), 256, 0, g.stream>>>((const uint8_t*)m->buf, elem_off / 256, tmp, n_elems / 256);
+    } else return fail(ADAMAH_ERR_INVALID, "map %u does not hold GGUF blocks", id);
+    count_launch();
+    CU(cudaMemcpyAsync(out, tmp, n_elems * 4, cudaMemcpyDeviceToHost, g.stream));
+    CU(cudaFreeAsync(tmp, g.stream));
+    CU(cudaStreamSynchronize(g.stream));
+    return check_launch("map_dequant_gguf");
+}
+
+extern "C" int adam_b200_quantize_q4_0_dev(const float* w_dev, uint64_t n_elems, void* raw_dev) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    if (!w_dev || !raw_dev || n_elems % 32 || ((uintptr_t)w_dev & 15) || ((uintptr_t)raw_dev & 1))
+        return fail(ADAMAH_ERR_INVALID, "quantize_q4_0: need whole blocks, 16-byte aligned input, 2-byte aligned output");
+    // The caller's tensors live on its own stream: order after all prior work.
+    CU(cudaDeviceSynchronize());
+    k_quantize_q4_0<<<blocks_for(n_elems / 32, 128), 128, 0, g.stream>>>(w_dev, n_elems / 32, (uint16_t*)raw_dev);
+    count_launch();
+    CU(cudaStreamSynchronize(g.stream));
+    return check_launch("quantize_q4_0");
+}
+
+// ---- device timers and captured graphs (extension) ----------------------------
+//
+// Timers bracket work on the context stream with CUDA events.  A captured graph
+// records the operator calls made between capture_begin and capture_end (no host
+// I/O is allowed in between) and replays them with one launch each time.
+
+namespace ab {
+constexpr uint32_t MAX_GRAPHS = 64;
+struct GraphSlot { cudaGraphExec_t exec; cudaGraph_t graph; uint64_t kernels; bool used; };
+static GraphSlot g_graphs[MAX_GRAPHS];
+static cudaEvent_t g_ev0 = nullptr, g_ev1 = nullptr;
+static bool g_capturing = false;
+static uint64_t g_capture_launch0 = 0;
+bool capturing() { return g_capturing; }
+}
+
+extern "C" int adam_b200_timer_begin(void) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    if (!g_ev0) { CU(cudaEventCreate(&g_ev0)); CU(cudaEventCreate(&g_ev1)); }
+    CU(cudaEventRecord(g_ev0, g.stream));
+    return ADAMAH_OK;
+}
+extern "C" int adam_b200_timer_end(float* ms) {
+    if (!ready() || !g_ev0 || !ms) return fail(ADAMAH_ERR_INVALID, "timer_end without timer_begin");
+    CU(cudaEventRecord(g_ev1, g.stream));
+    CU(cudaEventSynchronize(g_ev1));
+    CU(cudaEventElapsedTime(ms, g_ev0, g_ev1));
+    return ADAMAH_OK;
+}
+
+extern "C" int adam_b200_capture_begin(void) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    if (g_capturing) return fail(ADAMAH_ERR_INVALID, "a capture is already open");
+    CU(cudaStreamSynchronize(g.stream));
+    CU(cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeThreadLocal));
+    g_capturing = true;
+    g_capture_launch0 = g.launches;
+    g.batch_depth++;                 // ops must not synchronise while capturing
+    return ADAMAH_OK;
+}
+extern "C" int adam_b200_capture_end(uint32_t* graph_id) {
+    if (!ready() || !g_capturing || !graph_id) return fail(ADAMAH_ERR_INVALID, "capture_end without capture_begin");
+    g_capturing = false;
+    g.batch_depth--;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(g.stream, &graph);
+    if (e != cudaSuccess || !graph) return cuda_fail(e, "cudaStreamEndCapture");
+    uint32_t id = MAX_GRAPHS;
+    for (uint32_t i = 0; i < MAX_GRAPHS; ++i) if (!g_graphs[i].used) { id = i; break; }
+    if (id == MAX_GRAPHS) { cudaGraphDestroy(graph); return fail(ADAMAH_ERR_MEMORY, "graph table full"); }
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    if (e != cudaSuccess) { cudaGraphDestroy(graph); return cuda_fail(e, "cudaGraphInstantiate"); }
+    g_graphs[id] = GraphSlot{exec, graph, g.launches - g_capture_launch0, true};
+    g.launches = g_capture_launch0;  // captured kernels have not run yet
+    *graph_id = id;
+    return ADAMAH_OK;
+}
+extern "C" int adam_b200_graph_launch(uint32_t graph_id, uint32_t times) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    if (graph_id >= MAX_GRAPHS || !g_graphs[graph_id].used) return fail(ADAMAH_ERR_NOT_FOUND, "graph %u does not exist", graph_id);
+    for (uint32_t i = 0; i < times; ++i) CU(cudaGraphLaunch(g_graphs[graph_id].exec, g.stream));
+    count_launch(g_graphs[graph_id].kernels * times);
+    end_of_op();
+    return ADAMAH_OK;
+}
+extern "C" int adam_b200_graph_destroy(uint32_t graph_id) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    if (graph_id >= MAX_GRAPHS || !g_graphs[graph_id].used) return fail(ADAMAH_ERR_NOT_FOUND, "graph %u does not exist", graph_id);
+    cudaStreamSynchronize(g.stream);
+    cudaGraphExecDestroy(g_graphs[graph_id].exec);
+    cudaGraphDestroy(g_graphs[graph_id].graph);
+    g_graphs[graph_id] = GraphSlot{};
+    return ADAMAH_OK;
+}

@@ -1,0 +1,229 @@
+/*
+ * adam_b200.h -- C ABI of libadam_b200.so, a CUDA (sm_100a) backend for ADAM's
+ * quantized decode path.
+ *
+ * Part 1 keeps the symbol names, argument order and status codes of the
+ * reference's native backend (adamah-MAIN/adamah/adamah.c) for the operators on
+ * the decode path, so the reference's ctypes binding
+ * (adamah-MAIN/adamah/__init__.py:_setup_ctypes, :527-1103) resolves them
+ * unchanged.  Every declaration cites the reference definition it replaces.
+ *
+ * Part 2 holds additive extensions (prefix adam_b200_ or a new map_ name): maps
+ * that keep weights as native GGUF blocks, and a fused decoder that runs a whole
+ * token as one CUDA graph.
+ *
+ * Conventions (same as the reference): one global context per process, calls
+ * come from one thread; a "map" is a flat typed device array addressed by
+ * element (pack) index; a "loc handle" is the id of a small device array of
+ * uint32 element indices (or of raw float data); functions returning int give 0
+ * on success and a negative ADAMAH_ERR_* code otherwise; host buffers are read
+ * or written before the call returns and stay owned by the caller.
+ * All pointers are host pointers unless a parameter says otherwise.
+ */
+#ifndef ADAM_B200_H
+#define ADAM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes: adamah.c:23-28 --------------------------------------- */
+#define ADAMAH_OK             0
+#define ADAMAH_ERR_BACKEND   -1   /* reference name: ADAMAH_ERR_VULKAN */
+#define ADAMAH_ERR_MEMORY    -2
+#define ADAMAH_ERR_INVALID   -3
+#define ADAMAH_ERR_NOT_FOUND -4
+
+/* ---- map element types: adamah.c:2698-2824 (DTYPE_*) ---------------------- */
+#define ADAMAH_DTYPE_F32       0
+#define ADAMAH_DTYPE_Q4        3    /* nibbles, 8 per uint32, + f32 (scale,zero) per group */
+#define ADAMAH_DTYPE_GGUF_Q4_0 16   /* extension: 18-byte GGUF blocks of 32 */
+#define ADAMAH_DTYPE_GGUF_Q4_K 17   /* extension: 144-byte GGUF superblocks of 256 */
+
+/* ======================= Part 1: reference-compatible ====================== */
+
+/* context: adamah.c:2503 adamah_init, :1975 adamah_init_ex, :2596, :1820 */
+int      adamah_init(void);
+int      adamah_init_ex(uint64_t hot_pool_bytes, uint64_t cold_pool_bytes);
+void     adamah_shutdown(void);
+void     adamah_sync(void);
+void     adamah_synchronize(uint64_t ticket);          /* adamah.c: adamah_synchronize */
+void     adamah_synchronize_all(void);
+
+/* active dtype for map_init: adamah.c:4585, :4614 */
+int      adamah_set_dtype(uint32_t dtype);
+uint32_t adamah_get_dtype(void);
+
+/* maps: adamah.c:2686 map_init, :2698 map_init_dtype, :2826 map_destroy, map_size */
+int      map_init(uint32_t id, uint32_t word_size, uint32_t pack_size, uint32_t n_packs);
+int      map_init_dtype(uint32_t id, uint32_t dtype, uint32_t pack_size, uint32_t n_packs, uint32_t group_size);
+int      map_destroy(uint32_t id);
+uint32_t map_size(uint32_t id);
+uint32_t map_get_dtype(uint32_t id);
+/* adamah.c:4621 -- per-group (scale, zero) of a Q4 map */
+int      map_set_qparams(uint32_t id, const float* scales, const float* zeros, uint32_t n_groups);
+
+/* host <-> map: adamah.c:3087, :2896, :3035, :3374 */
+int      map_scatter(uint32_t id, const uint32_t* locs, const void* data, uint32_t n_locs);
+int      map_scatter_contiguous(uint32_t id, uint32_t start_pack, const void* data, uint32_t n_locs);
+int      map_scatter_q4_packed_contiguous(uint32_t id, uint32_t start_pack, const void* packed_u8, uint32_t n_locs);
+int      map_gather(uint32_t id, const uint32_t* locs, void* out, uint32_t n_locs);
+
+/* loc handles: adamah.c:3570 map_upload_dev (returns handle | ticket<<32, 0 on
+ * failure; handle 0 creates, otherwise overwrites in place, same size), :3665 */
+uint64_t map_upload_dev(uint32_t handle_or_0, const void* data, uint32_t n_bytes);
+int      map_download_dev(uint32_t handle, void* out, uint32_t n_bytes);
+/* adamah.c:3788, :3703 -- device-side gather into a new data handle / scatter from one */
+uint64_t map_gather_dev(uint32_t id, uint32_t locs_handle, uint32_t n_locs);
+uint64_t map_scatter_dev(uint32_t id, uint32_t locs_handle, uint32_t n_locs, uint32_t src_handle);
+
+/* batching: adamah.c:1629, :1647 -- results are host-visible after batch_end */
+void     batch_begin(void);
+void     batch_end(void);
+
+/* fusion scheduler: adamah.c:4670, :4677, :5653, :708, :718, :675, :691.
+ * A CUDA stream already runs ops in program order, so these keep state and
+ * counters only. */
+void     adamah_fusion_enable(int enable);
+int      adamah_fusion_is_enabled(void);
+int      adamah_fusion_flush(void);
+void     adamah_fusion_set_scheduler_mode(int mode);
+int      adamah_fusion_get_scheduler_mode(void);
+int      adamah_register_loc_span(uint32_t handle, uint32_t map_id, uint32_t start, uint32_t count);
+int      adamah_register_row_base_span(uint32_t handle, uint32_t map_id, uint32_t start, uint32_t count,
+                                       uint32_t stride, uint32_t row_size);
+int      adamah_clear_loc_alias_meta(uint32_t handle);
+
+/* counters: adamah.c:316, :321 (nine uint64 outputs, any may be NULL) */
+void     adamah_stats_reset(void);
+void     adamah_stats_get(uint64_t* dispatch_count, uint64_t* submit_count, uint64_t* barrier_count,
+                          uint64_t* fusion_flush_count, uint64_t* descriptor_set_update_count,
+                          uint64_t* descriptor_cache_hit_count, uint64_t* descriptor_cache_miss_count,
+                          uint64_t* alias_conflict_count, uint64_t* scheduler_mode);
+
+/* ---- operators on the decode path ---------------------------------------- */
+/* adamah.c:7687, :8459, :7786 */
+int map_rmsnorm_dev(uint32_t map, uint32_t src_h, uint32_t wt_h, uint32_t dst_h, uint32_t n_rows, uint32_t dim, float eps);
+int map_rmsnorm_x_dev(uint32_t map_act, uint32_t map_wt, uint32_t src_h, uint32_t wt_h, uint32_t dst_h,
+                      uint32_t n_rows, uint32_t dim, float eps);
+int map_rmsnorm_add_dev(uint32_t map, uint32_t src_h, uint32_t wt_h, uint32_t resid_h, uint32_t dst_h,
+                        uint32_t n_rows, uint32_t dim, float eps);
+/* adamah.c:7879, :8586 */
+int map_rope_dev(uint32_t map, uint32_t src_h, uint32_t dst_h, uint32_t n_tokens, uint32_t n_heads,
+                 uint32_t head_dim, uint32_t pos_offset, float freq_base);
+int map_qk_norm_rope_x_dev(uint32_t map_act, uint32_t map_wt, uint32_t qsrc_h, uint32_t qwt_h,
+                           uint32_t ksrc_h, uint32_t kwt_h, uint32_t qkdst_h,
+                           uint32_t q_rows, uint32_t q_dim, uint32_t k_rows, uint32_t k_dim,
+                           uint32_t pos_offset, float freq_base);
+/* adamah.c:8061 (and map_row_copy_dev) -- KV append */
+int map_row_copy_dev(uint32_t map, uint32_t spec_h, uint32_t src_base_h, uint32_t n_copies, uint32_t row_size);
+int map_row_copy_offset_dev(uint32_t map, uint32_t spec_h, uint32_t src_base_h, uint32_t dst_row_offset,
+                            uint32_t n_copies, uint32_t row_size);
+/* adamah.c:7894 -- C[M,N] = A[M,K] * B[N,K]^T, n_ops independent problems */
+int map_matmul_t_dev(uint32_t map, uint32_t a_h, uint32_t b_h, uint32_t c_h,
+                     uint32_t M, uint32_t K, uint32_t N, uint32_t n_ops);
+/* adamah.c:8693 -- activations in map_act (f32), weights in map_wt (Q4 map or GGUF blocks) */
+int map_matmul_t_xq4_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h, uint32_t b_h, uint32_t c_h,
+                         uint32_t M, uint32_t K, uint32_t N, uint32_t n_ops);
+/* adamah.c:6768 */
+int map_attn_softmax_value_dev(uint32_t map, uint32_t scores_h, uint32_t values_h, uint32_t out_h,
+                               uint32_t n_ops, uint32_t row_size, uint32_t value_dim, float scale, float cap);
+/* adamah.c:5923, :6029, :6398 */
+int map_op1_dev(uint32_t map, uint32_t op, uint32_t src_h, uint32_t dst_h, uint32_t n);
+int map_op2_dev(uint32_t map, uint32_t op, uint32_t a_h, uint32_t b_h, uint32_t dst_h, uint32_t n);
+int map_broadcast_dev(uint32_t map, uint32_t op, uint32_t src_h, uint32_t scalar_h, uint32_t dst_h, uint32_t n);
+/* adamah.c:6875, :7210, :9699 */
+int map_argmax_dev(uint32_t map, uint32_t src_h, uint32_t dst_h, uint32_t n);
+int map_resolve_idx_dev(uint32_t map, uint32_t base_h, uint32_t sel_h, uint32_t dst_h, uint32_t n);
+int map_matvec_argmax_t_xq4_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h, uint32_t b_h,
+                                uint32_t idx_tmp_h, uint32_t val_tmp_h, uint32_t dst_h,
+                                uint32_t K, uint32_t N, uint32_t rows_per_group);
+
+/* decode plan: adamah.c:175-194 (struct), :10341, :10367, :10361 */
+typedef struct AdamahDecodePlanOp {
+    uint32_t kind, map_id, map_id2, op_code;
+    uint32_t h0, h1, h2, h3, h4, h5;
+    uint32_t u0, u1, u2, u3, u4, u5;
+    float    f0, f1;
+} AdamahDecodePlanOp;
+#define ADAMAH_DECODE_RUNTIME_POS     0xFFFFFFFEu
+#define ADAMAH_DECODE_RUNTIME_SEQ_LEN 0xFFFFFFFDu
+int  adamah_register_decode_plan(uint32_t plan_id, const AdamahDecodePlanOp* ops, uint32_t n_ops);
+int  adamah_decode_step(uint32_t plan_id, uint32_t pos, uint32_t seq_len);
+void adamah_clear_decode_plan(uint32_t plan_id);
+
+/* Symbols the reference binding resolves without a guard but which lie off the
+ * decode path (generic tensor ops, Q8 storage).  They exist so the binding
+ * loads, and return ADAMAH_ERR_INVALID.  adamah-MAIN/adamah/__init__.py:530-960. */
+int map_op1(uint32_t, uint32_t, const uint32_t*, const uint32_t*, uint32_t);
+int map_op2(uint32_t, uint32_t, const uint32_t*, const uint32_t*, const uint32_t*, uint32_t);
+int map_matmul(uint32_t, const uint32_t*, const uint32_t*, const uint32_t*, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_softmax(uint32_t, const uint32_t*, const uint32_t*, uint32_t, uint32_t);
+int map_layernorm(uint32_t, const uint32_t*, const uint32_t*, const uint32_t*, const uint32_t*, uint32_t, uint32_t, float);
+int map_broadcast(uint32_t, uint32_t, const uint32_t*, const uint32_t*, const uint32_t*, uint32_t);
+int map_reduce(uint32_t, uint32_t, const uint32_t*, const uint32_t*, uint32_t);
+int map_matmul_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_softmax_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_softmax_abs_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_attn_softmax_abs_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, float, float);
+int map_layernorm_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, float);
+int map_reduce_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_topk_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_topp_dev(uint32_t, uint32_t, uint32_t, uint32_t, float, float);
+int map_fma_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_matmul_t_x_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_matmul_x_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_matmul_xq4_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_matmul_t_xq8_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_matmul_xq8_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+int map_row_gather_xq8_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
+
+/* ============================ Part 2: extensions =========================== */
+
+/* Human-readable text for the last failure of any call (never NULL). */
+const char* adam_b200_last_error(void);
+/* Device ordinal in use, SM count, and library build tag. */
+int         adam_b200_device_info(int* device, int* sm_count, uint64_t* total_mem_bytes);
+/* Number of kernel launches (graph nodes count individually) since the last
+ * adamah_stats_reset; also reported as dispatch_count by adamah_stats_get. */
+uint64_t    adam_b200_kernel_launches(void);
+
+/* Reads and clears the device error word: bit 0 = a loc fell outside its map,
+ * bit 1 = a bounded device-side wait ran out, bit 2 = token id out of range.
+ * Kernels record these instead of faulting. */
+uint32_t    adam_b200_device_error(void);
+/* Free a loc handle (the reference evicts instead: adamah.c:1328 res_evict_one). */
+int         adam_b200_handle_free(uint32_t handle);
+
+/* CUDA-event timer around work on the context stream. */
+int adam_b200_timer_begin(void);
+int adam_b200_timer_end(float* ms);
+/* Record the operator calls made between begin and end into a CUDA graph (no
+ * host I/O in between), then replay it `times` times with one launch each.
+ * CUDA counterpart of batching many dispatches into one command buffer
+ * (adamah.c:1629-1721). */
+int adam_b200_capture_begin(void);
+int adam_b200_capture_end(uint32_t* graph_id);
+int adam_b200_graph_launch(uint32_t graph_id, uint32_t times);
+int adam_b200_graph_destroy(uint32_t graph_id);
+
+/* Copy raw GGUF blocks (ggml_type 2 = Q4_0, 12 = Q4_K) into a GGUF-block map at
+ * element offset elem_off (a multiple of the block size).  `raw` may be a host
+ * or a device pointer.  Replaces the reference's Python re-quantization at load
+ * (adam/models/engine.py:974-1116); op signatures are unchanged -- weight handles
+ * still carry element offsets. */
+int map_upload_gguf_blocks(uint32_t map_wt, uint32_t ggml_type, uint64_t elem_off, const void* raw, uint64_t n_bytes);
+/* Decode n_elems weights starting at elem_off of a GGUF-block or Q4 map to
+ * float32 (host pointer `out`); bit-exact w.r.t. adam/loaders/gguf.py:290-337. */
+int map_dequant_gguf(uint32_t map_wt, uint64_t elem_off, float* out, uint64_t n_elems);
+/* Quantize float32 rows (device pointer, n_elems multiple of 32) to raw Q4_0
+ * blocks (device pointer) with the ggml rule; load-time helper for synthetic
+ * models (role of adamah-MAIN/adamah/shaders/src/q4/map_scatter.comp). */
+int adam_b200_quantize_q4_0_dev(const float* w_dev, uint64_t n_elems, void* raw_dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADAM_B200_H */

@@ -1,0 +1,176 @@
+"""CUDA GEMV / block decode against the oracle, called through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+
+import adam_b200 as A
+from adam_b200 import gguf_blocks as gb
+from oracle import q4_blocks
+
+pytestmark = pytest.mark.gpu
+
+WS, WT = 0, 1          # map ids: float32 workspace, GGUF-block weights
+
+
+def _bits_equal(a, b):
+    a = np.asarray(a, np.float32); b = np.asarray(b, np.float32)
+    return bool(((a.view(np.uint32) == b.view(np.uint32)) | (np.isnan(a) & np.isnan(b))).all())
+
+
+def _gemv(gpu, ggml_type, raw, N, K, x, elem_off=0, pad_elems=0):
+    """y = W x through map_matmul_t_xq4_dev; x is [B,K]."""
+    B = x.shape[0]
+    dt = A.DTYPE_GGUF_Q4_0 if ggml_type == 2 else A.DTYPE_GGUF_Q4_K
+    gpu.map_create_typed(WT, dt, 1, elem_off + N * K + pad_elems)
+    gpu.upload_gguf_blocks(WT, ggml_type, elem_off, raw)
+    gpu.map_create_typed(WS, A.DTYPE_F32, 1, B * K + B * N + 8)
+    gpu.scatter_contiguous(WS, 0, x.reshape(-1))
+    a_h, _ = gpu.upload_dev(np.array([0], np.uint32))
+    b_h, _ = gpu.upload_dev(np.array([elem_off], np.uint32))
+    c_h, _ = gpu.upload_dev(np.array([B * K], np.uint32))
+    gpu.batch_begin()
+    gpu.map_matmul_t_xq4_dev(WS, WT, a_h, b_h, c_h, B, K, N)
+    gpu.batch_end()
+    y = gpu.gather(WS, np.arange(B * K, B * K + B * N, dtype=np.uint32)).view(np.float32).reshape(B, N)
+    for h in (a_h, b_h, c_h):
+        gpu.free_handle(h)
+    assert gpu.device_error() == 0
+    return y
+
+
+def _check(y, W, x, tol=1e-3):
+    ref = x.astype(np.float64) @ W.astype(np.float64).T
+    scale = np.abs(ref).max()
+    err = np.abs(y - ref).max() / scale
+    assert err < tol * 0.05, f"max error {err:.3e} of max |y|"         # far inside the 1e-3 budget
+    # element-wise: 1e-3 relative wherever the output is not tiny
+    big = np.abs(ref) > 0.05 * scale
+    assert (np.abs(y - ref)[big] / np.abs(ref)[big]).max() < tol
+
+
+def test_dequant_q4_0_bit_exact_vs_reference(gpu, golden_dir):
+    g = np.load(os.path.join(golden_dir, "q4_dequant.npz"))
+    raw = g["q4_0_raw"]
+    n = raw.shape[0] * 32
+    gpu.map_create_typed(WT, A.DTYPE_GGUF_Q4_0, 1, n)
+    gpu.upload_gguf_blocks(WT, 2, 0, raw)
+    assert _bits_equal(gpu.dequant_gguf(WT, 0, n), g["q4_0_out"])
+
+
+def test_dequant_q4_k_bit_exact_vs_reference(gpu, golden_dir):
+    g = np.load(os.path.join(golden_dir, "q4_dequant.npz"))
+    raw = g["q4_k_raw"]
+    n = raw.shape[0] * 256
+    gpu.map_create_typed(WT, A.DTYPE_GGUF_Q4_K, 1, n)
+    gpu.upload_gguf_blocks(WT, 12, 0, raw)
+    assert _bits_equal(gpu.dequant_gguf(WT, 0, n), g["q4_k_out"])
+
+
+def test_dequant_at_offset_and_partial(gpu):
+    rng = np.random.default_rng(7)
+    raw = gb.random_q4_0_blocks(rng, 8, 256)
+    gpu.map_create_typed(WT, A.DTYPE_GGUF_Q4_0, 1, 64 + 8 * 256)
+    gpu.upload_gguf_blocks(WT, 2, 64, raw)
+    ref = q4_blocks.dequant_q4_0(raw)
+    assert _bits_equal(gpu.dequant_gguf(WT, 64 + 512, 256), ref[512:768])
+
+
+def test_quantize_q4_0_kernel_matches_gguf(gpu, golden_dir):
+    import torch
+    g = np.load(os.path.join(golden_dir, "q4_0_quantize.npz"))
+    w = torch.from_numpy(g["w"]).cuda().contiguous()
+    raw = torch.empty(g["raw"].size, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    gpu.quantize_q4_0_dev(w.data_ptr(), w.numel(), raw.data_ptr())
+    assert np.array_equal(raw.cpu().numpy().reshape(g["raw"].shape), g["raw"])
+
+
+@pytest.mark.parametrize("N,K", [(6912, 1152), (1152, 6912), (1024, 1152), (1152, 1024), (7, 32), (5, 96), (33, 4096), (130, 160)])
+def test_q4_0_gemv(gpu, N, K):
+    rng = np.random.default_rng(N * 31 + K)
+    raw = gb.random_q4_0_blocks(rng, N, K)
+    x = rng.standard_normal((1, K), dtype=np.float32)
+    y = _gemv(gpu, 2, raw, N, K, x)
+    _check(y, q4_blocks.dequant(raw.reshape(-1), 2, N, K), x)
+
+
+@pytest.mark.parametrize("N,K", [(5376, 5376), (512, 21504), (2048, 4096), (3, 256), (9, 768), (64, 1024)])
+def test_q4_k_gemv(gpu, N, K):
+    rng = np.random.default_rng(N * 17 + K)
+    raw = gb.random_q4_k_blocks(rng, N, K)
+    x = rng.standard_normal((1, K), dtype=np.float32)
+    y = _gemv(gpu, 12, raw, N, K, x)
+    _check(y, q4_blocks.dequant(raw.reshape(-1), 12, N, K), x)
+
+
+@pytest.mark.parametrize("ggml_type,N,K,B", [(2, 300, 1152, 2), (2, 256, 6912, 3), (2, 64, 1024, 8), (12, 128, 5376, 8),
+                                             (12, 40, 21504, 8), (12, 100, 512, 5), (2, 50, 64, 13)])
+def test_gemv_batched(gpu, ggml_type, N, K, B):
+    rng = np.random.default_rng(N + K + B)
+    raw = (gb.random_q4_0_blocks if ggml_type == 2 else gb.random_q4_k_blocks)(rng, N, K)
+    x = rng.standard_normal((B, K), dtype=np.float32)
+    y = _gemv(gpu, ggml_type, raw, N, K, x)
+    _check(y, q4_blocks.dequant(raw.reshape(-1), ggml_type, N, K), x)
+
+
+def test_gemv_tensor_at_offset(gpu):
+    rng = np.random.default_rng(99)
+    N, K = 96, 1152
+    raw = gb.random_q4_0_blocks(rng, N, K)
+    x = rng.standard_normal((1, K), dtype=np.float32)
+    y = _gemv(gpu, 2, raw, N, K, x, elem_off=32 * 5, pad_elems=64)
+    _check(y, q4_blocks.dequant(raw.reshape(-1), 2, N, K), x)
+
+
+def test_gemv_is_linear_in_x_at_full_size(gpu):
+    """Size-independent property on the LM-head shape: W(ax + by) = aWx + bWy."""
+    rng = np.random.default_rng(5)
+    N, K = 262144, 1152
+    raw = gb.random_q4_0_blocks(rng, N, K)
+    x = rng.standard_normal((3, K), dtype=np.float32)
+    x[2] = 0.5 * x[0] - 2.0 * x[1]
+    y = _gemv(gpu, 2, raw, N, K, x)
+    comb = 0.5 * y[0].astype(np.float64) - 2.0 * y[1].astype(np.float64)
+    assert np.abs(y[2] - comb).max() < 2e-5 * np.abs(comb).max()
+    rows = rng.integers(0, N, 64)
+    W = q4_blocks.dequant(raw[rows].reshape(-1), 2, 64, K)
+    ref = x.astype(np.float64) @ W.astype(np.float64).T
+    assert np.abs(y[:, rows] - ref).max() < 5e-5 * np.abs(ref).max()
+
+
+def test_gemv_rejects_bad_arguments(gpu):
+    gpu.map_create_typed(WT, A.DTYPE_GGUF_Q4_0, 1, 64 * 32)
+    gpu.map_create_typed(WS, A.DTYPE_F32, 1, 256)
+    a_h, _ = gpu.upload_dev(np.array([0], np.uint32))
+    with pytest.raises(RuntimeError, match="code -3"):
+        gpu.map_matmul_t_xq4_dev(WS, WT, a_h, a_h, a_h, 1, 48, 4)        # K not a whole block
+    with pytest.raises(RuntimeError, match="code -3"):
+        gpu.map_matmul_t_xq4_dev(WS, WT, a_h, a_h, a_h, 1, 64, 64)       # weight range beyond the map
+    with pytest.raises(RuntimeError, match="code -4"):
+        gpu.map_matmul_t_xq4_dev(WS, 9, a_h, a_h, a_h, 1, 32, 4)         # no such map
+    with pytest.raises(RuntimeError, match="code -4"):
+        gpu.map_matmul_t_xq4_dev(WS, WT, 60000, a_h, a_h, 1, 32, 4)      # no such handle
+    with pytest.raises(RuntimeError):
+        gpu.upload_gguf_blocks(WT, 12, 0, np.zeros(144, np.uint8))        # type does not match the map
+    gpu.free_handle(a_h)
+
+
+def test_matvec_argmax_matches_full_logits(gpu):
+    rng = np.random.default_rng(11)
+    N, K = 20000, 1152
+    raw = gb.random_q4_0_blocks(rng, N, K)
+    x = rng.standard_normal((1, K), dtype=np.float32)
+    y = _gemv(gpu, 2, raw, N, K, x)[0]
+    # same maps are still alive: fused LM head + arg-max writes the id as float32
+    a_h, _ = gpu.upload_dev(np.array([0], np.uint32))
+    b_h, _ = gpu.upload_dev(np.array([0], np.uint32))
+    d_h, _ = gpu.upload_dev(np.array([K + 3], np.uint32))
+    t_h, _ = gpu.upload_dev(np.zeros(4, np.uint32))
+    gpu.batch_begin()
+    gpu.map_matvec_argmax_t_xq4_dev(WS, WT, a_h, b_h, t_h, t_h, d_h, K, N, 256)
+    gpu.batch_end()
+    tok = int(gpu.gather(WS, np.array([K + 3], np.uint32)).view(np.float32)[0])
+    assert tok == int(np.argmax(y))
+    for h in (a_h, b_h, d_h, t_h):
+        gpu.free_handle(h)
