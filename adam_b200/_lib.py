@@ -100,6 +100,17 @@ _SIGS = {
     "adam_b200_capture_end": (c_int, [POINTER(u32)]),
     "adam_b200_graph_launch": (c_int, [u32, u32]),
     "adam_b200_graph_destroy": (c_int, [u32]),
+    "adam_b200_decoder_create": (c_int, [POINTER(DecoderDesc), POINTER(u32)]),
+    "adam_b200_decoder_destroy": (c_int, [u32]),
+    "adam_b200_decoder_bind_matrix": (c_int, [u32, u32, u32, u32, u64, u32, u32]),
+    "adam_b200_decoder_bind_norm": (c_int, [u32, u32, u32, u32, u64, u32]),
+    "adam_b200_decoder_set_rope": (c_int, [u32, u32, c_void_p, c_void_p, u32, u32]),
+    "adam_b200_decoder_begin": (c_int, [u32, u32, c_void_p, c_void_p, c_void_p]),
+    "adam_b200_decoder_step": (c_int, [u32, u32, u32]),
+    "adam_b200_decoder_read_state": (c_int, [u32, c_void_p, c_void_p]),
+    "adam_b200_decoder_read_log": (c_int, [u32, u32, u32, u32, c_void_p]),
+    "adam_b200_decoder_read_logits": (c_int, [u32, u32, c_void_p]),
+    "adam_b200_decoder_read_buffer": (c_int, [u32, u32, u32, c_void_p, u32]),
     "map_upload_gguf_blocks": (c_int, [u32, u32, u64, c_void_p, u64]),
     "map_dequant_gguf": (c_int, [u32, u64, c_void_p, u64]),
     "adam_b200_quantize_q4_0_dev": (c_int, [c_void_p, u64, c_void_p]),

@@ -49,7 +49,8 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
         if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_time):
             return obj
-        cmd = [nvcc, *[f for f in NVCC_FLAGS if f != "--use_fast_math=false"], "-c", src, "-o", obj]
+        cmd = [nvcc, *[f for f in NVCC_FLAGS if f != "--use_fast_math=false"], *os.environ.get("ADAM_B200_NVCC_EXTRA", "").split(),
+               "-c", src, "-o", obj]
         if ptxas_info:
             cmd[1:1] = ["-Xptxas", "-v"]
         r = subprocess.run(cmd, capture_output=True, text=True)

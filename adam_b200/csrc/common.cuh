@@ -12,7 +12,7 @@
 
 namespace ab {
 
-constexpr uint32_t MAX_MAPS    = 64;      // reference: MAX_MAPS 16 (adamah.c:30)
+constexpr uint32_t MAX_MAPS    = 256;     // reference: MAX_MAPS 16 (adamah.c:30)
 constexpr uint32_t MAX_HANDLES = 1u << 16; // reference: MAX_RES 2048 (adamah.c:31)
 
 // Bits a kernel may OR into the device error word instead of faulting.

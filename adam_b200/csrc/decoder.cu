@@ -1,2 +1,721 @@
+// Fused decoder: one decoded token for a batch of sequences as a fixed sequence
+// of kernels (captured once into a CUDA graph and replayed), with positions and
+// token ids living in device memory so that consecutive tokens need no host work.
+//
+// It computes what the reference engine's per-token loop computes
+// (adam/models/engine.py:2971-3706 `_forward`: embed, per layer RMSNorm -> QKV ->
+// QK-norm + RoPE -> KV append -> attention -> o-proj -> post-norm + residual ->
+// RMSNorm -> gate/up -> GeGLU -> down -> post-norm + residual, final norm, LM head
+// + arg-max), with the arithmetic of the reference's numpy decoder
+// (tests/diagnostics/diag_inference.py:973-1037).  Differences from the reference
+// runtime, all additive: B independent sequences per step, a paged KV cache in
+// fp16 or fp32, an optional sliding-window mask on non-global layers, and rotary
+// angles read from a table the host supplies.
 #include "common.cuh"
-namespace ab { void decoder_destroy_all() {} }
+#include "gemv.cuh"
+
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+namespace ab {
+
+int weight_ref(const Map* m, uint64_t off, uint64_t n_elems, int* wtype, WeightRef* w);
+int argmax_scratch(float** pv, int** pi, unsigned int** tk);
+bool capturing();
+
+enum { MAT_Q = 0, MAT_K, MAT_V, MAT_O, MAT_GATE, MAT_UP, MAT_DOWN, MAT_EMBD, MAT_OUTPUT, MAT_KINDS };
+enum { NORM_ATTN = 0, NORM_POST_ATTN, NORM_FFN, NORM_POST_FFW, NORM_Q, NORM_K, NORM_OUTPUT, NORM_KINDS };
+
+struct Mat { bool bound; int wtype; WeightRef w; uint32_t rows, cols; };
+
+struct Layer {
+    Mat m[7];
+    const float* norm[6];       // NORM_ATTN .. NORM_K (NULL = absent)
+    bool qkv_contiguous, gateup_pairable;
+};
+
+struct Decoder {
+    bool used;
+    adam_b200_decoder_desc d;
+    std::vector<Layer> layers;
+    Mat embd, output;
+    const float* output_norm;
+    float* rope_cos[2]; float* rope_sin[2]; uint32_t rope_pos[2];
+    // device state
+    int32_t* pos;  int32_t* cur_tok;  int32_t* prompt_len;  int32_t* prompt_tok;  int32_t* gen_log;
+    int32_t* block_table; uint32_t max_pages_per_seq, n_pages;
+    void* kv_pool; size_t page_elems;
+    float *h, *normed, *qkv, *q_rot, *attn_out, *proj, *act, *logits;
+    float *part_o, *part_ml; unsigned int* attn_ticket; uint32_t n_splits;
+    uint32_t batch;             // active sequences
+    std::vector<uint32_t> free_pages;
+    cudaGraphExec_t graph[2]; cudaGraph_t graph_src[2]; uint32_t graph_batch[2]; uint64_t graph_kernels[2];
+};
+
+constexpr uint32_t MAX_DECODERS = 8;
+constexpr uint32_t ATTN_SPLIT = 256;       // tokens per attention split
+static Decoder* g_dec[MAX_DECODERS];
+
+static Decoder* get_dec(uint32_t id) {
+    if (!ready()) return nullptr;
+    if (id >= MAX_DECODERS || !g_dec[id]) { fail(ADAMAH_ERR_NOT_FOUND, "decoder %u does not exist", id); return nullptr; }
+    return g_dec[id];
+}
+
+// ---- kernels ---------------------------------------------------------------
+
+__device__ __forceinline__ float ld_kv(const float* p) { return *p; }
+__device__ __forceinline__ float ld_kv(const __half* p) { return __half2float(*p); }
+__device__ __forceinline__ void st_kv(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st_kv(__half* p, float v) { *p = __float2half_rn(v); }
+
+// h[b] = dequant(token_embd[row tok]) * emb_scale   (diag_inference.py:975-977)
+template <int WT>
+__global__ void k_embed(const WeightRef w, uint32_t n_embd, uint32_t n_vocab, float emb_scale,
+                        const int32_t* __restrict__ pos, const int32_t* __restrict__ prompt_len, const int32_t* __restrict__ prompt_tok,
+                        uint32_t prompt_ld, const int32_t* __restrict__ cur_tok, float* __restrict__ h, uint32_t* err) {
+    const uint32_t b = blockIdx.x;
+    const int32_t p = pos[b];
+    int32_t tok = (p < prompt_len[b]) ? prompt_tok[(size_t)b * prompt_ld + p] : cur_tok[b];
+    if (tok < 0 || (uint32_t)tok >= n_vocab) { if (threadIdx.x == 0) atomicOr(err, DEVERR_BAD_TOKEN); tok = 0; }
+    float* out = h + (size_t)b * n_embd;
+    if (WT == WT_Q4_0) {
+        const uint32_t nblk = n_embd / 32;
+        const uint8_t* q = reinterpret_cast<const uint8_t*>(w.q + (size_t)tok * nblk);
+        const __half* d = w.d + (size_t)tok * nblk;
+        for (uint32_t i = threadIdx.x; i < nblk * 16; i += blockDim.x) {
+            const uint32_t blk = i >> 4, j = i & 15;
+            const float s = __half2float(d[blk]);
+            const uint32_t byte = q[blk * 16 + j];
+            out[blk * 32 + j]      = __fmul_rn(__fmul_rn((float)(int)(byte & 15) - 8.f, s), emb_scale);
+            out[blk * 32 + 16 + j] = __fmul_rn(__fmul_rn((float)(int)(byte >> 4) - 8.f, s), emb_scale);
+        }
+    } else {
+        const uint32_t nsb = n_embd / 256;
+        const uint8_t* base = reinterpret_cast<const uint8_t*>(w.q) + (size_t)tok * nsb * 144;
+        for (uint32_t i = threadIdx.x; i < nsb * 128; i += blockDim.x) {
+            const uint32_t sb = i >> 7, bi = i & 127, grp = bi >> 5, j = bi & 31;
+            const uint8_t* blk = base + (size_t)sb * 144;
+            const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+            float s0, m0, s1, m1;
+            // same products as the loader: (d*sc), (dmin*m), each rounded once
+            {
+                const int sh = (grp & 1) * 16;
+                const uint32_t s16 = (hdr.y >> sh) & 0xFFFFu, m16 = (hdr.z >> sh) & 0xFFFFu, t16 = (hdr.w >> sh) & 0xFFFFu;
+                uint32_t sp, mp;
+                if (grp < 2) { sp = s16 & 0x3F3Fu; mp = m16 & 0x3F3Fu; }
+                else { sp = (t16 & 0x0F0Fu) | ((s16 >> 2) & 0x3030u); mp = ((t16 >> 4) & 0x0F0Fu) | ((m16 >> 2) & 0x3030u); }
+                const float dd = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xFFFFu)));
+                const float dm = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+                s0 = __fmul_rn(dd, (float)(sp & 0xFFu)); s1 = __fmul_rn(dd, (float)(sp >> 8));
+                m0 = __fmul_rn(dm, (float)(mp & 0xFFu)); m1 = __fmul_rn(dm, (float)(mp >> 8));
+            }
+            const uint32_t byte = blk[16 + bi];
+            float* o = out + sb * 256 + grp * 64;
+            o[j]      = __fmul_rn(__fsub_rn(__fmul_rn((float)(byte & 15), s0), m0), emb_scale);
+            o[32 + j] = __fmul_rn(__fsub_rn(__fmul_rn((float)(byte >> 4), s1), m1), emb_scale);
+        }
+    }
+}
+
+// One CTA per sequence:  h' = h + (w_post ? rms(a)*w_post : a)   (when a != NULL)
+//                        n  = rms(h') * w_pre                   (when w_pre != NULL)
+// rms(x)*w is (x / sqrt(mean(x^2)+eps)) * w   (diag_inference.py:938-939).
+__global__ void k_norm_add_norm(float* __restrict__ h, const float* __restrict__ a, const float* __restrict__ w_post,
+                                const float* __restrict__ w_pre, float* __restrict__ n_out, uint32_t E, float eps) {
+    __shared__ float red[33];
+    const uint32_t b = blockIdx.x;
+    float* hb = h + (size_t)b * E;
+    if (a) {
+        const float* ab_ = a + (size_t)b * E;
+        float rms = 1.f;
+        if (w_post) {
+            float ss = 0.f;
+            for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) { const float x = ab_[i]; ss = fmaf(x, x, ss); }
+            ss = block_sum(ss, red);
+            rms = sqrtf(ss / (float)E + eps);
+        }
+        for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) {
+            const float t = w_post ? __fdiv_rn(ab_[i], rms) * w_post[i] : ab_[i];
+            hb[i] = hb[i] + t;
+        }
+    }
+    if (w_pre) {
+        float ss = 0.f;
+        for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) { const float x = hb[i]; ss = fmaf(x, x, ss); }
+        ss = block_sum(ss, red);
+        const float rms = sqrtf(ss / (float)E + eps);
+        float* nb = n_out + (size_t)b * E;
+        for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) nb[i] = __fdiv_rn(hb[i], rms) * w_pre[i];
+    }
+}
+
+struct KvGeom {
+    uint32_t n_layer, n_kv, hd, page, max_pages;   // page = tokens per page
+    size_t page_elems;                              // elements of one page (all layers, K and V)
+};
+__device__ __forceinline__ size_t kv_index(const KvGeom& g, uint32_t page_id, uint32_t layer, uint32_t kv, uint32_t head, uint32_t slot) {
+    return (size_t)page_id * g.page_elems + ((((size_t)layer * 2 + kv) * g.n_kv + head) * g.page + slot) * g.hd;
+}
+
+// Per (sequence, row): q rows get per-head RMSNorm + RoPE into q_rot (fp32); k rows
+// the same into the cache; v rows are copied into the cache.
+// (map_qk_norm_rope_x.comp + map_row_copy.comp; diag_inference.py:989-999.)
+template <typename T>
+__global__ void k_qk_rope_append(const float* __restrict__ qkv, uint32_t qkv_ld, uint32_t n_head, uint32_t n_kv, uint32_t hd,
+                                 const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t, uint32_t n_pos,
+                                 const int32_t* __restrict__ pos, float* __restrict__ q_rot,
+                                 T* __restrict__ kv_pool, KvGeom geo, const int32_t* __restrict__ block_table, uint32_t layer, uint32_t* err) {
+    __shared__ float red[33];
+    const uint32_t b = blockIdx.y, row = blockIdx.x, half = hd / 2;
+    const int32_t p = pos[b];
+    const float* src = qkv + (size_t)b * qkv_ld + (size_t)row * hd;
+    const bool is_q = row < n_head, is_k = !is_q && row < n_head + n_kv;
+    const uint32_t pp = (uint32_t)p < n_pos ? (uint32_t)p : n_pos - 1;
+    if ((uint32_t)p >= n_pos && threadIdx.x == 0) atomicOr(err, DEVERR_OOB_MAP);
+    size_t kv_off = 0;
+    if (!is_q) {
+        const uint32_t head = is_k ? row - n_head : row - n_head - n_kv;
+        const uint32_t page_no = (uint32_t)p / geo.page, slot = (uint32_t)p % geo.page;
+        const int32_t page_id = block_table[(size_t)b * geo.max_pages + (page_no < geo.max_pages ? page_no : 0)];
+        if (page_no >= geo.max_pages || page_id < 0) { if (threadIdx.x == 0) atomicOr(err, DEVERR_OOB_MAP); return; }
+        kv_off = kv_index(geo, (uint32_t)page_id, layer, is_k ? 0u : 1u, head, slot);
+    }
+    if (!is_q && !is_k) {           // V: plain copy
+        for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) st_kv(kv_pool + kv_off + i, src[i]);
+        return;
+    }
+    const float* w = is_q ? q_norm : k_norm;
+    float rms = 1.f;
+    if (w) {
+        float ss = 0.f;
+        for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) { const float x = src[i]; ss = fmaf(x, x, ss); }
+        ss = block_sum(ss, red);
+        rms = sqrtf(ss / (float)hd + eps);
+    }
+    const float* ct = cos_t + (size_t)pp * half;
+    const float* st = sin_t + (size_t)pp * half;
+    for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
+        float x0 = src[i], x1 = src[i + half];
+        if (w) { x0 = __fdiv_rn(x0, rms) * w[i]; x1 = __fdiv_rn(x1, rms) * w[i + half]; }
+        const float c = ct[i], s = st[i];
+        const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        const float y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+        if (is_q) { float* dst = q_rot + ((size_t)b * n_head + row) * hd; dst[i] = y0; dst[i + half] = y1; }
+        else { st_kv(kv_pool + kv_off + i, y0); st_kv(kv_pool + kv_off + i + half, y1); }
+    }
+}
+
+// Decode attention for one (split, kv head, sequence): all query heads that share
+// the kv head.  p = softmax(cap*tanh(q.k*scale/cap)) over positions [start, seq);
+// partial (o, m, l) per split, combined by the CTA that finishes last.
+// (map_matmul_t.comp + map_attn_softmax_value.comp; diag_inference.py:1001-1012.)
+template <typename T, int GS_MAX>
+__global__ void __launch_bounds__(256) k_attention(const float* __restrict__ q_rot, const T* __restrict__ kv_pool, KvGeom geo,
+                                                   const int32_t* __restrict__ block_table, const int32_t* __restrict__ pos,
+                                                   uint32_t n_head, uint32_t layer, uint32_t window, float scale, float cap,
+                                                   float* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+                                                   unsigned int* __restrict__ ticket, uint32_t n_splits_max) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float red[33];
+    __shared__ float s_m[GS_MAX], s_l[GS_MAX];
+    __shared__ bool s_last;
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const uint32_t hd = geo.hd, gs = n_head / geo.n_kv;
+    const uint32_t seq = (uint32_t)pos[b] + 1;
+    const uint32_t start = (window > 0 && seq > window) ? seq - window : 0;
+    const uint32_t n_act = (seq - start + ATTN_SPLIT - 1) / ATTN_SPLIT;
+    if (split >= n_act) return;
+    const uint32_t t0 = start + split * ATTN_SPLIT, t1 = min(seq, t0 + ATTN_SPLIT), len = t1 - t0;
+    float* s_q = sm;                           // [gs][hd]
+    float* s_sc = sm + gs * hd;                // [gs][ATTN_SPLIT]
+    float* s_o = s_sc + gs * ATTN_SPLIT;       // [token lanes][gs][hd] for the PV reduction
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (uint32_t i = tid; i < gs * hd; i += blockDim.x) s_q[i] = q_rot[((size_t)b * n_head + (size_t)kvh * gs) * hd + i];
+    __syncthreads();
+
+    // ---- scores: one warp per position, lanes over head_dim ----
+    const int32_t* bt = block_table + (size_t)b * geo.max_pages;
+    for (uint32_t t = warp; t < len; t += 8) {
+        const uint32_t tp = t0 + t;
+        const T* kr = kv_pool + kv_index(geo, (uint32_t)max(bt[tp / geo.page], 0), layer, 0, kvh, tp % geo.page);
+        float acc[GS_MAX];
+#pragma unroll
+        for (int g = 0; g < GS_MAX; ++g) acc[g] = 0.f;
+        for (uint32_t d = lane; d < hd; d += 32) {
+            const float kd = ld_kv(kr + d);
+#pragma unroll
+            for (int g = 0; g < GS_MAX; ++g) if (g < (int)gs) acc[g] = fmaf(s_q[g * hd + d], kd, acc[g]);
+        }
+#pragma unroll
+        for (int g = 0; g < GS_MAX; ++g) {
+            if (g < (int)gs) {
+                float v = warp_sum(acc[g]) * scale;
+                if (cap > 0.f) v = tanhf(v / cap) * cap;
+                if (lane == 0) s_sc[g * ATTN_SPLIT + t] = v;
+            }
+        }
+    }
+    __syncthreads();
+    // ---- per-head max and exp-sum over this split ----
+    for (uint32_t g = 0; g < gs; ++g) {
+        float mx = -3.402823466e+38f;
+        for (uint32_t t = tid; t < len; t += blockDim.x) mx = fmaxf(mx, s_sc[g * ATTN_SPLIT + t]);
+        mx = block_max(mx, red);
+        float sum = 0.f;
+        for (uint32_t t = tid; t < len; t += blockDim.x) { const float pz = expf(s_sc[g * ATTN_SPLIT + t] - mx); s_sc[g * ATTN_SPLIT + t] = pz; sum += pz; }
+        sum = block_sum(sum, red);
+        if (tid == 0) { s_m[g] = mx; s_l[g] = sum; }
+    }
+    __syncthreads();
+    // ---- o = p @ V: thread owns 2 dims, token lanes stride over positions ----
+    const uint32_t tpt = hd / 2, n_tl = blockDim.x / tpt;      // threads per token, token lanes
+    const uint32_t tl = tid / tpt, dp = (tid % tpt) * 2;
+    float o0[GS_MAX], o1[GS_MAX];
+#pragma unroll
+    for (int g = 0; g < GS_MAX; ++g) { o0[g] = 0.f; o1[g] = 0.f; }
+    if (tl < n_tl) {
+        for (uint32_t t = tl; t < len; t += n_tl) {
+            const uint32_t tp = t0 + t;
+            const T* vr = kv_pool + kv_index(geo, (uint32_t)max(bt[tp / geo.page], 0), layer, 1, kvh, tp % geo.page);
+            const float v0 = ld_kv(vr + dp), v1 = ld_kv(vr + dp + 1);
+#pragma unroll
+            for (int g = 0; g < GS_MAX; ++g) if (g < (int)gs) { const float pz = s_sc[g * ATTN_SPLIT + t]; o0[g] = fmaf(pz, v0, o0[g]); o1[g] = fmaf(pz, v1, o1[g]); }
+        }
+#pragma unroll
+        for (int g = 0; g < GS_MAX; ++g) if (g < (int)gs) { s_o[(tl * gs + g) * hd + dp] = o0[g]; s_o[(tl * gs + g) * hd + dp + 1] = o1[g]; }
+    }
+    __syncthreads();
+    float* po = part_o + (((size_t)b * geo.n_kv + kvh) * n_splits_max + split) * gs * hd;
+    float* pml = part_ml + (((size_t)b * geo.n_kv + kvh) * n_splits_max + split) * gs * 2;
+    for (uint32_t i = tid; i < gs * hd; i += blockDim.x) {
+        float v = 0.f;
+        for (uint32_t l2 = 0; l2 < n_tl; ++l2) v += s_o[l2 * gs * hd + i];
+        if (n_act == 1) out[((size_t)b * n_head + (size_t)kvh * gs) * hd + i] = v / s_l[i / hd];
+        else po[i] = v;
+    }
+    if (n_act == 1) return;
+    if (tid < gs) { pml[tid * 2] = s_m[tid]; pml[tid * 2 + 1] = s_l[tid]; }
+    __threadfence();
+    __syncthreads();
+    unsigned int* tk = ticket + (size_t)b * geo.n_kv + kvh;
+    if (tid == 0) s_last = (atomicAdd(tk, 1u) == n_act - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* po0 = part_o + (((size_t)b * geo.n_kv + kvh) * n_splits_max) * gs * hd;
+    const float* pml0 = part_ml + (((size_t)b * geo.n_kv + kvh) * n_splits_max) * gs * 2;
+    for (uint32_t i = tid; i < gs * hd; i += blockDim.x) {
+        const uint32_t g = i / hd;
+        float M = -3.402823466e+38f;
+        for (uint32_t s = 0; s < n_act; ++s) M = fmaxf(M, __ldcg(pml0 + ((size_t)s * gs + g) * 2));
+        float num = 0.f, den = 0.f;
+        for (uint32_t s = 0; s < n_act; ++s) {
+            const float w = expf(__ldcg(pml0 + ((size_t)s * gs + g) * 2) - M);
+            num = fmaf(w, __ldcg(po0 + (size_t)s * gs * hd + i), num);
+            den = fmaf(w, __ldcg(pml0 + ((size_t)s * gs + g) * 2 + 1), den);
+        }
+        out[((size_t)b * n_head + (size_t)kvh * gs) * hd + i] = num / den;
+    }
+    if (tid == 0) *tk = 0u;
+}
+
+// End of a step: advance positions; when the LM head ran, log the sampled token.
+__global__ void k_advance(int32_t* __restrict__ pos, const int32_t* __restrict__ cur_tok, int32_t* __restrict__ gen_log,
+                          uint32_t log_ld, uint32_t batch, int with_lm) {
+    const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    const int32_t p = pos[b] + 1;
+    pos[b] = p;
+    if (with_lm && (uint32_t)p < log_ld) gen_log[(size_t)b * log_ld + p] = cur_tok[b];
+}
+
+__global__ void k_fill_i32(int32_t* p, int32_t v, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
+// ---- host side ---------------------------------------------------------------
+
+static void free_graphs(Decoder* D) {
+    for (int i = 0; i < 2; ++i) {
+        if (D->graph[i]) { cudaGraphExecDestroy(D->graph[i]); cudaGraphDestroy(D->graph_src[i]); D->graph[i] = nullptr; D->graph_src[i] = nullptr; }
+    }
+}
+
+static void destroy(Decoder* D) {
+    cudaStreamSynchronize(g.stream);
+    free_graphs(D);
+    void* ptrs[] = {D->pos, D->cur_tok, D->prompt_len, D->prompt_tok, D->gen_log, D->block_table, D->kv_pool, D->h, D->normed, D->qkv,
+                    D->q_rot, D->attn_out, D->proj, D->act, D->logits, D->part_o, D->part_ml, D->attn_ticket,
+                    D->rope_cos[0], D->rope_sin[0], D->rope_cos[1], D->rope_sin[1]};
+    for (void* p : ptrs) cudaFree(p);
+    delete D;
+}
+
+void decoder_destroy_all() {
+    for (uint32_t i = 0; i < MAX_DECODERS; ++i) if (g_dec[i]) { destroy(g_dec[i]); g_dec[i] = nullptr; }
+}
+
+#define DCU(x) do { cudaError_t e__ = (x); if (e__ != cudaSuccess) return fail(e__ == cudaErrorMemoryAllocation ? ADAMAH_ERR_MEMORY : ADAMAH_ERR_BACKEND, "%s: %s", #x, cudaGetErrorString(e__)); } while (0)
+
+static bool is_global_layer(const adam_b200_decoder_desc& d, uint32_t L) { return d.global_every == 0 || (L + 1) % d.global_every == 0; }
+
+static size_t kv_elem_size(const adam_b200_decoder_desc& d) { return d.kv_dtype == 1 ? 2 : 4; }
+
+template <typename T>
+static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch) {
+    const adam_b200_decoder_desc& d = D->d;
+    KvGeom geo{d.n_layer, d.n_head_kv, d.head_dim, d.page_size, D->max_pages_per_seq, D->page_elems};
+    const uint32_t gs = d.n_head / d.n_head_kv;
+    const uint32_t window = ((d.flags & 1u) && d.sliding_window > 0 && !is_global_layer(d, L)) ? d.sliding_window : 0;
+    const uint32_t tpt = d.head_dim / 2, n_tl = 256 / tpt;
+    const size_t smem = ((size_t)gs * d.head_dim + (size_t)gs * ATTN_SPLIT + (size_t)n_tl * gs * d.head_dim) * 4;
+    dim3 grid(D->n_splits, d.n_head_kv, batch);
+    auto kern = gs <= 2 ? k_attention<T, 2> : gs <= 4 ? k_attention<T, 4> : k_attention<T, 8>;
+    static bool raised[3][2] = {};
+    bool& r = raised[gs <= 2 ? 0 : gs <= 4 ? 1 : 2][sizeof(T) == 2];
+    if (!r && smem > 48 * 1024) { DCU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); r = true; }
+    kern<<<grid, 256, smem, g.stream>>>(D->q_rot, (const T*)D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
+                                        d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits);
+    count_launch();
+    return ADAMAH_OK;
+}
+
+template <typename T>
+static int launch_rope_t(Decoder* D, uint32_t L, uint32_t batch) {
+    const adam_b200_decoder_desc& d = D->d;
+    KvGeom geo{d.n_layer, d.n_head_kv, d.head_dim, d.page_size, D->max_pages_per_seq, D->page_elems};
+    const int which = is_global_layer(d, L) ? 1 : 0;
+    const Layer& ly = D->layers[L];
+    dim3 grid(d.n_head + 2 * d.n_head_kv, batch);
+    const uint32_t qkv_ld = (d.n_head + 2 * d.n_head_kv) * d.head_dim;
+    k_qk_rope_append<T><<<grid, 128, 0, g.stream>>>(D->qkv, qkv_ld, d.n_head, d.n_head_kv, d.head_dim, ly.norm[NORM_Q], ly.norm[NORM_K],
+                                                     d.norm_eps, D->rope_cos[which], D->rope_sin[which], D->rope_pos[which], D->pos,
+                                                     D->q_rot, (T*)D->kv_pool, geo, D->block_table, L, g.dev_err);
+    count_launch();
+    return ADAMAH_OK;
+}
+
+static int gemv(const Mat& m, const Mat* m2, const float* x, int ldx, float* y, int ldy, int B, int epi) {
+    GemvArgs a = {};
+    a.w0 = m.w; if (m2) a.w1 = m2->w;
+    a.x = x; a.ldx = ldx; a.y = y; a.ldy = ldy; a.N = (int)m.rows; a.K = (int)m.cols; a.B = B; a.epi = epi;
+    return launch_gemv(m.wtype, a, g.stream);
+}
+
+// Enqueue one token step for `batch` sequences on the context stream.
+static int enqueue_step(Decoder* D, uint32_t batch, bool with_lm, bool want_logits) {
+    const adam_b200_decoder_desc& d = D->d;
+    const uint32_t E = d.n_embd, q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim, qkv_ld = q_dim + 2 * k_dim;
+    int rc;
+    if (D->embd.wtype == WT_Q4_0)
+        k_embed<WT_Q4_0><<<batch, 256, 0, g.stream>>>(D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->h, g.dev_err);
+    else
+        k_embed<WT_Q4_K><<<batch, 256, 0, g.stream>>>(D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->h, g.dev_err);
+    count_launch();
+    k_norm_add_norm<<<batch, 256, 0, g.stream>>>(D->h, nullptr, nullptr, D->layers[0].norm[NORM_ATTN], D->normed, E, d.norm_eps);
+    count_launch();
+    for (uint32_t L = 0; L < d.n_layer; ++L) {
+        const Layer& ly = D->layers[L];
+        if (ly.qkv_contiguous) {
+            Mat qkv = ly.m[MAT_Q]; qkv.rows = qkv_ld;
+            if ((rc = gemv(qkv, nullptr, D->normed, E, D->qkv, qkv_ld, batch, EPI_STORE))) return rc;
+        } else {
+            if ((rc = gemv(ly.m[MAT_Q], nullptr, D->normed, E, D->qkv, qkv_ld, batch, EPI_STORE))) return rc;
+            if ((rc = gemv(ly.m[MAT_K], nullptr, D->normed, E, D->qkv + q_dim, qkv_ld, batch, EPI_STORE))) return rc;
+            if ((rc = gemv(ly.m[MAT_V], nullptr, D->normed, E, D->qkv + q_dim + k_dim, qkv_ld, batch, EPI_STORE))) return rc;
+        }
+        rc = d.kv_dtype == 1 ? launch_rope_t<__half>(D, L, batch) : launch_rope_t<float>(D, L, batch);
+        if (rc) return rc;
+        rc = d.kv_dtype == 1 ? launch_attn_t<__half>(D, L, batch) : launch_attn_t<float>(D, L, batch);
+        if (rc) return rc;
+        if ((rc = gemv(ly.m[MAT_O], nullptr, D->attn_out, q_dim, D->proj, E, batch, EPI_STORE))) return rc;
+        k_norm_add_norm<<<batch, 256, 0, g.stream>>>(D->h, D->proj, ly.norm[NORM_POST_ATTN], ly.norm[NORM_FFN], D->normed, E, d.norm_eps);
+        count_launch();
+        if ((rc = gemv(ly.m[MAT_GATE], &ly.m[MAT_UP], D->normed, E, D->act, d.n_ff, batch, d.ffn_act == 0 ? EPI_GEGLU : EPI_SWIGLU))) return rc;
+        if ((rc = gemv(ly.m[MAT_DOWN], nullptr, D->act, d.n_ff, D->proj, E, batch, EPI_STORE))) return rc;
+        const float* next_pre = (L + 1 < d.n_layer) ? D->layers[L + 1].norm[NORM_ATTN] : (with_lm ? D->output_norm : nullptr);
+        k_norm_add_norm<<<batch, 256, 0, g.stream>>>(D->h, D->proj, ly.norm[NORM_POST_FFW], next_pre, D->normed, E, d.norm_eps);
+        count_launch();
+    }
+    if (with_lm) {
+        const Mat& lm = D->output.bound ? D->output : D->embd;
+        GemvArgs a = {};
+        a.w0 = lm.w; a.x = D->normed; a.ldx = E; a.N = (int)lm.rows; a.K = (int)lm.cols; a.B = batch; a.epi = EPI_ARGMAX;
+        a.y = want_logits ? D->logits : nullptr; a.ldy = d.n_vocab; a.softcap = d.final_softcap;
+        a.out_tok = D->cur_tok;
+        if ((rc = argmax_scratch(&a.part_val, &a.part_idx, &a.ticket))) return rc;
+        if ((rc = launch_gemv(lm.wtype, a, g.stream))) return rc;
+    }
+    k_advance<<<(batch + 63) / 64, 64, 0, g.stream>>>(D->pos, D->cur_tok, D->gen_log, d.kv_cap, batch, with_lm ? 1 : 0);
+    count_launch();
+    return check_launch("decoder step");
+}
+
+static int validate_bound(Decoder* D) {
+    const adam_b200_decoder_desc& d = D->d;
+    if (!D->embd.bound) return fail(ADAMAH_ERR_INVALID, "decoder: token_embd is not bound");
+    if (!D->output_norm) return fail(ADAMAH_ERR_INVALID, "decoder: output_norm is not bound");
+    if (!D->rope_cos[0] || !D->rope_cos[1]) return fail(ADAMAH_ERR_INVALID, "decoder: rotary tables are not set");
+    for (uint32_t L = 0; L < d.n_layer; ++L) {
+        Layer& ly = D->layers[L];
+        for (int k = 0; k < 7; ++k) if (!ly.m[k].bound) return fail(ADAMAH_ERR_INVALID, "decoder: layer %u matrix %d is not bound", L, k);
+        if (!ly.norm[NORM_ATTN] || !ly.norm[NORM_FFN]) return fail(ADAMAH_ERR_INVALID, "decoder: layer %u pre-norms are not bound", L);
+        // q, k, v stored back to back -> one wider GEMV (adam/models/engine.py:1612-1661)
+        const Mat &q = ly.m[MAT_Q], &k = ly.m[MAT_K], &v = ly.m[MAT_V];
+        const size_t ipr = q.cols / (q.wtype == WT_Q4_0 ? 32 : 256) * (q.wtype == WT_Q4_0 ? 1 : 9);   // uint4 per row
+        ly.qkv_contiguous = q.wtype == k.wtype && k.wtype == v.wtype && k.w.q == q.w.q + (size_t)q.rows * ipr &&
+                            v.w.q == k.w.q + (size_t)k.rows * ipr;
+    }
+    return ADAMAH_OK;
+}
+
+}  // namespace ab
+
+using namespace ab;
+
+extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint32_t* id_out) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    if (!desc || !id_out) return fail(ADAMAH_ERR_INVALID, "decoder_create: null argument");
+    adam_b200_decoder_desc d = *desc;
+    if (!d.n_layer || !d.n_embd || !d.n_head || !d.n_head_kv || !d.head_dim || !d.n_ff || !d.n_vocab || !d.max_batch || !d.kv_cap)
+        return fail(ADAMAH_ERR_INVALID, "decoder_create: zero dimension");
+    if (d.n_head % d.n_head_kv || d.n_head / d.n_head_kv > 8) return fail(ADAMAH_ERR_INVALID, "decoder_create: unsupported GQA group");
+    if (d.head_dim != 32 && d.head_dim != 64 && d.head_dim != 128 && d.head_dim != 256)
+        return fail(ADAMAH_ERR_INVALID, "decoder_create: head_dim must be 32, 64, 128 or 256");
+    if (d.n_embd % 32 || d.n_ff % 32) return fail(ADAMAH_ERR_INVALID, "decoder_create: widths must be multiples of 32");
+    if (d.kv_dtype > 1) return fail(ADAMAH_ERR_INVALID, "decoder_create: kv_dtype must be 0 (f32) or 1 (f16)");
+    if (d.page_size == 0) d.page_size = 64;
+    if (d.attn_scale == 0.f) d.attn_scale = 1.0f / sqrtf((float)d.head_dim);
+    uint32_t id = MAX_DECODERS;
+    for (uint32_t i = 0; i < MAX_DECODERS; ++i) if (!g_dec[i]) { id = i; break; }
+    if (id == MAX_DECODERS) return fail(ADAMAH_ERR_MEMORY, "decoder table full");
+    Decoder* D = new Decoder();
+    D->d = d;
+    D->layers.resize(d.n_layer);
+    D->max_pages_per_seq = (d.kv_cap + d.page_size - 1) / d.page_size;
+    D->n_pages = d.n_pages ? d.n_pages : D->max_pages_per_seq * d.max_batch;
+    D->d.n_pages = D->n_pages;
+    D->page_elems = (size_t)d.n_layer * 2 * d.n_head_kv * d.page_size * d.head_dim;
+    D->n_splits = (d.kv_cap + ATTN_SPLIT - 1) / ATTN_SPLIT;
+    const size_t B = d.max_batch, E = d.n_embd, q_dim = (size_t)d.n_head * d.head_dim, k_dim = (size_t)d.n_head_kv * d.head_dim;
+    const uint32_t gs = d.n_head / d.n_head_kv;
+    g_dec[id] = D;
+#define DALLOC(p, bytes) do { cudaError_t e__ = cudaMalloc((void**)&(p), (bytes)); if (e__ != cudaSuccess) { destroy(D); g_dec[id] = nullptr; \
+        return fail(ADAMAH_ERR_MEMORY, "decoder_create: cudaMalloc(%zu) failed: %s", (size_t)(bytes), cudaGetErrorString(e__)); } } while (0)
+    DALLOC(D->pos, B * 4); DALLOC(D->cur_tok, B * 4); DALLOC(D->prompt_len, B * 4);
+    DALLOC(D->prompt_tok, B * d.kv_cap * 4); DALLOC(D->gen_log, B * d.kv_cap * 4);
+    DALLOC(D->block_table, B * D->max_pages_per_seq * 4);
+    DALLOC(D->kv_pool, (size_t)D->n_pages * D->page_elems * kv_elem_size(d));
+    DALLOC(D->h, B * E * 4); DALLOC(D->normed, B * E * 4); DALLOC(D->qkv, B * (q_dim + 2 * k_dim) * 4);
+    DALLOC(D->q_rot, B * q_dim * 4); DALLOC(D->attn_out, B * q_dim * 4); DALLOC(D->proj, B * E * 4);
+    DALLOC(D->act, B * d.n_ff * 4); DALLOC(D->logits, B * (size_t)d.n_vocab * 4);
+    DALLOC(D->part_o, B * d.n_head_kv * D->n_splits * gs * d.head_dim * 4);
+    DALLOC(D->part_ml, B * d.n_head_kv * D->n_splits * gs * 2 * 4);
+    DALLOC(D->attn_ticket, B * d.n_head_kv * 4);
+#undef DALLOC
+    cudaMemsetAsync(D->attn_ticket, 0, B * d.n_head_kv * 4, g.stream);
+    cudaMemsetAsync(D->pos, 0, B * 4, g.stream);
+    cudaMemsetAsync(D->cur_tok, 0, B * 4, g.stream);
+    cudaMemsetAsync(D->prompt_len, 0, B * 4, g.stream);
+    cudaMemsetAsync(D->kv_pool, 0, (size_t)D->n_pages * D->page_elems * kv_elem_size(d), g.stream);
+    k_fill_i32<<<(unsigned)((B * D->max_pages_per_seq + 255) / 256), 256, 0, g.stream>>>(D->block_table, -1, B * D->max_pages_per_seq);
+    cudaStreamSynchronize(g.stream);
+    for (uint32_t p = 0; p < D->n_pages; ++p) D->free_pages.push_back(D->n_pages - 1 - p);
+    *id_out = id;
+    return ADAMAH_OK;
+}
+
+extern "C" int adam_b200_decoder_destroy(uint32_t id) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    destroy(D);
+    g_dec[id] = nullptr;
+    return ADAMAH_OK;
+}
+
+extern "C" int adam_b200_decoder_bind_matrix(uint32_t id, uint32_t layer, uint32_t kind, uint32_t map_wt, uint64_t elem_off,
+                                             uint32_t rows, uint32_t cols) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    Map* m = get_map(map_wt);
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (kind >= MAT_KINDS || (kind < MAT_EMBD && layer >= D->d.n_layer)) return fail(ADAMAH_ERR_INVALID, "bind_matrix: bad layer/kind");
+    const adam_b200_decoder_desc& d = D->d;
+    const uint32_t q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim;
+    const uint32_t want_r[MAT_KINDS] = {q_dim, k_dim, k_dim, d.n_embd, d.n_ff, d.n_ff, d.n_embd, d.n_vocab, d.n_vocab};
+    const uint32_t want_c[MAT_KINDS] = {d.n_embd, d.n_embd, d.n_embd, q_dim, d.n_embd, d.n_embd, d.n_ff, d.n_embd, d.n_embd};
+    if (rows != want_r[kind] || cols != want_c[kind])
+        return fail(ADAMAH_ERR_INVALID, "bind_matrix: kind %u expects [%u,%u], got [%u,%u]", kind, want_r[kind], want_c[kind], rows, cols);
+    Mat mt = {};
+    int rc = weight_ref(m, elem_off, (uint64_t)rows * cols, &mt.wtype, &mt.w);
+    if (rc) return rc;
+    if (mt.wtype == WT_Q4_K && cols % 256) return fail(ADAMAH_ERR_INVALID, "bind_matrix: Q4_K needs cols %% 256 == 0");
+    mt.rows = rows; mt.cols = cols; mt.bound = true;
+    if (kind == MAT_EMBD) D->embd = mt; else if (kind == MAT_OUTPUT) D->output = mt; else D->layers[layer].m[kind] = mt;
+    free_graphs(D);
+    return ADAMAH_OK;
+}
+
+extern "C" int adam_b200_decoder_bind_norm(uint32_t id, uint32_t layer, uint32_t kind, uint32_t map_f32, uint64_t elem_off, uint32_t n) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    Map* m = get_map(map_f32);
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (m->dtype != ADAMAH_DTYPE_F32) return fail(ADAMAH_ERR_INVALID, "bind_norm: map %u is not float32", map_f32);
+    if (kind >= NORM_KINDS || (kind != NORM_OUTPUT && layer >= D->d.n_layer)) return fail(ADAMAH_ERR_INVALID, "bind_norm: bad layer/kind");
+    const uint32_t want = (kind == NORM_Q || kind == NORM_K) ? D->d.head_dim : D->d.n_embd;
+    if (n != want) return fail(ADAMAH_ERR_INVALID, "bind_norm: kind %u expects %u weights, got %u", kind, want, n);
+    if (elem_off + n > m->n_elems) return fail(ADAMAH_ERR_INVALID, "bind_norm: range beyond map %u", map_f32);
+    const float* p = (const float*)m->buf + elem_off;
+    if (kind == NORM_OUTPUT) D->output_norm = p; else D->layers[layer].norm[kind] = p;
+    free_graphs(D);
+    return ADAMAH_OK;
+}
+
+extern "C" int adam_b200_decoder_set_rope(uint32_t id, uint32_t which, const float* cos_t, const float* sin_t, uint32_t n_pos, uint32_t half) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (which > 1 || !cos_t || !sin_t || half != D->d.head_dim / 2 || n_pos < D->d.kv_cap)
+        return fail(ADAMAH_ERR_INVALID, "set_rope: need which in {0,1}, half == head_dim/2 and n_pos >= kv_cap");
+    cudaStreamSynchronize(g.stream);
+    cudaFree(D->rope_cos[which]); cudaFree(D->rope_sin[which]);
+    D->rope_cos[which] = D->rope_sin[which] = nullptr;
+    const size_t bytes = (size_t)n_pos * half * 4;
+    DCU(cudaMalloc((void**)&D->rope_cos[which], bytes));
+    DCU(cudaMalloc((void**)&D->rope_sin[which], bytes));
+    DCU(cudaMemcpy(D->rope_cos[which], cos_t, bytes, cudaMemcpyHostToDevice));
+    DCU(cudaMemcpy(D->rope_sin[which], sin_t, bytes, cudaMemcpyHostToDevice));
+    D->rope_pos[which] = n_pos;
+    free_graphs(D);
+    return ADAMAH_OK;
+}
+
+// Start `batch` sequences: prompts (ragged, concatenated) are copied to the
+// device, positions reset to 0, and pages reserved for `reserve[b]` tokens each.
+extern "C" int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_t* prompt_tokens, const uint32_t* prompt_lens,
+                                       const uint32_t* reserve) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    const adam_b200_decoder_desc& d = D->d;
+    if (batch == 0 || batch > d.max_batch || !prompt_lens || !reserve) return fail(ADAMAH_ERR_INVALID, "decoder_begin: bad batch");
+    if (capturing()) return fail(ADAMAH_ERR_INVALID, "decoder_begin: not allowed while a graph is being captured");
+    int rc = validate_bound(D);
+    if (rc) return rc;
+    DCU(cudaStreamSynchronize(g.stream));
+    // return all pages, then reserve
+    D->free_pages.clear();
+    for (uint32_t p = 0; p < D->n_pages; ++p) D->free_pages.push_back(D->n_pages - 1 - p);
+    std::vector<int32_t> bt((size_t)d.max_batch * D->max_pages_per_seq, -1), plen(d.max_batch, 0), ptok((size_t)batch * d.kv_cap, 0);
+    size_t off = 0;
+    for (uint32_t b = 0; b < batch; ++b) {
+        if (prompt_lens[b] == 0 || prompt_lens[b] > d.kv_cap || reserve[b] < prompt_lens[b] || reserve[b] > d.kv_cap)
+            return fail(ADAMAH_ERR_INVALID, "decoder_begin: sequence %u needs 1 <= prompt <= reserve <= kv_cap (%u)", b, d.kv_cap);
+        const uint32_t need = (reserve[b] + d.page_size - 1) / d.page_size;
+        if (need > D->free_pages.size()) return fail(ADAMAH_ERR_MEMORY, "decoder_begin: KV page pool exhausted (%u pages)", D->n_pages);
+        for (uint32_t p = 0; p < need; ++p) { bt[(size_t)b * D->max_pages_per_seq + p] = (int32_t)D->free_pages.back(); D->free_pages.pop_back(); }
+        plen[b] = (int32_t)prompt_lens[b];
+        if (!prompt_tokens) return fail(ADAMAH_ERR_INVALID, "decoder_begin: null prompt");
+        for (uint32_t t = 0; t < prompt_lens[b]; ++t) {
+            const int32_t tk = prompt_tokens[off + t];
+            if (tk < 0 || (uint32_t)tk >= d.n_vocab) return fail(ADAMAH_ERR_INVALID, "decoder_begin: token id %d outside the vocabulary", tk);
+            ptok[(size_t)b * d.kv_cap + t] = tk;
+        }
+        off += prompt_lens[b];
+    }
+    DCU(cudaMemcpyAsync(D->block_table, bt.data(), bt.size() * 4, cudaMemcpyHostToDevice, g.stream));
+    DCU(cudaMemcpyAsync(D->prompt_len, plen.data(), plen.size() * 4, cudaMemcpyHostToDevice, g.stream));
+    DCU(cudaMemcpyAsync(D->prompt_tok, ptok.data(), ptok.size() * 4, cudaMemcpyHostToDevice, g.stream));
+    DCU(cudaMemsetAsync(D->pos, 0, (size_t)d.max_batch * 4, g.stream));
+    DCU(cudaMemsetAsync(D->cur_tok, 0, (size_t)d.max_batch * 4, g.stream));
+    DCU(cudaMemsetAsync(D->gen_log, 0xFF, (size_t)d.max_batch * d.kv_cap * 4, g.stream));
+    DCU(cudaStreamSynchronize(g.stream));
+    D->batch = batch;
+    return ADAMAH_OK;
+}
+
+// Run `n_steps` token steps.  flags bit0: run the LM head + arg-max (the sampled
+// id feeds the next step once the prompt is consumed); bit1: also store the
+// soft-capped logits; bit2: launch kernels directly instead of replaying a graph.
+// Returns without waiting unless called outside batch_begin/batch_end.
+extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t flags) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (D->batch == 0) return fail(ADAMAH_ERR_INVALID, "decoder_step: call decoder_begin first");
+    const bool with_lm = flags & 1u, want_logits = (flags & 2u) != 0, direct = (flags & 4u) != 0;
+    if (want_logits && !with_lm) return fail(ADAMAH_ERR_INVALID, "decoder_step: logits need the LM head flag");
+    int rc = ADAMAH_OK;
+    if (direct || want_logits || capturing()) {
+        for (uint32_t s = 0; s < n_steps && rc == ADAMAH_OK; ++s) rc = enqueue_step(D, D->batch, with_lm, want_logits);
+    } else {
+        const int gi = with_lm ? 1 : 0;
+        if (!D->graph[gi] || D->graph_batch[gi] != D->batch) {
+            if (D->graph[gi]) { cudaGraphExecDestroy(D->graph[gi]); cudaGraphDestroy(D->graph_src[gi]); D->graph[gi] = nullptr; }
+            {   // scratch must exist before the capture starts (no allocation inside it)
+                float* pv; int* pi; unsigned int* tk;
+                if ((rc = argmax_scratch(&pv, &pi, &tk))) return rc;
+            }
+            const uint64_t l0 = g.launches;
+            DCU(cudaStreamSynchronize(g.stream));
+            DCU(cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeRelaxed));
+            rc = enqueue_step(D, D->batch, with_lm, false);
+            cudaGraph_t graph = nullptr;
+            cudaError_t e = cudaStreamEndCapture(g.stream, &graph);
+            if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+            if (e != cudaSuccess) return fail(ADAMAH_ERR_BACKEND, "decoder_step: capture failed: %s", cudaGetErrorString(e));
+            DCU(cudaGraphInstantiate(&D->graph[gi], graph, 0));
+            D->graph_src[gi] = graph;
+            D->graph_batch[gi] = D->batch;
+            D->graph_kernels[gi] = g.launches - l0;
+            g.launches = l0;
+        }
+        for (uint32_t s = 0; s < n_steps; ++s) DCU(cudaGraphLaunch(D->graph[gi], g.stream));
+        count_launch(D->graph_kernels[gi] * n_steps);
+    }
+    end_of_op();
+    return rc;
+}
+
+// Reads (after synchronising): positions, current sampled tokens, and the log of
+// sampled tokens: out_log[b][p] = id sampled for position p (-1 where none).
+extern "C" int adam_b200_decoder_read_state(uint32_t id, int32_t* pos_out, int32_t* cur_tok_out) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (pos_out) DCU(cudaMemcpyAsync(pos_out, D->pos, (size_t)D->d.max_batch * 4, cudaMemcpyDeviceToHost, g.stream));
+    if (cur_tok_out) DCU(cudaMemcpyAsync(cur_tok_out, D->cur_tok, (size_t)D->d.max_batch * 4, cudaMemcpyDeviceToHost, g.stream));
+    DCU(cudaStreamSynchronize(g.stream));
+    return ADAMAH_OK;
+}
+extern "C" int adam_b200_decoder_read_log(uint32_t id, uint32_t seq, uint32_t first_pos, uint32_t n, int32_t* out) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (!out || seq >= D->d.max_batch || (uint64_t)first_pos + n > D->d.kv_cap) return fail(ADAMAH_ERR_INVALID, "decoder_read_log: bad range");
+    DCU(cudaMemcpyAsync(out, D->gen_log + (size_t)seq * D->d.kv_cap + first_pos, (size_t)n * 4, cudaMemcpyDeviceToHost, g.stream));
+    DCU(cudaStreamSynchronize(g.stream));
+    return ADAMAH_OK;
+}
+extern "C" int adam_b200_decoder_read_logits(uint32_t id, uint32_t seq, float* out) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (!out || seq >= D->d.max_batch) return fail(ADAMAH_ERR_INVALID, "decoder_read_logits: bad sequence");
+    DCU(cudaMemcpyAsync(out, D->logits + (size_t)seq * D->d.n_vocab, (size_t)D->d.n_vocab * 4, cudaMemcpyDeviceToHost, g.stream));
+    DCU(cudaStreamSynchronize(g.stream));
+    return ADAMAH_OK;
+}
+// Debug/verification read of an activation buffer of the last step:
+// what = 0 hidden [E], 1 normed [E], 2 qkv, 3 q_rot, 4 attn_out, 5 proj [E], 6 act [FF].
+extern "C" int adam_b200_decoder_read_buffer(uint32_t id, uint32_t what, uint32_t seq, float* out, uint32_t n) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    const adam_b200_decoder_desc& d = D->d;
+    const uint32_t q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim;
+    const float* bufs[7] = {D->h, D->normed, D->qkv, D->q_rot, D->attn_out, D->proj, D->act};
+    const uint32_t lds[7] = {d.n_embd, d.n_embd, q_dim + 2 * k_dim, q_dim, q_dim, d.n_embd, d.n_ff};
+    if (what > 6 || !out || seq >= d.max_batch || n > lds[what]) return fail(ADAMAH_ERR_INVALID, "decoder_read_buffer: bad arguments");
+    DCU(cudaMemcpyAsync(out, bufs[what] + (size_t)seq * lds[what], (size_t)n * 4, cudaMemcpyDeviceToHost, g.stream));
+    DCU(cudaStreamSynchronize(g.stream));
+    return ADAMAH_OK;
+}

@@ -692,7 +692,7 @@ extern "C" int adam_b200_capture_begin(void) {
     if (!ready()) return ADAMAH_ERR_INVALID;
     if (g_capturing) return fail(ADAMAH_ERR_INVALID, "a capture is already open");
     CU(cudaStreamSynchronize(g.stream));
-    CU(cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeThreadLocal));
+    CU(cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeRelaxed));
     g_capturing = true;
     g_capture_launch0 = g.launches;
     g.batch_depth++;                 // ops must not synchronise while capturing

@@ -1,0 +1,302 @@
+"""Model engine with the surface of the reference's ``ADAMEngine``
+(adam/models/engine.py:114-3964): ``ADAMEngine(gpu, cfg, tensors, adamah_mod=A,
+**kw)``, ``generate(token_ids, GenerationConfig, stream=..., **kw) -> (tokens,
+stats)``, ``reset()``.  All device work goes through the backend object's C ABI.
+
+What differs from the reference engine, by design:
+
+* weights arrive as raw GGUF Q4_0 / Q4_K blocks and are uploaded as they are
+  (``map_upload_gguf_blocks``), instead of being re-quantized into the Q4 map with
+  per-group Python loops (engine.py:974-1116);
+* the per-token loop of ~400 backend calls (engine.py:2971-3706) is one fused
+  decoder step replayed from a CUDA graph, positions and sampled ids stay on the
+  device, and the prompt is consumed without host work between tokens;
+* extensions: several independent sequences per step (``generate_batch``), fp16
+  paged KV cache, optional sliding-window mask.
+
+Only greedy decoding is implemented (the reference's ``gpu_matvec_argmax`` sampling
+mode, engine.py:3357-3402, 3793).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import time
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+from . import _lib
+from . import constants as C
+from .config import GenerationConfig, ModelConfig
+from .synth import LAYER_MATS, QTensor
+
+_MAT_KIND = {"attn_q": 0, "attn_k": 1, "attn_v": 2, "attn_output": 3, "ffn_gate": 4, "ffn_up": 5, "ffn_down": 6}
+_NORM_KIND = {"attn_norm": 0, "post_attention_norm": 1, "ffn_norm": 2, "post_ffw_norm": 3, "attn_q_norm": 4, "attn_k_norm": 5}
+_KIND_EMBD, _KIND_OUTPUT, _KIND_OUTPUT_NORM = 7, 8, 6
+
+STEP_LM, STEP_LOGITS, STEP_DIRECT = 1, 2, 4
+
+
+def rope_tables(n_pos: int, head_dim: int, freq_base: float):
+    """cos/sin of the rotary angles for positions 0..n_pos-1, formed exactly as the
+    reference's numpy decoder forms them (tests/diagnostics/diag_inference.py:948-954):
+    float32 inverse frequencies, float32 angle = float32(pos) * freq, float32 cos/sin."""
+    half = head_dim // 2
+    freqs = np.float32(1.0) / (freq_base ** (np.arange(0, half, dtype=np.float32) * np.float32(2.0) / head_dim))
+    theta = np.arange(n_pos, dtype=np.float32)[:, None] * freqs[None, :]
+    return np.ascontiguousarray(np.cos(theta).astype(np.float32)), np.ascontiguousarray(np.sin(theta).astype(np.float32))
+
+
+class ADAMEngine:
+    WS_MAP = 0                       # float32 map: norm weights (the reference's workspace map id)
+    FIRST_WT_MAP = 1                 # GGUF-block maps start here (the reference's Q4 map id)
+
+    def __init__(self, gpu, cfg: ModelConfig, tensors: Dict[str, object], adamah_mod=None, kv_cap: int = 1024,
+                 max_batch: int = 1, kv_dtype: str = "f16", window: bool = False, page_size: int = 64,
+                 n_pages: int = 0, verbose: bool = False, **kw):
+        self.gpu = gpu
+        self.A = adamah_mod if adamah_mod is not None else C
+        self.cfg = cfg
+        self.tensors = tensors
+        self._kv_cap = int(kv_cap)
+        self._max_batch = int(max_batch)
+        self._lib = gpu._lib
+        self.timing: Dict[str, float] = {}
+        self.ws_map_id = self.WS_MAP
+        if not getattr(gpu, "_has_decoder", False):
+            raise RuntimeError("backend has no fused decoder (libadam_b200.so is out of date)")
+        if cfg.head_dim != cfg.head_dim_kv:
+            raise ValueError("head_dim and head_dim_kv must match")
+        self._tied = "output.weight" not in tensors
+        self._upload_all(verbose)
+        desc = _lib.DecoderDesc(
+            n_layer=cfg.n_layer, n_embd=cfg.n_embd, n_head=cfg.n_head, n_head_kv=cfg.n_head_kv, head_dim=cfg.head_dim,
+            n_ff=cfg.n_ff, n_vocab=cfg.n_vocab, ffn_act=0 if cfg.ffn_act == "gelu" else 1,
+            norm_eps=cfg.norm_eps, emb_scale=cfg.emb_scale, attn_softcap=cfg.attn_softcap, final_softcap=cfg.final_softcap,
+            attn_scale=float(np.float32(1.0 / np.sqrt(cfg.head_dim))),
+            sliding_window=cfg.sliding_window, global_every=6 if cfg.arch == "gemma3" else 0,
+            max_batch=self._max_batch, kv_cap=self._kv_cap, kv_dtype={"f32": 0, "f16": 1}[kv_dtype], page_size=page_size,
+            n_pages=n_pages, tp_rank=0, tp_size=1, flags=1 if window else 0)
+        did = ctypes.c_uint32(0)
+        self._check(self._lib.adam_b200_decoder_create(ctypes.byref(desc), ctypes.byref(did)), "adam_b200_decoder_create")
+        self._dec = int(did.value)
+        self._bind_all()
+        for which, base in ((0, cfg.rope_base_local), (1, cfg.rope_base_global)):
+            cos_t, sin_t = rope_tables(self._kv_cap, cfg.head_dim, base)
+            self._check(self._lib.adam_b200_decoder_set_rope(self._dec, which, cos_t.ctypes.data, sin_t.ctypes.data,
+                                                             self._kv_cap, cfg.head_dim // 2), "adam_b200_decoder_set_rope")
+        self._closed = False
+
+    # ---- helpers ---------------------------------------------------------------------
+    def _check(self, rc: int, name: str):
+        if rc != 0:
+            raise RuntimeError(f"{name} failed with code {rc}: {_lib.last_error()}")
+
+    def _upload_all(self, verbose: bool):
+        """Weight layout (role of ``_build_layout`` / ``_upload_all``,
+        engine.py:518, :929): one GGUF-block map per layer holding q,k,v back to back
+        (so QKV is one GEMV), then o, gate, up, down; one map for token_embd (+ output);
+        norm weights in the float32 map."""
+        c, g = self.cfg, self.gpu
+        t0 = time.perf_counter()
+        self._mat_loc: Dict[str, tuple] = {}
+        self._norm_loc: Dict[str, tuple] = {}
+        wtypes = {t.ggml_type for t in self.tensors.values() if isinstance(t, QTensor)}
+        if len(wtypes) != 1:
+            raise ValueError("all matrices must share one GGUF block type")
+        self._ggml_type = wtypes.pop()
+        dt = C.DTYPE_GGUF_Q4_0 if self._ggml_type == C.GGML_TYPE_Q4_0 else C.DTYPE_GGUF_Q4_K
+        next_map = self.FIRST_WT_MAP
+
+        def put(map_id, names):
+            total = sum(self.tensors[n].rows * self.tensors[n].cols for n in names)
+            g.map_create_typed(map_id, dt, 1, total)
+            off = 0
+            for n in names:
+                t = self.tensors[n]
+                g.upload_gguf_blocks(map_id, t.ggml_type, off, t.raw)
+                self._mat_loc[n] = (map_id, off, t.rows, t.cols)
+                off += t.rows * t.cols
+
+        head = ["token_embd.weight"] + ([] if self._tied else ["output.weight"])
+        put(next_map, head)
+        next_map += 1
+        for L in range(c.n_layer):
+            put(next_map, [f"blk.{L}.{m}.weight" for m in LAYER_MATS])
+            next_map += 1
+        self._n_wt_maps = next_map - self.FIRST_WT_MAP
+        norms = [(n, t) for n, t in self.tensors.items() if isinstance(t, np.ndarray)]
+        total = sum(int(t.size) for _, t in norms)
+        g.map_create_typed(self.WS_MAP, C.DTYPE_F32, 1, max(total, 16))
+        off = 0
+        for n, t in norms:
+            g.scatter_contiguous(self.WS_MAP, off, np.ascontiguousarray(t, np.float32).reshape(-1))
+            self._norm_loc[n] = (self.WS_MAP, off, int(t.size))
+            off += int(t.size)
+        if verbose:
+            print(f"[GPU] uploaded {len(self._mat_loc)} matrices, {len(norms)} norm vectors in {time.perf_counter() - t0:.2f}s")
+
+    def _bind_all(self):
+        c, lib, d = self.cfg, self._lib, self._dec
+        m = self._mat_loc["token_embd.weight"]
+        self._check(lib.adam_b200_decoder_bind_matrix(d, 0, _KIND_EMBD, m[0], m[1], m[2], m[3]), "bind token_embd")
+        if not self._tied:
+            m = self._mat_loc["output.weight"]
+            self._check(lib.adam_b200_decoder_bind_matrix(d, 0, _KIND_OUTPUT, m[0], m[1], m[2], m[3]), "bind output")
+        n = self._norm_loc["output_norm.weight"]
+        self._check(lib.adam_b200_decoder_bind_norm(d, 0, _KIND_OUTPUT_NORM, n[0], n[1], n[2]), "bind output_norm")
+        for L in range(c.n_layer):
+            for name, kind in _MAT_KIND.items():
+                m = self._mat_loc[f"blk.{L}.{name}.weight"]
+                self._check(lib.adam_b200_decoder_bind_matrix(d, L, kind, m[0], m[1], m[2], m[3]), f"bind blk.{L}.{name}")
+            for name, kind in _NORM_KIND.items():
+                key = f"blk.{L}.{name}.weight"
+                if key in self._norm_loc:
+                    n = self._norm_loc[key]
+                    self._check(lib.adam_b200_decoder_bind_norm(d, L, kind, n[0], n[1], n[2]), f"bind {key}")
+
+    # ---- low-level stepping ------------------------------------------------------------
+    def begin(self, prompts: Sequence[Sequence[int]], reserve: Sequence[int]):
+        """Start ``len(prompts)`` sequences at position 0 (host prompts are copied to the device here)."""
+        lens = np.array([len(p) for p in prompts], np.uint32)
+        flat = np.ascontiguousarray(np.concatenate([np.asarray(p, np.int32) for p in prompts]), np.int32)
+        res = np.asarray(reserve, np.uint32)
+        self._check(self._lib.adam_b200_decoder_begin(self._dec, len(prompts), flat.ctypes.data, lens.ctypes.data, res.ctypes.data),
+                    "adam_b200_decoder_begin")
+        self._batch = len(prompts)
+        self._h2d_bytes = flat.nbytes + lens.nbytes + res.nbytes
+
+    def step(self, n_steps: int = 1, lm_head: bool = True, logits: bool = False, direct: bool = False):
+        flags = (STEP_LM if lm_head else 0) | (STEP_LOGITS if logits else 0) | (STEP_DIRECT if direct else 0)
+        self._check(self._lib.adam_b200_decoder_step(self._dec, n_steps, flags), "adam_b200_decoder_step")
+
+    def read_state(self):
+        pos = np.empty(self._max_batch, np.int32)
+        tok = np.empty(self._max_batch, np.int32)
+        self._check(self._lib.adam_b200_decoder_read_state(self._dec, pos.ctypes.data, tok.ctypes.data), "adam_b200_decoder_read_state")
+        return pos, tok
+
+    def read_log(self, seq: int, first_pos: int, n: int) -> np.ndarray:
+        out = np.empty(n, np.int32)
+        self._check(self._lib.adam_b200_decoder_read_log(self._dec, seq, first_pos, n, out.ctypes.data), "adam_b200_decoder_read_log")
+        return out
+
+    def read_logits(self, seq: int = 0) -> np.ndarray:
+        out = np.empty(self.cfg.n_vocab, np.float32)
+        self._check(self._lib.adam_b200_decoder_read_logits(self._dec, seq, out.ctypes.data), "adam_b200_decoder_read_logits")
+        return out
+
+    def read_buffer(self, what: int, n: int, seq: int = 0) -> np.ndarray:
+        out = np.empty(n, np.float32)
+        self._check(self._lib.adam_b200_decoder_read_buffer(self._dec, what, seq, out.ctypes.data, n), "adam_b200_decoder_read_buffer")
+        return out
+
+    def logits_trace(self, tokens: Sequence[int], direct: bool = True) -> np.ndarray:
+        """Teacher-forced pass over ``tokens``: the soft-capped logits after every
+        position, ``[len(tokens), n_vocab]`` (for parity checks)."""
+        self.begin([tokens], [len(tokens)])
+        out = np.empty((len(tokens), self.cfg.n_vocab), np.float32)
+        for i in range(len(tokens)):
+            self.step(1, lm_head=True, logits=True, direct=direct)
+            out[i] = self.read_logits(0)
+        return out
+
+    # ---- generate ----------------------------------------------------------------------
+    def _select_sampling_mode(self, config: GenerationConfig) -> str:
+        if not config.is_greedy():
+            raise NotImplementedError("only greedy decoding (top_k == 1 or temperature == 0) is implemented")
+        return "gpu_matvec_argmax"
+
+    def generate_batch(self, prompts: Sequence[Sequence[int]], config: Optional[GenerationConfig] = None, sync_every: int = 1):
+        """Greedy generation for independent sequences (one step advances all of them).
+        Returns (list of token lists, stats).  ``sync_every`` tokens are decoded between
+        host reads of the sampled ids (1 = the reference's per-token read, engine.py:1979)."""
+        config = config or GenerationConfig(top_k=1)
+        mode = self._select_sampling_mode(config)
+        if len(prompts) == 0 or len(prompts) > self._max_batch:
+            raise ValueError(f"need 1..{self._max_batch} prompts")
+        lens = [len(p) for p in prompts]
+        for n in lens:
+            total_needed = n + config.max_tokens
+            if n == 0:
+                raise ValueError("empty prompt")
+            if total_needed > self._kv_cap:
+                raise RuntimeError(f"KV cache too small: need {total_needed} tokens but kv_cap={self._kv_cap}. "
+                                   f"Reinitialize with kv_cap>={total_needed}.")
+        g = self.gpu
+        g.reset_native_stats()
+        tp = time.perf_counter()
+        # all sequences step together, so each needs room up to the longest one's end
+        max_len, min_len = max(lens), min(lens)
+        self.begin(prompts, [max_len + config.max_tokens] * len(prompts))
+        # prefill: every sequence consumes its own prompt; shorter ones start decoding earlier
+        g.batch_begin()
+        if min_len > 1:
+            self.step(min_len - 1, lm_head=False)
+        g.batch_end()
+        t_pre = time.perf_counter() - tp
+        td = time.perf_counter()
+        n_steps = (max_len - min_len) + config.max_tokens          # steps that run the LM head
+        eos = set(int(e) for e in config.eos_token_ids)
+        done_at = [None] * len(prompts)
+        steps_done = 0
+        d2h = 0
+        while steps_done < n_steps:
+            k = min(sync_every, n_steps - steps_done)
+            g.batch_begin()
+            self.step(k, lm_head=True)
+            g.batch_end()
+            steps_done += k
+            # sampled ids of the new positions
+            all_done = True
+            for b, n in enumerate(lens):
+                if done_at[b] is not None:
+                    continue
+                first = max(n, min_len + steps_done - k)
+                last = min(min_len + steps_done, n + config.max_tokens)
+                if last > first:
+                    ids = self.read_log(b, first, last - first)
+                    d2h += ids.nbytes
+                    for j, t in enumerate(ids):
+                        if int(t) in eos:
+                            done_at[b] = first + j
+                            break
+                if done_at[b] is None and min_len + steps_done < n + config.max_tokens:
+                    all_done = False
+            if all_done:
+                break
+        t_dec = time.perf_counter() - td
+        outs: List[List[int]] = []
+        for b, n in enumerate(lens):
+            end = done_at[b] if done_at[b] is not None else min(n + config.max_tokens, min_len + steps_done)
+            ids = self.read_log(b, n, max(0, end - n)) if end > n else np.empty(0, np.int32)
+            outs.append([int(t) for t in ids])
+        ng = sum(len(o) for o in outs)
+        stats = {
+            "n_prompt": sum(lens), "n_prompt_total": sum(lens), "n_prompt_reused": 0, "n_prompt_prefilled": sum(lens),
+            "n_gen": ng, "prefill_s": t_pre, "decode_s": t_dec, "total_s": time.perf_counter() - tp,
+            "prefill_tps": (sum(lens) - len(lens)) / t_pre if t_pre > 0 else 0.0,
+            "decode_tps": ng / t_dec if t_dec > 0 else 0.0,
+            "avg_ms": 1000.0 * t_dec / max(1, steps_done), "sampling_mode": mode, "batch": len(prompts),
+            "h2d_bytes": self._h2d_bytes, "d2h_bytes": d2h, "timing": dict(self.timing),
+            "native_stats": g.get_native_stats(), "trace_summary": {}, "trace_steps": [],
+        }
+        return outs, stats
+
+    def generate(self, token_ids, config: Optional[GenerationConfig] = None, stream: bool = False, **kw):
+        """Single sequence; same return shape as the reference: (tokens, stats dict)
+        (engine.py:3810-3944).  Stops at the first id in ``config.eos_token_ids``."""
+        outs, stats = self.generate_batch([list(token_ids)], config, sync_every=int(kw.get("sync_every", 1)))
+        return outs[0], stats
+
+    def reset(self):
+        """Kept for interface parity (engine.py:3946): sequences restart in ``begin``."""
+        self.timing = {}
+
+    def close(self):
+        if not self._closed:
+            self._closed = True
+            self._lib.adam_b200_decoder_destroy(self._dec)
+            for mid in range(self.FIRST_WT_MAP, self.FIRST_WT_MAP + self._n_wt_maps):
+                self.gpu.map_destroy(mid)

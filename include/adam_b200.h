@@ -223,6 +223,50 @@ int map_dequant_gguf(uint32_t map_wt, uint64_t elem_off, float* out, uint64_t n_
  * models (role of adamah-MAIN/adamah/shaders/src/q4/map_scatter.comp). */
 int adam_b200_quantize_q4_0_dev(const float* w_dev, uint64_t n_elems, void* raw_dev);
 
+/* ---- fused decoder ------------------------------------------------------------
+ * Runs the reference engine's per-token loop (adam/models/engine.py:2971-3706
+ * `_forward`, generate loop :3810-3944) for a batch of sequences as one CUDA
+ * graph per token.  Weights stay in GGUF-block maps and norm weights in a
+ * float32 map; the decoder keeps pointers into them.  Extensions over the
+ * reference: batch > 1, paged fp16/fp32 KV cache, optional sliding-window mask. */
+typedef struct adam_b200_decoder_desc {
+    uint32_t n_layer, n_embd, n_head, n_head_kv, head_dim, n_ff, n_vocab;
+    uint32_t ffn_act;            /* 0 = GeGLU (gelu), 1 = SwiGLU (silu) */
+    float    norm_eps, emb_scale, attn_softcap, final_softcap;
+    float    attn_scale;         /* 0 -> 1/sqrt(head_dim) */
+    uint32_t sliding_window;     /* tokens; used on non-global layers when flags bit 0 is set */
+    uint32_t global_every;       /* layer L is global when (L+1) % global_every == 0; 0 = all global */
+    uint32_t max_batch, kv_cap;
+    uint32_t kv_dtype;           /* 0 = float32, 1 = float16 */
+    uint32_t page_size;          /* tokens per KV page (0 -> 64) */
+    uint32_t n_pages;            /* 0 -> max_batch * ceil(kv_cap / page_size) */
+    uint32_t tp_rank, tp_size;   /* tensor-parallel shard (1 = whole model) */
+    uint32_t flags;              /* bit 0: apply the sliding-window mask */
+} adam_b200_decoder_desc;
+
+int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint32_t* id_out);
+int adam_b200_decoder_destroy(uint32_t id);
+/* kind: 0 attn_q, 1 attn_k, 2 attn_v, 3 attn_output, 4 ffn_gate, 5 ffn_up, 6 ffn_down,
+ * 7 token_embd, 8 output (LM head; token_embd is used when unbound). */
+int adam_b200_decoder_bind_matrix(uint32_t id, uint32_t layer, uint32_t kind, uint32_t map_wt, uint64_t elem_off,
+                                  uint32_t rows, uint32_t cols);
+/* kind: 0 attn_norm, 1 post_attention_norm, 2 ffn_norm, 3 post_ffw_norm, 4 attn_q_norm,
+ * 5 attn_k_norm, 6 output_norm. */
+int adam_b200_decoder_bind_norm(uint32_t id, uint32_t layer, uint32_t kind, uint32_t map_f32, uint64_t elem_off, uint32_t n);
+/* cos/sin of the rotary angles, [n_pos][half] float32, which: 0 = local layers, 1 = global layers. */
+int adam_b200_decoder_set_rope(uint32_t id, uint32_t which, const float* cos_t, const float* sin_t, uint32_t n_pos, uint32_t half);
+/* Start `batch` sequences from position 0.  prompt_tokens holds the prompts back to
+ * back; reserve[b] >= prompt_lens[b] tokens of KV pages are set aside per sequence. */
+int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_t* prompt_tokens, const uint32_t* prompt_lens,
+                            const uint32_t* reserve);
+/* n_steps token steps.  flags: bit 0 LM head + arg-max, bit 1 also store logits,
+ * bit 2 launch kernels directly (no graph replay). */
+int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t flags);
+int adam_b200_decoder_read_state(uint32_t id, int32_t* pos_out, int32_t* cur_tok_out);   /* [max_batch] each, may be NULL */
+int adam_b200_decoder_read_log(uint32_t id, uint32_t seq, uint32_t first_pos, uint32_t n, int32_t* out);
+int adam_b200_decoder_read_logits(uint32_t id, uint32_t seq, float* out);                 /* [n_vocab] */
+int adam_b200_decoder_read_buffer(uint32_t id, uint32_t what, uint32_t seq, float* out, uint32_t n);
+
 #ifdef __cplusplus
 }
 #endif

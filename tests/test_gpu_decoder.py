@@ -1,0 +1,198 @@
+"""Fused decoder against the oracle and against greedy ids produced by the
+unmodified reference (tests/golden/decode_tiny.npz).  Through the C ABI."""
+import os
+from dataclasses import replace
+
+import numpy as np
+import pytest
+
+from adam_b200 import gguf_blocks as gb
+from adam_b200 import synth
+from adam_b200.config import GenerationConfig, tiny_gemma3
+from adam_b200.engine import ADAMEngine
+from oracle.decoder import OracleDecoder, dequant_model
+
+from tests.golden.make_golden import DECODE_CASES
+
+pytestmark = pytest.mark.gpu
+
+GREEDY = dict(top_k=1, temperature=0.0, eos_token_ids=())
+
+
+def _cfg(ckw):
+    cfg = replace(tiny_gemma3(), **ckw)
+    if "head_dim" in ckw:
+        cfg = replace(cfg, head_dim_kv=ckw["head_dim"])
+    return cfg
+
+
+def _rel(a, b):
+    return float(np.abs(a - b).max() / np.abs(b).max())
+
+
+@pytest.mark.parametrize("case", DECODE_CASES, ids=[c[0] for c in DECODE_CASES])
+def test_greedy_ids_equal_reference(gpu, golden_dir, case):
+    """Token ids from the unmodified reference numpy decoder (fp32 KV, no window)."""
+    name, bkw, ckw, n_prompt, n_gen = case
+    g = np.load(os.path.join(golden_dir, "decode_tiny.npz"))
+    cfg = _cfg(ckw)
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, **bkw)
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=64, kv_dtype="f32")
+    try:
+        toks, stats = eng.generate(g[f"{name}_prompt"], GenerationConfig(max_tokens=n_gen, **GREEDY))
+        assert toks == g[f"{name}_tokens"].tolist()
+        assert stats["n_gen"] == n_gen and stats["sampling_mode"] == "gpu_matvec_argmax"
+        assert gpu.device_error() == 0
+    finally:
+        eng.close()
+
+
+@pytest.mark.parametrize("ggml_type,tied", [(gb.GGML_TYPE_Q4_0, True), (gb.GGML_TYPE_Q4_0, False), (gb.GGML_TYPE_Q4_K, False)])
+def test_teacher_forced_logits_match_oracle(gpu, ggml_type, tied):
+    """Every position's logits within 1e-3 (relative to the largest logit), fp32 KV."""
+    cfg = _cfg(dict(n_layer=4))
+    tensors = synth.build_model(cfg, ggml_type, seed=31, tied=tied)
+    toks = synth.random_prompt(cfg.n_vocab, 20, seed=3)
+    dec = OracleDecoder(cfg, dequant_model(tensors), kv_cap=32)
+    ref = np.stack([dec.forward(int(t), i) for i, t in enumerate(toks)])
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=32, kv_dtype="f32")
+    try:
+        out = eng.logits_trace(toks)
+        assert _rel(out, ref) < 1e-3
+        assert _rel(out, ref) < 1e-4          # in practice far inside the budget
+        assert np.array_equal(out.argmax(1), ref.argmax(1))
+        # the hidden state of the last step as well
+        dec.trace = {}
+        dec.reset()
+        for i, t in enumerate(toks):
+            dec.forward(int(t), i)
+        h = eng.read_buffer(0, cfg.n_embd)
+        assert _rel(h, dec.trace[f"hidden.{cfg.n_layer - 1}"]) < 1e-4
+        assert gpu.device_error() == 0
+    finally:
+        eng.close()
+
+
+def test_fp16_kv_matches_oracle_extension(gpu):
+    """KV rounded to fp16 when stored (extension; oracle flag kv_dtype=float16)."""
+    cfg = _cfg(dict(n_layer=3))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=32, tied=False)
+    toks = synth.random_prompt(cfg.n_vocab, 24, seed=4)
+    f32 = dequant_model(tensors)
+    ref16 = OracleDecoder(cfg, f32, kv_cap=32, kv_dtype=np.float16)
+    ref = np.stack([ref16.forward(int(t), i) for i, t in enumerate(toks)])
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=32, kv_dtype="f16")
+    try:
+        out = eng.logits_trace(toks)
+        assert _rel(out, ref) < 1e-3
+        prompt = toks[:8]
+        want, _ = OracleDecoder(cfg, f32, kv_cap=64, kv_dtype=np.float16).generate(prompt, 24)
+        got, _ = eng.generate(prompt, GenerationConfig(max_tokens=24, **GREEDY))
+        assert got == want
+    finally:
+        eng.close()
+
+
+def test_sliding_window_matches_oracle_extension(gpu):
+    """Window mask on non-global layers (extension; oracle flag window=True)."""
+    cfg = _cfg(dict(n_layer=7, sliding_window=8))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=33, tied=False)
+    toks = synth.random_prompt(cfg.n_vocab, 30, seed=5)
+    f32 = dequant_model(tensors)
+    dec = OracleDecoder(cfg, f32, kv_cap=32, window=True)
+    ref = np.stack([dec.forward(int(t), i) for i, t in enumerate(toks)])
+    nowin = OracleDecoder(cfg, f32, kv_cap=32)
+    ref_nw = np.stack([nowin.forward(int(t), i) for i, t in enumerate(toks)])
+    assert _rel(ref, ref_nw) > 1e-2                     # the mask matters at this length
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=32, kv_dtype="f32", window=True)
+    try:
+        assert _rel(eng.logits_trace(toks), ref) < 1e-4
+    finally:
+        eng.close()
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=32, kv_dtype="f32", window=False)   # reference behaviour: no mask
+    try:
+        assert _rel(eng.logits_trace(toks), ref_nw) < 1e-4
+    finally:
+        eng.close()
+
+
+def test_long_context_uses_several_attention_splits_and_pages(gpu):
+    cfg = _cfg(dict(n_layer=2, n_head=4, n_head_kv=2, head_dim=64))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=34, tied=True)
+    n = 600                                               # > 2 splits of 256, 10 pages of 64
+    toks = synth.random_prompt(cfg.n_vocab, n, seed=6)
+    dec = OracleDecoder(cfg, dequant_model(tensors), kv_cap=n + 8)
+    for i, t in enumerate(toks):
+        ref = dec.forward(int(t), i, want_logits=(i == n - 1))
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=n + 8, kv_dtype="f32")
+    try:
+        eng.begin([toks], [n])
+        eng.step(n - 1, lm_head=False)
+        eng.step(1, lm_head=True, logits=True)
+        assert _rel(eng.read_logits(0), ref) < 1e-4
+        assert gpu.device_error() == 0
+    finally:
+        eng.close()
+
+
+def test_batch_of_ragged_prompts_equals_single_sequence_runs(gpu):
+    cfg = _cfg(dict(n_layer=3))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=35, tied=False)
+    f32 = dequant_model(tensors)
+    prompts = [synth.random_prompt(cfg.n_vocab, n, seed=40 + n) for n in (5, 11, 8, 11, 1, 7)]
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=48, kv_dtype="f32", max_batch=6)
+    try:
+        outs, stats = eng.generate_batch(prompts, GenerationConfig(max_tokens=12, **GREEDY))
+        for p, o in zip(prompts, outs):
+            want, _ = OracleDecoder(cfg, f32, kv_cap=48).generate(p, 12)
+            assert o == want
+        assert stats["batch"] == 6 and stats["n_gen"] == 72
+        # fewer host syncs give the same ids
+        outs2, _ = eng.generate_batch(prompts, GenerationConfig(max_tokens=12, **GREEDY), sync_every=5)
+        assert outs2 == outs
+        # and a smaller batch on the same engine still works (graph is rebuilt)
+        outs3, _ = eng.generate_batch(prompts[:2], GenerationConfig(max_tokens=12, **GREEDY))
+        assert outs3 == outs[:2]
+    finally:
+        eng.close()
+
+
+def test_graph_replay_equals_direct_launches(gpu):
+    cfg = _cfg(dict(n_layer=2))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=36)
+    prompt = synth.random_prompt(cfg.n_vocab, 6, seed=7)
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=32)
+    try:
+        eng.begin([prompt], [30])
+        eng.step(5, lm_head=False, direct=True)
+        eng.step(10, lm_head=True, direct=True)
+        a = eng.read_log(0, 6, 10)
+        eng.begin([prompt], [30])
+        gpu.reset_native_stats()
+        eng.step(5, lm_head=False)
+        eng.step(10, lm_head=True)
+        b = eng.read_log(0, 6, 10)
+        assert np.array_equal(a, b) and (a >= 0).all()
+        assert gpu.get_native_stats()["dispatch_count"] > 15 * 8 * cfg.n_layer      # graph nodes are counted
+    finally:
+        eng.close()
+
+
+def test_eos_stops_generation_and_kv_cap_is_enforced(gpu):
+    cfg = _cfg(dict(n_layer=2))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=37, tied=False)
+    prompt = synth.random_prompt(cfg.n_vocab, 6, seed=8)
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=32)
+    try:
+        full, _ = eng.generate(prompt, GenerationConfig(max_tokens=10, **GREEDY))
+        eos = full[4]
+        cut, _ = eng.generate(prompt, GenerationConfig(max_tokens=10, top_k=1, temperature=0.0, eos_token_ids=(eos,)))
+        assert cut == full[:full.index(eos)]
+        with pytest.raises(RuntimeError, match="KV cache too small"):
+            eng.generate(prompt, GenerationConfig(max_tokens=27, **GREEDY))
+        with pytest.raises(NotImplementedError):
+            eng.generate(prompt, GenerationConfig(max_tokens=4))                 # sampled decoding is not implemented
+        with pytest.raises(RuntimeError, match="outside the vocabulary"):
+            eng.begin([[cfg.n_vocab + 3]], [4])
+    finally:
+        eng.close()

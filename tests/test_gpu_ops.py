@@ -250,12 +250,17 @@ def test_rope_and_qk_norm_rope_match_oracle(gpu, pos, base):
     qn = np.stack([od.rms_norm(q[i], qw, 1e-6) for i in range(H)])
     kn = np.stack([od.rms_norm(k[i], kw, 1e-6) for i in range(KV)])
     ref = np.concatenate([od.rope_half(qn, pos, base), od.rope_half(kn, pos, base)])
-    assert np.abs(out - ref).max() < 3e-6 * np.abs(ref).max()
+    # This operator receives only freq_base, so the angle pos*base^(-2i/d) is formed
+    # on the device; numpy's float32 pow is a few ulp off the correctly rounded
+    # value and the angle error grows with pos.  (The fused decoder takes the
+    # host-made angle table instead and is held to a tighter bound.)
+    tol = (3e-6 + 4e-7 * pos) * np.abs(ref).max()
+    assert np.abs(out - ref).max() < tol
     # plain rope over [tokens=1, heads, hd]
     src1, dst1 = _h(gpu, [0]), _h(gpu, [off])
     gpu.map_rope_dev(3, src1, dst1, 1, H, hd, pos, base)
     out = _read(gpu, 3, np.arange(off, off + H * hd)).reshape(H, hd)
-    assert np.abs(out - od.rope_half(q, pos, base)).max() < 3e-6 * np.abs(q).max()
+    assert np.abs(out - od.rope_half(q, pos, base)).max() < (3e-6 + 4e-7 * pos) * np.abs(q).max()
 
 
 def test_attention_ops_match_oracle(gpu):
