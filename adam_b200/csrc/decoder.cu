@@ -46,7 +46,7 @@ struct Decoder {
     int32_t* pos;  int32_t* cur_tok;  int32_t* prompt_len;  int32_t* prompt_tok;  int32_t* gen_log;
     int32_t* block_table; uint32_t max_pages_per_seq, n_pages;
     void* kv_pool; size_t page_elems;
-    float *h, *normed, *qkv, *q_rot, *attn_out, *proj, *act, *logits;
+    float *hbuf[2], *qkv, *attn_out, *proj, *act, *logits; int h_final;
     float *part_o, *part_ml; unsigned int* attn_ticket; uint32_t n_splits;
     uint32_t batch;             // active sequences
     std::vector<uint32_t> free_pages;
@@ -54,7 +54,7 @@ struct Decoder {
 };
 
 constexpr uint32_t MAX_DECODERS = 8;
-constexpr uint32_t ATTN_SPLIT = 256;       // tokens per attention split
+constexpr uint32_t ATTN_SPLIT = 64;        // tokens per attention split
 static Decoder* g_dec[MAX_DECODERS];
 
 static Decoder* get_dec(uint32_t id) {
@@ -159,72 +159,33 @@ __device__ __forceinline__ size_t kv_index(const KvGeom& g, uint32_t page_id, ui
     return (size_t)page_id * g.page_elems + ((((size_t)layer * 2 + kv) * g.n_kv + head) * g.page + slot) * g.hd;
 }
 
-// Per (sequence, row): q rows get per-head RMSNorm + RoPE into q_rot (fp32); k rows
-// the same into the cache; v rows are copied into the cache.
-// (map_qk_norm_rope_x.comp + map_row_copy.comp; diag_inference.py:989-999.)
-template <typename T>
-__global__ void k_qk_rope_append(const float* __restrict__ qkv, uint32_t qkv_ld, uint32_t n_head, uint32_t n_kv, uint32_t hd,
-                                 const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
-                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t, uint32_t n_pos,
-                                 const int32_t* __restrict__ pos, float* __restrict__ q_rot,
-                                 T* __restrict__ kv_pool, KvGeom geo, const int32_t* __restrict__ block_table, uint32_t layer, uint32_t* err) {
-    __shared__ float red[33];
-    const uint32_t b = blockIdx.y, row = blockIdx.x, half = hd / 2;
-    const int32_t p = pos[b];
-    const float* src = qkv + (size_t)b * qkv_ld + (size_t)row * hd;
-    const bool is_q = row < n_head, is_k = !is_q && row < n_head + n_kv;
-    const uint32_t pp = (uint32_t)p < n_pos ? (uint32_t)p : n_pos - 1;
-    if ((uint32_t)p >= n_pos && threadIdx.x == 0) atomicOr(err, DEVERR_OOB_MAP);
-    size_t kv_off = 0;
-    if (!is_q) {
-        const uint32_t head = is_k ? row - n_head : row - n_head - n_kv;
-        const uint32_t page_no = (uint32_t)p / geo.page, slot = (uint32_t)p % geo.page;
-        const int32_t page_id = block_table[(size_t)b * geo.max_pages + (page_no < geo.max_pages ? page_no : 0)];
-        if (page_no >= geo.max_pages || page_id < 0) { if (threadIdx.x == 0) atomicOr(err, DEVERR_OOB_MAP); return; }
-        kv_off = kv_index(geo, (uint32_t)page_id, layer, is_k ? 0u : 1u, head, slot);
-    }
-    if (!is_q && !is_k) {           // V: plain copy
-        for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) st_kv(kv_pool + kv_off + i, src[i]);
-        return;
-    }
-    const float* w = is_q ? q_norm : k_norm;
-    float rms = 1.f;
-    if (w) {
-        float ss = 0.f;
-        for (uint32_t i = threadIdx.x; i < hd; i += blockDim.x) { const float x = src[i]; ss = fmaf(x, x, ss); }
-        ss = block_sum(ss, red);
-        rms = sqrtf(ss / (float)hd + eps);
-    }
-    const float* ct = cos_t + (size_t)pp * half;
-    const float* st = sin_t + (size_t)pp * half;
-    for (uint32_t i = threadIdx.x; i < half; i += blockDim.x) {
-        float x0 = src[i], x1 = src[i + half];
-        if (w) { x0 = __fdiv_rn(x0, rms) * w[i]; x1 = __fdiv_rn(x1, rms) * w[i + half]; }
-        const float c = ct[i], s = st[i];
-        const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-        const float y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
-        if (is_q) { float* dst = q_rot + ((size_t)b * n_head + row) * hd; dst[i] = y0; dst[i + half] = y1; }
-        else { st_kv(kv_pool + kv_off + i, y0); st_kv(kv_pool + kv_off + i + half, y1); }
-    }
-}
-
-// Decode attention for one (split, kv head, sequence): all query heads that share
-// the kv head.  p = softmax(cap*tanh(q.k*scale/cap)) over positions [start, seq);
-// partial (o, m, l) per split, combined by the CTA that finishes last.
-// (map_matmul_t.comp + map_attn_softmax_value.comp; diag_inference.py:1001-1012.)
+// Decode attention for one (split, kv head, sequence), all query heads that share
+// the kv head, with the steps that precede it folded in:
+//   * per-head RMSNorm + half-split RoPE of the query rows (map_qk_norm_rope_x.comp),
+//     angles read from the host-made table;
+//   * the CTA that owns the newest position does the same for the key row and
+//     appends key and value to the paged cache (map_row_copy.comp) before reading it;
+//   * p = softmax(cap*tanh(q.k*scale/cap)) over positions [start, seq), o = p @ V
+//     (map_matmul_t.comp + map_attn_softmax_value.comp; diag_inference.py:989-1012).
+// Long contexts are cut into splits of ATTN_SPLIT positions; every split leaves
+// (o, max, sum) in scratch and the CTA that finishes last merges them.
 template <typename T, int GS_MAX>
-__global__ void __launch_bounds__(256) k_attention(const float* __restrict__ q_rot, const T* __restrict__ kv_pool, KvGeom geo,
+__global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv, uint32_t qkv_ld,
+                                                   const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, uint32_t n_pos,
+                                                   T* __restrict__ kv_pool, KvGeom geo,
                                                    const int32_t* __restrict__ block_table, const int32_t* __restrict__ pos,
                                                    uint32_t n_head, uint32_t layer, uint32_t window, float scale, float cap,
                                                    float* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-                                                   unsigned int* __restrict__ ticket, uint32_t n_splits_max) {
+                                                   unsigned int* __restrict__ ticket, uint32_t n_splits_max, uint32_t* err) {
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[33];
     __shared__ float s_m[GS_MAX], s_l[GS_MAX];
     __shared__ bool s_last;
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const uint32_t hd = geo.hd, gs = n_head / geo.n_kv;
-    const uint32_t seq = (uint32_t)pos[b] + 1;
+    const uint32_t hd = geo.hd, half = hd / 2, gs = n_head / geo.n_kv;
+    const int32_t p = pos[b];
+    const uint32_t seq = (uint32_t)p + 1;
     const uint32_t start = (window > 0 && seq > window) ? seq - window : 0;
     const uint32_t n_act = (seq - start + ATTN_SPLIT - 1) / ATTN_SPLIT;
     if (split >= n_act) return;
@@ -233,11 +194,54 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ q_r
     float* s_sc = sm + gs * hd;                // [gs][ATTN_SPLIT]
     float* s_o = s_sc + gs * ATTN_SPLIT;       // [token lanes][gs][hd] for the PV reduction
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (uint32_t i = tid; i < gs * hd; i += blockDim.x) s_q[i] = q_rot[((size_t)b * n_head + (size_t)kvh * gs) * hd + i];
-    __syncthreads();
+    const int32_t* bt = block_table + (size_t)b * geo.max_pages;
+    const uint32_t pp = (uint32_t)p < n_pos ? (uint32_t)p : n_pos - 1;
+    if ((uint32_t)p >= n_pos && tid == 0) atomicOr(err, DEVERR_OOB_MAP);
+    const float* ct = cos_t + (size_t)pp * half;
+    const float* st = sin_t + (size_t)pp * half;
+    const float* row_q = qkv + (size_t)b * qkv_ld + (size_t)kvh * gs * hd;
+    const float* row_k = qkv + (size_t)b * qkv_ld + (size_t)n_head * hd + (size_t)kvh * hd;
+    const float* row_v = row_k + (size_t)geo.n_kv * hd;
+
+    // ---- a warp per row: query heads, and (newest split only) the key and value rows ----
+    const bool owner = (split == n_act - 1);
+    const uint32_t n_rows = gs + (owner ? 2u : 0u);
+    for (uint32_t r = warp; r < n_rows; r += 8) {
+        const bool is_q = r < gs, is_k = (r == gs);
+        const float* src = is_q ? row_q + (size_t)r * hd : (is_k ? row_k : row_v);
+        size_t kv_off = 0;
+        bool ok = true;
+        if (!is_q) {
+            const uint32_t page_no = (uint32_t)p / geo.page;
+            const int32_t page_id = page_no < geo.max_pages ? bt[page_no] : -1;
+            if (page_id < 0) { ok = false; if (lane == 0) atomicOr(err, DEVERR_OOB_MAP); }
+            else kv_off = kv_index(geo, (uint32_t)page_id, layer, is_k ? 0u : 1u, kvh, (uint32_t)p % geo.page);
+        }
+        if (!is_q && !is_k) {
+            if (ok) for (uint32_t i = lane; i < hd; i += 32) st_kv(kv_pool + kv_off + i, src[i]);
+            continue;
+        }
+        const float* w = is_q ? q_norm : k_norm;
+        float rms = 1.f;
+        if (w) {
+            float ss = 0.f;
+            for (uint32_t i = lane; i < hd; i += 32) { const float x = src[i]; ss = fmaf(x, x, ss); }
+            ss = warp_sum(ss);
+            rms = sqrtf(ss / (float)hd + eps);
+        }
+        for (uint32_t i = lane; i < half; i += 32) {
+            float x0 = src[i], x1 = src[i + half];
+            if (w) { x0 = __fdiv_rn(x0, rms) * w[i]; x1 = __fdiv_rn(x1, rms) * w[i + half]; }
+            const float c = ct[i], s = st[i];
+            const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+            const float y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+            if (is_q) { s_q[r * hd + i] = y0; s_q[r * hd + i + half] = y1; }
+            else if (ok) { st_kv(kv_pool + kv_off + i, y0); st_kv(kv_pool + kv_off + i + half, y1); }
+        }
+    }
+    __syncthreads();            // s_q complete; this CTA's own cache writes are visible to it
 
     // ---- scores: one warp per position, lanes over head_dim ----
-    const int32_t* bt = block_table + (size_t)b * geo.max_pages;
     for (uint32_t t = warp; t < len; t += 8) {
         const uint32_t tp = t0 + t;
         const T* kr = kv_pool + kv_index(geo, (uint32_t)max(bt[tp / geo.page], 0), layer, 0, kvh, tp % geo.page);
@@ -277,6 +281,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ q_r
 #pragma unroll
     for (int g = 0; g < GS_MAX; ++g) { o0[g] = 0.f; o1[g] = 0.f; }
     if (tl < n_tl) {
+#pragma unroll 4
         for (uint32_t t = tl; t < len; t += n_tl) {
             const uint32_t tp = t0 + t;
             const T* vr = kv_pool + kv_index(geo, (uint32_t)max(bt[tp / geo.page], 0), layer, 1, kvh, tp % geo.page);
@@ -348,8 +353,8 @@ static void free_graphs(Decoder* D) {
 static void destroy(Decoder* D) {
     cudaStreamSynchronize(g.stream);
     free_graphs(D);
-    void* ptrs[] = {D->pos, D->cur_tok, D->prompt_len, D->prompt_tok, D->gen_log, D->block_table, D->kv_pool, D->h, D->normed, D->qkv,
-                    D->q_rot, D->attn_out, D->proj, D->act, D->logits, D->part_o, D->part_ml, D->attn_ticket,
+    void* ptrs[] = {D->pos, D->cur_tok, D->prompt_len, D->prompt_tok, D->gen_log, D->block_table, D->kv_pool, D->hbuf[0], D->hbuf[1], D->qkv,
+                    D->attn_out, D->proj, D->act, D->logits, D->part_o, D->part_ml, D->attn_ticket,
                     D->rope_cos[0], D->rope_sin[0], D->rope_cos[1], D->rope_sin[1]};
     for (void* p : ptrs) cudaFree(p);
     delete D;
@@ -373,82 +378,87 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch) {
     const uint32_t window = ((d.flags & 1u) && d.sliding_window > 0 && !is_global_layer(d, L)) ? d.sliding_window : 0;
     const uint32_t tpt = d.head_dim / 2, n_tl = 256 / tpt;
     const size_t smem = ((size_t)gs * d.head_dim + (size_t)gs * ATTN_SPLIT + (size_t)n_tl * gs * d.head_dim) * 4;
-    dim3 grid(D->n_splits, d.n_head_kv, batch);
-    auto kern = gs <= 2 ? k_attention<T, 2> : gs <= 4 ? k_attention<T, 4> : k_attention<T, 8>;
-    static bool raised[3][2] = {};
-    bool& r = raised[gs <= 2 ? 0 : gs <= 4 ? 1 : 2][sizeof(T) == 2];
-    if (!r && smem > 48 * 1024) { DCU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); r = true; }
-    kern<<<grid, 256, smem, g.stream>>>(D->q_rot, (const T*)D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
-                                        d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits);
-    count_launch();
-    return ADAMAH_OK;
-}
-
-template <typename T>
-static int launch_rope_t(Decoder* D, uint32_t L, uint32_t batch) {
-    const adam_b200_decoder_desc& d = D->d;
-    KvGeom geo{d.n_layer, d.n_head_kv, d.head_dim, d.page_size, D->max_pages_per_seq, D->page_elems};
     const int which = is_global_layer(d, L) ? 1 : 0;
     const Layer& ly = D->layers[L];
-    dim3 grid(d.n_head + 2 * d.n_head_kv, batch);
     const uint32_t qkv_ld = (d.n_head + 2 * d.n_head_kv) * d.head_dim;
-    k_qk_rope_append<T><<<grid, 128, 0, g.stream>>>(D->qkv, qkv_ld, d.n_head, d.n_head_kv, d.head_dim, ly.norm[NORM_Q], ly.norm[NORM_K],
-                                                     d.norm_eps, D->rope_cos[which], D->rope_sin[which], D->rope_pos[which], D->pos,
-                                                     D->q_rot, (T*)D->kv_pool, geo, D->block_table, L, g.dev_err);
+    dim3 grid(D->n_splits, d.n_head_kv, batch);
+    auto kern = gs <= 2 ? k_attention<T, 2> : gs <= 4 ? k_attention<T, 4> : k_attention<T, 8>;
+    static bool raised[3] = {};
+    bool& r = raised[gs <= 2 ? 0 : gs <= 4 ? 1 : 2];
+    if (!r && smem > 48 * 1024) { DCU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); r = true; }
+    kern<<<grid, 256, smem, g.stream>>>(D->qkv, qkv_ld, ly.norm[NORM_Q], ly.norm[NORM_K], d.norm_eps,
+                                        D->rope_cos[which], D->rope_sin[which], D->rope_pos[which],
+                                        (T*)D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
+                                        d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, g.dev_err);
     count_launch();
     return ADAMAH_OK;
 }
 
-static int gemv(const Mat& m, const Mat* m2, const float* x, int ldx, float* y, int ldy, int B, int epi) {
-    GemvArgs a = {};
+static int gemv(const Mat& m, const Mat* m2, GemvArgs a, int B, int epi) {
     a.w0 = m.w; if (m2) a.w1 = m2->w;
-    a.x = x; a.ldx = ldx; a.y = y; a.ldy = ldy; a.N = (int)m.rows; a.K = (int)m.cols; a.B = B; a.epi = epi;
+    a.N = (int)m.rows; a.K = (int)m.cols; a.B = B; a.epi = epi;
     return launch_gemv(m.wtype, a, g.stream);
 }
 
-// Enqueue one token step for `batch` sequences on the context stream.
+// Enqueue one token step for `batch` sequences on the context stream.  Five
+// kernels per layer: QKV GEMV (input RMSNorm and, past layer 0, the previous
+// layer's post-FFN norm + residual folded into its prologue), attention (QK-norm,
+// RoPE, KV append folded in), o-proj GEMV, gate/up GEMV (post-attention norm +
+// residual + FFN norm in the prologue, GeGLU in the epilogue), down GEMV.  The
+// residual stream alternates between two buffers because a prologue's CTA 0
+// writes the updated stream while the other CTAs still read the old one.
 static int enqueue_step(Decoder* D, uint32_t batch, bool with_lm, bool want_logits) {
     const adam_b200_decoder_desc& d = D->d;
     const uint32_t E = d.n_embd, q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim, qkv_ld = q_dim + 2 * k_dim;
     int rc;
+    int cur = 0;
     if (D->embd.wtype == WT_Q4_0)
-        k_embed<WT_Q4_0><<<batch, 256, 0, g.stream>>>(D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->h, g.dev_err);
+        k_embed<WT_Q4_0><<<batch, 256, 0, g.stream>>>(D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
     else
-        k_embed<WT_Q4_K><<<batch, 256, 0, g.stream>>>(D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->h, g.dev_err);
-    count_launch();
-    k_norm_add_norm<<<batch, 256, 0, g.stream>>>(D->h, nullptr, nullptr, D->layers[0].norm[NORM_ATTN], D->normed, E, d.norm_eps);
+        k_embed<WT_Q4_K><<<batch, 256, 0, g.stream>>>(D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
     count_launch();
     for (uint32_t L = 0; L < d.n_layer; ++L) {
         const Layer& ly = D->layers[L];
+        GemvArgs in = {};
+        in.ldx = (int)E; in.eps = d.norm_eps; in.h_in = D->hbuf[cur]; in.w_pre = ly.norm[NORM_ATTN];
+        if (L > 0) { in.add_src = D->proj; in.w_post = D->layers[L - 1].norm[NORM_POST_FFW]; in.h_out = D->hbuf[cur ^ 1]; }
+        in.y = D->qkv; in.ldy = (int)qkv_ld;
         if (ly.qkv_contiguous) {
             Mat qkv = ly.m[MAT_Q]; qkv.rows = qkv_ld;
-            if ((rc = gemv(qkv, nullptr, D->normed, E, D->qkv, qkv_ld, batch, EPI_STORE))) return rc;
+            if ((rc = gemv(qkv, nullptr, in, batch, EPI_STORE))) return rc;
         } else {
-            if ((rc = gemv(ly.m[MAT_Q], nullptr, D->normed, E, D->qkv, qkv_ld, batch, EPI_STORE))) return rc;
-            if ((rc = gemv(ly.m[MAT_K], nullptr, D->normed, E, D->qkv + q_dim, qkv_ld, batch, EPI_STORE))) return rc;
-            if ((rc = gemv(ly.m[MAT_V], nullptr, D->normed, E, D->qkv + q_dim + k_dim, qkv_ld, batch, EPI_STORE))) return rc;
+            if ((rc = gemv(ly.m[MAT_Q], nullptr, in, batch, EPI_STORE))) return rc;
+            GemvArgs in2 = in; in2.h_out = nullptr;
+            in2.y = D->qkv + q_dim;
+            if ((rc = gemv(ly.m[MAT_K], nullptr, in2, batch, EPI_STORE))) return rc;
+            in2.y = D->qkv + q_dim + k_dim;
+            if ((rc = gemv(ly.m[MAT_V], nullptr, in2, batch, EPI_STORE))) return rc;
         }
-        rc = d.kv_dtype == 1 ? launch_rope_t<__half>(D, L, batch) : launch_rope_t<float>(D, L, batch);
-        if (rc) return rc;
+        if (L > 0) cur ^= 1;
         rc = d.kv_dtype == 1 ? launch_attn_t<__half>(D, L, batch) : launch_attn_t<float>(D, L, batch);
         if (rc) return rc;
-        if ((rc = gemv(ly.m[MAT_O], nullptr, D->attn_out, q_dim, D->proj, E, batch, EPI_STORE))) return rc;
-        k_norm_add_norm<<<batch, 256, 0, g.stream>>>(D->h, D->proj, ly.norm[NORM_POST_ATTN], ly.norm[NORM_FFN], D->normed, E, d.norm_eps);
-        count_launch();
-        if ((rc = gemv(ly.m[MAT_GATE], &ly.m[MAT_UP], D->normed, E, D->act, d.n_ff, batch, d.ffn_act == 0 ? EPI_GEGLU : EPI_SWIGLU))) return rc;
-        if ((rc = gemv(ly.m[MAT_DOWN], nullptr, D->act, d.n_ff, D->proj, E, batch, EPI_STORE))) return rc;
-        const float* next_pre = (L + 1 < d.n_layer) ? D->layers[L + 1].norm[NORM_ATTN] : (with_lm ? D->output_norm : nullptr);
-        k_norm_add_norm<<<batch, 256, 0, g.stream>>>(D->h, D->proj, ly.norm[NORM_POST_FFW], next_pre, D->normed, E, d.norm_eps);
-        count_launch();
+        GemvArgs o = {};
+        o.x = D->attn_out; o.ldx = (int)q_dim; o.y = D->proj; o.ldy = (int)E;
+        if ((rc = gemv(ly.m[MAT_O], nullptr, o, batch, EPI_STORE))) return rc;
+        GemvArgs gu = {};
+        gu.ldx = (int)E; gu.eps = d.norm_eps; gu.h_in = D->hbuf[cur]; gu.add_src = D->proj; gu.w_post = ly.norm[NORM_POST_ATTN];
+        gu.w_pre = ly.norm[NORM_FFN]; gu.h_out = D->hbuf[cur ^ 1]; gu.y = D->act; gu.ldy = (int)d.n_ff;
+        if ((rc = gemv(ly.m[MAT_GATE], &ly.m[MAT_UP], gu, batch, d.ffn_act == 0 ? EPI_GEGLU : EPI_SWIGLU))) return rc;
+        cur ^= 1;
+        GemvArgs dn = {};
+        dn.x = D->act; dn.ldx = (int)d.n_ff; dn.y = D->proj; dn.ldy = (int)E;
+        if ((rc = gemv(ly.m[MAT_DOWN], nullptr, dn, batch, EPI_STORE))) return rc;
     }
     if (with_lm) {
         const Mat& lm = D->output.bound ? D->output : D->embd;
         GemvArgs a = {};
-        a.w0 = lm.w; a.x = D->normed; a.ldx = E; a.N = (int)lm.rows; a.K = (int)lm.cols; a.B = batch; a.epi = EPI_ARGMAX;
-        a.y = want_logits ? D->logits : nullptr; a.ldy = d.n_vocab; a.softcap = d.final_softcap;
+        a.ldx = (int)E; a.eps = d.norm_eps; a.h_in = D->hbuf[cur]; a.add_src = D->proj;
+        a.w_post = D->layers[d.n_layer - 1].norm[NORM_POST_FFW]; a.w_pre = D->output_norm; a.h_out = D->hbuf[cur ^ 1];
+        a.y = want_logits ? D->logits : nullptr; a.ldy = (int)d.n_vocab; a.softcap = d.final_softcap;
         a.out_tok = D->cur_tok;
         if ((rc = argmax_scratch(&a.part_val, &a.part_idx, &a.ticket))) return rc;
-        if ((rc = launch_gemv(lm.wtype, a, g.stream))) return rc;
+        if ((rc = gemv(lm, nullptr, a, batch, EPI_ARGMAX))) return rc;
+        D->h_final = cur ^ 1;
     }
     k_advance<<<(batch + 63) / 64, 64, 0, g.stream>>>(D->pos, D->cur_tok, D->gen_log, d.kv_cap, batch, with_lm ? 1 : 0);
     count_launch();
@@ -510,8 +520,8 @@ extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint
     DALLOC(D->prompt_tok, B * d.kv_cap * 4); DALLOC(D->gen_log, B * d.kv_cap * 4);
     DALLOC(D->block_table, B * D->max_pages_per_seq * 4);
     DALLOC(D->kv_pool, (size_t)D->n_pages * D->page_elems * kv_elem_size(d));
-    DALLOC(D->h, B * E * 4); DALLOC(D->normed, B * E * 4); DALLOC(D->qkv, B * (q_dim + 2 * k_dim) * 4);
-    DALLOC(D->q_rot, B * q_dim * 4); DALLOC(D->attn_out, B * q_dim * 4); DALLOC(D->proj, B * E * 4);
+    DALLOC(D->hbuf[0], B * E * 4); DALLOC(D->hbuf[1], B * E * 4); DALLOC(D->qkv, B * (q_dim + 2 * k_dim) * 4);
+    DALLOC(D->attn_out, B * q_dim * 4); DALLOC(D->proj, B * E * 4);
     DALLOC(D->act, B * d.n_ff * 4); DALLOC(D->logits, B * (size_t)d.n_vocab * 4);
     DALLOC(D->part_o, B * d.n_head_kv * D->n_splits * gs * d.head_dim * 4);
     DALLOC(D->part_ml, B * d.n_head_kv * D->n_splits * gs * 2 * 4);
@@ -706,15 +716,15 @@ extern "C" int adam_b200_decoder_read_logits(uint32_t id, uint32_t seq, float* o
     return ADAMAH_OK;
 }
 // Debug/verification read of an activation buffer of the last step:
-// what = 0 hidden [E], 1 normed [E], 2 qkv, 3 q_rot, 4 attn_out, 5 proj [E], 6 act [FF].
+// what = 0 hidden after the last layer [E] (steps that ran the LM head), 2 qkv, 4 attn_out, 5 proj [E], 6 act [FF].
 extern "C" int adam_b200_decoder_read_buffer(uint32_t id, uint32_t what, uint32_t seq, float* out, uint32_t n) {
     Decoder* D = get_dec(id);
     if (!D) return ADAMAH_ERR_NOT_FOUND;
     const adam_b200_decoder_desc& d = D->d;
     const uint32_t q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim;
-    const float* bufs[7] = {D->h, D->normed, D->qkv, D->q_rot, D->attn_out, D->proj, D->act};
+    const float* bufs[7] = {D->hbuf[D->h_final], nullptr, D->qkv, nullptr, D->attn_out, D->proj, D->act};
     const uint32_t lds[7] = {d.n_embd, d.n_embd, q_dim + 2 * k_dim, q_dim, q_dim, d.n_embd, d.n_ff};
-    if (what > 6 || !out || seq >= d.max_batch || n > lds[what]) return fail(ADAMAH_ERR_INVALID, "decoder_read_buffer: bad arguments");
+    if (what > 6 || !bufs[what] || !out || seq >= d.max_batch || n > lds[what]) return fail(ADAMAH_ERR_INVALID, "decoder_read_buffer: bad arguments");
     DCU(cudaMemcpyAsync(out, bufs[what] + (size_t)seq * lds[what], (size_t)n * 4, cudaMemcpyDeviceToHost, g.stream));
     DCU(cudaStreamSynchronize(g.stream));
     return ADAMAH_OK;

@@ -60,7 +60,8 @@ static void choose_shape(int units, int n_slots, int sm_count, int* L_out, int* 
 int launch_gemv(int wtype, GemvArgs a, cudaStream_t stream) {
     if (a.N <= 0 || a.K <= 0 || a.B <= 0) return fail(ADAMAH_ERR_INVALID, "gemv: empty shape");
     if (wtype == WT_Q4_0 ? (a.K % 32) : (a.K % 256)) return fail(ADAMAH_ERR_INVALID, "gemv: K=%d is not a whole number of blocks", a.K);
-    if (((uintptr_t)a.x & 15) || (a.ldx & 3)) return fail(ADAMAH_ERR_INVALID, "gemv: activations must be 16-byte aligned");
+    if (!a.h_in && (((uintptr_t)a.x & 15) || (a.ldx & 3))) return fail(ADAMAH_ERR_INVALID, "gemv: activations must be 16-byte aligned");
+    if (a.h_in && a.h_out == a.h_in) return fail(ADAMAH_ERR_INVALID, "gemv: h_out must not alias h_in");
     const int units = (wtype == WT_Q4_0) ? a.K / Geo<WT_Q4_0>::ELEMS : a.K / Geo<WT_Q4_K>::ELEMS;   // work items per row
     const bool pair = (a.epi == EPI_GEGLU || a.epi == EPI_SWIGLU);
     const int n_slots = pair ? a.N : (a.N + 1) / 2;
@@ -76,7 +77,10 @@ int launch_gemv(int wtype, GemvArgs a, cudaStream_t stream) {
         GemvArgs g1 = a;
         g1.B = (a.B - b0 < nb_max) ? a.B - b0 : nb_max;
         const int nb = g1.B == 1 ? 1 : g1.B == 2 ? 2 : 4;
-        g1.x = a.x + (size_t)b0 * a.ldx;
+        if (a.x) g1.x = a.x + (size_t)b0 * a.ldx;
+        if (a.h_in) g1.h_in = a.h_in + (size_t)b0 * a.ldx;
+        if (a.add_src) g1.add_src = a.add_src + (size_t)b0 * a.ldx;
+        if (a.h_out) g1.h_out = a.h_out + (size_t)b0 * a.ldx;
         if (a.y) g1.y = a.y + (size_t)b0 * a.ldy;
         if (a.out_tok) g1.out_tok = a.out_tok + b0;
         if (a.out_tok_f32) g1.out_tok_f32 = a.out_tok_f32 + b0;

@@ -57,6 +57,14 @@ struct GemvArgs {
     float* y; int ldy;              // outputs [B][ldy] (may be NULL for ARGMAX)
     int N, K, B;
     int epi;
+    // Optional fused input chain (replaces x; rows of length K, leading dimension ldx):
+    //   h' = h_in + (add_src ? (w_post ? rms(add_src) * w_post : add_src) : 0)
+    //   x  = w_pre ? rms(h') * w_pre : h'
+    // with rms(v) * w = (v / sqrt(mean(v^2) + eps)) * w.  CTA 0 stores h' to h_out
+    // (must not alias h_in: other CTAs still read it).  This is the reference's
+    // map_rmsnorm_add + map_rmsnorm pair (engine.py:3259, :3267) folded into the
+    // consumer instead of two single-CTA dispatches.
+    const float* h_in; const float* add_src; const float* w_post; const float* w_pre; float* h_out; float eps;
     // ARGMAX epilogue
     float* part_val; int* part_idx; // [B][gridDim.x] scratch
     unsigned int* ticket;           // one counter, zero between launches
@@ -289,11 +297,44 @@ __global__ void __launch_bounds__(256) k_gemv(const GemvArgs a) {
 
     {   // stage activations: group g of GE floats lands at xs[g * GS], its half sums in the pad
         const int n4 = a.K >> 2;
-        for (int b = 0; b < NB; ++b) {
-            const float4* src = reinterpret_cast<const float4*>(a.x + (size_t)min(b, a.B - 1) * a.ldx);
-            for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-                const int e = i * 4;
-                *reinterpret_cast<float4*>(xs + b * xs_ld + (e / GE) * GS + (e % GE)) = src[i];
+        if (a.h_in) {
+            __shared__ float red[33];
+            for (int b = 0; b < NB; ++b) {
+                const size_t row = (size_t)min(b, a.B - 1) * a.ldx;
+                const float* hp = a.h_in + row;
+                const float* ap = a.add_src ? a.add_src + row : nullptr;
+                float* xb = xs + b * xs_ld;
+                float rms_a = 1.f;
+                if (ap && a.w_post) {
+                    float ss = 0.f;
+                    for (int i = threadIdx.x; i < a.K; i += blockDim.x) { const float v = ap[i]; ss = fmaf(v, v, ss); }
+                    ss = block_sum(ss, red);
+                    rms_a = sqrtf(ss / (float)a.K + a.eps);
+                }
+                float ss = 0.f;
+                for (int i = threadIdx.x; i < a.K; i += blockDim.x) {
+                    float v = hp[i];
+                    if (ap) v = v + (a.w_post ? __fdiv_rn(ap[i], rms_a) * a.w_post[i] : ap[i]);
+                    xb[(i / GE) * GS + (i % GE)] = v;
+                    ss = fmaf(v, v, ss);
+                    if (a.h_out && blockIdx.x == 0 && b < a.B) a.h_out[row + i] = v;
+                }
+                if (a.w_pre) {
+                    ss = block_sum(ss, red);
+                    const float rms = sqrtf(ss / (float)a.K + a.eps);
+                    for (int i = threadIdx.x; i < a.K; i += blockDim.x) {
+                        float* p = xb + (i / GE) * GS + (i % GE);
+                        *p = __fdiv_rn(*p, rms) * a.w_pre[i];
+                    }
+                }
+            }
+        } else {
+            for (int b = 0; b < NB; ++b) {
+                const float4* src = reinterpret_cast<const float4*>(a.x + (size_t)min(b, a.B - 1) * a.ldx);
+                for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+                    const int e = i * 4;
+                    *reinterpret_cast<float4*>(xs + b * xs_ld + (e / GE) * GS + (e % GE)) = src[i];
+                }
             }
         }
         __syncthreads();

@@ -115,7 +115,10 @@ class ADAMEngine:
             off = 0
             for n in names:
                 t = self.tensors[n]
-                g.upload_gguf_blocks(map_id, t.ggml_type, off, t.raw)
+                if hasattr(t.raw, "data_ptr"):          # CUDA tensor: blocks already on the device
+                    g.upload_gguf_blocks(map_id, t.ggml_type, off, int(t.raw.data_ptr()), int(t.raw.numel()))
+                else:
+                    g.upload_gguf_blocks(map_id, t.ggml_type, off, t.raw)
                 self._mat_loc[n] = (map_id, off, t.rows, t.cols)
                 off += t.rows * t.cols
 

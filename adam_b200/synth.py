@@ -89,6 +89,55 @@ def build_model(cfg: ModelConfig, ggml_type: int = gb.GGML_TYPE_Q4_0, seed: int 
     return t
 
 
+def build_model_cuda(gpu, cfg: ModelConfig, seed: int = 0, tied: bool = True, norm_noise: float = 0.1) -> Dict[str, Tensor]:
+    """The same kind of model as ``build_model`` (Q4_0 only), generated on the GPU so
+    that billion-weight shapes take seconds: seeded N(0, 0.02) matrices from torch's
+    CUDA generator, quantized to raw Q4_0 blocks by the library's ggml-rule kernel.
+    ``QTensor.raw`` is then a CUDA uint8 tensor (device memory), which the engine
+    uploads without a host round trip.  torch is used for device memory and random
+    numbers only."""
+    import torch
+
+    dev = torch.device("cuda", gpu.device_index)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    rng = np.random.default_rng(seed)
+
+    def mat(rows, cols):
+        w = torch.randn((rows, cols), generator=gen, device=dev, dtype=torch.float32) * 0.02
+        raw = torch.empty(rows * cols // gb.Q4_0_BLOCK * gb.Q4_0_BYTES, dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize(dev)
+        gpu.quantize_q4_0_dev(w.data_ptr(), rows * cols, raw.data_ptr())
+        del w
+        return QTensor(gb.GGML_TYPE_Q4_0, rows, cols, raw)
+
+    def norm(n):
+        return (np.float32(1) + np.float32(norm_noise) * rng.standard_normal(n, dtype=np.float32)).astype(np.float32)
+
+    t: Dict[str, Tensor] = {}
+    t["token_embd.weight"] = mat(cfg.n_vocab, cfg.n_embd)
+    if not tied:
+        t["output.weight"] = mat(cfg.n_vocab, cfg.n_embd)
+    t["output_norm.weight"] = norm(cfg.n_embd)
+    shapes = mat_shapes(cfg)
+    for L in range(cfg.n_layer):
+        p = f"blk.{L}"
+        for n in LAYER_NORMS:
+            t[f"{p}.{n}.weight"] = norm(cfg.n_embd)
+        t[f"{p}.attn_q_norm.weight"] = norm(cfg.head_dim)
+        t[f"{p}.attn_k_norm.weight"] = norm(cfg.head_dim_kv)
+        for n in LAYER_MATS:
+            t[f"{p}.{n}.weight"] = mat(*shapes[n])
+    return t
+
+
+def raw_to_host(t: "QTensor") -> np.ndarray:
+    """Raw GGUF bytes of a tensor as a numpy array, wherever they live."""
+    if isinstance(t.raw, np.ndarray):
+        return t.raw
+    return t.raw.cpu().numpy()
+
+
 def model_weight_elems(cfg: ModelConfig, tied: bool = True) -> int:
     """Number of quantized weights one decoded token reads."""
     per_layer = sum(r * c for r, c in mat_shapes(cfg).values())

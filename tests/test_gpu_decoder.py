@@ -173,7 +173,7 @@ def test_graph_replay_equals_direct_launches(gpu):
         eng.step(10, lm_head=True)
         b = eng.read_log(0, 6, 10)
         assert np.array_equal(a, b) and (a >= 0).all()
-        assert gpu.get_native_stats()["dispatch_count"] > 15 * 8 * cfg.n_layer      # graph nodes are counted
+        assert gpu.get_native_stats()["dispatch_count"] >= 15 * 5 * cfg.n_layer     # graph nodes are counted (5 kernels per layer)
     finally:
         eng.close()
 
