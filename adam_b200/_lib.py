@@ -85,6 +85,7 @@ _SIGS = {
     "map_argmax_dev": (c_int, [u32] * 4),
     "map_resolve_idx_dev": (c_int, [u32] * 5),
     "map_matvec_argmax_t_xq4_dev": (c_int, [u32] * 10),
+    "map_matvec_argmax_t_xq4_static_dev": (c_int, [u32] * 10),
     "adamah_register_decode_plan": (c_int, [u32, POINTER(DecodePlanOp), u32]),
     "adamah_decode_step": (c_int, [u32, u32, u32]),
     "adamah_clear_decode_plan": (None, [u32]),

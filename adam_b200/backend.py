@@ -253,6 +253,18 @@ class Adamah:
                                                           locs_val_tmp_handle, locs_dst_handle, K, N, rows_per_group),
                     "map_matvec_argmax_t_xq4_dev")
 
+    def map_matvec_argmax_t_xq4_static_dev(self, map_act, map_wt, locs_a_handle, locs_b_handle, locs_idx_tmp_handle,
+                                           locs_val_tmp_handle, locs_dst_handle, K, N, rows_per_group=256):
+        """``map_matvec_argmax_t_xq4_dev`` for callers that must not allocate device memory
+        during the call (their own memory pool owns the card, or an allocation's implicit
+        device-wide sync is unacceptable where they call from).  Scratch is a fixed ~32 KB
+        array in the library; N is limited to 4096 * rows_per_group rows, larger N raises.
+        Calls share that array, so do not overlap them; make the first call on a device
+        before any stream capture (it resolves the array's address)."""
+        self._check(self._lib.map_matvec_argmax_t_xq4_static_dev(map_act, map_wt, locs_a_handle, locs_b_handle, locs_idx_tmp_handle,
+                                                                 locs_val_tmp_handle, locs_dst_handle, K, N, rows_per_group),
+                    "map_matvec_argmax_t_xq4_static_dev")
+
     # ---- batching / fusion / stats -------------------------------------------------
     def batch_begin(self):
         self._lib.batch_begin()

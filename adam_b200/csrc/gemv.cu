@@ -103,6 +103,7 @@ int launch_gemv(int wtype, GemvArgs a, cudaStream_t stream) {
         if (grid > need) grid = need;
         if (grid < 1) grid = 1;
         if (a.epi == EPI_ARGMAX && grid > GEMV_MAX_GRID) grid = GEMV_MAX_GRID;
+        if (a.max_grid > 0 && grid > a.max_grid) grid = a.max_grid;
         k<<<grid, block, smem, stream>>>(g1);
         count_launch();
     }

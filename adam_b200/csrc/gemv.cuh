@@ -71,6 +71,7 @@ struct GemvArgs {
     int* out_tok;                   // [B] winning row per batch entry
     float* out_tok_f32;             // optional: same id stored as float (reference convention)
     float softcap;                  // applied to stored logits only (monotone)
+    int max_grid;                   // 0 = launcher's choice; otherwise an upper bound on the CTAs launched
 };
 
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }

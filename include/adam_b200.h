@@ -223,6 +223,24 @@ int map_dequant_gguf(uint32_t map_wt, uint64_t elem_off, float* out, uint64_t n_
  * models (role of adamah-MAIN/adamah/shaders/src/q4/map_scatter.comp). */
 int adam_b200_quantize_q4_0_dev(const float* w_dev, uint64_t n_elems, void* raw_dev);
 
+/* LM head + arg-max that allocates nothing (no counterpart in the reference, whose
+ * callers always hand in their own partial buffers).  Same arguments and result as
+ * map_matvec_argmax_t_xq4_dev, for callers that must not trigger cudaMalloc when they
+ * call in (a serving loop that owns the card's memory through its own pool, a
+ * latency-critical section that cannot afford the device-wide synchronisation an
+ * allocation implies, a process already at its memory cap).  The partial-result
+ * scratch is a fixed array inside the library image: about 32 KB of device memory on
+ * every GPU that loads the library, until the process exits.  Limit: N may not exceed
+ * 4096 * rows_per_group rows (rows_per_group 0 -> 256, i.e. 1,048,576 rows); larger N
+ * returns ADAMAH_ERR_INVALID.  All calls share that one array and it keeps the last
+ * call's contents (the arrival counter is cleared before every launch): calls that
+ * overlap on the GPU race, so issue them from one thread on the library's stream.  The
+ * first call on a device looks up the array's device address; make that call before
+ * starting a stream capture. */
+int map_matvec_argmax_t_xq4_static_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h, uint32_t b_h,
+                                       uint32_t idx_tmp_h, uint32_t val_tmp_h, uint32_t dst_h,
+                                       uint32_t K, uint32_t N, uint32_t rows_per_group);
+
 /* ---- fused decoder ------------------------------------------------------------
  * Runs the reference engine's per-token loop (adam/models/engine.py:2971-3706
  * `_forward`, generate loop :3810-3944) for a batch of sequences as one CUDA
