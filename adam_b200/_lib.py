@@ -114,6 +114,7 @@ _SIGS = {
     "adam_b200_decoder_read_buffer": (c_int, [u32, u32, u32, c_void_p, u32]),
     "map_upload_gguf_blocks": (c_int, [u32, u32, u64, c_void_p, u64]),
     "map_dequant_gguf": (c_int, [u32, u64, c_void_p, u64]),
+    "adam_b200_tensor_tile": (c_int, [u32, u64, u32, u32]),
     "adam_b200_quantize_q4_0_dev": (c_int, [c_void_p, u64, c_void_p]),
 }
 

@@ -385,6 +385,10 @@ class Adamah:
             ptr, nb = self._ptr(a), a.nbytes
         self._check(self._lib.map_upload_gguf_blocks(map_id, ggml_type, elem_off, ptr, nb), "map_upload_gguf_blocks")
 
+    def tile_tensor(self, map_id: int, elem_off: int, rows: int, cols: int):
+        """Register a row-tiled copy of a Q4_0 tensor so GEMVs on it use the tensor-core kernel."""
+        self._check(self._lib.adam_b200_tensor_tile(map_id, elem_off, rows, cols), "adam_b200_tensor_tile")
+
     def dequant_gguf(self, map_id: int, elem_off: int, n_elems: int) -> np.ndarray:
         out = np.empty(n_elems, np.float32)
         self._check(self._lib.map_dequant_gguf(map_id, elem_off, self._ptr(out), n_elems), "map_dequant_gguf")

@@ -13,6 +13,7 @@
 // angles read from a table the host supplies.
 #include "common.cuh"
 #include "gemv.cuh"
+#include "gemv_mma.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -27,12 +28,13 @@ bool capturing();
 enum { MAT_Q = 0, MAT_K, MAT_V, MAT_O, MAT_GATE, MAT_UP, MAT_DOWN, MAT_EMBD, MAT_OUTPUT, MAT_KINDS };
 enum { NORM_ATTN = 0, NORM_POST_ATTN, NORM_FFN, NORM_POST_FFW, NORM_Q, NORM_K, NORM_OUTPUT, NORM_KINDS };
 
-struct Mat { bool bound; int wtype; WeightRef w; uint32_t rows, cols; };
+struct Mat { bool bound; int wtype; WeightRef w; uint32_t rows, cols; uint32_t map_id; uint64_t elem_off; const uint8_t* tiled; };
 
 struct Layer {
     Mat m[7];
     const float* norm[6];       // NORM_ATTN .. NORM_K (NULL = absent)
     bool qkv_contiguous, gateup_pairable;
+    const uint8_t* qkv_tiled;   // row-tiled copy of the q,k,v rows as one tensor
 };
 
 struct Decoder {
@@ -49,6 +51,7 @@ struct Decoder {
     float *hbuf[2], *qkv, *attn_out, *proj, *act, *logits; int h_final;
     float *part_o, *part_ml; unsigned int* attn_ticket; uint32_t n_splits;
     uint32_t batch;             // active sequences
+    bool use_tiles;             // build row-tiled weight copies for the tensor-core GEMV
     std::vector<uint32_t> free_pages;
     cudaGraphExec_t graph[2]; cudaGraph_t graph_src[2]; uint32_t graph_batch[2]; uint64_t graph_kernels[2];
 };
@@ -164,37 +167,96 @@ __device__ __forceinline__ size_t kv_index(const KvGeom& g, uint32_t page_id, ui
 //   * per-head RMSNorm + half-split RoPE of the query rows (map_qk_norm_rope_x.comp),
 //     angles read from the host-made table;
 //   * the CTA that owns the newest position does the same for the key row and
-//     appends key and value to the paged cache (map_row_copy.comp) before reading it;
+//     appends key and value to the paged cache (map_row_copy.comp);
 //   * p = softmax(cap*tanh(q.k*scale/cap)) over positions [start, seq), o = p @ V
 //     (map_matmul_t.comp + map_attn_softmax_value.comp; diag_inference.py:989-1012).
-// Long contexts are cut into splits of ATTN_SPLIT positions; every split leaves
-// (o, max, sum) in scratch and the CTA that finishes last merges them.
-template <typename T, int GS_MAX>
+// A split covers ATTN_SPLIT = 64 positions.  Every thread fetches its slice of the
+// cached K and V rows into registers at the very start (they do not depend on this
+// step's query), so the whole split costs one memory round trip; the newest
+// position is taken from shared memory instead.  Scores: 4 threads per position,
+// each over head_dim/4 dims; PV: 8 dims per thread.  Every split leaves (o, max,
+// sum) in scratch and the CTA that finishes last merges them.
+template <typename T> struct KvCvt;
+template <> struct KvCvt<__half> {
+    static constexpr int EPV = 8;            // elements per uint4
+    static __device__ __forceinline__ void cvt(const uint4& r, float (&f)[8]) {
+        const __half2* h = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 v = __half22float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+    }
+    static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+};
+template <> struct KvCvt<float> {
+    static constexpr int EPV = 4;
+    static __device__ __forceinline__ void cvt(const uint4& r, float (&f)[4]) {
+        f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+    }
+    static __device__ __forceinline__ float round(float v) { return v; }
+};
+
+template <typename T, int GS_MAX, int HD>
 __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv, uint32_t qkv_ld,
                                                    const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
                                                    const float* __restrict__ cos_t, const float* __restrict__ sin_t, uint32_t n_pos,
-                                                   T* __restrict__ kv_pool, KvGeom geo,
+                                                   void* __restrict__ kv_pool_v, KvGeom geo,
                                                    const int32_t* __restrict__ block_table, const int32_t* __restrict__ pos,
                                                    uint32_t n_head, uint32_t layer, uint32_t window, float scale, float cap,
                                                    float* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                                                    unsigned int* __restrict__ ticket, uint32_t n_splits_max, uint32_t* err) {
+    T* __restrict__ kv_pool = reinterpret_cast<T*>(kv_pool_v);
+    constexpr int EPV = KvCvt<T>::EPV;
+    constexpr int QD = HD / 4;                  // dims per thread in the score phase
+    constexpr int NVK = QD / EPV;               // uint4 per thread per key row
+    constexpr int TPT = HD / 8;                 // threads per value row (8 dims each)
+    constexpr int TL = 256 / TPT;               // token lanes in the PV phase
+    constexpr int TPL = (int)ATTN_SPLIT / TL;   // positions per thread in the PV phase
+    constexpr int NVV = 8 / EPV;                // uint4 per thread per value row
+    static_assert(NVK >= 1 && TPL >= 1, "unsupported head_dim");
     extern __shared__ __align__(16) float sm[];
     __shared__ float red[33];
     __shared__ float s_m[GS_MAX], s_l[GS_MAX];
     __shared__ bool s_last;
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const uint32_t hd = geo.hd, half = hd / 2, gs = n_head / geo.n_kv;
+    const uint32_t hd = HD, half = HD / 2, gs = n_head / geo.n_kv;
     const int32_t p = pos[b];
     const uint32_t seq = (uint32_t)p + 1;
     const uint32_t start = (window > 0 && seq > window) ? seq - window : 0;
     const uint32_t n_act = (seq - start + ATTN_SPLIT - 1) / ATTN_SPLIT;
     if (split >= n_act) return;
     const uint32_t t0 = start + split * ATTN_SPLIT, t1 = min(seq, t0 + ATTN_SPLIT), len = t1 - t0;
+    const bool owner = (split == n_act - 1);
     float* s_q = sm;                           // [gs][hd]
-    float* s_sc = sm + gs * hd;                // [gs][ATTN_SPLIT]
-    float* s_o = s_sc + gs * ATTN_SPLIT;       // [token lanes][gs][hd] for the PV reduction
+    float* s_sc = s_q + gs * hd;               // [gs][ATTN_SPLIT]
+    float* s_kn = s_sc + gs * ATTN_SPLIT;      // [hd] newest key (as stored)
+    float* s_vn = s_kn + hd;                   // [hd] newest value (as stored)
+    float* s_o = s_vn + hd;                    // [TL][gs][hd] for the PV reduction
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int32_t* bt = block_table + (size_t)b * geo.max_pages;
+
+    // ---- 1. cached K / V slices of this split into registers ----
+    const uint32_t tk = tid >> 2, part = tid & 3;
+    const bool k_live = tk < len, k_new = k_live && owner && (t0 + tk == (uint32_t)p);
+    uint4 kreg[NVK];
+    if (k_live && !k_new) {
+        const uint32_t tp = t0 + tk;
+        const uint4* kr = reinterpret_cast<const uint4*>(kv_pool + kv_index(geo, (uint32_t)max(bt[tp / geo.page], 0), layer, 0, kvh, tp % geo.page) + part * QD);
+#pragma unroll
+        for (int v = 0; v < NVK; ++v) kreg[v] = kr[v];
+    }
+    const uint32_t tl = tid / TPT, dc = tid % TPT;
+    uint4 vreg[TPL][NVV];
+#pragma unroll
+    for (int j = 0; j < TPL; ++j) {
+        const uint32_t tv = tl + j * TL;
+        if (tv < len && !(owner && t0 + tv == (uint32_t)p)) {
+            const uint32_t tp = t0 + tv;
+            const uint4* vr = reinterpret_cast<const uint4*>(kv_pool + kv_index(geo, (uint32_t)max(bt[tp / geo.page], 0), layer, 1, kvh, tp % geo.page) + dc * 8);
+#pragma unroll
+            for (int v = 0; v < NVV; ++v) vreg[j][v] = vr[v];
+        }
+    }
+
+    // ---- 2. a warp per row: query heads, and (newest split only) the key and value rows ----
     const uint32_t pp = (uint32_t)p < n_pos ? (uint32_t)p : n_pos - 1;
     if ((uint32_t)p >= n_pos && tid == 0) atomicOr(err, DEVERR_OOB_MAP);
     const float* ct = cos_t + (size_t)pp * half;
@@ -202,9 +264,6 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     const float* row_q = qkv + (size_t)b * qkv_ld + (size_t)kvh * gs * hd;
     const float* row_k = qkv + (size_t)b * qkv_ld + (size_t)n_head * hd + (size_t)kvh * hd;
     const float* row_v = row_k + (size_t)geo.n_kv * hd;
-
-    // ---- a warp per row: query heads, and (newest split only) the key and value rows ----
-    const bool owner = (split == n_act - 1);
     const uint32_t n_rows = gs + (owner ? 2u : 0u);
     for (uint32_t r = warp; r < n_rows; r += 8) {
         const bool is_q = r < gs, is_k = (r == gs);
@@ -218,52 +277,90 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             else kv_off = kv_index(geo, (uint32_t)page_id, layer, is_k ? 0u : 1u, kvh, (uint32_t)p % geo.page);
         }
         if (!is_q && !is_k) {
-            if (ok) for (uint32_t i = lane; i < hd; i += 32) st_kv(kv_pool + kv_off + i, src[i]);
+            for (uint32_t i = lane; i < hd; i += 32) {
+                const float v = src[i];
+                s_vn[i] = KvCvt<T>::round(v);
+                if (ok) st_kv(kv_pool + kv_off + i, v);
+            }
             continue;
         }
         const float* w = is_q ? q_norm : k_norm;
+        constexpr int NP = (HD / 2 + 31) / 32;          // rotation pairs per lane
+        float x0[NP], x1[NP];
+#pragma unroll
+        for (int j = 0; j < NP; ++j) {
+            const uint32_t i = lane + 32 * j;
+            x0[j] = i < half ? src[i] : 0.f;
+            x1[j] = i < half ? src[i + half] : 0.f;
+        }
         float rms = 1.f;
         if (w) {
             float ss = 0.f;
-            for (uint32_t i = lane; i < hd; i += 32) { const float x = src[i]; ss = fmaf(x, x, ss); }
+#pragma unroll
+            for (int j = 0; j < NP; ++j) ss = fmaf(x0[j], x0[j], ss);
+#pragma unroll
+            for (int j = 0; j < NP; ++j) ss = fmaf(x1[j], x1[j], ss);
             ss = warp_sum(ss);
             rms = sqrtf(ss / (float)hd + eps);
         }
-        for (uint32_t i = lane; i < half; i += 32) {
-            float x0 = src[i], x1 = src[i + half];
-            if (w) { x0 = __fdiv_rn(x0, rms) * w[i]; x1 = __fdiv_rn(x1, rms) * w[i + half]; }
-            const float c = ct[i], s = st[i];
-            const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-            const float y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
-            if (is_q) { s_q[r * hd + i] = y0; s_q[r * hd + i + half] = y1; }
-            else if (ok) { st_kv(kv_pool + kv_off + i, y0); st_kv(kv_pool + kv_off + i + half, y1); }
-        }
-    }
-    __syncthreads();            // s_q complete; this CTA's own cache writes are visible to it
-
-    // ---- scores: one warp per position, lanes over head_dim ----
-    for (uint32_t t = warp; t < len; t += 8) {
-        const uint32_t tp = t0 + t;
-        const T* kr = kv_pool + kv_index(geo, (uint32_t)max(bt[tp / geo.page], 0), layer, 0, kvh, tp % geo.page);
-        float acc[GS_MAX];
 #pragma unroll
-        for (int g = 0; g < GS_MAX; ++g) acc[g] = 0.f;
-        for (uint32_t d = lane; d < hd; d += 32) {
-            const float kd = ld_kv(kr + d);
-#pragma unroll
-            for (int g = 0; g < GS_MAX; ++g) if (g < (int)gs) acc[g] = fmaf(s_q[g * hd + d], kd, acc[g]);
-        }
-#pragma unroll
-        for (int g = 0; g < GS_MAX; ++g) {
-            if (g < (int)gs) {
-                float v = warp_sum(acc[g]) * scale;
-                if (cap > 0.f) v = tanhf(v / cap) * cap;
-                if (lane == 0) s_sc[g * ATTN_SPLIT + t] = v;
+        for (int j = 0; j < NP; ++j) {
+            const uint32_t i = lane + 32 * j;
+            if (i < half) {
+                float a0 = x0[j], a1 = x1[j];
+                if (w) { a0 = __fdiv_rn(a0, rms) * w[i]; a1 = __fdiv_rn(a1, rms) * w[i + half]; }
+                const float c = ct[i], s = st[i];
+                const float y0 = __fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, s));
+                const float y1 = __fadd_rn(__fmul_rn(a0, s), __fmul_rn(a1, c));
+                if (is_q) { s_q[r * hd + i] = y0; s_q[r * hd + i + half] = y1; }
+                else {
+                    s_kn[i] = KvCvt<T>::round(y0); s_kn[i + half] = KvCvt<T>::round(y1);
+                    if (ok) { st_kv(kv_pool + kv_off + i, y0); st_kv(kv_pool + kv_off + i + half, y1); }
+                }
             }
         }
     }
     __syncthreads();
-    // ---- per-head max and exp-sum over this split ----
+
+    // ---- 3. scores: 4 threads per position ----
+    {
+        float acc[GS_MAX];
+#pragma unroll
+        for (int g = 0; g < GS_MAX; ++g) acc[g] = 0.f;
+        if (k_live) {
+            if (k_new) {
+                for (int i = 0; i < QD; ++i) {
+                    const float kd = s_kn[part * QD + i];
+#pragma unroll
+                    for (int g = 0; g < GS_MAX; ++g) if (g < (int)gs) acc[g] = fmaf(s_q[g * hd + part * QD + i], kd, acc[g]);
+                }
+            } else {
+#pragma unroll
+                for (int v = 0; v < NVK; ++v) {
+                    float kf[EPV];
+                    KvCvt<T>::cvt(kreg[v], kf);
+#pragma unroll
+                    for (int e = 0; e < EPV; ++e) {
+#pragma unroll
+                        for (int g = 0; g < GS_MAX; ++g) if (g < (int)gs) acc[g] = fmaf(s_q[g * hd + part * QD + v * EPV + e], kf[e], acc[g]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < GS_MAX; ++g) {
+            float v = acc[g];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            if (g < (int)gs && k_live && part == 0) {
+                v *= scale;
+                if (cap > 0.f) v = tanhf(v / cap) * cap;
+                s_sc[g * ATTN_SPLIT + tk] = v;
+            }
+        }
+    }
+    __syncthreads();
+    // ---- 4. per-head max and exp-sum over this split ----
     for (uint32_t g = 0; g < gs; ++g) {
         float mx = -3.402823466e+38f;
         for (uint32_t t = tid; t < len; t += blockDim.x) mx = fmaxf(mx, s_sc[g * ATTN_SPLIT + t]);
@@ -274,30 +371,53 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         if (tid == 0) { s_m[g] = mx; s_l[g] = sum; }
     }
     __syncthreads();
-    // ---- o = p @ V: thread owns 2 dims, token lanes stride over positions ----
-    const uint32_t tpt = hd / 2, n_tl = blockDim.x / tpt;      // threads per token, token lanes
-    const uint32_t tl = tid / tpt, dp = (tid % tpt) * 2;
-    float o0[GS_MAX], o1[GS_MAX];
+    // ---- 5. o = p @ V: 8 dims per thread ----
+    {
+        float o[GS_MAX][8];
 #pragma unroll
-    for (int g = 0; g < GS_MAX; ++g) { o0[g] = 0.f; o1[g] = 0.f; }
-    if (tl < n_tl) {
-#pragma unroll 4
-        for (uint32_t t = tl; t < len; t += n_tl) {
-            const uint32_t tp = t0 + t;
-            const T* vr = kv_pool + kv_index(geo, (uint32_t)max(bt[tp / geo.page], 0), layer, 1, kvh, tp % geo.page);
-            const float v0 = ld_kv(vr + dp), v1 = ld_kv(vr + dp + 1);
+        for (int g = 0; g < GS_MAX; ++g)
 #pragma unroll
-            for (int g = 0; g < GS_MAX; ++g) if (g < (int)gs) { const float pz = s_sc[g * ATTN_SPLIT + t]; o0[g] = fmaf(pz, v0, o0[g]); o1[g] = fmaf(pz, v1, o1[g]); }
+            for (int e = 0; e < 8; ++e) o[g][e] = 0.f;
+#pragma unroll
+        for (int j = 0; j < TPL; ++j) {
+            const uint32_t tv = tl + j * TL;
+            if (tv < len) {
+                float vf[8];
+                if (owner && t0 + tv == (uint32_t)p) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) vf[e] = s_vn[dc * 8 + e];
+                } else {
+#pragma unroll
+                    for (int v = 0; v < NVV; ++v) {
+                        float t8[EPV];
+                        KvCvt<T>::cvt(vreg[j][v], t8);
+#pragma unroll
+                        for (int e = 0; e < EPV; ++e) vf[v * EPV + e] = t8[e];
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < GS_MAX; ++g) {
+                    if (g < (int)gs) {
+                        const float pz = s_sc[g * ATTN_SPLIT + tv];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) o[g][e] = fmaf(pz, vf[e], o[g][e]);
+                    }
+                }
+            }
         }
 #pragma unroll
-        for (int g = 0; g < GS_MAX; ++g) if (g < (int)gs) { s_o[(tl * gs + g) * hd + dp] = o0[g]; s_o[(tl * gs + g) * hd + dp + 1] = o1[g]; }
+        for (int g = 0; g < GS_MAX; ++g)
+            if (g < (int)gs)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s_o[(tl * gs + g) * hd + dc * 8 + e] = o[g][e];
     }
     __syncthreads();
     float* po = part_o + (((size_t)b * geo.n_kv + kvh) * n_splits_max + split) * gs * hd;
     float* pml = part_ml + (((size_t)b * geo.n_kv + kvh) * n_splits_max + split) * gs * 2;
     for (uint32_t i = tid; i < gs * hd; i += blockDim.x) {
         float v = 0.f;
-        for (uint32_t l2 = 0; l2 < n_tl; ++l2) v += s_o[l2 * gs * hd + i];
+#pragma unroll 8
+        for (uint32_t l2 = 0; l2 < (uint32_t)TL; ++l2) v += s_o[l2 * gs * hd + i];
         if (n_act == 1) out[((size_t)b * n_head + (size_t)kvh * gs) * hd + i] = v / s_l[i / hd];
         else po[i] = v;
     }
@@ -305,8 +425,8 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     if (tid < gs) { pml[tid * 2] = s_m[tid]; pml[tid * 2 + 1] = s_l[tid]; }
     __threadfence();
     __syncthreads();
-    unsigned int* tk = ticket + (size_t)b * geo.n_kv + kvh;
-    if (tid == 0) s_last = (atomicAdd(tk, 1u) == n_act - 1);
+    unsigned int* tkt = ticket + (size_t)b * geo.n_kv + kvh;
+    if (tid == 0) s_last = (atomicAdd(tkt, 1u) == n_act - 1);
     __syncthreads();
     if (!s_last) return;
     __threadfence();
@@ -324,7 +444,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         }
         out[((size_t)b * n_head + (size_t)kvh * gs) * hd + i] = num / den;
     }
-    if (tid == 0) *tk = 0u;
+    if (tid == 0) *tkt = 0u;
 }
 
 // End of a step: advance positions; when the LM head ran, log the sampled token.
@@ -370,25 +490,37 @@ static bool is_global_layer(const adam_b200_decoder_desc& d, uint32_t L) { retur
 
 static size_t kv_elem_size(const adam_b200_decoder_desc& d) { return d.kv_dtype == 1 ? 2 : 4; }
 
+typedef void (*AttnKernel)(const float*, uint32_t, const float*, const float*, float, const float*, const float*, uint32_t, void*, KvGeom,
+                           const int32_t*, const int32_t*, uint32_t, uint32_t, uint32_t, float, float, float*, float*, float*,
+                           unsigned int*, uint32_t, uint32_t*);
+
+template <typename T, int GS>
+static AttnKernel pick_attn_hd(uint32_t hd) {
+    switch (hd) {
+    case 32: return k_attention<T, GS, 32>;
+    case 64: return k_attention<T, GS, 64>;
+    case 128: return k_attention<T, GS, 128>;
+    default: return k_attention<T, GS, 256>;
+    }
+}
+
 template <typename T>
 static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch) {
     const adam_b200_decoder_desc& d = D->d;
     KvGeom geo{d.n_layer, d.n_head_kv, d.head_dim, d.page_size, D->max_pages_per_seq, D->page_elems};
     const uint32_t gs = d.n_head / d.n_head_kv;
     const uint32_t window = ((d.flags & 1u) && d.sliding_window > 0 && !is_global_layer(d, L)) ? d.sliding_window : 0;
-    const uint32_t tpt = d.head_dim / 2, n_tl = 256 / tpt;
-    const size_t smem = ((size_t)gs * d.head_dim + (size_t)gs * ATTN_SPLIT + (size_t)n_tl * gs * d.head_dim) * 4;
+    const uint32_t n_tl = 256 / (d.head_dim / 8);
+    const size_t smem = ((size_t)gs * d.head_dim + (size_t)gs * ATTN_SPLIT + 2 * (size_t)d.head_dim + (size_t)n_tl * gs * d.head_dim) * 4;
     const int which = is_global_layer(d, L) ? 1 : 0;
     const Layer& ly = D->layers[L];
     const uint32_t qkv_ld = (d.n_head + 2 * d.n_head_kv) * d.head_dim;
     dim3 grid(D->n_splits, d.n_head_kv, batch);
-    auto kern = gs <= 2 ? k_attention<T, 2> : gs <= 4 ? k_attention<T, 4> : k_attention<T, 8>;
-    static bool raised[3] = {};
-    bool& r = raised[gs <= 2 ? 0 : gs <= 4 ? 1 : 2];
-    if (!r && smem > 48 * 1024) { DCU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); r = true; }
+    AttnKernel kern = gs <= 2 ? pick_attn_hd<T, 2>(d.head_dim) : gs <= 4 ? pick_attn_hd<T, 4>(d.head_dim) : pick_attn_hd<T, 8>(d.head_dim);
+    if (smem > 48 * 1024) DCU(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, 256, smem, g.stream>>>(D->qkv, qkv_ld, ly.norm[NORM_Q], ly.norm[NORM_K], d.norm_eps,
                                         D->rope_cos[which], D->rope_sin[which], D->rope_pos[which],
-                                        (T*)D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
+                                        D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
                                         d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, g.dev_err);
     count_launch();
     return ADAMAH_OK;
@@ -397,6 +529,8 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch) {
 static int gemv(const Mat& m, const Mat* m2, GemvArgs a, int B, int epi) {
     a.w0 = m.w; if (m2) a.w1 = m2->w;
     a.N = (int)m.rows; a.K = (int)m.cols; a.B = B; a.epi = epi;
+    if (m.tiled && (!m2 || m2->tiled) && gemv_mma_supports(a))
+        return launch_gemv_mma(m.tiled, m2 ? m2->tiled : nullptr, a, g.stream);
     return launch_gemv(m.wtype, a, g.stream);
 }
 
@@ -424,7 +558,7 @@ static int enqueue_step(Decoder* D, uint32_t batch, bool with_lm, bool want_logi
         if (L > 0) { in.add_src = D->proj; in.w_post = D->layers[L - 1].norm[NORM_POST_FFW]; in.h_out = D->hbuf[cur ^ 1]; }
         in.y = D->qkv; in.ldy = (int)qkv_ld;
         if (ly.qkv_contiguous) {
-            Mat qkv = ly.m[MAT_Q]; qkv.rows = qkv_ld;
+            Mat qkv = ly.m[MAT_Q]; qkv.rows = qkv_ld; qkv.tiled = ly.qkv_tiled;
             if ((rc = gemv(qkv, nullptr, in, batch, EPI_STORE))) return rc;
         } else {
             if ((rc = gemv(ly.m[MAT_Q], nullptr, in, batch, EPI_STORE))) return rc;
@@ -479,6 +613,11 @@ static int validate_bound(Decoder* D) {
         const size_t ipr = q.cols / (q.wtype == WT_Q4_0 ? 32 : 256) * (q.wtype == WT_Q4_0 ? 1 : 9);   // uint4 per row
         ly.qkv_contiguous = q.wtype == k.wtype && k.wtype == v.wtype && k.w.q == q.w.q + (size_t)q.rows * ipr &&
                             v.w.q == k.w.q + (size_t)k.rows * ipr;
+        if (ly.qkv_contiguous && D->use_tiles && q.wtype == WT_Q4_0 && !ly.qkv_tiled) {
+            const uint32_t rows = q.rows + k.rows + v.rows;
+            if (rows % 16 == 0 && q.cols % 64 == 0 && tile_tensor(q.map_id, q.elem_off, rows, q.cols) == ADAMAH_OK)
+                ly.qkv_tiled = (const uint8_t*)find_tiled(q.map_id, q.elem_off, rows, q.cols);
+        }
     }
     return ADAMAH_OK;
 }
@@ -505,6 +644,7 @@ extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint
     if (id == MAX_DECODERS) return fail(ADAMAH_ERR_MEMORY, "decoder table full");
     Decoder* D = new Decoder();
     D->d = d;
+    D->use_tiles = !(d.flags & 2u);
     D->layers.resize(d.n_layer);
     D->max_pages_per_seq = (d.kv_cap + d.page_size - 1) / d.page_size;
     D->n_pages = d.n_pages ? d.n_pages : D->max_pages_per_seq * d.max_batch;
@@ -564,7 +704,12 @@ extern "C" int adam_b200_decoder_bind_matrix(uint32_t id, uint32_t layer, uint32
     int rc = weight_ref(m, elem_off, (uint64_t)rows * cols, &mt.wtype, &mt.w);
     if (rc) return rc;
     if (mt.wtype == WT_Q4_K && cols % 256) return fail(ADAMAH_ERR_INVALID, "bind_matrix: Q4_K needs cols %% 256 == 0");
-    mt.rows = rows; mt.cols = cols; mt.bound = true;
+    mt.rows = rows; mt.cols = cols; mt.bound = true; mt.map_id = map_wt; mt.elem_off = elem_off; mt.tiled = nullptr;
+    // q, k, v get one combined tiled copy later (validate_bound); token_embd is tiled only as the LM head
+    const bool solo = kind == MAT_O || kind == MAT_GATE || kind == MAT_UP || kind == MAT_DOWN || kind == MAT_OUTPUT || kind == MAT_EMBD;
+    if (D->use_tiles && solo && mt.wtype == WT_Q4_0 && rows % 16 == 0 && cols % 64 == 0) {
+        if (tile_tensor(map_wt, elem_off, rows, cols) == ADAMAH_OK) mt.tiled = (const uint8_t*)find_tiled(map_wt, elem_off, rows, cols);
+    }
     if (kind == MAT_EMBD) D->embd = mt; else if (kind == MAT_OUTPUT) D->output = mt; else D->layers[layer].m[kind] = mt;
     free_graphs(D);
     return ADAMAH_OK;

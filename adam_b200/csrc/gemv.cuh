@@ -72,6 +72,7 @@ struct GemvArgs {
     float* out_tok_f32;             // optional: same id stored as float (reference convention)
     float softcap;                  // applied to stored logits only (monotone)
     int max_grid;                   // 0 = launcher's choice; otherwise an upper bound on the CTAs launched
+    uint32_t* err;                  // device error word (set by launch_gemv_mma)
 };
 
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
@@ -253,7 +254,7 @@ __device__ __forceinline__ void consume_slot(const Slot<WT>& s, int it, const fl
 }
 
 template <int WT, int L, int NB>
-__global__ void __launch_bounds__(256) k_gemv(const GemvArgs a) {
+__global__ void __launch_bounds__(256, (WT == WT_Q4_0 && NB == 1) ? 2 : 1) k_gemv(const GemvArgs a) {
     extern __shared__ __align__(16) float xs[];
     __shared__ float s_bv[8 * NB];
     __shared__ int   s_bi[8 * NB];
@@ -305,6 +306,56 @@ __global__ void __launch_bounds__(256) k_gemv(const GemvArgs a) {
                 const float* hp = a.h_in + row;
                 const float* ap = a.add_src ? a.add_src + row : nullptr;
                 float* xb = xs + b * xs_ld;
+                if (n4 <= 3 * (int)blockDim.x) {
+                    // Fast path: every vector this chain touches is fetched up front (at most
+                    // three float4 per thread and vector), so the chain costs two reductions
+                    // and one memory round trip instead of a round trip per loop iteration.
+                    float4 va[3], vh[3], vp[3], vw[3];
+                    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f), o4 = make_float4(1.f, 1.f, 1.f, 1.f);
+#pragma unroll
+                    for (int j = 0; j < 3; ++j) {
+                        const int i = threadIdx.x + j * blockDim.x;
+                        const bool in = i < n4;
+                        vh[j] = in ? reinterpret_cast<const float4*>(hp)[i] : z4;
+                        va[j] = (in && ap) ? reinterpret_cast<const float4*>(ap)[i] : z4;
+                        vp[j] = (in && ap && a.w_post) ? reinterpret_cast<const float4*>(a.w_post)[i] : o4;
+                        vw[j] = (in && a.w_pre) ? reinterpret_cast<const float4*>(a.w_pre)[i] : o4;
+                    }
+                    float rms_a = 1.f;
+                    if (ap && a.w_post) {
+                        float ss = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 3; ++j) { ss = fmaf(va[j].x, va[j].x, ss); ss = fmaf(va[j].y, va[j].y, ss); ss = fmaf(va[j].z, va[j].z, ss); ss = fmaf(va[j].w, va[j].w, ss); }
+                        ss = block_sum(ss, red);
+                        rms_a = sqrtf(ss / (float)a.K + a.eps);
+                    }
+                    float ss = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 3; ++j) {
+                        if (ap) {
+                            if (a.w_post) {
+                                vh[j].x += __fdiv_rn(va[j].x, rms_a) * vp[j].x; vh[j].y += __fdiv_rn(va[j].y, rms_a) * vp[j].y;
+                                vh[j].z += __fdiv_rn(va[j].z, rms_a) * vp[j].z; vh[j].w += __fdiv_rn(va[j].w, rms_a) * vp[j].w;
+                            } else { vh[j].x += va[j].x; vh[j].y += va[j].y; vh[j].z += va[j].z; vh[j].w += va[j].w; }
+                        }
+                        ss = fmaf(vh[j].x, vh[j].x, ss); ss = fmaf(vh[j].y, vh[j].y, ss); ss = fmaf(vh[j].z, vh[j].z, ss); ss = fmaf(vh[j].w, vh[j].w, ss);
+                        const int i = threadIdx.x + j * blockDim.x;
+                        if (i < n4 && a.h_out && blockIdx.x == 0 && b < a.B) reinterpret_cast<float4*>(a.h_out + row)[i] = vh[j];
+                    }
+                    float rms = 1.f;
+                    if (a.w_pre) { ss = block_sum(ss, red); rms = sqrtf(ss / (float)a.K + a.eps); }
+#pragma unroll
+                    for (int j = 0; j < 3; ++j) {
+                        const int i = threadIdx.x + j * blockDim.x;
+                        if (i < n4) {
+                            float4 v = vh[j];
+                            if (a.w_pre) { v.x = __fdiv_rn(v.x, rms) * vw[j].x; v.y = __fdiv_rn(v.y, rms) * vw[j].y; v.z = __fdiv_rn(v.z, rms) * vw[j].z; v.w = __fdiv_rn(v.w, rms) * vw[j].w; }
+                            const int e = i * 4;
+                            *reinterpret_cast<float4*>(xb + (e / GE) * GS + (e % GE)) = v;
+                        }
+                    }
+                    continue;
+                }
                 float rms_a = 1.f;
                 if (ap && a.w_post) {
                     float ss = 0.f;

@@ -33,6 +33,7 @@
 namespace ab {
 
 int weight_ref(const Map* m, uint64_t off, uint64_t n_elems, int* wtype, WeightRef* w);
+int run_gemv(uint32_t map_id, uint64_t off, int wtype, GemvArgs& ga);
 
 constexpr uint32_t NOALLOC_MAX_GROUPS = 4096;
 struct NoAllocScratch {
@@ -103,7 +104,7 @@ extern "C" int map_matvec_argmax_t_xq4_static_dev(uint32_t map_act, uint32_t map
     ga.max_grid = (int)n_groups;                 // one partial slot per CTA, never more than the slots that exist
     ga.x = (const float*)a->buf + ab_; ga.ldx = (int)K; ga.y = nullptr; ga.ldy = (int)N; ga.N = (int)N; ga.K = (int)K; ga.B = 1;
     ga.epi = EPI_ARGMAX; ga.out_tok = nullptr; ga.out_tok_f32 = (float*)a->buf + db;
-    if ((rc = launch_gemv(wtype, ga, g.stream))) return rc;
+    if ((rc = run_gemv(map_wt, bb, wtype, ga))) return rc;
     rc = check_launch("map_matvec_argmax_t_xq4_static_dev");
     end_of_op();
     return rc;

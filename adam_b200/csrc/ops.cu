@@ -5,6 +5,7 @@
 // the two differ (division by the RMS instead of a reciprocal multiply).
 #include "common.cuh"
 #include "gemv.cuh"
+#include "gemv_mma.cuh"
 
 #include <cstring>
 
@@ -348,6 +349,16 @@ int weight_ref(const Map* m, uint64_t off, uint64_t n_elems, int* wtype, WeightR
     return fail(ADAMAH_ERR_INVALID, "map does not hold GGUF blocks");
 }
 
+// Run a GEMV on the tensor at (map, off): the tensor-core kernel when a row-tiled
+// copy of exactly this tensor is registered and the shape fits, the generic one otherwise.
+int run_gemv(uint32_t map_id, uint64_t off, int wtype, GemvArgs& ga) {
+    if (wtype == WT_Q4_0 && ga.epi != EPI_GEGLU && ga.epi != EPI_SWIGLU) {
+        const void* t = find_tiled(map_id, off, (uint32_t)ga.N, (uint32_t)ga.K);
+        if (t && gemv_mma_supports(ga)) return launch_gemv_mma((const uint8_t*)t, nullptr, ga, g.stream);
+    }
+    return launch_gemv(wtype, ga, g.stream);
+}
+
 }  // namespace ab
 
 using namespace ab;
@@ -543,7 +554,7 @@ extern "C" int map_matmul_t_xq4_dev(uint32_t map_act, uint32_t map_wt, uint32_t 
             if (rc) return rc;
             if (ab_ % 4 || K % 4) return fail(ADAMAH_ERR_INVALID, "matmul_t_xq4: activation offset must be a multiple of 4 elements");
             ga.x = x; ga.ldx = K; ga.y = y; ga.ldy = N; ga.N = N; ga.K = K; ga.B = M; ga.epi = EPI_STORE;
-            rc = launch_gemv(wtype, ga, g.stream);
+            rc = run_gemv(map_wt, bb, wtype, ga);
             if (rc) return rc;
         }
     }
@@ -578,7 +589,7 @@ extern "C" int map_matvec_argmax_t_xq4_dev(uint32_t map_act, uint32_t map_wt, ui
     if (rc) return rc;
     ga.x = (const float*)a->buf + ab_; ga.ldx = K; ga.y = nullptr; ga.ldy = N; ga.N = N; ga.K = K; ga.B = 1; ga.epi = EPI_ARGMAX;
     ga.out_tok = nullptr; ga.out_tok_f32 = (float*)a->buf + db;
-    rc = launch_gemv(wtype, ga, g.stream);
+    rc = run_gemv(map_wt, bb, wtype, ga);
     if (rc) return rc;
     rc = check_launch("map_matvec_argmax_t_xq4");
     end_of_op();

@@ -238,7 +238,7 @@ extern "C" int adamah_init_ex(uint64_t, uint64_t) {
 }
 extern "C" int adamah_init(void) { return adamah_init_ex(0, 0); }
 
-namespace ab { void decoder_destroy_all(); void plans_clear_all(); }
+namespace ab { void decoder_destroy_all(); void plans_clear_all(); void tiled_drop_map(uint32_t map_id); }
 
 extern "C" void adamah_shutdown(void) {
     if (!g.inited) return;
@@ -246,6 +246,7 @@ extern "C" void adamah_shutdown(void) {
     cudaStreamSynchronize(g.stream);
     decoder_destroy_all();
     plans_clear_all();
+    tiled_drop_map(0xFFFFFFFFu);
     for (uint32_t i = 0; i < MAX_MAPS; ++i) if (g.maps[i].used) { cudaFree(g.maps[i].buf); cudaFree(g.maps[i].qparams); }
     for (uint32_t i = 0; i < MAX_HANDLES; ++i) if (g.handles[i].used) { cudaFree(g.handles[i].dev); free(g.handles[i].shadow); }
     free(g.handles);
@@ -293,6 +294,7 @@ extern "C" int map_destroy(uint32_t id) {
     Map* m = get_map(id);
     if (!m) return ADAMAH_ERR_NOT_FOUND;
     cudaStreamSynchronize(g.stream);
+    tiled_drop_map(id);
     cudaFree(m->buf);
     cudaFree(m->qparams);
     memset(m, 0, sizeof *m);

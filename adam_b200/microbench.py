@@ -31,7 +31,7 @@ def _peak():
         return 6650.0
 
 
-def _weights(gpu, A, t, N, K, copies):
+def _weights(gpu, A, t, N, K, copies, tile=False):
     dt = A.DTYPE_GGUF_Q4_0 if t == 2 else A.DTYPE_GGUF_Q4_K
     rng = np.random.default_rng(0)
     ru = min(N, 4096)
@@ -40,13 +40,15 @@ def _weights(gpu, A, t, N, K, copies):
     gpu.map_create_typed(1, dt, 1, copies * N * K)
     for c in range(copies):
         gpu.upload_gguf_blocks(1, t, c * N * K, raw)
+        if tile and t == 2 and N % 16 == 0 and K % 64 == 0:
+            gpu.tile_tensor(1, c * N * K, N, K)
     return rng
 
 
-def run_shape(gpu, A, t, N, K, B=1, target_bytes=600e6, reps=5):
+def run_shape(gpu, A, t, N, K, B=1, target_bytes=600e6, reps=5, tile=False):
     wbytes = N * K * 0.5625
     copies = int(min(160, max(1, np.ceil(target_bytes / wbytes))))
-    rng = _weights(gpu, A, t, N, K, copies)
+    rng = _weights(gpu, A, t, N, K, copies, tile)
     gpu.map_create_typed(0, A.DTYPE_F32, 1, B * K + B * N + 8)
     gpu.scatter_contiguous(0, 0, rng.standard_normal(B * K).astype(np.float32))
     a_h = gpu.upload_dev(np.array([0], np.uint32))[0]
@@ -70,7 +72,7 @@ def run_shape(gpu, A, t, N, K, B=1, target_bytes=600e6, reps=5):
     gpu.graph_launch(gid2, 2)
     gpu.batch_begin(); gpu.timer_begin(); gpu.graph_launch(gid2, 1); ms2 = gpu.timer_end(); gpu.batch_end()
     peak = _peak()
-    out = dict(type="Q4_0" if t == 2 else "Q4_K", N=N, K=K, B=B, copies=copies, bytes_per_launch=int(alg),
+    out = dict(type="Q4_0" if t == 2 else "Q4_K", kernel="tensor-core (tiled)" if tile and t == 2 else "generic", N=N, K=K, B=B, copies=copies, bytes_per_launch=int(alg),
                us_per_launch=round(best * 1e3 / copies, 3), GBs=round(gbs, 1), frac_of_measured=round(gbs / peak, 3),
                frac_of_8TBs=round(gbs / 8000, 3), warm_us_per_launch=round(ms2 * 1e3 / 20, 3))
     gpu.graph_destroy(gid); gpu.graph_destroy(gid2)
@@ -80,8 +82,8 @@ def run_shape(gpu, A, t, N, K, B=1, target_bytes=600e6, reps=5):
     return out
 
 
-def run_once(gpu, A, t, N, K, B, reps):
-    rng = _weights(gpu, A, t, N, K, 1)
+def run_once(gpu, A, t, N, K, B, reps, tile=False):
+    rng = _weights(gpu, A, t, N, K, 1, tile)
     gpu.map_create_typed(0, A.DTYPE_F32, 1, B * K + B * N + 8)
     gpu.scatter_contiguous(0, 0, rng.standard_normal(B * K).astype(np.float32))
     a_h = gpu.upload_dev(np.array([0], np.uint32))[0]
@@ -102,16 +104,17 @@ def main():
     ap.add_argument("--k", type=int, default=0)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--reps", type=int, default=4)
+    ap.add_argument("--tile", action="store_true", help="register row-tiled copies (tensor-core kernel for Q4_0)")
     a = ap.parse_args()
     gpu = A.init()
     try:
         if a.cmd == "gemv-once":
-            err = run_once(gpu, A, a.type or 2, a.n or 262144, a.k or 1152, a.batch, a.reps)
+            err = run_once(gpu, A, a.type or 2, a.n or 262144, a.k or 1152, a.batch, a.reps, a.tile)
             print(json.dumps({"ok": err == 0}))
         else:
             shapes = [(a.type, a.n, a.k, a.batch)] if a.type and a.n and a.k else SWEEP
             for s in shapes:
-                print(json.dumps(run_shape(gpu, A, *s)), flush=True)
+                print(json.dumps(run_shape(gpu, A, *s, tile=a.tile)), flush=True)
     finally:
         gpu.shutdown()
 

@@ -215,6 +215,11 @@ int adam_b200_graph_destroy(uint32_t graph_id);
  * (adam/models/engine.py:974-1116); op signatures are unchanged -- weight handles
  * still carry element offsets. */
 int map_upload_gguf_blocks(uint32_t map_wt, uint32_t ggml_type, uint64_t elem_off, const void* raw, uint64_t n_bytes);
+/* Build and register a row-tiled copy of the [rows, cols] Q4_0 tensor at elem_off of a
+ * GGUF Q4_0 map (rows % 16 == 0, cols % 64 == 0).  Later GEMV / arg-max calls on exactly
+ * that tensor run the tensor-core kernel on the copy; results stay within the same
+ * tolerance.  Costs one extra copy of the tensor's bytes; freed with the map. */
+int adam_b200_tensor_tile(uint32_t map_wt, uint64_t elem_off, uint32_t rows, uint32_t cols);
 /* Decode n_elems weights starting at elem_off of a GGUF-block or Q4 map to
  * float32 (host pointer `out`); bit-exact w.r.t. adam/loaders/gguf.py:290-337. */
 int map_dequant_gguf(uint32_t map_wt, uint64_t elem_off, float* out, uint64_t n_elems);
@@ -259,7 +264,7 @@ typedef struct adam_b200_decoder_desc {
     uint32_t page_size;          /* tokens per KV page (0 -> 64) */
     uint32_t n_pages;            /* 0 -> max_batch * ceil(kv_cap / page_size) */
     uint32_t tp_rank, tp_size;   /* tensor-parallel shard (1 = whole model) */
-    uint32_t flags;              /* bit 0: apply the sliding-window mask */
+    uint32_t flags;              /* bit 0: apply the sliding-window mask; bit 1: no row-tiled weight copies */
 } adam_b200_decoder_desc;
 
 int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint32_t* id_out);

@@ -18,12 +18,15 @@ def _bits_equal(a, b):
     return bool(((a.view(np.uint32) == b.view(np.uint32)) | (np.isnan(a) & np.isnan(b))).all())
 
 
-def _gemv(gpu, ggml_type, raw, N, K, x, elem_off=0, pad_elems=0):
-    """y = W x through map_matmul_t_xq4_dev; x is [B,K]."""
+def _gemv(gpu, ggml_type, raw, N, K, x, elem_off=0, pad_elems=0, tile=False):
+    """y = W x through map_matmul_t_xq4_dev; x is [B,K].  ``tile`` registers the row-tiled
+    copy first, which routes the call to the tensor-core kernel."""
     B = x.shape[0]
     dt = A.DTYPE_GGUF_Q4_0 if ggml_type == 2 else A.DTYPE_GGUF_Q4_K
     gpu.map_create_typed(WT, dt, 1, elem_off + N * K + pad_elems)
     gpu.upload_gguf_blocks(WT, ggml_type, elem_off, raw)
+    if tile:
+        gpu.tile_tensor(WT, elem_off, N, K)
     gpu.map_create_typed(WS, A.DTYPE_F32, 1, B * K + B * N + 8)
     gpu.scatter_contiguous(WS, 0, x.reshape(-1))
     a_h, _ = gpu.upload_dev(np.array([0], np.uint32))
@@ -95,6 +98,32 @@ def test_q4_0_gemv(gpu, N, K):
     _check(y, q4_blocks.dequant(raw.reshape(-1), 2, N, K), x)
 
 
+@pytest.mark.parametrize("N,K,B", [(6912, 1152, 1), (1152, 6912, 1), (1536, 1152, 1), (1152, 1024, 1), (16, 64, 1), (48, 128, 1),
+                                   (4096, 1152, 2), (2048, 1152, 3), (1024, 6912, 4), (512, 1152, 7), (64, 21504, 1), (32, 8192, 5)])
+def test_q4_0_gemv_tensor_core_path(gpu, N, K, B):
+    rng = np.random.default_rng(N * 7 + K + B)
+    raw = gb.random_q4_0_blocks(rng, N, K)
+    x = rng.standard_normal((B, K), dtype=np.float32)
+    x[0, :5] = [1e-7, -3e4, 2.5e4, 0.0, -1e-3]            # wide dynamic range in one vector
+    y = _gemv(gpu, 2, raw, N, K, x, tile=True)
+    _check(y, q4_blocks.dequant(raw.reshape(-1), 2, N, K), x)
+    y0 = _gemv(gpu, 2, raw, N, K, x, tile=False)             # same call without the tiled copy
+    assert np.abs(y - y0).max() < 1e-4 * np.abs(y0).max()
+
+
+def test_tensor_core_path_at_offset_and_bad_shapes(gpu):
+    rng = np.random.default_rng(123)
+    N, K = 96, 1152
+    raw = gb.random_q4_0_blocks(rng, N, K)
+    x = rng.standard_normal((1, K), dtype=np.float32)
+    y = _gemv(gpu, 2, raw, N, K, x, elem_off=32 * 6, pad_elems=64, tile=True)
+    _check(y, q4_blocks.dequant(raw.reshape(-1), 2, N, K), x)
+    with pytest.raises(RuntimeError, match="code -3"):
+        gpu.tile_tensor(WT, 32 * 6, 40, K)                   # rows not a multiple of 16
+    with pytest.raises(RuntimeError, match="code -3"):
+        gpu.tile_tensor(WT, 32 * 6, 96, 96)                  # cols not a multiple of 64
+
+
 @pytest.mark.parametrize("N,K", [(5376, 5376), (512, 21504), (2048, 4096), (3, 256), (9, 768), (64, 1024)])
 def test_q4_k_gemv(gpu, N, K):
     rng = np.random.default_rng(N * 17 + K)
@@ -156,12 +185,13 @@ def test_gemv_rejects_bad_arguments(gpu):
     gpu.free_handle(a_h)
 
 
-def test_matvec_argmax_matches_full_logits(gpu):
+@pytest.mark.parametrize("tile", [False, True])
+def test_matvec_argmax_matches_full_logits(gpu, tile):
     rng = np.random.default_rng(11)
     N, K = 20000, 1152
     raw = gb.random_q4_0_blocks(rng, N, K)
     x = rng.standard_normal((1, K), dtype=np.float32)
-    y = _gemv(gpu, 2, raw, N, K, x)[0]
+    y = _gemv(gpu, 2, raw, N, K, x, tile=tile)[0]
     # same maps are still alive: fused LM head + arg-max writes the id as float32
     a_h, _ = gpu.upload_dev(np.array([0], np.uint32))
     b_h, _ = gpu.upload_dev(np.array([0], np.uint32))
