@@ -12,7 +12,7 @@ bool gemv_mma_supports(const GemvArgs& a) {
     if (a.N % 16 || a.K % 64) return false;
     if (a.h_in) { if ((a.K >> 2) > 3 * 256 || (a.ldx & 3)) return false; }
     else if (((uintptr_t)a.x & 15) || (a.ldx & 3)) return false;
-    const size_t smem1 = (size_t)(a.K / 32) * 2 * 64 + 8 * 4 * 3 * 576 + 128;
+    const size_t smem1 = (size_t)(a.K / 32) * (2 * 64 + 4) + 8 * 4 * 3 * 576 + 128;
     return smem1 <= (size_t)MMA_SMEM_LIMIT;
 }
 
@@ -26,7 +26,7 @@ int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream
     const int units = a.K / 32, pairs = a.K / 64, n_rg = a.N / 16;
     // batch rows per pass: 1 (two staged columns) or up to 4 (eight columns)
     int nb_max = 4;
-    while (nb_max > 1 && (size_t)units * nb_max * 2 * 64 + 8 * 4 * 3 * 576 + 128 > (size_t)MMA_SMEM_LIMIT) nb_max >>= 1;
+    while (nb_max > 1 && (size_t)units * nb_max * (2 * 64 + 4) + 8 * 4 * 3 * 576 + 128 > (size_t)MMA_SMEM_LIMIT) nb_max >>= 1;
     for (int b0 = 0; b0 < a.B; b0 += nb_max) {
         GemvArgs g1 = a;
         g1.B = (a.B - b0 < nb_max) ? a.B - b0 : nb_max;
@@ -39,7 +39,7 @@ int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream
         if (a.out_tok_f32) g1.out_tok_f32 = a.out_tok_f32 + b0;
         const int ncol = g1.B == 1 ? 2 : 8;
         const size_t ring_bytes = (size_t)8 * (pair ? 2 : 4) * 3 * 576 * (pair ? 2 : 1);
-        const size_t smem = (((size_t)units * ncol * 64 + 127) & ~(size_t)127) + ring_bytes;
+        const size_t smem = (((size_t)units * (ncol * 64 + (ncol / 2) * 4) + 127) & ~(size_t)127) + ring_bytes;
         g1.err = g.dev_err;
         MmaKernel k = ncol == 2 ? (pair ? k_gemv_mma<2, true> : k_gemv_mma<2, false>) : (pair ? k_gemv_mma<8, true> : k_gemv_mma<8, false>);
         MmaInfo& ki = g_mma_info[ncol == 2 ? 0 : 1][pair ? 1 : 0];

@@ -3,84 +3,86 @@
 // Why tensor cores in a memory-bound GEMV: on the plain CUDA-core path the unpack
 // (one byte-permute per weight, on the half-rate integer pipe) and one FMA per weight
 // cap the kernel at about half of HBM bandwidth.  Here a 16-row x 32-weight block is
-// two mma.sync.m16n8k16 (fp16 in, fp32 accumulate): weights enter as exact fp16
-// integers q-8 (two nibbles per logic op, offset removed by one packed half op), the
-// activation vector enters as the B operand split into fp16 high and low parts
-// (x*s = hi + lo/2048 with a power-of-two scale s chosen per vector so hi never
-// overflows), which keeps 22 bits of every activation; the block's fp32 sums are
-// then scaled by the block scale d on the CUDA cores.  About 0.055 warp instructions
-// per weight instead of 0.114.  The tensor pipe itself stays almost idle: the kernel
-// is still a stream over the weight bytes, bound by HBM.
+// one integer MMA (mma.sync.m16n8k32, u8 x s8 -> s32) per activation operand:
+//   * weights enter as the raw nibbles 0..15 (u8): two logic ops split a 32-bit word
+//     into its four low and four high nibbles, which are exactly the A registers;
+//   * the activation vector is scaled by a power of two s (chosen per vector so that
+//     |x*s| <= 2^22), rounded to an integer and split into three signed bytes
+//     x*s = hi*65536 + mid*256 + lo, i.e. 23 bits of every activation are kept; the
+//     B operand of the first MMA holds the (hi, mid) columns, the second the lo column;
+//   * the block's exact integer sums are recombined in fp32, the -8 offset of Q4_0 is
+//     removed with the pre-summed activations of the block, and the result is scaled
+//     by the block scale d and accumulated in fp32 on the CUDA cores.
+// The tensor pipe stays almost idle: the kernel is a stream over the weight bytes.
 //
-// Columns of the 8-wide B operand: (2b, 2b+1) = (hi, lo) of batch row b, b < 4.  With
-// one batch row only columns 0,1 are staged (NCOL = 2) and the rest are zero.
+// Columns of the 8-wide B operand: (2b, 2b+1) = (hi, mid) [first MMA] or (lo, 0)
+// [second MMA] of batch row b, b < 4.  With one batch row only columns 0,1 are staged.
 // A warp owns one 16-row group and a slice of K; the KS warps that share a row group
 // combine through shared memory.  Lane (g, t) = (lane/4, lane%4) holds rows g and g+8
-// for batch row t.  k-order inside a block is permuted consistently in A and B so that
-// each lane's A registers come from one 32-bit word of each of its two rows.
+// for batch row t.  Weight tiles reach shared memory through a per-warp ring of bulk
+// copies (cp.async.bulk + mbarrier), so no load scoreboard limits the bytes in flight.
 #pragma once
 #include "common.cuh"
 #include "gemv.cuh"
 
 namespace ab {
 
-constexpr float MMA_LO_SCALE = 2048.0f;
-
 struct MmaSlot { uint4 q; uint2 sc; };
 
-__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// D = A(u8, 16x32) * B(s8, 32x8) with a zero accumulator input.
+__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 
-// Same with a zero accumulator input (the zero operands become the zero register).
-__device__ __forceinline__ void mma16816_z(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
-}
-
-// One 32-bit word of nibbles (low nibbles = weights 4t..4t+3, high = 16+4t..) -> four
-// half2 registers holding q-8:  r0 = (w0, w2), r1 = (w1, w3), r2 = (w16, w18), r3 = (w17, w19)
-// in units relative to 4t.
-__device__ __forceinline__ void unpack_word(uint32_t w, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    const uint32_t w8 = w >> 8;
-    uint32_t a0 = (w & 0x000F000Fu) | 0x64006400u;      // 1024 + q
-    uint32_t a1 = (w8 & 0x000F000Fu) | 0x64006400u;
-    uint32_t a2 = (w & 0x00F000F0u) | 0x64006400u;      // 1024 + 16 q
-    uint32_t a3 = (w8 & 0x00F000F0u) | 0x64006400u;
-    const __half2 m1032 = __floats2half2_rn(-1032.f, -1032.f);
-    const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f), m72 = __floats2half2_rn(-72.f, -72.f);
-    __half2 h0 = __hadd2(*reinterpret_cast<__half2*>(&a0), m1032);
-    __half2 h1 = __hadd2(*reinterpret_cast<__half2*>(&a1), m1032);
-    __half2 h2 = __hfma2(*reinterpret_cast<__half2*>(&a2), sixteenth, m72);
-    __half2 h3 = __hfma2(*reinterpret_cast<__half2*>(&a3), sixteenth, m72);
-    r0 = *reinterpret_cast<uint32_t*>(&h0); r1 = *reinterpret_cast<uint32_t*>(&h1);
-    r2 = *reinterpret_cast<uint32_t*>(&h2); r3 = *reinterpret_cast<uint32_t*>(&h3);
-}
-
-// Offset (in halves) of activation element k of column `col` inside the staged buffer.
+// Staged activation bytes: block u (32 activations), column c, quad lane t -> 8 bytes
+// { k = 4t..4t+3 , k = 16+4t..16+4t+3 } which are the two B registers of lane (c, t).
 template <int NCOL>
-__device__ __forceinline__ int xs16_index(int k, int col) {
-    const int u = k >> 5, w = k & 31, tg = (w & 15) >> 2, i = w & 3, mm = w >> 4;
-    return ((u * NCOL + col) * 4 + tg) * 8 + mm * 4 + (i & 1) * 2 + (i >> 1);
+__device__ __forceinline__ int xb_index(int k, int col) {
+    const int u = k >> 5, w = k & 31;
+    return ((u * NCOL + col) * 4 + ((w & 15) >> 2)) * 8 + (w >> 4) * 4 + (w & 3);
 }
 
+// x*s rounded to an integer and split into three signed bytes (hi, mid, lo).
 template <int NCOL>
-__device__ __forceinline__ void put_x(__half* xs, int k, int b, float v_scaled) {
-    const __half hi = __float2half_rn(v_scaled);
-    const __half lo = __float2half_rn((v_scaled - __half2float(hi)) * MMA_LO_SCALE);
-    xs[xs16_index<NCOL>(k, 2 * b)] = hi;
-    xs[xs16_index<NCOL>(k, 2 * b + 1)] = lo;
+__device__ __forceinline__ void put_x(signed char* xb1, signed char* xb2, int k, int b, float v_scaled) {
+    const int xi = __float2int_rn(v_scaled);
+    const int lo = ((xi + 128) & 0xFF) - 128;
+    const int r = (xi - lo) >> 8;
+    const int mid = ((r + 128) & 0xFF) - 128;
+    const int hi = (r - mid) >> 8;
+    xb1[xb_index<NCOL>(k, 2 * b)] = (signed char)hi;
+    xb1[xb_index<NCOL>(k, 2 * b + 1)] = (signed char)mid;
+    xb2[xb_index<NCOL>(k, 2 * b)] = (signed char)lo;
 }
 
-// Power-of-two scale that brings amax to at most 2^14 (and its inverse).
+// Four consecutive activations (k0 a multiple of 4) at once: they share one 32-bit word
+// in each of the three byte planes.
+template <int NCOL>
+__device__ __forceinline__ void put_x4(signed char* xb1, signed char* xb2, int k0, int b, float4 v) {
+    const float f[4] = {v.x, v.y, v.z, v.w};
+    uint32_t wh = 0, wm = 0, wl = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int xi = __float2int_rn(f[i]);
+        const int lo = ((xi + 128) & 0xFF) - 128;
+        const int r = (xi - lo) >> 8;
+        const int mid = ((r + 128) & 0xFF) - 128;
+        const int hi = (r - mid) >> 8;
+        wh |= (uint32_t)(hi & 0xFF) << (8 * i); wm |= (uint32_t)(mid & 0xFF) << (8 * i); wl |= (uint32_t)(lo & 0xFF) << (8 * i);
+    }
+    *reinterpret_cast<uint32_t*>(xb1 + xb_index<NCOL>(k0, 2 * b)) = wh;
+    *reinterpret_cast<uint32_t*>(xb1 + xb_index<NCOL>(k0, 2 * b + 1)) = wm;
+    *reinterpret_cast<uint32_t*>(xb2 + xb_index<NCOL>(k0, 2 * b)) = wl;
+}
+
+// Power-of-two scale that brings amax to at most 2^22 (and its inverse).
 __device__ __forceinline__ void pow2_scale(float amax, float& s, float& inv) {
     if (!(amax > 0.f) || !(amax < 3.0e38f)) { s = 1.f; inv = 1.f; return; }
     int e;
     frexpf(amax, &e);
-    e = max(-100, min(100, 14 - e));
+    e = max(-100, min(100, 22 - e));
     s = ldexpf(1.f, e); inv = ldexpf(1.f, -e);
 }
 
@@ -114,7 +116,6 @@ constexpr int MMA_TILE = 576;              // bytes per tile pair
 template <int NCOL, bool PAIR>
 __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uint8_t* __restrict__ t0, const uint8_t* __restrict__ t1, int KS) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __half* xs = reinterpret_cast<__half*>(smem_raw);
     __shared__ float s_red[2][8][PAIR ? 2 : 1][16][4];
     __shared__ float s_inv[4];
     __shared__ float red[33];
@@ -139,7 +140,11 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
     constexpr int NSTAGE = PAIR ? 2 : 4;
     constexpr int STAGE_BYTES = MMA_CH * MMA_TILE * (PAIR ? 2 : 1);
     __shared__ __align__(8) uint64_t s_bar[8][NSTAGE];
-    unsigned char* ring = smem_raw + (((size_t)units * NCOL * 64 + 127) & ~(size_t)127) + (size_t)warp * NSTAGE * STAGE_BYTES;
+    // staged activations: (hi, mid) bytes, lo bytes, per-block integer sums
+    signed char* xb1 = reinterpret_cast<signed char*>(smem_raw);
+    signed char* xb2 = xb1 + (size_t)units * NCOL * 32;
+    float* s_sx = reinterpret_cast<float*>(smem_raw + (size_t)units * NCOL * 64);          // [units][NB]
+    unsigned char* ring = smem_raw + (((size_t)units * (NCOL * 64 + NB * 4) + 127) & ~(size_t)127) + (size_t)warp * NSTAGE * STAGE_BYTES;
     const int nch = (np + MMA_CH - 1) / MMA_CH;             // chunks per row group for this warp
     const int n_chunks = my_sets * nch;
     if (lane == 0) {
@@ -149,29 +154,27 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
-    auto issue_chunk = [&](int c) {                         // lane 0 only
-        const int set_i = c / nch, j = c % nch;
-        const int rg = min(((int)blockIdx.x + set_i * (int)gridDim.x) * RG + rg_l, n_rg - 1);   // clamped: rows past the end are dropped later
-        const int pp0 = p0 + j * MMA_CH, n = min(MMA_CH, p1 - pp0);
+    // issue cursor (lane 0): chunk `i_c` is chunk `i_j` of this warp's `i_set`-th row group
+    int i_c = 0, i_j = 0, i_rg = (int)blockIdx.x * RG + rg_l;
+    auto issue_next = [&]() {                                // lane 0 only
+        const int rg = min(i_rg, n_rg - 1);                 // clamped: rows past the end are dropped later
+        const int pp0 = p0 + i_j * MMA_CH, n = min(MMA_CH, p1 - pp0);
         const size_t off = ((size_t)rg * pairs + pp0) * MMA_TILE;
-        const int st = c % NSTAGE;
+        const int st = i_c & (NSTAGE - 1);
         unsigned char* dst = ring + (size_t)st * STAGE_BYTES;
         mbar_expect_tx(&s_bar[warp][st], (uint32_t)(n * MMA_TILE * (PAIR ? 2 : 1)));
         bulk_g2s(dst, t0 + off, (uint32_t)(n * MMA_TILE), &s_bar[warp][st]);
         if (PAIR) bulk_g2s(dst + MMA_CH * MMA_TILE, t1 + off, (uint32_t)(n * MMA_TILE), &s_bar[warp][st]);
+        ++i_c;
+        if (++i_j == nch) { i_j = 0; i_rg += (int)gridDim.x * RG; }
     };
     if (lane == 0) {
 #pragma unroll
-        for (int c = 0; c < NSTAGE; ++c) if (c < n_chunks) issue_chunk(c);
+        for (int c = 0; c < NSTAGE; ++c) if (i_c < n_chunks) issue_next();
     }
 
-    // ---- stage activations as fp16 (hi, lo) pairs in MMA operand order ----
+    // ---- stage activations as signed bytes (hi, mid | lo) in MMA operand order ----
     {
-        if (NCOL > 2) {     // unused batch columns must read as zero
-            uint4* z = reinterpret_cast<uint4*>(xs);
-            for (int i = threadIdx.x; i < units * NCOL * 4; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
-            __syncthreads();
-        }
         const int n4 = a.K >> 2;
         for (int b = 0; b < NB && b < a.B; ++b) {
             const size_t row = (size_t)b * a.ldx;
@@ -228,36 +231,65 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
 #pragma unroll
                 for (int j = 0; j < 3; ++j) {
                     const int i = threadIdx.x + j * blockDim.x;
-                    if (i < n4) {
-                        put_x<NCOL>(xs, 4 * i, b, vh[j].x * s); put_x<NCOL>(xs, 4 * i + 1, b, vh[j].y * s);
-                        put_x<NCOL>(xs, 4 * i + 2, b, vh[j].z * s); put_x<NCOL>(xs, 4 * i + 3, b, vh[j].w * s);
-                    }
+                    if (i < n4) put_x4<NCOL>(xb1, xb2, 4 * i, b, make_float4(vh[j].x * s, vh[j].y * s, vh[j].z * s, vh[j].w * s));
                 }
             } else {
-                // generic path: (optional) slow input chain into a float scratch view is not
-                // supported here; the launcher only takes this kernel with plain x or the fast chain.
+                // plain activations: read once into registers when they fit (K <= 8192), scale, pack
                 const float4* src = reinterpret_cast<const float4*>(a.x + row);
                 float am = 0.f;
-#pragma unroll 4
-                for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-                    const float4 v = src[i];
-                    am = fmaxf(am, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                }
-                am = block_max(am, red);
                 float s, inv;
-                pow2_scale(am, s, inv);
-                if (threadIdx.x == 0) s_inv[b] = inv;
+                if (n4 <= 8 * (int)blockDim.x) {
+                    float4 v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int i = threadIdx.x + j * blockDim.x;
+                        v[j] = i < n4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) am = fmaxf(am, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+                    am = block_max(am, red);
+                    pow2_scale(am, s, inv);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int i = threadIdx.x + j * blockDim.x;
+                        if (i < n4) put_x4<NCOL>(xb1, xb2, 4 * i, b, make_float4(v[j].x * s, v[j].y * s, v[j].z * s, v[j].w * s));
+                    }
+                } else {
 #pragma unroll 4
-                for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-                    const float4 v = src[i];
-                    put_x<NCOL>(xs, 4 * i, b, v.x * s); put_x<NCOL>(xs, 4 * i + 1, b, v.y * s);
-                    put_x<NCOL>(xs, 4 * i + 2, b, v.z * s); put_x<NCOL>(xs, 4 * i + 3, b, v.w * s);
+                    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+                        const float4 v = src[i];
+                        am = fmaxf(am, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                    }
+                    am = block_max(am, red);
+                    pow2_scale(am, s, inv);
+#pragma unroll 4
+                    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+                        const float4 v = src[i];
+                        put_x4<NCOL>(xb1, xb2, 4 * i, b, make_float4(v.x * s, v.y * s, v.z * s, v.w * s));
+                    }
                 }
+                if (threadIdx.x == 0) s_inv[b] = inv;
             }
         }
         __syncthreads();
     }
 
+    // per-block sums of the integer activations (they remove the -8 of Q4_0 later)
+    for (int i = threadIdx.x; i < units * NB; i += blockDim.x) {
+        const int u = i / NB, b = i % NB;
+        int acc = 0;
+        if (b < a.B) {
+            const int* h = reinterpret_cast<const int*>(xb1 + (size_t)(u * NCOL + 2 * b) * 32);
+            const int* m = h + 8;
+            const int* l = reinterpret_cast<const int*>(xb2 + (size_t)(u * NCOL + 2 * b) * 32);
+            int sh = 0, sm2 = 0, sl = 0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { sh = __dp4a(h[e], 0x01010101, sh); sm2 = __dp4a(m[e], 0x01010101, sm2); sl = __dp4a(l[e], 0x01010101, sl); }
+            acc = sm2 * 256 + sl;
+            s_sx[i] = (float)sh * 65536.0f + (float)acc;
+        } else s_sx[i] = 0.f;
+    }
+    __syncthreads();
     float best_v = -3.402823466e+38f; int best_i = -1;        // for batch row t
     float accA[2] = {0.f, 0.f}, accB[2] = {0.f, 0.f};
     int parity = 0;
@@ -265,35 +297,32 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
     __shared__ __align__(16) uint4 s_zero[4];
     if (threadIdx.x < 4) s_zero[threadIdx.x] = make_uint4(0, 0, 0, 0);
     __syncthreads();
-    const bool xlive = g < NCOL;
-    const uint4* xq = xlive ? reinterpret_cast<const uint4*>(xs) + g * 4 + t : s_zero + t;
-    const int xstep = xlive ? NCOL * 4 : 0;                    // uint4 per block
-    constexpr float LO = 1.0f / MMA_LO_SCALE;
+    // Lane (g, t) supplies B column g.  Only columns < NCOL are staged; the other lanes
+    // re-read a staged column: whatever lands in B columns >= 2*B only reaches output
+    // columns that are never read.
+    const uint2* xq1 = reinterpret_cast<const uint2*>(xb1) + (g % NCOL) * 4 + t;
+    const uint2* xq2 = reinterpret_cast<const uint2*>(xb2) + (g % NCOL) * 4 + t;
+    constexpr int xstep = NCOL * 4;                            // uint2 per block
+    const float* sxp = s_sx + (t < NB ? t : 0);
 
-    // One tile pair of one matrix: four independent MMAs (two blocks x two k-halves) are
-    // issued before any result is used, then the block scales are applied.
-    auto pair_mma = [&](const uint4& q, const uint2& sc, const uint4& xb0, const uint4& xb1, float& acc0, float& acc1) {
-        uint32_t p0g[4], p0h[4], p1g[4], p1h[4];
-        unpack_word(q.x, p0g[0], p0g[1], p0g[2], p0g[3]);
-        unpack_word(q.y, p0h[0], p0h[1], p0h[2], p0h[3]);
-        unpack_word(q.z, p1g[0], p1g[1], p1g[2], p1g[3]);
-        unpack_word(q.w, p1h[0], p1h[1], p1h[2], p1h[3]);
-        float c00[4], c01[4], c10[4], c11[4];
-        { const uint32_t av[4] = {p0g[0], p0h[0], p0g[1], p0h[1]}; mma16816_z(c00, av, xb0.x, xb0.y); }
-        { const uint32_t av[4] = {p0g[2], p0h[2], p0g[3], p0h[3]}; mma16816_z(c01, av, xb0.z, xb0.w); }
-        { const uint32_t av[4] = {p1g[0], p1h[0], p1g[1], p1h[1]}; mma16816_z(c10, av, xb1.x, xb1.y); }
-        { const uint32_t av[4] = {p1g[2], p1h[2], p1g[3], p1h[3]}; mma16816_z(c11, av, xb1.z, xb1.w); }
-        const float2 d0 = __half22float2(*reinterpret_cast<const __half2*>(&sc.x));
-        const float2 d1 = __half22float2(*reinterpret_cast<const __half2*>(&sc.y));
-        acc0 = fmaf(d0.x, fmaf(c00[1] + c01[1], LO, c00[0] + c01[0]), acc0);
-        acc1 = fmaf(d0.y, fmaf(c00[3] + c01[3], LO, c00[2] + c01[2]), acc1);
-        acc0 = fmaf(d1.x, fmaf(c10[1] + c11[1], LO, c10[0] + c11[0]), acc0);
-        acc1 = fmaf(d1.y, fmaf(c10[3] + c11[3], LO, c10[2] + c11[2]), acc1);
+    // One 16x32 block of one matrix: raw nibbles against (hi, mid) and against (lo, 0).
+    auto block_imma = [&](uint32_t wg, uint32_t wh, const uint2& b1, const uint2& b2, uint32_t sc2, float sx, float& acc0, float& acc1) {
+        const uint32_t a0 = wg & 0x0F0F0F0Fu, a2 = (wg >> 4) & 0x0F0F0F0Fu;
+        const uint32_t a1 = wh & 0x0F0F0F0Fu, a3 = (wh >> 4) & 0x0F0F0F0Fu;
+        int d1[4], d2[4];
+        imma16832(d1, a0, a1, a2, a3, b1.x, b1.y);
+        imma16832(d2, a0, a1, a2, a3, b2.x, b2.y);
+        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&sc2));
+        const float s0 = fmaf((float)d1[0], 65536.0f, (float)(d1[1] * 256 + d2[0]));
+        const float s1 = fmaf((float)d1[2], 65536.0f, (float)(d1[3] * 256 + d2[2]));
+        acc0 = fmaf(d.x, fmaf(-8.0f, sx, s0), acc0);
+        acc1 = fmaf(d.y, fmaf(-8.0f, sx, s1), acc1);
     };
 
     bool timed_out = false;
+    int j = 0, c_rg = (int)blockIdx.x * RG + rg_l;
     for (int c = 0; c < n_chunks; ++c) {
-        const int st = c % NSTAGE, j = c % nch, set_i = c / nch;
+        const int st = c & (NSTAGE - 1);
         if (!timed_out) {
             const bool ok = mbar_wait(&s_bar[warp][st], (uint32_t)((c / NSTAGE) & 1));
             if (!__all_sync(0xffffffffu, ok)) {
@@ -306,27 +335,35 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
         if (!timed_out) {
             const unsigned char* buf = ring + (size_t)st * STAGE_BYTES;
             const int pp0 = p0 + j * MMA_CH, n = min(MMA_CH, p1 - pp0);
-            const uint4* xp = xq + (size_t)pp0 * 2 * xstep;
+            const uint2* xp1 = xq1 + (size_t)pp0 * 2 * xstep;
+            const uint2* xp2 = xq2 + (size_t)pp0 * 2 * xstep;
+            const float* sx = sxp + (size_t)pp0 * 2 * NB;
 #pragma unroll
             for (int k = 0; k < MMA_CH; ++k) {
                 if (k < n) {
                     const uint4 q = reinterpret_cast<const uint4*>(buf + k * MMA_TILE)[lane];
                     const uint2 sc = reinterpret_cast<const uint2*>(buf + k * MMA_TILE + 512)[g];
-                    const uint4 xb0 = xp[(2 * k) * xstep], xb1 = xp[(2 * k + 1) * xstep];
-                    pair_mma(q, sc, xb0, xb1, accA[0], accA[1]);
+                    const uint2 b10 = xp1[(2 * k) * xstep], b11 = xp1[(2 * k + 1) * xstep];
+                    const uint2 b20 = xp2[(2 * k) * xstep], b21 = xp2[(2 * k + 1) * xstep];
+                    const float sx0 = sx[(2 * k) * NB], sx1 = sx[(2 * k + 1) * NB];
+                    block_imma(q.x, q.y, b10, b20, sc.x, sx0, accA[0], accA[1]);
+                    block_imma(q.z, q.w, b11, b21, sc.y, sx1, accA[0], accA[1]);
                     if (PAIR) {
                         const uint4 q1 = reinterpret_cast<const uint4*>(buf + (MMA_CH + k) * MMA_TILE)[lane];
                         const uint2 sc1 = reinterpret_cast<const uint2*>(buf + (MMA_CH + k) * MMA_TILE + 512)[g];
-                        pair_mma(q1, sc1, xb0, xb1, accB[0], accB[1]);
+                        block_imma(q1.x, q1.y, b10, b20, sc1.x, sx0, accB[0], accB[1]);
+                        block_imma(q1.z, q1.w, b11, b21, sc1.y, sx1, accB[0], accB[1]);
                     }
                 }
             }
             __syncwarp();                                   // every lane is done with this stage
-            if (lane == 0 && c + NSTAGE < n_chunks) issue_chunk(c + NSTAGE);
+            if (lane == 0 && i_c < n_chunks) issue_next();
         }
-        if (j == nch - 1) {
+        if (++j == nch) {
             // ---- end of this warp's K slice for the row group ----
-            const int rg = ((int)blockIdx.x + set_i * (int)gridDim.x) * RG + rg_l;
+            const int rg = c_rg;
+            j = 0;
+            c_rg += (int)gridDim.x * RG;
             float vA[2] = {accA[0], accA[1]}, vB[2] = {accB[0], accB[1]};
             bool writer = true;
             if (KS > 1) {       // combine the KS slices through shared memory
