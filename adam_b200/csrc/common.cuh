@@ -63,6 +63,7 @@ struct Context {
     uint64_t     submits;       // stream synchronisations that closed a batch
     uint64_t     flushes;
     uint32_t*    dev_err;       // device error word
+    bool         pdl;           // launch with programmatic stream serialization (set by the decoder while it enqueues a step)
 };
 
 extern Context g;
@@ -81,7 +82,27 @@ int  check_launch(const char* what);                // cudaGetLastError -> statu
 inline void count_launch(uint64_t n = 1) { g.launches += n; }
 void end_of_op();                                   // sync when not inside a batch
 
+// Launch `k` on `st`; with `pdl` the launch may begin before the previous kernel in the
+// stream has finished (programmatic dependent launch).  Every kernel launched that way
+// calls pdl_wait() before it touches anything an earlier kernel writes.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*k)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k, KArgs(args)...);
+}
+
 // ---- device helpers --------------------------------------------------------
+
+// Programmatic dependent launch: let the next kernel in the stream start its
+// independent prologue now / wait until every earlier kernel's writes are visible.
+// Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -57,7 +57,8 @@ struct Decoder {
 };
 
 constexpr uint32_t MAX_DECODERS = 8;
-constexpr uint32_t ATTN_SPLIT = 64;        // tokens per attention split
+constexpr uint32_t ATTN_SPLIT = 64;        // fewest tokens an attention CTA takes before another CTA is added
+constexpr uint32_t ATTN_MAX_SPLITS = 64;   // attention CTAs per (sequence, kv head)
 static Decoder* g_dec[MAX_DECODERS];
 
 static Decoder* get_dec(uint32_t id) {
@@ -78,6 +79,8 @@ template <int WT>
 __global__ void k_embed(const WeightRef w, uint32_t n_embd, uint32_t n_vocab, float emb_scale,
                         const int32_t* __restrict__ pos, const int32_t* __restrict__ prompt_len, const int32_t* __restrict__ prompt_tok,
                         uint32_t prompt_ld, const int32_t* __restrict__ cur_tok, float* __restrict__ h, uint32_t* err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t b = blockIdx.x;
     const int32_t p = pos[b];
     int32_t tok = (p < prompt_len[b]) ? prompt_tok[(size_t)b * prompt_ld + p] : cur_tok[b];
@@ -166,33 +169,91 @@ __device__ __forceinline__ size_t kv_index(const KvGeom& g, uint32_t page_id, ui
 // the kv head, with the steps that precede it folded in:
 //   * per-head RMSNorm + half-split RoPE of the query rows (map_qk_norm_rope_x.comp),
 //     angles read from the host-made table;
-//   * the CTA that owns the newest position does the same for the key row and
-//     appends key and value to the paged cache (map_row_copy.comp);
+//   * the CTA whose range holds the newest position does the same for the key row
+//     and appends key and value to the paged cache (map_row_copy.comp);
 //   * p = softmax(cap*tanh(q.k*scale/cap)) over positions [start, seq), o = p @ V
 //     (map_matmul_t.comp + map_attn_softmax_value.comp; diag_inference.py:989-1012).
-// A split covers ATTN_SPLIT = 64 positions.  Every thread fetches its slice of the
-// cached K and V rows into registers at the very start (they do not depend on this
-// step's query), so the whole split costs one memory round trip; the newest
-// position is taken from shared memory instead.  Scores: 4 threads per position,
-// each over head_dim/4 dims; PV: 8 dims per thread.  Every split leaves (o, max,
-// sum) in scratch and the CTA that finishes last merges them.
-template <typename T> struct KvCvt;
-template <> struct KvCvt<__half> {
-    static constexpr int EPV = 8;            // elements per uint4
-    static __device__ __forceinline__ void cvt(const uint4& r, float (&f)[8]) {
-        const __half2* h = reinterpret_cast<const __half2*>(&r);
+// Work split.  Positions are walked in chunks of ATTN_CP = 8 (aligned to absolute
+// multiples of 8, so a chunk never straddles a page whose size is a multiple of 8).
+// The active CTAs (at most gridDim.x, at least one per 8 chunks) take contiguous
+// runs of chunks; inside a CTA the 8 warps take chunks round-robin.  A lane owns
+// head_dim/32 consecutive dims of every K and V row, so one row is one coalesced
+// warp load, and all 8+8 row loads of a chunk are issued before any is used; the
+// next chunk's K rows are requested as soon as the scores are done and its V rows
+// after the P@V accumulation.  The 8 x heads partial dot products of a chunk are
+// summed over the lanes with a reduce-scatter (one shuffle per value) that leaves
+// score (position j, head g) on one lane; the soft-max runs online per warp, and
+// (max, sum, o) are merged across warps in shared memory, then across CTAs by the
+// CTA that finishes last.
+constexpr int ATTN_CP = 8;
+
+template <typename T, int DPL> struct KvRow {
+    static constexpr int BYTES = DPL * (int)sizeof(T);
+    static constexpr int NW = BYTES >= 4 ? BYTES / 4 : 1;
+    uint32_t w[NW];
+    __device__ __forceinline__ void zero() {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { const float2 v = __half22float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+        for (int i = 0; i < NW; ++i) w[i] = 0u;
     }
-    static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
-};
-template <> struct KvCvt<float> {
-    static constexpr int EPV = 4;
-    static __device__ __forceinline__ void cvt(const uint4& r, float (&f)[4]) {
-        f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+    __device__ __forceinline__ void load(const T* p) {
+        if constexpr (BYTES == 32) {
+            const uint4 a = reinterpret_cast<const uint4*>(p)[0], b = reinterpret_cast<const uint4*>(p)[1];
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+        } else if constexpr (BYTES == 16) {
+            const uint4 a = *reinterpret_cast<const uint4*>(p);
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+        } else if constexpr (BYTES == 8) {
+            const uint2 a = *reinterpret_cast<const uint2*>(p);
+            w[0] = a.x; w[1] = a.y;
+        } else if constexpr (BYTES == 4) {
+            w[0] = *reinterpret_cast<const uint32_t*>(p);
+        } else {
+            w[0] = *reinterpret_cast<const unsigned short*>(p);
+        }
     }
-    static __device__ __forceinline__ float round(float v) { return v; }
+    __device__ __forceinline__ void to_float(float (&f)[DPL]) const {
+        if constexpr (sizeof(T) == 4) {
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) f[i] = __uint_as_float(w[i]);
+        } else if constexpr (DPL >= 2) {
+#pragma unroll
+            for (int i = 0; i < DPL / 2; ++i) {
+                const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                f[2 * i] = v.x; f[2 * i + 1] = v.y;
+            }
+        } else {
+            f[0] = __half2float(__ushort_as_half((unsigned short)w[0]));
+        }
+    }
 };
+template <typename T> __device__ __forceinline__ float kv_round(float v);
+template <> __device__ __forceinline__ float kv_round<__half>(float v) { return __half2float(__float2half_rn(v)); }
+template <> __device__ __forceinline__ float kv_round<float>(float v) { return v; }
+
+// Sum a[0..NV) over the 32 lanes.  NV >= 32: lane l ends with the totals of values
+// l*NV/32 .. in a[0..NV/32).  NV == 16: lanes 2v and 2v+1 end with value v in a[0].
+template <int NV>
+__device__ __forceinline__ void warp_reduce_scatter(float (&a)[NV], uint32_t lane) {
+    int n = NV;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        if (n > 1) {
+            const int h = n >> 1;
+            const bool up = (lane & off) != 0;
+#pragma unroll
+            for (int i = 0; i < NV / 2; ++i) {
+                if (i < h) {
+                    const float send = up ? a[i] : a[i + h];
+                    const float keep = up ? a[i + h] : a[i];
+                    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+            n = h;
+        } else {
+            a[0] += __shfl_xor_sync(0xffffffffu, a[0], off);
+        }
+    }
+}
 
 template <typename T, int GS_MAX, int HD>
 __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv, uint32_t qkv_ld,
@@ -204,59 +265,58 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
                                                    float* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                                                    unsigned int* __restrict__ ticket, uint32_t n_splits_max, uint32_t* err) {
     T* __restrict__ kv_pool = reinterpret_cast<T*>(kv_pool_v);
-    constexpr int EPV = KvCvt<T>::EPV;
-    constexpr int QD = HD / 4;                  // dims per thread in the score phase
-    constexpr int NVK = QD / EPV;               // uint4 per thread per key row
-    constexpr int TPT = HD / 8;                 // threads per value row (8 dims each)
-    constexpr int TL = 256 / TPT;               // token lanes in the PV phase
-    constexpr int TPL = (int)ATTN_SPLIT / TL;   // positions per thread in the PV phase
-    constexpr int NVV = 8 / EPV;                // uint4 per thread per value row
-    static_assert(NVK >= 1 && TPL >= 1, "unsupported head_dim");
+    constexpr int DPL = HD / 32;                // dims per lane
+    constexpr int CP = ATTN_CP;                 // positions per chunk
+    constexpr int NV = CP * GS_MAX;             // scores per chunk
+    constexpr int VPL = NV >= 32 ? NV / 32 : 1; // scores a lane holds after the reduce-scatter
+    constexpr float NEG = -1.0e30f;
+    static_assert(DPL >= 1 && (GS_MAX == 2 || GS_MAX == 4 || GS_MAX == 8), "unsupported attention shape");
     extern __shared__ __align__(16) float sm[];
-    __shared__ float red[33];
-    __shared__ float s_m[GS_MAX], s_l[GS_MAX];
+    __shared__ float s_m[8][GS_MAX], s_l[8][GS_MAX];
+    __shared__ float s_M[GS_MAX], s_L[GS_MAX];
     __shared__ bool s_last;
+    pdl_launch_dependents();
+    pdl_wait();             // positions, q/k/v rows and the cache all come from earlier kernels
     const uint32_t split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const uint32_t hd = HD, half = HD / 2, gs = n_head / geo.n_kv;
     const int32_t p = pos[b];
     const uint32_t seq = (uint32_t)p + 1;
     const uint32_t start = (window > 0 && seq > window) ? seq - window : 0;
-    const uint32_t n_act = (seq - start + ATTN_SPLIT - 1) / ATTN_SPLIT;
+    const uint32_t c_first = start / CP, n_chunks = (seq - 1) / CP - c_first + 1;
+    const uint32_t n_act = min((uint32_t)gridDim.x, (n_chunks + 7) / 8);
     if (split >= n_act) return;
-    const uint32_t t0 = start + split * ATTN_SPLIT, t1 = min(seq, t0 + ATTN_SPLIT), len = t1 - t0;
-    const bool owner = (split == n_act - 1);
-    float* s_q = sm;                           // [gs][hd]
-    float* s_sc = s_q + gs * hd;               // [gs][ATTN_SPLIT]
-    float* s_kn = s_sc + gs * ATTN_SPLIT;      // [hd] newest key (as stored)
-    float* s_vn = s_kn + hd;                   // [hd] newest value (as stored)
-    float* s_o = s_vn + hd;                    // [TL][gs][hd] for the PV reduction
+    const uint32_t cpc = (n_chunks + n_act - 1) / n_act;
+    const uint32_t c0 = min(c_first + split * cpc, c_first + n_chunks), c1 = min(c_first + n_chunks, c0 + cpc);
+    const uint32_t c_new = (uint32_t)p / CP;
+    const bool owner = c_new >= c0 && c_new < c1;
+    float* s_q = sm;                            // [gs][hd]
+    float* s_kn = s_q + gs * hd;                // [hd] newest key (as stored)
+    float* s_vn = s_kn + hd;                    // [hd] newest value (as stored)
+    float* s_o = s_vn + hd;                     // [8 warps][gs][hd]
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int32_t* bt = block_table + (size_t)b * geo.max_pages;
+    const bool page8 = (geo.page % CP) == 0;
 
-    // ---- 1. cached K / V slices of this split into registers ----
-    const uint32_t tk = tid >> 2, part = tid & 3;
-    const bool k_live = tk < len, k_new = k_live && owner && (t0 + tk == (uint32_t)p);
-    uint4 kreg[NVK];
-    if (k_live && !k_new) {
-        const uint32_t tp = t0 + tk;
-        const uint4* kr = reinterpret_cast<const uint4*>(kv_pool + kv_index(geo, (uint32_t)max(bt[tp / geo.page], 0), layer, 0, kvh, tp % geo.page) + part * QD);
+    // Row j of chunk c: cache address, or null when the position is outside
+    // [start, seq) or is the newest one (taken from shared memory instead).
+    KvRow<T, DPL> kr[CP], vr[CP];
+    auto load_rows = [&](uint32_t c, uint32_t kv, KvRow<T, DPL> (&rows)[CP]) {
+        const uint32_t tp0 = c * CP;
+        int32_t pg0 = 0;
+        if (page8) pg0 = max(bt[min(tp0 / geo.page, geo.max_pages - 1)], 0);
 #pragma unroll
-        for (int v = 0; v < NVK; ++v) kreg[v] = kr[v];
-    }
-    const uint32_t tl = tid / TPT, dc = tid % TPT;
-    uint4 vreg[TPL][NVV];
-#pragma unroll
-    for (int j = 0; j < TPL; ++j) {
-        const uint32_t tv = tl + j * TL;
-        if (tv < len && !(owner && t0 + tv == (uint32_t)p)) {
-            const uint32_t tp = t0 + tv;
-            const uint4* vr = reinterpret_cast<const uint4*>(kv_pool + kv_index(geo, (uint32_t)max(bt[tp / geo.page], 0), layer, 1, kvh, tp % geo.page) + dc * 8);
-#pragma unroll
-            for (int v = 0; v < NVV; ++v) vreg[j][v] = vr[v];
+        for (int j = 0; j < CP; ++j) {
+            const uint32_t tp = tp0 + j;
+            if (tp >= start && tp < seq && tp != (uint32_t)p) {
+                const int32_t pg = page8 ? pg0 : max(bt[min(tp / geo.page, geo.max_pages - 1)], 0);
+                rows[j].load(kv_pool + kv_index(geo, (uint32_t)pg, layer, kv, kvh, tp % geo.page) + lane * DPL);
+            } else rows[j].zero();
         }
-    }
+    };
+    uint32_t c = c0 + warp;
+    if (c < c1) { load_rows(c, 0, kr); load_rows(c, 1, vr); }
 
-    // ---- 2. a warp per row: query heads, and (newest split only) the key and value rows ----
+    // ---- a warp per row: query heads, and (owner only) the newest key and value rows ----
     const uint32_t pp = (uint32_t)p < n_pos ? (uint32_t)p : n_pos - 1;
     if ((uint32_t)p >= n_pos && tid == 0) atomicOr(err, DEVERR_OOB_MAP);
     const float* ct = cos_t + (size_t)pp * half;
@@ -279,19 +339,24 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         if (!is_q && !is_k) {
             for (uint32_t i = lane; i < hd; i += 32) {
                 const float v = src[i];
-                s_vn[i] = KvCvt<T>::round(v);
+                s_vn[i] = kv_round<T>(v);
                 if (ok) st_kv(kv_pool + kv_off + i, v);
             }
             continue;
         }
         const float* w = is_q ? q_norm : k_norm;
         constexpr int NP = (HD / 2 + 31) / 32;          // rotation pairs per lane
-        float x0[NP], x1[NP];
+        float x0[NP], x1[NP], w0[NP], w1[NP], cs[NP], sn[NP];
 #pragma unroll
         for (int j = 0; j < NP; ++j) {
             const uint32_t i = lane + 32 * j;
-            x0[j] = i < half ? src[i] : 0.f;
-            x1[j] = i < half ? src[i + half] : 0.f;
+            const bool in = i < half;
+            x0[j] = in ? src[i] : 0.f;
+            x1[j] = in ? src[i + half] : 0.f;
+            w0[j] = (in && w) ? w[i] : 1.f;
+            w1[j] = (in && w) ? w[i + half] : 1.f;
+            cs[j] = in ? ct[i] : 1.f;
+            sn[j] = in ? st[i] : 0.f;
         }
         float rms = 1.f;
         if (w) {
@@ -308,13 +373,12 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             const uint32_t i = lane + 32 * j;
             if (i < half) {
                 float a0 = x0[j], a1 = x1[j];
-                if (w) { a0 = __fdiv_rn(a0, rms) * w[i]; a1 = __fdiv_rn(a1, rms) * w[i + half]; }
-                const float c = ct[i], s = st[i];
-                const float y0 = __fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, s));
-                const float y1 = __fadd_rn(__fmul_rn(a0, s), __fmul_rn(a1, c));
+                if (w) { a0 = __fdiv_rn(a0, rms) * w0[j]; a1 = __fdiv_rn(a1, rms) * w1[j]; }
+                const float y0 = __fsub_rn(__fmul_rn(a0, cs[j]), __fmul_rn(a1, sn[j]));
+                const float y1 = __fadd_rn(__fmul_rn(a0, sn[j]), __fmul_rn(a1, cs[j]));
                 if (is_q) { s_q[r * hd + i] = y0; s_q[r * hd + i + half] = y1; }
                 else {
-                    s_kn[i] = KvCvt<T>::round(y0); s_kn[i + half] = KvCvt<T>::round(y1);
+                    s_kn[i] = kv_round<T>(y0); s_kn[i + half] = kv_round<T>(y1);
                     if (ok) { st_kv(kv_pool + kv_off + i, y0); st_kv(kv_pool + kv_off + i + half, y1); }
                 }
             }
@@ -322,107 +386,121 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     }
     __syncthreads();
 
-    // ---- 3. scores: 4 threads per position ----
-    {
-        float acc[GS_MAX];
+    // ---- this warp's chunks: scores, online soft-max, P@V ----
+    float q[GS_MAX][DPL], o[GS_MAX][DPL], m_run[VPL], l_run[VPL];
 #pragma unroll
-        for (int g = 0; g < GS_MAX; ++g) acc[g] = 0.f;
-        if (k_live) {
-            if (k_new) {
-                for (int i = 0; i < QD; ++i) {
-                    const float kd = s_kn[part * QD + i];
+    for (int g = 0; g < GS_MAX; ++g)
 #pragma unroll
-                    for (int g = 0; g < GS_MAX; ++g) if (g < (int)gs) acc[g] = fmaf(s_q[g * hd + part * QD + i], kd, acc[g]);
-                }
-            } else {
+        for (int d = 0; d < DPL; ++d) { q[g][d] = g < (int)gs ? s_q[g * hd + lane * DPL + d] : 0.f; o[g][d] = 0.f; }
 #pragma unroll
-                for (int v = 0; v < NVK; ++v) {
-                    float kf[EPV];
-                    KvCvt<T>::cvt(kreg[v], kf);
+    for (int r = 0; r < VPL; ++r) { m_run[r] = NEG; l_run[r] = 0.f; }
+    for (; c < c1; c += 8) {
+        const bool has_new = (c == c_new);
+        float sc[NV];
 #pragma unroll
-                    for (int e = 0; e < EPV; ++e) {
+        for (int j = 0; j < CP; ++j) {
+            float kf[DPL];
+            kr[j].to_float(kf);
+            if (has_new && j == (int)((uint32_t)p % CP)) {
 #pragma unroll
-                        for (int g = 0; g < GS_MAX; ++g) if (g < (int)gs) acc[g] = fmaf(s_q[g * hd + part * QD + v * EPV + e], kf[e], acc[g]);
-                    }
-                }
+                for (int d = 0; d < DPL; ++d) kf[d] = s_kn[lane * DPL + d];
             }
+#pragma unroll
+            for (int g = 0; g < GS_MAX; ++g) {
+                float acc = 0.f;
+#pragma unroll
+                for (int d = 0; d < DPL; ++d) acc = fmaf(q[g][d], kf[d], acc);
+                sc[j * GS_MAX + g] = acc;
+            }
+        }
+        const uint32_t c_next = c + 8;
+        if (c_next < c1) load_rows(c_next, 0, kr);
+        warp_reduce_scatter<NV>(sc, lane);
+        float pz[VPL], alpha[VPL];
+#pragma unroll
+        for (int r = 0; r < VPL; ++r) {
+            const uint32_t v = NV >= 32 ? lane * VPL + r : lane >> 1;
+            const uint32_t j = v / GS_MAX, g = v % GS_MAX;
+            const uint32_t tp = c * CP + j;
+            const bool valid = tp >= start && tp < seq && g < gs;
+            float sv = sc[r] * scale;
+            if (cap > 0.f) sv = tanhf(sv / cap) * cap;
+            sv = valid ? sv : NEG;
+            float cm = sv;
+            cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, 4));
+            cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, 8));
+            cm = fmaxf(cm, __shfl_xor_sync(0xffffffffu, cm, 16));
+            const float m_new = fmaxf(m_run[r], cm);
+            alpha[r] = expf(m_run[r] - m_new);
+            pz[r] = valid ? expf(sv - m_new) : 0.f;
+            float ps = pz[r];
+            ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+            ps += __shfl_xor_sync(0xffffffffu, ps, 8);
+            ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+            l_run[r] = fmaf(l_run[r], alpha[r], ps);
+            m_run[r] = m_new;
         }
 #pragma unroll
         for (int g = 0; g < GS_MAX; ++g) {
-            float v = acc[g];
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            if (g < (int)gs && k_live && part == 0) {
-                v *= scale;
-                if (cap > 0.f) v = tanhf(v / cap) * cap;
-                s_sc[g * ATTN_SPLIT + tk] = v;
-            }
-        }
-    }
-    __syncthreads();
-    // ---- 4. per-head max and exp-sum over this split ----
-    for (uint32_t g = 0; g < gs; ++g) {
-        float mx = -3.402823466e+38f;
-        for (uint32_t t = tid; t < len; t += blockDim.x) mx = fmaxf(mx, s_sc[g * ATTN_SPLIT + t]);
-        mx = block_max(mx, red);
-        float sum = 0.f;
-        for (uint32_t t = tid; t < len; t += blockDim.x) { const float pz = expf(s_sc[g * ATTN_SPLIT + t] - mx); s_sc[g * ATTN_SPLIT + t] = pz; sum += pz; }
-        sum = block_sum(sum, red);
-        if (tid == 0) { s_m[g] = mx; s_l[g] = sum; }
-    }
-    __syncthreads();
-    // ---- 5. o = p @ V: 8 dims per thread ----
-    {
-        float o[GS_MAX][8];
+            // lane and slot that hold (position 0, head g)
+            constexpr int SH = NV >= 32 ? 1 : 2;
+            const float al = __shfl_sync(0xffffffffu, alpha[g % VPL], NV >= 32 ? g / VPL : g * SH);
 #pragma unroll
-        for (int g = 0; g < GS_MAX; ++g)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) o[g][e] = 0.f;
-#pragma unroll
-        for (int j = 0; j < TPL; ++j) {
-            const uint32_t tv = tl + j * TL;
-            if (tv < len) {
-                float vf[8];
-                if (owner && t0 + tv == (uint32_t)p) {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) vf[e] = s_vn[dc * 8 + e];
-                } else {
-#pragma unroll
-                    for (int v = 0; v < NVV; ++v) {
-                        float t8[EPV];
-                        KvCvt<T>::cvt(vreg[j][v], t8);
-#pragma unroll
-                        for (int e = 0; e < EPV; ++e) vf[v * EPV + e] = t8[e];
-                    }
-                }
-#pragma unroll
-                for (int g = 0; g < GS_MAX; ++g) {
-                    if (g < (int)gs) {
-                        const float pz = s_sc[g * ATTN_SPLIT + tv];
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) o[g][e] = fmaf(pz, vf[e], o[g][e]);
-                    }
-                }
-            }
+            for (int d = 0; d < DPL; ++d) o[g][d] *= al;
         }
 #pragma unroll
-        for (int g = 0; g < GS_MAX; ++g)
-            if (g < (int)gs)
+        for (int j = 0; j < CP; ++j) {
+            float vf[DPL];
+            vr[j].to_float(vf);
+            if (has_new && j == (int)((uint32_t)p % CP)) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) s_o[(tl * gs + g) * hd + dc * 8 + e] = o[g][e];
+                for (int d = 0; d < DPL; ++d) vf[d] = s_vn[lane * DPL + d];
+            }
+#pragma unroll
+            for (int g = 0; g < GS_MAX; ++g) {
+                constexpr int vidx0 = 0;
+                const int v = j * GS_MAX + g + vidx0;
+                const float pv = __shfl_sync(0xffffffffu, pz[v % VPL], NV >= 32 ? v / VPL : v * 2);
+#pragma unroll
+                for (int d = 0; d < DPL; ++d) o[g][d] = fmaf(pv, vf[d], o[g][d]);
+            }
+        }
+        if (c_next < c1) load_rows(c_next, 1, vr);
+    }
+    // ---- merge the warps ----
+#pragma unroll
+    for (int g = 0; g < GS_MAX; ++g)
+        if (g < (int)gs)
+#pragma unroll
+            for (int d = 0; d < DPL; ++d) s_o[(warp * gs + g) * hd + lane * DPL + d] = o[g][d];
+#pragma unroll
+    for (int r = 0; r < VPL; ++r) {
+        const uint32_t v = NV >= 32 ? lane * VPL + r : lane >> 1;
+        if (v < GS_MAX && (NV >= 32 || (lane & 1) == 0)) { s_m[warp][v] = m_run[r]; s_l[warp][v] = l_run[r]; }
+    }
+    __syncthreads();
+    if (tid < gs) {
+        float M = NEG, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) M = fmaxf(M, s_m[w][tid]);
+#pragma unroll
+        for (int w = 0; w < 8; ++w) L = fmaf(expf(s_m[w][tid] - M), s_l[w][tid], L);
+        s_M[tid] = M; s_L[tid] = L;
     }
     __syncthreads();
     float* po = part_o + (((size_t)b * geo.n_kv + kvh) * n_splits_max + split) * gs * hd;
     float* pml = part_ml + (((size_t)b * geo.n_kv + kvh) * n_splits_max + split) * gs * 2;
     for (uint32_t i = tid; i < gs * hd; i += blockDim.x) {
+        const uint32_t g = i / hd;
+        const float M = s_M[g];
         float v = 0.f;
-#pragma unroll 8
-        for (uint32_t l2 = 0; l2 < (uint32_t)TL; ++l2) v += s_o[l2 * gs * hd + i];
-        if (n_act == 1) out[((size_t)b * n_head + (size_t)kvh * gs) * hd + i] = v / s_l[i / hd];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) v = fmaf(expf(s_m[w][g] - M), s_o[w * gs * hd + i], v);
+        if (n_act == 1) out[((size_t)b * n_head + (size_t)kvh * gs) * hd + i] = v / s_L[g];
         else po[i] = v;
     }
     if (n_act == 1) return;
-    if (tid < gs) { pml[tid * 2] = s_m[tid]; pml[tid * 2 + 1] = s_l[tid]; }
+    if (tid < gs) { pml[tid * 2] = s_M[tid]; pml[tid * 2 + 1] = s_L[tid]; }
     __threadfence();
     __syncthreads();
     unsigned int* tkt = ticket + (size_t)b * geo.n_kv + kvh;
@@ -430,17 +508,25 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // ---- merge the splits (last CTA to arrive) ----
     const float* po0 = part_o + (((size_t)b * geo.n_kv + kvh) * n_splits_max) * gs * hd;
     const float* pml0 = part_ml + (((size_t)b * geo.n_kv + kvh) * n_splits_max) * gs * 2;
+    if (tid < gs) {
+        float M = NEG;
+        for (uint32_t s = 0; s < n_act; ++s) M = fmaxf(M, __ldcg(pml0 + ((size_t)s * gs + tid) * 2));
+        s_M[tid] = M;
+    }
+    __syncthreads();
     for (uint32_t i = tid; i < gs * hd; i += blockDim.x) {
         const uint32_t g = i / hd;
-        float M = -3.402823466e+38f;
-        for (uint32_t s = 0; s < n_act; ++s) M = fmaxf(M, __ldcg(pml0 + ((size_t)s * gs + g) * 2));
+        const float M = s_M[g];
         float num = 0.f, den = 0.f;
+#pragma unroll 4
         for (uint32_t s = 0; s < n_act; ++s) {
-            const float w = expf(__ldcg(pml0 + ((size_t)s * gs + g) * 2) - M);
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(pml0 + ((size_t)s * gs + g) * 2));
+            const float w = expf(ml.x - M);
             num = fmaf(w, __ldcg(po0 + (size_t)s * gs * hd + i), num);
-            den = fmaf(w, __ldcg(pml0 + ((size_t)s * gs + g) * 2 + 1), den);
+            den = fmaf(w, ml.y, den);
         }
         out[((size_t)b * n_head + (size_t)kvh * gs) * hd + i] = num / den;
     }
@@ -450,6 +536,8 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
 // End of a step: advance positions; when the LM head ran, log the sampled token.
 __global__ void k_advance(int32_t* __restrict__ pos, const int32_t* __restrict__ cur_tok, int32_t* __restrict__ gen_log,
                           uint32_t log_ld, uint32_t batch, int with_lm) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= batch) return;
     const int32_t p = pos[b] + 1;
@@ -510,18 +598,17 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch) {
     KvGeom geo{d.n_layer, d.n_head_kv, d.head_dim, d.page_size, D->max_pages_per_seq, D->page_elems};
     const uint32_t gs = d.n_head / d.n_head_kv;
     const uint32_t window = ((d.flags & 1u) && d.sliding_window > 0 && !is_global_layer(d, L)) ? d.sliding_window : 0;
-    const uint32_t n_tl = 256 / (d.head_dim / 8);
-    const size_t smem = ((size_t)gs * d.head_dim + (size_t)gs * ATTN_SPLIT + 2 * (size_t)d.head_dim + (size_t)n_tl * gs * d.head_dim) * 4;
+    const size_t smem = ((size_t)gs * d.head_dim + 2 * (size_t)d.head_dim + (size_t)8 * gs * d.head_dim) * 4;
     const int which = is_global_layer(d, L) ? 1 : 0;
     const Layer& ly = D->layers[L];
     const uint32_t qkv_ld = (d.n_head + 2 * d.n_head_kv) * d.head_dim;
     dim3 grid(D->n_splits, d.n_head_kv, batch);
     AttnKernel kern = gs <= 2 ? pick_attn_hd<T, 2>(d.head_dim) : gs <= 4 ? pick_attn_hd<T, 4>(d.head_dim) : pick_attn_hd<T, 8>(d.head_dim);
     if (smem > 48 * 1024) DCU(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, 256, smem, g.stream>>>(D->qkv, qkv_ld, ly.norm[NORM_Q], ly.norm[NORM_K], d.norm_eps,
-                                        D->rope_cos[which], D->rope_sin[which], D->rope_pos[which],
-                                        D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
-                                        d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, g.dev_err);
+    launch_k(kern, grid, dim3(256), smem, g.stream, g.pdl, D->qkv, qkv_ld, ly.norm[NORM_Q], ly.norm[NORM_K], d.norm_eps,
+             D->rope_cos[which], D->rope_sin[which], D->rope_pos[which],
+             D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
+             d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, g.dev_err);
     count_launch();
     return ADAMAH_OK;
 }
@@ -541,15 +628,23 @@ static int gemv(const Mat& m, const Mat* m2, GemvArgs a, int B, int epi) {
 // residual + FFN norm in the prologue, GeGLU in the epilogue), down GEMV.  The
 // residual stream alternates between two buffers because a prologue's CTA 0
 // writes the updated stream while the other CTAs still read the old one.
+static int enqueue_step_impl(Decoder* D, uint32_t batch, bool with_lm, bool want_logits);
 static int enqueue_step(Decoder* D, uint32_t batch, bool with_lm, bool want_logits) {
+    static const bool allow = !(getenv("ADAM_B200_PDL") && atoi(getenv("ADAM_B200_PDL")) == 0);
+    g.pdl = allow;
+    const int rc = enqueue_step_impl(D, batch, with_lm, want_logits);
+    g.pdl = false;
+    return rc;
+}
+static int enqueue_step_impl(Decoder* D, uint32_t batch, bool with_lm, bool want_logits) {
     const adam_b200_decoder_desc& d = D->d;
     const uint32_t E = d.n_embd, q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim, qkv_ld = q_dim + 2 * k_dim;
     int rc;
     int cur = 0;
     if (D->embd.wtype == WT_Q4_0)
-        k_embed<WT_Q4_0><<<batch, 256, 0, g.stream>>>(D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
+        launch_k(k_embed<WT_Q4_0>, dim3(batch), dim3(256), 0, g.stream, g.pdl, D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
     else
-        k_embed<WT_Q4_K><<<batch, 256, 0, g.stream>>>(D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
+        launch_k(k_embed<WT_Q4_K>, dim3(batch), dim3(256), 0, g.stream, g.pdl, D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
     count_launch();
     for (uint32_t L = 0; L < d.n_layer; ++L) {
         const Layer& ly = D->layers[L];
@@ -594,7 +689,7 @@ static int enqueue_step(Decoder* D, uint32_t batch, bool with_lm, bool want_logi
         if ((rc = gemv(lm, nullptr, a, batch, EPI_ARGMAX))) return rc;
         D->h_final = cur ^ 1;
     }
-    k_advance<<<(batch + 63) / 64, 64, 0, g.stream>>>(D->pos, D->cur_tok, D->gen_log, d.kv_cap, batch, with_lm ? 1 : 0);
+    launch_k(k_advance, dim3((batch + 63) / 64), dim3(64), 0, g.stream, g.pdl, D->pos, D->cur_tok, D->gen_log, d.kv_cap, batch, with_lm ? 1 : 0);
     count_launch();
     return check_launch("decoder step");
 }
@@ -651,6 +746,7 @@ extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint
     D->d.n_pages = D->n_pages;
     D->page_elems = (size_t)d.n_layer * 2 * d.n_head_kv * d.page_size * d.head_dim;
     D->n_splits = (d.kv_cap + ATTN_SPLIT - 1) / ATTN_SPLIT;
+    if (D->n_splits > ATTN_MAX_SPLITS) D->n_splits = ATTN_MAX_SPLITS;
     const size_t B = d.max_batch, E = d.n_embd, q_dim = (size_t)d.n_head * d.head_dim, k_dim = (size_t)d.n_head_kv * d.head_dim;
     const uint32_t gs = d.n_head / d.n_head_kv;
     g_dec[id] = D;

@@ -104,7 +104,7 @@ int launch_gemv(int wtype, GemvArgs a, cudaStream_t stream) {
         if (grid < 1) grid = 1;
         if (a.epi == EPI_ARGMAX && grid > GEMV_MAX_GRID) grid = GEMV_MAX_GRID;
         if (a.max_grid > 0 && grid > a.max_grid) grid = a.max_grid;
-        k<<<grid, block, smem, stream>>>(g1);
+        if (launch_k(k, dim3(grid), dim3(block), smem, stream, g.pdl, g1) != cudaSuccess) return fail(ADAMAH_ERR_BACKEND, "gemv: launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         count_launch();
     }
     return ADAMAH_OK;

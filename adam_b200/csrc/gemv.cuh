@@ -297,6 +297,8 @@ __global__ void __launch_bounds__(256, (WT == WT_Q4_0 && NB == 1) ? 2 : 1) k_gem
 #pragma unroll
     for (int i = 0; i < PF; ++i) if (f_cnt < T) fetch_next(ring[i]);
 
+    pdl_launch_dependents();
+    pdl_wait();             // the weight prefetch above is independent of earlier kernels; the activations are not
     {   // stage activations: group g of GE floats lands at xs[g * GS], its half sums in the pad
         const int n4 = a.K >> 2;
         if (a.h_in) {

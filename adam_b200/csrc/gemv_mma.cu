@@ -69,7 +69,7 @@ int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream
         if (a.epi == EPI_ARGMAX && grid > gemv_max_grid()) grid = gemv_max_grid();
         if (a.max_grid > 0 && grid > a.max_grid) grid = a.max_grid;
         if (grid < 1) grid = 1;
-        k<<<grid, 256, smem, stream>>>(g1, t0, t1, KS);
+        if (launch_k(k, dim3(grid), dim3(256), smem, stream, g.pdl, g1, t0, t1, KS) != cudaSuccess) return fail(ADAMAH_ERR_BACKEND, "gemv_mma: launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         count_launch();
     }
     return ADAMAH_OK;

@@ -173,6 +173,10 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
         for (int c = 0; c < NSTAGE; ++c) if (i_c < n_chunks) issue_next();
     }
 
+    // Everything above touches only the read-only weights; the activations come from the
+    // previous kernel.
+    pdl_launch_dependents();
+    pdl_wait();
     // ---- stage activations as signed bytes (hi, mid | lo) in MMA operand order ----
     {
         const int n4 = a.K >> 2;
