@@ -273,11 +273,28 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     static_assert(DPL >= 1 && (GS_MAX == 2 || GS_MAX == 4 || GS_MAX == 8), "unsupported attention shape");
     extern __shared__ __align__(16) float sm[];
     __shared__ float s_m[8][GS_MAX], s_l[8][GS_MAX];
-    __shared__ float s_M[GS_MAX], s_L[GS_MAX];
+    __shared__ float s_w[8][GS_MAX], s_M[GS_MAX];
     __shared__ bool s_last;
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // The block table is written by the host before the step's first kernel, so it can be
+    // read ahead of the dependency wait: up to 128 entries sit in registers across the warp.
+    const int32_t* bt = block_table + (size_t)b * geo.max_pages;
+    const bool bt_regs = geo.max_pages <= 128;
+    int32_t btr[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { const uint32_t i = lane + 32 * k; btr[k] = (bt_regs && i < geo.max_pages) ? bt[i] : -1; }
+    auto page_of = [&](uint32_t pn) -> int32_t {        // pn is the same for the whole warp
+        if (pn >= geo.max_pages) return -1;
+        if (!bt_regs) return bt[pn];
+        int32_t v = btr[0];
+        if (pn >= 32) v = btr[1];
+        if (pn >= 64) v = btr[2];
+        if (pn >= 96) v = btr[3];
+        return __shfl_sync(0xffffffffu, v, pn & 31);
+    };
     pdl_launch_dependents();
     pdl_wait();             // positions, q/k/v rows and the cache all come from earlier kernels
-    const uint32_t split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const uint32_t hd = HD, half = HD / 2, gs = n_head / geo.n_kv;
     const int32_t p = pos[b];
     const uint32_t seq = (uint32_t)p + 1;
@@ -293,24 +310,34 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     float* s_kn = s_q + gs * hd;                // [hd] newest key (as stored)
     float* s_vn = s_kn + hd;                    // [hd] newest value (as stored)
     float* s_o = s_vn + hd;                     // [8 warps][gs][hd]
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int32_t* bt = block_table + (size_t)b * geo.max_pages;
     const bool page8 = (geo.page % CP) == 0;
 
-    // Row j of chunk c: cache address, or null when the position is outside
-    // [start, seq) or is the newest one (taken from shared memory instead).
+    // Rows of chunk c.  Every load is unconditional (a predicated load would have to be
+    // merged with a zero right away, which serialises the loads): positions outside
+    // [start, seq) read a neighbouring valid row instead, and their scores are masked
+    // later; the cache is zero-filled at creation, so whatever is read is finite.
     KvRow<T, DPL> kr[CP], vr[CP];
     auto load_rows = [&](uint32_t c, uint32_t kv, KvRow<T, DPL> (&rows)[CP]) {
         const uint32_t tp0 = c * CP;
-        int32_t pg0 = 0;
-        if (page8) pg0 = max(bt[min(tp0 / geo.page, geo.max_pages - 1)], 0);
+        if (page8) {
+            // the chunk lies inside one page and its rows are consecutive
+            const uint32_t lo = max(tp0, start), hi = min(tp0 + CP, seq) - 1;
+            const uint32_t pn = tp0 / geo.page, slot0 = tp0 - pn * geo.page;
+            const int32_t pg0 = max(page_of(pn), 0);
+            const T* base = kv_pool + kv_index(geo, (uint32_t)pg0, layer, kv, kvh, slot0) + lane * DPL;
 #pragma unroll
-        for (int j = 0; j < CP; ++j) {
-            const uint32_t tp = tp0 + j;
-            if (tp >= start && tp < seq && tp != (uint32_t)p) {
-                const int32_t pg = page8 ? pg0 : max(bt[min(tp / geo.page, geo.max_pages - 1)], 0);
-                rows[j].load(kv_pool + kv_index(geo, (uint32_t)pg, layer, kv, kvh, tp % geo.page) + lane * DPL);
-            } else rows[j].zero();
+            for (int j = 0; j < CP; ++j) {
+                const uint32_t tp = min(max(tp0 + j, lo), hi);
+                rows[j].load(base + (size_t)(tp - tp0) * HD);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < CP; ++j) {
+                const uint32_t tp = min(max(tp0 + j, start), seq - 1);
+                const uint32_t pn = tp / geo.page;
+                const int32_t pg = max(page_of(pn), 0);
+                rows[j].load(kv_pool + kv_index(geo, (uint32_t)pg, layer, kv, kvh, tp - pn * geo.page) + lane * DPL);
+            }
         }
     };
     uint32_t c = c0 + warp;
@@ -332,7 +359,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         bool ok = true;
         if (!is_q) {
             const uint32_t page_no = (uint32_t)p / geo.page;
-            const int32_t page_id = page_no < geo.max_pages ? bt[page_no] : -1;
+            const int32_t page_id = page_of(page_no);
             if (page_id < 0) { ok = false; if (lane == 0) atomicOr(err, DEVERR_OOB_MAP); }
             else kv_off = kv_index(geo, (uint32_t)page_id, layer, is_k ? 0u : 1u, kvh, (uint32_t)p % geo.page);
         }
@@ -468,39 +495,59 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         if (c_next < c1) load_rows(c_next, 1, vr);
     }
     // ---- merge the warps ----
+    {
+        float* so = s_o + (size_t)warp * gs * hd + lane * DPL;
 #pragma unroll
-    for (int g = 0; g < GS_MAX; ++g)
-        if (g < (int)gs)
+        for (int g = 0; g < GS_MAX; ++g) {
+            if (g < (int)gs) {
+                if constexpr (DPL % 4 == 0) {
 #pragma unroll
-            for (int d = 0; d < DPL; ++d) s_o[(warp * gs + g) * hd + lane * DPL + d] = o[g][d];
+                    for (int d = 0; d < DPL; d += 4) *reinterpret_cast<float4*>(so + g * hd + d) = make_float4(o[g][d], o[g][d + 1], o[g][d + 2], o[g][d + 3]);
+                } else {
+#pragma unroll
+                    for (int d = 0; d < DPL; ++d) so[g * hd + d] = o[g][d];
+                }
+            }
+        }
+    }
 #pragma unroll
     for (int r = 0; r < VPL; ++r) {
         const uint32_t v = NV >= 32 ? lane * VPL + r : lane >> 1;
         if (v < GS_MAX && (NV >= 32 || (lane & 1) == 0)) { s_m[warp][v] = m_run[r]; s_l[warp][v] = l_run[r]; }
     }
     __syncthreads();
-    if (tid < gs) {
-        float M = NEG, L = 0.f;
+    if (tid < 8 * GS_MAX) {                     // weight of warp w for head g
+        const uint32_t w = tid / GS_MAX, g = tid % GS_MAX;
+        float M = NEG;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) M = fmaxf(M, s_m[w][tid]);
-#pragma unroll
-        for (int w = 0; w < 8; ++w) L = fmaf(expf(s_m[w][tid] - M), s_l[w][tid], L);
-        s_M[tid] = M; s_L[tid] = L;
+        for (int w2 = 0; w2 < 8; ++w2) M = fmaxf(M, s_m[w2][g]);
+        s_w[w][g] = expf(s_m[w][g] - M);
+        if (w == 0) s_M[g] = M;
     }
     __syncthreads();
+    // thread -> 4 consecutive outputs (all of one head)
+    const uint32_t n_out4 = gs * hd / 4;
     float* po = part_o + (((size_t)b * geo.n_kv + kvh) * n_splits_max + split) * gs * hd;
     float* pml = part_ml + (((size_t)b * geo.n_kv + kvh) * n_splits_max + split) * gs * 2;
-    for (uint32_t i = tid; i < gs * hd; i += blockDim.x) {
-        const uint32_t g = i / hd;
-        const float M = s_M[g];
-        float v = 0.f;
+    float* orow = out + ((size_t)b * n_head + (size_t)kvh * gs) * hd;
+    for (uint32_t i4 = tid; i4 < n_out4; i4 += blockDim.x) {
+        const uint32_t g = (i4 * 4) / hd;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) v = fmaf(expf(s_m[w][g] - M), s_o[w * gs * hd + i], v);
-        if (n_act == 1) out[((size_t)b * n_head + (size_t)kvh * gs) * hd + i] = v / s_L[g];
-        else po[i] = v;
+        for (int w = 0; w < 8; ++w) {
+            const float ww = s_w[w][g];
+            const float4 x = *reinterpret_cast<const float4*>(s_o + (size_t)w * gs * hd + i4 * 4);
+            v.x = fmaf(ww, x.x, v.x); v.y = fmaf(ww, x.y, v.y); v.z = fmaf(ww, x.z, v.z); v.w = fmaf(ww, x.w, v.w);
+            L = fmaf(ww, s_l[w][g], L);
+        }
+        if (n_act == 1) { v.x /= L; v.y /= L; v.z /= L; v.w /= L; reinterpret_cast<float4*>(orow)[i4] = v; }
+        else {
+            reinterpret_cast<float4*>(po)[i4] = v;
+            if ((i4 * 4) % hd == 0) *reinterpret_cast<float2*>(pml + g * 2) = make_float2(s_M[g], L);
+        }
     }
     if (n_act == 1) return;
-    if (tid < gs) { pml[tid * 2] = s_M[tid]; pml[tid * 2 + 1] = s_L[tid]; }
     __threadfence();
     __syncthreads();
     unsigned int* tkt = ticket + (size_t)b * geo.n_kv + kvh;
@@ -508,27 +555,39 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // ---- merge the splits (last CTA to arrive) ----
+    // ---- merge the splits (last CTA to arrive): all loads of a batch of 4 splits are
+    // issued together, then folded in with a running maximum ----
     const float* po0 = part_o + (((size_t)b * geo.n_kv + kvh) * n_splits_max) * gs * hd;
     const float* pml0 = part_ml + (((size_t)b * geo.n_kv + kvh) * n_splits_max) * gs * 2;
-    if (tid < gs) {
-        float M = NEG;
-        for (uint32_t s = 0; s < n_act; ++s) M = fmaxf(M, __ldcg(pml0 + ((size_t)s * gs + tid) * 2));
-        s_M[tid] = M;
-    }
-    __syncthreads();
-    for (uint32_t i = tid; i < gs * hd; i += blockDim.x) {
-        const uint32_t g = i / hd;
-        const float M = s_M[g];
-        float num = 0.f, den = 0.f;
-#pragma unroll 4
-        for (uint32_t s = 0; s < n_act; ++s) {
-            const float2 ml = __ldcg(reinterpret_cast<const float2*>(pml0 + ((size_t)s * gs + g) * 2));
-            const float w = expf(ml.x - M);
-            num = fmaf(w, __ldcg(po0 + (size_t)s * gs * hd + i), num);
-            den = fmaf(w, ml.y, den);
+    for (uint32_t i4 = tid; i4 < n_out4; i4 += blockDim.x) {
+        const uint32_t g = (i4 * 4) / hd;
+        float M = NEG, den = 0.f;
+        float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t s0 = 0; s0 < n_act; s0 += 4) {
+            float2 ml[4]; float4 x[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t sidx = min(s0 + k, n_act - 1);
+                ml[k] = __ldcg(reinterpret_cast<const float2*>(pml0 + ((size_t)sidx * gs + g) * 2));
+                x[k] = __ldcg(reinterpret_cast<const float4*>(po0 + (size_t)sidx * gs * hd) + i4);
+            }
+            float Mn = M;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) if (s0 + k < n_act) Mn = fmaxf(Mn, ml[k].x);
+            const float a0 = expf(M - Mn);
+            num.x *= a0; num.y *= a0; num.z *= a0; num.w *= a0; den *= a0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (s0 + k < n_act) {
+                    const float w = expf(ml[k].x - Mn);
+                    num.x = fmaf(w, x[k].x, num.x); num.y = fmaf(w, x[k].y, num.y);
+                    num.z = fmaf(w, x[k].z, num.z); num.w = fmaf(w, x[k].w, num.w);
+                    den = fmaf(w, ml[k].y, den);
+                }
+            }
+            M = Mn;
         }
-        out[((size_t)b * n_head + (size_t)kvh * gs) * hd + i] = num / den;
+        reinterpret_cast<float4*>(orow)[i4] = make_float4(num.x / den, num.y / den, num.z / den, num.w / den);
     }
     if (tid == 0) *tkt = 0u;
 }
