@@ -80,10 +80,27 @@ __device__ __forceinline__ void put_x4(signed char* xb1, signed char* xb2, int k
 // Power-of-two scale that brings amax to at most 2^22 (and its inverse).
 __device__ __forceinline__ void pow2_scale(float amax, float& s, float& inv) {
     if (!(amax > 0.f) || !(amax < 3.0e38f)) { s = 1.f; inv = 1.f; return; }
-    int e;
-    frexpf(amax, &e);
+    // amax = m * 2^e with m in [0.5, 1)  (denormals count as e = -126)
+    int e = (int)((__float_as_uint(amax) >> 23) & 0xFFu) - 126;
     e = max(-100, min(100, 22 - e));
-    s = ldexpf(1.f, e); inv = ldexpf(1.f, -e);
+    s = __uint_as_float((uint32_t)(127 + e) << 23);
+    inv = __uint_as_float((uint32_t)(127 - e) << 23);
+}
+
+// Block-wide sum of `sv` and maximum of `mv` in one pass (red: 66 floats).
+__device__ __forceinline__ void block_sum_max(float& sv, float& mv, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sv += __shfl_xor_sync(0xffffffffu, sv, o);
+        mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, o));
+    }
+    __syncthreads();
+    if (lane == 0) { red[warp] = sv; red[33 + warp] = mv; }
+    __syncthreads();
+    float a = 0.f, m = -3.402823466e+38f;
+    for (int w = 0; w < nw; ++w) { a += red[w]; m = fmaxf(m, red[33 + w]); }
+    sv = a; mv = m;
 }
 
 // ---- bulk-copy pipeline primitives (cp.async.bulk + mbarrier, all waits bounded) ----
@@ -118,7 +135,7 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ float s_red[2][8][PAIR ? 2 : 1][16][4];
     __shared__ float s_inv[4];
-    __shared__ float red[33];
+    __shared__ float red[66];
     __shared__ float s_bv[8 * 4];
     __shared__ int   s_bi[8 * 4];
     __shared__ bool  s_last;
@@ -173,7 +190,21 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
         for (int c = 0; c < NSTAGE; ++c) if (i_c < n_chunks) issue_next();
     }
 
-    // Everything above touches only the read-only weights; the activations come from the
+    // Norm weights of the input chain (read-only, like the matrix): fetched ahead of the wait.
+    float4 vp[3], vw[3];
+    {
+        const float4 o4 = make_float4(1.f, 1.f, 1.f, 1.f);
+        const int n4 = a.K >> 2;
+        const bool chain = a.h_in && n4 <= 3 * (int)blockDim.x;
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            const bool in = chain && i < n4;
+            vp[j] = (in && a.add_src && a.w_post) ? reinterpret_cast<const float4*>(a.w_post)[i] : o4;
+            vw[j] = (in && a.w_pre) ? reinterpret_cast<const float4*>(a.w_pre)[i] : o4;
+        }
+    }
+    // Everything above touches only read-only weights; the activations come from the
     // previous kernel.
     pdl_launch_dependents();
     pdl_wait();
@@ -185,16 +216,14 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
             if (a.h_in && n4 <= 3 * (int)blockDim.x) {
                 const float* hp = a.h_in + row;
                 const float* ap = a.add_src ? a.add_src + row : nullptr;
-                float4 va[3], vh[3], vp[3], vw[3];
-                const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f), o4 = make_float4(1.f, 1.f, 1.f, 1.f);
+                float4 va[3], vh[3];
+                const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int j = 0; j < 3; ++j) {
                     const int i = threadIdx.x + j * blockDim.x;
                     const bool in = i < n4;
                     vh[j] = in ? reinterpret_cast<const float4*>(hp)[i] : z4;
                     va[j] = (in && ap) ? reinterpret_cast<const float4*>(ap)[i] : z4;
-                    vp[j] = (in && ap && a.w_post) ? reinterpret_cast<const float4*>(a.w_post)[i] : o4;
-                    vw[j] = (in && a.w_pre) ? reinterpret_cast<const float4*>(a.w_pre)[i] : o4;
                 }
                 float rms_a = 1.f;
                 if (ap && a.w_post) {
@@ -204,7 +233,8 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
                     ss = block_sum(ss, red);
                     rms_a = sqrtf(ss / (float)a.K + a.eps);
                 }
-                float ss = 0.f;
+                // h' and, in the same reduction, its sum of squares and max |h' * w_pre|
+                float ss = 0.f, am = 0.f;
 #pragma unroll
                 for (int j = 0; j < 3; ++j) {
                     if (ap) {
@@ -214,21 +244,21 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
                         } else { vh[j].x += va[j].x; vh[j].y += va[j].y; vh[j].z += va[j].z; vh[j].w += va[j].w; }
                     }
                     ss = fmaf(vh[j].x, vh[j].x, ss); ss = fmaf(vh[j].y, vh[j].y, ss); ss = fmaf(vh[j].z, vh[j].z, ss); ss = fmaf(vh[j].w, vh[j].w, ss);
+                    am = fmaxf(am, fmaxf(fmaxf(fabsf(vh[j].x * vw[j].x), fabsf(vh[j].y * vw[j].y)), fmaxf(fabsf(vh[j].z * vw[j].z), fabsf(vh[j].w * vw[j].w))));
                     const int i = threadIdx.x + j * blockDim.x;
                     if (i < n4 && a.h_out && blockIdx.x == 0) reinterpret_cast<float4*>(a.h_out + row)[i] = vh[j];
                 }
+                block_sum_max(ss, am, red);
                 float rms = 1.f;
-                if (a.w_pre) { ss = block_sum(ss, red); rms = sqrtf(ss / (float)a.K + a.eps); }
-                float am = 0.f;
+                if (a.w_pre) {
+                    rms = sqrtf(ss / (float)a.K + a.eps);
+                    am = am / rms * 1.000001f;             // bound on max |x| (the scale has a factor 2 to spare)
 #pragma unroll
-                for (int j = 0; j < 3; ++j) {
-                    if (a.w_pre) {
+                    for (int j = 0; j < 3; ++j) {
                         vh[j].x = __fdiv_rn(vh[j].x, rms) * vw[j].x; vh[j].y = __fdiv_rn(vh[j].y, rms) * vw[j].y;
                         vh[j].z = __fdiv_rn(vh[j].z, rms) * vw[j].z; vh[j].w = __fdiv_rn(vh[j].w, rms) * vw[j].w;
                     }
-                    am = fmaxf(am, fmaxf(fmaxf(fabsf(vh[j].x), fabsf(vh[j].y)), fmaxf(fabsf(vh[j].z), fabsf(vh[j].w))));
                 }
-                am = block_max(am, red);
                 float s, inv;
                 pow2_scale(am, s, inv);
                 if (threadIdx.x == 0) s_inv[b] = inv;
