@@ -101,6 +101,14 @@ inline cudaError_t launch_k(void (*k)(KArgs...), dim3 grid, dim3 block, size_t s
 // Programmatic dependent launch: let the next kernel in the stream start its
 // independent prologue now / wait until every earlier kernel's writes are visible.
 // Both are no-ops for kernels launched the ordinary way.
+// x / d for many x and one d, without the branchy IEEE division sequence: r = RN(1/d)
+// once, then one Newton correction of the quotient (correctly rounded whenever nothing
+// under- or overflows on the way).
+__device__ __forceinline__ float div_by(float x, float d, float r) {
+    const float q = x * r;
+    return fmaf(fmaf(-q, d, x), r, q);
+}
+
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

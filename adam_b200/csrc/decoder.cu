@@ -395,12 +395,13 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             ss = warp_sum(ss);
             rms = sqrtf(ss / (float)hd + eps);
         }
+        const float rcp = __frcp_rn(rms);
 #pragma unroll
         for (int j = 0; j < NP; ++j) {
             const uint32_t i = lane + 32 * j;
             if (i < half) {
                 float a0 = x0[j], a1 = x1[j];
-                if (w) { a0 = __fdiv_rn(a0, rms) * w0[j]; a1 = __fdiv_rn(a1, rms) * w1[j]; }
+                if (w) { a0 = div_by(a0, rms, rcp) * w0[j]; a1 = div_by(a1, rms, rcp) * w1[j]; }
                 const float y0 = __fsub_rn(__fmul_rn(a0, cs[j]), __fmul_rn(a1, sn[j]));
                 const float y1 = __fadd_rn(__fmul_rn(a0, sn[j]), __fmul_rn(a1, cs[j]));
                 if (is_q) { s_q[r * hd + i] = y0; s_q[r * hd + i + half] = y1; }

@@ -332,12 +332,13 @@ __global__ void __launch_bounds__(256, (WT == WT_Q4_0 && NB == 1) ? 2 : 1) k_gem
                         rms_a = sqrtf(ss / (float)a.K + a.eps);
                     }
                     float ss = 0.f;
+                    const float rcp_a = __frcp_rn(rms_a);
 #pragma unroll
                     for (int j = 0; j < 3; ++j) {
                         if (ap) {
                             if (a.w_post) {
-                                vh[j].x += __fdiv_rn(va[j].x, rms_a) * vp[j].x; vh[j].y += __fdiv_rn(va[j].y, rms_a) * vp[j].y;
-                                vh[j].z += __fdiv_rn(va[j].z, rms_a) * vp[j].z; vh[j].w += __fdiv_rn(va[j].w, rms_a) * vp[j].w;
+                                vh[j].x += div_by(va[j].x, rms_a, rcp_a) * vp[j].x; vh[j].y += div_by(va[j].y, rms_a, rcp_a) * vp[j].y;
+                                vh[j].z += div_by(va[j].z, rms_a, rcp_a) * vp[j].z; vh[j].w += div_by(va[j].w, rms_a, rcp_a) * vp[j].w;
                             } else { vh[j].x += va[j].x; vh[j].y += va[j].y; vh[j].z += va[j].z; vh[j].w += va[j].w; }
                         }
                         ss = fmaf(vh[j].x, vh[j].x, ss); ss = fmaf(vh[j].y, vh[j].y, ss); ss = fmaf(vh[j].z, vh[j].z, ss); ss = fmaf(vh[j].w, vh[j].w, ss);
@@ -346,12 +347,13 @@ __global__ void __launch_bounds__(256, (WT == WT_Q4_0 && NB == 1) ? 2 : 1) k_gem
                     }
                     float rms = 1.f;
                     if (a.w_pre) { ss = block_sum(ss, red); rms = sqrtf(ss / (float)a.K + a.eps); }
+                    const float rcp = __frcp_rn(rms);
 #pragma unroll
                     for (int j = 0; j < 3; ++j) {
                         const int i = threadIdx.x + j * blockDim.x;
                         if (i < n4) {
                             float4 v = vh[j];
-                            if (a.w_pre) { v.x = __fdiv_rn(v.x, rms) * vw[j].x; v.y = __fdiv_rn(v.y, rms) * vw[j].y; v.z = __fdiv_rn(v.z, rms) * vw[j].z; v.w = __fdiv_rn(v.w, rms) * vw[j].w; }
+                            if (a.w_pre) { v.x = div_by(v.x, rms, rcp) * vw[j].x; v.y = div_by(v.y, rms, rcp) * vw[j].y; v.z = div_by(v.z, rms, rcp) * vw[j].z; v.w = div_by(v.w, rms, rcp) * vw[j].w; }
                             const int e = i * 4;
                             *reinterpret_cast<float4*>(xb + (e / GE) * GS + (e % GE)) = v;
                         }

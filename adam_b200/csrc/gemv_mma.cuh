@@ -233,14 +233,15 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
                     ss = block_sum(ss, red);
                     rms_a = sqrtf(ss / (float)a.K + a.eps);
                 }
+                const float rcp_a = __frcp_rn(rms_a);
                 // h' and, in the same reduction, its sum of squares and max |h' * w_pre|
                 float ss = 0.f, am = 0.f;
 #pragma unroll
                 for (int j = 0; j < 3; ++j) {
                     if (ap) {
                         if (a.w_post) {
-                            vh[j].x += __fdiv_rn(va[j].x, rms_a) * vp[j].x; vh[j].y += __fdiv_rn(va[j].y, rms_a) * vp[j].y;
-                            vh[j].z += __fdiv_rn(va[j].z, rms_a) * vp[j].z; vh[j].w += __fdiv_rn(va[j].w, rms_a) * vp[j].w;
+                            vh[j].x += div_by(va[j].x, rms_a, rcp_a) * vp[j].x; vh[j].y += div_by(va[j].y, rms_a, rcp_a) * vp[j].y;
+                            vh[j].z += div_by(va[j].z, rms_a, rcp_a) * vp[j].z; vh[j].w += div_by(va[j].w, rms_a, rcp_a) * vp[j].w;
                         } else { vh[j].x += va[j].x; vh[j].y += va[j].y; vh[j].z += va[j].z; vh[j].w += va[j].w; }
                     }
                     ss = fmaf(vh[j].x, vh[j].x, ss); ss = fmaf(vh[j].y, vh[j].y, ss); ss = fmaf(vh[j].z, vh[j].z, ss); ss = fmaf(vh[j].w, vh[j].w, ss);
@@ -252,11 +253,12 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
                 float rms = 1.f;
                 if (a.w_pre) {
                     rms = sqrtf(ss / (float)a.K + a.eps);
-                    am = am / rms * 1.000001f;             // bound on max |x| (the scale has a factor 2 to spare)
+                    const float rcp = __frcp_rn(rms);
+                    am = am * rcp * 1.000001f;             // bound on max |x| (the scale has a factor 2 to spare)
 #pragma unroll
                     for (int j = 0; j < 3; ++j) {
-                        vh[j].x = __fdiv_rn(vh[j].x, rms) * vw[j].x; vh[j].y = __fdiv_rn(vh[j].y, rms) * vw[j].y;
-                        vh[j].z = __fdiv_rn(vh[j].z, rms) * vw[j].z; vh[j].w = __fdiv_rn(vh[j].w, rms) * vw[j].w;
+                        vh[j].x = div_by(vh[j].x, rms, rcp) * vw[j].x; vh[j].y = div_by(vh[j].y, rms, rcp) * vw[j].y;
+                        vh[j].z = div_by(vh[j].z, rms, rcp) * vw[j].z; vh[j].w = div_by(vh[j].w, rms, rcp) * vw[j].w;
                     }
                 }
                 float s, inv;
