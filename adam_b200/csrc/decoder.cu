@@ -211,6 +211,20 @@ template <typename T, int DPL> struct KvRow {
             w[0] = *reinterpret_cast<const unsigned short*>(p);
         }
     }
+    __device__ __forceinline__ void from_float(const float* f) {      // values already rounded to T
+        if constexpr (sizeof(T) == 4) {
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) w[i] = __float_as_uint(f[i]);
+        } else if constexpr (DPL >= 2) {
+#pragma unroll
+            for (int i = 0; i < DPL / 2; ++i) {
+                const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        } else {
+            w[0] = __half_as_ushort(__float2half_rn(f[0]));
+        }
+    }
     __device__ __forceinline__ void to_float(float (&f)[DPL]) const {
         if constexpr (sizeof(T) == 4) {
 #pragma unroll
@@ -293,6 +307,16 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         if (pn >= 96) v = btr[3];
         return __shfl_sync(0xffffffffu, v, pn & 31);
     };
+    // QK-norm weights are read-only too.
+    constexpr int NP = (HD / 2 + 31) / 32;          // rotation pairs per lane
+    float wq0[NP], wq1[NP], wk0[NP], wk1[NP];
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+        const uint32_t i = lane + 32 * j;
+        const bool in = i < HD / 2;
+        wq0[j] = (in && q_norm) ? q_norm[i] : 1.f; wq1[j] = (in && q_norm) ? q_norm[i + HD / 2] : 1.f;
+        wk0[j] = (in && k_norm) ? k_norm[i] : 1.f; wk1[j] = (in && k_norm) ? k_norm[i + HD / 2] : 1.f;
+    }
     pdl_launch_dependents();
     pdl_wait();             // positions, q/k/v rows and the cache all come from earlier kernels
     const uint32_t hd = HD, half = HD / 2, gs = n_head / geo.n_kv;
@@ -372,7 +396,6 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             continue;
         }
         const float* w = is_q ? q_norm : k_norm;
-        constexpr int NP = (HD / 2 + 31) / 32;          // rotation pairs per lane
         float x0[NP], x1[NP], w0[NP], w1[NP], cs[NP], sn[NP];
 #pragma unroll
         for (int j = 0; j < NP; ++j) {
@@ -380,8 +403,8 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             const bool in = i < half;
             x0[j] = in ? src[i] : 0.f;
             x1[j] = in ? src[i + half] : 0.f;
-            w0[j] = (in && w) ? w[i] : 1.f;
-            w1[j] = (in && w) ? w[i + half] : 1.f;
+            w0[j] = is_q ? wq0[j] : wk0[j];
+            w1[j] = is_q ? wq1[j] : wk1[j];
             cs[j] = in ? ct[i] : 1.f;
             sn[j] = in ? st[i] : 0.f;
         }
@@ -423,22 +446,29 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
 #pragma unroll
     for (int r = 0; r < VPL; ++r) { m_run[r] = NEG; l_run[r] = 0.f; }
     for (; c < c1; c += 8) {
-        const bool has_new = (c == c_new);
+        if (c == c_new) {
+            // the newest position's rows come from this step's q/k/v, not from the cache
+            KvRow<T, DPL> nk, nv;
+            nk.from_float(s_kn + lane * DPL); nv.from_float(s_vn + lane * DPL);
+            const int jn = (int)((uint32_t)p % CP);
+#pragma unroll
+            for (int j = 0; j < CP; ++j) if (j == jn) { kr[j] = nk; vr[j] = nv; }
+        }
         float sc[NV];
 #pragma unroll
         for (int j = 0; j < CP; ++j) {
             float kf[DPL];
             kr[j].to_float(kf);
-            if (has_new && j == (int)((uint32_t)p % CP)) {
-#pragma unroll
-                for (int d = 0; d < DPL; ++d) kf[d] = s_kn[lane * DPL + d];
-            }
 #pragma unroll
             for (int g = 0; g < GS_MAX; ++g) {
-                float acc = 0.f;
+                if constexpr (DPL >= 2) {
+                    float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-                for (int d = 0; d < DPL; ++d) acc = fmaf(q[g][d], kf[d], acc);
-                sc[j * GS_MAX + g] = acc;
+                    for (int d = 0; d < DPL; d += 2) fma2(a0, a1, q[g][d], q[g][d + 1], kf[d], kf[d + 1]);
+                    sc[j * GS_MAX + g] = a0 + a1;
+                } else {
+                    sc[j * GS_MAX + g] = q[g][0] * kf[0];
+                }
             }
         }
         const uint32_t c_next = c + 8;
@@ -480,17 +510,16 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         for (int j = 0; j < CP; ++j) {
             float vf[DPL];
             vr[j].to_float(vf);
-            if (has_new && j == (int)((uint32_t)p % CP)) {
-#pragma unroll
-                for (int d = 0; d < DPL; ++d) vf[d] = s_vn[lane * DPL + d];
-            }
 #pragma unroll
             for (int g = 0; g < GS_MAX; ++g) {
-                constexpr int vidx0 = 0;
-                const int v = j * GS_MAX + g + vidx0;
+                const int v = j * GS_MAX + g;
                 const float pv = __shfl_sync(0xffffffffu, pz[v % VPL], NV >= 32 ? v / VPL : v * 2);
+                if constexpr (DPL >= 2) {
 #pragma unroll
-                for (int d = 0; d < DPL; ++d) o[g][d] = fmaf(pv, vf[d], o[g][d]);
+                    for (int d = 0; d < DPL; d += 2) fma2(o[g][d], o[g][d + 1], pv, pv, vf[d], vf[d + 1]);
+                } else {
+                    o[g][0] = fmaf(pv, vf[0], o[g][0]);
+                }
             }
         }
         if (c_next < c1) load_rows(c_next, 1, vr);
