@@ -3,31 +3,31 @@
 // Why tensor cores in a memory-bound GEMV: on the plain CUDA-core path the unpack
 // (one byte-permute per weight, on the half-rate integer pipe) and one FMA per weight
 // cap the kernel at about half of HBM bandwidth.  Here a 16-row x 32-weight block is
-// one integer MMA (mma.sync.m16n8k32, u8 x s8 -> s32) per activation operand:
-//   * weights enter as the raw nibbles 0..15 (u8): two logic ops split a 32-bit word
+// ONE integer MMA (mma.sync.m16n8k32, u8 x s8 -> s32):
+//   * weights enter as the raw nibbles 0..15 (u8): three logic ops split a 32-bit word
 //     into its four low and four high nibbles, which are exactly the A registers;
 //   * the activation vector is scaled by a power of two s (chosen per vector so that
 //     |x*s| <= 2^22), rounded to an integer and split into three signed bytes
-//     x*s = hi*65536 + mid*256 + lo, i.e. 23 bits of every activation are kept; the
-//     B operand of the first MMA holds the (hi, mid) columns, the second the lo column;
-//   * the block's exact integer sums are recombined in fp32, the -8 offset of Q4_0 is
-//     removed with the pre-summed activations of the block, and the result is scaled
-//     by the block scale d and accumulated in fp32 on the CUDA cores.
+//     x*s = hi*65536 + mid*256 + lo, i.e. 23 bits of every activation are kept.  The
+//     8-wide B operand holds, for up to two batch rows, the columns (hi, mid, lo, 0);
+//   * lane (g, t) = (lane/4, lane%4) receives rows g and g+8 of column pair t: an even
+//     t sees (hi, mid), an odd t sees (lo, 0), and both form v = d0*256 + d1 in integer
+//     arithmetic (exact), convert it once, remove the -8 offset of Q4_0 with the block's
+//     pre-summed activations (kept in the same units), scale by the block scale d and
+//     accumulate in fp32.  Even and odd lanes differ by the constant factor 65536, which
+//     is applied once per row group when the two are added.
 // The tensor pipe stays almost idle: the kernel is a stream over the weight bytes.
 //
-// Columns of the 8-wide B operand: (2b, 2b+1) = (hi, mid) [first MMA] or (lo, 0)
-// [second MMA] of batch row b, b < 4.  With one batch row only columns 0,1 are staged.
+// Batch rows 2i and 2i+1 use MMA i of a block (NI = 1 or 2 MMAs per block, batch <= 4).
 // A warp owns one 16-row group and a slice of K; the KS warps that share a row group
-// combine through shared memory.  Lane (g, t) = (lane/4, lane%4) holds rows g and g+8
-// for batch row t.  Weight tiles reach shared memory through a per-warp ring of bulk
-// copies (cp.async.bulk + mbarrier), so no load scoreboard limits the bytes in flight.
+// combine through shared memory.  Weight tiles reach shared memory through a per-warp
+// ring of bulk copies (cp.async.bulk + mbarrier), so no load scoreboard limits the
+// bytes in flight; every wait on the ring is bounded.
 #pragma once
 #include "common.cuh"
 #include "gemv.cuh"
 
 namespace ab {
-
-struct MmaSlot { uint4 q; uint2 sc; };
 
 // D = A(u8, 16x32) * B(s8, 32x8) with a zero accumulator input.
 __device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -38,29 +38,18 @@ __device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1,
 
 // Staged activation bytes: block u (32 activations), column c, quad lane t -> 8 bytes
 // { k = 4t..4t+3 , k = 16+4t..16+4t+3 } which are the two B registers of lane (c, t).
+// NCOL columns are staged per block: 4 (one batch row), 8 (two) or 16 (up to four).
 template <int NCOL>
 __device__ __forceinline__ int xb_index(int k, int col) {
     const int u = k >> 5, w = k & 31;
     return ((u * NCOL + col) * 4 + ((w & 15) >> 2)) * 8 + (w >> 4) * 4 + (w & 3);
 }
 
-// x*s rounded to an integer and split into three signed bytes (hi, mid, lo).
+// Four consecutive scaled activations (k0 a multiple of 4) of batch row b: round to
+// integers, split into three signed bytes each, and store one 32-bit word into each
+// of the row's four columns (hi, mid, lo, zero).
 template <int NCOL>
-__device__ __forceinline__ void put_x(signed char* xb1, signed char* xb2, int k, int b, float v_scaled) {
-    const int xi = __float2int_rn(v_scaled);
-    const int lo = ((xi + 128) & 0xFF) - 128;
-    const int r = (xi - lo) >> 8;
-    const int mid = ((r + 128) & 0xFF) - 128;
-    const int hi = (r - mid) >> 8;
-    xb1[xb_index<NCOL>(k, 2 * b)] = (signed char)hi;
-    xb1[xb_index<NCOL>(k, 2 * b + 1)] = (signed char)mid;
-    xb2[xb_index<NCOL>(k, 2 * b)] = (signed char)lo;
-}
-
-// Four consecutive activations (k0 a multiple of 4) at once: they share one 32-bit word
-// in each of the three byte planes.
-template <int NCOL>
-__device__ __forceinline__ void put_x4(signed char* xb1, signed char* xb2, int k0, int b, float4 v) {
+__device__ __forceinline__ void put_x4(signed char* xb, int k0, int b, float4 v) {
     const float f[4] = {v.x, v.y, v.z, v.w};
     uint32_t wh = 0, wm = 0, wl = 0;
 #pragma unroll
@@ -72,9 +61,12 @@ __device__ __forceinline__ void put_x4(signed char* xb1, signed char* xb2, int k
         const int hi = (r - mid) >> 8;
         wh |= (uint32_t)(hi & 0xFF) << (8 * i); wm |= (uint32_t)(mid & 0xFF) << (8 * i); wl |= (uint32_t)(lo & 0xFF) << (8 * i);
     }
-    *reinterpret_cast<uint32_t*>(xb1 + xb_index<NCOL>(k0, 2 * b)) = wh;
-    *reinterpret_cast<uint32_t*>(xb1 + xb_index<NCOL>(k0, 2 * b + 1)) = wm;
-    *reinterpret_cast<uint32_t*>(xb2 + xb_index<NCOL>(k0, 2 * b)) = wl;
+    const int c0 = 4 * b;
+    const int i0 = xb_index<NCOL>(k0, c0);          // columns of one block are 32 bytes apart
+    *reinterpret_cast<uint32_t*>(xb + i0) = wh;
+    *reinterpret_cast<uint32_t*>(xb + i0 + 32) = wm;
+    *reinterpret_cast<uint32_t*>(xb + i0 + 64) = wl;
+    *reinterpret_cast<uint32_t*>(xb + i0 + 96) = 0u;
 }
 
 // Power-of-two scale that brings amax to at most 2^22 (and its inverse).
@@ -127,20 +119,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
-constexpr int MMA_CH = 3;                  // tile pairs per bulk copy
-constexpr int MMA_TILE = 576;              // bytes per tile pair
+constexpr int MMA_TILE = 576;              // bytes per tile pair (16 rows x 64 weights: 512 nibble bytes + 32 fp16 scales)
+constexpr int MMA_NSTAGE = 3;              // ring stages per warp
+constexpr int MMA_MAX_WARPS = 16;
+template <bool PAIR> struct MmaGeo {
+    static constexpr int CH = PAIR ? 3 : 6;                                 // tile pairs per stage and matrix
+    static constexpr int STAGE_BYTES = CH * MMA_TILE * (PAIR ? 2 : 1);      // 3456
+};
+constexpr int MMA_RING_BYTES_PER_WARP = MMA_NSTAGE * 6 * MMA_TILE;
 
 template <int NCOL, bool PAIR>
-__global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uint8_t* __restrict__ t0, const uint8_t* __restrict__ t1, int KS) {
+__global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a, const uint8_t* __restrict__ t0, const uint8_t* __restrict__ t1, int KS) {
+    constexpr int NI = NCOL == 16 ? 2 : 1;      // MMAs per block
+    constexpr int NBR = NCOL / 4;               // batch rows staged
+    constexpr int NPR = NCOL / 2;               // column pairs per block (one pre-summed value each)
+    constexpr int NM = PAIR ? 2 : 1;
+    constexpr int CH = MmaGeo<PAIR>::CH;
+    constexpr int STAGE_BYTES = MmaGeo<PAIR>::STAGE_BYTES;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __shared__ float s_red[2][8][PAIR ? 2 : 1][16][4];
+    __shared__ float s_red[2][MMA_MAX_WARPS][NM][NI][16][2];
+    __shared__ __align__(8) uint64_t s_bar[MMA_MAX_WARPS][MMA_NSTAGE];
     __shared__ float s_inv[4];
     __shared__ float red[66];
-    __shared__ float s_bv[8 * 4];
-    __shared__ int   s_bi[8 * 4];
+    __shared__ float s_bv[MMA_MAX_WARPS * 4];
+    __shared__ int   s_bi[MMA_MAX_WARPS * 4];
     __shared__ bool  s_last;
-    constexpr int NB = NCOL / 2;
-    constexpr int MMA_PF = PAIR ? 3 : 6;       // tile pairs in flight per warp and matrix
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int RG = n_warps / KS, rg_l = warp / KS, ks = warp % KS;
@@ -149,47 +152,40 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
     const int n_sets = (n_rg + RG - 1) / RG;
     const int p0 = (int)((long long)ks * pairs / KS), p1 = (int)((long long)(ks + 1) * pairs / KS), np = p1 - p0;
     const int my_sets = (n_sets > (int)blockIdx.x) ? (n_sets - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    const int T = my_sets * np;
 
     // ---- weight stream: every warp runs its own ring of bulk copies into shared memory ----
-    // Stage = MMA_CH consecutive tile pairs of the warp's row group (contiguous in memory),
+    // Stage = up to CH consecutive tile pairs of the warp's row group (contiguous in memory),
     // one cp.async.bulk per matrix, completion counted on the stage's mbarrier.
-    constexpr int NSTAGE = PAIR ? 2 : 4;
-    constexpr int STAGE_BYTES = MMA_CH * MMA_TILE * (PAIR ? 2 : 1);
-    __shared__ __align__(8) uint64_t s_bar[8][NSTAGE];
-    // staged activations: (hi, mid) bytes, lo bytes, per-block integer sums
-    signed char* xb1 = reinterpret_cast<signed char*>(smem_raw);
-    signed char* xb2 = xb1 + (size_t)units * NCOL * 32;
-    float* s_sx = reinterpret_cast<float*>(smem_raw + (size_t)units * NCOL * 64);          // [units][NB]
-    unsigned char* ring = smem_raw + (((size_t)units * (NCOL * 64 + NB * 4) + 127) & ~(size_t)127) + (size_t)warp * NSTAGE * STAGE_BYTES;
-    const int nch = (np + MMA_CH - 1) / MMA_CH;             // chunks per row group for this warp
+    signed char* xb = reinterpret_cast<signed char*>(smem_raw);                            // [units][NCOL][32]
+    float* s_sx = reinterpret_cast<float*>(smem_raw + (size_t)units * NCOL * 32);          // [units][NPR], already times -8
+    unsigned char* ring = smem_raw + (((size_t)units * (NCOL * 32 + NPR * 4) + 127) & ~(size_t)127) + (size_t)warp * MMA_NSTAGE * STAGE_BYTES;
+    const int nch = (np + CH - 1) / CH;                     // chunks per row group for this warp
     const int n_chunks = my_sets * nch;
     if (lane == 0) {
 #pragma unroll
-        for (int st = 0; st < NSTAGE; ++st) mbar_init(&s_bar[warp][st], 1);
+        for (int st = 0; st < MMA_NSTAGE; ++st) mbar_init(&s_bar[warp][st], 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
-    // issue cursor (lane 0): chunk `i_c` is chunk `i_j` of this warp's `i_set`-th row group
-    int i_c = 0, i_j = 0, i_rg = (int)blockIdx.x * RG + rg_l;
+    // issue cursor (lane 0): the next chunk to request is chunk `i_j` of row group `i_rg`, into stage `i_st`
+    int i_c = 0, i_j = 0, i_st = 0, i_rg = (int)blockIdx.x * RG + rg_l;
     auto issue_next = [&]() {                                // lane 0 only
         const int rg = min(i_rg, n_rg - 1);                 // clamped: rows past the end are dropped later
-        const int pp0 = p0 + i_j * MMA_CH, n = min(MMA_CH, p1 - pp0);
+        const int pp0 = p0 + i_j * CH, n = min(CH, p1 - pp0);
         const size_t off = ((size_t)rg * pairs + pp0) * MMA_TILE;
-        const int st = i_c & (NSTAGE - 1);
-        unsigned char* dst = ring + (size_t)st * STAGE_BYTES;
-        mbar_expect_tx(&s_bar[warp][st], (uint32_t)(n * MMA_TILE * (PAIR ? 2 : 1)));
-        bulk_g2s(dst, t0 + off, (uint32_t)(n * MMA_TILE), &s_bar[warp][st]);
-        if (PAIR) bulk_g2s(dst + MMA_CH * MMA_TILE, t1 + off, (uint32_t)(n * MMA_TILE), &s_bar[warp][st]);
+        unsigned char* dst = ring + (size_t)i_st * STAGE_BYTES;
+        mbar_expect_tx(&s_bar[warp][i_st], (uint32_t)(n * MMA_TILE * NM));
+        bulk_g2s(dst, t0 + off, (uint32_t)(n * MMA_TILE), &s_bar[warp][i_st]);
+        if (PAIR) bulk_g2s(dst + CH * MMA_TILE, t1 + off, (uint32_t)(n * MMA_TILE), &s_bar[warp][i_st]);
         ++i_c;
+        if (++i_st == MMA_NSTAGE) i_st = 0;
         if (++i_j == nch) { i_j = 0; i_rg += (int)gridDim.x * RG; }
     };
     if (lane == 0) {
 #pragma unroll
-        for (int c = 0; c < NSTAGE; ++c) if (i_c < n_chunks) issue_next();
+        for (int c = 0; c < MMA_NSTAGE; ++c) if (i_c < n_chunks) issue_next();
     }
-
     // Norm weights of the input chain (read-only, like the matrix): fetched ahead of the wait.
     float4 vp[3], vw[3];
     {
@@ -211,7 +207,7 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
     // ---- stage activations as signed bytes (hi, mid | lo) in MMA operand order ----
     {
         const int n4 = a.K >> 2;
-        for (int b = 0; b < NB && b < a.B; ++b) {
+        for (int b = 0; b < NBR && b < a.B; ++b) {
             const size_t row = (size_t)b * a.ldx;
             if (a.h_in && n4 <= 3 * (int)blockDim.x) {
                 const float* hp = a.h_in + row;
@@ -267,7 +263,7 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
 #pragma unroll
                 for (int j = 0; j < 3; ++j) {
                     const int i = threadIdx.x + j * blockDim.x;
-                    if (i < n4) put_x4<NCOL>(xb1, xb2, 4 * i, b, make_float4(vh[j].x * s, vh[j].y * s, vh[j].z * s, vh[j].w * s));
+                    if (i < n4) put_x4<NCOL>(xb, 4 * i, b, make_float4(vh[j].x * s, vh[j].y * s, vh[j].z * s, vh[j].w * s));
                 }
             } else {
                 // plain activations: read once into registers when they fit (K <= 8192), scale, pack
@@ -288,7 +284,7 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int i = threadIdx.x + j * blockDim.x;
-                        if (i < n4) put_x4<NCOL>(xb1, xb2, 4 * i, b, make_float4(v[j].x * s, v[j].y * s, v[j].z * s, v[j].w * s));
+                        if (i < n4) put_x4<NCOL>(xb, 4 * i, b, make_float4(v[j].x * s, v[j].y * s, v[j].z * s, v[j].w * s));
                     }
                 } else {
 #pragma unroll 4
@@ -301,7 +297,7 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
 #pragma unroll 4
                     for (int i = threadIdx.x; i < n4; i += blockDim.x) {
                         const float4 v = src[i];
-                        put_x4<NCOL>(xb1, xb2, 4 * i, b, make_float4(v.x * s, v.y * s, v.z * s, v.w * s));
+                        put_x4<NCOL>(xb, 4 * i, b, make_float4(v.x * s, v.y * s, v.z * s, v.w * s));
                     }
                 }
                 if (threadIdx.x == 0) s_inv[b] = inv;
@@ -310,57 +306,76 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
         __syncthreads();
     }
 
-    // per-block sums of the integer activations (they remove the -8 of Q4_0 later)
-    for (int i = threadIdx.x; i < units * NB; i += blockDim.x) {
-        const int u = i / NB, b = i % NB;
-        int acc = 0;
-        if (b < a.B) {
-            const int* h = reinterpret_cast<const int*>(xb1 + (size_t)(u * NCOL + 2 * b) * 32);
-            const int* m = h + 8;
-            const int* l = reinterpret_cast<const int*>(xb2 + (size_t)(u * NCOL + 2 * b) * 32);
-            int sh = 0, sm2 = 0, sl = 0;
+    // per-block, per-column-pair sums of the integer activations, in the units of the
+    // lane that uses them (256 * first column + second column) and already times -8
+    for (int i = threadIdx.x; i < units * NPR; i += blockDim.x) {
+        const int u = i / NPR, pr = i % NPR;
+        float v = 0.f;
+        if ((pr >> 1) < a.B) {
+            const int* c0 = reinterpret_cast<const int*>(xb + (size_t)(u * NCOL + 2 * pr) * 32);
+            const int* c1 = c0 + 8;
+            int s0 = 0, s1 = 0;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { sh = __dp4a(h[e], 0x01010101, sh); sm2 = __dp4a(m[e], 0x01010101, sm2); sl = __dp4a(l[e], 0x01010101, sl); }
-            acc = sm2 * 256 + sl;
-            s_sx[i] = (float)sh * 65536.0f + (float)acc;
-        } else s_sx[i] = 0.f;
+            for (int e = 0; e < 8; ++e) { s0 = __dp4a(c0[e], 0x01010101, s0); s1 = __dp4a(c1[e], 0x01010101, s1); }
+            v = -8.0f * (float)(s0 * 256 + s1);
+        }
+        s_sx[i] = v;
     }
     __syncthreads();
-    float best_v = -3.402823466e+38f; int best_i = -1;        // for batch row t
-    float accA[2] = {0.f, 0.f}, accB[2] = {0.f, 0.f};
+    float best_v[NI]; int best_i[NI];                       // arg-max candidates of batch rows 2i + t/2
+    float acc[NM][NI][2];
+#pragma unroll
+    for (int i = 0; i < NI; ++i) { best_v[i] = -3.402823466e+38f; best_i[i] = -1; }
+#pragma unroll
+    for (int m = 0; m < NM; ++m)
+#pragma unroll
+        for (int i = 0; i < NI; ++i) acc[m][i][0] = acc[m][i][1] = 0.f;
     int parity = 0;
-    // Lanes g >= NCOL supply all-zero B columns: they read a zero block with stride 0.
-    __shared__ __align__(16) uint4 s_zero[4];
-    if (threadIdx.x < 4) s_zero[threadIdx.x] = make_uint4(0, 0, 0, 0);
-    __syncthreads();
-    // Lane (g, t) supplies B column g.  Only columns < NCOL are staged; the other lanes
-    // re-read a staged column: whatever lands in B columns >= 2*B only reaches output
-    // columns that are never read.
-    const uint2* xq1 = reinterpret_cast<const uint2*>(xb1) + (g % NCOL) * 4 + t;
-    const uint2* xq2 = reinterpret_cast<const uint2*>(xb2) + (g % NCOL) * 4 + t;
+    // Lane (g, t) supplies B column g of every MMA.  With one batch row only columns 0..3
+    // are staged and lanes g >= 4 re-read them: what lands in B columns >= 4 only reaches
+    // output columns that are never read.
+    const uint2* xq = reinterpret_cast<const uint2*>(xb) + (g % (NCOL < 8 ? NCOL : 8)) * 4 + t;
     constexpr int xstep = NCOL * 4;                            // uint2 per block
-    const float* sxp = s_sx + (t < NB ? t : 0);
+    const float* sxp = s_sx + (t % (NPR < 4 ? NPR : 4));
+    const float cm = (t & 1) ? (1.0f / 256.0f) : 256.0f;      // even lanes hold (hi, mid), odd lanes (lo, 0)
 
-    // One 16x32 block of one matrix: raw nibbles against (hi, mid) and against (lo, 0).
-    auto block_imma = [&](uint32_t wg, uint32_t wh, const uint2& b1, const uint2& b2, uint32_t sc2, float sx, float& acc0, float& acc1) {
+    // One 16x32 block of one matrix against the staged columns.
+    auto block_imma = [&](uint32_t wg, uint32_t wh, const uint2* xu, const float* sxu, uint32_t sc2, float (&ac)[NI][2]) {
         const uint32_t a0 = wg & 0x0F0F0F0Fu, a2 = (wg >> 4) & 0x0F0F0F0Fu;
         const uint32_t a1 = wh & 0x0F0F0F0Fu, a3 = (wh >> 4) & 0x0F0F0F0Fu;
-        int d1[4], d2[4];
-        imma16832(d1, a0, a1, a2, a3, b1.x, b1.y);
-        imma16832(d2, a0, a1, a2, a3, b2.x, b2.y);
         const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&sc2));
-        const float s0 = fmaf((float)d1[0], 65536.0f, (float)(d1[1] * 256 + d2[0]));
-        const float s1 = fmaf((float)d1[2], 65536.0f, (float)(d1[3] * 256 + d2[2]));
-        acc0 = fmaf(d.x, fmaf(-8.0f, sx, s0), acc0);
-        acc1 = fmaf(d.y, fmaf(-8.0f, sx, s1), acc1);
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const uint2 b = xu[i * 32];
+            int dd[4];
+            imma16832(dd, a0, a1, a2, a3, b.x, b.y);
+            const float sx = sxu[i * 4];
+            ac[i][0] = fmaf(d.x, (float)(dd[0] * 256 + dd[1]) + sx, ac[i][0]);
+            ac[i][1] = fmaf(d.y, (float)(dd[2] * 256 + dd[3]) + sx, ac[i][1]);
+        }
+    };
+    // Tile pair k of the current stage (both 32-weight blocks, both matrices).
+    auto do_pair = [&](const unsigned char* buf, int k, const uint2* xp, const float* sx) {
+        const uint4 q = reinterpret_cast<const uint4*>(buf + k * MMA_TILE)[lane];
+        const uint2 sc = reinterpret_cast<const uint2*>(buf + k * MMA_TILE + 512)[g];
+        const uint2* xu0 = xp + (2 * k) * xstep;
+        const float* sx0 = sx + (2 * k) * NPR;
+        block_imma(q.x, q.y, xu0, sx0, sc.x, acc[0]);
+        block_imma(q.z, q.w, xu0 + xstep, sx0 + NPR, sc.y, acc[0]);
+        if (PAIR) {
+            const uint4 q1 = reinterpret_cast<const uint4*>(buf + (CH + k) * MMA_TILE)[lane];
+            const uint2 sc1 = reinterpret_cast<const uint2*>(buf + (CH + k) * MMA_TILE + 512)[g];
+            block_imma(q1.x, q1.y, xu0, sx0, sc1.x, acc[NM - 1]);
+            block_imma(q1.z, q1.w, xu0 + xstep, sx0 + NPR, sc1.y, acc[NM - 1]);
+        }
     };
 
     bool timed_out = false;
-    int j = 0, c_rg = (int)blockIdx.x * RG + rg_l;
+    int j = 0, st = 0, c_rg = (int)blockIdx.x * RG + rg_l;
+    uint32_t ph = 0;
     for (int c = 0; c < n_chunks; ++c) {
-        const int st = c & (NSTAGE - 1);
         if (!timed_out) {
-            const bool ok = mbar_wait(&s_bar[warp][st], (uint32_t)((c / NSTAGE) & 1));
+            const bool ok = mbar_wait(&s_bar[warp][st], ph);
             if (!__all_sync(0xffffffffu, ok)) {
                 // A copy never completed.  Record it and stop touching the ring; the warp keeps
                 // walking its chunks so that it still meets its peers at every CTA barrier.
@@ -370,89 +385,106 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
         }
         if (!timed_out) {
             const unsigned char* buf = ring + (size_t)st * STAGE_BYTES;
-            const int pp0 = p0 + j * MMA_CH, n = min(MMA_CH, p1 - pp0);
-            const uint2* xp1 = xq1 + (size_t)pp0 * 2 * xstep;
-            const uint2* xp2 = xq2 + (size_t)pp0 * 2 * xstep;
-            const float* sx = sxp + (size_t)pp0 * 2 * NB;
+            const int pp0 = p0 + j * CH, n = p1 - pp0;
+            const uint2* xp = xq + (size_t)pp0 * 2 * xstep;
+            const float* sx = sxp + (size_t)pp0 * 2 * NPR;
+            if (n >= CH) {
 #pragma unroll
-            for (int k = 0; k < MMA_CH; ++k) {
-                if (k < n) {
-                    const uint4 q = reinterpret_cast<const uint4*>(buf + k * MMA_TILE)[lane];
-                    const uint2 sc = reinterpret_cast<const uint2*>(buf + k * MMA_TILE + 512)[g];
-                    const uint2 b10 = xp1[(2 * k) * xstep], b11 = xp1[(2 * k + 1) * xstep];
-                    const uint2 b20 = xp2[(2 * k) * xstep], b21 = xp2[(2 * k + 1) * xstep];
-                    const float sx0 = sx[(2 * k) * NB], sx1 = sx[(2 * k + 1) * NB];
-                    block_imma(q.x, q.y, b10, b20, sc.x, sx0, accA[0], accA[1]);
-                    block_imma(q.z, q.w, b11, b21, sc.y, sx1, accA[0], accA[1]);
-                    if (PAIR) {
-                        const uint4 q1 = reinterpret_cast<const uint4*>(buf + (MMA_CH + k) * MMA_TILE)[lane];
-                        const uint2 sc1 = reinterpret_cast<const uint2*>(buf + (MMA_CH + k) * MMA_TILE + 512)[g];
-                        block_imma(q1.x, q1.y, b10, b20, sc1.x, sx0, accB[0], accB[1]);
-                        block_imma(q1.z, q1.w, b11, b21, sc1.y, sx1, accB[0], accB[1]);
-                    }
-                }
+                for (int k = 0; k < CH; ++k) do_pair(buf, k, xp, sx);
+            } else {
+                for (int k = 0; k < n; ++k) do_pair(buf, k, xp, sx);
             }
             __syncwarp();                                   // every lane is done with this stage
             if (lane == 0 && i_c < n_chunks) issue_next();
         }
+        if (++st == MMA_NSTAGE) { st = 0; ph ^= 1u; }
         if (++j == nch) {
             // ---- end of this warp's K slice for the row group ----
             const int rg = c_rg;
             j = 0;
             c_rg += (int)gridDim.x * RG;
-            float vA[2] = {accA[0], accA[1]}, vB[2] = {accB[0], accB[1]};
+            // even lanes: 256 * acc + (odd neighbour's acc) / 256  ->  batch row 2i + t/2
+            float val[NM][NI][2];
+#pragma unroll
+            for (int m = 0; m < NM; ++m)
+#pragma unroll
+                for (int i = 0; i < NI; ++i)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const float v = acc[m][i][h] * cm;
+                        val[m][i][h] = v + __shfl_xor_sync(0xffffffffu, v, 1);
+                        acc[m][i][h] = 0.f;
+                    }
             bool writer = true;
             if (KS > 1) {       // combine the KS slices through shared memory
-                float* mine = &s_red[parity][warp][0][0][0];
-                mine[g * 4 + t] = accA[0]; mine[(g + 8) * 4 + t] = accA[1];
-                if (PAIR) { mine[64 + g * 4 + t] = accB[0]; mine[64 + (g + 8) * 4 + t] = accB[1]; }
+                if (!(t & 1)) {
+#pragma unroll
+                    for (int m = 0; m < NM; ++m)
+#pragma unroll
+                        for (int i = 0; i < NI; ++i) {
+                            s_red[parity][warp][m][i][g][t >> 1] = val[m][i][0];
+                            s_red[parity][warp][m][i][g + 8][t >> 1] = val[m][i][1];
+                        }
+                }
                 __syncthreads();
                 writer = (ks == 0);
-                if (writer) {
+                if (writer && !(t & 1)) {
                     for (int k2 = 1; k2 < KS; ++k2) {
-                        const float* o = &s_red[parity][warp + k2][0][0][0];
-                        vA[0] += o[g * 4 + t]; vA[1] += o[(g + 8) * 4 + t];
-                        if (PAIR) { vB[0] += o[64 + g * 4 + t]; vB[1] += o[64 + (g + 8) * 4 + t]; }
+#pragma unroll
+                        for (int m = 0; m < NM; ++m)
+#pragma unroll
+                            for (int i = 0; i < NI; ++i) {
+                                val[m][i][0] += s_red[parity][warp + k2][m][i][g][t >> 1];
+                                val[m][i][1] += s_red[parity][warp + k2][m][i][g + 8][t >> 1];
+                            }
                     }
                 }
                 parity ^= 1;
             }
-            if (writer && rg < n_rg && t < a.B) {
-                const float inv = s_inv[t];
+            if (writer && rg < n_rg && !(t & 1)) {
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int row = rg * 16 + g + 8 * h;
-                    const float va = vA[h] * inv;
-                    if (a.epi == EPI_STORE) a.y[(size_t)t * a.ldy + row] = va;
-                    else if (a.epi == EPI_GEGLU) a.y[(size_t)t * a.ldy + row] = gelu_tanh(va) * (vB[h] * inv);
-                    else if (a.epi == EPI_SWIGLU) a.y[(size_t)t * a.ldy + row] = silu_clip(va) * (vB[h] * inv);
-                    else {
-                        float v = va;
-                        if (a.y) a.y[(size_t)t * a.ldy + row] = a.softcap > 0.f ? tanhf(v / a.softcap) * a.softcap : v;
-                        if (!(v == v)) v = -3.402823466e+38f;
-                        if (better(v, row, best_v, best_i)) { best_v = v; best_i = row; }
+                for (int i = 0; i < NI; ++i) {
+                    const int bt = 2 * i + (t >> 1);
+                    if (bt < a.B) {
+                        const float inv = s_inv[bt];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int row = rg * 16 + g + 8 * h;
+                            const float va = val[0][i][h] * inv;
+                            if (a.epi == EPI_STORE) a.y[(size_t)bt * a.ldy + row] = va;
+                            else if (a.epi == EPI_GEGLU) a.y[(size_t)bt * a.ldy + row] = gelu_tanh(va) * (val[NM - 1][i][h] * inv);
+                            else if (a.epi == EPI_SWIGLU) a.y[(size_t)bt * a.ldy + row] = silu_clip(va) * (val[NM - 1][i][h] * inv);
+                            else {
+                                float v = va;
+                                if (a.y) a.y[(size_t)bt * a.ldy + row] = a.softcap > 0.f ? tanhf(v / a.softcap) * a.softcap : v;
+                                if (!(v == v)) v = -3.402823466e+38f;
+                                if (better(v, row, best_v[i], best_i[i])) { best_v[i] = v; best_i[i] = row; }
+                            }
+                        }
                     }
                 }
             }
-            accA[0] = accA[1] = accB[0] = accB[1] = 0.f;
         }
     }
     if (timed_out) {
         // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
-        for (int st = 0; st < NSTAGE; ++st) { mbar_wait(&s_bar[warp][st], 0u); mbar_wait(&s_bar[warp][st], 1u); }
+        for (int s2 = 0; s2 < MMA_NSTAGE; ++s2) { mbar_wait(&s_bar[warp][s2], 0u); mbar_wait(&s_bar[warp][s2], 1u); }
     }
 
     if (a.epi != EPI_ARGMAX) return;
     // lanes that share a batch row (same t) -> lane g == 0; then across warps; then across CTAs
 #pragma unroll
-    for (int o = 4; o < 32; o <<= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-        if (better(ov, oi, best_v, best_i)) { best_v = ov; best_i = oi; }
+    for (int i = 0; i < NI; ++i) {
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best_v[i], o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i[i], o);
+            if (better(ov, oi, best_v[i], best_i[i])) { best_v[i] = ov; best_i[i] = oi; }
+        }
+        if (g == 0 && !(t & 1)) { s_bv[warp * 4 + 2 * i + (t >> 1)] = best_v[i]; s_bi[warp * 4 + 2 * i + (t >> 1)] = best_i[i]; }
     }
-    if (g == 0) { s_bv[warp * 4 + t] = best_v; s_bi[warp * 4 + t] = best_i; }
     __syncthreads();
-    if ((int)threadIdx.x < a.B && threadIdx.x < 4) {
+    if ((int)threadIdx.x < a.B && threadIdx.x < 4 && threadIdx.x < NBR) {
         const int b = threadIdx.x;
         float bv = s_bv[b]; int bi = s_bi[b];
         for (int w = 1; w < n_warps; ++w) if (better(s_bv[w * 4 + b], s_bi[w * 4 + b], bv, bi)) { bv = s_bv[w * 4 + b]; bi = s_bi[w * 4 + b]; }
@@ -465,7 +497,7 @@ __global__ void __launch_bounds__(256, 2) k_gemv_mma(const GemvArgs a, const uin
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    for (int b = 0; b < a.B && b < 4; ++b) {
+    for (int b = 0; b < a.B && b < NBR; ++b) {
         float bv = -3.402823466e+38f; int bi = -1;
         for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) {
             const float v = __ldcg(a.part_val + (size_t)b * gridDim.x + i);
