@@ -19,7 +19,7 @@ bool gemv_mma_supports(const GemvArgs& a) {
     return x_bytes(a.K / 32, 4) + ring_bytes(8) <= (size_t)MMA_SMEM_LIMIT;
 }
 
-struct MmaInfo { bool attr; size_t occ_smem; int occ_threads; int per_sm; };
+struct MmaInfo { bool attr; size_t occ_smem[3]; int per_sm[3]; };   // per warp count 8, 12, 16
 static MmaInfo g_mma_info[3][2];
 
 int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream_t stream) {
@@ -41,10 +41,6 @@ int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream
         if (a.out_tok) g1.out_tok = a.out_tok + b0;
         if (a.out_tok_f32) g1.out_tok_f32 = a.out_tok_f32 + b0;
         const int ncol = g1.B == 1 ? 4 : (g1.B == 2 ? 8 : 16);
-        // 16 warps per CTA when there are too few row groups to give every SM a CTA
-        int n_warps = 8;
-        if (n_rg < g.sm_count && pairs >= 32 && x_bytes(units, ncol) + ring_bytes(16) <= (size_t)MMA_SMEM_LIMIT) n_warps = 16;
-        const size_t smem = x_bytes(units, ncol) + ring_bytes(n_warps);
         g1.err = g.dev_err;
         const int vi = ncol == 4 ? 0 : (ncol == 8 ? 1 : 2);
         MmaKernel k = vi == 0 ? (pair ? k_gemv_mma<4, true> : k_gemv_mma<4, false>)
@@ -56,23 +52,42 @@ int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream
                 return fail(ADAMAH_ERR_BACKEND, "gemv_mma: cannot raise the shared-memory limit");
             ki.attr = true;
         }
-        if (ki.occ_smem != smem || ki.occ_threads != n_warps * 32) {
-            int per_sm = 0;
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, n_warps * 32, smem);
-            ki.per_sm = per_sm < 1 ? 1 : per_sm; ki.occ_smem = smem; ki.occ_threads = n_warps * 32;
+        // Shape of the launch: warps per CTA (8, 12 or 16) and K slices per row group (a
+        // divisor of the warp count).  The estimate is the time of the busiest SM: tile pairs
+        // per warp (plus a fixed cost per finished row group) times the larger of a lone
+        // warp's latency per pair and the SM's issue time for all resident warps; ties go to
+        // the smaller CTA and the smaller split.
+        int n_warps = 8, KS = 1, best_per_sm = 1;
+        double best_cost = 1e300;
+        const int nm = pair ? 2 : 1;
+        for (int nw = 8; nw <= 16; nw += 4) {
+            const size_t sm_bytes = x_bytes(units, ncol) + ring_bytes(nw);
+            if (sm_bytes > (size_t)MMA_SMEM_LIMIT) break;
+            int per_sm = ki.per_sm[nw / 4 - 2];
+            if (ki.occ_smem[nw / 4 - 2] != sm_bytes) {
+                per_sm = 0;
+                cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, nw * 32, sm_bytes);
+                if (per_sm < 1) per_sm = 1;
+                ki.per_sm[nw / 4 - 2] = per_sm; ki.occ_smem[nw / 4 - 2] = sm_bytes;
+            }
+            for (int c = 1; c <= nw; ++c) {
+                if (nw % c || c > pairs) continue;
+                const int rgs = nw / c;                              // row groups per CTA pass
+                const long long n_sets = (n_rg + rgs - 1) / rgs;
+                long long ctas = (long long)g.sm_count * per_sm;
+                if (ctas > n_sets) ctas = n_sets;
+                const long long passes = (n_sets + ctas - 1) / ctas;            // per CTA
+                const long long resident = (ctas + g.sm_count - 1) / g.sm_count; // CTAs on the busiest SM
+                const int slice = (pairs + c - 1) / c;
+                // a warp alone needs ~300 cycles per tile pair; an SM issues one per ~16 cycles
+                const double busy = (double)resident * nw * 16.0;
+                const double cost = (double)passes * (slice * nm + 3.0 + 0.25 * c) * (busy > 300.0 ? busy : 300.0);
+                if (cost < best_cost * 0.999) { best_cost = cost; n_warps = nw; KS = c; best_per_sm = per_sm; }
+            }
         }
-        // K slices per row group: the fewest that still give every SM two CTAs; small
-        // problems take the most parallel split.
-        int KS = n_warps;
-        for (int c = 1; c <= n_warps; c <<= 1) {
-            if (c > pairs) break;
-            const int n_sets = (n_rg + n_warps / c - 1) / (n_warps / c);
-            if (n_sets >= 2 * g.sm_count) { KS = c; break; }
-        }
-        while (KS > pairs) KS >>= 1;
-        if (KS < 1) KS = 1;
+        const size_t smem = x_bytes(units, ncol) + ring_bytes(n_warps);
         const int n_sets = (n_rg + n_warps / KS - 1) / (n_warps / KS);
-        int grid = g.sm_count * ki.per_sm;
+        int grid = g.sm_count * best_per_sm;
         if (grid > n_sets) grid = n_sets;
         if (a.epi == EPI_ARGMAX && grid > gemv_max_grid()) grid = gemv_max_grid();
         if (a.max_grid > 0 && grid > a.max_grid) grid = a.max_grid;
