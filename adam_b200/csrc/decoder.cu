@@ -57,7 +57,7 @@ struct Decoder {
 };
 
 constexpr uint32_t MAX_DECODERS = 8;
-constexpr uint32_t ATTN_SPLIT = 64;        // fewest tokens an attention CTA takes before another CTA is added
+constexpr uint32_t ATTN_SPLIT = 256;       // fewest tokens an attention CTA takes before another CTA is added
 constexpr uint32_t ATTN_MAX_SPLITS = 64;   // attention CTAs per (sequence, kv head)
 static Decoder* g_dec[MAX_DECODERS];
 
@@ -186,6 +186,7 @@ __device__ __forceinline__ size_t kv_index(const KvGeom& g, uint32_t page_id, ui
 // (max, sum, o) are merged across warps in shared memory, then across CTAs by the
 // CTA that finishes last.
 constexpr int ATTN_CP = 8;
+constexpr uint32_t ATTN_CHUNKS_PER_CTA = 32;   // chunks a CTA takes (4 per warp) before another CTA joins
 
 template <typename T, int DPL> struct KvRow {
     static constexpr int BYTES = DPL * (int)sizeof(T);
@@ -245,7 +246,7 @@ template <> __device__ __forceinline__ float kv_round<__half>(float v) { return 
 template <> __device__ __forceinline__ float kv_round<float>(float v) { return v; }
 
 // Sum a[0..NV) over the 32 lanes.  NV >= 32: lane l ends with the totals of values
-// l*NV/32 .. in a[0..NV/32).  NV == 16: lanes 2v and 2v+1 end with value v in a[0].
+// l*NV/32 .. in a[0..NV/32).  NV < 32: the 32/NV lanes v*32/NV .. end with value v in a[0].
 template <int NV>
 __device__ __forceinline__ void warp_reduce_scatter(float (&a)[NV], uint32_t lane) {
     int n = NV;
@@ -277,19 +278,24 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
                                                    const int32_t* __restrict__ block_table, const int32_t* __restrict__ pos,
                                                    uint32_t n_head, uint32_t layer, uint32_t window, float scale, float cap,
                                                    float* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-                                                   unsigned int* __restrict__ ticket, uint32_t n_splits_max, uint32_t* err) {
+                                                   unsigned int* __restrict__ ticket, uint32_t n_splits_max, uint32_t hpc, uint32_t* err) {
     T* __restrict__ kv_pool = reinterpret_cast<T*>(kv_pool_v);
     constexpr int DPL = HD / 32;                // dims per lane
     constexpr int CP = ATTN_CP;                 // positions per chunk
     constexpr int NV = CP * GS_MAX;             // scores per chunk
     constexpr int VPL = NV >= 32 ? NV / 32 : 1; // scores a lane holds after the reduce-scatter
+    constexpr int LPV = NV >= 32 ? 1 : 32 / NV; // lanes that hold the same score
     constexpr float NEG = -1.0e30f;
-    static_assert(DPL >= 1 && (GS_MAX == 2 || GS_MAX == 4 || GS_MAX == 8), "unsupported attention shape");
+    static_assert(DPL >= 1 && (GS_MAX == 1 || GS_MAX == 2 || GS_MAX == 4 || GS_MAX == 8), "unsupported attention shape");
     extern __shared__ __align__(16) float sm[];
     __shared__ float s_m[8][GS_MAX], s_l[8][GS_MAX];
     __shared__ float s_w[8][GS_MAX], s_M[GS_MAX];
     __shared__ bool s_last;
-    const uint32_t split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    // blockIdx.y = (kv head, group of `hpc` query heads that share it)
+    const uint32_t hgn = (n_head / geo.n_kv) / hpc;
+    const uint32_t split = blockIdx.x, kvh = blockIdx.y / hgn, hg = blockIdx.y % hgn, b = blockIdx.z;
+    const uint32_t head0 = kvh * (n_head / geo.n_kv) + hg * hpc;
+    const uint32_t slot_y = b * gridDim.y + blockIdx.y;        // scratch slot of this (sequence, head group)
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // The block table is written by the host before the step's first kernel, so it can be
     // read ahead of the dependency wait: up to 128 entries sit in registers across the warp.
@@ -317,14 +323,15 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         wq0[j] = (in && q_norm) ? q_norm[i] : 1.f; wq1[j] = (in && q_norm) ? q_norm[i + HD / 2] : 1.f;
         wk0[j] = (in && k_norm) ? k_norm[i] : 1.f; wk1[j] = (in && k_norm) ? k_norm[i + HD / 2] : 1.f;
     }
-    pdl_launch_dependents();
-    pdl_wait();             // positions, q/k/v rows and the cache all come from earlier kernels
-    const uint32_t hd = HD, half = HD / 2, gs = n_head / geo.n_kv;
+    // Positions only change in the step's last kernel, and the step's first kernel is
+    // launched with a full dependency on it, so the position, and everything in the cache
+    // older than this step, can be read ahead of the wait as well.
+    const uint32_t hd = HD, half = HD / 2, gs = hpc;
     const int32_t p = pos[b];
     const uint32_t seq = (uint32_t)p + 1;
     const uint32_t start = (window > 0 && seq > window) ? seq - window : 0;
     const uint32_t c_first = start / CP, n_chunks = (seq - 1) / CP - c_first + 1;
-    const uint32_t n_act = min((uint32_t)gridDim.x, (n_chunks + 7) / 8);
+    const uint32_t n_act = min((uint32_t)gridDim.x, (n_chunks + ATTN_CHUNKS_PER_CTA - 1) / ATTN_CHUNKS_PER_CTA);
     if (split >= n_act) return;
     const uint32_t cpc = (n_chunks + n_act - 1) / n_act;
     const uint32_t c0 = min(c_first + split * cpc, c_first + n_chunks), c1 = min(c_first + n_chunks, c0 + cpc);
@@ -372,7 +379,16 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     if ((uint32_t)p >= n_pos && tid == 0) atomicOr(err, DEVERR_OOB_MAP);
     const float* ct = cos_t + (size_t)pp * half;
     const float* st = sin_t + (size_t)pp * half;
-    const float* row_q = qkv + (size_t)b * qkv_ld + (size_t)kvh * gs * hd;
+    float cs[NP], sn[NP];
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+        const uint32_t i = lane + 32 * j;
+        cs[j] = i < half ? ct[i] : 1.f;
+        sn[j] = i < half ? st[i] : 0.f;
+    }
+    pdl_launch_dependents();
+    pdl_wait();             // this step's q/k/v rows come from the previous kernel
+    const float* row_q = qkv + (size_t)b * qkv_ld + (size_t)head0 * hd;
     const float* row_k = qkv + (size_t)b * qkv_ld + (size_t)n_head * hd + (size_t)kvh * hd;
     const float* row_v = row_k + (size_t)geo.n_kv * hd;
     const uint32_t n_rows = gs + (owner ? 2u : 0u);
@@ -385,7 +401,8 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             const uint32_t page_no = (uint32_t)p / geo.page;
             const int32_t page_id = page_of(page_no);
             if (page_id < 0) { ok = false; if (lane == 0) atomicOr(err, DEVERR_OOB_MAP); }
-            else kv_off = kv_index(geo, (uint32_t)page_id, layer, is_k ? 0u : 1u, kvh, (uint32_t)p % geo.page);
+            else if (hg != 0) ok = false;               // one head group appends to the cache; the others only need the rows
+            if (ok) kv_off = kv_index(geo, (uint32_t)page_id, layer, is_k ? 0u : 1u, kvh, (uint32_t)p % geo.page);
         }
         if (!is_q && !is_k) {
             for (uint32_t i = lane; i < hd; i += 32) {
@@ -396,7 +413,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             continue;
         }
         const float* w = is_q ? q_norm : k_norm;
-        float x0[NP], x1[NP], w0[NP], w1[NP], cs[NP], sn[NP];
+        float x0[NP], x1[NP], w0[NP], w1[NP];
 #pragma unroll
         for (int j = 0; j < NP; ++j) {
             const uint32_t i = lane + 32 * j;
@@ -405,8 +422,6 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             x1[j] = in ? src[i + half] : 0.f;
             w0[j] = is_q ? wq0[j] : wk0[j];
             w1[j] = is_q ? wq1[j] : wk1[j];
-            cs[j] = in ? ct[i] : 1.f;
-            sn[j] = in ? st[i] : 0.f;
         }
         float rms = 1.f;
         if (w) {
@@ -477,7 +492,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         float pz[VPL], alpha[VPL];
 #pragma unroll
         for (int r = 0; r < VPL; ++r) {
-            const uint32_t v = NV >= 32 ? lane * VPL + r : lane >> 1;
+            const uint32_t v = NV >= 32 ? lane * VPL + r : lane / LPV;
             const uint32_t j = v / GS_MAX, g = v % GS_MAX;
             const uint32_t tp = c * CP + j;
             const bool valid = tp >= start && tp < seq && g < gs;
@@ -501,8 +516,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
 #pragma unroll
         for (int g = 0; g < GS_MAX; ++g) {
             // lane and slot that hold (position 0, head g)
-            constexpr int SH = NV >= 32 ? 1 : 2;
-            const float al = __shfl_sync(0xffffffffu, alpha[g % VPL], NV >= 32 ? g / VPL : g * SH);
+            const float al = __shfl_sync(0xffffffffu, alpha[g % VPL], NV >= 32 ? g / VPL : g * LPV);
 #pragma unroll
             for (int d = 0; d < DPL; ++d) o[g][d] *= al;
         }
@@ -513,7 +527,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
 #pragma unroll
             for (int g = 0; g < GS_MAX; ++g) {
                 const int v = j * GS_MAX + g;
-                const float pv = __shfl_sync(0xffffffffu, pz[v % VPL], NV >= 32 ? v / VPL : v * 2);
+                const float pv = __shfl_sync(0xffffffffu, pz[v % VPL], NV >= 32 ? v / VPL : v * LPV);
                 if constexpr (DPL >= 2) {
 #pragma unroll
                     for (int d = 0; d < DPL; d += 2) fma2(o[g][d], o[g][d + 1], pv, pv, vf[d], vf[d + 1]);
@@ -542,8 +556,8 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     }
 #pragma unroll
     for (int r = 0; r < VPL; ++r) {
-        const uint32_t v = NV >= 32 ? lane * VPL + r : lane >> 1;
-        if (v < GS_MAX && (NV >= 32 || (lane & 1) == 0)) { s_m[warp][v] = m_run[r]; s_l[warp][v] = l_run[r]; }
+        const uint32_t v = NV >= 32 ? lane * VPL + r : lane / LPV;
+        if (v < GS_MAX && (NV >= 32 || (lane % LPV) == 0)) { s_m[warp][v] = m_run[r]; s_l[warp][v] = l_run[r]; }
     }
     __syncthreads();
     if (tid < 8 * GS_MAX) {                     // weight of warp w for head g
@@ -557,9 +571,9 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     __syncthreads();
     // thread -> 4 consecutive outputs (all of one head)
     const uint32_t n_out4 = gs * hd / 4;
-    float* po = part_o + (((size_t)b * geo.n_kv + kvh) * n_splits_max + split) * gs * hd;
-    float* pml = part_ml + (((size_t)b * geo.n_kv + kvh) * n_splits_max + split) * gs * 2;
-    float* orow = out + ((size_t)b * n_head + (size_t)kvh * gs) * hd;
+    float* po = part_o + ((size_t)slot_y * n_splits_max + split) * gs * hd;
+    float* pml = part_ml + ((size_t)slot_y * n_splits_max + split) * gs * 2;
+    float* orow = out + ((size_t)b * n_head + head0) * hd;
     for (uint32_t i4 = tid; i4 < n_out4; i4 += blockDim.x) {
         const uint32_t g = (i4 * 4) / hd;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -580,15 +594,15 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     if (n_act == 1) return;
     __threadfence();
     __syncthreads();
-    unsigned int* tkt = ticket + (size_t)b * geo.n_kv + kvh;
+    unsigned int* tkt = ticket + slot_y;
     if (tid == 0) s_last = (atomicAdd(tkt, 1u) == n_act - 1);
     __syncthreads();
     if (!s_last) return;
     __threadfence();
     // ---- merge the splits (last CTA to arrive): all loads of a batch of 4 splits are
     // issued together, then folded in with a running maximum ----
-    const float* po0 = part_o + (((size_t)b * geo.n_kv + kvh) * n_splits_max) * gs * hd;
-    const float* pml0 = part_ml + (((size_t)b * geo.n_kv + kvh) * n_splits_max) * gs * 2;
+    const float* po0 = part_o + ((size_t)slot_y * n_splits_max) * gs * hd;
+    const float* pml0 = part_ml + ((size_t)slot_y * n_splits_max) * gs * 2;
     for (uint32_t i4 = tid; i4 < n_out4; i4 += blockDim.x) {
         const uint32_t g = (i4 * 4) / hd;
         float M = NEG, den = 0.f;
@@ -669,7 +683,7 @@ static size_t kv_elem_size(const adam_b200_decoder_desc& d) { return d.kv_dtype 
 
 typedef void (*AttnKernel)(const float*, uint32_t, const float*, const float*, float, const float*, const float*, uint32_t, void*, KvGeom,
                            const int32_t*, const int32_t*, uint32_t, uint32_t, uint32_t, float, float, float*, float*, float*,
-                           unsigned int*, uint32_t, uint32_t*);
+                           unsigned int*, uint32_t, uint32_t, uint32_t*);
 
 template <typename T, int GS>
 static AttnKernel pick_attn_hd(uint32_t hd) {
@@ -686,18 +700,22 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch) {
     const adam_b200_decoder_desc& d = D->d;
     KvGeom geo{d.n_layer, d.n_head_kv, d.head_dim, d.page_size, D->max_pages_per_seq, D->page_elems};
     const uint32_t gs = d.n_head / d.n_head_kv;
+    // Query heads per CTA: one while that still leaves SMs idle (lowest latency; the CTAs
+    // of a kv head re-read its rows from L2), the whole group once the grid is large.
+    const uint32_t hpc = (batch * d.n_head <= 2u * (uint32_t)g.sm_count) ? 1u : gs;
     const uint32_t window = ((d.flags & 1u) && d.sliding_window > 0 && !is_global_layer(d, L)) ? d.sliding_window : 0;
-    const size_t smem = ((size_t)gs * d.head_dim + 2 * (size_t)d.head_dim + (size_t)8 * gs * d.head_dim) * 4;
+    const size_t smem = ((size_t)hpc * d.head_dim + 2 * (size_t)d.head_dim + (size_t)8 * hpc * d.head_dim) * 4;
     const int which = is_global_layer(d, L) ? 1 : 0;
     const Layer& ly = D->layers[L];
     const uint32_t qkv_ld = (d.n_head + 2 * d.n_head_kv) * d.head_dim;
-    dim3 grid(D->n_splits, d.n_head_kv, batch);
-    AttnKernel kern = gs <= 2 ? pick_attn_hd<T, 2>(d.head_dim) : gs <= 4 ? pick_attn_hd<T, 4>(d.head_dim) : pick_attn_hd<T, 8>(d.head_dim);
+    dim3 grid(D->n_splits, d.n_head_kv * (gs / hpc), batch);
+    AttnKernel kern = hpc <= 1 ? pick_attn_hd<T, 1>(d.head_dim) : hpc <= 2 ? pick_attn_hd<T, 2>(d.head_dim)
+                    : hpc <= 4 ? pick_attn_hd<T, 4>(d.head_dim) : pick_attn_hd<T, 8>(d.head_dim);
     if (smem > 48 * 1024) DCU(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_k(kern, grid, dim3(256), smem, g.stream, g.pdl, D->qkv, qkv_ld, ly.norm[NORM_Q], ly.norm[NORM_K], d.norm_eps,
              D->rope_cos[which], D->rope_sin[which], D->rope_pos[which],
              D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
-             d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, g.dev_err);
+             d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, hpc, g.dev_err);
     count_launch();
     return ADAMAH_OK;
 }
@@ -730,10 +748,13 @@ static int enqueue_step_impl(Decoder* D, uint32_t batch, bool with_lm, bool want
     const uint32_t E = d.n_embd, q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim, qkv_ld = q_dim + 2 * k_dim;
     int rc;
     int cur = 0;
+    // The embedding kernel takes a full dependency on everything before it (no programmatic
+    // launch): later kernels of the step rely on the previous step's position update and
+    // cache writes being complete before any of them starts.
     if (D->embd.wtype == WT_Q4_0)
-        launch_k(k_embed<WT_Q4_0>, dim3(batch), dim3(256), 0, g.stream, g.pdl, D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
+        launch_k(k_embed<WT_Q4_0>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
     else
-        launch_k(k_embed<WT_Q4_K>, dim3(batch), dim3(256), 0, g.stream, g.pdl, D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
+        launch_k(k_embed<WT_Q4_K>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
     count_launch();
     for (uint32_t L = 0; L < d.n_layer; ++L) {
         const Layer& ly = D->layers[L];
@@ -834,7 +855,7 @@ extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint
     D->n_pages = d.n_pages ? d.n_pages : D->max_pages_per_seq * d.max_batch;
     D->d.n_pages = D->n_pages;
     D->page_elems = (size_t)d.n_layer * 2 * d.n_head_kv * d.page_size * d.head_dim;
-    D->n_splits = (d.kv_cap + ATTN_SPLIT - 1) / ATTN_SPLIT;
+    D->n_splits = (d.kv_cap + ATTN_SPLIT - 1) / ATTN_SPLIT;      // ATTN_SPLIT = ATTN_CP * ATTN_CHUNKS_PER_CTA
     if (D->n_splits > ATTN_MAX_SPLITS) D->n_splits = ATTN_MAX_SPLITS;
     const size_t B = d.max_batch, E = d.n_embd, q_dim = (size_t)d.n_head * d.head_dim, k_dim = (size_t)d.n_head_kv * d.head_dim;
     const uint32_t gs = d.n_head / d.n_head_kv;
@@ -850,9 +871,9 @@ extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint
     DALLOC(D->act, B * d.n_ff * 4); DALLOC(D->logits, B * (size_t)d.n_vocab * 4);
     DALLOC(D->part_o, B * d.n_head_kv * D->n_splits * gs * d.head_dim * 4);
     DALLOC(D->part_ml, B * d.n_head_kv * D->n_splits * gs * 2 * 4);
-    DALLOC(D->attn_ticket, B * d.n_head_kv * 4);
+    DALLOC(D->attn_ticket, B * d.n_head * 4);
 #undef DALLOC
-    cudaMemsetAsync(D->attn_ticket, 0, B * d.n_head_kv * 4, g.stream);
+    cudaMemsetAsync(D->attn_ticket, 0, B * d.n_head * 4, g.stream);
     cudaMemsetAsync(D->pos, 0, B * 4, g.stream);
     cudaMemsetAsync(D->cur_tok, 0, B * 4, g.stream);
     cudaMemsetAsync(D->prompt_len, 0, B * 4, g.stream);
