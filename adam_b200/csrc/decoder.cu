@@ -371,8 +371,14 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             }
         }
     };
+    // With one query head per CTA there are registers for a second chunk in flight, so a
+    // warp that owns up to two chunks waits for memory only once.
+    constexpr bool DB = (GS_MAX == 1) && (DPL * sizeof(T) <= 16);
+    constexpr uint32_t CSTEP = DB ? 16 : 8;     // chunk stride of one loop iteration
+    KvRow<T, DPL> kr2[DB ? CP : 1], vr2[DB ? CP : 1];
     uint32_t c = c0 + warp;
     if (c < c1) { load_rows(c, 0, kr); load_rows(c, 1, vr); }
+    if constexpr (DB) { if (c + 8 < c1) { load_rows(c + 8, 0, kr2); load_rows(c + 8, 1, vr2); } }
 
     // ---- a warp per row: query heads, and (owner only) the newest key and value rows ----
     const uint32_t pp = (uint32_t)p < n_pos ? (uint32_t)p : n_pos - 1;
@@ -460,7 +466,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         for (int d = 0; d < DPL; ++d) { q[g][d] = g < (int)gs ? s_q[g * hd + lane * DPL + d] : 0.f; o[g][d] = 0.f; }
 #pragma unroll
     for (int r = 0; r < VPL; ++r) { m_run[r] = NEG; l_run[r] = 0.f; }
-    for (; c < c1; c += 8) {
+    auto process = [&](uint32_t c, KvRow<T, DPL> (&kr)[CP], KvRow<T, DPL> (&vr)[CP]) {
         if (c == c_new) {
             // the newest position's rows come from this step's q/k/v, not from the cache
             KvRow<T, DPL> nk, nv;
@@ -486,7 +492,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
                 }
             }
         }
-        const uint32_t c_next = c + 8;
+        const uint32_t c_next = c + CSTEP;
         if (c_next < c1) load_rows(c_next, 0, kr);
         warp_reduce_scatter<NV>(sc, lane);
         float pz[VPL], alpha[VPL];
@@ -537,6 +543,10 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             }
         }
         if (c_next < c1) load_rows(c_next, 1, vr);
+    };
+    for (; c < c1; c += CSTEP) {
+        process(c, kr, vr);
+        if constexpr (DB) { if (c + 8 < c1) process(c + 8, kr2, vr2); }
     }
     // ---- merge the warps ----
     {
