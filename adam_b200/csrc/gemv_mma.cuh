@@ -392,7 +392,9 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a, const uin
 #pragma unroll
                 for (int k = 0; k < CH; ++k) do_pair(buf, k, xp, sx);
             } else {
-                for (int k = 0; k < n; ++k) do_pair(buf, k, xp, sx);
+                int k = 0;
+                for (; k + 1 < n; k += 2) { do_pair(buf, k, xp, sx); do_pair(buf, k + 1, xp, sx); }
+                if (k < n) do_pair(buf, k, xp, sx);
             }
             __syncwarp();                                   // every lane is done with this stage
             if (lane == 0 && i_c < n_chunks) issue_next();
