@@ -33,9 +33,10 @@ sys.path.insert(0, ROOT)
 
 PROMPT_LEN = 128
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one LM-head GEMV launch
-# (profiles/gemv_q4_0_lmhead_262144x1152.md)
-LMHEAD_DRAM_TRAFFIC = 169_933_568 + 5_597_440
+# dram__bytes_read.sum + dram__bytes_write.sum of one LM-head GEMV launch, from the ncu capture
+# summarised in profiles/gemv_mma_q4_0_lmhead_262144x1152.md (same kernel and shape; that capture's
+# entry point also stores the 1 MB of logits)
+LMHEAD_DRAM_TRAFFIC = 169_949_184 + 4_576_256
 
 
 def measured_peaks():
@@ -286,7 +287,7 @@ def main():
                     "d2h_bytes_per_step": st["d2h_bytes"] / max(1, st["n_gen"]), "ids_equal_device_run": same_ids},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
-                         "traffic": LMHEAD_DRAM_TRAFFIC, "kernel": "k_gemv<Q4_0> (LM head 262144x1152 + arg-max)",
+                         "traffic": LMHEAD_DRAM_TRAFFIC, "kernel": "k_gemv_mma<4,false> (LM head %dx%d Q4_0 + arg-max, tensor-core path)" % (N, K),
                          "bytes_per_launch": gemv_bytes, "us_per_launch": best / reps * 1e3, "peak_kind": peak_kind,
                          "frac_of_8TBs": gemv_gbs / 8000.0},
             "step_hbm": {"bytes_per_step": step_bytes, "achieved_GBs": step_bytes / (ms / steps * 1e-3) / 1e9,
