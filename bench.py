@@ -96,7 +96,8 @@ class ClockSampler:
 
 
 def dist_env():
-    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    from adam_b200.replicas import dist_env as _env
+    return _env()
 
 
 def cpu_decode_sample(cfg, tensors, n_prompt, n_decode, warmup):
@@ -181,7 +182,7 @@ def main():
         cores = threads_used()
         sample = f"full {cfg.n_layer}-layer model, 16-token prefill, {n_dec} decode tokens (of --steps {steps}); fp32 numpy on dequantized weights"
         print(json.dumps({"impl": "reference", "metric": "decode tok/s (Gemma-3-1B-shape Q4, b=1)", "value": tps, "unit": "tok/s",
-                          "n_gpus": 0, "steps": n_dec, "warmup": min(warmup, 3), "ms_per_step": 1000.0 / tps, "higher_is_better": True,
+                          "n_gpus": world, "steps": n_dec, "warmup": min(warmup, 3), "ms_per_step": 1000.0 / tps, "higher_is_better": True,
                           "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload,
                           "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
                           "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
@@ -265,10 +266,9 @@ def main():
     step_bytes = synth.model_weight_elems(cfg) * 18 // 32
 
     # ---- reduce over ranks -------------------------------------------------------------------
-    if world > 1:
-        tmax = torch.tensor([ms], device="cuda"); dist.all_reduce(tmax, op=dist.ReduceOp.MAX); ms = float(tmax.item())
-        emin = torch.tensor([e2e_tps], device="cuda"); dist.all_reduce(emin, op=dist.ReduceOp.MIN); e2e_tps = float(emin.item())
-    value = world * steps / (ms * 1e-3)
+    from adam_b200.replicas import combine_timings
+    comb = combine_timings(ms, steps, e2e_tps, world, device="cuda")     # a collective when world > 1
+    ms, value = comb["ms"], comb["value"]
 
     line = None
     if rank == 0:
@@ -283,7 +283,7 @@ def main():
             "metric": "decode tok/s (Gemma-3-1B-shape Q4, b=1)", "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": workload,
-            "e2e": {"value": e2e_tps * world, "unit": "tok/s", "h2d_bytes_per_step": st["h2d_bytes"] / max(1, st["n_gen"]),
+            "e2e": {"value": comb["e2e"], "unit": "tok/s", "h2d_bytes_per_step": st["h2d_bytes"] / max(1, st["n_gen"]),
                     "d2h_bytes_per_step": st["d2h_bytes"] / max(1, st["n_gen"]), "ids_equal_device_run": same_ids},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
