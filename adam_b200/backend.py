@@ -357,6 +357,11 @@ class Adamah:
         self._check(self._lib.adam_b200_capture_end(ctypes.byref(gid)), "adam_b200_capture_end")
         return int(gid.value)
 
+    def set_stream(self, cuda_stream: int = 0):
+        """Enqueue on a caller-owned CUDA stream (``torch.cuda.current_stream().cuda_stream``); 0 restores
+        the library's own stream.  Lets collectives issued by the caller order with the library's kernels."""
+        self._check(self._lib.adam_b200_set_stream(int(cuda_stream)), "adam_b200_set_stream")
+
     def graph_launch(self, graph_id: int, times: int = 1):
         self._check(self._lib.adam_b200_graph_launch(graph_id, times), "adam_b200_graph_launch")
 

@@ -50,7 +50,8 @@ struct Context {
     int          device;
     int          sm_count;
     size_t       total_mem;
-    cudaStream_t stream;
+    cudaStream_t stream;        // where everything is enqueued (own_stream unless the caller lent one)
+    cudaStream_t own_stream;
     Map          maps[MAX_MAPS];
     Handle*      handles;       // [MAX_HANDLES], index = handle id
     uint32_t     handle_cursor;

@@ -45,7 +45,7 @@ struct Decoder {
     const float* output_norm;
     float* rope_cos[2]; float* rope_sin[2]; uint32_t rope_pos[2];
     // device state
-    int32_t* pos;  int32_t* cur_tok;  int32_t* prompt_len;  int32_t* prompt_tok;  int32_t* gen_log;
+    int32_t* pos;  int32_t* cur_tok;  float* cur_val;  int32_t* prompt_len;  int32_t* prompt_tok;  int32_t* gen_log;
     int32_t* block_table; uint32_t max_pages_per_seq, n_pages;
     void* kv_pool; size_t page_elems;
     float *hbuf[2], *qkv, *attn_out, *proj, *act, *logits; int h_final;
@@ -674,7 +674,7 @@ static void free_graphs(Decoder* D) {
 static void destroy(Decoder* D) {
     cudaStreamSynchronize(g.stream);
     free_graphs(D);
-    void* ptrs[] = {D->pos, D->cur_tok, D->prompt_len, D->prompt_tok, D->gen_log, D->block_table, D->kv_pool, D->hbuf[0], D->hbuf[1], D->qkv,
+    void* ptrs[] = {D->pos, D->cur_tok, D->cur_val, D->prompt_len, D->prompt_tok, D->gen_log, D->block_table, D->kv_pool, D->hbuf[0], D->hbuf[1], D->qkv,
                     D->attn_out, D->proj, D->act, D->logits, D->part_o, D->part_ml, D->attn_ticket,
                     D->rope_cos[0], D->rope_sin[0], D->rope_cos[1], D->rope_sin[1]};
     for (void* p : ptrs) cudaFree(p);
@@ -753,21 +753,29 @@ static int enqueue_step(Decoder* D, uint32_t batch, bool with_lm, bool want_logi
     g.pdl = false;
     return rc;
 }
-static int enqueue_step_impl(Decoder* D, uint32_t batch, bool with_lm, bool want_logits) {
+// One part of a token step.  Parts 2L and 2L+1 are the attention half (embedding for L = 0,
+// QKV, attention, o-proj) and the FFN half (gate/up, down) of layer L; part 2*n_layer is the
+// LM head, part 2*n_layer + 1 advances the positions.  A tensor-parallel caller all-reduces
+// `proj` after every layer part and merges the arg-max pairs after the LM-head part.
+static uint32_t n_parts(const Decoder* D) { return 2 * D->d.n_layer + 2; }
+static int enqueue_part(Decoder* D, uint32_t batch, uint32_t part, bool with_lm, bool want_logits) {
     const adam_b200_decoder_desc& d = D->d;
     const uint32_t E = d.n_embd, q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim, qkv_ld = q_dim + 2 * k_dim;
     int rc;
-    int cur = 0;
-    // The embedding kernel takes a full dependency on everything before it (no programmatic
-    // launch): later kernels of the step rely on the previous step's position update and
-    // cache writes being complete before any of them starts.
-    if (D->embd.wtype == WT_Q4_0)
-        launch_k(k_embed<WT_Q4_0>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
-    else
-        launch_k(k_embed<WT_Q4_K>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, d.n_vocab, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
-    count_launch();
-    for (uint32_t L = 0; L < d.n_layer; ++L) {
+    if (part < 2 * d.n_layer && !(part & 1u)) {
+        const uint32_t L = part / 2;
         const Layer& ly = D->layers[L];
+        // The embedding kernel takes a full dependency on everything before it (no programmatic
+        // launch): later kernels of the step rely on the previous step's position update and
+        // cache writes being complete before any of them starts.
+        if (L == 0) {
+            if (D->embd.wtype == WT_Q4_0)
+                launch_k(k_embed<WT_Q4_0>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
+            else
+                launch_k(k_embed<WT_Q4_K>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
+            count_launch();
+        }
+        const int cur = L == 0 ? 0 : 1;             // residual stream buffer on entry
         GemvArgs in = {};
         in.ldx = (int)E; in.eps = d.norm_eps; in.h_in = D->hbuf[cur]; in.w_pre = ly.norm[NORM_ATTN];
         if (L > 0) { in.add_src = D->proj; in.w_post = D->layers[L - 1].norm[NORM_POST_FFW]; in.h_out = D->hbuf[cur ^ 1]; }
@@ -783,35 +791,46 @@ static int enqueue_step_impl(Decoder* D, uint32_t batch, bool with_lm, bool want
             in2.y = D->qkv + q_dim + k_dim;
             if ((rc = gemv(ly.m[MAT_V], nullptr, in2, batch, EPI_STORE))) return rc;
         }
-        if (L > 0) cur ^= 1;
         rc = d.kv_dtype == 1 ? launch_attn_t<__half>(D, L, batch) : launch_attn_t<float>(D, L, batch);
         if (rc) return rc;
         GemvArgs o = {};
         o.x = D->attn_out; o.ldx = (int)q_dim; o.y = D->proj; o.ldy = (int)E;
         if ((rc = gemv(ly.m[MAT_O], nullptr, o, batch, EPI_STORE))) return rc;
+    } else if (part < 2 * d.n_layer) {
+        const Layer& ly = D->layers[part / 2];
+        // the stream is in buffer 0 here for every layer (layer 0 never flipped, the others flipped in their QKV)
         GemvArgs gu = {};
-        gu.ldx = (int)E; gu.eps = d.norm_eps; gu.h_in = D->hbuf[cur]; gu.add_src = D->proj; gu.w_post = ly.norm[NORM_POST_ATTN];
-        gu.w_pre = ly.norm[NORM_FFN]; gu.h_out = D->hbuf[cur ^ 1]; gu.y = D->act; gu.ldy = (int)d.n_ff;
+        gu.ldx = (int)E; gu.eps = d.norm_eps; gu.h_in = D->hbuf[0]; gu.add_src = D->proj; gu.w_post = ly.norm[NORM_POST_ATTN];
+        gu.w_pre = ly.norm[NORM_FFN]; gu.h_out = D->hbuf[1]; gu.y = D->act; gu.ldy = (int)d.n_ff;
         if ((rc = gemv(ly.m[MAT_GATE], &ly.m[MAT_UP], gu, batch, d.ffn_act == 0 ? EPI_GEGLU : EPI_SWIGLU))) return rc;
-        cur ^= 1;
         GemvArgs dn = {};
         dn.x = D->act; dn.ldx = (int)d.n_ff; dn.y = D->proj; dn.ldy = (int)E;
         if ((rc = gemv(ly.m[MAT_DOWN], nullptr, dn, batch, EPI_STORE))) return rc;
+    } else if (part == 2 * d.n_layer) {
+        if (with_lm) {
+            const Mat& lm = D->output.bound ? D->output : D->embd;
+            GemvArgs a = {};
+            a.ldx = (int)E; a.eps = d.norm_eps; a.h_in = D->hbuf[1]; a.add_src = D->proj;
+            a.w_post = D->layers[d.n_layer - 1].norm[NORM_POST_FFW]; a.w_pre = D->output_norm; a.h_out = D->hbuf[0];
+            a.y = want_logits ? D->logits : nullptr; a.ldy = (int)lm.rows; a.softcap = d.final_softcap;
+            a.out_tok = D->cur_tok; a.out_val = D->cur_val;
+            if ((rc = argmax_scratch(&a.part_val, &a.part_idx, &a.ticket))) return rc;
+            if ((rc = gemv(lm, nullptr, a, batch, EPI_ARGMAX))) return rc;
+            D->h_final = 0;
+        }
+    } else {
+        launch_k(k_advance, dim3((batch + 63) / 64), dim3(64), 0, g.stream, g.pdl, D->pos, D->cur_tok, D->gen_log, d.kv_cap, batch, with_lm ? 1 : 0);
+        count_launch();
     }
-    if (with_lm) {
-        const Mat& lm = D->output.bound ? D->output : D->embd;
-        GemvArgs a = {};
-        a.ldx = (int)E; a.eps = d.norm_eps; a.h_in = D->hbuf[cur]; a.add_src = D->proj;
-        a.w_post = D->layers[d.n_layer - 1].norm[NORM_POST_FFW]; a.w_pre = D->output_norm; a.h_out = D->hbuf[cur ^ 1];
-        a.y = want_logits ? D->logits : nullptr; a.ldy = (int)d.n_vocab; a.softcap = d.final_softcap;
-        a.out_tok = D->cur_tok;
-        if ((rc = argmax_scratch(&a.part_val, &a.part_idx, &a.ticket))) return rc;
-        if ((rc = gemv(lm, nullptr, a, batch, EPI_ARGMAX))) return rc;
-        D->h_final = cur ^ 1;
-    }
-    launch_k(k_advance, dim3((batch + 63) / 64), dim3(64), 0, g.stream, g.pdl, D->pos, D->cur_tok, D->gen_log, d.kv_cap, batch, with_lm ? 1 : 0);
-    count_launch();
     return check_launch("decoder step");
+}
+
+static int enqueue_step_impl(Decoder* D, uint32_t batch, bool with_lm, bool want_logits) {
+    for (uint32_t part = 0; part < n_parts(D); ++part) {
+        const int rc = enqueue_part(D, batch, part, with_lm, want_logits);
+        if (rc) return rc;
+    }
+    return ADAMAH_OK;
 }
 
 static int validate_bound(Decoder* D) {
@@ -872,7 +891,7 @@ extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint
     g_dec[id] = D;
 #define DALLOC(p, bytes) do { cudaError_t e__ = cudaMalloc((void**)&(p), (bytes)); if (e__ != cudaSuccess) { destroy(D); g_dec[id] = nullptr; \
         return fail(ADAMAH_ERR_MEMORY, "decoder_create: cudaMalloc(%zu) failed: %s", (size_t)(bytes), cudaGetErrorString(e__)); } } while (0)
-    DALLOC(D->pos, B * 4); DALLOC(D->cur_tok, B * 4); DALLOC(D->prompt_len, B * 4);
+    DALLOC(D->pos, B * 4); DALLOC(D->cur_tok, B * 4); DALLOC(D->cur_val, B * 4); DALLOC(D->prompt_len, B * 4);
     DALLOC(D->prompt_tok, B * d.kv_cap * 4); DALLOC(D->gen_log, B * d.kv_cap * 4);
     DALLOC(D->block_table, B * D->max_pages_per_seq * 4);
     DALLOC(D->kv_pool, (size_t)D->n_pages * D->page_elems * kv_elem_size(d));
@@ -886,6 +905,7 @@ extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint
     cudaMemsetAsync(D->attn_ticket, 0, B * d.n_head * 4, g.stream);
     cudaMemsetAsync(D->pos, 0, B * 4, g.stream);
     cudaMemsetAsync(D->cur_tok, 0, B * 4, g.stream);
+    cudaMemsetAsync(D->cur_val, 0, B * 4, g.stream);
     cudaMemsetAsync(D->prompt_len, 0, B * 4, g.stream);
     cudaMemsetAsync(D->kv_pool, 0, (size_t)D->n_pages * D->page_elems * kv_elem_size(d), g.stream);
     k_fill_i32<<<(unsigned)((B * D->max_pages_per_seq + 255) / 256), 256, 0, g.stream>>>(D->block_table, -1, B * D->max_pages_per_seq);
@@ -914,7 +934,10 @@ extern "C" int adam_b200_decoder_bind_matrix(uint32_t id, uint32_t layer, uint32
     const uint32_t q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim;
     const uint32_t want_r[MAT_KINDS] = {q_dim, k_dim, k_dim, d.n_embd, d.n_ff, d.n_ff, d.n_embd, d.n_vocab, d.n_vocab};
     const uint32_t want_c[MAT_KINDS] = {d.n_embd, d.n_embd, d.n_embd, q_dim, d.n_embd, d.n_embd, d.n_ff, d.n_embd, d.n_embd};
-    if (rows != want_r[kind] || cols != want_c[kind])
+    // A tensor-parallel shard looks tokens up in the whole embedding table while its LM head
+    // (n_vocab) covers only the shard's vocabulary rows.
+    const bool full_embd = kind == MAT_EMBD && d.tp_size > 1 && rows >= d.n_vocab && cols == d.n_embd;
+    if (!full_embd && (rows != want_r[kind] || cols != want_c[kind]))
         return fail(ADAMAH_ERR_INVALID, "bind_matrix: kind %u expects [%u,%u], got [%u,%u]", kind, want_r[kind], want_c[kind], rows, cols);
     Mat mt = {};
     int rc = weight_ref(m, elem_off, (uint64_t)rows * cols, &mt.wtype, &mt.w);
@@ -1048,6 +1071,47 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
     }
     end_of_op();
     return rc;
+}
+
+// One part of a token step, enqueued directly on the stream (no graph): see enqueue_part.
+// For callers that interleave their own work between parts (tensor parallelism: an
+// all-reduce of the projection buffer after every layer part, a merge of the arg-max
+// pairs after the LM-head part).  flags as in adam_b200_decoder_step.
+extern "C" int adam_b200_decoder_n_parts(uint32_t id) {
+    Decoder* D = get_dec(id);
+    return D ? (int)n_parts(D) : ADAMAH_ERR_NOT_FOUND;
+}
+extern "C" int adam_b200_decoder_step_part(uint32_t id, uint32_t part, uint32_t flags) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (!D->batch) return fail(ADAMAH_ERR_INVALID, "decoder_step_part: call decoder_begin first");
+    if (part >= n_parts(D)) return fail(ADAMAH_ERR_INVALID, "decoder_step_part: part %u of %u", part, n_parts(D));
+    const bool with_lm = flags & 1u, want_logits = (flags & 2u) != 0;
+    static const bool allow = !(getenv("ADAM_B200_PDL") && atoi(getenv("ADAM_B200_PDL")) == 0);
+    g.pdl = allow;
+    const int rc = enqueue_part(D, D->batch, part, with_lm, want_logits);
+    g.pdl = false;
+    end_of_op();
+    return rc;
+}
+// Device address and size of one of the decoder's buffers, for callers that run their own
+// kernels or collectives on them (same stream, see adam_b200_set_stream):
+//   0 = projection output [batch][n_embd] f32 (what a tensor-parallel caller all-reduces)
+//   1 = current token ids [max_batch] i32     2 = their logit values [max_batch] f32
+//   3 = positions [max_batch] i32
+extern "C" int adam_b200_decoder_buffer_ptr(uint32_t id, uint32_t which, uint64_t* ptr_out, uint64_t* bytes_out) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (!ptr_out || !bytes_out) return fail(ADAMAH_ERR_INVALID, "decoder_buffer_ptr: null argument");
+    const size_t B = D->d.max_batch;
+    switch (which) {
+    case 0: *ptr_out = (uint64_t)(uintptr_t)D->proj; *bytes_out = B * D->d.n_embd * 4; break;
+    case 1: *ptr_out = (uint64_t)(uintptr_t)D->cur_tok; *bytes_out = B * 4; break;
+    case 2: *ptr_out = (uint64_t)(uintptr_t)D->cur_val; *bytes_out = B * 4; break;
+    case 3: *ptr_out = (uint64_t)(uintptr_t)D->pos; *bytes_out = B * 4; break;
+    default: return fail(ADAMAH_ERR_INVALID, "decoder_buffer_ptr: unknown buffer %u", which);
+    }
+    return ADAMAH_OK;
 }
 
 // Reads (after synchronising): positions, current sampled tokens, and the log of

@@ -70,6 +70,7 @@ struct GemvArgs {
     unsigned int* ticket;           // one counter, zero between launches
     int* out_tok;                   // [B] winning row per batch entry
     float* out_tok_f32;             // optional: same id stored as float (reference convention)
+    float* out_val;                 // optional: the winning logit (before any softcap)
     float softcap;                  // applied to stored logits only (monotone)
     int max_grid;                   // 0 = launcher's choice; otherwise an upper bound on the CTAs launched
     uint32_t* err;                  // device error word (set by launch_gemv_mma)
@@ -518,6 +519,7 @@ __global__ void __launch_bounds__(256, (WT == WT_Q4_0 && NB == 1) ? 2 : 1) k_gem
             for (int w = 1; w < n_warps; ++w) if (better(s_bv[w], s_bi[w], bv, bi)) { bv = s_bv[w]; bi = s_bi[w]; }
             const int tok = bi < 0 ? 0 : bi;
             if (a.out_tok) a.out_tok[b] = tok;
+            if (a.out_val) a.out_val[b] = bv;
             if (a.out_tok_f32) a.out_tok_f32[b] = (float)tok;
         }
     }

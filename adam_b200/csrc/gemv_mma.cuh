@@ -519,6 +519,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a, const uin
             for (int w = 1; w < n_warps; ++w) if (better(s_bv[w], s_bi[w], bv, bi)) { bv = s_bv[w]; bi = s_bi[w]; }
             const int tok = bi < 0 ? 0 : bi;
             if (a.out_tok) a.out_tok[b] = tok;
+            if (a.out_val) a.out_val[b] = bv;
             if (a.out_tok_f32) a.out_tok_f32[b] = (float)tok;
         }
     }

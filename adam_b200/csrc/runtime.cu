@@ -225,7 +225,8 @@ extern "C" int adamah_init_ex(uint64_t, uint64_t) {
     g.device = dev;
     g.sm_count = p.multiProcessorCount;
     g.total_mem = p.totalGlobalMem;
-    CU(cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking));
+    CU(cudaStreamCreateWithFlags(&g.own_stream, cudaStreamNonBlocking));
+    g.stream = g.own_stream;
     g.handles = (Handle*)calloc(MAX_HANDLES, sizeof(Handle));
     if (!g.handles) return fail(ADAMAH_ERR_MEMORY, "out of host memory");
     CU(cudaMalloc(&g.dev_err, sizeof(uint32_t)));
@@ -251,8 +252,19 @@ extern "C" void adamah_shutdown(void) {
     for (uint32_t i = 0; i < MAX_HANDLES; ++i) if (g.handles[i].used) { cudaFree(g.handles[i].dev); free(g.handles[i].shadow); }
     free(g.handles);
     cudaFree(g.dev_err);
-    cudaStreamDestroy(g.stream);
+    cudaStreamDestroy(g.own_stream);
     memset(&g, 0, sizeof g);
+}
+
+namespace ab { bool capturing(); }
+// Enqueue on a stream the caller owns (0 = back to the library's own stream), so that the
+// caller's other work on that stream, e.g. collectives, is ordered with the library's kernels.
+extern "C" int adam_b200_set_stream(uint64_t stream) {
+    if (!g.inited) return ADAMAH_ERR_INVALID;
+    if (ab::capturing()) return fail(ADAMAH_ERR_INVALID, "set_stream: a capture is open");
+    cudaStreamSynchronize(g.stream);
+    g.stream = stream ? (cudaStream_t)(uintptr_t)stream : g.own_stream;
+    return ADAMAH_OK;
 }
 
 extern "C" void adamah_sync(void) { if (g.inited) cudaStreamSynchronize(g.stream); }

@@ -54,7 +54,7 @@ class ADAMEngine:
 
     def __init__(self, gpu, cfg: ModelConfig, tensors: Dict[str, object], adamah_mod=None, kv_cap: int = 1024,
                  max_batch: int = 1, kv_dtype: str = "f16", window: bool = False, page_size: int = 64,
-                 n_pages: int = 0, verbose: bool = False, tile: bool = True, **kw):
+                 n_pages: int = 0, verbose: bool = False, tile: bool = True, tp_rank: int = 0, tp_size: int = 1, **kw):
         self.gpu = gpu
         self.A = adamah_mod if adamah_mod is not None else C
         self.cfg = cfg
@@ -77,7 +77,7 @@ class ADAMEngine:
             attn_scale=float(np.float32(1.0 / np.sqrt(cfg.head_dim))),
             sliding_window=cfg.sliding_window, global_every=6 if cfg.arch == "gemma3" else 0,
             max_batch=self._max_batch, kv_cap=self._kv_cap, kv_dtype={"f32": 0, "f16": 1}[kv_dtype], page_size=page_size,
-            n_pages=n_pages, tp_rank=0, tp_size=1, flags=(1 if window else 0) | (0 if tile else 2))
+            n_pages=n_pages, tp_rank=tp_rank, tp_size=tp_size, flags=(1 if window else 0) | (0 if tile else 2))
         did = ctypes.c_uint32(0)
         self._check(self._lib.adam_b200_decoder_create(ctypes.byref(desc), ctypes.byref(did)), "adam_b200_decoder_create")
         self._dec = int(did.value)

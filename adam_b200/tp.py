@@ -1,0 +1,218 @@
+"""Tensor-parallel decode: one process per GPU, NCCL all-reduce of the projection partial sums.
+
+Sharding (the usual Megatron split, applied to the decode path of the 27B shape):
+
+* q, k, v by whole heads and gate/up by rows of ``n_ff`` (column-parallel): every rank runs
+  attention for its own heads and GeGLU for its own slice of the FFN with no communication;
+* o-proj and down-proj along K (row-parallel): each rank produces a partial ``[batch, n_embd]``
+  sum, one all-reduce each, i.e. two per layer;
+* the LM head by vocabulary rows: each rank finds the arg-max of its rows, the ``(value, id)``
+  pairs are all-gathered and the best one (ties to the lower id) becomes every rank's next token;
+* norm weights and the embedding table are replicated.
+
+K shards must be whole GGUF blocks (32 weights for Q4_0, 256 for Q4_K), so ``n_ff`` is split in
+block units and may be uneven across ranks; heads must divide evenly.
+
+The reference has no multi-GPU path; parity is defined against the oracle decoder summing the
+shard partials in rank order (``OracleDecoder(tp_size=..)``).
+
+The step runs as the decoder's parts (``adam_b200_decoder_step_part``) on torch's current stream
+with ``torch.distributed`` collectives between them; after a warm-up the whole step, collectives
+included, is captured into one CUDA graph and replayed.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import gguf_blocks as gb
+from .engine import ADAMEngine, STEP_LM, STEP_LOGITS
+from .replicas import shard_sequences
+from .synth import QTensor
+
+
+@dataclasses.dataclass
+class ShardPlan:
+    rank: int
+    world: int
+    heads: range          # query heads of this rank
+    kv_heads: range
+    ff: range             # rows of gate/up = K range of down
+    vocab: range          # LM-head rows
+    ff_bounds: Tuple[int, ...]   # K boundaries of down-proj over all ranks (len world + 1)
+
+
+def block_elems(ggml_type: int) -> int:
+    return 32 if ggml_type == gb.GGML_TYPE_Q4_0 else 256
+
+
+def block_bytes(ggml_type: int) -> int:
+    return 18 if ggml_type == gb.GGML_TYPE_Q4_0 else 144
+
+
+def shard_plan(cfg, rank: int, world: int, ggml_type: int) -> ShardPlan:
+    if cfg.n_head % world or cfg.n_head_kv % world:
+        raise ValueError(f"{cfg.n_head} query / {cfg.n_head_kv} kv heads do not split over {world} ranks")
+    be = block_elems(ggml_type)
+    if (cfg.n_head // world) * cfg.head_dim % be:
+        raise ValueError("a rank's heads must cover whole weight blocks of the o-proj K dimension")
+    if cfg.n_ff % be:
+        raise ValueError("n_ff must be a multiple of the weight block size")
+    hq, hk = cfg.n_head // world, cfg.n_head_kv // world
+
+    def scaled(r: range, unit: int) -> range:
+        return range(r.start * unit, r.stop * unit)
+
+    ff_units = cfg.n_ff // be
+    bounds = tuple(shard_sequences(ff_units, r, world).start * be for r in range(world)) + (cfg.n_ff,)
+    v_unit = 16
+    if cfg.n_vocab % v_unit:
+        v_unit = 1
+    return ShardPlan(rank, world, range(rank * hq, (rank + 1) * hq), range(rank * hk, (rank + 1) * hk),
+                     scaled(shard_sequences(ff_units, rank, world), be),
+                     scaled(shard_sequences(cfg.n_vocab // v_unit, rank, world), v_unit), bounds)
+
+
+def _rows(t: QTensor, r: range) -> QTensor:
+    bpr = t.cols // block_elems(t.ggml_type) * block_bytes(t.ggml_type)
+    raw = t.raw.reshape(t.rows, bpr)[r.start:r.stop]
+    raw = raw.contiguous().reshape(-1) if hasattr(raw, "contiguous") else np.ascontiguousarray(raw).reshape(-1)
+    return QTensor(t.ggml_type, len(r), t.cols, raw)
+
+
+def _cols(t: QTensor, r: range) -> QTensor:
+    be, bb = block_elems(t.ggml_type), block_bytes(t.ggml_type)
+    if r.start % be or r.stop % be:
+        raise ValueError("K shards must be whole weight blocks")
+    raw = t.raw.reshape(t.rows, t.cols // be, bb)[:, r.start // be:r.stop // be]
+    raw = raw.contiguous().reshape(-1) if hasattr(raw, "contiguous") else np.ascontiguousarray(raw).reshape(-1)
+    return QTensor(t.ggml_type, t.rows, len(r), raw)
+
+
+def shard_tensors(cfg, tensors: Dict[str, object], plan: ShardPlan):
+    """This rank's configuration and tensors.  The local ``n_vocab`` is the LM-head shard; the
+    embedding table stays whole (``token_embd.weight``) and the shard is ``output.weight``."""
+    hd = cfg.head_dim
+    q_rows = range(plan.heads.start * hd, plan.heads.stop * hd)
+    k_rows = range(plan.kv_heads.start * hd, plan.kv_heads.stop * hd)
+    local = dataclasses.replace(cfg, n_head=len(plan.heads), n_head_kv=len(plan.kv_heads), n_ff=len(plan.ff),
+                                n_vocab=len(plan.vocab))
+    out: Dict[str, object] = {}
+    lm = tensors["output.weight"] if "output.weight" in tensors else tensors["token_embd.weight"]
+    for name, t in tensors.items():
+        if not isinstance(t, QTensor):
+            out[name] = t
+        elif name == "token_embd.weight":
+            out[name] = t
+        elif name == "output.weight":
+            continue
+        elif name.endswith(("attn_q.weight",)):
+            out[name] = _rows(t, q_rows)
+        elif name.endswith(("attn_k.weight", "attn_v.weight")):
+            out[name] = _rows(t, k_rows)
+        elif name.endswith("attn_output.weight"):
+            out[name] = _cols(t, q_rows)
+        elif name.endswith(("ffn_gate.weight", "ffn_up.weight")):
+            out[name] = _rows(t, plan.ff)
+        elif name.endswith("ffn_down.weight"):
+            out[name] = _cols(t, plan.ff)
+        else:
+            raise KeyError(f"do not know how to shard {name}")
+    out["output.weight"] = _rows(lm, plan.vocab)
+    return local, out
+
+
+class _DeviceArray:
+    """Just enough of the CUDA array interface for ``torch.as_tensor`` to alias library memory."""
+
+    def __init__(self, ptr: int, n: int, typestr: str):
+        self.__cuda_array_interface__ = {"shape": (int(n),), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+
+class ADAMEngineTP(ADAMEngine):
+    """``ADAMEngine`` over this rank's shard; ``step`` adds the collectives.  Needs an initialised
+    ``torch.distributed`` process group (NCCL) and the library on this rank's GPU."""
+
+    def __init__(self, gpu, cfg, tensors, rank: int, world: int, group=None, use_graph: bool = True, **kw):
+        import torch
+        ggml_type = next(t.ggml_type for t in tensors.values() if isinstance(t, QTensor))
+        self.plan = shard_plan(cfg, rank, world, ggml_type)
+        self.full_cfg = cfg
+        local_cfg, local_t = shard_tensors(cfg, tensors, self.plan)
+        self._group = group
+        self._world = world
+        self._use_graph = use_graph
+        self._graphs: Dict[tuple, object] = {}
+        self._eager_steps: Dict[tuple, int] = {}
+        self._torch = torch
+        # the library enqueues on this torch stream from here on, so the collectives order with its kernels
+        self._stream = torch.cuda.Stream(device=gpu.device_index)
+        gpu.set_stream(self._stream.cuda_stream)
+        super().__init__(gpu, local_cfg, local_t, tp_rank=rank, tp_size=world, **kw)
+        self._n_parts = int(self._lib.adam_b200_decoder_n_parts(self._dec))
+        dev = f"cuda:{gpu.device_index}"
+        mb = self._max_batch
+        self._proj = torch.as_tensor(_DeviceArray(self._buf(0), mb * cfg.n_embd, "<f4"), device=dev).view(mb, cfg.n_embd)
+        self._tok = torch.as_tensor(_DeviceArray(self._buf(1), mb, "<i4"), device=dev)
+        self._val = torch.as_tensor(_DeviceArray(self._buf(2), mb, "<f4"), device=dev)
+
+    def _buf(self, which: int) -> int:
+        import ctypes
+        p, n = ctypes.c_uint64(0), ctypes.c_uint64(0)
+        self._check(self._lib.adam_b200_decoder_buffer_ptr(self._dec, which, ctypes.byref(p), ctypes.byref(n)), "adam_b200_decoder_buffer_ptr")
+        return int(p.value)
+
+    def _one_step(self, flags: int):
+        """All parts of one token step with the collectives between them, on the current stream."""
+        import torch.distributed as dist
+        torch = self._torch
+        B, L2, W = self._batch, 2 * self.cfg.n_layer, self._world
+        for part in range(self._n_parts):
+            self._check(self._lib.adam_b200_decoder_step_part(self._dec, part, flags), "adam_b200_decoder_step_part")
+            if W == 1:
+                continue
+            if part < L2:
+                dist.all_reduce(self._proj[:B], group=self._group)
+            elif part == L2 and (flags & STEP_LM):
+                # (value, global id) of every rank's best row; the best value wins, ties go to the lower id
+                gid = self._tok[:B] + self.plan.vocab.start
+                vals = torch.empty(W * B, dtype=torch.float32, device=gid.device)
+                ids = torch.empty(W * B, dtype=torch.int32, device=gid.device)
+                dist.all_gather_into_tensor(vals, self._val[:B].contiguous(), group=self._group)
+                dist.all_gather_into_tensor(ids, gid.contiguous(), group=self._group)
+                v, i = vals.view(W, B), ids.view(W, B)
+                best = v.max(dim=0).values
+                cand = torch.where(v == best.unsqueeze(0), i, torch.full_like(i, 2 ** 31 - 1))
+                self._tok[:B].copy_(cand.min(dim=0).values)
+
+    def step(self, n_steps: int = 1, lm_head: bool = True, logits: bool = False, direct: bool = False):
+        torch = self._torch
+        flags = (STEP_LM if lm_head else 0) | (STEP_LOGITS if logits else 0)
+        key = (flags, self._batch)
+        with torch.cuda.stream(self._stream):
+            for _ in range(n_steps):
+                if self._use_graph and not direct and key in self._graphs:
+                    self._graphs[key].replay()
+                    continue
+                self._one_step(flags)
+                n = self._eager_steps.get(key, 0) + 1
+                self._eager_steps[key] = n
+                if self._use_graph and not direct and n == 2:
+                    # after two eager steps of a kind the step is recorded once (recording does not run
+                    # it), collectives included, and replayed from then on
+                    self._stream.synchronize()
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr, stream=self._stream):
+                        self._one_step(flags)
+                    self._graphs[key] = gr
+
+    def begin(self, prompts, reserve):
+        super().begin(prompts, reserve)
+        self._graphs = {k: g for k, g in self._graphs.items() if k[1] == self._batch}
+
+    def close(self):
+        self._graphs.clear()
+        super().close()
+        self.gpu.set_stream(0)

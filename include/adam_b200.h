@@ -246,6 +246,11 @@ int map_matvec_argmax_t_xq4_static_dev(uint32_t map_act, uint32_t map_wt, uint32
                                        uint32_t idx_tmp_h, uint32_t val_tmp_h, uint32_t dst_h,
                                        uint32_t K, uint32_t N, uint32_t rows_per_group);
 
+/* Enqueue everything on a CUDA stream the caller owns (a cudaStream_t passed as an
+ * integer; 0 = back to the library's own stream), so the caller's collectives or kernels on
+ * that stream are ordered with the library's.  Synchronises the stream in use first. */
+int adam_b200_set_stream(uint64_t stream);
+
 /* ---- fused decoder ------------------------------------------------------------
  * Runs the reference engine's per-token loop (adam/models/engine.py:2971-3706
  * `_forward`, generate loop :3810-3944) for a batch of sequences as one CUDA
@@ -285,6 +290,16 @@ int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_t* prompt_t
 /* n_steps token steps.  flags: bit 0 LM head + arg-max, bit 1 also store logits,
  * bit 2 launch kernels directly (no graph replay). */
 int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t flags);
+/* The same step in parts, each enqueued directly on the stream, for callers that put their
+ * own work between them (tensor parallelism).  Parts 2L / 2L+1 = attention half (embedding
+ * for L = 0, QKV, attention, o-proj) / FFN half (gate+up, down) of layer L; then the LM head
+ * (flags bit 0) and the position update.  After each layer part the projection buffer holds
+ * this shard's partial sums.  No counterpart in the reference (it has no multi-GPU path). */
+int adam_b200_decoder_n_parts(uint32_t id);                                   /* 2*n_layer + 2, or a negative status */
+int adam_b200_decoder_step_part(uint32_t id, uint32_t part, uint32_t flags);
+/* Device address / size of a decoder buffer: 0 projection output [batch][n_embd] f32,
+ * 1 current token ids [max_batch] i32, 2 their logit values [max_batch] f32, 3 positions. */
+int adam_b200_decoder_buffer_ptr(uint32_t id, uint32_t which, uint64_t* ptr_out, uint64_t* bytes_out);
 int adam_b200_decoder_read_state(uint32_t id, int32_t* pos_out, int32_t* cur_tok_out);   /* [max_batch] each, may be NULL */
 int adam_b200_decoder_read_log(uint32_t id, uint32_t seq, uint32_t first_pos, uint32_t n, int32_t* out);
 int adam_b200_decoder_read_logits(uint32_t id, uint32_t seq, float* out);                 /* [n_vocab] */

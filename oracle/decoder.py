@@ -86,13 +86,15 @@ class OracleDecoder:
     """Single-sequence greedy decoder on float32 weights."""
 
     def __init__(self, cfg, tensors_f32: Dict[str, np.ndarray], kv_cap: int,
-                 window: bool = False, kv_dtype=np.float32, tp_size: int = 1):
+                 window: bool = False, kv_dtype=np.float32, tp_size: int = 1, tp_ff_bounds=None):
         self.c = cfg
         self.t = tensors_f32
         self.kv_cap = kv_cap
         self.window = window
         self.kv_dtype = np.dtype(kv_dtype)
         self.tp = tp_size
+        # K boundaries of the down-projection shards (len tp_size + 1); equal shards when None
+        self.tp_ff_bounds = None if tp_ff_bounds is None else [int(b) for b in tp_ff_bounds]
         c = cfg
         # diag_inference.py:958-961
         self.k_cache = np.zeros((c.n_layer, c.n_head_kv, kv_cap, c.head_dim_kv), np.float32)
@@ -103,16 +105,20 @@ class OracleDecoder:
         self.k_cache[:] = 0
         self.v_cache[:] = 0
 
-    def _row_sharded(self, x: np.ndarray, W: np.ndarray) -> np.ndarray:
-        """``x @ W.T`` ; with tp_size>1 the K dimension is split into equal
-        contiguous shards whose partial products are added in rank order."""
+    def _row_sharded(self, x: np.ndarray, W: np.ndarray, bounds=None) -> np.ndarray:
+        """``x @ W.T`` ; with tp_size>1 the K dimension is split into contiguous
+        shards (equal ones unless ``bounds`` gives the boundaries) whose partial
+        products are added in rank order."""
         if self.tp == 1:
             return x @ W.T
         K = x.shape[0]
-        step = K // self.tp
+        if bounds is None:
+            step = K // self.tp
+            bounds = [r * step for r in range(self.tp)] + [K]
         acc = None
         for r in range(self.tp):
-            part = x[r * step:(r + 1) * step] @ W[:, r * step:(r + 1) * step].T
+            a, b = bounds[r], bounds[r + 1]
+            part = x[a:b] @ W[:, a:b].T
             acc = part if acc is None else acc + part
         return acc
 
@@ -171,7 +177,7 @@ class OracleDecoder:
             gate = normed2 @ T[f"{p}.ffn_gate.weight"].T
             up = normed2 @ T[f"{p}.ffn_up.weight"].T
             gate = gelu_tanh(gate) if c.ffn_act == "gelu" else silu(gate)
-            ffn = self._row_sharded(gate * up, T[f"{p}.ffn_down.weight"])
+            ffn = self._row_sharded(gate * up, T[f"{p}.ffn_down.weight"], self.tp_ff_bounds)
             pfn = f"{p}.post_ffw_norm.weight"
             if pfn in T:
                 ffn = rms_norm(ffn, T[pfn], eps)
