@@ -1015,7 +1015,7 @@ extern "C" int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_
         if (!prompt_tokens) return fail(ADAMAH_ERR_INVALID, "decoder_begin: null prompt");
         for (uint32_t t = 0; t < prompt_lens[b]; ++t) {
             const int32_t tk = prompt_tokens[off + t];
-            if (tk < 0 || (uint32_t)tk >= d.n_vocab) return fail(ADAMAH_ERR_INVALID, "decoder_begin: token id %d outside the vocabulary", tk);
+            if (tk < 0 || (uint32_t)tk >= D->embd.rows) return fail(ADAMAH_ERR_INVALID, "decoder_begin: token id %d outside the vocabulary", tk);
             ptok[(size_t)b * d.kv_cap + t] = tk;
         }
         off += prompt_lens[b];
