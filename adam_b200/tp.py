@@ -91,14 +91,19 @@ def _cols(t: QTensor, r: range) -> QTensor:
     return QTensor(t.ggml_type, t.rows, len(r), raw)
 
 
+def local_config(cfg, plan: ShardPlan):
+    """The configuration one rank's decoder is created with: its own heads, FFN rows and LM-head rows."""
+    return dataclasses.replace(cfg, n_head=len(plan.heads), n_head_kv=len(plan.kv_heads), n_ff=len(plan.ff),
+                               n_vocab=len(plan.vocab))
+
+
 def shard_tensors(cfg, tensors: Dict[str, object], plan: ShardPlan):
     """This rank's configuration and tensors.  The local ``n_vocab`` is the LM-head shard; the
     embedding table stays whole (``token_embd.weight``) and the shard is ``output.weight``."""
     hd = cfg.head_dim
     q_rows = range(plan.heads.start * hd, plan.heads.stop * hd)
     k_rows = range(plan.kv_heads.start * hd, plan.kv_heads.stop * hd)
-    local = dataclasses.replace(cfg, n_head=len(plan.heads), n_head_kv=len(plan.kv_heads), n_ff=len(plan.ff),
-                                n_vocab=len(plan.vocab))
+    local = local_config(cfg, plan)
     out: Dict[str, object] = {}
     lm = tensors["output.weight"] if "output.weight" in tensors else tensors["token_embd.weight"]
     for name, t in tensors.items():
@@ -135,12 +140,20 @@ class ADAMEngineTP(ADAMEngine):
     """``ADAMEngine`` over this rank's shard; ``step`` adds the collectives.  Needs an initialised
     ``torch.distributed`` process group (NCCL) and the library on this rank's GPU."""
 
-    def __init__(self, gpu, cfg, tensors, rank: int, world: int, group=None, use_graph: bool = True, **kw):
+    def __init__(self, gpu, cfg, tensors, rank: int, world: int, group=None, use_graph: bool = True,
+                 presharded: bool = False, **kw):
+        """``cfg`` is the whole model's configuration.  ``tensors`` is the whole model (each rank
+        keeps its slice) or, with ``presharded``, already this rank's tensors as ``shard_tensors``
+        would return them (``token_embd.weight`` whole, ``output.weight`` = the vocabulary shard)."""
         import torch
         ggml_type = next(t.ggml_type for t in tensors.values() if isinstance(t, QTensor))
         self.plan = shard_plan(cfg, rank, world, ggml_type)
         self.full_cfg = cfg
-        local_cfg, local_t = shard_tensors(cfg, tensors, self.plan)
+        if presharded:
+            local_cfg = local_config(cfg, self.plan)
+            local_t = tensors
+        else:
+            local_cfg, local_t = shard_tensors(cfg, tensors, self.plan)
         self._group = group
         self._world = world
         self._use_graph = use_graph
