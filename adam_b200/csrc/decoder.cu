@@ -733,8 +733,8 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch) {
 static int gemv(const Mat& m, const Mat* m2, GemvArgs a, int B, int epi) {
     a.w0 = m.w; if (m2) a.w1 = m2->w;
     a.N = (int)m.rows; a.K = (int)m.cols; a.B = B; a.epi = epi;
-    if (m.tiled && (!m2 || m2->tiled) && gemv_mma_supports(a))
-        return launch_gemv_mma(m.tiled, m2 ? m2->tiled : nullptr, a, g.stream);
+    if (m.tiled && (!m2 || (m2->tiled && m2->wtype == m.wtype)) && gemv_mma_supports(m.wtype, a))
+        return launch_gemv_mma(m.wtype, m.tiled, m2 ? m2->tiled : nullptr, a, g.stream);
     return launch_gemv(m.wtype, a, g.stream);
 }
 
@@ -847,7 +847,7 @@ static int validate_bound(Decoder* D) {
         const size_t ipr = q.cols / (q.wtype == WT_Q4_0 ? 32 : 256) * (q.wtype == WT_Q4_0 ? 1 : 9);   // uint4 per row
         ly.qkv_contiguous = q.wtype == k.wtype && k.wtype == v.wtype && k.w.q == q.w.q + (size_t)q.rows * ipr &&
                             v.w.q == k.w.q + (size_t)k.rows * ipr;
-        if (ly.qkv_contiguous && D->use_tiles && q.wtype == WT_Q4_0 && !ly.qkv_tiled) {
+        if (ly.qkv_contiguous && D->use_tiles && !ly.qkv_tiled) {
             const uint32_t rows = q.rows + k.rows + v.rows;
             if (rows % 16 == 0 && q.cols % 64 == 0 && tile_tensor(q.map_id, q.elem_off, rows, q.cols) == ADAMAH_OK)
                 ly.qkv_tiled = (const uint8_t*)find_tiled(q.map_id, q.elem_off, rows, q.cols);
@@ -946,7 +946,7 @@ extern "C" int adam_b200_decoder_bind_matrix(uint32_t id, uint32_t layer, uint32
     mt.rows = rows; mt.cols = cols; mt.bound = true; mt.map_id = map_wt; mt.elem_off = elem_off; mt.tiled = nullptr;
     // q, k, v get one combined tiled copy later (validate_bound); token_embd is tiled only as the LM head
     const bool solo = kind == MAT_O || kind == MAT_GATE || kind == MAT_UP || kind == MAT_DOWN || kind == MAT_OUTPUT || kind == MAT_EMBD;
-    if (D->use_tiles && solo && mt.wtype == WT_Q4_0 && rows % 16 == 0 && cols % 64 == 0) {
+    if (D->use_tiles && solo && rows % 16 == 0 && cols % 64 == 0) {
         if (tile_tensor(map_wt, elem_off, rows, cols) == ADAMAH_OK) mt.tiled = (const uint8_t*)find_tiled(map_wt, elem_off, rows, cols);
     }
     if (kind == MAT_EMBD) D->embd = mt; else if (kind == MAT_OUTPUT) D->output = mt; else D->layers[layer].m[kind] = mt;

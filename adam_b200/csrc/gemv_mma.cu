@@ -9,27 +9,40 @@ typedef void (*MmaKernel)(const GemvArgs, const uint8_t*, const uint8_t*, int);
 
 // staged bytes per 32-activation block: NCOL columns of 32 bytes + NCOL/2 pre-summed floats
 static size_t x_bytes(int units, int ncol) { return (((size_t)units * (ncol * 32 + (ncol / 2) * 4)) + 127) & ~(size_t)127; }
-static size_t ring_bytes(int n_warps) { return (size_t)n_warps * MMA_RING_BYTES_PER_WARP; }
+static size_t ring_bytes(int wt, int n_warps) { return (size_t)n_warps * mma_ring_bytes_per_warp(wt); }
+// fewest warps whose threads hold a fused input chain in registers (three float4 each)
+static int chain_min_warps(const GemvArgs& a) { return a.h_in ? ((a.K >> 2) + 95) / 96 : 1; }
 
-bool gemv_mma_supports(const GemvArgs& a) {
+bool gemv_mma_supports(int wt, const GemvArgs& a) {
     if (a.N <= 0 || a.K <= 0 || a.B <= 0) return false;
     if (a.N % 16 || a.K % 64) return false;
-    if (a.h_in) { if ((a.K >> 2) > 3 * 256 || (a.ldx & 3)) return false; }
+    if (wt != WT_Q4_0 && wt != WT_Q4_K) return false;
+    if (wt == WT_Q4_K && a.K % 256) return false;
+    if (a.h_in) { if (chain_min_warps(a) > MMA_MAX_WARPS || (a.ldx & 3)) return false; }
     else if (((uintptr_t)a.x & 15) || (a.ldx & 3)) return false;
-    return x_bytes(a.K / 32, 4) + ring_bytes(8) <= (size_t)MMA_SMEM_LIMIT;
+    int nw = chain_min_warps(a) <= 8 ? 8 : (chain_min_warps(a) <= 12 ? 12 : 16);
+    return x_bytes(a.K / 32, 4) + ring_bytes(wt, nw) <= (size_t)MMA_SMEM_LIMIT;
 }
 
 struct MmaInfo { bool attr; size_t occ_smem[3]; int per_sm[3]; };   // per warp count 8, 12, 16
-static MmaInfo g_mma_info[3][2];
+static MmaInfo g_mma_info[2][3][2];
 
-int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream_t stream) {
-    if (!gemv_mma_supports(a)) return fail(ADAMAH_ERR_INVALID, "gemv_mma: shape not supported");
+template <int WT>
+static MmaKernel pick_kernel(int vi, bool pair) {
+    return vi == 0 ? (pair ? k_gemv_mma<4, true, WT> : k_gemv_mma<4, false, WT>)
+         : vi == 1 ? (pair ? k_gemv_mma<8, true, WT> : k_gemv_mma<8, false, WT>)
+                   : (pair ? k_gemv_mma<16, true, WT> : k_gemv_mma<16, false, WT>);
+}
+
+int launch_gemv_mma(int wt, const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream_t stream) {
+    if (!gemv_mma_supports(wt, a)) return fail(ADAMAH_ERR_INVALID, "gemv_mma: shape not supported");
     const bool pair = (a.epi == EPI_GEGLU || a.epi == EPI_SWIGLU);
     if (pair && !t1) return fail(ADAMAH_ERR_INVALID, "gemv_mma: second matrix missing");
     const int units = a.K / 32, pairs = a.K / 64, n_rg = a.N / 16;
     // batch rows per pass: as many of 4, 2, 1 as shared memory allows
     int nb_max = 4;
-    while (nb_max > 1 && x_bytes(units, 4 * nb_max) + ring_bytes(8) > (size_t)MMA_SMEM_LIMIT) nb_max >>= 1;
+    const int nw_min = chain_min_warps(a) <= 8 ? 8 : (chain_min_warps(a) <= 12 ? 12 : 16);
+    while (nb_max > 1 && x_bytes(units, 4 * nb_max) + ring_bytes(wt, nw_min) > (size_t)MMA_SMEM_LIMIT) nb_max >>= 1;
     for (int b0 = 0; b0 < a.B; b0 += nb_max) {
         GemvArgs g1 = a;
         g1.B = (a.B - b0 < nb_max) ? a.B - b0 : nb_max;
@@ -43,10 +56,8 @@ int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream
         const int ncol = g1.B == 1 ? 4 : (g1.B == 2 ? 8 : 16);
         g1.err = g.dev_err;
         const int vi = ncol == 4 ? 0 : (ncol == 8 ? 1 : 2);
-        MmaKernel k = vi == 0 ? (pair ? k_gemv_mma<4, true> : k_gemv_mma<4, false>)
-                    : vi == 1 ? (pair ? k_gemv_mma<8, true> : k_gemv_mma<8, false>)
-                              : (pair ? k_gemv_mma<16, true> : k_gemv_mma<16, false>);
-        MmaInfo& ki = g_mma_info[vi][pair ? 1 : 0];
+        MmaKernel k = wt == WT_Q4_0 ? pick_kernel<WT_Q4_0>(vi, pair) : pick_kernel<WT_Q4_K>(vi, pair);
+        MmaInfo& ki = g_mma_info[wt == WT_Q4_0 ? 0 : 1][vi][pair ? 1 : 0];
         if (!ki.attr) {
             if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM_LIMIT) != cudaSuccess)
                 return fail(ADAMAH_ERR_BACKEND, "gemv_mma: cannot raise the shared-memory limit");
@@ -60,8 +71,8 @@ int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream
         int n_warps = 8, KS = 1, best_per_sm = 1;
         double best_cost = 1e300;
         const int nm = pair ? 2 : 1;
-        for (int nw = 8; nw <= 16; nw += 4) {
-            const size_t sm_bytes = x_bytes(units, ncol) + ring_bytes(nw);
+        for (int nw = nw_min; nw <= 16; nw += 4) {
+            const size_t sm_bytes = x_bytes(units, ncol) + ring_bytes(wt, nw);
             if (sm_bytes > (size_t)MMA_SMEM_LIMIT) break;
             int per_sm = ki.per_sm[nw / 4 - 2];
             if (ki.occ_smem[nw / 4 - 2] != sm_bytes) {
@@ -85,7 +96,7 @@ int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream
                 if (cost < best_cost * 0.999) { best_cost = cost; n_warps = nw; KS = c; best_per_sm = per_sm; }
             }
         }
-        const size_t smem = x_bytes(units, ncol) + ring_bytes(n_warps);
+        const size_t smem = x_bytes(units, ncol) + ring_bytes(wt, n_warps);
         const int n_sets = (n_rg + n_warps / KS - 1) / (n_warps / KS);
         int grid = g.sm_count * best_per_sm;
         if (grid > n_sets) grid = n_sets;

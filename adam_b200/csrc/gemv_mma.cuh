@@ -119,23 +119,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
-constexpr int MMA_TILE = 576;              // bytes per tile pair (16 rows x 64 weights: 512 nibble bytes + 32 fp16 scales)
+// bytes per tile pair (16 rows x 64 weights): 512 nibble bytes + 32 fp16 scales (Q4_0), or
+// + 64 bytes of 6-bit scales/mins as bytes + 64 bytes of fp16 (d, dmin) per row (Q4_K)
+constexpr int mma_tile_bytes(int wt) { return wt == WT_Q4_0 ? 576 : 640; }
 constexpr int MMA_NSTAGE = 3;              // ring stages per warp
 constexpr int MMA_MAX_WARPS = 16;
-template <bool PAIR> struct MmaGeo {
-    static constexpr int CH = PAIR ? 3 : 6;                                 // tile pairs per stage and matrix
-    static constexpr int STAGE_BYTES = CH * MMA_TILE * (PAIR ? 2 : 1);      // 3456
+template <bool PAIR, int WT> struct MmaGeo {
+    static constexpr int TILE = mma_tile_bytes(WT);
+    static constexpr int CH = WT == WT_Q4_0 ? (PAIR ? 3 : 6) : (PAIR ? 2 : 4);   // tile pairs per stage and matrix
+    static constexpr int STAGE_BYTES = CH * TILE * (PAIR ? 2 : 1);               // 3456 (Q4_0), 2560 (Q4_K)
 };
-constexpr int MMA_RING_BYTES_PER_WARP = MMA_NSTAGE * 6 * MMA_TILE;
+constexpr int mma_ring_bytes_per_warp(int wt) { return MMA_NSTAGE * (wt == WT_Q4_0 ? 6 * 576 : 4 * 640); }
 
-template <int NCOL, bool PAIR>
+template <int NCOL, bool PAIR, int WT>
 __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a, const uint8_t* __restrict__ t0, const uint8_t* __restrict__ t1, int KS) {
     constexpr int NI = NCOL == 16 ? 2 : 1;      // MMAs per block
     constexpr int NBR = NCOL / 4;               // batch rows staged
     constexpr int NPR = NCOL / 2;               // column pairs per block (one pre-summed value each)
     constexpr int NM = PAIR ? 2 : 1;
-    constexpr int CH = MmaGeo<PAIR>::CH;
-    constexpr int STAGE_BYTES = MmaGeo<PAIR>::STAGE_BYTES;
+    constexpr int CH = MmaGeo<PAIR, WT>::CH;
+    constexpr int STAGE_BYTES = MmaGeo<PAIR, WT>::STAGE_BYTES;
+    constexpr int MMA_TILE = MmaGeo<PAIR, WT>::TILE;
+    constexpr float SXF = WT == WT_Q4_0 ? -8.0f : -1.0f;    // Q4_0: d*(q-8); Q4_K: (d*sc)*q - (dmin*m)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ float s_red[2][MMA_MAX_WARPS][NM][NI][16][2];
     __shared__ __align__(8) uint64_t s_bar[MMA_MAX_WARPS][MMA_NSTAGE];
@@ -317,7 +322,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a, const uin
             int s0 = 0, s1 = 0;
 #pragma unroll
             for (int e = 0; e < 8; ++e) { s0 = __dp4a(c0[e], 0x01010101, s0); s1 = __dp4a(c1[e], 0x01010101, s1); }
-            v = -8.0f * (float)(s0 * 256 + s1);
+            v = SXF * (float)(s0 * 256 + s1);
         }
         s_sx[i] = v;
     }
@@ -354,19 +359,41 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a, const uin
             ac[i][1] = fmaf(d.y, (float)(dd[2] * 256 + dd[3]) + sx, ac[i][1]);
         }
     };
+    // Same for Q4_K: sc4 = { sc[g], m[g], sc[g+8], m[g+8] } of this block as bytes, (d, dmin) of the two rows.
+    auto block_imma_k = [&](uint32_t wg, uint32_t wh, const uint2* xu, const float* sxu, uint32_t sc4, float2 dm0, float2 dm1, float (&ac)[NI][2]) {
+        const uint32_t a0 = wg & 0x0F0F0F0Fu, a2 = (wg >> 4) & 0x0F0F0F0Fu;
+        const uint32_t a1 = wh & 0x0F0F0F0Fu, a3 = (wh >> 4) & 0x0F0F0F0Fu;
+        const float es0 = dm0.x * (float)(sc4 & 0xFFu), em0 = dm0.y * (float)((sc4 >> 8) & 0xFFu);
+        const float es1 = dm1.x * (float)((sc4 >> 16) & 0xFFu), em1 = dm1.y * (float)(sc4 >> 24);
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const uint2 b = xu[i * 32];
+            int dd[4];
+            imma16832(dd, a0, a1, a2, a3, b.x, b.y);
+            const float sx = sxu[i * 4];                     // minus the block's activation sum
+            ac[i][0] = fmaf(es0, (float)(dd[0] * 256 + dd[1]), fmaf(em0, sx, ac[i][0]));
+            ac[i][1] = fmaf(es1, (float)(dd[2] * 256 + dd[3]), fmaf(em1, sx, ac[i][1]));
+        }
+    };
     // Tile pair k of the current stage (both 32-weight blocks, both matrices).
     auto do_pair = [&](const unsigned char* buf, int k, const uint2* xp, const float* sx) {
-        const uint4 q = reinterpret_cast<const uint4*>(buf + k * MMA_TILE)[lane];
-        const uint2 sc = reinterpret_cast<const uint2*>(buf + k * MMA_TILE + 512)[g];
         const uint2* xu0 = xp + (2 * k) * xstep;
         const float* sx0 = sx + (2 * k) * NPR;
-        block_imma(q.x, q.y, xu0, sx0, sc.x, acc[0]);
-        block_imma(q.z, q.w, xu0 + xstep, sx0 + NPR, sc.y, acc[0]);
-        if (PAIR) {
-            const uint4 q1 = reinterpret_cast<const uint4*>(buf + (CH + k) * MMA_TILE)[lane];
-            const uint2 sc1 = reinterpret_cast<const uint2*>(buf + (CH + k) * MMA_TILE + 512)[g];
-            block_imma(q1.x, q1.y, xu0, sx0, sc1.x, acc[NM - 1]);
-            block_imma(q1.z, q1.w, xu0 + xstep, sx0 + NPR, sc1.y, acc[NM - 1]);
+#pragma unroll
+        for (int m = 0; m < NM; ++m) {
+            const unsigned char* tile = buf + (m * CH + k) * MMA_TILE;
+            const uint4 q = reinterpret_cast<const uint4*>(tile)[lane];
+            const uint2 sc = reinterpret_cast<const uint2*>(tile + 512)[g];
+            if constexpr (WT == WT_Q4_0) {
+                block_imma(q.x, q.y, xu0, sx0, sc.x, acc[m]);
+                block_imma(q.z, q.w, xu0 + xstep, sx0 + NPR, sc.y, acc[m]);
+            } else {
+                const uint2 hd = reinterpret_cast<const uint2*>(tile + 576)[g];
+                const float2 dm0 = __half22float2(*reinterpret_cast<const __half2*>(&hd.x));
+                const float2 dm1 = __half22float2(*reinterpret_cast<const __half2*>(&hd.y));
+                block_imma_k(q.x, q.y, xu0, sx0, sc.x, dm0, dm1, acc[m]);
+                block_imma_k(q.z, q.w, xu0 + xstep, sx0 + NPR, sc.y, dm0, dm1, acc[m]);
+            }
         }
     };
 
@@ -530,8 +557,8 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a, const uin
 // ADAMAH_ERR_INVALID without launching when the shape does not fit this kernel
 // (the caller then uses the generic kernel): needs N % 16 == 0, K % 64 == 0, and
 // either plain x or an input chain short enough for the register-resident path.
-int launch_gemv_mma(const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream_t stream);
-bool gemv_mma_supports(const GemvArgs& a);
+int launch_gemv_mma(int wtype, const uint8_t* t0, const uint8_t* t1, GemvArgs a, cudaStream_t stream);
+bool gemv_mma_supports(int wtype, const GemvArgs& a);
 const void* find_tiled(uint32_t map_id, uint64_t elem_off, uint32_t rows, uint32_t cols);
 const void* find_tiled_prefix(uint32_t map_id, uint64_t elem_off, uint32_t rows, uint32_t cols);
 int tile_tensor(uint32_t map_id, uint64_t elem_off, uint32_t rows, uint32_t cols);

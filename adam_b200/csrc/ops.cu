@@ -352,9 +352,9 @@ int weight_ref(const Map* m, uint64_t off, uint64_t n_elems, int* wtype, WeightR
 // Run a GEMV on the tensor at (map, off): the tensor-core kernel when a row-tiled
 // copy of exactly this tensor is registered and the shape fits, the generic one otherwise.
 int run_gemv(uint32_t map_id, uint64_t off, int wtype, GemvArgs& ga) {
-    if (wtype == WT_Q4_0 && ga.epi != EPI_GEGLU && ga.epi != EPI_SWIGLU) {
+    if (ga.epi != EPI_GEGLU && ga.epi != EPI_SWIGLU) {
         const void* t = find_tiled(map_id, off, (uint32_t)ga.N, (uint32_t)ga.K);
-        if (t && gemv_mma_supports(ga)) return launch_gemv_mma((const uint8_t*)t, nullptr, ga, g.stream);
+        if (t && gemv_mma_supports(wtype, ga)) return launch_gemv_mma(wtype, (const uint8_t*)t, nullptr, ga, g.stream);
     }
     return launch_gemv(wtype, ga, g.stream);
 }

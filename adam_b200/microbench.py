@@ -40,7 +40,7 @@ def _weights(gpu, A, t, N, K, copies, tile=False):
     gpu.map_create_typed(1, dt, 1, copies * N * K)
     for c in range(copies):
         gpu.upload_gguf_blocks(1, t, c * N * K, raw)
-        if tile and t == 2 and N % 16 == 0 and K % 64 == 0:
+        if tile and N % 16 == 0 and K % (64 if t == 2 else 256) == 0:
             gpu.tile_tensor(1, c * N * K, N, K)
     return rng
 
@@ -72,7 +72,7 @@ def run_shape(gpu, A, t, N, K, B=1, target_bytes=600e6, reps=5, tile=False):
     gpu.graph_launch(gid2, 2)
     gpu.batch_begin(); gpu.timer_begin(); gpu.graph_launch(gid2, 1); ms2 = gpu.timer_end(); gpu.batch_end()
     peak = _peak()
-    out = dict(type="Q4_0" if t == 2 else "Q4_K", kernel="tensor-core (tiled)" if tile and t == 2 else "generic", N=N, K=K, B=B, copies=copies, bytes_per_launch=int(alg),
+    out = dict(type="Q4_0" if t == 2 else "Q4_K", kernel="tensor-core (tiled)" if tile else "generic", N=N, K=K, B=B, copies=copies, bytes_per_launch=int(alg),
                us_per_launch=round(best * 1e3 / copies, 3), GBs=round(gbs, 1), frac_of_measured=round(gbs / peak, 3),
                frac_of_8TBs=round(gbs / 8000, 3), warm_us_per_launch=round(ms2 * 1e3 / 20, 3))
     gpu.graph_destroy(gid); gpu.graph_destroy(gid2)

@@ -141,7 +141,7 @@ class ADAMEngineTP(ADAMEngine):
     ``torch.distributed`` process group (NCCL) and the library on this rank's GPU."""
 
     def __init__(self, gpu, cfg, tensors, rank: int, world: int, group=None, use_graph: bool = True,
-                 presharded: bool = False, **kw):
+                 presharded: bool = False, collectives: bool = True, **kw):
         """``cfg`` is the whole model's configuration.  ``tensors`` is the whole model (each rank
         keeps its slice) or, with ``presharded``, already this rank's tensors as ``shard_tensors``
         would return them (``token_embd.weight`` whole, ``output.weight`` = the vocabulary shard)."""
@@ -156,6 +156,7 @@ class ADAMEngineTP(ADAMEngine):
             local_cfg, local_t = shard_tensors(cfg, tensors, self.plan)
         self._group = group
         self._world = world
+        self._collectives = collectives and world > 1      # False: time one shard's kernels alone (results are partial sums)
         self._use_graph = use_graph
         self._graphs: Dict[tuple, object] = {}
         self._eager_steps: Dict[tuple, int] = {}
@@ -184,7 +185,7 @@ class ADAMEngineTP(ADAMEngine):
         B, L2, W = self._batch, 2 * self.cfg.n_layer, self._world
         for part in range(self._n_parts):
             self._check(self._lib.adam_b200_decoder_step_part(self._dec, part, flags), "adam_b200_decoder_step_part")
-            if W == 1:
+            if not self._collectives:
                 continue
             if part < L2:
                 dist.all_reduce(self._proj[:B], group=self._group)

@@ -79,6 +79,8 @@ def main():
     ap.add_argument("--prompt", type=int, default=16)
     ap.add_argument("--type", type=int, default=gb.GGML_TYPE_Q4_K)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--shard-of", type=int, default=0, help="one process: run rank 0's shard of an N-way split without collectives "
+                                                            "(kernel time of a shard; the outputs are partial sums)")
     a = ap.parse_args()
     rank, local_rank, world = dist_env()
     import torch
@@ -92,10 +94,11 @@ def main():
     if a.layers:
         cfg = with_layers(cfg, a.layers)
     gpu = A.init()
-    plan = shard_plan(cfg, rank, world, a.type)
+    tp_world = a.shard_of if (a.shard_of and world == 1) else world
+    plan = shard_plan(cfg, rank, tp_world, a.type)
     tensors = build_shard(torch, gpu, cfg, plan, a.type, seed=100 + rank)
     kv_cap = a.prompt + a.warmup + a.steps + 8
-    eng = ADAMEngineTP(gpu, cfg, tensors, rank, world, presharded=True, use_graph=not a.no_graph,
+    eng = ADAMEngineTP(gpu, cfg, tensors, rank, tp_world, presharded=True, use_graph=not a.no_graph, collectives=(tp_world == world),
                        kv_cap=kv_cap, max_batch=a.batch, kv_dtype="f16")
     del tensors
     prompts = [list(map(int, np.random.default_rng(b).integers(0, cfg.n_vocab, a.prompt))) for b in range(a.batch)]
@@ -132,7 +135,7 @@ def main():
         ms_tok = ms / a.steps
         print(json.dumps({"metric": "decode tok/s (Gemma-3-27B-shape, tensor parallel)", "value": a.batch * a.steps / (ms * 1e-3), "unit": "tok/s",
                           "n_gpus": world, "steps": a.steps, "ms_per_step": ms_tok, "batch": a.batch, "n_layer": cfg.n_layer,
-                          "weights": "Q4_K" if a.type == gb.GGML_TYPE_Q4_K else "Q4_0", "parallelism": f"tp{world}",
+                          "weights": "Q4_K" if a.type == gb.GGML_TYPE_Q4_K else "Q4_0", "parallelism": f"tp{tp_world}" + ("" if tp_world == world else " (one shard, no collectives)"),
                           "weight_bytes_per_rank_per_step": int(w_bytes), "GBs_per_gpu": w_bytes / (ms_tok * 1e-3) / 1e9,
                           "collectives_per_step": 2 * cfg.n_layer + 2 if world > 1 else 0, "graph": graph_used, "device_error": int(err),
                           "data": "synthetic random blocks"}))

@@ -124,6 +124,19 @@ def test_tensor_core_path_at_offset_and_bad_shapes(gpu):
         gpu.tile_tensor(WT, 32 * 6, 96, 96)                  # cols not a multiple of 64
 
 
+@pytest.mark.parametrize("N,K,B", [(5376, 5376, 1), (512, 21504, 1), (2048, 4096, 1), (16, 256, 1), (48, 768, 2), (64, 1024, 3),
+                                   (1024, 5376, 4), (128, 2816, 7)])
+def test_q4_k_gemv_tensor_core_path(gpu, N, K, B):
+    rng = np.random.default_rng(N * 5 + K + B)
+    raw = gb.random_q4_k_blocks(rng, N, K)
+    x = rng.standard_normal((B, K), dtype=np.float32)
+    x[0, :5] = [1e-7, -3e4, 2.5e4, 0.0, -1e-3]
+    y = _gemv(gpu, 12, raw, N, K, x, tile=True)
+    _check(y, q4_blocks.dequant(raw.reshape(-1), 12, N, K), x)
+    y0 = _gemv(gpu, 12, raw, N, K, x, tile=False)
+    assert np.abs(y - y0).max() < 1e-4 * np.abs(y0).max()
+
+
 @pytest.mark.parametrize("N,K", [(5376, 5376), (512, 21504), (2048, 4096), (3, 256), (9, 768), (64, 1024)])
 def test_q4_k_gemv(gpu, N, K):
     rng = np.random.default_rng(N * 17 + K)
