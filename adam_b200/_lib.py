@@ -112,6 +112,10 @@ _SIGS = {
     "adam_b200_decoder_step_part": (c_int, [u32, u32, u32]),
     "adam_b200_decoder_buffer_ptr": (c_int, [u32, u32, POINTER(u64), POINTER(u64)]),
     "adam_b200_set_stream": (c_int, [u64]),
+    "adam_b200_ar_create": (c_int, [u32, u32, u64, POINTER(u32), c_void_p]),
+    "adam_b200_ar_open": (c_int, [u32, c_void_p]),
+    "adam_b200_ar_allreduce": (c_int, [u32, u64, u32]),
+    "adam_b200_ar_destroy": (c_int, [u32]),
     "adam_b200_decoder_read_state": (c_int, [u32, c_void_p, c_void_p]),
     "adam_b200_decoder_read_log": (c_int, [u32, u32, u32, u32, c_void_p]),
     "adam_b200_decoder_read_logits": (c_int, [u32, u32, c_void_p]),

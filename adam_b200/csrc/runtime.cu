@@ -239,12 +239,13 @@ extern "C" int adamah_init_ex(uint64_t, uint64_t) {
 }
 extern "C" int adamah_init(void) { return adamah_init_ex(0, 0); }
 
-namespace ab { void decoder_destroy_all(); void plans_clear_all(); void tiled_drop_map(uint32_t map_id); }
+namespace ab { void decoder_destroy_all(); void plans_clear_all(); void tiled_drop_map(uint32_t map_id); void ar_destroy_all(); }
 
 extern "C" void adamah_shutdown(void) {
     if (!g.inited) return;
     cudaSetDevice(g.device);
     cudaStreamSynchronize(g.stream);
+    ar_destroy_all();
     decoder_destroy_all();
     plans_clear_all();
     tiled_drop_map(0xFFFFFFFFu);

@@ -141,7 +141,7 @@ class ADAMEngineTP(ADAMEngine):
     ``torch.distributed`` process group (NCCL) and the library on this rank's GPU."""
 
     def __init__(self, gpu, cfg, tensors, rank: int, world: int, group=None, use_graph: bool = True,
-                 presharded: bool = False, collectives: bool = True, **kw):
+                 presharded: bool = False, collectives: bool = True, allreduce: str = "p2p", **kw):
         """``cfg`` is the whole model's configuration.  ``tensors`` is the whole model (each rank
         keeps its slice) or, with ``presharded``, already this rank's tensors as ``shard_tensors``
         would return them (``token_embd.weight`` whole, ``output.weight`` = the vocabulary shard)."""
@@ -166,6 +166,9 @@ class ADAMEngineTP(ADAMEngine):
         gpu.set_stream(self._stream.cuda_stream)
         super().__init__(gpu, local_cfg, local_t, tp_rank=rank, tp_size=world, **kw)
         self._n_parts = int(self._lib.adam_b200_decoder_n_parts(self._dec))
+        self._ar = None
+        if self._collectives and allreduce == "p2p":
+            self._ar = self._open_peer_allreduce(cfg.n_embd * self._max_batch * 4)
         dev = f"cuda:{gpu.device_index}"
         mb = self._max_batch
         self._proj = torch.as_tensor(_DeviceArray(self._buf(0), mb * cfg.n_embd, "<f4"), device=dev).view(mb, cfg.n_embd)
@@ -178,6 +181,29 @@ class ADAMEngineTP(ADAMEngine):
         self._check(self._lib.adam_b200_decoder_buffer_ptr(self._dec, which, ctypes.byref(p), ctypes.byref(n)), "adam_b200_decoder_buffer_ptr")
         return int(p.value)
 
+    def _open_peer_allreduce(self, max_bytes: int):
+        """The library's one-shot all-reduce over peer memory: exchange the CUDA IPC handles of every
+        rank's staging area and flags, map them, and line the ranks up once before first use.
+        Returns the communicator id, or None when peer mapping is not possible (NCCL is used then)."""
+        import ctypes
+        import torch.distributed as dist
+        cid = ctypes.c_uint32(0)
+        mine = ctypes.create_string_buffer(128)
+        rc = self._lib.adam_b200_ar_create(self._world, self.plan.rank, max_bytes, ctypes.byref(cid), mine)
+        handles = [None] * self._world
+        dist.all_gather_object(handles, bytes(mine.raw) if rc == 0 else None, group=self._group)
+        ok = rc == 0 and all(h is not None for h in handles)
+        if ok:
+            blob = ctypes.create_string_buffer(b"".join(handles), 128 * self._world)
+            ok = self._lib.adam_b200_ar_open(int(cid.value), blob) == 0
+        flags = [None] * self._world
+        dist.all_gather_object(flags, bool(ok), group=self._group)          # also the barrier before first use
+        if all(flags):
+            return int(cid.value)
+        if rc == 0:
+            self._lib.adam_b200_ar_destroy(int(cid.value))
+        return None
+
     def _one_step(self, flags: int):
         """All parts of one token step with the collectives between them, on the current stream."""
         import torch.distributed as dist
@@ -188,7 +214,10 @@ class ADAMEngineTP(ADAMEngine):
             if not self._collectives:
                 continue
             if part < L2:
-                dist.all_reduce(self._proj[:B], group=self._group)
+                if self._ar is not None:
+                    self._check(self._lib.adam_b200_ar_allreduce(self._ar, self._proj.data_ptr(), B * self.full_cfg.n_embd), "adam_b200_ar_allreduce")
+                else:
+                    dist.all_reduce(self._proj[:B], group=self._group)
             elif part == L2 and (flags & STEP_LM):
                 # (value, global id) of every rank's best row; the best value wins, ties go to the lower id
                 gid = self._tok[:B] + self.plan.vocab.start
@@ -228,5 +257,8 @@ class ADAMEngineTP(ADAMEngine):
 
     def close(self):
         self._graphs.clear()
+        if self._ar is not None:
+            self._lib.adam_b200_ar_destroy(self._ar)
+            self._ar = None
         super().close()
         self.gpu.set_stream(0)

@@ -79,6 +79,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=16)
     ap.add_argument("--type", type=int, default=gb.GGML_TYPE_Q4_K)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"], help="library peer-memory all-reduce or torch.distributed NCCL")
     ap.add_argument("--shard-of", type=int, default=0, help="one process: run rank 0's shard of an N-way split without collectives "
                                                             "(kernel time of a shard; the outputs are partial sums)")
     a = ap.parse_args()
@@ -98,7 +99,7 @@ def main():
     plan = shard_plan(cfg, rank, tp_world, a.type)
     tensors = build_shard(torch, gpu, cfg, plan, a.type, seed=100 + rank)
     kv_cap = a.prompt + a.warmup + a.steps + 8
-    eng = ADAMEngineTP(gpu, cfg, tensors, rank, tp_world, presharded=True, use_graph=not a.no_graph, collectives=(tp_world == world),
+    eng = ADAMEngineTP(gpu, cfg, tensors, rank, tp_world, presharded=True, use_graph=not a.no_graph, collectives=(tp_world == world), allreduce=a.allreduce,
                        kv_cap=kv_cap, max_batch=a.batch, kv_dtype="f16")
     del tensors
     prompts = [list(map(int, np.random.default_rng(b).integers(0, cfg.n_vocab, a.prompt))) for b in range(a.batch)]
@@ -129,6 +130,7 @@ def main():
                             + 3 * lc.n_ff * cfg.n_embd) + lc.n_vocab * cfg.n_embd
     w_bytes = w_elems * block_bytes(a.type) // block_elems(a.type)
     graph_used = bool(eng._graphs)
+    ar_used = eng._ar is not None
     eng.close()
     gpu.shutdown()
     if rank == 0:
@@ -137,7 +139,7 @@ def main():
                           "n_gpus": world, "steps": a.steps, "ms_per_step": ms_tok, "batch": a.batch, "n_layer": cfg.n_layer,
                           "weights": "Q4_K" if a.type == gb.GGML_TYPE_Q4_K else "Q4_0", "parallelism": f"tp{tp_world}" + ("" if tp_world == world else " (one shard, no collectives)"),
                           "weight_bytes_per_rank_per_step": int(w_bytes), "GBs_per_gpu": w_bytes / (ms_tok * 1e-3) / 1e9,
-                          "collectives_per_step": 2 * cfg.n_layer + 2 if world > 1 else 0, "graph": graph_used, "device_error": int(err),
+                          "collectives_per_step": 2 * cfg.n_layer + 2 if world > 1 else 0, "graph": graph_used, "allreduce": ("p2p" if ar_used else "nccl") if world > 1 else None, "device_error": int(err),
                           "data": "synthetic random blocks"}))
     if world > 1:
         dist.barrier()

@@ -251,6 +251,20 @@ int map_matvec_argmax_t_xq4_static_dev(uint32_t map_act, uint32_t map_wt, uint32
  * that stream are ordered with the library's.  Synchronises the stream in use first. */
 int adam_b200_set_stream(uint64_t stream);
 
+/* ---- one-shot all-reduce over peer memory (tensor-parallel decode) -----------------
+ * Sum of a small fp32 buffer over 2..8 ranks (one process per GPU of one node): every rank
+ * stages its values in its own memory, raises a flag in every peer's memory and, once all
+ * flags of the call are up (bounded wait: bit value 2 of adam_b200_device_error on expiry,
+ * the kernel still ends), adds the peers' staged values in rank order.  ar_create returns
+ * this rank's two 64-byte CUDA IPC handles; the caller gathers all ranks' (world x 128 bytes,
+ * rank order), passes them to ar_open and synchronises the ranks once before the first
+ * all-reduce.  All ranks issue the same sequence of calls with the same sizes.  No counterpart
+ * in the reference (it has no multi-GPU path). */
+int adam_b200_ar_create(uint32_t world, uint32_t rank, uint64_t max_bytes, uint32_t* id_out, void* handles_out);
+int adam_b200_ar_open(uint32_t id, const void* all_handles);
+int adam_b200_ar_allreduce(uint32_t id, uint64_t buf, uint32_t n_floats);     /* in place, on the library stream */
+int adam_b200_ar_destroy(uint32_t id);
+
 /* ---- fused decoder ------------------------------------------------------------
  * Runs the reference engine's per-token loop (adam/models/engine.py:2971-3706
  * `_forward`, generate loop :3810-3944) for a batch of sequences as one CUDA

@@ -130,18 +130,20 @@ def _free_port():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("ggml_type", [gb.GGML_TYPE_Q4_0, gb.GGML_TYPE_Q4_K])
-def test_two_ranks_match_the_oracle(ggml_type):
-    """Two NCCL ranks (needs two GPUs): greedy ids equal the rank-ordered oracle's, logits within 1e-3."""
+@pytest.mark.parametrize("ggml_type,allreduce", [(gb.GGML_TYPE_Q4_0, "p2p"), (gb.GGML_TYPE_Q4_K, "p2p"), (gb.GGML_TYPE_Q4_K, "nccl")])
+def test_two_ranks_match_the_oracle(ggml_type, allreduce):
+    """Two ranks (needs two GPUs), projections summed by the library's peer-memory all-reduce or by NCCL:
+    greedy ids equal the rank-ordered oracle's, logits within 1e-3."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "tp_rank_main.py"), str(int(ggml_type))]
+           "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "tp_rank_main.py"), str(int(ggml_type)), allreduce]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
     assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-3000:])
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
     assert res["ids_equal"], res
     assert res["logit_rel_err"] < 1e-3
     assert res["graph_used"] and res["device_error"] == 0
+    assert res["p2p_allreduce"] == (allreduce == "p2p")

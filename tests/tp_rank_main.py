@@ -14,6 +14,7 @@ sys.path.insert(0, ROOT)
 
 def main():
     ggml_type = int(sys.argv[1])
+    allreduce = sys.argv[2] if len(sys.argv) > 2 else "p2p"
     rank, local_rank, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
     import torch
     import torch.distributed as dist
@@ -31,7 +32,8 @@ def main():
     prompt = synth.random_prompt(cfg.n_vocab, 9, seed=4)
     n_gen = 12
     gpu = A.init()
-    eng = ADAMEngineTP(gpu, cfg, tensors, rank, world, kv_cap=64, kv_dtype="f32")
+    eng = ADAMEngineTP(gpu, cfg, tensors, rank, world, kv_cap=64, kv_dtype="f32", allreduce=allreduce)
+    ar_used = eng._ar is not None
     toks, _ = eng.generate(prompt, GenerationConfig(max_tokens=n_gen, top_k=1, temperature=0.0, eos_token_ids=()))
     graph_used = bool(eng._graphs)
     # teacher-forced logits of this rank's vocabulary shard for the whole sequence
@@ -51,7 +53,7 @@ def main():
         ref_ids = [int(r.argmax()) for r in ref_logits[len(prompt) - 1:]]
         rel = float(np.abs(logits - ref_logits).max() / np.abs(ref_logits).max())
         print(json.dumps({"ids_equal": toks == ref_ids, "tokens": toks, "ref": ref_ids, "logit_rel_err": rel,
-                          "graph_used": graph_used, "device_error": int(err)}))
+                          "graph_used": graph_used, "p2p_allreduce": ar_used, "device_error": int(err)}))
     dist.barrier()
     dist.destroy_process_group()
 
