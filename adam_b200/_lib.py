@@ -84,6 +84,10 @@ _SIGS = {
     "map_broadcast_dev": (c_int, [u32] * 6),
     "map_argmax_dev": (c_int, [u32] * 4),
     "map_resolve_idx_dev": (c_int, [u32] * 5),
+    "map_topk_dev": (c_int, [u32] * 6),
+    "map_topp_dev": (c_int, [u32] * 4 + [ctypes.c_float, ctypes.c_float]),
+    "map_sample_categorical_dev": (c_int, [u32] * 6),
+    "map_repeat_penalty_dev": (c_int, [u32] * 4 + [ctypes.c_float]),
     "map_matvec_argmax_t_xq4_dev": (c_int, [u32] * 10),
     "map_matvec_argmax_t_xq4_static_dev": (c_int, [u32] * 10),
     "adamah_register_decode_plan": (c_int, [u32, POINTER(DecodePlanOp), u32]),
@@ -130,7 +134,7 @@ _SIGS = {
 OFF_PATH_SYMBOLS = [
     "map_op1", "map_op2", "map_matmul", "map_softmax", "map_layernorm", "map_broadcast", "map_reduce",
     "map_matmul_dev", "map_softmax_dev", "map_softmax_abs_dev", "map_attn_softmax_abs_dev", "map_layernorm_dev",
-    "map_reduce_dev", "map_topk_dev", "map_topp_dev", "map_fma_dev", "map_matmul_t_x_dev", "map_matmul_x_dev",
+    "map_reduce_dev", "map_fma_dev", "map_matmul_t_x_dev", "map_matmul_x_dev",
     "map_matmul_xq4_dev", "map_matmul_t_xq8_dev", "map_matmul_xq8_dev", "map_row_gather_xq8_dev",
 ]
 

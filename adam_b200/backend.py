@@ -43,6 +43,8 @@ class Adamah:
         self._has_map_scatter_q4_packed_contiguous = True
         self._has_map_matvec_argmax_t_xq4_dev = True
         self._has_map_resolve_idx_dev = True
+        self._has_map_sample_categorical_dev = True
+        self._has_map_repeat_penalty_dev = True
         self._has_map_upload_gguf_blocks = True
         self._has_decoder = True
         self._is_integrated_gpu = False
@@ -246,6 +248,19 @@ class Adamah:
 
     def map_resolve_idx_dev(self, map_id, base_locs_handle, locs_sel_handle, locs_dst_handle, n):
         self._check(self._lib.map_resolve_idx_dev(map_id, base_locs_handle, locs_sel_handle, locs_dst_handle, n), "map_resolve_idx_dev")
+
+    def map_topk_dev(self, map_id, locs_src_handle, locs_idx_dst_handle, locs_val_dst_handle, n, k):
+        self._check(self._lib.map_topk_dev(map_id, locs_src_handle, locs_idx_dst_handle, locs_val_dst_handle, n, k), "map_topk_dev")
+
+    def map_topp_dev(self, map_id, locs_src_handle, locs_dst_handle, n, temperature, top_p):
+        self._check(self._lib.map_topp_dev(map_id, locs_src_handle, locs_dst_handle, n, float(temperature), float(top_p)), "map_topp_dev")
+
+    def map_sample_categorical_dev(self, map_id, locs_idx_handle, locs_prob_handle, rand_loc_handle, dst_loc_handle, n):
+        self._check(self._lib.map_sample_categorical_dev(map_id, locs_idx_handle, locs_prob_handle, rand_loc_handle, dst_loc_handle, n),
+                    "map_sample_categorical_dev")
+
+    def map_repeat_penalty_dev(self, map_id, locs_src_handle, token_ids_handle, n_ids, penalty):
+        self._check(self._lib.map_repeat_penalty_dev(map_id, locs_src_handle, token_ids_handle, n_ids, float(penalty)), "map_repeat_penalty_dev")
 
     def map_matvec_argmax_t_xq4_dev(self, map_act, map_wt, locs_a_handle, locs_b_handle, locs_idx_tmp_handle, locs_val_tmp_handle,
                                     locs_dst_handle, K, N, rows_per_group=256):

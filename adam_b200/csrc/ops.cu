@@ -271,6 +271,123 @@ __global__ void k_argmax(float* __restrict__ m, uint64_t n_el, const uint32_t* _
     }
 }
 
+// ---- sampled-decoding tail (map_topk.comp, map_topp.comp, map_sample_categorical.comp,
+// map_repeat_penalty.comp; adamah.c:6787, :6978, :7095, :7286).  Small inputs (at most 64
+// candidates after top-k), one CTA each. ----
+
+// The k largest of n values with their indices into the loc list, largest first, ties to the
+// lower index, NaN as -FLT_MAX; index stored as float32.  k <= 64.
+__global__ void k_topk(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ ls, const uint32_t* __restrict__ li,
+                       const uint32_t* __restrict__ lv, uint32_t n, uint32_t k, uint32_t* err) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    __shared__ int top[64];
+    for (uint32_t out = 0; out < k; ++out) {
+        float bv = -3.402823466e+38f; int bi = -1;
+        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+            bool taken = false;
+            for (uint32_t j = 0; j < out; ++j) taken |= (top[j] == (int)i);
+            if (taken) continue;
+            const uint64_t a = ls[i];
+            if (a >= n_el) { atomicOr(err, DEVERR_OOB_MAP); continue; }
+            float v = m[a];
+            if (!(v == v)) v = -3.402823466e+38f;
+            if (better(v, (int)i, bv, bi)) { bv = v; bi = (int)i; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) if (better(sv[w], si[w], bv, bi)) { bv = sv[w]; bi = si[w]; }
+            top[out] = bi;
+            const uint64_t di = li[out], dv = lv[out];
+            if (di >= n_el || dv >= n_el) atomicOr(err, DEVERR_OOB_MAP);
+            else { m[di] = (float)(bi < 0 ? 0 : bi); m[dv] = bi < 0 ? -3.402823466e+38f : bv; }
+        }
+        __syncthreads();
+    }
+}
+
+// Soft-max with temperature over n <= 64 candidates (already sorted by the caller), nucleus cut at
+// top_p, renormalised; the rest gets probability 0.  Serial, like the shader.
+__global__ void k_topp(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ ls, const uint32_t* __restrict__ ld,
+                       uint32_t n, float temperature, float top_p, uint32_t* err) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const float NEG = -3.402823466e+38f;
+    float lg[64], pr[64];
+    for (uint32_t i = 0; i < n; ++i) {
+        const uint64_t a = ls[i];
+        if (a >= n_el || ld[i] >= n_el) { atomicOr(err, DEVERR_OOB_MAP); return; }
+        float v = m[a];
+        if (!(v == v) || isinf(v)) v = NEG;
+        lg[i] = v;
+    }
+    const float temp = fmaxf(temperature, 1e-6f);
+    const float keep_p = fminf(fmaxf(top_p, 0.f), 1.f);
+    float mx = NEG;
+    for (uint32_t i = 0; i < n; ++i) if (lg[i] > mx) mx = lg[i];
+    if (mx == NEG) { for (uint32_t i = 0; i < n; ++i) m[ld[i]] = 0.f; return; }
+    float sum = 0.f;
+    for (uint32_t i = 0; i < n; ++i) {
+        if (lg[i] == NEG) { pr[i] = 0.f; continue; }
+        pr[i] = expf(__fdiv_rn(lg[i] - mx, temp));
+        sum += pr[i];
+    }
+    if (sum <= 0.f) { for (uint32_t i = 0; i < n; ++i) m[ld[i]] = (i == 0) ? 1.f : 0.f; return; }
+    for (uint32_t i = 0; i < n; ++i) pr[i] = __fdiv_rn(pr[i], sum);
+    uint32_t keep = 0;
+    float csum = 0.f;
+    for (uint32_t i = 0; i < n; ++i) {
+        csum += pr[i];
+        keep = i + 1;
+        if (keep_p >= 0.999999f || csum >= keep_p) break;
+    }
+    if (keep == 0 && n > 0) keep = 1;
+    float ks = 0.f;
+    for (uint32_t i = 0; i < keep; ++i) ks += pr[i];
+    if (ks <= 0.f) ks = 1.f;
+    for (uint32_t i = 0; i < n; ++i) m[ld[i]] = i < keep ? __fdiv_rn(pr[i], ks) : 0.f;
+}
+
+// Inverse-CDF draw: the first candidate whose running probability sum exceeds r * total.
+__global__ void k_sample_categorical(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ lidx, const uint32_t* __restrict__ lprob,
+                                     const uint32_t* __restrict__ lrand, const uint32_t* __restrict__ ldst, uint32_t n, uint32_t* err) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    if (lrand[0] >= n_el || ldst[0] >= n_el) { atomicOr(err, DEVERR_OOB_MAP); return; }
+    for (uint32_t i = 0; i < n; ++i) if (lidx[i] >= n_el || lprob[i] >= n_el) { atomicOr(err, DEVERR_OOB_MAP); return; }
+    auto prob = [&](uint32_t i) { float p = m[lprob[i]]; return (!(p == p) || isinf(p) || p < 0.f) ? 0.f : p; };
+    float total = 0.f;
+    for (uint32_t i = 0; i < n; ++i) total += prob(i);
+    if (!(total > 0.f)) { m[ldst[0]] = m[lidx[0]]; return; }
+    float r = m[lrand[0]];
+    if (!(r == r) || isinf(r)) r = 0.f;
+    r = fminf(fmaxf(r, 0.f), 0.99999994f);
+    const float target = r * total;
+    float acc = 0.f;
+    uint32_t chosen = n - 1;
+    for (uint32_t i = 0; i < n; ++i) {
+        acc += prob(i);
+        if (target < acc) { chosen = i; break; }
+    }
+    m[ldst[0]] = m[lidx[chosen]];
+}
+
+// logit[tok] = logit > 0 ? logit / penalty : logit * penalty for each listed token id.
+__global__ void k_repeat_penalty(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ llogit, uint32_t n_logit_locs,
+                                 const uint32_t* __restrict__ toks, uint32_t n_ids, float penalty, uint32_t* err) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_ids) return;
+    const uint32_t tok = toks[i];
+    if (tok >= n_logit_locs) { atomicOr(err, DEVERR_OOB_MAP); return; }
+    const uint64_t a = llogit[tok];
+    OOB(a, n_el, err);
+    const float v = m[a];
+    m[a] = v > 0.f ? __fdiv_rn(v, penalty) : v * penalty;
+}
+
 // map_resolve_idx.comp
 __global__ void k_resolve_idx(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ lbase, const uint32_t* __restrict__ lsel,
                               const uint32_t* __restrict__ ld, uint32_t n, uint32_t* err) {
@@ -510,6 +627,48 @@ extern "C" int map_argmax_dev(uint32_t map, uint32_t src_h, uint32_t dst_h, uint
     k_argmax<<<1, 1024, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(src_h), hlocs(dst_h), n, g.dev_err);
     DONE("map_argmax");
 }
+extern "C" int map_topk_dev(uint32_t map, uint32_t src_h, uint32_t idx_dst_h, uint32_t val_dst_h, uint32_t n, uint32_t k) {
+    REQ_READY();
+    Map* m = f32_map(map, "topk");
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (!n || !k) return ADAMAH_OK;
+    if (k > 64) return fail(ADAMAH_ERR_INVALID, "topk: k must be at most 64");
+    REQ_H(src_h, (uint64_t)n * 4); REQ_H(idx_dst_h, (uint64_t)k * 4); REQ_H(val_dst_h, (uint64_t)k * 4);
+    k_topk<<<1, 1024, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(src_h), hlocs(idx_dst_h), hlocs(val_dst_h), n, k, g.dev_err);
+    DONE("map_topk");
+}
+extern "C" int map_topp_dev(uint32_t map, uint32_t src_h, uint32_t dst_h, uint32_t n, float temperature, float top_p) {
+    REQ_READY();
+    Map* m = f32_map(map, "topp");
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (!n) return ADAMAH_OK;
+    if (n > 64) return fail(ADAMAH_ERR_INVALID, "topp: at most 64 candidates");
+    REQ_H(src_h, (uint64_t)n * 4); REQ_H(dst_h, (uint64_t)n * 4);
+    k_topp<<<1, 32, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(src_h), hlocs(dst_h), n, temperature, top_p, g.dev_err);
+    DONE("map_topp");
+}
+extern "C" int map_sample_categorical_dev(uint32_t map, uint32_t idx_h, uint32_t prob_h, uint32_t rand_h, uint32_t dst_h, uint32_t n) {
+    REQ_READY();
+    Map* m = f32_map(map, "sample_categorical");
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (!n) return ADAMAH_OK;
+    if (n > 64) n = 64;
+    REQ_H(idx_h, (uint64_t)n * 4); REQ_H(prob_h, (uint64_t)n * 4); REQ_H(rand_h, 4); REQ_H(dst_h, 4);
+    k_sample_categorical<<<1, 32, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(idx_h), hlocs(prob_h), hlocs(rand_h), hlocs(dst_h), n, g.dev_err);
+    DONE("map_sample_categorical");
+}
+// token_ids_h holds raw uint32 token ids (not locs); src_h lists the logits' locs.
+extern "C" int map_repeat_penalty_dev(uint32_t map, uint32_t src_h, uint32_t token_ids_h, uint32_t n_ids, float penalty) {
+    REQ_READY();
+    Map* m = f32_map(map, "repeat_penalty");
+    if (!m) return ADAMAH_ERR_NOT_FOUND;
+    if (!n_ids) return ADAMAH_OK;
+    if (n_ids > 64) return fail(ADAMAH_ERR_INVALID, "repeat_penalty: at most 64 token ids");
+    REQ_H(src_h, 4); REQ_H(token_ids_h, (uint64_t)n_ids * 4);
+    const uint32_t n_logit_locs = (uint32_t)(g.handles[src_h].nbytes / 4);
+    k_repeat_penalty<<<1, 64, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(src_h), n_logit_locs, hlocs(token_ids_h), n_ids, penalty, g.dev_err);
+    DONE("map_repeat_penalty");
+}
 extern "C" int map_resolve_idx_dev(uint32_t map, uint32_t base_h, uint32_t sel_h, uint32_t dst_h, uint32_t n) {
     REQ_READY();
     Map* m = f32_map(map, "resolve_idx");
@@ -677,8 +836,6 @@ OFFPATH(map_softmax_abs_dev, u32, u32, u32, u32, u32)
 OFFPATH(map_attn_softmax_abs_dev, u32, u32, u32, u32, u32, float, float)
 OFFPATH(map_layernorm_dev, u32, u32, u32, u32, u32, u32, u32, float)
 OFFPATH(map_reduce_dev, u32, u32, u32, u32, u32)
-OFFPATH(map_topk_dev, u32, u32, u32, u32, u32, u32)
-OFFPATH(map_topp_dev, u32, u32, u32, u32, float, float)
 OFFPATH(map_fma_dev, u32, u32, u32, u32, u32, u32)
 OFFPATH(map_matmul_t_x_dev, u32, u32, u32, u32, u32, u32, u32, u32, u32)
 OFFPATH(map_matmul_x_dev, u32, u32, u32, u32, u32, u32, u32, u32, u32)

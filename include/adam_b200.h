@@ -137,6 +137,15 @@ int map_broadcast_dev(uint32_t map, uint32_t op, uint32_t src_h, uint32_t scalar
 /* adamah.c:6875, :7210, :9699 */
 int map_argmax_dev(uint32_t map, uint32_t src_h, uint32_t dst_h, uint32_t n);
 int map_resolve_idx_dev(uint32_t map, uint32_t base_h, uint32_t sel_h, uint32_t dst_h, uint32_t n);
+/* Sampled-decoding tail (adamah.c:6978 map_topk_dev, :7095 map_topp_dev, :7286
+ * map_sample_categorical_dev, :6787 map_repeat_penalty_dev): the k <= 64 largest values and their
+ * indices (ties to the lower index), soft-max with temperature + nucleus cut over <= 64 sorted
+ * candidates, inverse-CDF draw from a uniform number stored in the map, and the repeat penalty on
+ * listed token ids (raw uint32 ids, not locs).  Indices travel as float32, like everything else. */
+int map_topk_dev(uint32_t map, uint32_t src_h, uint32_t idx_dst_h, uint32_t val_dst_h, uint32_t n, uint32_t k);
+int map_topp_dev(uint32_t map, uint32_t src_h, uint32_t dst_h, uint32_t n, float temperature, float top_p);
+int map_sample_categorical_dev(uint32_t map, uint32_t idx_h, uint32_t prob_h, uint32_t rand_h, uint32_t dst_h, uint32_t n);
+int map_repeat_penalty_dev(uint32_t map, uint32_t src_h, uint32_t token_ids_h, uint32_t n_ids, float penalty);
 int map_matvec_argmax_t_xq4_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h, uint32_t b_h,
                                 uint32_t idx_tmp_h, uint32_t val_tmp_h, uint32_t dst_h,
                                 uint32_t K, uint32_t N, uint32_t rows_per_group);
@@ -170,8 +179,6 @@ int map_softmax_abs_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
 int map_attn_softmax_abs_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, float, float);
 int map_layernorm_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, float);
 int map_reduce_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
-int map_topk_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
-int map_topp_dev(uint32_t, uint32_t, uint32_t, uint32_t, float, float);
 int map_fma_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
 int map_matmul_t_x_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
 int map_matmul_x_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);

@@ -321,7 +321,77 @@ def test_out_of_range_loc_is_reported_not_faulted(gpu):
 
 
 def test_off_path_symbols_return_invalid(gpu):
-    assert gpu._lib.map_topk_dev(0, 0, 0, 0, 0, 0) == -3
+    assert gpu._lib.map_fma_dev(0, 0, 0, 0, 0, 0) == -3
+
+
+def test_topk_reference_vector(gpu):
+    """tests/test_decode_primitives.py:32-47 (ties to the lower index, indices as float32)."""
+    _f32map(gpu, 3, 20, [-3.0, 5.5, 2.0, 5.5, 4.0, -1.0])
+    src, idx, val = _h(gpu, np.arange(6)), _h(gpu, [8, 9, 10]), _h(gpu, [12, 13, 14])
+    gpu.map_topk_dev(3, src, idx, val, 6, 3)
+    assert _read(gpu, 3, [8, 9, 10]).astype(np.int32).tolist() == [1, 3, 4]
+    assert np.allclose(_read(gpu, 3, [12, 13, 14]), [5.5, 5.5, 4.0], atol=1e-6)
+    # NaN counts as the lowest value; k beyond 64 is refused
+    _f32map(gpu, 3, 20, [np.nan, 1.0, np.nan, 0.5])
+    gpu.map_topk_dev(3, _h(gpu, np.arange(4)), idx, val, 4, 3)
+    assert _read(gpu, 3, [8, 9, 10]).astype(np.int32).tolist() == [1, 3, 0]
+    assert gpu._lib.map_topk_dev(3, src, idx, val, 6, 65) == -3
+    # against numpy on a larger input
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal(5000).astype(np.float32)
+    _f32map(gpu, 3, 5200, x)
+    idx, val = _h(gpu, 5000 + np.arange(64)), _h(gpu, 5100 + np.arange(64))
+    gpu.map_topk_dev(3, _h(gpu, np.arange(5000)), idx, val, 5000, 64)
+    order = np.argsort(-x, kind="stable")[:64]
+    assert _read(gpu, 3, 5000 + np.arange(64)).astype(np.int64).tolist() == order.tolist()
+    assert np.array_equal(_read(gpu, 3, 5100 + np.arange(64)), x[order])
+
+
+def test_topp_reference_vector(gpu):
+    """tests/test_decode_primitives.py:50-63."""
+    _f32map(gpu, 3, 16, [5.0, 4.0, 1.0, -1.0])
+    gpu.map_topp_dev(3, _h(gpu, [0, 1, 2, 3]), _h(gpu, [8, 9, 10, 11]), 4, 1.0, 0.9)
+    assert np.allclose(_read(gpu, 3, [8, 9, 10, 11]), [0.7310586, 0.26894143, 0.0, 0.0], atol=1e-5)
+    # temperature sharpens the soft-max before the cut: at 0.5 the first two candidates reach 0.99
+    gpu.map_topp_dev(3, _h(gpu, [0, 1, 2, 3]), _h(gpu, [8, 9, 10, 11]), 4, 0.5, 0.99)
+    z = np.exp((np.array([5.0, 4.0, 1.0, -1.0]) - 5.0) / 0.5)
+    assert np.allclose(_read(gpu, 3, [8, 9, 10, 11]), [z[0] / (z[0] + z[1]), z[1] / (z[0] + z[1]), 0.0, 0.0], atol=1e-6)
+    # the shader leaves its loop at the first candidate when top_p >= 0.999999 (map_topp.comp:78-81): kept as is
+    gpu.map_topp_dev(3, _h(gpu, [0, 1, 2, 3]), _h(gpu, [8, 9, 10, 11]), 4, 1.0, 1.0)
+    assert _read(gpu, 3, [8, 9, 10, 11]).tolist() == [1.0, 0.0, 0.0, 0.0]
+    assert gpu._lib.map_topp_dev(3, 1, 1, 65, 1.0, 0.9) == -3
+
+
+def test_resolve_idx_and_categorical_reference_vector(gpu):
+    """tests/test_decode_primitives.py:66-101: candidates 33 and 11 with p = (0.25, 0.75), r = 0.6 -> 11."""
+    vals = np.zeros(32, np.float32)
+    vals[4:8] = [11.0, 22.0, 33.0, 44.0]
+    vals[8:10] = [2.0, 0.0]
+    vals[16:18] = [0.25, 0.75]
+    vals[20] = 0.6
+    _f32map(gpu, 3, 32, vals)
+    base = gpu.upload_dev(np.array([4], np.uint32))[0]
+    gpu.map_resolve_idx_dev(3, base, _h(gpu, [8, 9]), _h(gpu, [12, 13]), 2)
+    gpu.map_sample_categorical_dev(3, _h(gpu, [12, 13]), _h(gpu, [16, 17]), _h(gpu, [20]), _h(gpu, [21]), 2)
+    assert _read(gpu, 3, [12, 13]).astype(np.int32).tolist() == [33, 11]
+    assert int(_read(gpu, 3, [21])[0]) == 11
+    # r below the first probability picks the first candidate; all-zero probabilities fall back to it too
+    gpu.scatter(3, np.array([20], np.uint32), np.array([0.1], np.float32))
+    gpu.map_sample_categorical_dev(3, _h(gpu, [12, 13]), _h(gpu, [16, 17]), _h(gpu, [20]), _h(gpu, [21]), 2)
+    assert int(_read(gpu, 3, [21])[0]) == 33
+    gpu.map_sample_categorical_dev(3, _h(gpu, [12, 13]), _h(gpu, [30, 31]), _h(gpu, [20]), _h(gpu, [21]), 2)
+    assert int(_read(gpu, 3, [21])[0]) == 33
+
+
+def test_repeat_penalty(gpu):
+    """map_repeat_penalty.comp: positive logits are divided, the others multiplied; ids index the loc list."""
+    _f32map(gpu, 3, 8, [2.0, -2.0, 0.0, 4.0, 1.0, 1.0, 1.0, 1.0])
+    ids = gpu.upload_dev(np.array([0, 1, 3], np.uint32))[0]
+    gpu.map_repeat_penalty_dev(3, _h(gpu, np.arange(8)), ids, 3, 2.0)
+    assert _read(gpu, 3, np.arange(8)).tolist() == [1.0, -4.0, 0.0, 2.0, 1.0, 1.0, 1.0, 1.0]
+    bad = gpu.upload_dev(np.array([99], np.uint32))[0]
+    gpu.map_repeat_penalty_dev(3, _h(gpu, np.arange(8)), bad, 1, 2.0)
+    assert gpu.device_error() & 1
 
 
 def test_native_stats_count_launches(gpu):
