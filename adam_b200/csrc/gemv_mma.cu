@@ -4,6 +4,7 @@
 namespace ab {
 
 constexpr int MMA_SMEM_LIMIT = 200 * 1024;
+constexpr int MMA_MAX_PASSES = 16;          // batch-row groups per launch (arg-max scratch is sized for it)
 
 typedef void (*MmaKernel)(const GemvArgs, const uint8_t*, const uint8_t*, int);
 
@@ -43,9 +44,11 @@ int launch_gemv_mma(int wt, const uint8_t* t0, const uint8_t* t1, GemvArgs a, cu
     int nb_max = 4;
     const int nw_min = chain_min_warps(a) <= 8 ? 8 : (chain_min_warps(a) <= 12 ? 12 : 16);
     while (nb_max > 1 && x_bytes(units, 4 * nb_max) + ring_bytes(wt, nw_min) > (size_t)MMA_SMEM_LIMIT) nb_max >>= 1;
-    for (int b0 = 0; b0 < a.B; b0 += nb_max) {
+    // One launch covers up to MMA_MAX_PASSES groups of nb_max batch rows (gridDim.y); more rows take more launches.
+    const int rows_per_launch = a.B <= nb_max ? a.B : nb_max * MMA_MAX_PASSES;
+    for (int b0 = 0; b0 < a.B; b0 += rows_per_launch) {
         GemvArgs g1 = a;
-        g1.B = (a.B - b0 < nb_max) ? a.B - b0 : nb_max;
+        g1.B = (a.B - b0 < rows_per_launch) ? a.B - b0 : rows_per_launch;
         if (a.x) g1.x = a.x + (size_t)b0 * a.ldx;
         if (a.h_in) g1.h_in = a.h_in + (size_t)b0 * a.ldx;
         if (a.add_src) g1.add_src = a.add_src + (size_t)b0 * a.ldx;
@@ -53,7 +56,10 @@ int launch_gemv_mma(int wt, const uint8_t* t0, const uint8_t* t1, GemvArgs a, cu
         if (a.y) g1.y = a.y + (size_t)b0 * a.ldy;
         if (a.out_tok) g1.out_tok = a.out_tok + b0;
         if (a.out_tok_f32) g1.out_tok_f32 = a.out_tok_f32 + b0;
-        const int ncol = g1.B == 1 ? 4 : (g1.B == 2 ? 8 : 16);
+        if (a.out_val) g1.out_val = a.out_val + b0;
+        const int rows_per_pass = g1.B < nb_max ? g1.B : nb_max;
+        const int n_pass = (g1.B + rows_per_pass - 1) / rows_per_pass;
+        const int ncol = rows_per_pass == 1 ? 4 : (rows_per_pass == 2 ? 8 : 16);
         g1.err = g.dev_err;
         const int vi = ncol == 4 ? 0 : (ncol == 8 ? 1 : 2);
         MmaKernel k = wt == WT_Q4_0 ? pick_kernel<WT_Q4_0>(vi, pair) : pick_kernel<WT_Q4_K>(vi, pair);
@@ -71,6 +77,7 @@ int launch_gemv_mma(int wt, const uint8_t* t0, const uint8_t* t1, GemvArgs a, cu
         int n_warps = 8, KS = 1, best_per_sm = 1;
         double best_cost = 1e300;
         const int nm = pair ? 2 : 1;
+        const int sm_eff = g.sm_count / n_pass > 0 ? g.sm_count / n_pass : 1;   // the row groups of a launch share the SMs
         for (int nw = nw_min; nw <= 16; nw += 4) {
             const size_t sm_bytes = x_bytes(units, ncol) + ring_bytes(wt, nw);
             if (sm_bytes > (size_t)MMA_SMEM_LIMIT) break;
@@ -85,10 +92,10 @@ int launch_gemv_mma(int wt, const uint8_t* t0, const uint8_t* t1, GemvArgs a, cu
                 if (nw % c || c > pairs) continue;
                 const int rgs = nw / c;                              // row groups per CTA pass
                 const long long n_sets = (n_rg + rgs - 1) / rgs;
-                long long ctas = (long long)g.sm_count * per_sm;
+                long long ctas = (long long)sm_eff * per_sm;
                 if (ctas > n_sets) ctas = n_sets;
                 const long long passes = (n_sets + ctas - 1) / ctas;            // per CTA
-                const long long resident = (ctas + g.sm_count - 1) / g.sm_count; // CTAs on the busiest SM
+                const long long resident = (ctas + sm_eff - 1) / sm_eff;           // CTAs on the busiest SM
                 const int slice = (pairs + c - 1) / c;
                 // a warp alone needs ~300 cycles per tile pair; an SM issues one per ~16 cycles
                 const double busy = (double)resident * nw * 16.0;
@@ -98,12 +105,12 @@ int launch_gemv_mma(int wt, const uint8_t* t0, const uint8_t* t1, GemvArgs a, cu
         }
         const size_t smem = x_bytes(units, ncol) + ring_bytes(wt, n_warps);
         const int n_sets = (n_rg + n_warps / KS - 1) / (n_warps / KS);
-        int grid = g.sm_count * best_per_sm;
+        int grid = sm_eff * best_per_sm;
         if (grid > n_sets) grid = n_sets;
         if (a.epi == EPI_ARGMAX && grid > gemv_max_grid()) grid = gemv_max_grid();
         if (a.max_grid > 0 && grid > a.max_grid) grid = a.max_grid;
         if (grid < 1) grid = 1;
-        if (launch_k(k, dim3(grid), dim3(n_warps * 32), smem, stream, g.pdl, g1, t0, t1, KS) != cudaSuccess)
+        if (launch_k(k, dim3(grid, n_pass), dim3(n_warps * 32), smem, stream, g.pdl, g1, t0, t1, KS) != cudaSuccess)
             return fail(ADAMAH_ERR_BACKEND, "gemv_mma: launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         count_launch();
     }

@@ -132,9 +132,28 @@ template <bool PAIR, int WT> struct MmaGeo {
 constexpr int mma_ring_bytes_per_warp(int wt) { return MMA_NSTAGE * (wt == WT_Q4_0 ? 6 * 576 : 4 * 640); }
 
 template <int NCOL, bool PAIR, int WT>
-__global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a, const uint8_t* __restrict__ t0, const uint8_t* __restrict__ t1, int KS) {
+__global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const uint8_t* __restrict__ t0, const uint8_t* __restrict__ t1, int KS) {
     constexpr int NI = NCOL == 16 ? 2 : 1;      // MMAs per block
     constexpr int NBR = NCOL / 4;               // batch rows staged
+    // blockIdx.y = group of NBR batch rows.  The groups of one launch are independent problems
+    // over the same weights; running them side by side keeps the SMs busy where one group alone
+    // is bound by latency, and the groups' reads of a tile arrive close together (L2 hits).
+    GemvArgs a = a_in;
+    {
+        const int r0 = (int)blockIdx.y * NBR;
+        a.B = min(NBR, a_in.B - r0);
+        if (r0) {
+            if (a.x) a.x += (size_t)r0 * a.ldx;
+            if (a.h_in) a.h_in += (size_t)r0 * a.ldx;
+            if (a.add_src) a.add_src += (size_t)r0 * a.ldx;
+            if (a.h_out) a.h_out += (size_t)r0 * a.ldx;
+            if (a.y) a.y += (size_t)r0 * a.ldy;
+            if (a.out_tok) a.out_tok += r0;
+            if (a.out_tok_f32) a.out_tok_f32 += r0;
+            if (a.out_val) a.out_val += r0;
+            if (a.part_val) { a.part_val += (size_t)r0 * gridDim.x; a.part_idx += (size_t)r0 * gridDim.x; a.ticket += blockIdx.y; }
+        }
+    }
     constexpr int NPR = NCOL / 2;               // column pairs per block (one pre-summed value each)
     constexpr int NM = PAIR ? 2 : 1;
     constexpr int CH = MmaGeo<PAIR, WT>::CH;

@@ -440,11 +440,12 @@ static int* s_tok = nullptr;
 
 int argmax_scratch(float** pv, int** pi, unsigned int** tk) {
     if (!s_part_val) {
-        size_t n = (size_t)8 * gemv_max_grid();
+        // per-CTA partial winners for up to 64 batch rows of one launch (16 row groups of 4), one ticket per group
+        size_t n = (size_t)64 * gemv_max_grid();
         if (cudaMalloc((void**)&s_part_val, n * 4) != cudaSuccess || cudaMalloc((void**)&s_part_idx, n * 4) != cudaSuccess ||
-            cudaMalloc((void**)&s_ticket, 4) != cudaSuccess || cudaMalloc((void**)&s_tok, 64 * 4) != cudaSuccess)
+            cudaMalloc((void**)&s_ticket, 16 * 4) != cudaSuccess || cudaMalloc((void**)&s_tok, 64 * 4) != cudaSuccess)
             return fail(ADAMAH_ERR_MEMORY, "out of device memory for argmax scratch");
-        cudaMemset(s_ticket, 0, 4);
+        cudaMemset(s_ticket, 0, 16 * 4);
     }
     *pv = s_part_val; *pi = s_part_idx; *tk = s_ticket;
     return ADAMAH_OK;
