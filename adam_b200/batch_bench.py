@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--token-prefill", action="store_true", help="consume the prompt one position per step instead of in 64-row chunks")
     a = ap.parse_args()
     import adam_b200 as A
     from adam_b200 import synth
@@ -39,7 +40,10 @@ def main():
     eng.begin(prompts, [kv_cap] * a.batch)
     gpu.batch_begin()
     gpu.timer_begin()
-    eng.step(a.prompt - 1, lm_head=False)
+    if a.token_prefill:
+        eng.step(a.prompt - 1, lm_head=False)
+    else:
+        eng.prefill(a.prompt - 1)
     pre_ms = gpu.timer_end()
     eng.step(max(3, a.warmup), lm_head=True)
     gpu.batch_end()
@@ -55,7 +59,7 @@ def main():
     w_bytes = synth.model_weight_elems(cfg) * 18 // 32
     print(json.dumps({"metric": "decode tok/s (Gemma-3-1B-shape Q4_0, batched)", "value": a.batch * a.steps / (ms * 1e-3), "unit": "tok/s",
                       "batch": a.batch, "steps": a.steps, "ms_per_step": ms / a.steps, "n_layer": cfg.n_layer,
-                      "prefill_tok_s": a.batch * (a.prompt - 1) / (pre_ms * 1e-3), "prefill": "token by token, all sequences per step",
+                      "prefill_tok_s": a.batch * (a.prompt - 1) / (pre_ms * 1e-3), "prefill": "token by token, all sequences per step" if a.token_prefill else "64 rows (sequences x positions) per pass",
                       "weight_bytes_per_step_if_read_once": int(w_bytes), "passes_over_weights_per_step": (a.batch + 3) // 4,
                       "kernel_launches_total": int(launches), "device_error": int(err), "data": "synthetic"}))
 

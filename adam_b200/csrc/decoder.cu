@@ -50,6 +50,9 @@ struct Decoder {
     void* kv_pool; size_t page_elems;
     float *hbuf[2], *qkv, *attn_out, *proj, *act, *logits; int h_final;
     float *part_o, *part_ml; unsigned int* attn_ticket; uint32_t n_splits;
+    int32_t *row_seq, *row_pos; // chunked prefill: (sequence, position) of every row of the chunk
+    uint32_t rows_cap;          // rows the activation buffers hold: max(max_batch, PREFILL_ROWS)
+    std::vector<uint32_t> hpos, hplen;   // host mirror of positions and prompt lengths (argument checks)
     uint32_t batch;             // active sequences
     bool use_tiles;             // build row-tiled weight copies for the tensor-core GEMV
     std::vector<uint32_t> free_pages;
@@ -59,6 +62,7 @@ struct Decoder {
 constexpr uint32_t MAX_DECODERS = 8;
 constexpr uint32_t ATTN_SPLIT = 256;       // fewest tokens an attention CTA takes before another CTA is added
 constexpr uint32_t ATTN_MAX_SPLITS = 64;   // attention CTAs per (sequence, kv head)
+constexpr uint32_t PREFILL_ROWS = 64;      // rows (sequences x tokens) of one prefill chunk
 static Decoder* g_dec[MAX_DECODERS];
 
 static Decoder* get_dec(uint32_t id) {
@@ -78,14 +82,17 @@ __device__ __forceinline__ void st_kv(__half* p, float v) { *p = __float2half_rn
 template <int WT>
 __global__ void k_embed(const WeightRef w, uint32_t n_embd, uint32_t n_vocab, float emb_scale,
                         const int32_t* __restrict__ pos, const int32_t* __restrict__ prompt_len, const int32_t* __restrict__ prompt_tok,
-                        uint32_t prompt_ld, const int32_t* __restrict__ cur_tok, float* __restrict__ h, uint32_t* err) {
+                        uint32_t prompt_ld, const int32_t* __restrict__ cur_tok, float* __restrict__ h,
+                        const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_pos, uint32_t* err) {
     pdl_launch_dependents();
     pdl_wait();
-    const uint32_t b = blockIdx.x;
-    const int32_t p = pos[b];
+    // decode: row = sequence at its own position; prefill: row r = (sequence row_seq[r], position row_pos[r])
+    const uint32_t r = blockIdx.x;
+    const uint32_t b = row_seq ? (uint32_t)row_seq[r] : r;
+    const int32_t p = row_pos ? row_pos[r] : pos[b];
     int32_t tok = (p < prompt_len[b]) ? prompt_tok[(size_t)b * prompt_ld + p] : cur_tok[b];
     if (tok < 0 || (uint32_t)tok >= n_vocab) { if (threadIdx.x == 0) atomicOr(err, DEVERR_BAD_TOKEN); tok = 0; }
-    float* out = h + (size_t)b * n_embd;
+    float* out = h + (size_t)r * n_embd;
     if (WT == WT_Q4_0) {
         const uint32_t nblk = n_embd / 32;
         const uint8_t* q = reinterpret_cast<const uint8_t*>(w.q + (size_t)tok * nblk);
@@ -122,38 +129,6 @@ __global__ void k_embed(const WeightRef w, uint32_t n_embd, uint32_t n_vocab, fl
             o[j]      = __fmul_rn(__fsub_rn(__fmul_rn((float)(byte & 15), s0), m0), emb_scale);
             o[32 + j] = __fmul_rn(__fsub_rn(__fmul_rn((float)(byte >> 4), s1), m1), emb_scale);
         }
-    }
-}
-
-// One CTA per sequence:  h' = h + (w_post ? rms(a)*w_post : a)   (when a != NULL)
-//                        n  = rms(h') * w_pre                   (when w_pre != NULL)
-// rms(x)*w is (x / sqrt(mean(x^2)+eps)) * w   (diag_inference.py:938-939).
-__global__ void k_norm_add_norm(float* __restrict__ h, const float* __restrict__ a, const float* __restrict__ w_post,
-                                const float* __restrict__ w_pre, float* __restrict__ n_out, uint32_t E, float eps) {
-    __shared__ float red[33];
-    const uint32_t b = blockIdx.x;
-    float* hb = h + (size_t)b * E;
-    if (a) {
-        const float* ab_ = a + (size_t)b * E;
-        float rms = 1.f;
-        if (w_post) {
-            float ss = 0.f;
-            for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) { const float x = ab_[i]; ss = fmaf(x, x, ss); }
-            ss = block_sum(ss, red);
-            rms = sqrtf(ss / (float)E + eps);
-        }
-        for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) {
-            const float t = w_post ? __fdiv_rn(ab_[i], rms) * w_post[i] : ab_[i];
-            hb[i] = hb[i] + t;
-        }
-    }
-    if (w_pre) {
-        float ss = 0.f;
-        for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) { const float x = hb[i]; ss = fmaf(x, x, ss); }
-        ss = block_sum(ss, red);
-        const float rms = sqrtf(ss / (float)E + eps);
-        float* nb = n_out + (size_t)b * E;
-        for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) nb[i] = __fdiv_rn(hb[i], rms) * w_pre[i];
     }
 }
 
@@ -278,7 +253,11 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
                                                    const int32_t* __restrict__ block_table, const int32_t* __restrict__ pos,
                                                    uint32_t n_head, uint32_t layer, uint32_t window, float scale, float cap,
                                                    float* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-                                                   unsigned int* __restrict__ ticket, uint32_t n_splits_max, uint32_t hpc, uint32_t* err) {
+                                                   unsigned int* __restrict__ ticket, uint32_t n_splits_max, uint32_t hpc,
+                                                   const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_pos, uint32_t* err) {
+    // row_seq / row_pos != NULL: chunked prefill.  Row b of qkv/out belongs to sequence row_seq[b] at position
+    // row_pos[b], and the keys and values of the whole chunk are already in the cache (k_kv_append ran before).
+    const bool appended = row_pos != nullptr;
     T* __restrict__ kv_pool = reinterpret_cast<T*>(kv_pool_v);
     constexpr int DPL = HD / 32;                // dims per lane
     constexpr int CP = ATTN_CP;                 // positions per chunk
@@ -299,7 +278,8 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // The block table is written by the host before the step's first kernel, so it can be
     // read ahead of the dependency wait: up to 128 entries sit in registers across the warp.
-    const int32_t* bt = block_table + (size_t)b * geo.max_pages;
+    const uint32_t sq = row_seq ? (uint32_t)row_seq[b] : b;
+    const int32_t* bt = block_table + (size_t)sq * geo.max_pages;
     const bool bt_regs = geo.max_pages <= 128;
     int32_t btr[4];
 #pragma unroll
@@ -326,8 +306,11 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     // Positions only change in the step's last kernel, and the step's first kernel is
     // launched with a full dependency on it, so the position, and everything in the cache
     // older than this step, can be read ahead of the wait as well.
+    // In chunked prefill the chunk's own keys and values were written by the kernel just before
+    // this one, so the wait comes first there.
+    if (appended) { pdl_launch_dependents(); pdl_wait(); }
     const uint32_t hd = HD, half = HD / 2, gs = hpc;
-    const int32_t p = pos[b];
+    const int32_t p = appended ? row_pos[b] : pos[b];
     const uint32_t seq = (uint32_t)p + 1;
     const uint32_t start = (window > 0 && seq > window) ? seq - window : 0;
     const uint32_t c_first = start / CP, n_chunks = (seq - 1) / CP - c_first + 1;
@@ -335,8 +318,8 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     if (split >= n_act) return;
     const uint32_t cpc = (n_chunks + n_act - 1) / n_act;
     const uint32_t c0 = min(c_first + split * cpc, c_first + n_chunks), c1 = min(c_first + n_chunks, c0 + cpc);
-    const uint32_t c_new = (uint32_t)p / CP;
-    const bool owner = c_new >= c0 && c_new < c1;
+    const uint32_t c_new = appended ? 0xFFFFFFFFu : (uint32_t)p / CP;      // chunk whose newest row comes from this step's q/k/v
+    const bool owner = !appended && c_new >= c0 && c_new < c1;
     float* s_q = sm;                            // [gs][hd]
     float* s_kn = s_q + gs * hd;                // [hd] newest key (as stored)
     float* s_vn = s_kn + hd;                    // [hd] newest value (as stored)
@@ -392,8 +375,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         cs[j] = i < half ? ct[i] : 1.f;
         sn[j] = i < half ? st[i] : 0.f;
     }
-    pdl_launch_dependents();
-    pdl_wait();             // this step's q/k/v rows come from the previous kernel
+    if (!appended) { pdl_launch_dependents(); pdl_wait(); }     // this step's q/k/v rows come from the previous kernel
     const float* row_q = qkv + (size_t)b * qkv_ld + (size_t)head0 * hd;
     const float* row_k = qkv + (size_t)b * qkv_ld + (size_t)n_head * hd + (size_t)kvh * hd;
     const float* row_v = row_k + (size_t)geo.n_kv * hd;
@@ -646,6 +628,79 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     if (tid == 0) *tkt = 0u;
 }
 
+// Chunked prefill: QK-norm + RoPE of the key row and append of key and value to the paged
+// cache for every row of the chunk, one warp per (row, kv head, K|V); the same arithmetic as
+// the key/value part of k_attention.
+template <typename T, int HD>
+__global__ void __launch_bounds__(256) k_kv_append(const float* __restrict__ qkv, uint32_t qkv_ld, const float* __restrict__ k_norm, float eps,
+                                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t, uint32_t n_pos,
+                                                   void* __restrict__ kv_pool_v, KvGeom geo, const int32_t* __restrict__ block_table,
+                                                   const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_pos,
+                                                   uint32_t n_rows, uint32_t n_head, uint32_t layer, uint32_t* err) {
+    T* __restrict__ kv_pool = reinterpret_cast<T*>(kv_pool_v);
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t lane = threadIdx.x & 31, w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (w >= n_rows * geo.n_kv * 2) return;
+    const uint32_t kv = w & 1u, kvh = (w >> 1) % geo.n_kv, r = (w >> 1) / geo.n_kv;
+    const uint32_t sq = (uint32_t)row_seq[r];
+    const int32_t p = row_pos[r];
+    const uint32_t page_no = (uint32_t)p / geo.page;
+    const int32_t page_id = page_no < geo.max_pages ? block_table[(size_t)sq * geo.max_pages + page_no] : -1;
+    if (page_id < 0 || (uint32_t)p >= n_pos) { if (lane == 0) atomicOr(err, DEVERR_OOB_MAP); return; }
+    T* dst = kv_pool + kv_index(geo, (uint32_t)page_id, layer, kv, kvh, (uint32_t)p % geo.page);
+    const float* src = qkv + (size_t)r * qkv_ld + (size_t)n_head * HD + (size_t)kv * geo.n_kv * HD + (size_t)kvh * HD;
+    if (kv == 1) {
+        for (uint32_t i = lane; i < HD; i += 32) st_kv(dst + i, src[i]);
+        return;
+    }
+    constexpr uint32_t half = HD / 2;
+    constexpr int NP = (HD / 2 + 31) / 32;
+    const float* ct = cos_t + (size_t)p * half;
+    const float* st = sin_t + (size_t)p * half;
+    float x0[NP], x1[NP];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+        const uint32_t i = lane + 32 * j;
+        x0[j] = i < half ? src[i] : 0.f;
+        x1[j] = i < half ? src[i + half] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < NP; ++j) ss = fmaf(x0[j], x0[j], ss);
+#pragma unroll
+    for (int j = 0; j < NP; ++j) ss = fmaf(x1[j], x1[j], ss);
+    float rms = 1.f;
+    if (k_norm) { ss = warp_sum(ss); rms = sqrtf(ss / (float)HD + eps); }
+    const float rcp = __frcp_rn(rms);
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+        const uint32_t i = lane + 32 * j;
+        if (i < half) {
+            float a0 = x0[j], a1 = x1[j];
+            if (k_norm) { a0 = div_by(a0, rms, rcp) * k_norm[i]; a1 = div_by(a1, rms, rcp) * k_norm[i + half]; }
+            const float c = ct[i], sn = st[i];
+            st_kv(dst + i, __fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, sn)));
+            st_kv(dst + i + half, __fadd_rn(__fmul_rn(a0, sn), __fmul_rn(a1, c)));
+        }
+    }
+}
+
+// Chunked prefill: row r = (sequence r / T, position pos[sequence] + r % T).
+__global__ void k_prefill_rows(const int32_t* __restrict__ pos, uint32_t batch, uint32_t T, int32_t* __restrict__ row_seq, int32_t* __restrict__ row_pos) {
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= batch * T) return;
+    const uint32_t s = r / T;
+    row_seq[r] = (int32_t)s;
+    row_pos[r] = pos[s] + (int32_t)(r % T);
+}
+__global__ void k_advance_n(int32_t* __restrict__ pos, uint32_t batch, int32_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < batch) pos[b] += n;
+}
+
 // End of a step: advance positions; when the LM head ran, log the sampled token.
 __global__ void k_advance(int32_t* __restrict__ pos, const int32_t* __restrict__ cur_tok, int32_t* __restrict__ gen_log,
                           uint32_t log_ld, uint32_t batch, int with_lm) {
@@ -675,7 +730,7 @@ static void destroy(Decoder* D) {
     cudaStreamSynchronize(g.stream);
     free_graphs(D);
     void* ptrs[] = {D->pos, D->cur_tok, D->cur_val, D->prompt_len, D->prompt_tok, D->gen_log, D->block_table, D->kv_pool, D->hbuf[0], D->hbuf[1], D->qkv,
-                    D->attn_out, D->proj, D->act, D->logits, D->part_o, D->part_ml, D->attn_ticket,
+                    D->attn_out, D->proj, D->act, D->logits, D->part_o, D->part_ml, D->attn_ticket, D->row_seq, D->row_pos,
                     D->rope_cos[0], D->rope_sin[0], D->rope_cos[1], D->rope_sin[1]};
     for (void* p : ptrs) cudaFree(p);
     delete D;
@@ -693,7 +748,7 @@ static size_t kv_elem_size(const adam_b200_decoder_desc& d) { return d.kv_dtype 
 
 typedef void (*AttnKernel)(const float*, uint32_t, const float*, const float*, float, const float*, const float*, uint32_t, void*, KvGeom,
                            const int32_t*, const int32_t*, uint32_t, uint32_t, uint32_t, float, float, float*, float*, float*,
-                           unsigned int*, uint32_t, uint32_t, uint32_t*);
+                           unsigned int*, uint32_t, uint32_t, const int32_t*, const int32_t*, uint32_t*);
 
 template <typename T, int GS>
 static AttnKernel pick_attn_hd(uint32_t hd) {
@@ -706,7 +761,7 @@ static AttnKernel pick_attn_hd(uint32_t hd) {
 }
 
 template <typename T>
-static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch) {
+static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = false) {
     const adam_b200_decoder_desc& d = D->d;
     KvGeom geo{d.n_layer, d.n_head_kv, d.head_dim, d.page_size, D->max_pages_per_seq, D->page_elems};
     const uint32_t gs = d.n_head / d.n_head_kv;
@@ -725,7 +780,8 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch) {
     launch_k(kern, grid, dim3(256), smem, g.stream, g.pdl, D->qkv, qkv_ld, ly.norm[NORM_Q], ly.norm[NORM_K], d.norm_eps,
              D->rope_cos[which], D->rope_sin[which], D->rope_pos[which],
              D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
-             d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, hpc, g.dev_err);
+             d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, hpc,
+             prefill ? D->row_seq : nullptr, prefill ? D->row_pos : nullptr, g.dev_err);
     count_launch();
     return ADAMAH_OK;
 }
@@ -770,9 +826,9 @@ static int enqueue_part(Decoder* D, uint32_t batch, uint32_t part, bool with_lm,
         // cache writes being complete before any of them starts.
         if (L == 0) {
             if (D->embd.wtype == WT_Q4_0)
-                launch_k(k_embed<WT_Q4_0>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
+                launch_k(k_embed<WT_Q4_0>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], nullptr, nullptr, g.dev_err);
             else
-                launch_k(k_embed<WT_Q4_K>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], g.dev_err);
+                launch_k(k_embed<WT_Q4_K>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], nullptr, nullptr, g.dev_err);
             count_launch();
         }
         const int cur = L == 0 ? 0 : 1;             // residual stream buffer on entry
@@ -886,7 +942,8 @@ extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint
     D->page_elems = (size_t)d.n_layer * 2 * d.n_head_kv * d.page_size * d.head_dim;
     D->n_splits = (d.kv_cap + ATTN_SPLIT - 1) / ATTN_SPLIT;      // ATTN_SPLIT = ATTN_CP * ATTN_CHUNKS_PER_CTA
     if (D->n_splits > ATTN_MAX_SPLITS) D->n_splits = ATTN_MAX_SPLITS;
-    const size_t B = d.max_batch, E = d.n_embd, q_dim = (size_t)d.n_head * d.head_dim, k_dim = (size_t)d.n_head_kv * d.head_dim;
+    D->rows_cap = d.max_batch > PREFILL_ROWS ? d.max_batch : PREFILL_ROWS;
+    const size_t B = d.max_batch, R = D->rows_cap, E = d.n_embd, q_dim = (size_t)d.n_head * d.head_dim, k_dim = (size_t)d.n_head_kv * d.head_dim;
     const uint32_t gs = d.n_head / d.n_head_kv;
     g_dec[id] = D;
 #define DALLOC(p, bytes) do { cudaError_t e__ = cudaMalloc((void**)&(p), (bytes)); if (e__ != cudaSuccess) { destroy(D); g_dec[id] = nullptr; \
@@ -895,14 +952,15 @@ extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint
     DALLOC(D->prompt_tok, B * d.kv_cap * 4); DALLOC(D->gen_log, B * d.kv_cap * 4);
     DALLOC(D->block_table, B * D->max_pages_per_seq * 4);
     DALLOC(D->kv_pool, (size_t)D->n_pages * D->page_elems * kv_elem_size(d));
-    DALLOC(D->hbuf[0], B * E * 4); DALLOC(D->hbuf[1], B * E * 4); DALLOC(D->qkv, B * (q_dim + 2 * k_dim) * 4);
-    DALLOC(D->attn_out, B * q_dim * 4); DALLOC(D->proj, B * E * 4);
-    DALLOC(D->act, B * d.n_ff * 4); DALLOC(D->logits, B * (size_t)d.n_vocab * 4);
-    DALLOC(D->part_o, B * d.n_head_kv * D->n_splits * gs * d.head_dim * 4);
-    DALLOC(D->part_ml, B * d.n_head_kv * D->n_splits * gs * 2 * 4);
-    DALLOC(D->attn_ticket, B * d.n_head * 4);
+    DALLOC(D->hbuf[0], R * E * 4); DALLOC(D->hbuf[1], R * E * 4); DALLOC(D->qkv, R * (q_dim + 2 * k_dim) * 4);
+    DALLOC(D->attn_out, R * q_dim * 4); DALLOC(D->proj, R * E * 4);
+    DALLOC(D->act, R * d.n_ff * 4); DALLOC(D->logits, B * (size_t)d.n_vocab * 4);
+    DALLOC(D->part_o, R * d.n_head_kv * D->n_splits * gs * d.head_dim * 4);
+    DALLOC(D->part_ml, R * d.n_head_kv * D->n_splits * gs * 2 * 4);
+    DALLOC(D->attn_ticket, R * d.n_head * 4);
+    DALLOC(D->row_seq, R * 4); DALLOC(D->row_pos, R * 4);
 #undef DALLOC
-    cudaMemsetAsync(D->attn_ticket, 0, B * d.n_head * 4, g.stream);
+    cudaMemsetAsync(D->attn_ticket, 0, R * d.n_head * 4, g.stream);
     cudaMemsetAsync(D->pos, 0, B * 4, g.stream);
     cudaMemsetAsync(D->cur_tok, 0, B * 4, g.stream);
     cudaMemsetAsync(D->cur_val, 0, B * 4, g.stream);
@@ -1028,6 +1086,8 @@ extern "C" int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_
     DCU(cudaMemsetAsync(D->gen_log, 0xFF, (size_t)d.max_batch * d.kv_cap * 4, g.stream));
     DCU(cudaStreamSynchronize(g.stream));
     D->batch = batch;
+    D->hpos.assign(batch, 0);
+    D->hplen.assign(prompt_lens, prompt_lens + batch);
     return ADAMAH_OK;
 }
 
@@ -1042,6 +1102,7 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
     const bool with_lm = flags & 1u, want_logits = (flags & 2u) != 0, direct = (flags & 4u) != 0;
     if (want_logits && !with_lm) return fail(ADAMAH_ERR_INVALID, "decoder_step: logits need the LM head flag");
     int rc = ADAMAH_OK;
+    for (uint32_t& hp : D->hpos) hp += n_steps;
     if (direct || want_logits || capturing()) {
         for (uint32_t s = 0; s < n_steps && rc == ADAMAH_OK; ++s) rc = enqueue_step(D, D->batch, with_lm, want_logits);
     } else {
@@ -1073,6 +1134,105 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
     return rc;
 }
 
+// Chunked prefill: consume the next n_tokens prompt tokens of every active sequence, several
+// positions per pass: the rows of a chunk (sequence x token) go through the GEMVs together as
+// batch rows, their keys and values are appended first and attention then reads the whole
+// chunk from the cache (causal by position).  No LM head: the token after the prompt's last one
+// comes from a normal step.  Every sequence must still have n_tokens prompt tokens ahead.
+// Same results as n_tokens single steps (the reference consumes prompts token by token,
+// engine.py:3838-3847).
+template <typename T>
+static int launch_kv_append_t(Decoder* D, uint32_t L, uint32_t rows) {
+    const adam_b200_decoder_desc& d = D->d;
+    KvGeom geo{d.n_layer, d.n_head_kv, d.head_dim, d.page_size, D->max_pages_per_seq, D->page_elems};
+    const int which = is_global_layer(d, L) ? 1 : 0;
+    const uint32_t warps = rows * d.n_head_kv * 2, qkv_ld = (d.n_head + 2 * d.n_head_kv) * d.head_dim;
+    const dim3 grid((warps * 32 + 255) / 256);
+    const Layer& ly = D->layers[L];
+#define KVA(HD_) launch_k(k_kv_append<T, HD_>, grid, dim3(256), 0, g.stream, g.pdl, (const float*)D->qkv, qkv_ld, ly.norm[NORM_K], d.norm_eps, \
+        (const float*)D->rope_cos[which], (const float*)D->rope_sin[which], D->rope_pos[which], D->kv_pool, geo, (const int32_t*)D->block_table, \
+        (const int32_t*)D->row_seq, (const int32_t*)D->row_pos, rows, d.n_head, L, g.dev_err)
+    switch (d.head_dim) { case 32: KVA(32); break; case 64: KVA(64); break; case 128: KVA(128); break; default: KVA(256); break; }
+#undef KVA
+    count_launch();
+    return ADAMAH_OK;
+}
+
+static int enqueue_prefill_chunk(Decoder* D, uint32_t batch, uint32_t T) {
+    const adam_b200_decoder_desc& d = D->d;
+    const uint32_t rows = batch * T;
+    const uint32_t E = d.n_embd, q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim, qkv_ld = q_dim + 2 * k_dim;
+    int rc;
+    k_prefill_rows<<<(rows + 63) / 64, 64, 0, g.stream>>>(D->pos, batch, T, D->row_seq, D->row_pos);
+    count_launch();
+    if (D->embd.wtype == WT_Q4_0)
+        launch_k(k_embed<WT_Q4_0>, dim3(rows), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], (const int32_t*)D->row_seq, (const int32_t*)D->row_pos, g.dev_err);
+    else
+        launch_k(k_embed<WT_Q4_K>, dim3(rows), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], (const int32_t*)D->row_seq, (const int32_t*)D->row_pos, g.dev_err);
+    count_launch();
+    for (uint32_t L = 0; L < d.n_layer; ++L) {
+        const Layer& ly = D->layers[L];
+        const int cur = L == 0 ? 0 : 1;
+        GemvArgs in = {};
+        in.ldx = (int)E; in.eps = d.norm_eps; in.h_in = D->hbuf[cur]; in.w_pre = ly.norm[NORM_ATTN];
+        if (L > 0) { in.add_src = D->proj; in.w_post = D->layers[L - 1].norm[NORM_POST_FFW]; in.h_out = D->hbuf[cur ^ 1]; }
+        in.y = D->qkv; in.ldy = (int)qkv_ld;
+        if (ly.qkv_contiguous) {
+            Mat qkv = ly.m[MAT_Q]; qkv.rows = qkv_ld; qkv.tiled = ly.qkv_tiled;
+            if ((rc = gemv(qkv, nullptr, in, rows, EPI_STORE))) return rc;
+        } else {
+            if ((rc = gemv(ly.m[MAT_Q], nullptr, in, rows, EPI_STORE))) return rc;
+            GemvArgs in2 = in; in2.h_out = nullptr;
+            in2.y = D->qkv + q_dim;
+            if ((rc = gemv(ly.m[MAT_K], nullptr, in2, rows, EPI_STORE))) return rc;
+            in2.y = D->qkv + q_dim + k_dim;
+            if ((rc = gemv(ly.m[MAT_V], nullptr, in2, rows, EPI_STORE))) return rc;
+        }
+        rc = d.kv_dtype == 1 ? launch_kv_append_t<__half>(D, L, rows) : launch_kv_append_t<float>(D, L, rows);
+        if (rc) return rc;
+        rc = d.kv_dtype == 1 ? launch_attn_t<__half>(D, L, rows, true) : launch_attn_t<float>(D, L, rows, true);
+        if (rc) return rc;
+        GemvArgs o = {};
+        o.x = D->attn_out; o.ldx = (int)q_dim; o.y = D->proj; o.ldy = (int)E;
+        if ((rc = gemv(ly.m[MAT_O], nullptr, o, rows, EPI_STORE))) return rc;
+        GemvArgs gu = {};
+        gu.ldx = (int)E; gu.eps = d.norm_eps; gu.h_in = D->hbuf[0]; gu.add_src = D->proj; gu.w_post = ly.norm[NORM_POST_ATTN];
+        gu.w_pre = ly.norm[NORM_FFN]; gu.h_out = D->hbuf[1]; gu.y = D->act; gu.ldy = (int)d.n_ff;
+        if ((rc = gemv(ly.m[MAT_GATE], &ly.m[MAT_UP], gu, rows, d.ffn_act == 0 ? EPI_GEGLU : EPI_SWIGLU))) return rc;
+        GemvArgs dn = {};
+        dn.x = D->act; dn.ldx = (int)d.n_ff; dn.y = D->proj; dn.ldy = (int)E;
+        if ((rc = gemv(ly.m[MAT_DOWN], nullptr, dn, rows, EPI_STORE))) return rc;
+    }
+    launch_k(k_advance_n, dim3((batch + 63) / 64), dim3(64), 0, g.stream, g.pdl, D->pos, batch, (int32_t)T);
+    count_launch();
+    return check_launch("decoder prefill");
+}
+
+extern "C" int adam_b200_decoder_prefill(uint32_t id, uint32_t n_tokens) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (D->batch == 0) return fail(ADAMAH_ERR_INVALID, "decoder_prefill: call decoder_begin first");
+    if (capturing()) return fail(ADAMAH_ERR_INVALID, "decoder_prefill: not allowed while a graph is being captured");
+    for (uint32_t b = 0; b < D->batch; ++b)
+        if ((uint64_t)D->hpos[b] + n_tokens > D->hplen[b])
+            return fail(ADAMAH_ERR_INVALID, "decoder_prefill: sequence %u has only %u prompt tokens left", b, D->hplen[b] - D->hpos[b]);
+    const uint32_t t_max = D->rows_cap / D->batch;
+    if (t_max == 0) return fail(ADAMAH_ERR_INVALID, "decoder_prefill: batch larger than the row buffers");
+    static const bool allow = !(getenv("ADAM_B200_PDL") && atoi(getenv("ADAM_B200_PDL")) == 0);
+    int rc = ADAMAH_OK;
+    uint32_t left = n_tokens;
+    while (left && rc == ADAMAH_OK) {
+        const uint32_t T = left < t_max ? left : t_max;
+        g.pdl = allow;
+        rc = enqueue_prefill_chunk(D, D->batch, T);
+        g.pdl = false;
+        left -= T;
+    }
+    if (rc == ADAMAH_OK) for (uint32_t& hp : D->hpos) hp += n_tokens;
+    end_of_op();
+    return rc;
+}
+
 // One part of a token step, enqueued directly on the stream (no graph): see enqueue_part.
 // For callers that interleave their own work between parts (tensor parallelism: an
 // all-reduce of the projection buffer after every layer part, a merge of the arg-max
@@ -1091,6 +1251,7 @@ extern "C" int adam_b200_decoder_step_part(uint32_t id, uint32_t part, uint32_t 
     g.pdl = allow;
     const int rc = enqueue_part(D, D->batch, part, with_lm, want_logits);
     g.pdl = false;
+    if (rc == ADAMAH_OK && part + 1 == n_parts(D)) for (uint32_t& hp : D->hpos) hp += 1;
     end_of_op();
     return rc;
 }

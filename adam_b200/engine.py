@@ -174,6 +174,12 @@ class ADAMEngine:
         flags = (STEP_LM if lm_head else 0) | (STEP_LOGITS if logits else 0) | (STEP_DIRECT if direct else 0)
         self._check(self._lib.adam_b200_decoder_step(self._dec, n_steps, flags), "adam_b200_decoder_step")
 
+    def prefill(self, n_tokens: int):
+        """Consume the next ``n_tokens`` prompt tokens of every sequence, many positions per pass
+        (same results as ``step(n_tokens, lm_head=False)``)."""
+        if n_tokens > 0:
+            self._check(self._lib.adam_b200_decoder_prefill(self._dec, int(n_tokens)), "adam_b200_decoder_prefill")
+
     def read_state(self):
         pos = np.empty(self._max_batch, np.int32)
         tok = np.empty(self._max_batch, np.int32)
@@ -236,7 +242,7 @@ class ADAMEngine:
         # prefill: every sequence consumes its own prompt; shorter ones start decoding earlier
         g.batch_begin()
         if min_len > 1:
-            self.step(min_len - 1, lm_head=False)
+            self.prefill(min_len - 1)
         g.batch_end()
         t_pre = time.perf_counter() - tp
         td = time.perf_counter()

@@ -251,6 +251,11 @@ class ADAMEngineTP(ADAMEngine):
                         self._one_step(flags)
                     self._graphs[key] = gr
 
+    def prefill(self, n_tokens: int):
+        """Token by token here: a chunked pass would need the collectives inside it."""
+        if n_tokens > 0:
+            self.step(n_tokens, lm_head=False)
+
     def begin(self, prompts, reserve):
         super().begin(prompts, reserve)
         self._graphs = {k: g for k, g in self._graphs.items() if k[1] == self._batch}

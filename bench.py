@@ -218,7 +218,7 @@ def main():
     eng.begin([prompt], [kv_cap - 4])
     gpu.batch_begin()
     t0 = time.perf_counter()
-    eng.step(PROMPT_LEN - 1, lm_head=False)
+    eng.prefill(PROMPT_LEN - 1)              # 64 prompt positions per pass through the layers
     gpu.batch_end()
     prefill_s = time.perf_counter() - t0
     gpu.batch_begin(); eng.step(warmup, lm_head=True); gpu.batch_end()

@@ -311,6 +311,11 @@ int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_t* prompt_t
 /* n_steps token steps.  flags: bit 0 LM head + arg-max, bit 1 also store logits,
  * bit 2 launch kernels directly (no graph replay). */
 int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t flags);
+/* Chunked prefill: consume the next n_tokens prompt tokens of every active sequence, up to 64
+ * rows (sequences x tokens) per pass through the layers; same results as n_tokens steps without
+ * the LM head.  Every sequence must still have n_tokens prompt tokens ahead.  The reference
+ * consumes prompts token by token (adam/models/engine.py:3838-3847). */
+int adam_b200_decoder_prefill(uint32_t id, uint32_t n_tokens);
 /* The same step in parts, each enqueued directly on the stream, for callers that put their
  * own work between them (tensor parallelism).  Parts 2L / 2L+1 = attention half (embedding
  * for L = 0, QKV, attention, o-proj) / FFN half (gate+up, down) of layer L; then the LM head

@@ -157,6 +157,38 @@ def test_batch_of_ragged_prompts_equals_single_sequence_runs(gpu):
         eng.close()
 
 
+@pytest.mark.parametrize("ggml_type,kv_dtype,window", [(gb.GGML_TYPE_Q4_0, "f32", False), (gb.GGML_TYPE_Q4_0, "f16", True), (gb.GGML_TYPE_Q4_K, "f32", False)])
+def test_chunked_prefill_equals_token_by_token(gpu, ggml_type, kv_dtype, window):
+    """The prompt consumed 64 rows (sequences x positions) at a time must leave the same state as single
+    steps: same logits for the token after the prompt, same greedy continuation, ragged prompts included."""
+    cfg = _cfg(dict(n_layer=3, sliding_window=8) if window else dict(n_layer=3))
+    tensors = synth.build_model(cfg, ggml_type, seed=41)
+    prompts = [synth.random_prompt(cfg.n_vocab, n, seed=50 + n) for n in (90, 71, 90)]      # > 64 rows: several chunks, 21 tokens each
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=128, kv_dtype=kv_dtype, max_batch=3, window=window)
+    try:
+        n_pre = min(len(p) for p in prompts) - 1
+        eng.begin(prompts, [120] * 3)
+        gpu.batch_begin(); eng.step(n_pre, lm_head=False); eng.step(1, lm_head=True, logits=True); gpu.batch_end()
+        ref_logits = np.stack([eng.read_logits(b) for b in range(3)])
+        gpu.batch_begin(); eng.step(8, lm_head=True); gpu.batch_end()
+        ref_ids = [eng.read_log(b, n_pre + 1, 9) for b in range(3)]
+        eng.begin(prompts, [120] * 3)
+        gpu.batch_begin(); eng.prefill(n_pre); eng.step(1, lm_head=True, logits=True); gpu.batch_end()
+        got_logits = np.stack([eng.read_logits(b) for b in range(3)])
+        gpu.batch_begin(); eng.step(8, lm_head=True); gpu.batch_end()
+        got_ids = [eng.read_log(b, n_pre + 1, 9) for b in range(3)]
+        assert np.abs(got_logits - ref_logits).max() <= 1e-5 * np.abs(ref_logits).max()
+        for a, b in zip(ref_ids, got_ids):
+            assert np.array_equal(a, b)
+        assert gpu.device_error() == 0
+        # asking for more prompt tokens than a sequence has left is refused
+        eng.begin(prompts, [120] * 3)
+        with pytest.raises(RuntimeError, match="prompt tokens left"):
+            eng.prefill(80)
+    finally:
+        eng.close()
+
+
 def test_graph_replay_equals_direct_launches(gpu):
     cfg = _cfg(dict(n_layer=2))
     tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=36)

@@ -111,6 +111,18 @@ def test_q4_0_gemv_tensor_core_path(gpu, N, K, B):
     assert np.abs(y - y0).max() < 1e-4 * np.abs(y0).max()
 
 
+@pytest.mark.parametrize("ggml_type,N,K,B", [(2, 256, 1152, 33), (12, 128, 1024, 37), (2, 64, 6912, 18)])
+def test_tensor_core_path_many_batch_rows(gpu, ggml_type, N, K, B):
+    """More than four batch rows: the row groups of one call run side by side in one launch."""
+    rng = np.random.default_rng(N + K + B)
+    raw = (gb.random_q4_0_blocks if ggml_type == 2 else gb.random_q4_k_blocks)(rng, N, K)
+    x = rng.standard_normal((B, K), dtype=np.float32) * rng.uniform(0.01, 100.0, (B, 1)).astype(np.float32)   # a scale per row
+    y = _gemv(gpu, ggml_type, raw, N, K, x, tile=True)
+    W = q4_blocks.dequant(raw.reshape(-1), ggml_type, N, K)
+    for b in range(B):          # every row against its own reference (rows differ in magnitude)
+        _check(y[b:b + 1], W, x[b:b + 1])
+
+
 def test_tensor_core_path_at_offset_and_bad_shapes(gpu):
     rng = np.random.default_rng(123)
     N, K = 96, 1152
