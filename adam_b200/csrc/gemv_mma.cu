@@ -110,7 +110,7 @@ int launch_gemv_mma(int wt, const uint8_t* t0, const uint8_t* t1, GemvArgs a, cu
         if (a.epi == EPI_ARGMAX && grid > gemv_max_grid()) grid = gemv_max_grid();
         if (a.max_grid > 0 && grid > a.max_grid) grid = a.max_grid;
         if (grid < 1) grid = 1;
-        if (launch_k(k, dim3(grid, n_pass), dim3(n_warps * 32), smem, stream, g.pdl, g1, t0, t1, KS) != cudaSuccess)
+        if (launch_k(k, dim3(n_pass, grid), dim3(n_warps * 32), smem, stream, g.pdl, g1, t0, t1, KS) != cudaSuccess)
             return fail(ADAMAH_ERR_BACKEND, "gemv_mma: launch failed: %s", cudaGetErrorString(cudaGetLastError()));
         count_launch();
     }

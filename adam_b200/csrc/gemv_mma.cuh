@@ -135,12 +135,15 @@ template <int NCOL, bool PAIR, int WT>
 __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const uint8_t* __restrict__ t0, const uint8_t* __restrict__ t1, int KS) {
     constexpr int NI = NCOL == 16 ? 2 : 1;      // MMAs per block
     constexpr int NBR = NCOL / 4;               // batch rows staged
-    // blockIdx.y = group of NBR batch rows.  The groups of one launch are independent problems
-    // over the same weights; running them side by side keeps the SMs busy where one group alone
-    // is bound by latency, and the groups' reads of a tile arrive close together (L2 hits).
+    // blockIdx.x = group of NBR batch rows, blockIdx.y = CTA index within a group.  The groups of one
+    // launch are independent problems over the same weights; running them side by side keeps the
+    // SMs busy where one group alone is bound by latency, and because the group index is the fast
+    // grid dimension the CTAs that stream the same tiles are scheduled together, so all groups but
+    // the first find them in L2.
+    const uint32_t bx = blockIdx.y, gx = gridDim.y, grp = blockIdx.x;
     GemvArgs a = a_in;
     {
-        const int r0 = (int)blockIdx.y * NBR;
+        const int r0 = (int)grp * NBR;
         a.B = min(NBR, a_in.B - r0);
         if (r0) {
             if (a.x) a.x += (size_t)r0 * a.ldx;
@@ -151,7 +154,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
             if (a.out_tok) a.out_tok += r0;
             if (a.out_tok_f32) a.out_tok_f32 += r0;
             if (a.out_val) a.out_val += r0;
-            if (a.part_val) { a.part_val += (size_t)r0 * gridDim.x; a.part_idx += (size_t)r0 * gridDim.x; a.ticket += blockIdx.y; }
+            if (a.part_val) { a.part_val += (size_t)r0 * gx; a.part_idx += (size_t)r0 * gx; a.ticket += grp; }
         }
     }
     constexpr int NPR = NCOL / 2;               // column pairs per block (one pre-summed value each)
@@ -175,7 +178,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
     const int n_rg = a.N >> 4;
     const int n_sets = (n_rg + RG - 1) / RG;
     const int p0 = (int)((long long)ks * pairs / KS), p1 = (int)((long long)(ks + 1) * pairs / KS), np = p1 - p0;
-    const int my_sets = (n_sets > (int)blockIdx.x) ? (n_sets - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int my_sets = (n_sets > (int)bx) ? (n_sets - (int)bx + (int)gx - 1) / (int)gx : 0;
 
     // ---- weight stream: every warp runs its own ring of bulk copies into shared memory ----
     // Stage = up to CH consecutive tile pairs of the warp's row group (contiguous in memory),
@@ -193,7 +196,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
     // issue cursor (lane 0): the next chunk to request is chunk `i_j` of row group `i_rg`, into stage `i_st`
-    int i_c = 0, i_j = 0, i_st = 0, i_rg = (int)blockIdx.x * RG + rg_l;
+    int i_c = 0, i_j = 0, i_st = 0, i_rg = (int)bx * RG + rg_l;
     auto issue_next = [&]() {                                // lane 0 only
         const int rg = min(i_rg, n_rg - 1);                 // clamped: rows past the end are dropped later
         const int pp0 = p0 + i_j * CH, n = min(CH, p1 - pp0);
@@ -204,7 +207,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
         if (PAIR) bulk_g2s(dst + CH * MMA_TILE, t1 + off, (uint32_t)(n * MMA_TILE), &s_bar[warp][i_st]);
         ++i_c;
         if (++i_st == MMA_NSTAGE) i_st = 0;
-        if (++i_j == nch) { i_j = 0; i_rg += (int)gridDim.x * RG; }
+        if (++i_j == nch) { i_j = 0; i_rg += (int)gx * RG; }
     };
     if (lane == 0) {
 #pragma unroll
@@ -267,7 +270,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
                     ss = fmaf(vh[j].x, vh[j].x, ss); ss = fmaf(vh[j].y, vh[j].y, ss); ss = fmaf(vh[j].z, vh[j].z, ss); ss = fmaf(vh[j].w, vh[j].w, ss);
                     am = fmaxf(am, fmaxf(fmaxf(fabsf(vh[j].x * vw[j].x), fabsf(vh[j].y * vw[j].y)), fmaxf(fabsf(vh[j].z * vw[j].z), fabsf(vh[j].w * vw[j].w))));
                     const int i = threadIdx.x + j * blockDim.x;
-                    if (i < n4 && a.h_out && blockIdx.x == 0) reinterpret_cast<float4*>(a.h_out + row)[i] = vh[j];
+                    if (i < n4 && a.h_out && bx == 0) reinterpret_cast<float4*>(a.h_out + row)[i] = vh[j];
                 }
                 block_sum_max(ss, am, red);
                 float rms = 1.f;
@@ -417,7 +420,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
     };
 
     bool timed_out = false;
-    int j = 0, st = 0, c_rg = (int)blockIdx.x * RG + rg_l;
+    int j = 0, st = 0, c_rg = (int)bx * RG + rg_l;
     uint32_t ph = 0;
     for (int c = 0; c < n_chunks; ++c) {
         if (!timed_out) {
@@ -450,7 +453,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
             // ---- end of this warp's K slice for the row group ----
             const int rg = c_rg;
             j = 0;
-            c_rg += (int)gridDim.x * RG;
+            c_rg += (int)gx * RG;
             // even lanes: 256 * acc + (odd neighbour's acc) / 256  ->  batch row 2i + t/2
             float val[NM][NI][2];
 #pragma unroll
@@ -536,20 +539,20 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
         const int b = threadIdx.x;
         float bv = s_bv[b]; int bi = s_bi[b];
         for (int w = 1; w < n_warps; ++w) if (better(s_bv[w * 4 + b], s_bi[w * 4 + b], bv, bi)) { bv = s_bv[w * 4 + b]; bi = s_bi[w * 4 + b]; }
-        a.part_val[(size_t)b * gridDim.x + blockIdx.x] = bv;
-        a.part_idx[(size_t)b * gridDim.x + blockIdx.x] = bi;
+        a.part_val[(size_t)b * gx + bx] = bv;
+        a.part_idx[(size_t)b * gx + bx] = bi;
     }
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1);
+    if (threadIdx.x == 0) s_last = (atomicAdd(a.ticket, 1u) == gx - 1);
     __syncthreads();
     if (!s_last) return;
     __threadfence();
     for (int b = 0; b < a.B && b < NBR; ++b) {
         float bv = -3.402823466e+38f; int bi = -1;
-        for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) {
-            const float v = __ldcg(a.part_val + (size_t)b * gridDim.x + i);
-            const int k = __ldcg(a.part_idx + (size_t)b * gridDim.x + i);
+        for (int i = threadIdx.x; i < (int)gx; i += blockDim.x) {
+            const float v = __ldcg(a.part_val + (size_t)b * gx + i);
+            const int k = __ldcg(a.part_idx + (size_t)b * gx + i);
             if (better(v, k, bv, bi)) { bv = v; bi = k; }
         }
 #pragma unroll
