@@ -4,7 +4,8 @@ reference (krokodil-byte/adam, mounted read-only) on seeded inputs.
 
 Run where the reference tree is available:
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference <checkout of krokodil-byte/adam>
+    (or set ADAM_REFERENCE_DIR)
 
 The fixtures are small ``.npz`` files; the parity tests only read them, so the
 reference tree is not needed when the tests run.  What each file pins:
@@ -48,9 +49,11 @@ DECODE_CASES = [
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("ADAM_REFERENCE_DIR", ""))
     args = ap.parse_args()
     ref = args.reference
+    if not ref or not os.path.isdir(ref):
+        ap.error("give the reference checkout with --reference or ADAM_REFERENCE_DIR")
     sys.path.insert(0, os.path.join(ref, "adamah-MAIN"))
     sys.path.insert(0, ref)
 
