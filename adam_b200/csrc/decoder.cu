@@ -53,6 +53,7 @@ struct Decoder {
     int32_t *row_seq, *row_pos; // chunked prefill: (sequence, position) of every row of the chunk
     uint32_t rows_cap;          // rows the activation buffers hold: max(max_batch, PREFILL_ROWS)
     std::vector<uint32_t> hpos, hplen;   // host mirror of positions and prompt lengths (argument checks)
+    std::vector<int32_t> hbt;            // host mirror of the block table
     uint32_t batch;             // active sequences
     bool use_tiles;             // build row-tiled weight copies for the tensor-core GEMV
     std::vector<uint32_t> free_pages;
@@ -1088,6 +1089,47 @@ extern "C" int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_
     D->batch = batch;
     D->hpos.assign(batch, 0);
     D->hplen.assign(prompt_lens, prompt_lens + batch);
+    D->hbt = bt;
+    return ADAMAH_OK;
+}
+
+// Continue the single active sequence with a new prompt whose first n_reuse tokens are the ones
+// whose keys and values are already in the cache (role of generate(reuse_prefix=..),
+// adam/models/engine.py:3815-3833): positions restart at n_reuse, the cache pages are kept and
+// extended to `reserve` tokens.  n_reuse must not exceed the positions computed so far.
+extern "C" int adam_b200_decoder_continue(uint32_t id, const int32_t* prompt_tokens, uint32_t prompt_len, uint32_t reserve, uint32_t n_reuse) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    const adam_b200_decoder_desc& d = D->d;
+    if (D->batch != 1) return fail(ADAMAH_ERR_INVALID, "decoder_continue: needs one active sequence");
+    if (capturing()) return fail(ADAMAH_ERR_INVALID, "decoder_continue: not allowed while a graph is being captured");
+    if (!prompt_tokens || prompt_len == 0 || prompt_len > d.kv_cap || reserve < prompt_len || reserve > d.kv_cap)
+        return fail(ADAMAH_ERR_INVALID, "decoder_continue: needs 1 <= prompt <= reserve <= kv_cap (%u)", d.kv_cap);
+    if (n_reuse >= prompt_len || n_reuse > D->hpos[0])
+        return fail(ADAMAH_ERR_INVALID, "decoder_continue: %u reused positions, but %u are cached and the prompt has %u tokens", n_reuse, D->hpos[0], prompt_len);
+    DCU(cudaStreamSynchronize(g.stream));
+    std::vector<int32_t> ptok(prompt_len);
+    for (uint32_t t = 0; t < prompt_len; ++t) {
+        if (prompt_tokens[t] < 0 || (uint32_t)prompt_tokens[t] >= D->embd.rows) return fail(ADAMAH_ERR_INVALID, "decoder_continue: token id %d outside the vocabulary", prompt_tokens[t]);
+        ptok[t] = prompt_tokens[t];
+    }
+    uint32_t have = 0;
+    while (have < D->max_pages_per_seq && D->hbt[have] >= 0) ++have;
+    const uint32_t need = (reserve + d.page_size - 1) / d.page_size;
+    if (need > have) {
+        if (need - have > D->free_pages.size()) return fail(ADAMAH_ERR_MEMORY, "decoder_continue: KV page pool exhausted (%u pages)", D->n_pages);
+        for (uint32_t p = have; p < need; ++p) { D->hbt[p] = (int32_t)D->free_pages.back(); D->free_pages.pop_back(); }
+        DCU(cudaMemcpyAsync(D->block_table, D->hbt.data(), (size_t)D->max_pages_per_seq * 4, cudaMemcpyHostToDevice, g.stream));
+    }
+    const int32_t plen = (int32_t)prompt_len, p0 = (int32_t)n_reuse;
+    DCU(cudaMemcpyAsync(D->prompt_len, &plen, 4, cudaMemcpyHostToDevice, g.stream));
+    DCU(cudaMemcpyAsync(D->prompt_tok, ptok.data(), (size_t)prompt_len * 4, cudaMemcpyHostToDevice, g.stream));
+    DCU(cudaMemcpyAsync(D->pos, &p0, 4, cudaMemcpyHostToDevice, g.stream));
+    DCU(cudaMemsetAsync(D->cur_tok, 0, 4, g.stream));
+    DCU(cudaMemsetAsync(D->gen_log, 0xFF, (size_t)d.kv_cap * 4, g.stream));
+    DCU(cudaStreamSynchronize(g.stream));
+    D->hpos[0] = n_reuse;
+    D->hplen[0] = prompt_len;
     return ADAMAH_OK;
 }
 

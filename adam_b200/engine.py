@@ -217,7 +217,17 @@ class ADAMEngine:
             raise NotImplementedError("only greedy decoding (top_k == 1 or temperature == 0) is implemented")
         return "gpu_matvec_argmax"
 
-    def generate_batch(self, prompts: Sequence[Sequence[int]], config: Optional[GenerationConfig] = None, sync_every: int = 1):
+    def continue_with(self, prompt: Sequence[int], reserve: int, n_reuse: int):
+        """Keep the active sequence's cache and restart at position ``n_reuse`` with a new prompt whose first
+        ``n_reuse`` tokens are the cached ones."""
+        arr = np.ascontiguousarray(np.asarray(prompt, np.int32))
+        self._check(self._lib.adam_b200_decoder_continue(self._dec, arr.ctypes.data, len(arr), int(reserve), int(n_reuse)),
+                    "adam_b200_decoder_continue")
+        self._batch = 1
+        self._h2d_bytes = arr.nbytes
+
+    def generate_batch(self, prompts: Sequence[Sequence[int]], config: Optional[GenerationConfig] = None, sync_every: int = 1,
+                       reuse_prefix: int = 0):
         """Greedy generation for independent sequences (one step advances all of them).
         Returns (list of token lists, stats).  ``sync_every`` tokens are decoded between
         host reads of the sampled ids (1 = the reference's per-token read, engine.py:1979)."""
@@ -238,11 +248,18 @@ class ADAMEngine:
         tp = time.perf_counter()
         # all sequences step together, so each needs room up to the longest one's end
         max_len, min_len = max(lens), min(lens)
-        self.begin(prompts, [max_len + config.max_tokens] * len(prompts))
+        # reuse_prefix (one sequence): the first tokens' keys and values are still cached from the previous call
+        reuse = int(reuse_prefix or 0)
+        if reuse >= min_len or len(prompts) != 1:
+            reuse = 0
+        if reuse:
+            self.continue_with(prompts[0], max_len + config.max_tokens, reuse)
+        else:
+            self.begin(prompts, [max_len + config.max_tokens] * len(prompts))
         # prefill: every sequence consumes its own prompt; shorter ones start decoding earlier
         g.batch_begin()
-        if min_len > 1:
-            self.prefill(min_len - 1)
+        if min_len - 1 > reuse:
+            self.prefill(min_len - 1 - reuse)
         g.batch_end()
         t_pre = time.perf_counter() - tp
         td = time.perf_counter()
@@ -283,7 +300,7 @@ class ADAMEngine:
             outs.append([int(t) for t in ids])
         ng = sum(len(o) for o in outs)
         stats = {
-            "n_prompt": sum(lens), "n_prompt_total": sum(lens), "n_prompt_reused": 0, "n_prompt_prefilled": sum(lens),
+            "n_prompt": sum(lens), "n_prompt_total": sum(lens), "n_prompt_reused": reuse, "n_prompt_prefilled": sum(lens) - reuse,
             "n_gen": ng, "prefill_s": t_pre, "decode_s": t_dec, "total_s": time.perf_counter() - tp,
             "prefill_tps": (sum(lens) - len(lens)) / t_pre if t_pre > 0 else 0.0,
             "decode_tps": ng / t_dec if t_dec > 0 else 0.0,
@@ -296,7 +313,8 @@ class ADAMEngine:
     def generate(self, token_ids, config: Optional[GenerationConfig] = None, stream: bool = False, **kw):
         """Single sequence; same return shape as the reference: (tokens, stats dict)
         (engine.py:3810-3944).  Stops at the first id in ``config.eos_token_ids``."""
-        outs, stats = self.generate_batch([list(token_ids)], config, sync_every=int(kw.get("sync_every", 1)))
+        outs, stats = self.generate_batch([list(token_ids)], config, sync_every=int(kw.get("sync_every", 1)),
+                                          reuse_prefix=int(kw.get("reuse_prefix", 0) or 0))
         return outs[0], stats
 
     def reset(self):

@@ -311,6 +311,10 @@ int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_t* prompt_t
 /* n_steps token steps.  flags: bit 0 LM head + arg-max, bit 1 also store logits,
  * bit 2 launch kernels directly (no graph replay). */
 int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t flags);
+/* Continue the single active sequence with a new prompt whose first n_reuse tokens are already in
+ * the cache (generate(reuse_prefix=..), adam/models/engine.py:3815-3833): positions restart at
+ * n_reuse (which must not exceed the positions computed so far), pages are kept and extended. */
+int adam_b200_decoder_continue(uint32_t id, const int32_t* prompt_tokens, uint32_t prompt_len, uint32_t reserve, uint32_t n_reuse);
 /* Chunked prefill: consume the next n_tokens prompt tokens of every active sequence, up to 64
  * rows (sequences x tokens) per pass through the layers; same results as n_tokens steps without
  * the LM head.  Every sequence must still have n_tokens prompt tokens ahead.  The reference

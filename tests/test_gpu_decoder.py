@@ -189,6 +189,31 @@ def test_chunked_prefill_equals_token_by_token(gpu, ggml_type, kv_dtype, window)
         eng.close()
 
 
+def test_prefix_reuse_continues_from_the_cache(gpu):
+    """generate(reuse_prefix=n) (engine.py:3815-3833): a second turn that repeats the first turn's tokens
+    gives the ids of a fresh run on the whole prompt, and only the new tokens are prefilled."""
+    cfg = _cfg(dict(n_layer=3))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=43)
+    p1 = [int(t) for t in synth.random_prompt(cfg.n_vocab, 23, seed=61)]
+    p2 = [int(t) for t in synth.random_prompt(cfg.n_vocab, 9, seed=62)]
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=96, kv_dtype="f32", page_size=16)
+    try:
+        t1, _ = eng.generate(p1, GenerationConfig(max_tokens=6, **GREEDY))
+        turn2 = p1 + t1 + p2
+        cached = len(p1) + len(t1) - 1                      # the last sampled token was never fed back
+        got, st = eng.generate(turn2, GenerationConfig(max_tokens=10, **GREEDY), reuse_prefix=cached)
+        assert st["n_prompt_reused"] == cached and st["n_prompt_prefilled"] == len(turn2) - cached
+        want, _ = eng.generate(turn2, GenerationConfig(max_tokens=10, **GREEDY))
+        assert got == want
+        # more reused positions than were ever computed are refused
+        eng.generate(p1, GenerationConfig(max_tokens=2, **GREEDY))
+        with pytest.raises(RuntimeError, match="are cached"):
+            eng.generate(turn2, GenerationConfig(max_tokens=2, **GREEDY), reuse_prefix=len(p1) + 5)
+        assert gpu.device_error() == 0
+    finally:
+        eng.close()
+
+
 def test_graph_replay_equals_direct_launches(gpu):
     cfg = _cfg(dict(n_layer=2))
     tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=36)
