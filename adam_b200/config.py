@@ -10,8 +10,9 @@ from typing import Optional
 
 @dataclass
 class GenerationConfig:
-    """Same fields and defaults as adam/models/engine.py:24-29.  Only greedy
-    decoding (``top_k == 1`` or ``temperature == 0``) is implemented."""
+    """Same fields and defaults as adam/models/engine.py:24-29.  Greedy decoding
+    (``top_k == 1`` or ``temperature == 0``) stays on the device; anything else
+    is sampled on the host from the logits."""
     max_tokens: int = 128
     temperature: float = 0.8
     top_k: int = 40

@@ -1176,6 +1176,20 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
     return rc;
 }
 
+// Overwrite the current token of every active sequence (host-side sampling: the caller read the
+// logits of the last step and drew its own tokens; they feed the next step).
+extern "C" int adam_b200_decoder_set_tokens(uint32_t id, const int32_t* tokens) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (!tokens || D->batch == 0) return fail(ADAMAH_ERR_INVALID, "decoder_set_tokens: no active sequences or null argument");
+    if (capturing()) return fail(ADAMAH_ERR_INVALID, "decoder_set_tokens: not allowed while a graph is being captured");
+    for (uint32_t b = 0; b < D->batch; ++b)
+        if (tokens[b] < 0 || (uint32_t)tokens[b] >= D->embd.rows) return fail(ADAMAH_ERR_INVALID, "decoder_set_tokens: token id %d outside the vocabulary", tokens[b]);
+    DCU(cudaMemcpyAsync(D->cur_tok, tokens, (size_t)D->batch * 4, cudaMemcpyHostToDevice, g.stream));
+    DCU(cudaStreamSynchronize(g.stream));
+    return ADAMAH_OK;
+}
+
 // Chunked prefill: consume the next n_tokens prompt tokens of every active sequence, several
 // positions per pass: the rows of a chunk (sequence x token) go through the GEMVs together as
 // batch rows, their keys and values are appended first and attention then reads the whole

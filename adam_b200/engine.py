@@ -213,9 +213,44 @@ class ADAMEngine:
 
     # ---- generate ----------------------------------------------------------------------
     def _select_sampling_mode(self, config: GenerationConfig) -> str:
-        if not config.is_greedy():
-            raise NotImplementedError("only greedy decoding (top_k == 1 or temperature == 0) is implemented")
-        return "gpu_matvec_argmax"
+        """'gpu_matvec_argmax' (fused LM head + arg-max, ids stay on the device) for greedy decoding without
+        a repeat penalty, else 'cpu': logits are read back and sampled on the host (engine.py:3760-3805)."""
+        if config.is_greedy() and (config.repeat_penalty == 1.0 or config.top_k == 1):
+            return "gpu_matvec_argmax"
+        return "cpu"
+
+    @staticmethod
+    def _sample(logits: np.ndarray, cfg: GenerationConfig, prev, rng) -> int:
+        """Host-side sampling, the reference's rule (engine.py:3711-3729): repeat penalty on the last 64
+        history ids, temperature, top-k mask, soft-max, nucleus cut, categorical draw."""
+        logits = logits.astype(np.float32).copy()
+        if cfg.repeat_penalty != 1.0 and prev:
+            for t in set(prev[-64:]):
+                if t < len(logits):
+                    logits[t] = logits[t] / cfg.repeat_penalty if logits[t] > 0 else logits[t] * cfg.repeat_penalty
+        if cfg.temperature <= 0:
+            return int(np.argmax(logits))
+        logits /= np.float32(cfg.temperature)
+        if cfg.top_k > 0:
+            tk = min(cfg.top_k, len(logits))
+            ti = np.argpartition(logits, -tk)[-tk:]
+            m = np.full_like(logits, -np.inf)
+            m[ti] = logits[ti]
+            logits = m
+        p = np.exp(logits - np.max(logits))
+        p /= p.sum()
+        if cfg.top_p < 1.0:
+            si = np.argsort(p)[::-1]
+            cs = np.cumsum(p[si])
+            co = int(np.searchsorted(cs, cfg.top_p)) + 1
+            m = np.zeros_like(p)
+            m[si[:co]] = p[si[:co]]
+            p = m / m.sum()
+        return int(rng.choice(len(p), p=p.astype(np.float64) / float(p.astype(np.float64).sum())))
+
+    def set_tokens(self, tokens: Sequence[int]):
+        arr = np.ascontiguousarray(np.asarray(tokens, np.int32))
+        self._check(self._lib.adam_b200_decoder_set_tokens(self._dec, arr.ctypes.data), "adam_b200_decoder_set_tokens")
 
     def continue_with(self, prompt: Sequence[int], reserve: int, n_reuse: int):
         """Keep the active sequence's cache and restart at position ``n_reuse`` with a new prompt whose first
@@ -268,7 +303,35 @@ class ADAMEngine:
         done_at = [None] * len(prompts)
         steps_done = 0
         d2h = 0
-        while steps_done < n_steps:
+        sampled: List[List[int]] = [[] for _ in prompts]
+        if mode == "cpu":
+            # one step at a time: read the logits of every sequence that is past its prompt, draw its token on
+            # the host and hand it back as the next step's input
+            rng = np.random.default_rng(config.seed)
+            finished = [False] * len(prompts)
+            while steps_done < n_steps and not all(finished):
+                g.batch_begin()
+                self.step(1, lm_head=True, logits=True)
+                g.batch_end()
+                new_pos = min_len + steps_done              # position of the token this step produced
+                steps_done += 1
+                toks = np.zeros(len(prompts), np.int32)
+                for b, n in enumerate(lens):
+                    if finished[b] or new_pos < n:
+                        continue
+                    lg = self.read_logits(b)
+                    d2h += lg.nbytes
+                    hist = (list(prompts[b]) if config.repeat_on_prompt else []) + sampled[b]
+                    t = self._sample(lg, config, hist, rng)
+                    if t in eos:
+                        finished[b] = True
+                        continue
+                    sampled[b].append(t)
+                    toks[b] = t
+                    if len(sampled[b]) >= config.max_tokens:
+                        finished[b] = True
+                self.set_tokens(toks)
+        while mode != "cpu" and steps_done < n_steps:
             k = min(sync_every, n_steps - steps_done)
             g.batch_begin()
             self.step(k, lm_head=True)
@@ -295,6 +358,9 @@ class ADAMEngine:
         t_dec = time.perf_counter() - td
         outs: List[List[int]] = []
         for b, n in enumerate(lens):
+            if mode == "cpu":
+                outs.append(sampled[b])
+                continue
             end = done_at[b] if done_at[b] is not None else min(n + config.max_tokens, min_len + steps_done)
             ids = self.read_log(b, n, max(0, end - n)) if end > n else np.empty(0, np.int32)
             outs.append([int(t) for t in ids])

@@ -311,6 +311,9 @@ int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_t* prompt_t
 /* n_steps token steps.  flags: bit 0 LM head + arg-max, bit 1 also store logits,
  * bit 2 launch kernels directly (no graph replay). */
 int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t flags);
+/* Replace the current token of every active sequence ([batch] host ids): for callers that sample on
+ * the host from the logits of the last step (the reference's 'cpu' sampling mode, engine.py:3711-3729). */
+int adam_b200_decoder_set_tokens(uint32_t id, const int32_t* tokens);
 /* Continue the single active sequence with a new prompt whose first n_reuse tokens are already in
  * the cache (generate(reuse_prefix=..), adam/models/engine.py:3815-3833): positions restart at
  * n_reuse (which must not exceed the positions computed so far), pages are kept and extended. */

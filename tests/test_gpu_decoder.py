@@ -189,6 +189,39 @@ def test_chunked_prefill_equals_token_by_token(gpu, ggml_type, kv_dtype, window)
         eng.close()
 
 
+def test_host_sampling_mode(gpu):
+    """Non-greedy configurations are sampled on the host from the logits (the reference's 'cpu' mode,
+    engine.py:3711-3729): every drawn id lies in the oracle's top-k set after the repeat penalty, the same seed
+    gives the same ids, and a one-candidate nucleus reduces to arg-max."""
+    cfg = _cfg(dict(n_layer=2))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=44)
+    f32 = dequant_model(tensors)
+    prompt = [int(t) for t in synth.random_prompt(cfg.n_vocab, 7, seed=9)]
+    gen = GenerationConfig(max_tokens=12, temperature=0.9, top_k=5, top_p=0.95, repeat_penalty=1.3, seed=123, eos_token_ids=())
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=32, kv_dtype="f32")
+    try:
+        ids, st = eng.generate(prompt, gen)
+        assert st["sampling_mode"] == "cpu" and len(ids) == 12
+        ids2, _ = eng.generate(prompt, gen)
+        assert ids2 == ids
+        dec = OracleDecoder(cfg, f32, kv_cap=32)
+        seq = prompt + ids
+        for i, t in enumerate(seq[:-1]):
+            logits = dec.forward(t, i)
+            if i >= len(prompt) - 1:
+                lg = logits.copy()
+                for h in set(seq[len(prompt):i + 1][-64:]):
+                    lg[h] = lg[h] / 1.3 if lg[h] > 0 else lg[h] * 1.3
+                assert seq[i + 1] in set(np.argsort(-lg)[:5].tolist())
+        # a nucleus that keeps one candidate is arg-max of the penalised logits
+        one, _ = eng.generate(prompt, GenerationConfig(max_tokens=6, temperature=0.7, top_k=40, top_p=1e-6, repeat_penalty=1.0, seed=1,
+                                                       eos_token_ids=()))
+        greedy, _ = eng.generate(prompt, GenerationConfig(max_tokens=6, **GREEDY))
+        assert one == greedy
+    finally:
+        eng.close()
+
+
 def test_prefix_reuse_continues_from_the_cache(gpu):
     """generate(reuse_prefix=n) (engine.py:3815-3833): a second turn that repeats the first turn's tokens
     gives the ids of a fresh run on the whole prompt, and only the new tokens are prefilled."""
@@ -247,8 +280,6 @@ def test_eos_stops_generation_and_kv_cap_is_enforced(gpu):
         assert cut == full[:full.index(eos)]
         with pytest.raises(RuntimeError, match="KV cache too small"):
             eng.generate(prompt, GenerationConfig(max_tokens=27, **GREEDY))
-        with pytest.raises(NotImplementedError):
-            eng.generate(prompt, GenerationConfig(max_tokens=4))                 # sampled decoding is not implemented
         with pytest.raises(RuntimeError, match="outside the vocabulary"):
             eng.begin([[cfg.n_vocab + 3]], [4])
     finally:
