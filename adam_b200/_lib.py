@@ -114,6 +114,8 @@ _SIGS = {
     "adam_b200_decoder_step": (c_int, [u32, u32, u32]),
     "adam_b200_decoder_prefill": (c_int, [u32, u32]),
     "adam_b200_decoder_set_tokens": (c_int, [u32, c_void_p]),
+    "adam_b200_decoder_tokens_async": (c_int, [u32, POINTER(u32)]),
+    "adam_b200_decoder_tokens_wait": (c_int, [u32, u32, c_void_p]),
     "adam_b200_decoder_continue": (c_int, [u32, c_void_p, u32, u32, u32]),
     "adam_b200_decoder_n_parts": (c_int, [u32]),
     "adam_b200_decoder_step_part": (c_int, [u32, u32, u32]),

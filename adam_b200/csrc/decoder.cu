@@ -54,6 +54,7 @@ struct Decoder {
     uint32_t rows_cap;          // rows the activation buffers hold: max(max_batch, PREFILL_ROWS)
     std::vector<uint32_t> hpos, hplen;   // host mirror of positions and prompt lengths (argument checks)
     std::vector<int32_t> hbt;            // host mirror of the block table
+    int32_t* tok_ring[4]; cudaEvent_t tok_event[4]; uint32_t tok_next;   // pinned slots for asynchronous token reads
     uint32_t batch;             // active sequences
     bool use_tiles;             // build row-tiled weight copies for the tensor-core GEMV
     std::vector<uint32_t> free_pages;
@@ -730,6 +731,7 @@ static void free_graphs(Decoder* D) {
 static void destroy(Decoder* D) {
     cudaStreamSynchronize(g.stream);
     free_graphs(D);
+    for (int i = 0; i < 4; ++i) { if (D->tok_ring[i]) cudaFreeHost(D->tok_ring[i]); if (D->tok_event[i]) cudaEventDestroy(D->tok_event[i]); }
     void* ptrs[] = {D->pos, D->cur_tok, D->cur_val, D->prompt_len, D->prompt_tok, D->gen_log, D->block_table, D->kv_pool, D->hbuf[0], D->hbuf[1], D->qkv,
                     D->attn_out, D->proj, D->act, D->logits, D->part_o, D->part_ml, D->attn_ticket, D->row_seq, D->row_pos,
                     D->rope_cos[0], D->rope_sin[0], D->rope_cos[1], D->rope_sin[1]};
@@ -1174,6 +1176,35 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
     }
     end_of_op();
     return rc;
+}
+
+// Asynchronous read of the current tokens: tokens_async enqueues, behind everything issued so
+// far, a copy of the current token ids into one of four pinned slots and returns the slot;
+// tokens_wait blocks until that copy has landed (later work on the stream keeps running) and
+// hands the ids out.  Lets a caller keep the next step queued while it looks at the last ids.
+extern "C" int adam_b200_decoder_tokens_async(uint32_t id, uint32_t* slot_out) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (!slot_out || D->batch == 0) return fail(ADAMAH_ERR_INVALID, "decoder_tokens_async: no active sequences or null argument");
+    if (capturing()) return fail(ADAMAH_ERR_INVALID, "decoder_tokens_async: not allowed while a graph is being captured");
+    const uint32_t slot = D->tok_next;
+    D->tok_next = (slot + 1) & 3u;
+    if (!D->tok_ring[slot]) {
+        DCU(cudaMallocHost((void**)&D->tok_ring[slot], (size_t)D->d.max_batch * 4));
+        DCU(cudaEventCreateWithFlags(&D->tok_event[slot], cudaEventDisableTiming));
+    }
+    DCU(cudaMemcpyAsync(D->tok_ring[slot], D->cur_tok, (size_t)D->batch * 4, cudaMemcpyDeviceToHost, g.stream));
+    DCU(cudaEventRecord(D->tok_event[slot], g.stream));
+    *slot_out = slot;
+    return ADAMAH_OK;
+}
+extern "C" int adam_b200_decoder_tokens_wait(uint32_t id, uint32_t slot, int32_t* out) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (slot > 3 || !out || !D->tok_ring[slot]) return fail(ADAMAH_ERR_INVALID, "decoder_tokens_wait: bad slot");
+    DCU(cudaEventSynchronize(D->tok_event[slot]));
+    memcpy(out, D->tok_ring[slot], (size_t)D->batch * 4);
+    return ADAMAH_OK;
 }
 
 // Overwrite the current token of every active sequence (host-side sampling: the caller read the

@@ -264,8 +264,9 @@ class ADAMEngine:
     def generate_batch(self, prompts: Sequence[Sequence[int]], config: Optional[GenerationConfig] = None, sync_every: int = 1,
                        reuse_prefix: int = 0):
         """Greedy generation for independent sequences (one step advances all of them).
-        Returns (list of token lists, stats).  ``sync_every`` tokens are decoded between
-        host reads of the sampled ids (1 = the reference's per-token read, engine.py:1979)."""
+        Returns (list of token lists, stats).  The host reads every step's ids (as the reference does,
+        engine.py:1979) but asynchronously: up to ``sync_every`` (1..3) later steps are already queued
+        while it looks at them, so a sequence may run that many steps past its EOS before the loop stops."""
         config = config or GenerationConfig(top_k=1)
         mode = self._select_sampling_mode(config)
         if len(prompts) == 0 or len(prompts) > self._max_batch:
@@ -300,7 +301,6 @@ class ADAMEngine:
         td = time.perf_counter()
         n_steps = (max_len - min_len) + config.max_tokens          # steps that run the LM head
         eos = set(int(e) for e in config.eos_token_ids)
-        done_at = [None] * len(prompts)
         steps_done = 0
         d2h = 0
         sampled: List[List[int]] = [[] for _ in prompts]
@@ -331,39 +331,47 @@ class ADAMEngine:
                     if len(sampled[b]) >= config.max_tokens:
                         finished[b] = True
                 self.set_tokens(toks)
-        while mode != "cpu" and steps_done < n_steps:
-            k = min(sync_every, n_steps - steps_done)
+        if mode != "cpu":
+            # Greedy: the sampled id feeds the next step on the device, so the host only watches for EOS.  The
+            # ids of a step are fetched asynchronously while up to ``sync_every`` later steps are already queued.
+            import collections
+            import ctypes as _ct
+            finished = [False] * len(prompts)
+            pending = collections.deque()
+            buf = np.zeros(self._max_batch, np.int32)
+
+            def consume(step_no, slot):
+                nonlocal d2h
+                self._check(self._lib.adam_b200_decoder_tokens_wait(self._dec, slot, buf.ctypes.data), "adam_b200_decoder_tokens_wait")
+                d2h += 4 * len(prompts)
+                for b, n in enumerate(lens):
+                    if finished[b] or min_len + step_no < n:          # still inside its prompt
+                        continue
+                    t = int(buf[b])
+                    if t in eos:
+                        finished[b] = True
+                        continue
+                    sampled[b].append(t)
+                    if len(sampled[b]) >= config.max_tokens:
+                        finished[b] = True
+
+            depth = max(1, int(sync_every))
             g.batch_begin()
-            self.step(k, lm_head=True)
+            while steps_done < n_steps and not all(finished):
+                self.step(1, lm_head=True)
+                slot = _ct.c_uint32(0)
+                self._check(self._lib.adam_b200_decoder_tokens_async(self._dec, _ct.byref(slot)), "adam_b200_decoder_tokens_async")
+                pending.append((steps_done, int(slot.value)))
+                steps_done += 1
+                if len(pending) > min(depth, 3):
+                    consume(*pending.popleft())
+            while pending:
+                consume(*pending.popleft())
             g.batch_end()
-            steps_done += k
-            # sampled ids of the new positions
-            all_done = True
-            for b, n in enumerate(lens):
-                if done_at[b] is not None:
-                    continue
-                first = max(n, min_len + steps_done - k)
-                last = min(min_len + steps_done, n + config.max_tokens)
-                if last > first:
-                    ids = self.read_log(b, first, last - first)
-                    d2h += ids.nbytes
-                    for j, t in enumerate(ids):
-                        if int(t) in eos:
-                            done_at[b] = first + j
-                            break
-                if done_at[b] is None and min_len + steps_done < n + config.max_tokens:
-                    all_done = False
-            if all_done:
-                break
         t_dec = time.perf_counter() - td
         outs: List[List[int]] = []
         for b, n in enumerate(lens):
-            if mode == "cpu":
-                outs.append(sampled[b])
-                continue
-            end = done_at[b] if done_at[b] is not None else min(n + config.max_tokens, min_len + steps_done)
-            ids = self.read_log(b, n, max(0, end - n)) if end > n else np.empty(0, np.int32)
-            outs.append([int(t) for t in ids])
+            outs.append(sampled[b])
         ng = sum(len(o) for o in outs)
         stats = {
             "n_prompt": sum(lens), "n_prompt_total": sum(lens), "n_prompt_reused": reuse, "n_prompt_prefilled": sum(lens) - reuse,

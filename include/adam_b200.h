@@ -311,6 +311,11 @@ int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_t* prompt_t
 /* n_steps token steps.  flags: bit 0 LM head + arg-max, bit 1 also store logits,
  * bit 2 launch kernels directly (no graph replay). */
 int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t flags);
+/* Asynchronous read of the current token ids: tokens_async queues a copy into one of four pinned
+ * slots behind the work issued so far; tokens_wait blocks only until that copy has landed, so the
+ * caller can keep the next step queued while it inspects the last ids ([batch] values). */
+int adam_b200_decoder_tokens_async(uint32_t id, uint32_t* slot_out);
+int adam_b200_decoder_tokens_wait(uint32_t id, uint32_t slot, int32_t* out);
 /* Replace the current token of every active sequence ([batch] host ids): for callers that sample on
  * the host from the logits of the last step (the reference's 'cpu' sampling mode, engine.py:3711-3729). */
 int adam_b200_decoder_set_tokens(uint32_t id, const int32_t* tokens);
