@@ -9,8 +9,9 @@
 // + arg-max), with the arithmetic of the reference's numpy decoder
 // (tests/diagnostics/diag_inference.py:973-1037).  Differences from the reference
 // runtime, all additive: B independent sequences per step, a paged KV cache in
-// fp16 or fp32, an optional sliding-window mask on non-global layers, and rotary
-// angles read from a table the host supplies.
+// fp16 or fp32, an optional sliding-window mask on non-global layers, rotary angles
+// read from a table the host supplies, chunked prefill (many prompt positions per
+// pass), prefix reuse, and a part-wise step for tensor-parallel callers.
 #include "common.cuh"
 #include "gemv.cuh"
 #include "gemv_mma.cuh"

@@ -1,4 +1,4 @@
-// Tensor-core variant of the Q4_0 dequant GEMV over row-tiled weights (tile.cu).
+// Tensor-core variant of the Q4_0 / Q4_K dequant GEMV over row-tiled weights (tile.cu).
 //
 // Why tensor cores in a memory-bound GEMV: on the plain CUDA-core path the unpack
 // (one byte-permute per weight, on the half-rate integer pipe) and one FMA per weight
@@ -18,7 +18,12 @@
 //     is applied once per row group when the two are added.
 // The tensor pipe stays almost idle: the kernel is a stream over the weight bytes.
 //
-// Batch rows 2i and 2i+1 use MMA i of a block (NI = 1 or 2 MMAs per block, batch <= 4).
+// Q4_K blocks go through the same MMA; their tile carries the 6-bit scale and min as bytes
+// and the superblock's (d, dmin) per row, the block scale is d*sc and the offset term
+// -(dmin*m)*sum(x) replaces -8*d*sum(x).
+//
+// Batch rows 2i and 2i+1 use MMA i of a block (NI = 1 or 2 MMAs per block, four rows per
+// group); a call with more rows runs its groups as the fast grid dimension of one launch.
 // A warp owns one 16-row group and a slice of K; the KS warps that share a row group
 // combine through shared memory.  Weight tiles reach shared memory through a per-warp
 // ring of bulk copies (cp.async.bulk + mbarrier), so no load scoreboard limits the

@@ -1,16 +1,16 @@
-// Row-tiled copies of Q4_0 tensors for the tensor-core GEMV (gemv_mma.cuh).
+// Row-tiled copies of Q4_0 and Q4_K tensors for the tensor-core GEMV (gemv_mma.cuh).
 //
 // A GGUF-block map is a flat element array and does not know tensor shapes, so the
 // plane layout used by the generic kernels keeps rows apart (a row's blocks are
 // contiguous).  The tensor-core GEMV wants 16 rows of the same block side by side, in
 // the order its lanes consume them.  `adam_b200_tensor_tile` builds such a copy for one
-// [rows, cols] tensor of a Q4_0 map and registers it under (map, element offset, rows,
+// [rows, cols] tensor of a GGUF-block map and registers it under (map, element offset, rows,
 // cols); operators that are later called on exactly that tensor use the copy.  The
-// bytes are the same 18 per block (16 nibble bytes + fp16 scale), only their order
-// changes, so block decode stays bit-identical (role of the reference's load-time
+// Q4_0 bytes are the same 18 per block (16 nibble bytes + fp16 scale), only their order
+// changes, so block decode stays bit-identical; the Q4_K form is described at k_tile_q4_k (role of the reference's load-time
 // re-layout into its Q4 map, adam/models/engine.py:1049-1056).
 //
-// Tile pair = 16 rows x 2 blocks (64 weights per row) = 576 bytes:
+// Q4_0 tile pair = 16 rows x 2 blocks (64 weights per row) = 576 bytes:
 //   bytes   0..511  one uint4 per lane (lane = 4*g + t, g = 0..7, t = 0..3):
 //                   { block0: row g word t, row g+8 word t, block1: row g word t, row g+8 word t }
 //                   where word t of a block is its nibble bytes 4t..4t+3
