@@ -129,6 +129,15 @@ def shard_tensors(cfg, tensors: Dict[str, object], plan: ShardPlan):
     return local, out
 
 
+def merge_argmax_pairs(vals, ids):
+    """Winner over ranks of per-rank ``(max logit, global id)`` pairs, ``[world, batch]`` torch tensors:
+    the largest value wins, equal values go to the lower id (the single-GPU arg-max rule)."""
+    import torch
+    best = vals.max(dim=0).values
+    cand = torch.where(vals == best.unsqueeze(0), ids, torch.full_like(ids, 2 ** 31 - 1))
+    return cand.min(dim=0).values
+
+
 class _DeviceArray:
     """Just enough of the CUDA array interface for ``torch.as_tensor`` to alias library memory."""
 
@@ -225,10 +234,7 @@ class ADAMEngineTP(ADAMEngine):
                 ids = torch.empty(W * B, dtype=torch.int32, device=gid.device)
                 dist.all_gather_into_tensor(vals, self._val[:B].contiguous(), group=self._group)
                 dist.all_gather_into_tensor(ids, gid.contiguous(), group=self._group)
-                v, i = vals.view(W, B), ids.view(W, B)
-                best = v.max(dim=0).values
-                cand = torch.where(v == best.unsqueeze(0), i, torch.full_like(i, 2 ** 31 - 1))
-                self._tok[:B].copy_(cand.min(dim=0).values)
+                self._tok[:B].copy_(merge_argmax_pairs(vals.view(W, B), ids.view(W, B)))
 
     def step(self, n_steps: int = 1, lm_head: bool = True, logits: bool = False, direct: bool = False):
         torch = self._torch

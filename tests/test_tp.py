@@ -147,3 +147,53 @@ def test_two_ranks_match_the_oracle(ggml_type, allreduce):
     assert res["logit_rel_err"] < 1e-3
     assert res["graph_used"] and res["device_error"] == 0
     assert res["p2p_allreduce"] == (allreduce == "p2p")
+
+
+_TP_GLOO_SCRIPT = '''
+import json, os, sys
+sys.path.insert(0, %r)
+import numpy as np, torch, torch.distributed as dist
+from dataclasses import replace
+from adam_b200 import gguf_blocks as gb, synth
+from adam_b200.config import tiny_gemma3
+from adam_b200.tp import merge_argmax_pairs, shard_plan, shard_tensors
+from oracle.q4_blocks import dequant_q4_k
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo")
+cfg = replace(tiny_gemma3(), n_layer=1, n_embd=256, n_head=4, n_head_kv=2, head_dim=128, head_dim_kv=128, n_ff=768, n_vocab=512)
+tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_K, seed=5)
+deq = lambda t: dequant_q4_k(np.asarray(t.raw, np.uint8), t.rows * t.cols).reshape(t.rows, t.cols)
+plan = shard_plan(cfg, rank, world, gb.GGML_TYPE_Q4_K)
+local, lt = shard_tensors(cfg, tensors, plan)
+rng = np.random.default_rng(0)
+x_ff = rng.standard_normal(cfg.n_ff).astype(np.float32)          # same on every rank (seeded)
+z = rng.standard_normal(cfg.n_embd).astype(np.float32)
+# row-parallel down-proj: partial sums, all-reduce
+part = torch.from_numpy(deq(lt["blk.0.ffn_down.weight"]) @ x_ff[plan.ff.start:plan.ff.stop])
+dist.all_reduce(part)
+# vocabulary-parallel LM head: local arg-max pair, gather, merge (with a forced tie across ranks)
+logits = deq(lt["output.weight"]) @ z
+logits[3] = 1e6                                                    # every rank's row 3 ties at the top
+v = torch.tensor([float(logits.max())]); i = torch.tensor([int(logits.argmax()) + plan.vocab.start], dtype=torch.int32)
+vs = [torch.empty_like(v) for _ in range(world)]; is_ = [torch.empty_like(i) for _ in range(world)]
+dist.all_gather(vs, v); dist.all_gather(is_, i)
+tok = int(merge_argmax_pairs(torch.stack(vs), torch.stack(is_))[0])
+if rank == 0:
+    full = deq(tensors["blk.0.ffn_down.weight"]) @ x_ff
+    print(json.dumps({"down_err": float(np.abs(part.numpy() - full).max() / np.abs(full).max()), "tok": tok}))
+dist.destroy_process_group()
+'''
+
+
+def test_two_gloo_ranks_reduce_and_merge_like_the_tp_engine(tmp_path):
+    """The host side of tensor parallelism on CPU: shards from ``shard_tensors``, a gloo all-reduce of the
+    row-parallel partial sums, and the arg-max merge with a tie across ranks (lower id wins)."""
+    script = tmp_path / "tp_rank.py"
+    script.write_text(_TP_GLOO_SCRIPT % ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), str(script)]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    res = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert res["down_err"] < 1e-5
+    assert res["tok"] == 3                          # rank 0's row 3, not rank 1's row 3 (global id 259)
