@@ -117,7 +117,9 @@ _SIGS = {
     "adam_b200_decoder_tokens_async": (c_int, [u32, POINTER(u32)]),
     "adam_b200_decoder_tokens_wait": (c_int, [u32, u32, c_void_p]),
     "adam_b200_decoder_continue": (c_int, [u32, c_void_p, u32, u32, u32]),
+    "adam_b200_tc_gemm_count": (ctypes.c_uint64, []),
     "adam_b200_decoder_n_parts": (c_int, [u32]),
+    "adam_b200_decoder_prefill_part": (c_int, [u32, u32, u32]),
     "adam_b200_decoder_step_part": (c_int, [u32, u32, u32]),
     "adam_b200_decoder_buffer_ptr": (c_int, [u32, u32, POINTER(u64), POINTER(u64)]),
     "adam_b200_set_stream": (c_int, [u64]),

@@ -350,6 +350,10 @@ class Adamah:
     def kernel_launches(self) -> int:
         return int(self._lib.adam_b200_kernel_launches())
 
+    def tc_gemm_count(self) -> int:
+        """Matrix products enqueued so far on the tcgen05 GEMM (calls with 9..64 activation rows)."""
+        return int(self._lib.adam_b200_tc_gemm_count())
+
     def device_error(self) -> int:
         """Reads and clears the device error word (0 = none)."""
         return int(self._lib.adam_b200_device_error())

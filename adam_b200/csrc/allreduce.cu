@@ -2,11 +2,13 @@
 //
 // The reference has no multi-GPU path; this replaces an NCCL all-reduce of the 21 KB projection
 // vector, which costs ~12 us per call inside a CUDA graph and is issued 2 x n_layer times per
-// token.  One process per GPU; every rank owns a staging area in its own memory and maps its
+// token (and, in a prefill chunk, of up to 64 such rows).  One process per GPU; every rank owns a staging area in its own memory and maps its
 // peers' through CUDA IPC.
 //
 // Protocol of one call (number s, kept in device memory so that a replayed CUDA graph advances it
-// by itself; staging slot p = s & 1).  Data and hand-shake travel together, as in a low-latency
+// by itself; every CTA keeps a copy of the same number and CTA 0 also writes the copies of the CTAs
+// a smaller call does not launch, so calls of different sizes may follow one another; staging slot
+// p = s & 1).  Data and hand-shake travel together, as in a low-latency
 // ring protocol: every pair of floats is sent as one 16-byte packet { x, s, y, s } whose two 8-byte
 // halves each carry the call number, so the receiver needs no separate flag and no fence.
 //   1. every thread reads its floats of the buffer and stores the packets into region
@@ -19,8 +21,9 @@
 // s + 2, which it reaches only after my packets of call s + 1 arrived, i.e. after I finished call s.
 // Sums are formed in rank order on every rank, so all ranks get the same bits.  Launched like the
 // decoder's kernels: it waits for the producer of the buffer with the programmatic-dependency wait
-// and lets the next kernel (a GEMV) start its weight prefetch at once.  All calls between two
-// host-side synchronisations of the ranks must have the same size.
+// and lets the next kernel (a GEMV) start its weight prefetch at once.  A packet at a given
+// place of a slot only ever carries growing call numbers, so a stale one is never taken for the
+// expected one whatever the sizes of earlier calls were.
 #include "common.cuh"
 
 #include <cstring>
@@ -28,7 +31,7 @@
 namespace ab {
 
 constexpr uint32_t AR_MAX_RANKS = 8;
-constexpr uint32_t AR_MAX_CTAS = 32;
+constexpr uint32_t AR_MAX_CTAS = 64;
 constexpr uint32_t AR_MAX_COMMS = 4;
 constexpr int AR_POLL_LIMIT = 1 << 20;      // about a second of polling
 
@@ -93,6 +96,7 @@ __global__ void __launch_bounds__(256) k_allreduce(float* __restrict__ buf, uint
     }
     __syncthreads();
     if (tid == 0) *counter = s;
+    if (c == 0 && tid >= gridDim.x && tid < AR_MAX_CTAS) state[tid] = s;   // copies of the CTAs this call did not launch
 }
 
 static ArComm* get_ar(uint32_t id) { return (id < AR_MAX_COMMS && g_ar[id].used) ? &g_ar[id] : nullptr; }

@@ -15,6 +15,7 @@
 #include "common.cuh"
 #include "gemv.cuh"
 #include "gemv_mma.cuh"
+#include "gemm_tc.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -793,6 +794,7 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
 static int gemv(const Mat& m, const Mat* m2, GemvArgs a, int B, int epi) {
     a.w0 = m.w; if (m2) a.w1 = m2->w;
     a.N = (int)m.rows; a.K = (int)m.cols; a.B = B; a.epi = epi;
+    if (B >= TC_MIN_ROWS && (!m2 || m2->wtype == m.wtype) && gemm_tc_supports(m.wtype, a)) return launch_gemm_tc(m.wtype, a, g.stream);
     if (m.tiled && (!m2 || (m2->tiled && m2->wtype == m.wtype)) && gemv_mma_supports(m.wtype, a))
         return launch_gemv_mma(m.wtype, m.tiled, m2 ? m2->tiled : nullptr, a, g.stream);
     return launch_gemv(m.wtype, a, g.stream);
@@ -947,6 +949,7 @@ extern "C" int adam_b200_decoder_create(const adam_b200_decoder_desc* desc, uint
     D->n_splits = (d.kv_cap + ATTN_SPLIT - 1) / ATTN_SPLIT;      // ATTN_SPLIT = ATTN_CP * ATTN_CHUNKS_PER_CTA
     if (D->n_splits > ATTN_MAX_SPLITS) D->n_splits = ATTN_MAX_SPLITS;
     D->rows_cap = d.max_batch > PREFILL_ROWS ? d.max_batch : PREFILL_ROWS;
+    gemm_tc_prepare();                          // workspace of the many-row GEMM (without it those rows run on the GEMV kernels)
     const size_t B = d.max_batch, R = D->rows_cap, E = d.n_embd, q_dim = (size_t)d.n_head * d.head_dim, k_dim = (size_t)d.n_head_kv * d.head_dim;
     const uint32_t gs = d.n_head / d.n_head_kv;
     g_dec[id] = D;
@@ -1246,20 +1249,31 @@ static int launch_kv_append_t(Decoder* D, uint32_t L, uint32_t rows) {
     return ADAMAH_OK;
 }
 
-static int enqueue_prefill_chunk(Decoder* D, uint32_t batch, uint32_t T) {
+// One part of a prefill chunk of T tokens per sequence; parts as in enqueue_part (2L = attention half
+// of layer L, preceded by the row set-up and the embedding for L = 0; 2L+1 = FFN half), and part
+// 2*n_layer advances the positions by T.
+static int enqueue_prefill_part(Decoder* D, uint32_t batch, uint32_t T, uint32_t part) {
     const adam_b200_decoder_desc& d = D->d;
     const uint32_t rows = batch * T;
     const uint32_t E = d.n_embd, q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim, qkv_ld = q_dim + 2 * k_dim;
     int rc;
-    k_prefill_rows<<<(rows + 63) / 64, 64, 0, g.stream>>>(D->pos, batch, T, D->row_seq, D->row_pos);
-    count_launch();
-    if (D->embd.wtype == WT_Q4_0)
-        launch_k(k_embed<WT_Q4_0>, dim3(rows), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], (const int32_t*)D->row_seq, (const int32_t*)D->row_pos, g.dev_err);
-    else
-        launch_k(k_embed<WT_Q4_K>, dim3(rows), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], (const int32_t*)D->row_seq, (const int32_t*)D->row_pos, g.dev_err);
-    count_launch();
-    for (uint32_t L = 0; L < d.n_layer; ++L) {
-        const Layer& ly = D->layers[L];
+    if (part == 2 * d.n_layer) {
+        launch_k(k_advance_n, dim3((batch + 63) / 64), dim3(64), 0, g.stream, g.pdl, D->pos, batch, (int32_t)T);
+        count_launch();
+        return check_launch("decoder prefill");
+    }
+    const uint32_t L = part / 2;
+    const Layer& ly = D->layers[L];
+    if (!(part & 1u)) {
+        if (L == 0) {
+            k_prefill_rows<<<(rows + 63) / 64, 64, 0, g.stream>>>(D->pos, batch, T, D->row_seq, D->row_pos);
+            count_launch();
+            if (D->embd.wtype == WT_Q4_0)
+                launch_k(k_embed<WT_Q4_0>, dim3(rows), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], (const int32_t*)D->row_seq, (const int32_t*)D->row_pos, g.dev_err);
+            else
+                launch_k(k_embed<WT_Q4_K>, dim3(rows), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], (const int32_t*)D->row_seq, (const int32_t*)D->row_pos, g.dev_err);
+            count_launch();
+        }
         const int cur = L == 0 ? 0 : 1;
         GemvArgs in = {};
         in.ldx = (int)E; in.eps = d.norm_eps; in.h_in = D->hbuf[cur]; in.w_pre = ly.norm[NORM_ATTN];
@@ -1283,6 +1297,7 @@ static int enqueue_prefill_chunk(Decoder* D, uint32_t batch, uint32_t T) {
         GemvArgs o = {};
         o.x = D->attn_out; o.ldx = (int)q_dim; o.y = D->proj; o.ldy = (int)E;
         if ((rc = gemv(ly.m[MAT_O], nullptr, o, rows, EPI_STORE))) return rc;
+    } else {
         GemvArgs gu = {};
         gu.ldx = (int)E; gu.eps = d.norm_eps; gu.h_in = D->hbuf[0]; gu.add_src = D->proj; gu.w_post = ly.norm[NORM_POST_ATTN];
         gu.w_pre = ly.norm[NORM_FFN]; gu.h_out = D->hbuf[1]; gu.y = D->act; gu.ldy = (int)d.n_ff;
@@ -1291,9 +1306,37 @@ static int enqueue_prefill_chunk(Decoder* D, uint32_t batch, uint32_t T) {
         dn.x = D->act; dn.ldx = (int)d.n_ff; dn.y = D->proj; dn.ldy = (int)E;
         if ((rc = gemv(ly.m[MAT_DOWN], nullptr, dn, rows, EPI_STORE))) return rc;
     }
-    launch_k(k_advance_n, dim3((batch + 63) / 64), dim3(64), 0, g.stream, g.pdl, D->pos, batch, (int32_t)T);
-    count_launch();
     return check_launch("decoder prefill");
+}
+
+static int enqueue_prefill_chunk(Decoder* D, uint32_t batch, uint32_t T) {
+    for (uint32_t part = 0; part <= 2 * D->d.n_layer; ++part) {
+        const int rc = enqueue_prefill_part(D, batch, T, part);
+        if (rc) return rc;
+    }
+    return ADAMAH_OK;
+}
+
+// One part of one prefill chunk of n_tokens (<= 64 / batch) tokens per sequence, for tensor-parallel
+// callers: parts 0 .. 2*n_layer-1 as in adam_b200_decoder_step_part (all-reduce the projection
+// buffer, batch * n_tokens rows, after each), part 2*n_layer advances the positions.
+extern "C" int adam_b200_decoder_prefill_part(uint32_t id, uint32_t n_tokens, uint32_t part) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (D->batch == 0) return fail(ADAMAH_ERR_INVALID, "decoder_prefill_part: call decoder_begin first");
+    if (part > 2 * D->d.n_layer) return fail(ADAMAH_ERR_INVALID, "decoder_prefill_part: part %u of %u", part, 2 * D->d.n_layer + 1);
+    if (n_tokens == 0 || (uint64_t)n_tokens * D->batch > D->rows_cap) return fail(ADAMAH_ERR_INVALID, "decoder_prefill_part: a chunk holds at most %u rows", D->rows_cap);
+    if (part == 0)
+        for (uint32_t b = 0; b < D->batch; ++b)
+            if ((uint64_t)D->hpos[b] + n_tokens > D->hplen[b])
+                return fail(ADAMAH_ERR_INVALID, "decoder_prefill_part: sequence %u has only %u prompt tokens left", b, D->hplen[b] - D->hpos[b]);
+    static const bool allow = !(getenv("ADAM_B200_PDL") && atoi(getenv("ADAM_B200_PDL")) == 0);
+    g.pdl = allow;
+    const int rc = enqueue_prefill_part(D, D->batch, n_tokens, part);
+    g.pdl = false;
+    if (rc == ADAMAH_OK && part == 2 * D->d.n_layer) for (uint32_t& hp : D->hpos) hp += n_tokens;
+    end_of_op();
+    return rc;
 }
 
 extern "C" int adam_b200_decoder_prefill(uint32_t id, uint32_t n_tokens) {
@@ -1345,7 +1388,8 @@ extern "C" int adam_b200_decoder_step_part(uint32_t id, uint32_t part, uint32_t 
 }
 // Device address and size of one of the decoder's buffers, for callers that run their own
 // kernels or collectives on them (same stream, see adam_b200_set_stream):
-//   0 = projection output [batch][n_embd] f32 (what a tensor-parallel caller all-reduces)
+//   0 = projection output [rows][n_embd] f32 (what a tensor-parallel caller all-reduces; rows =
+//       batch in a decode step, batch * n_tokens in a prefill chunk; sized for max(max_batch, 64) rows)
 //   1 = current token ids [max_batch] i32     2 = their logit values [max_batch] f32
 //   3 = positions [max_batch] i32
 extern "C" int adam_b200_decoder_buffer_ptr(uint32_t id, uint32_t which, uint64_t* ptr_out, uint64_t* bytes_out) {
@@ -1354,7 +1398,7 @@ extern "C" int adam_b200_decoder_buffer_ptr(uint32_t id, uint32_t which, uint64_
     if (!ptr_out || !bytes_out) return fail(ADAMAH_ERR_INVALID, "decoder_buffer_ptr: null argument");
     const size_t B = D->d.max_batch;
     switch (which) {
-    case 0: *ptr_out = (uint64_t)(uintptr_t)D->proj; *bytes_out = B * D->d.n_embd * 4; break;
+    case 0: *ptr_out = (uint64_t)(uintptr_t)D->proj; *bytes_out = (size_t)D->rows_cap * D->d.n_embd * 4; break;
     case 1: *ptr_out = (uint64_t)(uintptr_t)D->cur_tok; *bytes_out = B * 4; break;
     case 2: *ptr_out = (uint64_t)(uintptr_t)D->cur_val; *bytes_out = B * 4; break;
     case 3: *ptr_out = (uint64_t)(uintptr_t)D->pos; *bytes_out = B * 4; break;

@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "gemv.cuh"
 #include "gemv_mma.cuh"
+#include "gemm_tc.cuh"
 
 #include <cstring>
 
@@ -470,6 +471,12 @@ int weight_ref(const Map* m, uint64_t off, uint64_t n_elems, int* wtype, WeightR
 // Run a GEMV on the tensor at (map, off): the tensor-core kernel when a row-tiled
 // copy of exactly this tensor is registered and the shape fits, the generic one otherwise.
 int run_gemv(uint32_t map_id, uint64_t off, int wtype, GemvArgs& ga) {
+    if (ga.B >= TC_MIN_ROWS) {
+        // many rows: the tcgen05 GEMM (its workspace is allocated on first use, never inside a capture)
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(g.stream, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone) gemm_tc_prepare();
+        if (gemm_tc_supports(wtype, ga)) return launch_gemm_tc(wtype, ga, g.stream);
+    }
     if (ga.epi != EPI_GEGLU && ga.epi != EPI_SWIGLU) {
         const void* t = find_tiled(map_id, off, (uint32_t)ga.N, (uint32_t)ga.K);
         if (t && gemv_mma_supports(wtype, ga)) return launch_gemv_mma(wtype, (const uint8_t*)t, nullptr, ga, g.stream);

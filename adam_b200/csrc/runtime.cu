@@ -239,7 +239,7 @@ extern "C" int adamah_init_ex(uint64_t, uint64_t) {
 }
 extern "C" int adamah_init(void) { return adamah_init_ex(0, 0); }
 
-namespace ab { void decoder_destroy_all(); void plans_clear_all(); void tiled_drop_map(uint32_t map_id); void ar_destroy_all(); }
+namespace ab { void decoder_destroy_all(); void plans_clear_all(); void tiled_drop_map(uint32_t map_id); void ar_destroy_all(); void gemm_tc_release(); }
 
 extern "C" void adamah_shutdown(void) {
     if (!g.inited) return;
@@ -247,6 +247,7 @@ extern "C" void adamah_shutdown(void) {
     cudaStreamSynchronize(g.stream);
     ar_destroy_all();
     decoder_destroy_all();
+    gemm_tc_release();
     plans_clear_all();
     tiled_drop_map(0xFFFFFFFFu);
     for (uint32_t i = 0; i < MAX_MAPS; ++i) if (g.maps[i].used) { cudaFree(g.maps[i].buf); cudaFree(g.maps[i].qparams); }

@@ -32,6 +32,8 @@ from .engine import ADAMEngine, STEP_LM, STEP_LOGITS
 from .replicas import shard_sequences
 from .synth import QTensor
 
+PREFILL_ROWS = 64      # (sequence, position) rows of one prefill pass; the library's buffers hold max(max_batch, 64)
+
 
 @dataclasses.dataclass
 class ShardPlan:
@@ -176,11 +178,12 @@ class ADAMEngineTP(ADAMEngine):
         super().__init__(gpu, local_cfg, local_t, tp_rank=rank, tp_size=world, **kw)
         self._n_parts = int(self._lib.adam_b200_decoder_n_parts(self._dec))
         self._ar = None
+        self._rows_cap = max(self._max_batch, PREFILL_ROWS)     # rows of the activation buffers (a prefill chunk fills them)
         if self._collectives and allreduce == "p2p":
-            self._ar = self._open_peer_allreduce(cfg.n_embd * self._max_batch * 4)
+            self._ar = self._open_peer_allreduce(cfg.n_embd * self._rows_cap * 4)
         dev = f"cuda:{gpu.device_index}"
         mb = self._max_batch
-        self._proj = torch.as_tensor(_DeviceArray(self._buf(0), mb * cfg.n_embd, "<f4"), device=dev).view(mb, cfg.n_embd)
+        self._proj = torch.as_tensor(_DeviceArray(self._buf(0), self._rows_cap * cfg.n_embd, "<f4"), device=dev).view(self._rows_cap, cfg.n_embd)
         self._tok = torch.as_tensor(_DeviceArray(self._buf(1), mb, "<i4"), device=dev)
         self._val = torch.as_tensor(_DeviceArray(self._buf(2), mb, "<f4"), device=dev)
 
@@ -223,10 +226,7 @@ class ADAMEngineTP(ADAMEngine):
             if not self._collectives:
                 continue
             if part < L2:
-                if self._ar is not None:
-                    self._check(self._lib.adam_b200_ar_allreduce(self._ar, self._proj.data_ptr(), B * self.full_cfg.n_embd), "adam_b200_ar_allreduce")
-                else:
-                    dist.all_reduce(self._proj[:B], group=self._group)
+                self._reduce_proj(B)
             elif part == L2 and (flags & STEP_LM):
                 # (value, global id) of every rank's best row; the best value wins, ties go to the lower id
                 gid = self._tok[:B] + self.plan.vocab.start
@@ -257,10 +257,33 @@ class ADAMEngineTP(ADAMEngine):
                         self._one_step(flags)
                     self._graphs[key] = gr
 
-    def prefill(self, n_tokens: int):
-        """Token by token here: a chunked pass would need the collectives inside it."""
-        if n_tokens > 0:
+    def _reduce_proj(self, rows: int):
+        if self._ar is not None:
+            self._check(self._lib.adam_b200_ar_allreduce(self._ar, self._proj.data_ptr(), rows * self.full_cfg.n_embd), "adam_b200_ar_allreduce")
+        else:
+            import torch.distributed as dist
+            dist.all_reduce(self._proj[:rows], group=self._group)
+
+    def prefill(self, n_tokens: int, chunked: bool = True):
+        """Consumes ``n_tokens`` prompt positions of every sequence without the LM head, in chunks of
+        up to 64 (sequence, position) rows per pass over this rank's weights, the partial sums of the
+        o- and down-projections (one row per chunk row) all-reduced after each half layer."""
+        if n_tokens <= 0:
+            return
+        if not chunked:
             self.step(n_tokens, lm_head=False)
+            return
+        t_max = max(1, self._rows_cap // self._batch)
+        L2 = 2 * self.cfg.n_layer
+        with self._torch.cuda.stream(self._stream):
+            left = n_tokens
+            while left > 0:
+                T = min(t_max, left)
+                for part in range(L2 + 1):
+                    self._check(self._lib.adam_b200_decoder_prefill_part(self._dec, T, part), "adam_b200_decoder_prefill_part")
+                    if self._collectives and part < L2:
+                        self._reduce_proj(self._batch * T)
+                left -= T
 
     def begin(self, prompts, reserve):
         super().begin(prompts, reserve)

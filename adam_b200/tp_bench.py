@@ -77,6 +77,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="truncate the depth (say so when quoting the number)")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=16)
+    ap.add_argument("--token-prefill", action="store_true", help="consume the prompt one position per step instead of in 64-row chunks")
     ap.add_argument("--type", type=int, default=gb.GGML_TYPE_Q4_K)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"], help="library peer-memory all-reduce or torch.distributed NCCL")
@@ -104,10 +105,17 @@ def main():
     del tensors
     prompts = [list(map(int, np.random.default_rng(b).integers(0, cfg.n_vocab, a.prompt))) for b in range(a.batch)]
     eng.begin(prompts, [kv_cap] * a.batch)
+    pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     gpu.batch_begin()
-    eng.step(a.prompt - 1, lm_head=False)
+    with torch.cuda.stream(eng._stream):
+        pe0.record()
+    eng.prefill(a.prompt - 1, chunked=not a.token_prefill)
+    with torch.cuda.stream(eng._stream):
+        pe1.record()
     eng.step(max(3, a.warmup), lm_head=True)
     gpu.batch_end()
+    pe1.synchronize()
+    pre_ms = pe0.elapsed_time(pe1)
     if world > 1:
         dist.barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -139,6 +147,8 @@ def main():
                           "n_gpus": world, "steps": a.steps, "ms_per_step": ms_tok, "batch": a.batch, "n_layer": cfg.n_layer,
                           "weights": "Q4_K" if a.type == gb.GGML_TYPE_Q4_K else "Q4_0", "parallelism": f"tp{tp_world}" + ("" if tp_world == world else " (one shard, no collectives)"),
                           "weight_bytes_per_rank_per_step": int(w_bytes), "GBs_per_gpu": w_bytes / (ms_tok * 1e-3) / 1e9,
+                          "prefill_tok_s": a.batch * (a.prompt - 1) / (pre_ms * 1e-3) if a.prompt > 1 else None,
+                          "prefill": "token by token" if a.token_prefill else "64 rows per pass",
                           "collectives_per_step": 2 * cfg.n_layer + 2 if world > 1 else 0, "graph": graph_used, "allreduce": ("p2p" if ar_used else "nccl") if world > 1 else None, "device_error": int(err),
                           "data": "synthetic random blocks"}))
     if world > 1:

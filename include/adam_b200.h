@@ -335,6 +335,13 @@ int adam_b200_decoder_prefill(uint32_t id, uint32_t n_tokens);
  * this shard's partial sums.  No counterpart in the reference (it has no multi-GPU path). */
 int adam_b200_decoder_n_parts(uint32_t id);                                   /* 2*n_layer + 2, or a negative status */
 int adam_b200_decoder_step_part(uint32_t id, uint32_t part, uint32_t flags);
+/* Number of matrix products enqueued so far on the tcgen05 (tensor memory) GEMM, which takes calls
+ * with 9..64 activation rows; calls with fewer rows run on the GEMV kernels. */
+uint64_t adam_b200_tc_gemm_count(void);
+/* One part of one prefill chunk of n_tokens (batch * n_tokens <= 64 rows) tokens per sequence: parts
+ * 0 .. 2*n_layer-1 as above (the projection buffer then holds batch * n_tokens rows of partial
+ * sums), part 2*n_layer advances the positions by n_tokens. */
+int adam_b200_decoder_prefill_part(uint32_t id, uint32_t n_tokens, uint32_t part);
 /* Device address / size of a decoder buffer: 0 projection output [batch][n_embd] f32,
  * 1 current token ids [max_batch] i32, 2 their logit values [max_batch] f32, 3 positions. */
 int adam_b200_decoder_buffer_ptr(uint32_t id, uint32_t which, uint64_t* ptr_out, uint64_t* bytes_out);

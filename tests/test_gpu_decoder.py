@@ -177,7 +177,10 @@ def test_chunked_prefill_equals_token_by_token(gpu, ggml_type, kv_dtype, window)
         got_logits = np.stack([eng.read_logits(b) for b in range(3)])
         gpu.batch_begin(); eng.step(8, lm_head=True); gpu.batch_end()
         got_ids = [eng.read_log(b, n_pre + 1, 9) for b in range(3)]
-        assert np.abs(got_logits - ref_logits).max() <= 1e-5 * np.abs(ref_logits).max()
+        # the chunk's products run on another kernel (other summation order); with an f16 cache a last-bit
+        # difference can move a cached value by one f16 step, hence the wider bound there
+        tol = 1e-3 if kv_dtype == "f16" else 2e-5
+        assert np.abs(got_logits - ref_logits).max() <= tol * np.abs(ref_logits).max()
         for a, b in zip(ref_ids, got_ids):
             assert np.array_equal(a, b)
         assert gpu.device_error() == 0

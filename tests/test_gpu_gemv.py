@@ -123,6 +123,23 @@ def test_tensor_core_path_many_batch_rows(gpu, ggml_type, N, K, B):
         _check(y[b:b + 1], W, x[b:b + 1])
 
 
+@pytest.mark.parametrize("ggml_type,N,K,B", [(2, 1152, 1152, 64), (2, 300, 1152, 9), (2, 128, 6912, 33), (2, 1536, 256, 17), (2, 16, 32, 12),
+                                             (12, 256, 1024, 64), (12, 2048, 5376, 40), (12, 72, 256, 10)])
+def test_tcgen05_gemm_many_rows(gpu, ggml_type, N, K, B):
+    """9..64 activation rows run as one tcgen05 GEMM (integer products in tensor memory, block scales in
+    fp32): every row within 1e-3 of the dequantised reference, tile edges (N not a multiple of 128),
+    a ragged last K chunk and K splits included; the call counter shows the path was taken."""
+    rng = np.random.default_rng(7 * N + K + B)
+    raw = (gb.random_q4_0_blocks if ggml_type == 2 else gb.random_q4_k_blocks)(rng, N, K)
+    x = rng.standard_normal((B, K), dtype=np.float32) * rng.uniform(0.01, 100.0, (B, 1)).astype(np.float32)
+    before = gpu.tc_gemm_count()
+    y = _gemv(gpu, ggml_type, raw, N, K, x)
+    assert gpu.tc_gemm_count() == before + 1
+    W = q4_blocks.dequant(raw.reshape(-1), ggml_type, N, K)
+    for b in range(B):
+        _check(y[b:b + 1], W, x[b:b + 1])
+
+
 def test_tensor_core_path_at_offset_and_bad_shapes(gpu):
     rng = np.random.default_rng(123)
     N, K = 96, 1152

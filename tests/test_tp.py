@@ -144,6 +144,7 @@ def test_two_ranks_match_the_oracle(ggml_type, allreduce):
     assert out.returncode == 0, (out.stdout[-1500:], out.stderr[-3000:])
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
     assert res["ids_equal"], res
+    assert res["long_ids_equal"] and res["long_equals_by_token"], res      # chunked prefill across ranks
     assert res["logit_rel_err"] < 1e-3
     assert res["graph_used"] and res["device_error"] == 0
     assert res["p2p_allreduce"] == (allreduce == "p2p")
