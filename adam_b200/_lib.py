@@ -118,6 +118,7 @@ _SIGS = {
     "adam_b200_decoder_tokens_wait": (c_int, [u32, u32, c_void_p]),
     "adam_b200_decoder_continue": (c_int, [u32, c_void_p, u32, u32, u32]),
     "adam_b200_tc_gemm_count": (ctypes.c_uint64, []),
+    "adam_b200_tc_gemm_policy": (c_int, [c_int]),
     "adam_b200_decoder_n_parts": (c_int, [u32]),
     "adam_b200_decoder_prefill_part": (c_int, [u32, u32, u32]),
     "adam_b200_decoder_step_part": (c_int, [u32, u32, u32]),

@@ -354,6 +354,10 @@ class Adamah:
         """Matrix products enqueued so far on the tcgen05 GEMM (calls with 9..64 activation rows)."""
         return int(self._lib.adam_b200_tc_gemm_count())
 
+    def tc_gemm_policy(self, policy: int):
+        """0 = never take the tcgen05 GEMM, 1 = where it is expected to be faster (default), 2 = whenever the shape allows."""
+        self._check(self._lib.adam_b200_tc_gemm_policy(int(policy)), "adam_b200_tc_gemm_policy")
+
     def device_error(self) -> int:
         """Reads and clears the device error word (0 = none)."""
         return int(self._lib.adam_b200_device_error())

@@ -42,11 +42,15 @@ namespace ab {
 constexpr int TC_PLANES = 2;
 constexpr int TC_N = TC_PLANES * TC_COLS;                // 128 B-operand rows
 constexpr int TC_CH = 4;                                 // K blocks per chunk
-constexpr int TC_KG_STEP = 128 * 16;                     // bytes between groups of 8 values of K (both operands have 128 rows)
-constexpr int TC_A_STRIDE = 128 * 32 * 2;                // bytes of one K block of the A image (fp16)
-constexpr int TC_B_BLK = TC_N * 32 * 2;                  // 8192
-constexpr int TC_B_STRIDE = TC_B_BLK + TC_COLS * 4;      // + the block's 64 row sums
-constexpr int TC_SMEM = TC_CH * (TC_A_STRIDE + 2 * TC_B_STRIDE);    // 100352: A image + two B buffers; two CTAs per SM, never three (TMEM holds two allocations)
+// Operand images, K-major with the 128-byte swizzle: a "pair" image holds two K blocks (64 fp16 = 128
+// bytes per operand row) of 128 operand rows = 16 KB: 8-row groups of 1024 bytes, a row's 128 bytes
+// contiguous, and the 16-byte piece c of row r stored at piece c ^ (r & 7).  Images start at
+// multiples of 1024 bytes (the swizzle works on address bits).
+constexpr int TC_PAIR_IMG = 128 * 128;                   // 16384
+constexpr int TC_A_CHUNK = (TC_CH / 2) * TC_PAIR_IMG;    // 32768
+constexpr int TC_B_SUMS = TC_A_CHUNK;                    // offset of the chunk's [4][64] row sums in the B chunk image
+constexpr int TC_B_CHUNK = TC_A_CHUNK + TC_CH * TC_COLS * 4;        // 33792 = 33 * 1024
+constexpr int TC_SMEM = TC_A_CHUNK + 2 * TC_B_CHUNK + 1024;         // A image + two B buffers (+ alignment slack); two CTAs per SM, never three (TMEM holds two allocations)
 constexpr int TC_TMEM_COLS = 256;
 constexpr int TC_THREADS = 256;                         // two warps per TMEM lane quarter: each takes 32 of the 64 columns
 constexpr int TC_MYCOLS = TC_COLS / 2;
@@ -57,10 +61,11 @@ constexpr int TC_MAX_TILES = 4096;
 struct TcWork { uint8_t* bimg; float* inv; float* part; unsigned int* tickets; bool ok; };
 static TcWork g_tc = {};
 static uint64_t g_tc_calls = 0;
+static int g_tc_policy = -1;             // 0 never, 1 where it is expected to be faster, 2 whenever the shape allows; -1 = take it from ADAM_B200_TC
 
 bool gemm_tc_prepare() {
     if (g_tc.ok) return true;
-    const size_t bimg_bytes = (size_t)(TC_MAX_K / 32) * TC_B_STRIDE;
+    const size_t bimg_bytes = (size_t)(TC_MAX_K / 32 / TC_CH) * TC_B_CHUNK;
     if (cudaMalloc(&g_tc.bimg, bimg_bytes) != cudaSuccess || cudaMalloc(&g_tc.inv, TC_COLS * 4) != cudaSuccess ||
         cudaMalloc(&g_tc.part, (size_t)TC_MAX_CTAS * TC_COLS * 128 * 4) != cudaSuccess ||
         cudaMalloc(&g_tc.tickets, TC_MAX_TILES * 4) != cudaSuccess) {
@@ -79,10 +84,14 @@ void gemm_tc_release() {
     g_tc = TcWork{};
 }
 
-// Byte offset of (operand row n, value k of the block's 32) in a K-major fp16 core-matrix image of 128
-// rows: 8 rows x 8 values (16 bytes) are contiguous, 8-row groups follow each other, and the next 8
-// values of K lie 128 * 16 bytes further.
-__device__ __forceinline__ int core_off(int n, int k) { return (k >> 3) * TC_KG_STEP + (n >> 3) * 128 + (n & 7) * 16 + (k & 7) * 2; }
+// Byte offset of (operand row n, byte kb of the row's 128) in a pair image.
+__device__ __forceinline__ int swz_off(int n, int kb) { return (n >> 3) * 1024 + (n & 7) * 128 + ((((kb >> 4) ^ n) & 7) << 4) + (kb & 15); }
+// Byte offset in the B image of the 4 values k0 .. k0+3 (k0 a multiple of 4) of operand row n, and of block kb's row sums.
+__device__ __forceinline__ size_t bimg_off(int n, int k0) {
+    const int kb = k0 >> 5;
+    return (size_t)(kb >> 2) * TC_B_CHUNK + ((kb >> 1) & 1) * TC_PAIR_IMG + swz_off(n, (kb & 1) * 64 + (k0 & 31) * 2);
+}
+__device__ __forceinline__ size_t bsum_off(int kb) { return (size_t)(kb >> 2) * TC_B_CHUNK + TC_B_SUMS + (kb & 3) * (TC_COLS * 4); }
 
 // ---- activations: chain, scale, two fp16 planes in B-operand order -------------------------------
 // Four consecutive activations (k = 4i .. 4i+3) of column `col`, already scaled: round to integers,
@@ -106,10 +115,9 @@ __device__ __forceinline__ void put_planes(uint8_t* __restrict__ bimg, int col, 
     sum += __shfl_xor_sync(0xffffffffu, sum, 4);
     if (on) {
         const int k0 = 4 * i;
-        uint8_t* blk = bimg + (size_t)(k0 >> 5) * TC_B_STRIDE;
-        *reinterpret_cast<uint2*>(blk + core_off(col, k0 & 31)) = *reinterpret_cast<const uint2*>(hi);
-        *reinterpret_cast<uint2*>(blk + core_off(TC_COLS + col, k0 & 31)) = *reinterpret_cast<const uint2*>(lo);
-        if ((k0 & 31) == 0) reinterpret_cast<float*>(blk + TC_B_BLK)[col] = (float)sum;
+        *reinterpret_cast<uint2*>(bimg + bimg_off(col, k0)) = *reinterpret_cast<const uint2*>(hi);
+        *reinterpret_cast<uint2*>(bimg + bimg_off(TC_COLS + col, k0)) = *reinterpret_cast<const uint2*>(lo);
+        if ((k0 & 31) == 0) reinterpret_cast<float*>(bimg + bsum_off(k0 >> 5))[col] = (float)sum;
     }
 }
 
@@ -125,10 +133,9 @@ __global__ void __launch_bounds__(QR_THREADS) k_quant_rows(const GemvArgs a, uin
     if (col >= a.B) {                                   // unused columns multiply as zeros
         for (int i = tid; i < n4; i += blockDim.x) {
             const int k0 = 4 * i;
-            uint8_t* blk = bimg + (size_t)(k0 >> 5) * TC_B_STRIDE;
 #pragma unroll
-            for (int p = 0; p < TC_PLANES; ++p) *reinterpret_cast<uint2*>(blk + core_off(p * TC_COLS + col, k0 & 31)) = make_uint2(0u, 0u);
-            if ((k0 & 31) == 0) reinterpret_cast<float*>(blk + TC_B_BLK)[col] = 0.f;
+            for (int p = 0; p < TC_PLANES; ++p) *reinterpret_cast<uint2*>(bimg + bimg_off(p * TC_COLS + col, k0)) = make_uint2(0u, 0u);
+            if ((k0 & 31) == 0) reinterpret_cast<float*>(bimg + bsum_off(k0 >> 5))[col] = 0.f;
         }
         if (tid == 0) inv_out[col] = 0.f;
         return;
@@ -237,11 +244,12 @@ __global__ void __launch_bounds__(QR_THREADS) k_quant_rows(const GemvArgs a, uin
 }
 
 // ---- tcgen05 primitives --------------------------------------------------------------------------
-// Shared-memory matrix descriptor, K-major, no swizzle: start address, the byte distance between
-// core matrices along K ("leading" offset) and between 8-row groups ("stride" offset), all in
-// 16-byte units, and the descriptor version of this architecture (bit 46).
+// Shared-memory matrix descriptor, K-major with the 128-byte swizzle (layout 2 at bit 61): start
+// address and the distance between 8-row groups (1024 bytes), in 16-byte units, plus the descriptor
+// version of this architecture (bit 46).  The 16 values of K of one instruction are 32 bytes of a
+// row: the next instruction's descriptor starts 32 bytes further.
 __device__ __forceinline__ uint64_t tc_desc(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(TC_KG_STEP >> 4) << 16) | ((uint64_t)(128u >> 4) << 32) | (1ull << 46);
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 // Instruction descriptor of kind::f16: D = f32 (1 at bit 4), A = B = f16 (0 at bits 7 and 10), both
 // operands K-major, N / 8 at bit 17, M / 16 at bit 24.
@@ -294,9 +302,10 @@ __device__ __forceinline__ uint4 nib8_to_h8(uint32_t t0, uint32_t t1, __half2 of
 template <int WT, bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(const GemvArgs a, const uint8_t* __restrict__ bimg, const float* __restrict__ inv,
                                                     float* __restrict__ part, unsigned int* __restrict__ tickets, int S, int items) {
-    extern __shared__ __align__(128) uint8_t sm[];
+    extern __shared__ __align__(1024) uint8_t sm_raw[];
+    uint8_t* sm = sm_raw + ((1024u - (smem_u32(sm_raw) & 1023u)) & 1023u);     // the swizzle needs images at multiples of 1024 bytes
     uint8_t* smA = sm;
-    uint8_t* smB = sm + TC_CH * TC_A_STRIDE;
+    uint8_t* smB = sm + TC_A_CHUNK;
     __shared__ __align__(8) uint64_t bar_b[2], bar_m[2];
     __shared__ uint32_t s_tmem;
     __shared__ bool s_last;
@@ -328,11 +337,13 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(const GemvArgs a, con
 
     // block j of the chunk into accumulator j & 1: two instructions of 16 values of K each
     auto issue = [&](int j, const uint8_t* smBc) {
-        const uint32_t ab = smem_u32(smA + j * TC_A_STRIDE), bb = smem_u32(smBc + j * TC_B_STRIDE);
+        // block j = half (j & 1) of pair image j >> 1: its 32 values of K are bytes 64 * (j & 1) .. + 63 of every row
+        const uint32_t po = (uint32_t)(j >> 1) * TC_PAIR_IMG + (uint32_t)(j & 1) * 64u;
+        const uint32_t ab = smem_u32(smA) + po, bb = smem_u32(smBc) + po;
         const uint32_t d = tmem + (uint32_t)(j & 1) * TC_N;
         tc_fence_after();
         tc_mma_f16(d, tc_desc(ab), tc_desc(bb), TC_IDESC, 0u);
-        tc_mma_f16(d, tc_desc(ab + 2 * TC_KG_STEP), tc_desc(bb + 2 * TC_KG_STEP), TC_IDESC, 1u);
+        tc_mma_f16(d, tc_desc(ab + 32u), tc_desc(bb + 32u), TC_IDESC, 1u);
         tc_commit(&bar_m[j & 1]);
     };
 
@@ -359,8 +370,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(const GemvArgs a, con
     };
     auto fetch_b = [&](int ch) {                            // thread 0: bulk copy of chunk ch's B image into buffer (ch - ch0) & 1
         const int c0 = ch * TC_CH, nb = min(TC_CH, units - c0), st = (ch - ch0) & 1;
-        mbar_expect_tx(&bar_b[st], (uint32_t)nb * TC_B_STRIDE);
-        bulk_g2s(smB + st * (TC_CH * TC_B_STRIDE), bimg + (size_t)c0 * TC_B_STRIDE, (uint32_t)nb * TC_B_STRIDE, &bar_b[st]);
+        mbar_expect_tx(&bar_b[st], (uint32_t)TC_B_CHUNK);
+        bulk_g2s(smB + st * TC_B_CHUNK, bimg + (size_t)ch * TC_B_CHUNK, (uint32_t)TC_B_CHUNK, &bar_b[st]);
     };
     // Work items (tile, K split) are dealt round-robin to the CTAs of a grid that fills the GPU twice
     // over (two CTAs per SM); splits are cut finer than the grid so that the CTAs end together.
@@ -382,7 +393,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(const GemvArgs a, con
 
     for (int ch = ch0; ch < ch1; ++ch) {
         const int c0 = ch * TC_CH, nb = min(TC_CH, units - c0), st = (ch - ch0) & 1;
-        uint8_t* smBc = smB + st * (TC_CH * TC_B_STRIDE);
+        uint8_t* smBc = smB + st * TC_B_CHUNK;
         if (ch + 1 < ch1) {
             fetch(ch + 1, nxt);
             if (tid == 0) fetch_b(ch + 1);                  // its buffer was last read in chunk ch - 1, which ended with a barrier
@@ -406,23 +417,22 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(const GemvArgs a, con
             const uint4 q = cur.q[i];
             const uint32_t l0 = q.x & 0x0F0F0F0Fu, l1 = q.y & 0x0F0F0F0Fu, l2 = q.z & 0x0F0F0F0Fu, l3 = q.w & 0x0F0F0F0Fu;
             const uint32_t h0 = (q.x >> 4) & 0x0F0F0F0Fu, h1 = (q.y >> 4) & 0x0F0F0F0Fu, h2 = (q.z >> 4) & 0x0F0F0F0Fu, h3 = (q.w >> 4) & 0x0F0F0F0Fu;
-            const int ro = (rl >> 3) * 128 + (rl & 7) * 16;
+            // row rl of a pair image; the 16-byte piece c (8 values of K) goes to piece c ^ (rl & 7)
+            uint8_t* rowp = smA + (u >> 1) * TC_PAIR_IMG + (rl >> 3) * 1024 + (rl & 7) * 128;
+            const int x7 = rl & 7;
+            int c_lo, c_hi;                                     // first piece of the low / high nibbles' 16 values
             if constexpr (WT == WT_Q4_0) {
-                // unit u = block u: low nibbles are weights 0..15, high nibbles weights 16..31
-                uint8_t* blk = smA + u * TC_A_STRIDE + ro;
-                *reinterpret_cast<uint4*>(blk) = nib8_to_h8(l0, l1, off);
-                *reinterpret_cast<uint4*>(blk + TC_KG_STEP) = nib8_to_h8(l2, l3, off);
-                *reinterpret_cast<uint4*>(blk + 2 * TC_KG_STEP) = nib8_to_h8(h0, h1, off);
-                *reinterpret_cast<uint4*>(blk + 3 * TC_KG_STEP) = nib8_to_h8(h2, h3, off);
+                // unit u = block u = half (u & 1) of pair u >> 1: low nibbles are its values 0..15, high nibbles 16..31
+                c_lo = (u & 1) * 4; c_hi = c_lo + 2;
             } else {
-                // units 2g, 2g+1 = bytes 0..15, 16..31 of group g: low nibbles sub-block 2g, high 2g+1
-                const int gl = u >> 1, kg = (u & 1) * 2;
-                uint8_t* blk = smA + (2 * gl) * TC_A_STRIDE + kg * TC_KG_STEP + ro;
-                *reinterpret_cast<uint4*>(blk) = nib8_to_h8(l0, l1, off);
-                *reinterpret_cast<uint4*>(blk + TC_KG_STEP) = nib8_to_h8(l2, l3, off);
-                *reinterpret_cast<uint4*>(blk + TC_A_STRIDE) = nib8_to_h8(h0, h1, off);
-                *reinterpret_cast<uint4*>(blk + TC_A_STRIDE + TC_KG_STEP) = nib8_to_h8(h2, h3, off);
+                // units 2g, 2g+1 = bytes 0..15, 16..31 of group g = pair g: low nibbles sub-block 2g (first half
+                // of the pair), high nibbles sub-block 2g+1 (second half)
+                c_lo = (u & 1) * 2; c_hi = 4 + c_lo;
             }
+            *reinterpret_cast<uint4*>(rowp + (((c_lo) ^ x7) << 4)) = nib8_to_h8(l0, l1, off);
+            *reinterpret_cast<uint4*>(rowp + (((c_lo + 1) ^ x7) << 4)) = nib8_to_h8(l2, l3, off);
+            *reinterpret_cast<uint4*>(rowp + (((c_hi) ^ x7) << 4)) = nib8_to_h8(h0, h1, off);
+            *reinterpret_cast<uint4*>(rowp + (((c_hi + 1) ^ x7) << 4)) = nib8_to_h8(h2, h3, off);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncthreads();
@@ -440,7 +450,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(const GemvArgs a, con
                 if (!dead && !mbar_wait(&bar_m[j & 1], ph)) { dead = true; atomicOr(a.err, DEVERR_WAIT); }
                 ph ^= 1u;
                 tc_fence_after();
-                const float* sx = reinterpret_cast<const float*>(smBc + j * TC_B_STRIDE + TC_B_BLK);
+                const float* sx = reinterpret_cast<const float*>(smBc + TC_B_SUMS + j * (TC_COLS * 4));
                 const float fa = sa[j], fb = sb[j];
                 const uint32_t t0 = tlane + (uint32_t)(j & 1) * TC_N;
                 {
@@ -539,14 +549,20 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(const GemvArgs a, con
 
 // ---- host ----------------------------------------------------------------------------------------
 bool gemm_tc_supports(int wtype, const GemvArgs& a) {
-    static const bool off = getenv("ADAM_B200_TC") && atoi(getenv("ADAM_B200_TC")) == 0;
-    if (off || !g_tc.ok) return false;
+    if (g_tc_policy < 0) g_tc_policy = getenv("ADAM_B200_TC") ? atoi(getenv("ADAM_B200_TC")) : 1;
+    if (g_tc_policy == 0 || !g_tc.ok) return false;
     if (a.B < TC_MIN_ROWS || a.B > TC_COLS) return false;
     if (a.epi != EPI_STORE && a.epi != EPI_GEGLU && a.epi != EPI_SWIGLU) return false;
     if (a.K <= 0 || a.K > TC_MAX_K || a.N < 16 || !a.y) return false;
     if (wtype == WT_Q4_0 ? (a.K % 32) != 0 : (a.K % 256) != 0) return false;
     if ((a.ldx & 3) || (!a.h_in && !a.x)) return false;
     const bool pair = a.epi != EPI_STORE;
+    if (g_tc_policy == 1) {
+        // The GEMV kernels pass over the weights once per 4 rows; this kernel passes once but has a fixed
+        // cost of 10-15 us.  Measured cross-over: weights x passes of about 2e8 (Q4_0) / 1e8 (Q4_K) elements.
+        const double work = (double)a.N * a.K * (pair ? 2 : 1) * ((a.B + 3) / 4);
+        if (work < (wtype == WT_Q4_0 ? 2.0e8 : 1.0e8)) return false;
+    }
     const int tiles = pair ? (a.N + 63) / 64 : (a.N + 127) / 128;
     return tiles <= TC_MAX_CTAS && tiles <= TC_MAX_TILES && (size_t)a.K * 4 <= 160 * 1024;
 }
@@ -602,3 +618,9 @@ int launch_gemm_tc(int wtype, const GemvArgs& a_in, cudaStream_t stream) {
 // Number of GEMMs enqueued on the tcgen05 path since the library was loaded (tests use it to
 // see which kernel a call took).
 extern "C" uint64_t adam_b200_tc_gemm_count(void) { return ab::g_tc_calls; }
+// 0 = never use the tcgen05 GEMM, 1 = where it is expected to be faster (default), 2 = whenever the shape allows.
+extern "C" int adam_b200_tc_gemm_policy(int policy) {
+    if (policy < 0 || policy > 2) return ADAMAH_ERR_INVALID;
+    ab::g_tc_policy = policy;
+    return ADAMAH_OK;
+}

@@ -338,6 +338,9 @@ int adam_b200_decoder_step_part(uint32_t id, uint32_t part, uint32_t flags);
 /* Number of matrix products enqueued so far on the tcgen05 (tensor memory) GEMM, which takes calls
  * with 9..64 activation rows; calls with fewer rows run on the GEMV kernels. */
 uint64_t adam_b200_tc_gemm_count(void);
+/* Which calls take it: 0 = none, 1 = those expected to be faster than the GEMV kernels (default; also the
+ * initial value of environment variable ADAM_B200_TC), 2 = every call whose shape allows. */
+int adam_b200_tc_gemm_policy(int policy);
 /* One part of one prefill chunk of n_tokens (batch * n_tokens <= 64 rows) tokens per sequence: parts
  * 0 .. 2*n_layer-1 as above (the projection buffer then holds batch * n_tokens rows of partial
  * sums), part 2*n_layer advances the positions by n_tokens. */

@@ -133,7 +133,11 @@ def test_tcgen05_gemm_many_rows(gpu, ggml_type, N, K, B):
     raw = (gb.random_q4_0_blocks if ggml_type == 2 else gb.random_q4_k_blocks)(rng, N, K)
     x = rng.standard_normal((B, K), dtype=np.float32) * rng.uniform(0.01, 100.0, (B, 1)).astype(np.float32)
     before = gpu.tc_gemm_count()
-    y = _gemv(gpu, ggml_type, raw, N, K, x)
+    gpu.tc_gemm_policy(2)               # small shapes too (by default they stay on the GEMV kernels)
+    try:
+        y = _gemv(gpu, ggml_type, raw, N, K, x)
+    finally:
+        gpu.tc_gemm_policy(1)
     assert gpu.tc_gemm_count() == before + 1
     W = q4_blocks.dequant(raw.reshape(-1), ggml_type, N, K)
     for b in range(B):
