@@ -253,8 +253,12 @@ class ADAMEngineTP(ADAMEngine):
                     # it), collectives included, and replayed from then on
                     self._stream.synchronize()
                     gr = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(gr, stream=self._stream):
-                        self._one_step(flags)
+                    self.gpu.batch_begin()              # no per-call synchronisation inside the recording
+                    try:
+                        with torch.cuda.graph(gr, stream=self._stream):
+                            self._one_step(flags)
+                    finally:
+                        self.gpu.batch_end()
                     self._graphs[key] = gr
 
     def _reduce_proj(self, rows: int):
