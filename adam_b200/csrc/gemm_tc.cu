@@ -10,28 +10,31 @@
 //
 // Two kernels:
 //   k_quant_rows   one CTA per activation row: the optional input chain (residual add + RMS norms,
-//                  as the GEMV prologue), the row's scale, and the row's two fp16 planes written
-//                  into the B-operand image: per 32-wide K block a [128][32] fp16 K-major matrix
-//                  (row n = plane * 64 + activation row) in the tensor core's core-matrix order
-//                  (8 rows x 16 bytes contiguous, 8-row groups 128 bytes apart, the next 8 values
-//                  of K 2048 bytes further), followed by the 64 per-row integer sums of the block
-//                  as floats (the term that carries the Q4_K block minimum).
-//   k_gemm_tc      one CTA (128 threads) per (tile of 128 weight rows, K split).  Per chunk of 4
-//                  K blocks: one bulk copy brings the B image (33 KB) into shared memory, the
-//                  threads load the chunk's nibbles (64-byte runs per weight row), turn them into
-//                  fp16 (q - 8 for Q4_0, q for Q4_K: one byte permute per pair gives 1024 + q, one
-//                  packed subtract removes the offset) in the A image, and then per K block one
-//                  thread issues two tcgen05.mma (M 128 x N 128 x K 16 each, fp16 -> fp32 in TMEM)
-//                  and a commit whose completion arrives on an mbarrier.  TMEM holds two
-//                  accumulators of 128 columns: block j + 1 is issued before block j is read, so
-//                  the tensor core works under the arithmetic.  Every thread reads its weight
-//                  row's 128 sums (tcgen05.ld), recombines the planes (hi * 2048 + lo), applies the
-//                  block scale and accumulates 64 fp32 outputs in registers.  Two CTAs share an SM
-//                  (256 TMEM columns each).  K splits leave partial sums in a workspace; the last
+//                  as the GEMV prologue; the row stays in registers and all loads are issued before
+//                  the first use), the row's scale, and the row's two fp16 planes written straight
+//                  into the B-operand image in global memory: K-major with the 128-byte swizzle,
+//                  two 32-wide K blocks per 128-byte operand row, 128 operand rows (row n = plane *
+//                  64 + activation row) = 16 KB per block pair, and behind each chunk of four
+//                  blocks the 4 x 64 per-row integer sums as floats (the term that carries the Q4_K
+//                  block minimum).
+//   k_gemm_tc      256 threads, two CTAs per SM (256 TMEM columns and 99 KB of shared memory each), a
+//                  grid that fills the GPU twice over and takes work items (tile of 128 weight rows
+//                  x K split) round-robin.  Per chunk of 4 K blocks: one bulk copy brings the B
+//                  image (33 KB) into one of two buffers, the threads turn the chunk's nibbles
+//                  (64-byte runs per weight row, requested one chunk ahead and held in registers)
+//                  into fp16 (q - 8 for Q4_0, q for Q4_K: one byte permute per pair gives 1024 + q,
+//                  one packed subtract removes the offset) in the swizzled A image, and then per K
+//                  block one thread issues two tcgen05.mma (M 128 x N 128 x K 16 each, fp16 -> fp32
+//                  in TMEM) and a commit whose completion arrives on an mbarrier.  TMEM holds two
+//                  accumulators of 128 columns: block j + 1 is issued before block j is read.  The
+//                  two warps of a TMEM lane quarter read 32 of the 64 columns each (tcgen05.ld),
+//                  recombine the planes (hi * 2048 + lo), apply the block scale and accumulate 32
+//                  fp32 outputs per thread.  K splits leave partial sums in a workspace; the last
 //                  CTA of a tile (atomic ticket) adds them in split order and runs the epilogue
 //                  (store, or GeGLU / SwiGLU over a tile of 64 gate rows + 64 up rows).
 // Every wait (bulk copy, tensor-core completion) is bounded: when one runs out the kernel records
-// DEVERR_WAIT, stops waiting, and still frees its tensor memory.
+// DEVERR_WAIT, stops waiting, and still frees its tensor memory.  The shared-memory request keeps a
+// third CTA off an SM, so a TMEM allocation never waits on a CTA that cannot run.
 #include "gemm_tc.cuh"
 #include "gemv_mma.cuh"
 
