@@ -2,11 +2,11 @@
 // or a large decode batch) on the 5th-generation tensor cores: tcgen05.mma with the accumulator in
 // tensor memory (TMEM).  Same operator as the GEMV kernels (the reference's Q4 mat-vec shader
 // adamah-MAIN/adamah/shaders/src/f32/map_matvec_t_xq4.comp and map_fused_gateup_t_xq4.comp run once
-// per row by adamah.c:8606-8691), same arithmetic idea: activations become integers of up to 23 bits
-// with one power-of-two scale per row, the products with the 4-bit weights are formed exactly, and
-// each 32-weight block's sum is scaled by the block's scale and accumulated in fp32.  Here the
-// integers are split into two signed 11-bit planes, which fp16 holds exactly; a block's 32 products
-// per plane add up exactly in the tensor core's fp32 accumulator (|sum| < 2^20).
+// per row by adamah.c:8606-8691).  Arithmetic: a row's activations become integers of up to 23 bits
+// with one power-of-two scale per row, split into two signed parts that fp16 holds exactly
+// (x = 2048 x_hi + x_lo); a weight is dequantised in fp32 (block scale and offset applied) and split
+// into two fp16 terms (22 bits); the three significant cross products are accumulated over all of K in
+// fp32 in TMEM and combined once per output.  Measured error ~5e-7 of max |y| (operator tolerance 1e-3).
 //
 // Two kernels:
 //   k_quant_rows   one CTA per activation row: the optional input chain (residual add + RMS norms,
@@ -14,24 +14,14 @@
 //                  the first use), the row's scale, and the row's two fp16 planes written straight
 //                  into the B-operand image in global memory: K-major with the 128-byte swizzle,
 //                  two 32-wide K blocks per 128-byte operand row, 128 operand rows (row n = plane *
-//                  64 + activation row) = 16 KB per block pair, and behind each chunk of four
-//                  blocks the 4 x 64 per-row integer sums as floats (the term that carries the Q4_K
-//                  block minimum).
-//   k_gemm_tc      256 threads, two CTAs per SM (256 TMEM columns and 99 KB of shared memory each), a
+//                  64 + activation row) = 16 KB per block pair (behind each chunk of two pairs the
+//                  4 x 64 per-row integer sums are kept as floats for callers that want them).
+//   k_gemm_tc      256 threads, two CTAs per SM (256 TMEM columns and 97 KB of shared memory each), a
 //                  grid that fills the GPU twice over and takes work items (tile of 128 weight rows
-//                  x K split) round-robin.  Per chunk of 4 K blocks: one bulk copy brings the B
-//                  image (33 KB) into one of two buffers, the threads turn the chunk's nibbles
-//                  (64-byte runs per weight row, requested one chunk ahead and held in registers)
-//                  into fp16 (q - 8 for Q4_0, q for Q4_K: one byte permute per pair gives 1024 + q,
-//                  one packed subtract removes the offset) in the swizzled A image, and then per K
-//                  block one thread issues two tcgen05.mma (M 128 x N 128 x K 16 each, fp16 -> fp32
-//                  in TMEM) and a commit whose completion arrives on an mbarrier.  TMEM holds two
-//                  accumulators of 128 columns: block j + 1 is issued before block j is read.  The
-//                  two warps of a TMEM lane quarter read 32 of the 64 columns each (tcgen05.ld),
-//                  recombine the planes (hi * 2048 + lo), apply the block scale and accumulate 32
-//                  fp32 outputs per thread.  K splits leave partial sums in a workspace; the last
-//                  CTA of a tile (atomic ticket) adds them in split order and runs the epilogue
-//                  (store, or GeGLU / SwiGLU over a tile of 64 gate rows + 64 up rows).
+//                  x K split) round-robin; see the comment at the kernel.  K splits leave partial
+//                  sums in a workspace; the last CTA of a tile (atomic ticket) adds them in split
+//                  order and runs the epilogue (store, or GeGLU / SwiGLU over a tile of 64 gate
+//                  rows + 64 up rows).
 // Every wait (bulk copy, tensor-core completion) is bounded: when one runs out the kernel records
 // DEVERR_WAIT, stops waiting, and still frees its tensor memory.  The shared-memory request keeps a
 // third CTA off an SM, so a TMEM allocation never waits on a CTA that cannot run.
@@ -44,7 +34,7 @@ namespace ab {
 
 constexpr int TC_PLANES = 2;
 constexpr int TC_N = TC_PLANES * TC_COLS;                // 128 B-operand rows
-constexpr int TC_CH = 4;                                 // K blocks per chunk
+constexpr int TC_CH = 4;                                 // K blocks per chunk of the B image (two pair images + the sums)
 // Operand images, K-major with the 128-byte swizzle: a "pair" image holds two K blocks (64 fp16 = 128
 // bytes per operand row) of 128 operand rows = 16 KB: 8-row groups of 1024 bytes, a row's 128 bytes
 // contiguous, and the 16-byte piece c of row r stored at piece c ^ (r & 7).  Images start at
@@ -53,7 +43,6 @@ constexpr int TC_PAIR_IMG = 128 * 128;                   // 16384
 constexpr int TC_A_CHUNK = (TC_CH / 2) * TC_PAIR_IMG;    // 32768
 constexpr int TC_B_SUMS = TC_A_CHUNK;                    // offset of the chunk's [4][64] row sums in the B chunk image
 constexpr int TC_B_CHUNK = TC_A_CHUNK + TC_CH * TC_COLS * 4;        // 33792 = 33 * 1024
-constexpr int TC_SMEM = TC_A_CHUNK + 2 * TC_B_CHUNK + 1024;         // A image + two B buffers (+ alignment slack); two CTAs per SM, never three (TMEM holds two allocations)
 constexpr int TC_TMEM_COLS = 256;
 constexpr int TC_THREADS = 256;                         // two warps per TMEM lane quarter: each takes 32 of the 64 columns
 constexpr int TC_MYCOLS = TC_COLS / 2;
@@ -287,42 +276,65 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&r)[32]) {
 }
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Two nibbles-as-bytes (bytes `sel` picks from t) -> two fp16 values minus `off` (1024 + the zero point).
-__device__ __forceinline__ uint32_t nib2_to_h2(uint32_t t, uint32_t sel, __half2 off) {
-    const uint32_t v = __byte_perm(t, 0x64646464u, sel);       // { 0x64, nibble } per half = 1024 + nibble
-    const __half2 h = __hsub2(*reinterpret_cast<const __half2*>(&v), off);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-// Eight nibbles-as-bytes of two words -> eight consecutive fp16 values (one 16-byte core-matrix row).
-__device__ __forceinline__ uint4 nib8_to_h8(uint32_t t0, uint32_t t1, __half2 off) {
-    return make_uint4(nib2_to_h2(t0, 0x4140u, off), nib2_to_h2(t0, 0x4342u, off), nib2_to_h2(t1, 0x4140u, off), nib2_to_h2(t1, 0x4342u, off));
+// ---- the GEMM ---------------------------------------------------------------------------------
+// Weights enter the tensor core already scaled: w = 64 * (sa * q + sb) in fp32 (the factor keeps the low
+// term of typical weights out of the fp16 subnormals; |sa * q + sb| must stay below 1000) (sa, sb the block's
+// scale and offset: d and -8 d for Q4_0, d*sc and -dmin*m for Q4_K), split into two fp16 terms
+// w_hi + w_lo (22 bits).  With the activations' planes x_hi, x_lo the product is
+//   sum_k w x = 2048 * (sum w_hi x_hi + sum w_lo x_hi) + sum w_hi x_lo      (w_lo x_lo is below fp32 resolution)
+// and all of a work item's K is accumulated in TMEM: D1 (128 columns) = w_hi x [x_hi | x_lo],
+// D2 (64 columns) = w_lo x x_hi.  Nothing is read back per block.
+//
+// Per step of two K blocks (64 values of K, one 128-byte operand row): the threads expand one 16-byte
+// unit of nibbles each into the two A images of buffer b (the unit was requested one step ahead), one
+// thread waits for the step's B image (16 KB bulk copy, requested one step ahead into buffer b) and
+// issues 4 x 2 tcgen05.mma (K 16 each; N 128 and N 64) and a commit that frees buffer b two steps later.
+// grid = min(items, 2 per SM); item = (tile of 128 weight rows, K split) dealt round-robin.
+// PAIR: a tile is 64 rows of w0 (gate) in TMEM lanes 0..63 and the same 64 rows of w1 (up) in lanes 64..127.
+constexpr uint32_t TC_IDESC_N64 = (1u << 4) | ((uint32_t)(TC_COLS >> 3) << 17) | ((128u >> 4) << 24);
+constexpr int TC_A_BUF = 2 * TC_PAIR_IMG;               // w_hi image + w_lo image of one step
+constexpr int TC_SMEM2 = 2 * TC_A_BUF + 2 * TC_PAIR_IMG + 1024;     // 99328: two A buffers, two B buffers, alignment slack
+
+// Four nibbles-as-bytes of t -> sa * q + sb (the callers pass scales times 64) as fp16 high and low terms (two packed pairs each).
+__device__ __forceinline__ void nib4_split(uint32_t t, float sa, float sb, uint32_t (&hi)[2], uint32_t (&lo)[2]) {
+    float w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // byte i of t into mantissa bits 16..23 of 2^7: the float 128 + q, exactly
+        const float f = __uint_as_float(__byte_perm(t, 0x43000000u, 0x7054u | ((uint32_t)i << 8)));
+        w[i] = fmaf(sa, f - 128.f, sb);
+    }
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+        const __half2 h = __floats2half2_rn(w[2 * p], w[2 * p + 1]);
+        const float2 hf = __half22float2(h);
+        const __half2 l = __floats2half2_rn(w[2 * p] - hf.x, w[2 * p + 1] - hf.y);
+        hi[p] = *reinterpret_cast<const uint32_t*>(&h);
+        lo[p] = *reinterpret_cast<const uint32_t*>(&l);
+    }
 }
 
-// ---- the GEMM ---------------------------------------------------------------------------------
-// grid = tiles * S; CTA (tile, sp) covers chunks [sp * n_chunks / S, (sp + 1) * n_chunks / S).
-// PAIR: a tile is 64 rows of w0 (gate) in TMEM lanes 0..63 and the same 64 rows of w1 (up) in
-// lanes 64..127; otherwise 128 consecutive rows of w0.
 template <int WT, bool PAIR>
 __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(const GemvArgs a, const uint8_t* __restrict__ bimg, const float* __restrict__ inv,
-                                                    float* __restrict__ part, unsigned int* __restrict__ tickets, int S, int items) {
+                                                           float* __restrict__ part, unsigned int* __restrict__ tickets, int S, int items) {
     extern __shared__ __align__(1024) uint8_t sm_raw[];
     uint8_t* sm = sm_raw + ((1024u - (smem_u32(sm_raw) & 1023u)) & 1023u);     // the swizzle needs images at multiples of 1024 bytes
-    uint8_t* smA = sm;
-    uint8_t* smB = sm + TC_A_CHUNK;
-    __shared__ __align__(8) uint64_t bar_b[2], bar_m[2];
+    uint8_t* smA = sm;                                  // [2 buffers][w_hi image, w_lo image]
+    uint8_t* smB = sm + 2 * TC_A_BUF;                   // [2 buffers][pair image]
+    __shared__ __align__(8) uint64_t bar_b[2], bar_free[2];
     __shared__ uint32_t s_tmem;
     __shared__ bool s_last;
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int lane_row = tid & 127, chalf = tid >> 7;          // TMEM lane (row of the tile) and column half of this thread
-    int tile = 0, ch0 = 0, ch1 = 0;                           // of the work item in hand (set per item below)
-    const int units = a.K >> 5, n_chunks = (units + TC_CH - 1) / TC_CH;
+    const int lane_row = tid & 127, chalf = tid >> 7;          // TMEM lane (row of the tile) and column half this thread reads back
+    const int urow = tid >> 1, uu = tid & 1;                    // operand row and 16-byte unit (of the step's two) this thread expands
+    const int units = a.K >> 5, n_steps = (units + 1) >> 1;
     constexpr int TILE_ROWS = PAIR ? 64 : 128;
-    // the weight row behind TMEM lane `l` of this tile
-    auto row_of = [&](int l, const WeightRef*& w) -> int {
+    int tile = 0;
+    auto row_of = [&](int l, const WeightRef*& w) -> int {      // the weight row behind TMEM lane l of this tile
         if constexpr (PAIR) { w = (l >> 6) ? &a.w1 : &a.w0; return min(tile * 64 + (l & 63), a.N - 1); }
         else { w = &a.w0; return min(tile * 128 + l, a.N - 1); }
     };
-    if (tid == 0) { mbar_init(&bar_b[0], 1); mbar_init(&bar_b[1], 1); mbar_init(&bar_m[0], 1); mbar_init(&bar_m[1], 1); }
+    if (tid == 0) { mbar_init(&bar_b[0], 1); mbar_init(&bar_b[1], 1); mbar_init(&bar_free[0], 1); mbar_init(&bar_free[1], 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == 0) tc_alloc(&s_tmem, TC_TMEM_COLS);
@@ -331,156 +343,126 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(const GemvArgs a, con
     tc_fence_after();
     const uint32_t tmem = s_tmem;
     const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const WeightRef* wmine = nullptr;
-    int my_row = 0;
-    float acc[TC_MYCOLS];
-    uint32_t ph_b0 = 0, ph_b1 = 0, ph_m0 = 0, ph_m1 = 0;
     bool dead = false;
-    const __half2 off = __float2half2_rn(WT == WT_Q4_0 ? 1032.f : 1024.f);     // Q4_0 values are q - 8
-
-    // block j of the chunk into accumulator j & 1: two instructions of 16 values of K each
-    auto issue = [&](int j, const uint8_t* smBc) {
-        // block j = half (j & 1) of pair image j >> 1: its 32 values of K are bytes 64 * (j & 1) .. + 63 of every row
-        const uint32_t po = (uint32_t)(j >> 1) * TC_PAIR_IMG + (uint32_t)(j & 1) * 64u;
-        const uint32_t ab = smem_u32(smA) + po, bb = smem_u32(smBc) + po;
-        const uint32_t d = tmem + (uint32_t)(j & 1) * TC_N;
-        tc_fence_after();
-        tc_mma_f16(d, tc_desc(ab), tc_desc(bb), TC_IDESC, 0u);
-        tc_mma_f16(d, tc_desc(ab + 32u), tc_desc(bb + 32u), TC_IDESC, 1u);
-        tc_commit(&bar_m[j & 1]);
+    auto wait_on = [&](uint64_t* bar, uint32_t parity) {
+        if (!dead && !mbar_wait(bar, parity)) { dead = true; atomicOr(a.err, DEVERR_WAIT); }
     };
 
-    // ---- main loop: chunks of TC_CH blocks; the next chunk's nibbles, scales (registers) and B image
-    // (second shared-memory buffer) are requested while the current chunk is multiplied ----
-    constexpr int NQ = TC_CH * 128 / TC_THREADS;            // 16-byte units per thread and chunk
-    struct Raw { uint4 q[NQ]; uint4 h; unsigned short d[TC_CH]; };
-    auto fetch = [&](int ch, Raw& r) {                      // global loads of chunk ch (weights only: no dependency on earlier kernels)
-        const int c0 = ch * TC_CH, nb = min(TC_CH, units - c0);
-#pragma unroll
-        for (int i = 0; i < NQ; ++i) {
-            const int idx = i * TC_THREADS + tid, rl = idx >> 2, u = idx & 3;
-            const WeightRef* w;
-            const int rr = row_of(rl, w);
-            if constexpr (WT == WT_Q4_0) r.q[i] = ld_stream(w->q + (size_t)rr * units + c0 + min(u, nb - 1));
-            else r.q[i] = ld_stream(w->q + ((size_t)rr * (units >> 3) + (ch >> 1)) * 9 + 1 + (ch & 1) * 4 + u);
-        }
+    struct Raw { uint4 q; uint4 h; unsigned short d; };
+    const WeightRef* wu = nullptr;
+    int r_u = 0;
+    auto fetch = [&](int st, Raw& r) {                      // this thread's unit of step st (weights only: no dependency on earlier kernels)
         if constexpr (WT == WT_Q4_0) {
-#pragma unroll
-            for (int j = 0; j < TC_CH; ++j) r.d[j] = __ldg(reinterpret_cast<const unsigned short*>(wmine->d) + (size_t)my_row * units + c0 + min(j, nb - 1));
+            const int blk = min(2 * st + uu, units - 1);
+            r.q = ld_stream(wu->q + (size_t)r_u * units + blk);
+            r.d = __ldg(reinterpret_cast<const unsigned short*>(wu->d) + (size_t)r_u * units + blk);
         } else {
-            r.h = __ldg(wmine->q + ((size_t)my_row * (units >> 3) + (ch >> 1)) * 9);
+            const uint4* sb = wu->q + ((size_t)r_u * (units >> 3) + (st >> 2)) * 9;
+            r.h = __ldg(sb);
+            r.q = ld_stream(sb + 1 + (st & 3) * 2 + uu);
         }
     };
-    auto fetch_b = [&](int ch) {                            // thread 0: bulk copy of chunk ch's B image into buffer (ch - ch0) & 1
-        const int c0 = ch * TC_CH, nb = min(TC_CH, units - c0), st = (ch - ch0) & 1;
-        mbar_expect_tx(&bar_b[st], (uint32_t)TC_B_CHUNK);
-        bulk_g2s(smB + st * TC_B_CHUNK, bimg + (size_t)ch * TC_B_CHUNK, (uint32_t)TC_B_CHUNK, &bar_b[st]);
+    auto fetch_b = [&](int st, int b) {                     // thread 0: the step's B pair image into buffer b
+        mbar_expect_tx(&bar_b[b], (uint32_t)TC_PAIR_IMG);
+        bulk_g2s(smB + b * TC_PAIR_IMG, bimg + (size_t)(st >> 1) * TC_B_CHUNK + (size_t)(st & 1) * TC_PAIR_IMG, (uint32_t)TC_PAIR_IMG, &bar_b[b]);
     };
-    // Work items (tile, K split) are dealt round-robin to the CTAs of a grid that fills the GPU twice
-    // over (two CTAs per SM); splits are cut finer than the grid so that the CTAs end together.
+
     Raw cur, nxt;
     bool first = true;
+    uint32_t it = 0;                                        // steps done by this CTA: buffer = it & 1, use number of the buffer = it >> 1
     pdl_launch_dependents();
     for (int item = (int)blockIdx.x; item < items; item += (int)gridDim.x) {
-    {
         const int sp = item % S;
         tile = item / S;
-        ch0 = (int)((long long)sp * n_chunks / S); ch1 = (int)((long long)(sp + 1) * n_chunks / S);
-        my_row = row_of(lane_row, wmine);
-    }
-#pragma unroll
-    for (int c = 0; c < TC_MYCOLS; ++c) acc[c] = 0.f;
-    if (ch0 < ch1) fetch(ch0, cur);
-    if (first) { pdl_wait(); first = false; }           // the B image comes from the kernel before this one; weights were requested above
-    if (ch0 < ch1 && tid == 0) fetch_b(ch0);
-
-    for (int ch = ch0; ch < ch1; ++ch) {
-        const int c0 = ch * TC_CH, nb = min(TC_CH, units - c0), st = (ch - ch0) & 1;
-        uint8_t* smBc = smB + st * TC_B_CHUNK;
-        if (ch + 1 < ch1) {
-            fetch(ch + 1, nxt);
-            if (tid == 0) fetch_b(ch + 1);                  // its buffer was last read in chunk ch - 1, which ended with a barrier
+        const int st0 = (int)((long long)sp * n_steps / S), st1 = (int)((long long)(sp + 1) * n_steps / S);
+        r_u = row_of(urow, wu);
+        if (st0 < st1) fetch(st0, cur);
+        if (first) { pdl_wait(); first = false; }           // the B image comes from the kernel before this one; weights were requested above
+        if (tid == 0 && st0 < st1) {
+            if ((it >> 1) >= 1u) wait_on(&bar_free[it & 1u], ((it >> 1) - 1u) & 1u);
+            fetch_b(st0, (int)(it & 1u));
         }
-        // block scales of this thread's row: value = sa * q' + sb per weight (q' = q - 8 and sb = 0 for Q4_0)
-        float sa[TC_CH], sb[TC_CH];
-        if constexpr (WT == WT_Q4_0) {
+        for (int st = st0; st < st1; ++st, ++it) {
+            const uint32_t b = it & 1u, n = it >> 1;
+            if (st + 1 < st1) fetch(st + 1, nxt);
+            // scales of the unit's low-nibble and high-nibble halves, times 64
+            float sa0, sb0, sa1, sb1;
+            int p_lo, p_hi;                                 // first 16-byte piece (8 values of K) of the two halves in the 128-byte row
+            if constexpr (WT == WT_Q4_0) {
+                // unit = block 2 st + uu = half uu of the row: low nibbles are its values 0..15, high nibbles 16..31
+                const float d = (2 * st + uu < units) ? 64.f * __half2float(__ushort_as_half(cur.d)) : 0.f;
+                sa0 = sa1 = d; sb0 = sb1 = -8.f * d;
+                p_lo = uu * 4; p_hi = p_lo + 2;
+            } else {
+                // units 2g, 2g+1 = bytes 0..15, 16..31 of group g = this step: low nibbles sub-block 2g (first half
+                // of the row), high nibbles sub-block 2g+1 (second half)
+                float m0, m1;
+                q4k_scales(cur.h, st & 3, sa0, m0, sa1, m1);
+                sa0 *= 64.f; sa1 *= 64.f; sb0 = -64.f * m0; sb1 = -64.f * m1;
+                p_lo = uu * 2; p_hi = 4 + p_lo;
+            }
+            if (n >= 1u) wait_on(&bar_free[b], (n - 1u) & 1u);  // the tensor core has finished with buffer b
+            {
+                const uint32_t l[4] = {cur.q.x & 0x0F0F0F0Fu, cur.q.y & 0x0F0F0F0Fu, cur.q.z & 0x0F0F0F0Fu, cur.q.w & 0x0F0F0F0Fu};
+                const uint32_t h[4] = {(cur.q.x >> 4) & 0x0F0F0F0Fu, (cur.q.y >> 4) & 0x0F0F0F0Fu, (cur.q.z >> 4) & 0x0F0F0F0Fu, (cur.q.w >> 4) & 0x0F0F0F0Fu};
+                uint8_t* rowp = smA + b * TC_A_BUF + (urow >> 3) * 1024 + (urow & 7) * 128;
+                const int x7 = urow & 7;
 #pragma unroll
-            for (int j = 0; j < TC_CH; ++j) { sa[j] = __half2float(__ushort_as_half(cur.d[j])); sb[j] = 0.f; }
+                for (int pc = 0; pc < 2; ++pc) {            // 16-byte pieces: words 2 pc, 2 pc + 1 of each nibble half
+                    uint32_t ha[2], la[2], hb[2], lb[2];
+                    nib4_split(l[2 * pc], sa0, sb0, ha, la); nib4_split(l[2 * pc + 1], sa0, sb0, hb, lb);
+                    *reinterpret_cast<uint4*>(rowp + (((p_lo + pc) ^ x7) << 4)) = make_uint4(ha[0], ha[1], hb[0], hb[1]);
+                    *reinterpret_cast<uint4*>(rowp + TC_PAIR_IMG + (((p_lo + pc) ^ x7) << 4)) = make_uint4(la[0], la[1], lb[0], lb[1]);
+                    nib4_split(h[2 * pc], sa1, sb1, ha, la); nib4_split(h[2 * pc + 1], sa1, sb1, hb, lb);
+                    *reinterpret_cast<uint4*>(rowp + (((p_hi + pc) ^ x7) << 4)) = make_uint4(ha[0], ha[1], hb[0], hb[1]);
+                    *reinterpret_cast<uint4*>(rowp + TC_PAIR_IMG + (((p_hi + pc) ^ x7) << 4)) = make_uint4(la[0], la[1], lb[0], lb[1]);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncthreads();
+            if (tid == 0) {
+                if (st + 1 < st1) {                         // next step's B image into the other buffer (free once the step before this one is done)
+                    const uint32_t b1 = (it + 1u) & 1u, n1 = (it + 1u) >> 1;
+                    if (n1 >= 1u) wait_on(&bar_free[b1], (n1 - 1u) & 1u);
+                    fetch_b(st + 1, (int)b1);
+                }
+                wait_on(&bar_b[b], n & 1u);
+                tc_fence_after();
+                const uint32_t ahi = smem_u32(smA + b * TC_A_BUF), alo = ahi + TC_PAIR_IMG, bb = smem_u32(smB + b * TC_PAIR_IMG);
+#pragma unroll
+                for (uint32_t t = 0; t < 4; ++t) {
+                    const uint32_t accf = (st > st0 || t > 0) ? 1u : 0u;
+                    tc_mma_f16(tmem, tc_desc(ahi + t * 32u), tc_desc(bb + t * 32u), TC_IDESC, accf);
+                    tc_mma_f16(tmem + TC_N, tc_desc(alo + t * 32u), tc_desc(bb + t * 32u), TC_IDESC_N64, accf);
+                }
+                tc_commit(&bar_free[b]);
+            }
+            cur = nxt;
+        }
+        // ---- all of this item's K is in TMEM: read it back once ----
+        float acc[TC_MYCOLS];
+        if (st0 < st1) {
+            const uint32_t last = it - 1u;
+            wait_on(&bar_free[last & 1u], (last >> 1) & 1u);    // the last commit covers every instruction before it
+            tc_fence_after();
+            float hh[32], hl[32], lh[32];
+            tc_ld32(tlane + chalf * 32, hh);                    // w_hi x x_hi
+            tc_ld32(tlane + TC_COLS + chalf * 32, hl);          // w_hi x x_lo
+            tc_ld32(tlane + TC_N + chalf * 32, lh);             // w_lo x x_hi
+            tc_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) acc[c] = fmaf(hh[c] + lh[c], 2048.f, hl[c]);
+            tc_fence_before();
         } else {
 #pragma unroll
-            for (int gl = 0; gl < 2; ++gl) {
-                float m0, m1;
-                q4k_scales(cur.h, (ch & 1) * 2 + gl, sa[2 * gl], m0, sa[2 * gl + 1], m1);
-                sb[2 * gl] = -m0; sb[2 * gl + 1] = -m1;
-            }
+            for (int c = 0; c < 32; ++c) acc[c] = 0.f;
         }
-#pragma unroll
-        for (int i = 0; i < NQ; ++i) {
-            const int idx = i * TC_THREADS + tid, rl = idx >> 2, u = idx & 3;
-            const uint4 q = cur.q[i];
-            const uint32_t l0 = q.x & 0x0F0F0F0Fu, l1 = q.y & 0x0F0F0F0Fu, l2 = q.z & 0x0F0F0F0Fu, l3 = q.w & 0x0F0F0F0Fu;
-            const uint32_t h0 = (q.x >> 4) & 0x0F0F0F0Fu, h1 = (q.y >> 4) & 0x0F0F0F0Fu, h2 = (q.z >> 4) & 0x0F0F0F0Fu, h3 = (q.w >> 4) & 0x0F0F0F0Fu;
-            // row rl of a pair image; the 16-byte piece c (8 values of K) goes to piece c ^ (rl & 7)
-            uint8_t* rowp = smA + (u >> 1) * TC_PAIR_IMG + (rl >> 3) * 1024 + (rl & 7) * 128;
-            const int x7 = rl & 7;
-            int c_lo, c_hi;                                     // first piece of the low / high nibbles' 16 values
-            if constexpr (WT == WT_Q4_0) {
-                // unit u = block u = half (u & 1) of pair u >> 1: low nibbles are its values 0..15, high nibbles 16..31
-                c_lo = (u & 1) * 4; c_hi = c_lo + 2;
-            } else {
-                // units 2g, 2g+1 = bytes 0..15, 16..31 of group g = pair g: low nibbles sub-block 2g (first half
-                // of the pair), high nibbles sub-block 2g+1 (second half)
-                c_lo = (u & 1) * 2; c_hi = 4 + c_lo;
-            }
-            *reinterpret_cast<uint4*>(rowp + (((c_lo) ^ x7) << 4)) = nib8_to_h8(l0, l1, off);
-            *reinterpret_cast<uint4*>(rowp + (((c_lo + 1) ^ x7) << 4)) = nib8_to_h8(l2, l3, off);
-            *reinterpret_cast<uint4*>(rowp + (((c_hi) ^ x7) << 4)) = nib8_to_h8(h0, h1, off);
-            *reinterpret_cast<uint4*>(rowp + (((c_hi + 1) ^ x7) << 4)) = nib8_to_h8(h2, h3, off);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        {
-            uint32_t& ph = st ? ph_b1 : ph_b0;
-            if (!dead && !mbar_wait(&bar_b[st], ph)) { dead = true; atomicOr(a.err, DEVERR_WAIT); }
-            ph ^= 1u;
-        }
-        if (tid == 0) issue(0, smBc);
-#pragma unroll
-        for (int j = 0; j < TC_CH; ++j) {
-            if (j < nb) {
-                if (j + 1 < nb && tid == 0) issue(j + 1, smBc);    // runs while block j is read below
-                uint32_t& ph = (j & 1) ? ph_m1 : ph_m0;
-                if (!dead && !mbar_wait(&bar_m[j & 1], ph)) { dead = true; atomicOr(a.err, DEVERR_WAIT); }
-                ph ^= 1u;
-                tc_fence_after();
-                const float* sx = reinterpret_cast<const float*>(smBc + TC_B_SUMS + j * (TC_COLS * 4));
-                const float fa = sa[j], fb = sb[j];
-                const uint32_t t0 = tlane + (uint32_t)(j & 1) * TC_N;
-                {
-                    float hi[32], lo[32];
-                    tc_ld32(t0 + chalf * 32, hi);
-                    tc_ld32(t0 + TC_COLS + chalf * 32, lo);
-                    tc_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const float f = fmaf(hi[c], 2048.f, lo[c]);
-                        if constexpr (WT == WT_Q4_0) acc[c] = fmaf(fa, f, acc[c]);
-                        else acc[c] = fmaf(fa, f, fmaf(fb, sx[chalf * 32 + c], acc[c]));
-                    }
-                }
-                tc_fence_before();
-                __syncthreads();                        // this accumulator (and, after the last block, the images) may be overwritten
-            }
-        }
-        cur = nxt;
-    }
-
     // ---- epilogue ----
     const int r_out = PAIR ? (tid & 63) : lane_row;             // row of the tile this thread finishes
     const int row = tile * TILE_ROWS + r_out;
     auto finish = [&](int c, float v0, float v1) {              // column c: scale back, activation, store
         if (c < a.B && row < a.N) {
-            const float sc = inv[c];
+            const float sc = inv[c] * (1.f / 64.f);             // the weights went in times 64
             float out = v0 * sc;
             if constexpr (PAIR) out = (a.epi == EPI_GEGLU ? gelu_tanh(out) : silu_clip(out)) * (v1 * sc);
             a.y[(size_t)c * a.ldy + row] = out;
@@ -595,21 +577,21 @@ int launch_gemm_tc(int wtype, const GemvArgs& a_in, cudaStream_t stream) {
     static bool attr_done = false;
     if (!attr_done) {
         cudaFuncSetAttribute(k_quant_rows, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        cudaFuncSetAttribute(k_gemm_tc<WT_Q4_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        cudaFuncSetAttribute(k_gemm_tc<WT_Q4_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        cudaFuncSetAttribute(k_gemm_tc<WT_Q4_K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
-        cudaFuncSetAttribute(k_gemm_tc<WT_Q4_K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+        cudaFuncSetAttribute(k_gemm_tc<WT_Q4_0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM2);
+        cudaFuncSetAttribute(k_gemm_tc<WT_Q4_0, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM2);
+        cudaFuncSetAttribute(k_gemm_tc<WT_Q4_K, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM2);
+        cudaFuncSetAttribute(k_gemm_tc<WT_Q4_K, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM2);
         attr_done = true;
     }
     launch_k(k_quant_rows, dim3(TC_COLS), dim3(QR_THREADS), (a.K >> 2) <= QR_THREADS * QR_MAXV ? (size_t)0 : (size_t)a.K * 4, stream, g.pdl, a, g_tc.bimg, g_tc.inv);
     count_launch();
     const dim3 grid((unsigned)(items < slots ? items : slots)), block(TC_THREADS);
     if (wtype == WT_Q4_0) {
-        if (pair) launch_k(k_gemm_tc<WT_Q4_0, true>, grid, block, (size_t)TC_SMEM, stream, g.pdl, a, (const uint8_t*)g_tc.bimg, (const float*)g_tc.inv, g_tc.part, g_tc.tickets, S, items);
-        else launch_k(k_gemm_tc<WT_Q4_0, false>, grid, block, (size_t)TC_SMEM, stream, g.pdl, a, (const uint8_t*)g_tc.bimg, (const float*)g_tc.inv, g_tc.part, g_tc.tickets, S, items);
+        if (pair) launch_k(k_gemm_tc<WT_Q4_0, true>, grid, block, (size_t)TC_SMEM2, stream, g.pdl, a, (const uint8_t*)g_tc.bimg, (const float*)g_tc.inv, g_tc.part, g_tc.tickets, S, items);
+        else launch_k(k_gemm_tc<WT_Q4_0, false>, grid, block, (size_t)TC_SMEM2, stream, g.pdl, a, (const uint8_t*)g_tc.bimg, (const float*)g_tc.inv, g_tc.part, g_tc.tickets, S, items);
     } else {
-        if (pair) launch_k(k_gemm_tc<WT_Q4_K, true>, grid, block, (size_t)TC_SMEM, stream, g.pdl, a, (const uint8_t*)g_tc.bimg, (const float*)g_tc.inv, g_tc.part, g_tc.tickets, S, items);
-        else launch_k(k_gemm_tc<WT_Q4_K, false>, grid, block, (size_t)TC_SMEM, stream, g.pdl, a, (const uint8_t*)g_tc.bimg, (const float*)g_tc.inv, g_tc.part, g_tc.tickets, S, items);
+        if (pair) launch_k(k_gemm_tc<WT_Q4_K, true>, grid, block, (size_t)TC_SMEM2, stream, g.pdl, a, (const uint8_t*)g_tc.bimg, (const float*)g_tc.inv, g_tc.part, g_tc.tickets, S, items);
+        else launch_k(k_gemm_tc<WT_Q4_K, false>, grid, block, (size_t)TC_SMEM2, stream, g.pdl, a, (const uint8_t*)g_tc.bimg, (const float*)g_tc.inv, g_tc.part, g_tc.tickets, S, items);
     }
     count_launch();
     ++g_tc_calls;
