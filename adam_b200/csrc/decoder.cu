@@ -54,7 +54,7 @@ struct Decoder {
     float *part_o, *part_ml; unsigned int* attn_ticket; uint32_t n_splits;
     int32_t *row_seq, *row_pos; // chunked prefill: (sequence, position) of every row of the chunk
     uint32_t rows_cap;          // rows the activation buffers hold: max(max_batch, PREFILL_ROWS)
-    std::vector<uint32_t> hpos, hplen;   // host mirror of positions and prompt lengths (argument checks)
+    std::vector<uint32_t> hpos, hplen, hres;   // host mirror of positions, prompt lengths and reserved tokens (argument checks)
     std::vector<int32_t> hbt;            // host mirror of the block table
     int32_t* tok_ring[4]; cudaEvent_t tok_event[4]; uint32_t tok_next;   // pinned slots for asynchronous token reads
     uint32_t batch;             // active sequences
@@ -1095,6 +1095,7 @@ extern "C" int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_
     D->batch = batch;
     D->hpos.assign(batch, 0);
     D->hplen.assign(prompt_lens, prompt_lens + batch);
+    D->hres.assign(reserve, reserve + batch);
     D->hbt = bt;
     return ADAMAH_OK;
 }
@@ -1136,6 +1137,7 @@ extern "C" int adam_b200_decoder_continue(uint32_t id, const int32_t* prompt_tok
     DCU(cudaStreamSynchronize(g.stream));
     D->hpos[0] = n_reuse;
     D->hplen[0] = prompt_len;
+    D->hres[0] = reserve;
     return ADAMAH_OK;
 }
 
@@ -1150,6 +1152,10 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
     const bool with_lm = flags & 1u, want_logits = (flags & 2u) != 0, direct = (flags & 4u) != 0;
     if (want_logits && !with_lm) return fail(ADAMAH_ERR_INVALID, "decoder_step: logits need the LM head flag");
     int rc = ADAMAH_OK;
+    // a step past the reserved pages would only set a device error bit and return ids that look valid
+    for (uint32_t b = 0; b < D->batch; ++b)
+        if ((uint64_t)D->hpos[b] + n_steps > D->hres[b])
+            return fail(ADAMAH_ERR_INVALID, "decoder_step: sequence %u is at position %u of %u reserved, cannot take %u more steps", b, D->hpos[b], D->hres[b], n_steps);
     for (uint32_t& hp : D->hpos) hp += n_steps;
     if (direct || want_logits || capturing()) {
         for (uint32_t s = 0; s < n_steps && rc == ADAMAH_OK; ++s) rc = enqueue_step(D, D->batch, with_lm, want_logits);
@@ -1378,6 +1384,9 @@ extern "C" int adam_b200_decoder_step_part(uint32_t id, uint32_t part, uint32_t 
     if (!D->batch) return fail(ADAMAH_ERR_INVALID, "decoder_step_part: call decoder_begin first");
     if (part >= n_parts(D)) return fail(ADAMAH_ERR_INVALID, "decoder_step_part: part %u of %u", part, n_parts(D));
     const bool with_lm = flags & 1u, want_logits = (flags & 2u) != 0;
+    if (part == 0)
+        for (uint32_t b = 0; b < D->batch; ++b)
+            if (D->hpos[b] + 1u > D->hres[b]) return fail(ADAMAH_ERR_INVALID, "decoder_step_part: sequence %u has used all %u reserved positions", b, D->hres[b]);
     static const bool allow = !(getenv("ADAM_B200_PDL") && atoi(getenv("ADAM_B200_PDL")) == 0);
     g.pdl = allow;
     const int rc = enqueue_part(D, D->batch, part, with_lm, want_logits);

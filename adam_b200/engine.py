@@ -214,8 +214,10 @@ class ADAMEngine:
     # ---- generate ----------------------------------------------------------------------
     def _select_sampling_mode(self, config: GenerationConfig) -> str:
         """'gpu_matvec_argmax' (fused LM head + arg-max, ids stay on the device) for greedy decoding without
-        a repeat penalty, else 'cpu': logits are read back and sampled on the host (engine.py:3760-3805)."""
-        if config.is_greedy() and (config.repeat_penalty == 1.0 or config.top_k == 1):
+        a repeat penalty -- the reference refuses that mode when a penalty is set
+        (engine.py:1876-1881) -- else 'cpu': logits are read back and sampled on the host
+        (engine.py:3760-3805)."""
+        if config.is_greedy() and config.repeat_penalty == 1.0:
             return "gpu_matvec_argmax"
         return "cpu"
 
@@ -267,7 +269,7 @@ class ADAMEngine:
         Returns (list of token lists, stats).  The host reads every step's ids (as the reference does,
         engine.py:1979) but asynchronously: up to ``sync_every`` (1..3) later steps are already queued
         while it looks at them, so a sequence may run that many steps past its EOS before the loop stops."""
-        config = config or GenerationConfig(top_k=1)
+        config = config or GenerationConfig(top_k=1, repeat_penalty=1.0)
         mode = self._select_sampling_mode(config)
         if len(prompts) == 0 or len(prompts) > self._max_batch:
             raise ValueError(f"need 1..{self._max_batch} prompts")
@@ -293,10 +295,9 @@ class ADAMEngine:
         else:
             self.begin(prompts, [max_len + config.max_tokens] * len(prompts))
         # prefill: every sequence consumes its own prompt; shorter ones start decoding earlier
-        g.batch_begin()
-        if min_len - 1 > reuse:
-            self.prefill(min_len - 1 - reuse)
-        g.batch_end()
+        with g.batch():
+            if min_len - 1 > reuse:
+                self.prefill(min_len - 1 - reuse)
         t_pre = time.perf_counter() - tp
         td = time.perf_counter()
         n_steps = (max_len - min_len) + config.max_tokens          # steps that run the LM head
@@ -310,9 +311,8 @@ class ADAMEngine:
             rng = np.random.default_rng(config.seed)
             finished = [False] * len(prompts)
             while steps_done < n_steps and not all(finished):
-                g.batch_begin()
-                self.step(1, lm_head=True, logits=True)
-                g.batch_end()
+                with g.batch():
+                    self.step(1, lm_head=True, logits=True)
                 new_pos = min_len + steps_done              # position of the token this step produced
                 steps_done += 1
                 toks = np.zeros(len(prompts), np.int32)
@@ -356,19 +356,25 @@ class ADAMEngine:
                         finished[b] = True
 
             depth = max(1, int(sync_every))
-            g.batch_begin()
-            while steps_done < n_steps and not all(finished):
-                self.step(1, lm_head=True)
-                slot = _ct.c_uint32(0)
-                self._check(self._lib.adam_b200_decoder_tokens_async(self._dec, _ct.byref(slot)), "adam_b200_decoder_tokens_async")
-                pending.append((steps_done, int(slot.value)))
-                steps_done += 1
-                if len(pending) > min(depth, 3):
+            with g.batch():
+                while steps_done < n_steps and not all(finished):
+                    self.step(1, lm_head=True)
+                    slot = _ct.c_uint32(0)
+                    self._check(self._lib.adam_b200_decoder_tokens_async(self._dec, _ct.byref(slot)), "adam_b200_decoder_tokens_async")
+                    pending.append((steps_done, int(slot.value)))
+                    steps_done += 1
+                    if len(pending) > min(depth, 3):
+                        consume(*pending.popleft())
+                while pending:
                     consume(*pending.popleft())
-            while pending:
-                consume(*pending.popleft())
-            g.batch_end()
         t_dec = time.perf_counter() - td
+        # Kernels record trouble (a position past the reserved pages, a bounded wait that ran out, a
+        # token id outside the vocabulary) in a device word instead of faulting: tokens produced
+        # after that are not trustworthy, so say so rather than return them.
+        err = g.device_error()
+        if err:
+            raise RuntimeError(f"device error word {err:#x} after generation (1 = index outside its buffer, "
+                               f"2 = a bounded device-side wait ran out, 4 = token id outside the vocabulary)")
         outs: List[List[int]] = []
         for b, n in enumerate(lens):
             outs.append(sampled[b])

@@ -50,8 +50,23 @@ def mat_shapes(cfg: ModelConfig) -> Dict[str, tuple]:
     }
 
 
+_QUANT_CHUNK_ROWS = 4096
+
+
 def _quantize(w: np.ndarray, ggml_type: int) -> QTensor:
-    raw = gb.quantize_q4_0(w) if ggml_type == gb.GGML_TYPE_Q4_0 else gb.quantize_q4_k(w)
+    """Encode a matrix; large ones in row chunks on a thread pool (the encoders are
+    row-independent numpy code that releases the GIL, so the bytes do not depend on the split)."""
+    enc = gb.quantize_q4_0 if ggml_type == gb.GGML_TYPE_Q4_0 else gb.quantize_q4_k
+    rows = w.shape[0]
+    if rows <= _QUANT_CHUNK_ROWS:
+        raw = enc(w)
+    else:
+        import os
+        from concurrent.futures import ThreadPoolExecutor
+        cuts = list(range(0, rows, _QUANT_CHUNK_ROWS)) + [rows]
+        with ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as ex:
+            parts = list(ex.map(lambda i: enc(w[cuts[i]:cuts[i + 1]]), range(len(cuts) - 1)))
+        raw = np.concatenate(parts, axis=0)
     return QTensor(ggml_type, w.shape[0], w.shape[1], np.ascontiguousarray(raw).reshape(-1))
 
 

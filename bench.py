@@ -6,12 +6,14 @@ random prompt, greedy decode): one "step" is one decoded token.
 
 Prints ONE JSON line.  ``value`` is decode tok/s with everything resident in HBM
 (K graph replays timed with CUDA events on the library's stream); ``e2e`` is the
-same metric through ``ADAMEngine.generate`` with host prompt ids, the host->device
-prompt copy and one device->host token read per step inside the timed region.
+same metric through ``ADAMEngine.generate`` with host prompt ids: generated tokens divided by
+the whole call's time, i.e. the host->device prompt copy, the chunked prefill, every decode step
+and one device->host token read per step are all inside the timed region.
 ``roofline`` is the dominant kernel (the dequant GEMV, measured on the LM-head
 shape, 262144 x 1152 Q4_0, whose 170 MB exceed L2) against the measured HBM copy
 bandwidth.  ``cpu_baseline`` is the numpy restatement of the reference's CPU decoder
-timed on this box's host cores on a bounded sample.  With N > 1 (torchrun, one
+timed on this box's host cores on a bounded sample (same weights, same prompt); its greedy ids
+are compared with the GPU arm's (``ids_equal_oracle``).  With N > 1 (torchrun, one
 rank per GPU) every rank runs an independent replica: no collective on the data
 path, weak scaling, value = all ranks' tokens / slowest rank's time.
 """
@@ -100,33 +102,45 @@ def dist_env():
     return _env()
 
 
-def cpu_decode_sample(cfg, tensors, n_prompt, n_decode, warmup):
-    """Numpy restatement of the reference's CPU decoder on the same weights:
-    returns decode tok/s over ``n_decode`` tokens after an ``n_prompt``-token prefill."""
+def set_blas_threads():
+    """Use every host core for the numpy BLAS (torchrun exports OMP_NUM_THREADS=1 to its ranks)."""
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=os.cpu_count() or 1)
+    except Exception:
+        pass
+
+
+def cpu_decode_sample(cfg, tensors, prompt, n_decode):
+    """Numpy restatement of the reference's CPU decoder (tests/diagnostics/diag_inference.py:934-1061)
+    on the given weights, with the cache rounding and window mask of the benchmark configuration:
+    consumes ``prompt`` token by token, then decodes ``n_decode`` greedy tokens.  Returns (decode
+    tok/s, seconds of decode, seconds of prompt, decoded ids)."""
     from oracle.decoder import OracleDecoder
     from oracle import cref
     from adam_b200 import synth
-    t0 = time.perf_counter()
+    set_blas_threads()
     f32 = {}
     for name, t in tensors.items():
         if isinstance(t, np.ndarray):
             f32[name] = t
         else:       # the reference pre-decodes every matrix to float32 (diag_inference.py:966-969)
             f32[name] = cref.dequant(synth.raw_to_host(t), t.ggml_type, t.rows, t.cols)
-    t_deq = time.perf_counter() - t0
-    dec = OracleDecoder(cfg, f32, kv_cap=n_prompt + n_decode + warmup + 1)
-    prompt = synth.random_prompt(cfg.n_vocab, n_prompt, seed=1)
+    dec = OracleDecoder(cfg, f32, kv_cap=len(prompt) + n_decode + 1, window=True, kv_dtype=np.float16)
+    t0 = time.perf_counter()
     logits = None
     for i, t in enumerate(prompt):
-        logits = dec.forward(int(t), i, want_logits=(i == n_prompt - 1))
-    pos = n_prompt
-    for _ in range(warmup):
-        logits = dec.forward(int(np.argmax(logits)), pos); pos += 1
+        logits = dec.forward(int(t), i, want_logits=(i == len(prompt) - 1))
+    t_prompt = time.perf_counter() - t0
+    pos = len(prompt)
+    ids = []
     t0 = time.perf_counter()
     for _ in range(n_decode):
-        logits = dec.forward(int(np.argmax(logits)), pos); pos += 1
+        tok = int(np.argmax(logits))
+        ids.append(tok)
+        logits = dec.forward(tok, pos); pos += 1
     dt = time.perf_counter() - t0
-    return n_decode / dt, dt, t_deq
+    return n_decode / dt, dt, t_prompt, ids
 
 
 def threads_used():
@@ -171,18 +185,18 @@ def main():
         # (numpy decoder) is timed on the host cores.  Rank 0 only.
         if rank != 0:
             return
-        import torch
-        import adam_b200 as A
+        from adam_b200 import gguf_blocks as gb
         from adam_b200 import synth
-        gpu = A.init()
-        tensors = synth.build_model_cuda(gpu, cfg, seed=0)       # same seeded weights as the CUDA arm
-        n_dec = min(steps, 24)
-        tps, dt, t_deq = cpu_decode_sample(cfg, tensors, 16, n_dec, min(warmup, 3))
-        gpu.shutdown()
+        # Seeded N(0, 0.02) weights quantized to Q4_0 on the host (numpy): this arm loads no CUDA library.
+        tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=0)
+        prompt = synth.random_prompt(cfg.n_vocab, PROMPT_LEN, seed=1)
+        n_dec = min(steps, 128)
+        tps, dt, t_prompt, _ = cpu_decode_sample(cfg, tensors, prompt, n_dec)
         cores = threads_used()
-        sample = f"full {cfg.n_layer}-layer model, 16-token prefill, {n_dec} decode tokens (of --steps {steps}); fp32 numpy on dequantized weights"
+        sample = (f"full {cfg.n_layer}-layer model, {PROMPT_LEN}-token prompt consumed token by token ({t_prompt:.1f} s, untimed), then {n_dec} greedy "
+                  f"tokens timed ({dt:.1f} s; --steps {steps}); numpy restatement of the reference's CPU decoder on float32 weights decoded from Q4_0")
         print(json.dumps({"impl": "reference", "metric": "decode tok/s (Gemma-3-1B-shape Q4, b=1)", "value": tps, "unit": "tok/s",
-                          "n_gpus": world, "steps": n_dec, "warmup": min(warmup, 3), "ms_per_step": 1000.0 / tps, "higher_is_better": True,
+                          "n_gpus": world, "steps": n_dec, "warmup": 0, "ms_per_step": 1000.0 / tps, "higher_is_better": True,
                           "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload,
                           "cpu_baseline": {"value": tps, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
                           "e2e": {"value": tps, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
@@ -204,7 +218,7 @@ def main():
     tensors = synth.build_model_cuda(gpu, cfg, seed=0)
     torch.cuda.synchronize()
     kv_cap = PROMPT_LEN + warmup + steps + 8
-    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=kv_cap, kv_dtype="f16")
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=kv_cap, kv_dtype="f16", window=True)
     t_build = time.perf_counter() - t_build
     prompt = synth.random_prompt(cfg.n_vocab, PROMPT_LEN, seed=1)
 
@@ -235,12 +249,14 @@ def main():
     tokens_kernel = eng.read_log(0, PROMPT_LEN + warmup, steps)
 
     # ---- end to end through the public API: host prompt in, one token read back per step ----
-    gen_cfg = GenerationConfig(max_tokens=warmup + steps, top_k=1, temperature=0.0, eos_token_ids=())
-    eng.generate(prompt, GenerationConfig(max_tokens=4, top_k=1, temperature=0.0, eos_token_ids=()))      # warm
+    gen_cfg = GenerationConfig(max_tokens=warmup + steps, top_k=1, temperature=0.0, repeat_penalty=1.0, eos_token_ids=())
+    eng.generate(prompt, GenerationConfig(max_tokens=4, top_k=1, temperature=0.0, repeat_penalty=1.0, eos_token_ids=()))      # warm
     barrier()
     out, st = eng.generate(prompt, gen_cfg, sync_every=1)
     barrier()
-    e2e_tps = st["decode_tps"]
+    # the timed region of this figure starts before the prompt's host->device copy (begin) and ends after the
+    # last token id has been read back: prompt copy, chunked prefill, every decode step and its 4-byte read
+    e2e_tps = st["n_gen"] / st["total_s"]
     same_ids = [int(t) for t in tokens_kernel] == out[warmup:warmup + steps]
 
     # ---- dominant kernel: the dequant GEMV on the LM-head shape, alone on the stream --------
@@ -273,18 +289,24 @@ def main():
     line = None
     if rank == 0:
         cpu = None
+        ids_equal_oracle = None
         if not args.no_cpu_baseline and world == 1:
-            n_dec = 16
-            tps, dt, t_deq = cpu_decode_sample(cfg, tensors, 16, n_dec, 2)
+            n_dec = min(len(out), 128)
+            tps, dt, t_prompt, cpu_ids = cpu_decode_sample(cfg, tensors, prompt, n_dec)
+            ids_equal_oracle = (cpu_ids == out[:n_dec])
             cpu = {"value": tps, "unit": "tok/s", "cores": threads_used(), "kind": "port",
-                   "sample": f"full {cfg.n_layer}-layer model, 16-token prefill then {n_dec} decode tokens ({dt:.1f} s); "
-                             f"numpy restatement of the reference CPU decoder on dequantized fp32 weights"}
+                   "sample": f"full {cfg.n_layer}-layer model, same weights and {PROMPT_LEN}-token prompt as the GPU arm ({t_prompt:.1f} s, untimed), "
+                             f"then {n_dec} greedy tokens timed ({dt:.1f} s); numpy restatement of the reference CPU decoder on float32 weights decoded from Q4_0"}
         line = {
             "metric": "decode tok/s (Gemma-3-1B-shape Q4, b=1)", "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": workload,
+            "dtype": "f32 accumulate; weights int4 blocks; GEMV activations rounded to 23-bit block fixed point", "data": "synthetic", "config": workload,
             "e2e": {"value": comb["e2e"], "unit": "tok/s", "h2d_bytes_per_step": st["h2d_bytes"] / max(1, st["n_gen"]),
-                    "d2h_bytes_per_step": st["d2h_bytes"] / max(1, st["n_gen"]), "ids_equal_device_run": same_ids},
+                    "d2h_bytes_per_step": st["d2h_bytes"] / max(1, st["n_gen"]), "ids_equal_device_run": same_ids,
+                    "timed_region": "ADAMEngine.generate from the prompt's host-to-device copy to the last token read: "
+                                    "prompt copy + chunked prefill + every decode step with its 4-byte token read",
+                    "decode_only_tok_s": st["decode_tps"]},
+            "ids_equal_oracle": ids_equal_oracle, "ids_compared": (len(cpu_ids) if cpu else 0),
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
                          "traffic": LMHEAD_DRAM_TRAFFIC, "kernel": "k_gemv_mma<4,false> (LM head %dx%d Q4_0 + arg-max, tensor-core path)" % (N, K),

@@ -28,6 +28,8 @@ def lib():
         _lib.q4_dequant.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_void_p]
         _lib.q4_gemv.restype = ctypes.c_int
         _lib.q4_gemv.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+        _lib.q4_gemv_f64.restype = ctypes.c_int
+        _lib.q4_gemv_f64.argtypes = _lib.q4_gemv.argtypes
     return _lib
 
 
@@ -51,4 +53,15 @@ def gemv(raw: np.ndarray, ggml_type: int, N: int, K: int, x: np.ndarray) -> np.n
     rc = lib().q4_gemv(raw.ctypes.data, ggml_type, N, K, x.ctypes.data, x.shape[0], y.ctypes.data)
     if rc:
         raise ValueError(f"q4_gemv failed ({rc})")
+    return y
+
+
+def gemv_f64(raw: np.ndarray, ggml_type: int, N: int, K: int, x: np.ndarray) -> np.ndarray:
+    """Same product with double-precision terms and sums (float64 ``[B, N]``)."""
+    raw = np.ascontiguousarray(raw, np.uint8).reshape(-1)
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, K)
+    y = np.empty((x.shape[0], N), np.float64)
+    rc = lib().q4_gemv_f64(raw.ctypes.data, ggml_type, N, K, x.ctypes.data, x.shape[0], y.ctypes.data)
+    if rc:
+        raise ValueError(f"q4_gemv_f64 failed ({rc})")
     return y

@@ -145,6 +145,37 @@ static void gemv_range(int64_t lo, int64_t hi, void* p) {
     }
 }
 
+/* The same product with every term and the sum in double: a reference whose own rounding
+ * error is negligible beside the 1e-3 tolerance, for long rows (K of tens of thousands). */
+typedef struct { const uint8_t* raw; int type; int64_t N, K, B; const float* x; double* y; } gemv64_ctx;
+static void gemv64_range(int64_t lo, int64_t hi, void* p) {
+    gemv64_ctx* c = (gemv64_ctx*)p;
+    const int64_t be = c->type == 2 ? 32 : 256, bb = c->type == 2 ? 18 : 144, nb = c->K / be;
+    for (int64_t n = lo; n < hi; ++n) {
+        double acc[64];
+        float w[256];
+        for (int64_t b = 0; b < c->B; ++b) acc[b] = 0.0;
+        for (int64_t i = 0; i < nb; ++i) {
+            const uint8_t* blk = c->raw + (n * nb + i) * bb;
+            if (c->type == 2) dq4_0_block(blk, w); else dq4_k_block(blk, w);
+            for (int64_t b = 0; b < c->B; ++b) {
+                const float* xb = c->x + b * c->K + i * be;
+                double s = acc[b];
+                for (int64_t k = 0; k < be; ++k) s += (double)w[k] * (double)xb[k];
+                acc[b] = s;
+            }
+        }
+        for (int64_t b = 0; b < c->B; ++b) c->y[b * c->N + n] = acc[b];
+    }
+}
+int q4_gemv_f64(const uint8_t* raw, int ggml_type, int64_t N, int64_t K, const float* x, int64_t B, double* y) {
+    const int64_t be = ggml_type == 2 ? 32 : 256;
+    if ((ggml_type != 2 && ggml_type != 12) || K % be || B < 1 || B > 64) return -1;
+    gemv64_ctx c = {raw, ggml_type, N, K, B, x, y};
+    parallel_for(N, gemv64_range, &c);
+    return 0;
+}
+
 /* y[b][n] = sum_k W[n][k] x[b][k], rows decoded on the fly, float32 accumulation in
  * index order.  x is [B][K], y is [B][N], B <= 64. */
 int q4_gemv(const uint8_t* raw, int ggml_type, int64_t N, int64_t K, const float* x, int64_t B, float* y) {

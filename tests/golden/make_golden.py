@@ -22,6 +22,13 @@ reference tree is not needed when the tests run.  What each file pins:
                           (tests/diagnostics/diag_inference.py:917-1074) for small
                           Gemma-3-shaped models built by ``adam_b200.synth.build_model``
                           (tied / untied LM head, with / without QK-norm and post-norms).
+``decode_1b.npz``         (only with ``--full-size``; takes several minutes and ~12 GB of RAM)
+                          the same, at the full Gemma-3-1B shape of the headline benchmark:
+                          26 layers, hidden 1152, vocabulary 262144, Q4_0, a 128-token prompt and
+                          128 greedy tokens, tied and untied LM head.  Beside the reference's ids the
+                          file records the smallest gap between the best and the second-best logit
+                          along the decoded path (from the numpy restatement, whose ids must equal the
+                          reference's), so a reader can see how well-conditioned the arg-max is.
 """
 import argparse
 import hashlib
@@ -50,6 +57,7 @@ DECODE_CASES = [
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("ADAM_REFERENCE_DIR", ""))
+    ap.add_argument("--full-size", action="store_true", help="write decode_1b.npz (1B-shape model) instead of the small fixtures")
     args = ap.parse_args()
     ref = args.reference
     if not ref or not os.path.isdir(ref):
@@ -66,6 +74,9 @@ def main():
     from adam_b200 import synth
     from adam_b200.config import tiny_gemma3
     from dataclasses import asdict, replace
+
+    if args.full_size:
+        return full_size(ref, gguf, T, RefModelConfig)
 
     loader = GGUFLoader.__new__(GGUFLoader)
     rng = np.random.default_rng(20240601)
@@ -155,6 +166,76 @@ def main():
         out[f"{name}_sha256"] = np.frombuffer(h.digest(), np.uint8)
     np.savez_compressed(os.path.join(HERE, "decode_tiny.npz"), **out)
     print("fixtures written to", HERE)
+
+
+# the full-size decode cases: (name, build kwargs, n_prompt, n_gen); the model is
+# adam_b200.config.gemma3_1b() built by adam_b200.synth.build_model on the host
+FULL_SIZE_CASES = [
+    ("tied", dict(seed=21, tied=True), 128, 128),
+    ("untied", dict(seed=22, tied=False), 128, 128),
+]
+
+
+def full_size(ref, gguf, T, RefModelConfig):
+    """Greedy ids of the unmodified reference decoder at the Gemma-3-1B shape."""
+    from dataclasses import asdict
+    from adam_b200 import gguf_blocks as gb
+    from adam_b200 import synth
+    from adam_b200.config import gemma3_1b
+    from oracle import cref
+    from oracle.decoder import OracleDecoder
+
+    spec = importlib.util.spec_from_file_location("ref_diag_inference", os.path.join(ref, "tests/diagnostics/diag_inference.py"))
+    diag = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(diag)
+    cfg = gemma3_1b()
+    out = {}
+    for name, bkw, n_prompt, n_gen in FULL_SIZE_CASES:
+        tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, **bkw)
+        h = hashlib.sha256()
+        f32 = {}
+        for k in sorted(tensors):
+            t = tensors[k]
+            if isinstance(t, np.ndarray):
+                f32[k] = t
+                h.update(t.tobytes())
+            else:
+                h.update(t.raw.tobytes())
+                f32[k] = cref.dequant(t.raw, t.ggml_type, t.rows, t.cols)
+        # the threaded C decode is the same bits as gguf.dequantize (spot check on one layer's matrices)
+        for k in ("blk.0.attn_q.weight", "blk.0.ffn_down.weight"):
+            t = tensors[k]
+            lib = gguf.dequantize(t.raw.reshape(t.rows, -1), T.Q4_0).reshape(t.rows, t.cols)
+            assert np.array_equal(lib.view(np.uint32), f32[k].view(np.uint32))
+        del tensors
+        prompt = synth.random_prompt(cfg.n_vocab, n_prompt, seed=bkw["seed"] + 100)
+        rcfg = RefModelConfig(**{k: v for k, v in asdict(cfg).items()})
+
+        class Tok:
+            eos_id = -1; bos_id = 2; _specials = {}; _vocab = None
+            def encode(self, text, add_bos=True): return [int(x) for x in prompt]
+            def decode(self, toks): return " ".join(map(str, toks))
+
+        eng = types.SimpleNamespace(tensors=f32, _kv_cap=n_prompt + n_gen + 1)
+        with contextlib.redirect_stdout(io.StringIO()):
+            diag.check_cpu_generation(eng, Tok(), rcfg, n_tokens=n_gen)
+        toks = np.array(eng._last_cpu_gen_tokens, np.int32)
+        # the restatement must reproduce them; it also yields the logits, hence the arg-max margins
+        dec = OracleDecoder(cfg, f32, kv_cap=n_prompt + n_gen + 1)
+        got, logits = dec.generate(prompt, n_gen, keep_logits=True)
+        assert got == toks.tolist(), "oracle/decoder.py does not reproduce the reference's ids at full size"
+        gaps = []
+        for lg in logits:
+            top2 = np.partition(lg, -2)[-2:]
+            gaps.append(float(top2[1] - top2[0]))
+        print(f"{name}: {toks.tolist()}\n  smallest top-2 logit gap along the path: {min(gaps):.3e} (largest |logit| {float(np.abs(logits[0]).max()):.3f})")
+        out[f"{name}_tokens"] = toks
+        out[f"{name}_prompt"] = prompt
+        out[f"{name}_sha256"] = np.frombuffer(h.digest(), np.uint8)
+        out[f"{name}_top2_gaps"] = np.array(gaps, np.float32)
+        del f32, eng, dec
+    np.savez_compressed(os.path.join(HERE, "decode_1b.npz"), **out)
+    print("decode_1b.npz written to", HERE)
 
 
 if __name__ == "__main__":

@@ -16,7 +16,7 @@ from tests.golden.make_golden import DECODE_CASES
 
 pytestmark = pytest.mark.gpu
 
-GREEDY = dict(top_k=1, temperature=0.0, eos_token_ids=())
+GREEDY = dict(top_k=1, temperature=0.0, repeat_penalty=1.0, eos_token_ids=())
 
 
 def _cfg(ckw):
@@ -288,7 +288,7 @@ def test_eos_stops_generation_and_kv_cap_is_enforced(gpu):
     try:
         full, _ = eng.generate(prompt, GenerationConfig(max_tokens=10, **GREEDY))
         eos = full[4]
-        cut, _ = eng.generate(prompt, GenerationConfig(max_tokens=10, top_k=1, temperature=0.0, eos_token_ids=(eos,)))
+        cut, _ = eng.generate(prompt, GenerationConfig(max_tokens=10, top_k=1, temperature=0.0, repeat_penalty=1.0, eos_token_ids=(eos,)))
         assert cut == full[:full.index(eos)]
         with pytest.raises(RuntimeError, match="KV cache too small"):
             eng.generate(prompt, GenerationConfig(max_tokens=27, **GREEDY))

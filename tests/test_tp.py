@@ -19,7 +19,7 @@ from oracle.decoder import OracleDecoder, dequant_model
 from oracle.q4_blocks import dequant_q4_0, dequant_q4_k
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-GREEDY = dict(top_k=1, temperature=0.0, eos_token_ids=())
+GREEDY = dict(top_k=1, temperature=0.0, repeat_penalty=1.0, eos_token_ids=())
 
 
 def _deq(t):

@@ -34,12 +34,12 @@ def main():
     gpu = A.init()
     eng = ADAMEngineTP(gpu, cfg, tensors, rank, world, kv_cap=128, kv_dtype="f32", allreduce=allreduce)
     ar_used = eng._ar is not None
-    toks, _ = eng.generate(prompt, GenerationConfig(max_tokens=n_gen, top_k=1, temperature=0.0, eos_token_ids=()))
+    toks, _ = eng.generate(prompt, GenerationConfig(max_tokens=n_gen, top_k=1, temperature=0.0, repeat_penalty=1.0, eos_token_ids=()))
     graph_used = bool(eng._graphs)
     # a prompt of more than one 64-row chunk: chunked prefill (all-reduces of 64 and 13 rows, then of
     # one row per decode step) against the same prompt consumed token by token
     long_prompt = list(map(int, synth.random_prompt(cfg.n_vocab, 78, seed=5)))
-    long_toks, _ = eng.generate(long_prompt, GenerationConfig(max_tokens=6, top_k=1, temperature=0.0, eos_token_ids=()))
+    long_toks, _ = eng.generate(long_prompt, GenerationConfig(max_tokens=6, top_k=1, temperature=0.0, repeat_penalty=1.0, eos_token_ids=()))
     eng.begin([long_prompt], [128])
     eng.prefill(len(long_prompt) - 1, chunked=False)
     by_token = []
