@@ -16,6 +16,7 @@
 #include "gemv.cuh"
 #include "gemv_mma.cuh"
 #include "gemm_tc.cuh"
+#include "token.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -61,6 +62,8 @@ struct Decoder {
     bool use_tiles;             // build row-tiled weight copies for the tensor-core GEMV
     std::vector<uint32_t> free_pages;
     cudaGraphExec_t graph[2]; cudaGraph_t graph_src[2]; uint32_t graph_batch[2]; uint64_t graph_kernels[2];
+    // single-launch token kernel (token.cuh): 0 = not examined yet, 1 = ready, -1 = this model does not qualify
+    int tk_state; TkArgs tk; int tk_grid; int tk_wt; void* tk_mem[9];
 };
 
 constexpr uint32_t MAX_DECODERS = 8;
@@ -76,11 +79,6 @@ static Decoder* get_dec(uint32_t id) {
 }
 
 // ---- kernels ---------------------------------------------------------------
-
-__device__ __forceinline__ float ld_kv(const float* p) { return *p; }
-__device__ __forceinline__ float ld_kv(const __half* p) { return __half2float(*p); }
-__device__ __forceinline__ void st_kv(float* p, float v) { *p = v; }
-__device__ __forceinline__ void st_kv(__half* p, float v) { *p = __float2half_rn(v); }
 
 // h[b] = dequant(token_embd[row tok]) * emb_scale   (diag_inference.py:975-977)
 template <int WT>
@@ -136,14 +134,6 @@ __global__ void k_embed(const WeightRef w, uint32_t n_embd, uint32_t n_vocab, fl
     }
 }
 
-struct KvGeom {
-    uint32_t n_layer, n_kv, hd, page, max_pages;   // page = tokens per page
-    size_t page_elems;                              // elements of one page (all layers, K and V)
-};
-__device__ __forceinline__ size_t kv_index(const KvGeom& g, uint32_t page_id, uint32_t layer, uint32_t kv, uint32_t head, uint32_t slot) {
-    return (size_t)page_id * g.page_elems + ((((size_t)layer * 2 + kv) * g.n_kv + head) * g.page + slot) * g.hd;
-}
-
 // Decode attention for one (split, kv head, sequence), all query heads that share
 // the kv head, with the steps that precede it folded in:
 //   * per-head RMSNorm + half-split RoPE of the query rows (map_qk_norm_rope_x.comp),
@@ -166,88 +156,6 @@ __device__ __forceinline__ size_t kv_index(const KvGeom& g, uint32_t page_id, ui
 // CTA that finishes last.
 constexpr int ATTN_CP = 8;
 constexpr uint32_t ATTN_CHUNKS_PER_CTA = 32;   // chunks a CTA takes (4 per warp) before another CTA joins
-
-template <typename T, int DPL> struct KvRow {
-    static constexpr int BYTES = DPL * (int)sizeof(T);
-    static constexpr int NW = BYTES >= 4 ? BYTES / 4 : 1;
-    uint32_t w[NW];
-    __device__ __forceinline__ void zero() {
-#pragma unroll
-        for (int i = 0; i < NW; ++i) w[i] = 0u;
-    }
-    __device__ __forceinline__ void load(const T* p) {
-        if constexpr (BYTES == 32) {
-            const uint4 a = reinterpret_cast<const uint4*>(p)[0], b = reinterpret_cast<const uint4*>(p)[1];
-            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-        } else if constexpr (BYTES == 16) {
-            const uint4 a = *reinterpret_cast<const uint4*>(p);
-            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
-        } else if constexpr (BYTES == 8) {
-            const uint2 a = *reinterpret_cast<const uint2*>(p);
-            w[0] = a.x; w[1] = a.y;
-        } else if constexpr (BYTES == 4) {
-            w[0] = *reinterpret_cast<const uint32_t*>(p);
-        } else {
-            w[0] = *reinterpret_cast<const unsigned short*>(p);
-        }
-    }
-    __device__ __forceinline__ void from_float(const float* f) {      // values already rounded to T
-        if constexpr (sizeof(T) == 4) {
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) w[i] = __float_as_uint(f[i]);
-        } else if constexpr (DPL >= 2) {
-#pragma unroll
-            for (int i = 0; i < DPL / 2; ++i) {
-                const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
-                w[i] = *reinterpret_cast<const uint32_t*>(&h);
-            }
-        } else {
-            w[0] = __half_as_ushort(__float2half_rn(f[0]));
-        }
-    }
-    __device__ __forceinline__ void to_float(float (&f)[DPL]) const {
-        if constexpr (sizeof(T) == 4) {
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) f[i] = __uint_as_float(w[i]);
-        } else if constexpr (DPL >= 2) {
-#pragma unroll
-            for (int i = 0; i < DPL / 2; ++i) {
-                const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-                f[2 * i] = v.x; f[2 * i + 1] = v.y;
-            }
-        } else {
-            f[0] = __half2float(__ushort_as_half((unsigned short)w[0]));
-        }
-    }
-};
-template <typename T> __device__ __forceinline__ float kv_round(float v);
-template <> __device__ __forceinline__ float kv_round<__half>(float v) { return __half2float(__float2half_rn(v)); }
-template <> __device__ __forceinline__ float kv_round<float>(float v) { return v; }
-
-// Sum a[0..NV) over the 32 lanes.  NV >= 32: lane l ends with the totals of values
-// l*NV/32 .. in a[0..NV/32).  NV < 32: the 32/NV lanes v*32/NV .. end with value v in a[0].
-template <int NV>
-__device__ __forceinline__ void warp_reduce_scatter(float (&a)[NV], uint32_t lane) {
-    int n = NV;
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-        if (n > 1) {
-            const int h = n >> 1;
-            const bool up = (lane & off) != 0;
-#pragma unroll
-            for (int i = 0; i < NV / 2; ++i) {
-                if (i < h) {
-                    const float send = up ? a[i] : a[i + h];
-                    const float keep = up ? a[i + h] : a[i];
-                    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-                }
-            }
-            n = h;
-        } else {
-            a[0] += __shfl_xor_sync(0xffffffffu, a[0], off);
-        }
-    }
-}
 
 template <typename T, int GS_MAX, int HD>
 __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv, uint32_t qkv_ld,
@@ -724,15 +632,23 @@ __global__ void k_fill_i32(int32_t* p, int32_t v, size_t n) {
 
 // ---- host side ---------------------------------------------------------------
 
+static void free_token_kernel(Decoder* D) {
+    if (D->tk_state == 1) cudaStreamSynchronize(g.stream);
+    for (void*& m : D->tk_mem) { if (m) cudaFree(m); m = nullptr; }
+    D->tk_state = 0;
+}
+
 static void free_graphs(Decoder* D) {
     for (int i = 0; i < 2; ++i) {
         if (D->graph[i]) { cudaGraphExecDestroy(D->graph[i]); cudaGraphDestroy(D->graph_src[i]); D->graph[i] = nullptr; D->graph_src[i] = nullptr; }
     }
+    free_token_kernel(D);
 }
 
 static void destroy(Decoder* D) {
     cudaStreamSynchronize(g.stream);
     free_graphs(D);
+    free_token_kernel(D);
     for (int i = 0; i < 4; ++i) { if (D->tok_ring[i]) cudaFreeHost(D->tok_ring[i]); if (D->tok_event[i]) cudaEventDestroy(D->tok_event[i]); }
     void* ptrs[] = {D->pos, D->cur_tok, D->cur_val, D->prompt_len, D->prompt_tok, D->gen_log, D->block_table, D->kv_pool, D->hbuf[0], D->hbuf[1], D->qkv,
                     D->attn_out, D->proj, D->act, D->logits, D->part_o, D->part_ml, D->attn_ticket, D->row_seq, D->row_pos,
@@ -918,6 +834,146 @@ static int validate_bound(Decoder* D) {
     return ADAMAH_OK;
 }
 
+// ---- single-launch token kernel: eligibility, work split, buffers -----------------------------
+
+// Spread one product over the grid (see TkPhase): the estimate is the number of tile pairs the busiest
+// warp walks plus fixed costs per row group, per K split inside the CTA and per K split across CTAs.
+static bool tk_pick_phase(TkPhase& P, int n_rg, int pairs, int nm, int grid, int max_cpr) {
+    double best = 1e300;
+    bool found = false;
+    for (int cpr = 1; cpr <= max_cpr; ++cpr) {
+        for (int KS = 1; KS <= TK_NW; ++KS) {
+            const int RG = TK_NW / KS;
+            if (RG < 1 || KS * cpr > pairs) continue;
+            if (KS > 1 && RG > 15) continue;                   // named barriers 1..15
+            const int n_sets = (n_rg + RG - 1) / RG;
+            int G = grid / cpr;
+            if (G > n_sets) G = n_sets;
+            if (G < 1) continue;
+            const int sets_per_cta = (n_sets + G - 1) / G;
+            const int per_warp = (pairs + KS * cpr - 1) / (KS * cpr);
+            const double cost = (double)sets_per_cta * (per_warp * nm + 2.0) + (KS > 1 ? 1.0 : 0.0) + (cpr > 1 ? 1.0 : 0.0) + 0.01 * KS;
+            if (cost < best) { best = cost; P.n_rg = n_rg; P.pairs = pairs; P.RG = RG; P.KS = KS; P.cpr = cpr; P.G = G; found = true; }
+        }
+    }
+    return found;
+}
+
+static int prepare_token_kernel(Decoder* D) {
+    const adam_b200_decoder_desc& d = D->d;
+    D->tk_state = -1;
+    static const bool allow = !(getenv("ADAM_B200_TOKEN_KERNEL") && atoi(getenv("ADAM_B200_TOKEN_KERNEL")) == 0);
+    if (!allow || !D->use_tiles || d.tp_size > 1) return ADAMAH_OK;
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, g.device);
+    if (!coop) return ADAMAH_OK;
+    const uint32_t E = d.n_embd, q_dim = d.n_head * d.head_dim, k_dim = d.n_head_kv * d.head_dim, FF = d.n_ff;
+    if (!token_supported_hd((int)d.head_dim) || d.n_layer > (uint32_t)TK_MAX_LAYERS || d.page_size % 8) return ADAMAH_OK;
+    if (E % 64 || q_dim % 64 || FF % 64 || E > (uint32_t)TK_MAX_E || q_dim > 2u * TK_THREADS * 4u) return ADAMAH_OK;
+    const Mat& lm = D->output.bound ? D->output : D->embd;
+    if (!lm.tiled || lm.rows % 16) return ADAMAH_OK;
+    const int wt = lm.wtype;
+    if (wt == WT_Q4_K && (E % 256 || q_dim % 256 || FF % 256)) return ADAMAH_OK;
+    auto al16 = [](const void* p) { return ((uintptr_t)p & 15u) == 0; };
+    if (!al16(D->output_norm)) return ADAMAH_OK;
+    for (uint32_t L = 0; L < d.n_layer; ++L) {
+        const Layer& ly = D->layers[L];
+        if (!ly.qkv_contiguous || !ly.qkv_tiled || !ly.m[MAT_O].tiled || !ly.m[MAT_GATE].tiled || !ly.m[MAT_UP].tiled || !ly.m[MAT_DOWN].tiled) return ADAMAH_OK;
+        for (int k : {MAT_Q, MAT_O, MAT_GATE, MAT_UP, MAT_DOWN}) if (ly.m[k].wtype != wt) return ADAMAH_OK;
+        for (int k : {NORM_ATTN, NORM_POST_ATTN, NORM_FFN, NORM_POST_FFW}) if (!al16(ly.norm[k])) return ADAMAH_OK;
+    }
+    TkArgs a = {};
+    // the gate/up product decides the grid: every CTA must take part in it (it is what makes each CTA's
+    // reads a precondition of the next layer, see token_kernel.cuh), so a product with fewer sets than SMs
+    // shrinks the grid instead
+    int grid = g.sm_count;
+    {
+        TkPhase best = {}; double best_cost = 1e300; int best_grid = 0;
+        for (int KS = 1; KS <= TK_NW; ++KS) {
+            const int RG = TK_NW / KS, pairs = (int)E / 64, n_rg = (int)FF / 16;
+            if (KS > pairs || (KS > 1 && RG > 15)) continue;
+            const int n_sets = (n_rg + RG - 1) / RG;
+            const int gr = n_sets < g.sm_count ? n_sets : g.sm_count;
+            const int sets_per_cta = (n_sets + gr - 1) / gr;
+            const int per_warp = (pairs + KS - 1) / KS;
+            // idle SMs cost LM-head bandwidth: weigh them in
+            const double cost = ((double)sets_per_cta * (per_warp * 2 + 2.0) + (KS > 1 ? 1.0 : 0.0) + 0.01 * KS) * (1.0 + 2.0 * (g.sm_count - gr) / (double)g.sm_count);
+            if (cost < best_cost) { best_cost = cost; best_grid = gr; best.n_rg = n_rg; best.pairs = pairs; best.RG = RG; best.KS = KS; best.cpr = 1; best.G = gr; }
+        }
+        if (best_grid < 1) return ADAMAH_OK;
+        grid = best_grid;
+        a.ph[TK_GU] = best;
+    }
+    if (grid < (int)d.n_head) return ADAMAH_OK;
+    if (!tk_pick_phase(a.ph[TK_QKV], (int)(q_dim + 2 * k_dim) / 16, (int)E / 64, 1, grid, 1)) return ADAMAH_OK;
+    if (!tk_pick_phase(a.ph[TK_O], (int)E / 16, (int)q_dim / 64, 1, grid, 1)) return ADAMAH_OK;
+    if (!tk_pick_phase(a.ph[TK_DOWN], (int)E / 16, (int)FF / 64, 1, grid, 2)) return ADAMAH_OK;
+    if (!tk_pick_phase(a.ph[TK_LM], (int)lm.rows / 16, (int)E / 64, 1, grid, 1)) return ADAMAH_OK;
+    a.s_max = grid / (int)d.n_head;
+    if (a.s_max > TK_MAX_SPLITS) a.s_max = TK_MAX_SPLITS;
+    a.n_layer = (int)d.n_layer; a.E = (int)E; a.q_dim = (int)q_dim; a.k_dim = (int)k_dim; a.FF = (int)FF; a.V = (int)lm.rows;
+    a.H = (int)d.n_head; a.KV = (int)d.n_head_kv;
+    a.embd = D->embd.w; a.embd_wt = D->embd.wtype; a.emb_scale = d.emb_scale;
+    a.lm_tiled = lm.tiled; a.out_norm = D->output_norm;
+    a.eps = d.norm_eps; a.attn_scale = d.attn_scale; a.attn_cap = d.attn_softcap; a.final_cap = d.final_softcap; a.act = (int)d.ffn_act;
+    a.pos = D->pos; a.cur_tok = D->cur_tok; a.cur_val = D->cur_val; a.prompt_len = D->prompt_len; a.prompt_tok = D->prompt_tok;
+    a.gen_log = D->gen_log; a.log_ld = d.kv_cap;
+    a.block_table = D->block_table;
+    a.geo = KvGeom{d.n_layer, d.n_head_kv, d.head_dim, d.page_size, D->max_pages_per_seq, D->page_elems};
+    a.kv_pool = D->kv_pool;
+    for (int w = 0; w < 2; ++w) { a.cos_t[w] = D->rope_cos[w]; a.sin_t[w] = D->rope_sin[w]; }
+    a.n_pos = D->rope_pos[0] < D->rope_pos[1] ? D->rope_pos[0] : D->rope_pos[1];
+    a.h_out = D->hbuf[0];
+    a.err = g.dev_err;
+    if (token_smem_bytes(wt, a, (int)d.head_dim) > 220 * 1024) return ADAMAH_OK;
+    // device memory: layer table, exchange buffers (two halves each), step counter and the sticky word
+    std::vector<TkLayer> hl(d.n_layer);
+    for (uint32_t L = 0; L < d.n_layer; ++L) {
+        const Layer& ly = D->layers[L];
+        TkLayer& t = hl[L];
+        t.w[0] = ly.qkv_tiled; t.w[1] = ly.m[MAT_O].tiled; t.w[2] = ly.m[MAT_GATE].tiled; t.w[3] = ly.m[MAT_UP].tiled; t.w[4] = ly.m[MAT_DOWN].tiled;
+        t.norm[TKN_ATTN] = ly.norm[NORM_ATTN]; t.norm[TKN_POST_ATTN] = ly.norm[NORM_POST_ATTN]; t.norm[TKN_FFN] = ly.norm[NORM_FFN];
+        t.norm[TKN_POST_FFW] = ly.norm[NORM_POST_FFW]; t.norm[TKN_Q] = ly.norm[NORM_Q]; t.norm[TKN_K] = ly.norm[NORM_K];
+        t.window = ((d.flags & 1u) && d.sliding_window > 0 && !is_global_layer(d, L)) ? d.sliding_window : 0;
+        t.rope = is_global_layer(d, L) ? 1u : 0u;
+    }
+    const size_t sizes[9] = {
+        hl.size() * sizeof(TkLayer),
+        2 * (size_t)(q_dim + 2 * k_dim) * 8,
+        2 * (size_t)d.n_head * a.s_max * (d.head_dim + 2) * 8,
+        2 * (size_t)a.ph[TK_O].cpr * E * 8,
+        2 * (size_t)FF * 8,
+        2 * (size_t)a.ph[TK_DOWN].cpr * E * 8,
+        2 * (size_t)grid * 8,
+        4, 4};
+    for (int i = 0; i < 9; ++i) {
+        if (cudaMalloc(&D->tk_mem[i], sizes[i]) != cudaSuccess) {
+            cudaGetLastError();
+            for (void*& m : D->tk_mem) { if (m) cudaFree(m); m = nullptr; }
+            return fail(ADAMAH_ERR_MEMORY, "decoder: out of device memory for the token kernel's buffers");
+        }
+        cudaMemsetAsync(D->tk_mem[i], 0, sizes[i], g.stream);
+    }
+    cudaMemcpyAsync(D->tk_mem[0], hl.data(), sizes[0], cudaMemcpyHostToDevice, g.stream);
+    cudaStreamSynchronize(g.stream);
+    a.layers = (const TkLayer*)D->tk_mem[0];
+    a.x_qkv = (uint2*)D->tk_mem[1]; a.x_att = (uint2*)D->tk_mem[2]; a.x_po = (uint2*)D->tk_mem[3]; a.x_act = (uint2*)D->tk_mem[4];
+    a.x_pd = (uint2*)D->tk_mem[5]; a.x_amax = (uint2*)D->tk_mem[6]; a.seq = (uint32_t*)D->tk_mem[7]; a.dead = (uint32_t*)D->tk_mem[8];
+    D->tk = a; D->tk_grid = grid; D->tk_wt = wt;
+    D->tk_state = 1;
+    return ADAMAH_OK;
+}
+
+// One token of the single active sequence as one launch.
+static int enqueue_token(Decoder* D, bool with_lm, bool want_logits) {
+    TkArgs a = D->tk;
+    a.with_lm = with_lm ? 1 : 0;
+    a.logits = want_logits ? D->logits : nullptr;
+    const int rc = launch_token(D->tk_wt, D->d.kv_dtype == 1, (int)D->d.head_dim, a, D->tk_grid, g.stream);
+    if (rc == ADAMAH_OK && with_lm) D->h_final = 0;
+    return rc;
+}
+
 }  // namespace ab
 
 using namespace ab;
@@ -1091,6 +1147,7 @@ extern "C" int adam_b200_decoder_begin(uint32_t id, uint32_t batch, const int32_
     DCU(cudaMemsetAsync(D->pos, 0, (size_t)d.max_batch * 4, g.stream));
     DCU(cudaMemsetAsync(D->cur_tok, 0, (size_t)d.max_batch * 4, g.stream));
     DCU(cudaMemsetAsync(D->gen_log, 0xFF, (size_t)d.max_batch * d.kv_cap * 4, g.stream));
+    if (D->tk_state == 1) DCU(cudaMemsetAsync(D->tk_mem[8], 0, 4, g.stream));
     DCU(cudaStreamSynchronize(g.stream));
     D->batch = batch;
     D->hpos.assign(batch, 0);
@@ -1134,6 +1191,7 @@ extern "C" int adam_b200_decoder_continue(uint32_t id, const int32_t* prompt_tok
     DCU(cudaMemcpyAsync(D->pos, &p0, 4, cudaMemcpyHostToDevice, g.stream));
     DCU(cudaMemsetAsync(D->cur_tok, 0, 4, g.stream));
     DCU(cudaMemsetAsync(D->gen_log, 0xFF, (size_t)d.kv_cap * 4, g.stream));
+    if (D->tk_state == 1) DCU(cudaMemsetAsync(D->tk_mem[8], 0, 4, g.stream));
     DCU(cudaStreamSynchronize(g.stream));
     D->hpos[0] = n_reuse;
     D->hplen[0] = prompt_len;
@@ -1143,13 +1201,15 @@ extern "C" int adam_b200_decoder_continue(uint32_t id, const int32_t* prompt_tok
 
 // Run `n_steps` token steps.  flags bit0: run the LM head + arg-max (the sampled
 // id feeds the next step once the prompt is consumed); bit1: also store the
-// soft-capped logits; bit2: launch kernels directly instead of replaying a graph.
+// soft-capped logits; bit2: launch kernels directly instead of replaying a graph;
+// bit3: use the chain of per-operation kernels even where the single-launch token
+// kernel (one sequence, row-tiled weights) would run.
 // Returns without waiting unless called outside batch_begin/batch_end.
 extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t flags) {
     Decoder* D = get_dec(id);
     if (!D) return ADAMAH_ERR_NOT_FOUND;
     if (D->batch == 0) return fail(ADAMAH_ERR_INVALID, "decoder_step: call decoder_begin first");
-    const bool with_lm = flags & 1u, want_logits = (flags & 2u) != 0, direct = (flags & 4u) != 0;
+    const bool with_lm = flags & 1u, want_logits = (flags & 2u) != 0, direct = (flags & 4u) != 0, chain = (flags & 8u) != 0;
     if (want_logits && !with_lm) return fail(ADAMAH_ERR_INVALID, "decoder_step: logits need the LM head flag");
     int rc = ADAMAH_OK;
     // a step past the reserved pages would only set a device error bit and return ids that look valid
@@ -1157,6 +1217,12 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
         if ((uint64_t)D->hpos[b] + n_steps > D->hres[b])
             return fail(ADAMAH_ERR_INVALID, "decoder_step: sequence %u is at position %u of %u reserved, cannot take %u more steps", b, D->hpos[b], D->hres[b], n_steps);
     for (uint32_t& hp : D->hpos) hp += n_steps;
+    if (D->batch == 1 && !chain && D->tk_state == 0 && !capturing()) { if ((rc = prepare_token_kernel(D))) return rc; }
+    if (D->batch == 1 && !chain && D->tk_state == 1 && !capturing()) {
+        for (uint32_t s = 0; s < n_steps && rc == ADAMAH_OK; ++s) rc = enqueue_token(D, with_lm, want_logits);
+        end_of_op();
+        return rc;
+    }
     if (direct || want_logits || capturing()) {
         for (uint32_t s = 0; s < n_steps && rc == ADAMAH_OK; ++s) rc = enqueue_step(D, D->batch, with_lm, want_logits);
     } else {

@@ -35,7 +35,7 @@ _MAT_KIND = {"attn_q": 0, "attn_k": 1, "attn_v": 2, "attn_output": 3, "ffn_gate"
 _NORM_KIND = {"attn_norm": 0, "post_attention_norm": 1, "ffn_norm": 2, "post_ffw_norm": 3, "attn_q_norm": 4, "attn_k_norm": 5}
 _KIND_EMBD, _KIND_OUTPUT, _KIND_OUTPUT_NORM = 7, 8, 6
 
-STEP_LM, STEP_LOGITS, STEP_DIRECT = 1, 2, 4
+STEP_LM, STEP_LOGITS, STEP_DIRECT, STEP_CHAIN = 1, 2, 4, 8
 
 
 def rope_tables(n_pos: int, head_dim: int, freq_base: float):
@@ -170,8 +170,9 @@ class ADAMEngine:
         self._batch = len(prompts)
         self._h2d_bytes = flat.nbytes + lens.nbytes + res.nbytes
 
-    def step(self, n_steps: int = 1, lm_head: bool = True, logits: bool = False, direct: bool = False):
-        flags = (STEP_LM if lm_head else 0) | (STEP_LOGITS if logits else 0) | (STEP_DIRECT if direct else 0)
+    def step(self, n_steps: int = 1, lm_head: bool = True, logits: bool = False, direct: bool = False, chain: bool = False):
+        """``chain=True`` forces the chain of per-operation kernels where the single-launch token kernel would run."""
+        flags = (STEP_LM if lm_head else 0) | (STEP_LOGITS if logits else 0) | (STEP_DIRECT if direct else 0) | (STEP_CHAIN if chain else 0)
         self._check(self._lib.adam_b200_decoder_step(self._dec, n_steps, flags), "adam_b200_decoder_step")
 
     def prefill(self, n_tokens: int):

@@ -266,16 +266,25 @@ def test_graph_replay_equals_direct_launches(gpu):
     eng = ADAMEngine(gpu, cfg, tensors, kv_cap=32)
     try:
         eng.begin([prompt], [30])
-        eng.step(5, lm_head=False, direct=True)
-        eng.step(10, lm_head=True, direct=True)
+        eng.step(5, lm_head=False, direct=True, chain=True)
+        eng.step(10, lm_head=True, direct=True, chain=True)
         a = eng.read_log(0, 6, 10)
+        eng.begin([prompt], [30])
+        gpu.reset_native_stats()
+        eng.step(5, lm_head=False, chain=True)
+        eng.step(10, lm_head=True, chain=True)
+        b = eng.read_log(0, 6, 10)
+        assert np.array_equal(a, b) and (a >= 0).all()
+        assert gpu.get_native_stats()["dispatch_count"] >= 15 * 5 * cfg.n_layer     # graph nodes are counted (5 kernels per layer)
+        # the single-launch token kernel: one launch per token, same ids
         eng.begin([prompt], [30])
         gpu.reset_native_stats()
         eng.step(5, lm_head=False)
         eng.step(10, lm_head=True)
-        b = eng.read_log(0, 6, 10)
-        assert np.array_equal(a, b) and (a >= 0).all()
-        assert gpu.get_native_stats()["dispatch_count"] >= 15 * 5 * cfg.n_layer     # graph nodes are counted (5 kernels per layer)
+        c = eng.read_log(0, 6, 10)
+        assert np.array_equal(a, c)
+        assert gpu.get_native_stats()["dispatch_count"] == 15
+        assert gpu.device_error() == 0
     finally:
         eng.close()
 
