@@ -132,6 +132,7 @@ _SIGS = {
     "adam_b200_decoder_read_log": (c_int, [u32, u32, u32, u32, c_void_p]),
     "adam_b200_decoder_read_logits": (c_int, [u32, u32, c_void_p]),
     "adam_b200_decoder_read_buffer": (c_int, [u32, u32, u32, c_void_p, u32]),
+    "adam_b200_decoder_token_trace": (c_int, [u32, u32, c_void_p, c_void_p]),
     "map_upload_gguf_blocks": (c_int, [u32, u32, u64, c_void_p, u64]),
     "map_dequant_gguf": (c_int, [u32, u64, c_void_p, u64]),
     "adam_b200_tensor_tile": (c_int, [u32, u64, u32, u32]),

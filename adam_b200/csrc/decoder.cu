@@ -64,6 +64,7 @@ struct Decoder {
     cudaGraphExec_t graph[2]; cudaGraph_t graph_src[2]; uint32_t graph_batch[2]; uint64_t graph_kernels[2];
     // single-launch token kernel (token.cuh): 0 = not examined yet, 1 = ready, -1 = this model does not qualify
     int tk_state; TkArgs tk; int tk_grid; int tk_wt; void* tk_mem[9];
+    cudaGraphExec_t tk_graph[2]; cudaGraph_t tk_graph_src[2]; int tk_graph_state[2];   // TK_GRAPH_N token kernels per replay (index = LM head or not); state -1 = capture refused
 };
 
 constexpr uint32_t MAX_DECODERS = 8;
@@ -632,8 +633,13 @@ __global__ void k_fill_i32(int32_t* p, int32_t v, size_t n) {
 
 // ---- host side ---------------------------------------------------------------
 
+constexpr uint32_t TK_GRAPH_N = 8;
 static void free_token_kernel(Decoder* D) {
     if (D->tk_state == 1) cudaStreamSynchronize(g.stream);
+    for (int i = 0; i < 2; ++i) {
+        if (D->tk_graph[i]) { cudaGraphExecDestroy(D->tk_graph[i]); cudaGraphDestroy(D->tk_graph_src[i]); D->tk_graph[i] = nullptr; D->tk_graph_src[i] = nullptr; }
+        D->tk_graph_state[i] = 0;
+    }
     for (void*& m : D->tk_mem) { if (m) cudaFree(m); m = nullptr; }
     D->tk_state = 0;
 }
@@ -909,8 +915,20 @@ static int prepare_token_kernel(Decoder* D) {
     if (!tk_pick_phase(a.ph[TK_O], (int)E / 16, (int)q_dim / 64, 1, grid, 1)) return ADAMAH_OK;
     if (!tk_pick_phase(a.ph[TK_DOWN], (int)E / 16, (int)FF / 64, 1, grid, 2)) return ADAMAH_OK;
     if (!tk_pick_phase(a.ph[TK_LM], (int)lm.rows / 16, (int)E / 64, 1, grid, 1)) return ADAMAH_OK;
+    // attention CTAs per query head: what the grid offers, at most 8192 gathered values per o-proj CTA
     a.s_max = grid / (int)d.n_head;
     if (a.s_max > TK_MAX_SPLITS) a.s_max = TK_MAX_SPLITS;
+    if (a.s_max > 4) a.s_max = 4;                         // the o-proj merges up to four splits in one poll
+    {   // per-warp staging regions of the o-proj and down-proj inputs: the widest K slice of a warp
+        int np = 0;
+        for (int ph : {TK_O, TK_DOWN}) {
+            const TkPhase& P = a.ph[ph];
+            const int n = (P.pairs + P.KS * P.cpr - 1) / (P.KS * P.cpr);
+            if (n > np) np = n;
+        }
+        if (np > 8) return ADAMAH_OK;                     // a warp's slice must fit sixteen loads per lane
+        a.wu_cap = 2 * np;
+    }
     a.n_layer = (int)d.n_layer; a.E = (int)E; a.q_dim = (int)q_dim; a.k_dim = (int)k_dim; a.FF = (int)FF; a.V = (int)lm.rows;
     a.H = (int)d.n_head; a.KV = (int)d.n_head_kv;
     a.embd = D->embd.w; a.embd_wt = D->embd.wtype; a.emb_scale = d.emb_scale;
@@ -964,9 +982,13 @@ static int prepare_token_kernel(Decoder* D) {
     return ADAMAH_OK;
 }
 
+static long long* g_tk_trace = nullptr;     // diagnostics buffer (device), see adam_b200_decoder_token_trace
+static int g_tk_trace_layer = 0, g_tk_trace_phase = 2;
+
 // One token of the single active sequence as one launch.
 static int enqueue_token(Decoder* D, bool with_lm, bool want_logits) {
     TkArgs a = D->tk;
+    a.trace = g_tk_trace; a.trace_layer = g_tk_trace_layer; a.trace_phase = g_tk_trace_phase;
     a.with_lm = with_lm ? 1 : 0;
     a.logits = want_logits ? D->logits : nullptr;
     const int rc = launch_token(D->tk_wt, D->d.kv_dtype == 1, (int)D->d.head_dim, a, D->tk_grid, g.stream);
@@ -1219,7 +1241,30 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
     for (uint32_t& hp : D->hpos) hp += n_steps;
     if (D->batch == 1 && !chain && D->tk_state == 0 && !capturing()) { if ((rc = prepare_token_kernel(D))) return rc; }
     if (D->batch == 1 && !chain && D->tk_state == 1 && !capturing()) {
-        for (uint32_t s = 0; s < n_steps && rc == ADAMAH_OK; ++s) rc = enqueue_token(D, with_lm, want_logits);
+        uint32_t s = 0;
+        // Several steps at once replay a graph of TK_GRAPH_N launches: a cooperative launch costs the host
+        // more than the kernel's start-up on the device, and back-to-back graph nodes close that gap.
+        static const bool use_graph = !(getenv("ADAM_B200_TOKEN_GRAPH") && atoi(getenv("ADAM_B200_TOKEN_GRAPH")) == 0);
+        const int gi = with_lm ? 1 : 0;
+        if (use_graph && !want_logits && !direct && n_steps >= TK_GRAPH_N && D->tk_graph_state[gi] >= 0) {
+            if (!D->tk_graph[gi]) {
+                const uint64_t l0 = g.launches;
+                DCU(cudaStreamSynchronize(g.stream));
+                cudaGraph_t graph = nullptr;
+                bool ok = cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeRelaxed) == cudaSuccess;
+                for (uint32_t k = 0; ok && k < TK_GRAPH_N; ++k) ok = enqueue_token(D, with_lm, false) == ADAMAH_OK;
+                if (cudaStreamEndCapture(g.stream, &graph) != cudaSuccess) ok = false;
+                if (ok && cudaGraphInstantiate(&D->tk_graph[gi], graph, 0) != cudaSuccess) ok = false;
+                g.launches = l0;
+                if (ok) { D->tk_graph_src[gi] = graph; D->tk_graph_state[gi] = 1; }
+                else { cudaGetLastError(); if (graph) cudaGraphDestroy(graph); D->tk_graph[gi] = nullptr; D->tk_graph_state[gi] = -1; }
+            }
+            if (D->tk_graph[gi]) {
+                for (; s + TK_GRAPH_N <= n_steps; s += TK_GRAPH_N) DCU(cudaGraphLaunch(D->tk_graph[gi], g.stream));
+                count_launch(s);
+            }
+        }
+        for (; s < n_steps && rc == ADAMAH_OK; ++s) rc = enqueue_token(D, with_lm, want_logits);
         end_of_op();
         return rc;
     }
@@ -1461,6 +1506,31 @@ extern "C" int adam_b200_decoder_step_part(uint32_t id, uint32_t part, uint32_t 
     end_of_op();
     return rc;
 }
+// Diagnostics of the single-launch token kernel: run ONE token step (LM head included) of the active
+// sequence with per-phase SM clock stamps of layer `layer` and of the LM head recorded by every CTA, and
+// return them: out[cta * 16 + slot] (clock64 values of that CTA's SM; slots 0..9 = layer phases, 10..13 = LM
+// head), n_cta_out = CTAs launched.  out must hold 16 * 256 values.
+extern "C" int adam_b200_decoder_token_trace(uint32_t id, uint32_t layer, long long* out, uint32_t* n_cta_out) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (!out || !n_cta_out || D->batch != 1) return fail(ADAMAH_ERR_INVALID, "decoder_token_trace: needs one active sequence");
+    if (D->tk_state == 0) { const int rc0 = prepare_token_kernel(D); if (rc0) return rc0; }
+    if (D->tk_state != 1) return fail(ADAMAH_ERR_INVALID, "decoder_token_trace: this model does not run on the token kernel");
+    if (D->hpos[0] + 1u > D->hres[0]) return fail(ADAMAH_ERR_INVALID, "decoder_token_trace: no reserved position left");
+    const size_t bytes = (size_t)TK_TRACE_SLOTS * 256 * sizeof(long long);
+    DCU(cudaMalloc((void**)&g_tk_trace, bytes));
+    DCU(cudaMemsetAsync(g_tk_trace, 0, bytes, g.stream));
+    g_tk_trace_layer = (int)(layer & 0xFFFFu); g_tk_trace_phase = (int)(layer >> 16);
+    D->hpos[0] += 1;
+    const int rc = enqueue_token(D, true, false);
+    cudaMemcpyAsync(out, g_tk_trace, bytes, cudaMemcpyDeviceToHost, g.stream);
+    cudaStreamSynchronize(g.stream);
+    cudaFree(g_tk_trace);
+    g_tk_trace = nullptr;
+    *n_cta_out = (uint32_t)D->tk_grid;
+    return rc;
+}
+
 // Device address and size of one of the decoder's buffers, for callers that run their own
 // kernels or collectives on them (same stream, see adam_b200_set_stream):
 //   0 = projection output [rows][n_embd] f32 (what a tensor-parallel caller all-reduces; rows =

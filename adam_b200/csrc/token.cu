@@ -10,17 +10,9 @@ int launch_token_q4k_f32(int hd, const TkArgs& a, int grid, size_t smem, cudaStr
 
 bool token_supported_hd(int hd) { return hd == 32 || hd == 64 || hd == 128 || hd == 256; }
 
-static int units_max_of(const TkArgs& a) {
-    int u = a.E / 32;
-    if (a.q_dim / 32 > u) u = a.q_dim / 32;
-    const TkPhase& P = a.ph[TK_DOWN];
-    const int pu = ((P.pairs + P.cpr - 1) / P.cpr + 1) * 2;
-    return pu > u ? pu : u;
-}
-
 size_t token_smem_bytes(int wt, const TkArgs& a, int hd) {
     const int ring = wt == WT_Q4_0 ? TkGeo<WT_Q4_0>::RING_BYTES : TkGeo<WT_Q4_K>::RING_BYTES;
-    return tk_smem_layout(units_max_of(a), hd, a.H, a.s_max, a.E, a.n_layer, ring).total;
+    return tk_smem_layout(a.E / 32, hd, a.wu_cap, a.E, a.n_layer, ring).total;
 }
 
 int launch_token(int wt, bool kv_half, int hd, const TkArgs& a, int grid, cudaStream_t st) {

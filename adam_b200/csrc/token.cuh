@@ -134,7 +134,8 @@ struct TkArgs {
     const TkLayer* layers; int n_layer;
     int E, q_dim, k_dim, FF, V, H, KV;
     TkPhase ph[TK_PHASES];
-    int s_max;                    // attention splits per head (<= TK_MAX_SPLITS, H * s_max <= grid)
+    int s_max;                    // attention splits per head (<= 4, H * s_max <= grid)
+    int wu_cap;                   // units (32 values) of the per-warp staging regions of the o-proj / down-proj inputs
     WeightRef embd; int embd_wt; float emb_scale;
     const uint8_t* lm_tiled; const float* out_norm;
     float eps, attn_scale, attn_cap, final_cap; int act;      // act: 0 = GeGLU, 1 = SwiGLU
@@ -151,7 +152,11 @@ struct TkArgs {
     float* h_out;                 // [E] hidden state after the last layer (verification reads)
     uint32_t* err;
     int with_lm;
+    // diagnostics: when set, thread 0 of every CTA stores its SM clock at TK_TRACE_SLOTS points of one layer
+    // (trace_layer) and of the LM head: trace[cta * TK_TRACE_SLOTS + slot]
+    long long* trace; int trace_layer; int trace_phase;
 };
+constexpr int TK_TRACE_SLOTS = 32;
 
 // Exchange buffer sizes in packets (one half).
 inline size_t tk_att_packets(const TkArgs& a, int hd) { return (size_t)a.H * a.s_max * (hd + 2); }

@@ -202,6 +202,15 @@ class ADAMEngine:
         self._check(self._lib.adam_b200_decoder_read_buffer(self._dec, what, seq, out.ctypes.data, n), "adam_b200_decoder_read_buffer")
         return out
 
+    def token_trace(self, layer: int = 1, phase: int = 2) -> np.ndarray:
+        """One token step on the single-launch token kernel with per-phase SM clock stamps: ``[n_cta, 32]``
+        (slots 0..9 = phases of ``layer``, 10..13 = LM head, 16..22 = inside product ``phase`` of that layer;
+        diagnostics)."""
+        out = np.zeros((256, 32), np.int64)
+        n = ctypes.c_uint32(0)
+        self._check(self._lib.adam_b200_decoder_token_trace(self._dec, int(layer) | (int(phase) << 16), out.ctypes.data, ctypes.byref(n)), "adam_b200_decoder_token_trace")
+        return out[:int(n.value)]
+
     def logits_trace(self, tokens: Sequence[int], direct: bool = True) -> np.ndarray:
         """Teacher-forced pass over ``tokens``: the soft-capped logits after every
         position, ``[len(tokens), n_vocab]`` (for parity checks)."""

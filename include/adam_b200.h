@@ -345,6 +345,11 @@ int adam_b200_tc_gemm_policy(int policy);
  * 0 .. 2*n_layer-1 as above (the projection buffer then holds batch * n_tokens rows of partial
  * sums), part 2*n_layer advances the positions by n_tokens. */
 int adam_b200_decoder_prefill_part(uint32_t id, uint32_t n_tokens, uint32_t part);
+/* Diagnostics of the single-launch token kernel (one active sequence; no counterpart in the reference): runs
+ * one token step with the LM head and returns every CTA's SM clock at 32 points: slots 0..9 phases of layer
+ * (layer & 0xFFFF), 10..13 LM head, 16..22 inside product (layer >> 16) of that layer; out[cta * 32 + slot],
+ * out holds 32 * 256 values. */
+int adam_b200_decoder_token_trace(uint32_t id, uint32_t layer, long long* out, uint32_t* n_cta_out);
 /* Device address / size of a decoder buffer: 0 projection output [batch][n_embd] f32,
  * 1 current token ids [max_batch] i32, 2 their logit values [max_batch] f32, 3 positions. */
 int adam_b200_decoder_buffer_ptr(uint32_t id, uint32_t which, uint64_t* ptr_out, uint64_t* bytes_out);
