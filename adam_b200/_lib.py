@@ -128,11 +128,17 @@ _SIGS = {
     "adam_b200_ar_open": (c_int, [u32, c_void_p]),
     "adam_b200_ar_allreduce": (c_int, [u32, u64, u32]),
     "adam_b200_ar_destroy": (c_int, [u32]),
+    "adam_b200_noalloc_prepare": (c_int, []),
+    "adam_b200_ar_set_wait_us": (c_int, [u32, u64]),
+    "adam_b200_ar_reset": (c_int, [u32]),
+    "adam_b200_ar_timed_out": (c_int, [u32]),
+    "adam_b200_ar_open_local": (c_int, [u32, c_void_p, u32]),
     "adam_b200_decoder_read_state": (c_int, [u32, c_void_p, c_void_p]),
     "adam_b200_decoder_read_log": (c_int, [u32, u32, u32, u32, c_void_p]),
     "adam_b200_decoder_read_logits": (c_int, [u32, u32, c_void_p]),
     "adam_b200_decoder_read_buffer": (c_int, [u32, u32, u32, c_void_p, u32]),
     "adam_b200_decoder_token_trace": (c_int, [u32, u32, c_void_p, c_void_p]),
+    "adam_b200_decoder_test_wait_expiry": (c_int, [u32, u32]),
     "map_upload_gguf_blocks": (c_int, [u32, u32, u64, c_void_p, u64]),
     "map_dequant_gguf": (c_int, [u32, u64, c_void_p, u64]),
     "adam_b200_tensor_tile": (c_int, [u32, u64, u32, u32]),

@@ -14,8 +14,9 @@
 //   1. every thread reads its floats of the buffer and stores the packets into region
 //      [p][my rank] of EVERY peer's staging area (posted peer stores);
 //   2. it then polls region [p][q] of its OWN staging area for every peer q until both halves of
-//      the packet carry s (bounded number of polls; on expiry DEVERR_WAIT is recorded, a sticky
-//      word stops later calls from waiting again, and the kernel carries on to its end);
+//      the packet carry s (bounded by the SM clock: a few seconds by default, settable per
+//      communicator; on expiry DEVERR_WAIT is recorded, a sticky word stops later calls from
+//      waiting again until adam_b200_ar_reset clears it, and the kernel carries on to its end);
 //   3. it adds the contributions in rank order (its own from registers) and writes the buffer.
 // Two slots are enough without an exit barrier: a peer overwrites my slot p only in its call
 // s + 2, which it reaches only after my packets of call s + 1 arrived, i.e. after I finished call s.
@@ -26,6 +27,7 @@
 // expected one whatever the sizes of earlier calls were.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace ab {
@@ -33,7 +35,7 @@ namespace ab {
 constexpr uint32_t AR_MAX_RANKS = 8;
 constexpr uint32_t AR_MAX_CTAS = 64;
 constexpr uint32_t AR_MAX_COMMS = 4;
-constexpr int AR_POLL_LIMIT = 1 << 20;      // about a second of polling
+constexpr long long AR_WAIT_CYCLES_DEFAULT = 10LL * 1000 * 1000 * 1000;   // about 5 s at 2 GHz: rank skew on a shared host (graph instantiation, module load, a preempted host thread) can reach a second
 
 struct ArComm {
     bool used, open;
@@ -42,6 +44,8 @@ struct ArComm {
     uint4* stage;                           // [2 slots][world][max_floats / 2] packets in my memory
     uint32_t* state;                        // [AR_MAX_CTAS] call counters, then the sticky "a wait ran out" word
     uint4* peer_stage[AR_MAX_RANKS];        // mapped (my own entry = stage)
+    long long wait_cycles;                  // bound of the wait of one call, in SM clocks
+    bool local_peers;                       // peers are other communicators of this process (test set-up): nothing to unmap
 };
 static ArComm g_ar[AR_MAX_COMMS];
 
@@ -57,7 +61,7 @@ __device__ __forceinline__ uint4 ld_packet(const uint4* p) {
 }
 
 __global__ void __launch_bounds__(256) k_allreduce(float* __restrict__ buf, uint32_t n2, ArPeers peers, uint32_t world, uint32_t rank,
-                                                   size_t region, uint32_t* __restrict__ state, uint32_t* err) {
+                                                   size_t region, uint32_t* __restrict__ state, uint32_t* err, long long wait_cycles) {
     const uint32_t c = blockIdx.x, tid = threadIdx.x;
     uint32_t* counter = state + c;
     uint32_t* dead = state + AR_MAX_CTAS;
@@ -66,7 +70,8 @@ __global__ void __launch_bounds__(256) k_allreduce(float* __restrict__ buf, uint
     uint32_t s = *counter + 1u;
     if (s == 0u) s = 1u;                                    // 0 is what untouched staging memory holds
     const uint32_t p = s & 1u;
-    const bool was_dead = *dead != 0u;
+    bool gave_up = *dead != 0u;                            // an earlier call ran out of time: do not wait again
+    const long long deadline = clock64() + wait_cycles;
     // slice of this CTA, in float2 units
     const uint32_t per = (n2 + gridDim.x - 1) / gridDim.x;
     const uint32_t i0 = min(c * per, n2), i1 = min(i0 + per, n2);
@@ -85,9 +90,9 @@ __global__ void __launch_bounds__(256) k_allreduce(float* __restrict__ buf, uint
             if (q == rank) { acc.x += v.x; acc.y += v.y; continue; }
             const uint4* src = mine + (size_t)q * region + i;
             uint4 pk = ld_packet(src);
-            int polls = was_dead ? AR_POLL_LIMIT : 0;
-            while (pk.y != s || pk.w != s) {
-                if (++polls > AR_POLL_LIMIT) { atomicOr(err, DEVERR_WAIT); *dead = 1u; break; }
+            uint32_t polls = 0;
+            while ((pk.y != s || pk.w != s) && !gave_up) {
+                if ((++polls & 31u) == 0u && clock64() > deadline) { atomicOr(err, DEVERR_WAIT); *dead = 1u; gave_up = true; break; }
                 pk = ld_packet(src);
             }
             acc.x += __uint_as_float(pk.x); acc.y += __uint_as_float(pk.z);
@@ -106,7 +111,7 @@ void ar_destroy_all() {
         ArComm& a = g_ar[i];
         if (!a.used) continue;
         for (uint32_t q = 0; q < a.world; ++q)
-            if (a.open && q != a.rank && a.peer_stage[q]) cudaIpcCloseMemHandle(a.peer_stage[q]);
+            if (a.open && !a.local_peers && q != a.rank && a.peer_stage[q]) cudaIpcCloseMemHandle(a.peer_stage[q]);
         cudaFree(a.stage); cudaFree(a.state);
         memset(&a, 0, sizeof a);
     }
@@ -147,6 +152,8 @@ extern "C" int adam_b200_ar_create(uint32_t world, uint32_t rank, uint64_t max_b
     }
     memcpy(handles_out, h, sizeof h);
     a.used = true; a.world = world; a.rank = rank;
+    a.wait_cycles = AR_WAIT_CYCLES_DEFAULT;
+    if (const char* e = getenv("ADAM_B200_AR_WAIT_US")) { const long long us = atoll(e); if (us > 0) a.wait_cycles = us * 2000; }
     *id_out = id;
     return ADAMAH_OK;
 }
@@ -184,11 +191,58 @@ extern "C" int adam_b200_ar_allreduce(uint32_t id, uint64_t buf, uint32_t n_floa
     if (grid > AR_MAX_CTAS) grid = AR_MAX_CTAS;
     static const bool allow = !(getenv("ADAM_B200_PDL") && atoi(getenv("ADAM_B200_PDL")) == 0);
     launch_k(k_allreduce, dim3(grid), dim3(256), 0, g.stream, allow, (float*)(uintptr_t)buf, n2, p, a->world, a->rank, a->max_floats / 2,
-             a->state, g.dev_err);
+             a->state, g.dev_err, a->wait_cycles);
     count_launch();
     int rc = check_launch("ar_allreduce");
     end_of_op();
     return rc;
+}
+
+// Bound of the wait of one call, in microseconds (about 5 s by default; ADAM_B200_AR_WAIT_US at creation).
+extern "C" int adam_b200_ar_set_wait_us(uint32_t id, uint64_t wait_us) {
+    ArComm* a = get_ar(id);
+    if (!a) return ADAMAH_ERR_NOT_FOUND;
+    if (wait_us == 0 || wait_us > 600ull * 1000 * 1000) return fail(ADAMAH_ERR_INVALID, "ar_set_wait_us: 1 .. 600000000");
+    a->wait_cycles = (long long)wait_us * 2000;
+    return ADAMAH_OK;
+}
+
+// Clears the sticky word a timed-out call leaves behind (calls made while it is set do not wait and so
+// return sums of whatever lies in the staging area).  Every rank resets, then the ranks meet at a host
+// barrier, before the next call; the call counters are left alone (they only ever grow).
+extern "C" int adam_b200_ar_reset(uint32_t id) {
+    ArComm* a = get_ar(id);
+    if (!a) return ADAMAH_ERR_NOT_FOUND;
+    cudaStreamSynchronize(g.stream);
+    if (cudaMemset(a->state + AR_MAX_CTAS, 0, 4) != cudaSuccess) return fail(ADAMAH_ERR_BACKEND, "ar_reset: %s", cudaGetErrorString(cudaGetLastError()));
+    return ADAMAH_OK;
+}
+
+// 1 if a call on this communicator ran out of time since creation / the last reset, else 0.
+extern "C" int adam_b200_ar_timed_out(uint32_t id) {
+    ArComm* a = get_ar(id);
+    if (!a) return ADAMAH_ERR_NOT_FOUND;
+    uint32_t v = 0;
+    cudaStreamSynchronize(g.stream);
+    if (cudaMemcpy(&v, a->state + AR_MAX_CTAS, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return fail(ADAMAH_ERR_BACKEND, "ar_timed_out: %s", cudaGetErrorString(cudaGetLastError()));
+    return v ? 1 : 0;
+}
+
+// Test set-up: connects communicators created in THIS process on this GPU (ids[q] = the communicator that
+// plays rank q) by plain pointers instead of IPC handles, which a process cannot open on its own memory.
+// Lets one process call one "rank" while nobody plays the others, so that a bounded wait can be seen to
+// run out and return.
+extern "C" int adam_b200_ar_open_local(uint32_t id, const uint32_t* ids, uint32_t n) {
+    ArComm* a = get_ar(id);
+    if (!a) return ADAMAH_ERR_NOT_FOUND;
+    if (!ids || n != a->world || a->open) return fail(ADAMAH_ERR_INVALID, "ar_open_local: bad arguments or already open");
+    for (uint32_t q = 0; q < n; ++q) {
+        ArComm* b = get_ar(ids[q]);
+        if (!b || b->world != a->world || b->rank != q || b->max_floats != a->max_floats) return fail(ADAMAH_ERR_INVALID, "ar_open_local: communicator %u does not play rank %u", ids[q], q);
+        a->peer_stage[q] = b->stage;
+    }
+    a->open = true; a->local_peers = true;
+    return ADAMAH_OK;
 }
 
 extern "C" int adam_b200_ar_destroy(uint32_t id) {
@@ -196,7 +250,7 @@ extern "C" int adam_b200_ar_destroy(uint32_t id) {
     if (!a) return ADAMAH_ERR_NOT_FOUND;
     cudaStreamSynchronize(g.stream);
     for (uint32_t q = 0; q < a->world; ++q)
-        if (a->open && q != a->rank) cudaIpcCloseMemHandle(a->peer_stage[q]);
+        if (a->open && !a->local_peers && q != a->rank) cudaIpcCloseMemHandle(a->peer_stage[q]);
     cudaFree(a->stage); cudaFree(a->state);
     memset(a, 0, sizeof *a);
     return ADAMAH_OK;

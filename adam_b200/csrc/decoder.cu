@@ -1531,6 +1531,26 @@ extern "C" int adam_b200_decoder_token_trace(uint32_t id, uint32_t layer, long l
     return rc;
 }
 
+// Exercises the bounded waits of the single-launch token kernel without any fault: ONE token step is launched
+// with its last CTA left out and every wait limited to `wait_us` microseconds.  The packets that CTA would have
+// produced never arrive, so the waits of the others run out; they record DEVERR_WAIT in the device error word,
+// set the decoder's sticky word and return.  Later steps return at once until decoder_begin / decoder_continue
+// clears the word.  Returns after the launch has finished.
+extern "C" int adam_b200_decoder_test_wait_expiry(uint32_t id, uint32_t wait_us) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (D->batch != 1) return fail(ADAMAH_ERR_INVALID, "decoder_test_wait_expiry: needs one active sequence");
+    if (D->tk_state == 0) { const int rc0 = prepare_token_kernel(D); if (rc0) return rc0; }
+    if (D->tk_state != 1 || D->tk_grid < 2) return fail(ADAMAH_ERR_INVALID, "decoder_test_wait_expiry: this model does not run on the token kernel");
+    if (wait_us == 0 || wait_us > 1000000u) return fail(ADAMAH_ERR_INVALID, "decoder_test_wait_expiry: wait_us must be 1 .. 1000000");
+    TkArgs a = D->tk;
+    a.with_lm = 1; a.logits = nullptr; a.trace = nullptr;
+    a.wait_cycles = (long long)wait_us * 2000;              // SM clocks at about 2 GHz
+    const int rc = launch_token(D->tk_wt, D->d.kv_dtype == 1, (int)D->d.head_dim, a, D->tk_grid - 1, g.stream);
+    DCU(cudaStreamSynchronize(g.stream));
+    return rc;
+}
+
 // Device address and size of one of the decoder's buffers, for callers that run their own
 // kernels or collectives on them (same stream, see adam_b200_set_stream):
 //   0 = projection output [rows][n_embd] f32 (what a tensor-parallel caller all-reduces; rows =

@@ -10,8 +10,10 @@
 // scratch in a fixed array that is part of the library image instead.
 //
 // The price.  The array below occupies NOALLOC_SCRATCH_BYTES (about 32 KB) of device
-// memory on every GPU that loads the library, from load until the process exits, used
-// or not.  Its size fixes the largest problem: one (value, index) slot per group of
+// memory on every GPU on which the library has been initialised, from that moment (the
+// CUDA runtime loads the module that holds it when it is first touched, which
+// adamah_init does through adam_b200_noalloc_prepare) until the process exits, used or
+// not.  Its size fixes the largest problem: one (value, index) slot per group of
 // `rows_per_group` rows, at most NOALLOC_MAX_GROUPS slots, so N may not exceed
 // NOALLOC_MAX_GROUPS * rows_per_group (1,048,576 rows at the default 256).  Larger N is
 // refused with ADAMAH_ERR_INVALID and a message; it is never silently truncated.
@@ -23,10 +25,14 @@
 // (different streams, or one call per thread) would race on the array: issue them from
 // one thread, as every other entry point of this library already requires.
 //
-// First call on a device.  Host code cannot use the array's name as an address -- in
-// host code it is only a stand-in symbol -- so the first call on each device asks the
-// runtime for the real device address (cudaGetSymbolAddress, with that device current)
-// and remembers it.  Make that first call before starting any stream capture.
+// Set-up.  Host code cannot use the array's name as an address -- in host code it is only
+// a stand-in symbol -- so once per device the runtime is asked for the real device address
+// (cudaGetSymbolAddress, with that device current; the caller's current device is put back)
+// and the answer is kept.  adamah_init / adamah_init_ex do this (adam_b200_noalloc_prepare),
+// so that no call on the hot path is the first touch of the module: that first touch may
+// itself load the module and synchronise, which is exactly what these callers want to avoid.
+// A process that skips the initialisation call gets the look-up on the first call of the
+// entry point instead; make that call before starting any stream capture.
 #include "common.cuh"
 #include "gemv.cuh"
 
@@ -52,10 +58,13 @@ static int scratch_for_current_device(NoAllocScratch** out) {
     const int dev = g.device;
     if (dev < 0 || dev >= MAX_DEVICES) return fail(ADAMAH_ERR_INVALID, "no-alloc arg-max: device ordinal %d out of range", dev);
     if (!g_scratch_addr[dev]) {
+        int before = -1;
+        cudaGetDevice(&before);
         cudaError_t e = cudaSetDevice(dev);
         if (e != cudaSuccess) return fail(ADAMAH_ERR_BACKEND, "no-alloc arg-max: cudaSetDevice(%d): %s", dev, cudaGetErrorString(e));
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (before >= 0 && before != dev) cudaSetDevice(before);
         if (e != cudaSuccess || !p) return fail(ADAMAH_ERR_BACKEND, "no-alloc arg-max: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
         g_scratch_addr[dev] = reinterpret_cast<NoAllocScratch*>(p);
     }
@@ -63,9 +72,20 @@ static int scratch_for_current_device(NoAllocScratch** out) {
     return ADAMAH_OK;
 }
 
+// Called by adamah_init_ex: resolves the array on the library's device ahead of any hot-path call.
+int noalloc_prepare() {
+    NoAllocScratch* s = nullptr;
+    return scratch_for_current_device(&s);
+}
+
 }  // namespace ab
 
 using namespace ab;
+
+extern "C" int adam_b200_noalloc_prepare(void) {
+    if (!ready()) return ADAMAH_ERR_INVALID;
+    return noalloc_prepare();
+}
 
 // Same arguments and result as map_matvec_argmax_t_xq4_dev: the index of the largest of
 // the N dot products W[n,:] . x (ties to the lower index) is stored as float32 at
@@ -74,7 +94,8 @@ extern "C" int map_matvec_argmax_t_xq4_static_dev(uint32_t map_act, uint32_t map
                                                   uint32_t idx_tmp_h, uint32_t val_tmp_h, uint32_t dst_h,
                                                   uint32_t K, uint32_t N, uint32_t rows_per_group) {
     if (!ready()) return ADAMAH_ERR_INVALID;
-    (void)idx_tmp_h; (void)val_tmp_h;
+    // the two scratch handles are not used, but both variants reject the same bad arguments
+    if (!handle_ok(idx_tmp_h, 4) || !handle_ok(val_tmp_h, 4)) return ADAMAH_ERR_NOT_FOUND;
     Map* a = get_map(map_act);
     Map* w = get_map(map_wt);
     if (!a || !w) return ADAMAH_ERR_NOT_FOUND;

@@ -210,6 +210,7 @@ using namespace ab;
 
 // ---- context ---------------------------------------------------------------
 
+namespace ab { int noalloc_prepare(); }
 extern "C" int adamah_init_ex(uint64_t, uint64_t) {
     if (g.inited) return ADAMAH_OK;
     int n = 0;
@@ -235,6 +236,10 @@ extern "C" int adamah_init_ex(uint64_t, uint64_t) {
     g.active_dtype = ADAMAH_DTYPE_F32;
     g.sched_mode = 2;
     g.inited = true;
+    {   // resolve the allocation-free arg-max's fixed scratch now, so that no later call is its module's first touch
+        const int rc = noalloc_prepare();
+        if (rc) { g.inited = false; return rc; }
+    }
     return ADAMAH_OK;
 }
 extern "C" int adamah_init(void) { return adamah_init_ex(0, 0); }

@@ -155,6 +155,7 @@ struct TkArgs {
     // diagnostics: when set, thread 0 of every CTA stores its SM clock at TK_TRACE_SLOTS points of one layer
     // (trace_layer) and of the LM head: trace[cta * TK_TRACE_SLOTS + slot]
     long long* trace; int trace_layer; int trace_phase;
+    long long wait_cycles;        // bound of every device-side wait of one launch, in SM clocks (0 = default, about 0.3 s)
 };
 constexpr int TK_TRACE_SLOTS = 32;
 

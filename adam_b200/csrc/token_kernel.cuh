@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) k_token(const __grid_constant__
     unsigned char* ring = smem_raw + lay.ring + (size_t)warp * G::RING_BYTES;
 
     TkWait wt;
-    wt.deadline = clock64() + TK_WAIT_CYCLES;
+    wt.deadline = clock64() + (a.wait_cycles > 0 ? a.wait_cycles : TK_WAIT_CYCLES);
     wt.dead = a.dead;
     wt.failed = false;
     wt.rounds = 0;
@@ -992,7 +992,8 @@ __global__ void __launch_bounds__(TK_THREADS, 1) k_token(const __grid_constant__
         }
     }
     if (bail) {
-        if (tid == 0) { atomicOr(a.err, DEVERR_WAIT); atomicExch(a.dead, 1u); }
+        // the step counter still moves on: packets this step left behind must never match a later step's tags
+        if (tid == 0) { atomicOr(a.err, DEVERR_WAIT); atomicExch(a.dead, 1u); atomicMax(a.seq, seq_no + 1u); }
     }
     // Copies still in flight must land before the CTA's shared memory is released.
     {

@@ -242,13 +242,15 @@ int adam_b200_quantize_q4_0_dev(const float* w_dev, uint64_t n_elems, void* raw_
  * latency-critical section that cannot afford the device-wide synchronisation an
  * allocation implies, a process already at its memory cap).  The partial-result
  * scratch is a fixed array inside the library image: about 32 KB of device memory on
- * every GPU that loads the library, until the process exits.  Limit: N may not exceed
+ * every GPU on which the library is initialised, from adamah_init until the process exits.  Limit: N may not exceed
  * 4096 * rows_per_group rows (rows_per_group 0 -> 256, i.e. 1,048,576 rows); larger N
  * returns ADAMAH_ERR_INVALID.  All calls share that one array and it keeps the last
  * call's contents (the arrival counter is cleared before every launch): calls that
  * overlap on the GPU race, so issue them from one thread on the library's stream.  The
- * first call on a device looks up the array's device address; make that call before
- * starting a stream capture. */
+ * array's device address is looked up once per device by adamah_init (adam_b200_noalloc_prepare);
+ * without that, by the first call of the entry point, which should then come before any
+ * stream capture. */
+int adam_b200_noalloc_prepare(void);
 int map_matvec_argmax_t_xq4_static_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h, uint32_t b_h,
                                        uint32_t idx_tmp_h, uint32_t val_tmp_h, uint32_t dst_h,
                                        uint32_t K, uint32_t N, uint32_t rows_per_group);
@@ -271,6 +273,13 @@ int adam_b200_ar_create(uint32_t world, uint32_t rank, uint64_t max_bytes, uint3
 int adam_b200_ar_open(uint32_t id, const void* all_handles);
 int adam_b200_ar_allreduce(uint32_t id, uint64_t buf, uint32_t n_floats);     /* in place, on the library stream */
 int adam_b200_ar_destroy(uint32_t id);
+/* Bound of one all-reduce call's wait in microseconds (about 5 s by default; env ADAM_B200_AR_WAIT_US). */
+int adam_b200_ar_set_wait_us(uint32_t id, uint64_t wait_us);
+/* Clears the sticky "a wait ran out" word (every rank, followed by a host barrier); _timed_out reads it. */
+int adam_b200_ar_reset(uint32_t id);
+int adam_b200_ar_timed_out(uint32_t id);
+/* Test set-up: connect communicators of this process (ids[q] plays rank q) by pointer instead of IPC. */
+int adam_b200_ar_open_local(uint32_t id, const uint32_t* ids, uint32_t n);
 
 /* ---- fused decoder ------------------------------------------------------------
  * Runs the reference engine's per-token loop (adam/models/engine.py:2971-3706
@@ -350,6 +359,11 @@ int adam_b200_decoder_prefill_part(uint32_t id, uint32_t n_tokens, uint32_t part
  * (layer & 0xFFFF), 10..13 LM head, 16..22 inside product (layer >> 16) of that layer; out[cta * 32 + slot],
  * out holds 32 * 256 values. */
 int adam_b200_decoder_token_trace(uint32_t id, uint32_t layer, long long* out, uint32_t* n_cta_out);
+/* Test hook for the bounded device-side waits (no counterpart in the reference): launches one token step of the
+ * single active sequence on the token kernel with its last CTA left out and every wait limited to wait_us
+ * microseconds; the waits run out, the kernel records error bit 2 (adam_b200_device_error), sets the decoder's
+ * sticky word and returns.  Later steps return at once until decoder_begin / decoder_continue. */
+int adam_b200_decoder_test_wait_expiry(uint32_t id, uint32_t wait_us);
 /* Device address / size of a decoder buffer: 0 projection output [batch][n_embd] f32,
  * 1 current token ids [max_batch] i32, 2 their logit values [max_batch] f32, 3 positions. */
 int adam_b200_decoder_buffer_ptr(uint32_t id, uint32_t which, uint64_t* ptr_out, uint64_t* bytes_out);

@@ -250,6 +250,8 @@ def test_prefix_reuse_continues_from_the_cache(gpu):
         assert st["n_prompt_reused"] == cached and st["n_prompt_prefilled"] == len(turn2) - cached
         want, _ = eng.generate(turn2, GenerationConfig(max_tokens=10, **GREEDY))
         assert got == want
+        oracle_ids, _ = OracleDecoder(cfg, dequant_model(tensors), kv_cap=96).generate(turn2, 10)   # and of the oracle
+        assert got == oracle_ids
         # more reused positions than were ever computed are refused
         eng.generate(p1, GenerationConfig(max_tokens=2, **GREEDY))
         with pytest.raises(RuntimeError, match="are cached"):
@@ -303,5 +305,39 @@ def test_eos_stops_generation_and_kv_cap_is_enforced(gpu):
             eng.generate(prompt, GenerationConfig(max_tokens=27, **GREEDY))
         with pytest.raises(RuntimeError, match="outside the vocabulary"):
             eng.begin([[cfg.n_vocab + 3]], [4])
+    finally:
+        eng.close()
+
+
+def test_bounded_wait_runs_out_and_the_kernel_returns(gpu):
+    """A device-side wait that nothing satisfies: the token kernel is launched once with its last CTA left
+    out and a 20 ms limit.  The kernel must come back by itself, report the expired wait (error bit 2), make
+    later steps return at once, and work again after the next begin()."""
+    import time
+    cfg = _cfg(dict(n_layer=3))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=41, tied=False)
+    prompt = synth.random_prompt(cfg.n_vocab, 6, seed=9)
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=48)
+    try:
+        good, _ = eng.generate(prompt, GenerationConfig(max_tokens=8, **GREEDY))
+        eng.begin([prompt], [40])
+        eng.step(5, lm_head=False)
+        t0 = time.perf_counter()
+        rc = eng._lib.adam_b200_decoder_test_wait_expiry(eng._dec, 20000)
+        dt = time.perf_counter() - t0
+        assert rc == 0
+        assert dt < 2.0, f"the kernel took {dt:.2f} s to give up"
+        assert gpu.device_error() & 2                     # DEVERR_WAIT (the read clears the word)
+        pos_before, _ = eng.read_state()
+        t0 = time.perf_counter()
+        eng.step(3, lm_head=True)                         # sticky word: these launches return at once
+        gpu.sync()
+        assert time.perf_counter() - t0 < 0.5
+        pos_after, _ = eng.read_state()
+        assert pos_after[0] == pos_before[0] == 5         # nothing advanced
+        gpu.device_error()
+        again, _ = eng.generate(prompt, GenerationConfig(max_tokens=8, **GREEDY))    # begin() clears the word
+        assert again == good
+        assert gpu.device_error() == 0
     finally:
         eng.close()

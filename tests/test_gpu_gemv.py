@@ -250,3 +250,27 @@ def test_matvec_argmax_matches_full_logits(gpu, tile):
     assert tok == int(np.argmax(y))
     for h in (a_h, b_h, d_h, t_h):
         gpu.free_handle(h)
+
+
+@pytest.mark.parametrize("tile", [False, True])
+def test_fused_argmax_tie_goes_to_the_lower_index(gpu, tile):
+    """Two identical rows share the largest product: the fused LM head + arg-max must name the lower one
+    (the reference's `better`, map_argmax.comp; its known-answer test is tests/test_decode_primitives.py:17-29)."""
+    rng = np.random.default_rng(21)
+    N, K = 4096, 1152
+    raw = gb.random_q4_0_blocks(rng, N, K)
+    lo, hi = 700, 3001                                  # different 16-row groups, different CTAs
+    raw[hi] = raw[lo]
+    x = (q4_blocks.dequant(raw[lo].reshape(-1), 2, 1, K)[0] * 50.0).astype(np.float32)[None, :]
+    y = _gemv(gpu, 2, raw, N, K, x, tile=tile)[0]
+    assert y[lo] == y[hi] == y.max()
+    a_h, _ = gpu.upload_dev(np.array([0], np.uint32))
+    b_h, _ = gpu.upload_dev(np.array([0], np.uint32))
+    d_h, _ = gpu.upload_dev(np.array([K + 3], np.uint32))
+    t_h, _ = gpu.upload_dev(np.zeros(4, np.uint32))
+    gpu.batch_begin()
+    gpu.map_matvec_argmax_t_xq4_dev(WS, WT, a_h, b_h, t_h, t_h, d_h, K, N, 256)
+    gpu.batch_end()
+    assert int(gpu.gather(WS, np.array([K + 3], np.uint32)).view(np.float32)[0]) == lo
+    for h in (a_h, b_h, d_h, t_h):
+        gpu.free_handle(h)

@@ -198,3 +198,47 @@ def test_two_gloo_ranks_reduce_and_merge_like_the_tp_engine(tmp_path):
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
     assert res["down_err"] < 1e-5
     assert res["tok"] == 3                          # rank 0's row 3, not rank 1's row 3 (global id 259)
+
+
+@pytest.mark.gpu
+def test_peer_allreduce_wait_runs_out_and_returns(gpu):
+    """Two communicator ends in one process stand for two ranks; only rank 0 ever calls.  Its wait for rank 1's
+    packets (memory nobody writes) must run out at the 30 ms limit, return, report error bit 2 and the sticky
+    word; while the word is set calls do not wait; after a reset they wait (and run out) again."""
+    import ctypes
+    import time
+    import torch
+    lib = gpu._lib
+    ids = (ctypes.c_uint32 * 2)()
+    blob = ctypes.create_string_buffer(128)
+    for r in range(2):
+        cid = ctypes.c_uint32(0)
+        assert lib.adam_b200_ar_create(2, r, 4096, ctypes.byref(cid), blob) == 0
+        ids[r] = cid.value
+    try:
+        for r in range(2):
+            assert lib.adam_b200_ar_open_local(ids[r], ids, 2) == 0
+        assert lib.adam_b200_ar_set_wait_us(ids[0], 30000) == 0
+        buf = torch.ones(256, dtype=torch.float32, device=f"cuda:{gpu.device_index}")
+        torch.cuda.synchronize()
+        gpu.device_error()
+        t0 = time.perf_counter()
+        assert lib.adam_b200_ar_allreduce(ids[0], buf.data_ptr(), 256) == 0
+        gpu.sync()
+        dt = time.perf_counter() - t0
+        assert 0.02 < dt < 2.0, dt
+        assert gpu.device_error() & 2
+        assert lib.adam_b200_ar_timed_out(ids[0]) == 1
+        t0 = time.perf_counter()
+        assert lib.adam_b200_ar_allreduce(ids[0], buf.data_ptr(), 256) == 0      # sticky: no second wait
+        gpu.sync()
+        assert time.perf_counter() - t0 < 0.02
+        assert lib.adam_b200_ar_reset(ids[0]) == 0 and lib.adam_b200_ar_timed_out(ids[0]) == 0
+        t0 = time.perf_counter()
+        assert lib.adam_b200_ar_allreduce(ids[0], buf.data_ptr(), 256) == 0
+        gpu.sync()
+        assert time.perf_counter() - t0 > 0.02 and lib.adam_b200_ar_timed_out(ids[0]) == 1
+        gpu.device_error()
+    finally:
+        for r in range(2):
+            lib.adam_b200_ar_destroy(ids[r])

@@ -12,6 +12,7 @@ import pytest
 
 import adam_b200 as A
 from adam_b200 import gguf_blocks as gb
+from oracle import cref
 
 pytestmark = pytest.mark.gpu
 
@@ -42,12 +43,28 @@ def _both(gpu, h, K, N, x, rows_per_group=256):
 
 @pytest.mark.parametrize("ggml_type,N,K", [(2, 40000, 1152), (12, 3000, 512), (2, 37, 64)])
 def test_static_scratch_argmax_equals_regular_entry_point(gpu, ggml_type, N, K):
+    import torch
     rng, h = _setup(gpu, ggml_type, N, K, seed=N)
+    raw = (gb.random_q4_0_blocks if ggml_type == 2 else gb.random_q4_k_blocks)(np.random.default_rng(N), N, K)   # what _setup uploaded
     # two calls in a row: the second one finds the first one's leftovers in the shared array
     for _ in range(2):
         x = rng.standard_normal(K).astype(np.float32)
         ref, got = _both(gpu, h, K, N, x)
         assert got == ref                       # token ids: exact
+        y = cref.gemv_f64(raw, ggml_type, N, K, x)[0]                  # the oracle's product: same winner
+        top = np.sort(y)[-2:]
+        if top[1] - top[0] > 1e-4 * np.abs(y).max():                   # (unless two rows tie within the kernel's tolerance)
+            assert got == int(np.argmax(y))
+    # the call itself must not allocate: free device memory is the same before and after
+    x = rng.standard_normal(K).astype(np.float32)
+    gpu.scatter_contiguous(WS, 0, x)
+    gpu.sync()
+    free0, _ = torch.cuda.mem_get_info(gpu.device_index)
+    gpu.batch_begin()
+    gpu.map_matvec_argmax_t_xq4_static_dev(WS, WT, h["a"], h["b"], h["tmp"], h["tmp"], h["d1"], K, N, 256)
+    gpu.batch_end()
+    free1, _ = torch.cuda.mem_get_info(gpu.device_index)
+    assert free1 == free0
     # small groups: fewer CTAs than the regular launch, same winner
     x = rng.standard_normal(K).astype(np.float32)
     ref, got = _both(gpu, h, K, N, x, rows_per_group=max(16, N // 4000 + 1))
