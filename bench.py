@@ -5,17 +5,29 @@ random prompt, greedy decode): one "step" is one decoded token.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 Prints ONE JSON line.  ``value`` is decode tok/s with everything resident in HBM
-(K graph replays timed with CUDA events on the library's stream); ``e2e`` is the
+(K token steps timed with CUDA events on the library's stream); ``e2e`` is the
 same metric through ``ADAMEngine.generate`` with host prompt ids: generated tokens divided by
 the whole call's time, i.e. the host->device prompt copy, the chunked prefill, every decode step
 and one device->host token read per step are all inside the timed region.
-``roofline`` is the dominant kernel (the dequant GEMV, measured on the LM-head
-shape, 262144 x 1152 Q4_0, whose 170 MB exceed L2) against the measured HBM copy
-bandwidth.  ``cpu_baseline`` is the numpy restatement of the reference's CPU decoder
-timed on this box's host cores on a bounded sample (same weights, same prompt); its greedy ids
-are compared with the GPU arm's (``ids_equal_oracle``).  With N > 1 (torchrun, one
-rank per GPU) every rank runs an independent replica: no collective on the data
-path, weak scaling, value = all ranks' tokens / slowest rank's time.
+``roofline`` is the dominant kernel of the metric's second half (the dequant GEMV, measured on the
+LM-head shape, 262144 x 1152 Q4_0, whose 170 MB exceed L2) against the measured HBM copy
+bandwidth; ``gemv_sweep`` lists the other GEMV shapes of the benchmark configurations (cold HBM:
+each launch of a graph reads a different copy of the weights).  ``cpu_baseline`` is the numpy
+restatement of the reference's CPU decoder timed on this box's host cores on a bounded sample
+(same weights, same prompt); its greedy ids are compared with the GPU arm's
+(``ids_equal_oracle``).  ``tp`` is the Gemma-3-27B-shaped Q4_K model (random blocks, all 62
+layers, batch 1) decoded tensor-parallel over the N GPUs of the run (N = 1: the same part-wise
+path without collectives).  With N > 1 (torchrun, one rank per GPU) ``value`` comes from N
+independent replicas of the 1B model: no collective on that path, weak scaling, value = all
+ranks' tokens / slowest rank's time.
+
+Other modes (one JSON line per result; what the summaries under profiles/ were made with):
+
+    python bench.py --mode gemv [--type 2|12 --n N --k K --batch B] [--no-tile]   GEMV bandwidth, one shape or the sweep
+    python bench.py --mode gemv-once --type 2 --n 262144 --k 1152 --reps 4          a few launches (for ncu)
+    python bench.py --mode batch --batch 32 --prompt 512 --steps 256                batched decode + chunked prefill, 1B shape
+    python bench.py --mode tp [--layers L --batch B --allreduce p2p|nccl --shard-of N]   27B-shape tensor-parallel decode
+    python bench.py --mode token-once [--layers L]                                  a few token-kernel steps (for ncu)
 """
 from __future__ import annotations
 
@@ -35,8 +47,8 @@ sys.path.insert(0, ROOT)
 
 PROMPT_LEN = 128
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one LM-head GEMV launch, from the ncu capture
-# summarised in profiles/gemv_mma_q4_0_lmhead_262144x1152.md (same kernel and shape; that capture's
+# dram__bytes_read.sum + dram__bytes_write.sum of one LM-head GEMV launch, from an ncu capture of
+# `bench.py --mode gemv-once --type 2 --n 262144 --k 1152` (same kernel and shape; that
 # entry point also stores the 1 MB of logits)
 LMHEAD_DRAM_TRAFFIC = 169_949_184 + 4_576_256
 
@@ -154,6 +166,255 @@ def threads_used():
     return os.cpu_count() or 1
 
 
+# ---- GEMV bandwidth (the metric's second half; configs 1 and 4) ------------------------------------------
+
+GEMV_SWEEP = [(2, 6912, 1152, 1), (2, 1152, 6912, 1), (12, 5376, 5376, 1), (12, 21504, 5376, 1), (12, 5376, 21504, 1),
+              (12, 262144, 5376, 1), (12, 5376, 5376, 8), (12, 21504, 5376, 8), (12, 5376, 21504, 8), (12, 262144, 5376, 8)]
+
+
+def _gemv_weights(gpu, A, t, N, K, copies, tile):
+    from adam_b200 import gguf_blocks as gb
+    dt = A.DTYPE_GGUF_Q4_0 if t == 2 else A.DTYPE_GGUF_Q4_K
+    rng = np.random.default_rng(0)
+    ru = min(N, 4096)
+    raw_u = (gb.random_q4_0_blocks if t == 2 else gb.random_q4_k_blocks)(rng, ru, K)
+    raw = np.tile(raw_u, (N // ru + 1, 1))[:N]
+    gpu.map_create_typed(1, dt, 1, copies * N * K)
+    for c in range(copies):
+        gpu.upload_gguf_blocks(1, t, c * N * K, raw)
+        if tile and N % 16 == 0 and K % (64 if t == 2 else 256) == 0:
+            gpu.tile_tensor(1, c * N * K, N, K)
+    return rng
+
+
+def gemv_shape(gpu, A, t, N, K, B=1, target_bytes=600e6, reps=5, tile=True):
+    """Cold-HBM bandwidth of y = W x for one shape: a CUDA graph whose launches walk over enough distinct
+    copies of W to exceed L2, timed with CUDA events on the library stream (best of ``reps``); plus the warm
+    (L2-resident) per-launch latency.  Algorithmic bytes = GGUF block bytes + fp32 x + fp32 y."""
+    wbytes = N * K * 0.5625
+    copies = int(min(160, max(1, np.ceil(target_bytes / wbytes))))
+    rng = _gemv_weights(gpu, A, t, N, K, copies, tile)
+    gpu.map_create_typed(0, A.DTYPE_F32, 1, B * K + B * N + 8)
+    gpu.scatter_contiguous(0, 0, rng.standard_normal(B * K).astype(np.float32))
+    a_h = gpu.upload_dev(np.array([0], np.uint32))[0]
+    c_h = gpu.upload_dev(np.array([B * K], np.uint32))[0]
+    bhs = [gpu.upload_dev(np.array([c * N * K], np.uint32))[0] for c in range(copies)]
+    tc0 = gpu.tc_gemm_count()
+    gpu.map_matmul_t_xq4_dev(0, 1, a_h, bhs[0], c_h, B, K, N)       # eager once: workspaces are allocated outside the capture
+    tc_path = gpu.tc_gemm_count() > tc0
+    gpu.capture_begin()
+    for c in range(copies):
+        gpu.map_matmul_t_xq4_dev(0, 1, a_h, bhs[c], c_h, B, K, N)
+    gid = gpu.capture_end()
+    gpu.graph_launch(gid, 3)
+    best = 1e30
+    for _ in range(reps):
+        gpu.batch_begin(); gpu.timer_begin(); gpu.graph_launch(gid, 1); ms = gpu.timer_end(); gpu.batch_end()
+        best = min(best, ms)
+    alg = wbytes + 4 * K * B + 4 * N * B
+    gbs = alg * copies / (best * 1e-3) / 1e9
+    gpu.capture_begin()
+    for _ in range(20):
+        gpu.map_matmul_t_xq4_dev(0, 1, a_h, bhs[0], c_h, B, K, N)
+    gid2 = gpu.capture_end()
+    gpu.graph_launch(gid2, 2)
+    gpu.batch_begin(); gpu.timer_begin(); gpu.graph_launch(gid2, 1); ms2 = gpu.timer_end(); gpu.batch_end()
+    peak, _ = measured_peaks()
+    out = dict(type="Q4_0" if t == 2 else "Q4_K", kernel="tcgen05 GEMM" if tc_path else ("tensor-core GEMV (tiled)" if tile else "CUDA-core GEMV"),
+               N=N, K=K, B=B, copies=copies, bytes_per_launch=int(alg), us_per_launch=round(best * 1e3 / copies, 3), GBs=round(gbs, 1),
+               frac_of_measured=round(gbs / peak, 3), frac_of_8TBs=round(gbs / 8000, 3), warm_us_per_launch=round(ms2 * 1e3 / 20, 3))
+    gpu.graph_destroy(gid); gpu.graph_destroy(gid2)
+    for h in [a_h, c_h] + bhs:
+        gpu.free_handle(h)
+    gpu.map_destroy(1)
+    return out
+
+
+def gemv_once(gpu, A, t, N, K, B, reps, tile=True):
+    rng = _gemv_weights(gpu, A, t, N, K, 1, tile)
+    gpu.map_create_typed(0, A.DTYPE_F32, 1, B * K + B * N + 8)
+    gpu.scatter_contiguous(0, 0, rng.standard_normal(B * K).astype(np.float32))
+    a_h = gpu.upload_dev(np.array([0], np.uint32))[0]
+    b_h = gpu.upload_dev(np.array([0], np.uint32))[0]
+    c_h = gpu.upload_dev(np.array([B * K], np.uint32))[0]
+    for _ in range(reps):
+        gpu.map_matmul_t_xq4_dev(0, 1, a_h, b_h, c_h, B, K, N)
+    gpu.sync()
+    return gpu.device_error()
+
+
+# ---- batched decode + chunked prefill on the 1B shape (config 3) -------------------------------------------
+
+def batch_decode(args):
+    import adam_b200 as A
+    from adam_b200 import synth
+    from adam_b200.config import gemma3_1b, with_layers
+    from adam_b200.engine import ADAMEngine
+    cfg = gemma3_1b()
+    if args.layers:
+        cfg = with_layers(cfg, args.layers)
+    gpu = A.init()
+    tensors = synth.build_model_cuda(gpu, cfg, seed=0)
+    warmup = max(3, args.warmup)
+    kv_cap = args.prompt + warmup + args.steps + 8
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=kv_cap, max_batch=args.batch, kv_dtype="f16", window=True)
+    prompts = [list(map(int, synth.random_prompt(cfg.n_vocab, args.prompt, seed=10 + b))) for b in range(args.batch)]
+    eng.begin(prompts, [kv_cap] * args.batch)
+    gpu.batch_begin()
+    gpu.timer_begin()
+    if args.token_prefill:
+        eng.step(args.prompt - 1, lm_head=False)
+    else:
+        eng.prefill(args.prompt - 1)
+    pre_ms = gpu.timer_end()
+    eng.step(warmup, lm_head=True)
+    gpu.batch_end()
+    gpu.batch_begin()
+    gpu.timer_begin()
+    eng.step(args.steps, lm_head=True)
+    ms = gpu.timer_end()
+    gpu.batch_end()
+    err = gpu.device_error()
+    launches = gpu.kernel_launches()
+    eng.close()
+    gpu.shutdown()
+    w_bytes = synth.model_weight_elems(cfg) * 18 // 32
+    print(json.dumps({"metric": "decode tok/s (Gemma-3-1B-shape Q4_0, batched)", "value": args.batch * args.steps / (ms * 1e-3), "unit": "tok/s",
+                      "batch": args.batch, "steps": args.steps, "ms_per_step": ms / args.steps, "n_layer": cfg.n_layer, "window": True,
+                      "prefill_tok_s": args.batch * (args.prompt - 1) / (pre_ms * 1e-3),
+                      "prefill": "token by token, all sequences per step" if args.token_prefill else "chunks of (sequence, position) rows per pass",
+                      "weight_bytes_per_step_if_read_once": int(w_bytes), "kernel_launches_total": int(launches), "device_error": int(err),
+                      "data": "synthetic"}))
+
+
+# ---- tensor-parallel decode on the 27B shape (config 5) ----------------------------------------------------
+
+def _random_blocks_cuda(torch, dev, gen, rows, cols, ggml_type):
+    """Seeded random GGUF blocks on the device: uniform quant/scale bytes, fp16 ``d`` (and ``dmin``) set to small
+    positive values so every decoded weight is finite and of the usual magnitude."""
+    from adam_b200 import gguf_blocks as gb
+    from adam_b200.synth import QTensor
+    from adam_b200.tp import block_bytes, block_elems
+    be, bb = block_elems(ggml_type), block_bytes(ggml_type)
+    n = rows * cols // be
+    raw = torch.randint(0, 256, (n, bb), dtype=torch.uint8, device=dev, generator=gen)
+    d = (torch.rand(n, device=dev, generator=gen) * 0.002 + 0.001).to(torch.float16).view(torch.uint8).view(n, 2)
+    raw[:, 0:2] = d
+    if ggml_type == gb.GGML_TYPE_Q4_K:
+        raw[:, 0:2] = (d.view(torch.float16).view(n) / 32).to(torch.float16).view(torch.uint8).view(n, 2)   # d * 6-bit scale
+        raw[:, 2:4] = raw[:, 0:2]
+    return QTensor(ggml_type, rows, cols, raw.reshape(-1))
+
+
+def _build_shard(torch, gpu, cfg, plan, ggml_type, seed):
+    from adam_b200.synth import LAYER_MATS, LAYER_NORMS, QTensor, mat_shapes
+    from adam_b200.tp import block_bytes, block_elems, local_config
+    dev = torch.device("cuda", gpu.device_index)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    rng = np.random.default_rng(seed)
+    lc = local_config(cfg, plan)
+    shapes = mat_shapes(lc)
+    shapes["attn_output"] = (cfg.n_embd, lc.n_head * lc.head_dim)     # K of the row-parallel matrices is local
+    shapes["ffn_down"] = (cfg.n_embd, lc.n_ff)
+    t = {}
+    embd = _random_blocks_cuda(torch, dev, gen, cfg.n_vocab, cfg.n_embd, ggml_type)
+    t["token_embd.weight"] = embd
+    bpr = cfg.n_embd // block_elems(ggml_type) * block_bytes(ggml_type)
+    t["output.weight"] = QTensor(ggml_type, len(plan.vocab), cfg.n_embd,
+                                 embd.raw.view(cfg.n_vocab, bpr)[plan.vocab.start:plan.vocab.stop].contiguous().reshape(-1))
+
+    def norm(n):
+        return (np.float32(1) + np.float32(0.1) * rng.standard_normal(n, dtype=np.float32)).astype(np.float32)
+
+    t["output_norm.weight"] = norm(cfg.n_embd)
+    for L in range(cfg.n_layer):
+        p = f"blk.{L}"
+        for n in LAYER_NORMS:
+            t[f"{p}.{n}.weight"] = norm(cfg.n_embd)
+        t[f"{p}.attn_q_norm.weight"] = norm(cfg.head_dim)
+        t[f"{p}.attn_k_norm.weight"] = norm(cfg.head_dim_kv)
+        for n in LAYER_MATS:
+            t[f"{p}.{n}.weight"] = _random_blocks_cuda(torch, dev, gen, *shapes[n], ggml_type)
+    return t
+
+
+def tp_decode(gpu, rank, world, steps=32, warmup=4, layers=0, batch=1, prompt=16, ggml_type=12, token_prefill=False,
+              use_graph=True, allreduce="p2p", shard_of=0):
+    """Gemma-3-27B-shaped decode, tensor parallel over ``world`` ranks (one per GPU; an initialised NCCL process
+    group when world > 1).  Every rank fills its own shard with seeded random GGUF blocks, consumes a short prompt,
+    then ``steps`` decode steps are timed with CUDA events on the stream the step runs on; time = max over ranks.
+    Returns the result dict on every rank."""
+    import torch
+    import torch.distributed as dist
+    from adam_b200.config import gemma3_27b, with_layers
+    from adam_b200.tp import ADAMEngineTP, block_bytes, block_elems, shard_plan
+    cfg = gemma3_27b()
+    if layers:
+        cfg = with_layers(cfg, layers)
+    tp_world = shard_of if (shard_of and world == 1) else world
+    plan = shard_plan(cfg, rank, tp_world, ggml_type)
+    tensors = _build_shard(torch, gpu, cfg, plan, ggml_type, seed=100 + rank)
+    warmup = max(3, warmup)
+    kv_cap = prompt + warmup + steps + 8
+    eng = ADAMEngineTP(gpu, cfg, tensors, rank, tp_world, presharded=True, use_graph=use_graph, collectives=(tp_world == world),
+                       allreduce=allreduce, kv_cap=kv_cap, max_batch=batch, kv_dtype="f16", window=True)
+    del tensors
+    prompts = [list(map(int, np.random.default_rng(b).integers(0, cfg.n_vocab, prompt))) for b in range(batch)]
+    eng.begin(prompts, [kv_cap] * batch)
+    pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gpu.batch_begin()
+    with torch.cuda.stream(eng._stream):
+        pe0.record()
+    eng.prefill(prompt - 1, chunked=not token_prefill)
+    with torch.cuda.stream(eng._stream):
+        pe1.record()
+    eng.step(warmup, lm_head=True)
+    gpu.batch_end()
+    pe1.synchronize()
+    pre_ms = pe0.elapsed_time(pe1)
+    if world > 1:
+        dist.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gpu.batch_begin()
+    with torch.cuda.stream(eng._stream):
+        ev0.record()
+    eng.step(steps, lm_head=True)
+    with torch.cuda.stream(eng._stream):
+        ev1.record()
+    gpu.batch_end()
+    ev1.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    ids = eng.read_log(0, prompt + warmup, steps)
+    ids_equal = True
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        mine = torch.from_numpy(np.asarray(ids, np.int64)).cuda()
+        allids = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allids, mine)
+        ids_equal = all(bool(torch.equal(allids[0], x)) for x in allids)
+    err = gpu.device_error()
+    lc = eng.cfg
+    w_elems = lc.n_layer * ((lc.n_head + 2 * lc.n_head_kv) * lc.head_dim * cfg.n_embd + cfg.n_embd * lc.n_head * lc.head_dim
+                            + 3 * lc.n_ff * cfg.n_embd) + lc.n_vocab * cfg.n_embd
+    w_bytes = w_elems * block_bytes(ggml_type) // block_elems(ggml_type)
+    graph_used = bool(eng._graphs)
+    ar_used = eng._ar is not None
+    eng.close()
+    ms_tok = ms / steps
+    n_coll = 2 * cfg.n_layer + 2 if world > 1 else 0
+    return {"metric": "decode tok/s (Gemma-3-27B-shape, tensor parallel)", "value": batch * steps / (ms * 1e-3), "unit": "tok/s",
+            "n_gpus": world, "steps": steps, "ms_per_token": ms_tok, "batch": batch, "n_layer": cfg.n_layer,
+            "weights": "Q4_K random blocks" if ggml_type == 12 else "Q4_0 random blocks",
+            "parallelism": f"tp{tp_world}" + ("" if tp_world == world else " (one shard, no collectives)"),
+            "weight_bytes_per_rank_per_token": int(w_bytes), "GBs_per_gpu": w_bytes / (ms_tok * 1e-3) / 1e9,
+            "prefill_tok_s": batch * (prompt - 1) / (pre_ms * 1e-3) if prompt > 1 else None,
+            "collectives_per_token": n_coll, "collective": (("peer-memory one-shot all-reduce (library kernel)" if ar_used else "NCCL all-reduce") + " x %d + arg-max all-gather" % (2 * cfg.n_layer)) if world > 1 else None,
+            "graph": graph_used, "ids_equal_across_ranks": ids_equal, "device_error": int(err)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -162,8 +423,24 @@ def main():
     ap.add_argument("--impl", default="adam_b200", choices=["adam_b200", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model depth (invalid as a benchmark number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the GEMV sweep of the default mode")
+    ap.add_argument("--no-tp", action="store_true", help="skip the 27B-shape tensor-parallel decode of the default mode")
+    ap.add_argument("--mode", default="decode", choices=["decode", "gemv", "gemv-once", "batch", "tp", "token-once"])
+    ap.add_argument("--type", type=int, default=0, help="gemv / tp modes: GGML block type (2 = Q4_0, 12 = Q4_K)")
+    ap.add_argument("--n", type=int, default=0)
+    ap.add_argument("--k", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--prompt", type=int, default=0)
+    ap.add_argument("--reps", type=int, default=4)
+    ap.add_argument("--no-tile", action="store_true", help="gemv modes: CUDA-core kernel over plain GGUF blocks")
+    ap.add_argument("--token-prefill", action="store_true", help="batch / tp modes: consume the prompt one position per step")
+    ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"], help="tp mode: library peer-memory all-reduce or NCCL")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--shard-of", type=int, default=0, help="tp mode, one process: rank 0's shard of an N-way split without collectives")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
+    if args.mode in ("gemv", "gemv-once", "batch", "token-once"):
+        return other_modes(args)
     if args.gpus > 1 and world == 1:
         # not under torchrun: relaunch one rank per GPU on this node
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
@@ -171,6 +448,25 @@ def main():
         sys.exit(subprocess.call(cmd))
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.mode == "tp":
+        import torch
+        torch.cuda.set_device(local_rank)
+        if world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        os.environ.setdefault("ADAM_B200_DEVICE", str(local_rank))
+        import adam_b200 as A
+        gpu = A.init()
+        res = tp_decode(gpu, rank, world, steps=steps, warmup=warmup, layers=args.layers, batch=args.batch or 1, prompt=args.prompt or 16,
+                        ggml_type=args.type or 12, token_prefill=args.token_prefill, use_graph=not args.no_graph, allreduce=args.allreduce,
+                        shard_of=args.shard_of)
+        gpu.shutdown()
+        if rank == 0:
+            print(json.dumps(res))
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     from adam_b200.config import gemma3_1b, with_layers
     cfg = gemma3_1b()
@@ -281,6 +577,21 @@ def main():
     gemv_gbs = gemv_bytes / (best / reps * 1e-3) / 1e9
     step_bytes = synth.model_weight_elems(cfg) * 18 // 32
 
+    # ---- the other GEMV shapes of the benchmark configurations (rank 0 of a single-GPU run) ---------
+    sweep = None
+    if world == 1 and not args.no_sweep and not args.layers:
+        eng.close()
+        sweep = [gemv_shape(gpu, A, *sh, target_bytes=300e6, reps=3) for sh in GEMV_SWEEP]
+        eng = None
+
+    # ---- the 27B shape, tensor parallel over the GPUs of this run --------------------------------------
+    tp = None
+    if not args.no_tp and not args.layers:
+        if eng is not None:
+            eng.close()
+            eng = None
+        tp = tp_decode(gpu, rank, world, steps=min(steps, 32), warmup=3)
+
     # ---- reduce over ranks -------------------------------------------------------------------
     from adam_b200.replicas import combine_timings
     comb = combine_timings(ms, steps, e2e_tps, world, device="cuda")     # a collective when world > 1
@@ -316,14 +627,52 @@ def main():
                          "frac": step_bytes / (ms / steps * 1e-3) / 1e9 / hbm_peak},
             "clocks": clk.summary(), "prefill_tok_s": (PROMPT_LEN - 1) / prefill_s, "build_s": t_build,
         }
+        if sweep is not None:
+            line["gemv_sweep"] = sweep
+        if tp is not None:
+            line["tp"] = tp
         if cpu:
             line["cpu_baseline"] = cpu
-    eng.close()
+    if eng is not None:
+        eng.close()
     gpu.shutdown()
     if world > 1:
         dist.destroy_process_group()
     if line is not None:
         print(json.dumps(line))
+
+
+def other_modes(args):
+    """Single-GPU modes besides the decode benchmark (see the module docstring)."""
+    if args.mode == "batch":
+        args.batch = args.batch or 32
+        args.prompt = args.prompt or 64
+        return batch_decode(args)
+    import adam_b200 as A
+    gpu = A.init()
+    try:
+        if args.mode == "gemv-once":
+            err = gemv_once(gpu, A, args.type or 2, args.n or 262144, args.k or 1152, args.batch or 1, args.reps, not args.no_tile)
+            print(json.dumps({"ok": err == 0}))
+        elif args.mode == "gemv":
+            shapes = [(args.type, args.n, args.k, args.batch or 1)] if args.type and args.n and args.k else GEMV_SWEEP
+            for sh in shapes:
+                print(json.dumps(gemv_shape(gpu, A, *sh, tile=not args.no_tile)), flush=True)
+        else:       # token-once: prompt, then a few single-launch token steps
+            from adam_b200 import synth
+            from adam_b200.config import gemma3_1b, with_layers
+            from adam_b200.engine import ADAMEngine
+            cfg = gemma3_1b()
+            if args.layers:
+                cfg = with_layers(cfg, args.layers)
+            tensors = synth.build_model_cuda(gpu, cfg, seed=0)
+            eng = ADAMEngine(gpu, cfg, tensors, kv_cap=PROMPT_LEN + 64, kv_dtype="f16", window=True)
+            eng.begin([synth.random_prompt(cfg.n_vocab, PROMPT_LEN, seed=1)], [PROMPT_LEN + 60])
+            gpu.batch_begin(); eng.prefill(PROMPT_LEN - 1); eng.step(max(1, min(args.steps, 32)), lm_head=True); gpu.batch_end()
+            print(json.dumps({"ok": gpu.device_error() == 0}))
+            eng.close()
+    finally:
+        gpu.shutdown()
 
 
 if __name__ == "__main__":
