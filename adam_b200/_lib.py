@@ -139,6 +139,9 @@ _SIGS = {
     "adam_b200_decoder_read_buffer": (c_int, [u32, u32, u32, c_void_p, u32]),
     "adam_b200_decoder_token_trace": (c_int, [u32, u32, c_void_p, c_void_p]),
     "adam_b200_decoder_test_wait_expiry": (c_int, [u32, u32]),
+    "adam_b200_decoder_set_sampling": (c_int, [u32, u32, f32, f32, f32, u32, u64]),
+    "map_matvec_topk_t_xq4_ex_dev": (c_int, [u32, u32, u32, u32, u32, u32, u32, u32, u32, u32, u32, f32, u32]),
+    "map_matvec_topk_t_xq4_dev": (c_int, [u32, u32, u32, u32, u32, u32, u32, u32, u32, u32, u32, f32]),
     "map_upload_gguf_blocks": (c_int, [u32, u32, u64, c_void_p, u64]),
     "map_dequant_gguf": (c_int, [u32, u64, c_void_p, u64]),
     "adam_b200_tensor_tile": (c_int, [u32, u64, u32, u32]),

@@ -42,6 +42,8 @@ class Adamah:
         self._has_map_scatter_contiguous = True
         self._has_map_scatter_q4_packed_contiguous = True
         self._has_map_matvec_argmax_t_xq4_dev = True
+        self._has_map_matvec_topk_t_xq4_dev = True
+        self._has_map_matvec_topk_t_xq4_ex_dev = True
         self._has_map_resolve_idx_dev = True
         self._has_map_sample_categorical_dev = True
         self._has_map_repeat_penalty_dev = True
@@ -248,6 +250,19 @@ class Adamah:
 
     def map_resolve_idx_dev(self, map_id, base_locs_handle, locs_sel_handle, locs_dst_handle, n):
         self._check(self._lib.map_resolve_idx_dev(map_id, base_locs_handle, locs_sel_handle, locs_dst_handle, n), "map_resolve_idx_dev")
+
+    def map_matvec_topk_t_xq4_dev(self, map_act_id, map_wt_id, locs_a_handle, locs_b_handle, penalty_ids_handle, locs_idx_dst_handle,
+                                  locs_val_dst_handle, K, N, k, n_penalty, repeat_penalty):
+        """adamah-MAIN/adamah/__init__.py `map_matvec_topk_t_xq4_dev` (adamah.c:9823)."""
+        self._check(self._lib.map_matvec_topk_t_xq4_dev(map_act_id, map_wt_id, locs_a_handle, locs_b_handle, penalty_ids_handle,
+                                                        locs_idx_dst_handle, locs_val_dst_handle, K, N, k, n_penalty, float(repeat_penalty)),
+                    "map_matvec_topk_t_xq4_dev")
+
+    def map_matvec_topk_t_xq4_ex_dev(self, map_act_id, map_wt_id, locs_a_handle, locs_b_handle, penalty_ids_handle, locs_idx_dst_handle,
+                                     locs_val_dst_handle, K, N, k, n_penalty, repeat_penalty, rows_per_group):
+        self._check(self._lib.map_matvec_topk_t_xq4_ex_dev(map_act_id, map_wt_id, locs_a_handle, locs_b_handle, penalty_ids_handle,
+                                                           locs_idx_dst_handle, locs_val_dst_handle, K, N, k, n_penalty, float(repeat_penalty),
+                                                           rows_per_group), "map_matvec_topk_t_xq4_ex_dev")
 
     def map_topk_dev(self, map_id, locs_src_handle, locs_idx_dst_handle, locs_val_dst_handle, n, k):
         self._check(self._lib.map_topk_dev(map_id, locs_src_handle, locs_idx_dst_handle, locs_val_dst_handle, n, k), "map_topk_dev")

@@ -26,6 +26,9 @@ namespace ab {
 
 int weight_ref(const Map* m, uint64_t off, uint64_t n_elems, int* wtype, WeightRef* w);
 int argmax_scratch(float** pv, int** pi, unsigned int** tk);
+int launch_sample(const float* logits, uint32_t V, uint32_t batch, uint32_t k, float temperature, float top_p, float penalty, int on_prompt,
+                  uint64_t seed, const int32_t* pos, const int32_t* prompt_len, const int32_t* prompt_tok, int32_t* gen_log, uint32_t ld,
+                  int32_t* cur_tok, float* cur_val);
 bool capturing();
 
 enum { MAT_Q = 0, MAT_K, MAT_V, MAT_O, MAT_GATE, MAT_UP, MAT_DOWN, MAT_EMBD, MAT_OUTPUT, MAT_KINDS };
@@ -60,6 +63,8 @@ struct Decoder {
     int32_t* tok_ring[4]; cudaEvent_t tok_event[4]; uint32_t tok_next;   // pinned slots for asynchronous token reads
     uint32_t batch;             // active sequences
     bool use_tiles;             // build row-tiled weight copies for the tensor-core GEMV
+    // device-side sampling (adam_b200_decoder_set_sampling; used by steps with flag bit4)
+    uint32_t smp_k; float smp_temp, smp_top_p, smp_penalty; int smp_on_prompt; uint64_t smp_seed;
     std::vector<uint32_t> free_pages;
     cudaGraphExec_t graph[2]; cudaGraph_t graph_src[2]; uint32_t graph_batch[2]; uint64_t graph_kernels[2];
     // single-launch token kernel (token.cuh): 0 = not examined yet, 1 = ready, -1 = this model does not qualify
@@ -1224,6 +1229,7 @@ extern "C" int adam_b200_decoder_continue(uint32_t id, const int32_t* prompt_tok
 // Run `n_steps` token steps.  flags bit0: run the LM head + arg-max (the sampled
 // id feeds the next step once the prompt is consumed); bit1: also store the
 // soft-capped logits; bit2: launch kernels directly instead of replaying a graph;
+// bit4: draw the token with the rule of adam_b200_decoder_set_sampling instead of the arg-max;
 // bit3: use the chain of per-operation kernels even where the single-launch token
 // kernel (one sequence, row-tiled weights) would run.
 // Returns without waiting unless called outside batch_begin/batch_end.
@@ -1231,8 +1237,17 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
     Decoder* D = get_dec(id);
     if (!D) return ADAMAH_ERR_NOT_FOUND;
     if (D->batch == 0) return fail(ADAMAH_ERR_INVALID, "decoder_step: call decoder_begin first");
-    const bool with_lm = flags & 1u, want_logits = (flags & 2u) != 0, direct = (flags & 4u) != 0, chain = (flags & 8u) != 0;
+    const bool sample = (flags & 16u) != 0;
+    const bool with_lm = flags & 1u, want_logits = (flags & 2u) != 0 || sample, direct = (flags & 4u) != 0, chain = (flags & 8u) != 0;
     if (want_logits && !with_lm) return fail(ADAMAH_ERR_INVALID, "decoder_step: logits need the LM head flag");
+    if (sample && D->smp_k == 0) return fail(ADAMAH_ERR_INVALID, "decoder_step: call adam_b200_decoder_set_sampling before a sampled step");
+    // the sampled token replaces the arg-max one right after every step (positions are already advanced)
+    auto sample_step = [&]() -> int {
+        if (!sample) return ADAMAH_OK;
+        const Mat& lm = D->output.bound ? D->output : D->embd;
+        return launch_sample(D->logits, lm.rows, D->batch, D->smp_k, D->smp_temp, D->smp_top_p, D->smp_penalty, D->smp_on_prompt, D->smp_seed,
+                             D->pos, D->prompt_len, D->prompt_tok, D->gen_log, D->d.kv_cap, D->cur_tok, D->cur_val);
+    };
     int rc = ADAMAH_OK;
     // a step past the reserved pages would only set a device error bit and return ids that look valid
     for (uint32_t b = 0; b < D->batch; ++b)
@@ -1264,12 +1279,12 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
                 count_launch(s);
             }
         }
-        for (; s < n_steps && rc == ADAMAH_OK; ++s) rc = enqueue_token(D, with_lm, want_logits);
+        for (; s < n_steps && rc == ADAMAH_OK; ++s) { rc = enqueue_token(D, with_lm, want_logits); if (rc == ADAMAH_OK) rc = sample_step(); }
         end_of_op();
         return rc;
     }
     if (direct || want_logits || capturing()) {
-        for (uint32_t s = 0; s < n_steps && rc == ADAMAH_OK; ++s) rc = enqueue_step(D, D->batch, with_lm, want_logits);
+        for (uint32_t s = 0; s < n_steps && rc == ADAMAH_OK; ++s) { rc = enqueue_step(D, D->batch, with_lm, want_logits); if (rc == ADAMAH_OK) rc = sample_step(); }
     } else {
         const int gi = with_lm ? 1 : 0;
         if (!D->graph[gi] || D->graph_batch[gi] != D->batch) {
@@ -1297,6 +1312,22 @@ extern "C" int adam_b200_decoder_step(uint32_t id, uint32_t n_steps, uint32_t fl
     }
     end_of_op();
     return rc;
+}
+
+// Sampling rule of steps that carry flag bit4 (role of GenerationConfig, adam/models/engine.py:24-29, applied as
+// `_sample` does, :3711-3729): repeat penalty on the distinct ids among the last 64 of the history (generated
+// tokens, plus the prompt with repeat_on_prompt), temperature, the top_k (1..64) best, soft-max, nucleus top_p,
+// one draw per step from a counter-based generator keyed by (seed, sequence, position).  temperature <= 0 or
+// top_k == 1 picks the best penalised logit.
+extern "C" int adam_b200_decoder_set_sampling(uint32_t id, uint32_t top_k, float top_p, float temperature, float repeat_penalty,
+                                              uint32_t repeat_on_prompt, uint64_t seed) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+    if (top_k == 0 || top_k > 64) return fail(ADAMAH_ERR_INVALID, "decoder_set_sampling: top_k must be 1..64");
+    if (!(repeat_penalty > 0.f)) return fail(ADAMAH_ERR_INVALID, "decoder_set_sampling: repeat_penalty must be positive");
+    D->smp_k = top_k; D->smp_top_p = top_p; D->smp_temp = temperature; D->smp_penalty = repeat_penalty;
+    D->smp_on_prompt = repeat_on_prompt ? 1 : 0; D->smp_seed = seed;
+    return ADAMAH_OK;
 }
 
 // Asynchronous read of the current tokens: tokens_async enqueues, behind everything issued so

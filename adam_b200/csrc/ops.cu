@@ -426,6 +426,12 @@ __global__ void k_gemv_q4map(const float* __restrict__ x, const uint32_t* __rest
 
 static inline unsigned nblk(uint64_t n, unsigned t) { return (unsigned)((n + t - 1) / t); }
 
+// y = W x for one row of activations over a Q4 map (for other translation units)
+void launch_gemv_q4map(const float* x, const Map* w, uint64_t w_off, float* y, uint32_t K, uint32_t N) {
+    k_gemv_q4map<<<nblk(N, 8), 256, 0, g.stream>>>(x, (const uint32_t*)w->buf, w->qparams, w->group_size, w_off, y, K, N);
+    count_launch();
+}
+
 static Map* f32_map(uint32_t id, const char* op) {
     Map* m = get_map(id);
     if (!m) return nullptr;

@@ -244,7 +244,7 @@ extern "C" int adamah_init_ex(uint64_t, uint64_t) {
 }
 extern "C" int adamah_init(void) { return adamah_init_ex(0, 0); }
 
-namespace ab { void decoder_destroy_all(); void plans_clear_all(); void tiled_drop_map(uint32_t map_id); void ar_destroy_all(); void gemm_tc_release(); }
+namespace ab { void decoder_destroy_all(); void plans_clear_all(); void tiled_drop_map(uint32_t map_id); void ar_destroy_all(); void gemm_tc_release(); void sample_free_all(); }
 
 extern "C" void adamah_shutdown(void) {
     if (!g.inited) return;
@@ -252,6 +252,7 @@ extern "C" void adamah_shutdown(void) {
     cudaStreamSynchronize(g.stream);
     ar_destroy_all();
     decoder_destroy_all();
+    sample_free_all();
     gemm_tc_release();
     plans_clear_all();
     tiled_drop_map(0xFFFFFFFFu);

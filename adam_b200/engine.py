@@ -14,8 +14,9 @@ What differs from the reference engine, by design:
 * extensions: several independent sequences per step (``generate_batch``), fp16
   paged KV cache, optional sliding-window mask.
 
-Only greedy decoding is implemented (the reference's ``gpu_matvec_argmax`` sampling
-mode, engine.py:3357-3402, 3793).
+Sampling modes (engine.py:3760-3805): ``gpu_matvec_argmax`` (greedy, fused LM head + arg-max),
+``gpu_fused_topk`` (repeat penalty, top-k <= 64, nucleus and the draw on the device: 4 bytes come
+back per token) and ``cpu`` (logits read back, the reference's host rule) for anything else.
 """
 from __future__ import annotations
 
@@ -35,7 +36,8 @@ _MAT_KIND = {"attn_q": 0, "attn_k": 1, "attn_v": 2, "attn_output": 3, "ffn_gate"
 _NORM_KIND = {"attn_norm": 0, "post_attention_norm": 1, "ffn_norm": 2, "post_ffw_norm": 3, "attn_q_norm": 4, "attn_k_norm": 5}
 _KIND_EMBD, _KIND_OUTPUT, _KIND_OUTPUT_NORM = 7, 8, 6
 
-STEP_LM, STEP_LOGITS, STEP_DIRECT, STEP_CHAIN = 1, 2, 4, 8
+STEP_LM, STEP_LOGITS, STEP_DIRECT, STEP_CHAIN, STEP_SAMPLE = 1, 2, 4, 8, 16
+SAMPLE_TOPK_MAX = 64           # candidates the device-side sampling step keeps (the reference's SAMPLE_TOPK_MAX)
 
 
 def rope_tables(n_pos: int, head_dim: int, freq_base: float):
@@ -170,10 +172,18 @@ class ADAMEngine:
         self._batch = len(prompts)
         self._h2d_bytes = flat.nbytes + lens.nbytes + res.nbytes
 
-    def step(self, n_steps: int = 1, lm_head: bool = True, logits: bool = False, direct: bool = False, chain: bool = False):
-        """``chain=True`` forces the chain of per-operation kernels where the single-launch token kernel would run."""
-        flags = (STEP_LM if lm_head else 0) | (STEP_LOGITS if logits else 0) | (STEP_DIRECT if direct else 0) | (STEP_CHAIN if chain else 0)
+    def step(self, n_steps: int = 1, lm_head: bool = True, logits: bool = False, direct: bool = False, chain: bool = False,
+             sample: bool = False):
+        """``chain=True`` forces the chain of per-operation kernels where the single-launch token kernel would run;
+        ``sample=True`` draws the token on the device with the rule given to ``set_sampling``."""
+        flags = ((STEP_LM if lm_head else 0) | (STEP_LOGITS if logits else 0) | (STEP_DIRECT if direct else 0) | (STEP_CHAIN if chain else 0)
+                 | (STEP_SAMPLE if sample else 0))
         self._check(self._lib.adam_b200_decoder_step(self._dec, n_steps, flags), "adam_b200_decoder_step")
+
+    def set_sampling(self, top_k: int, top_p: float, temperature: float, repeat_penalty: float, repeat_on_prompt: bool, seed: int):
+        self._check(self._lib.adam_b200_decoder_set_sampling(self._dec, int(top_k), float(top_p), float(temperature), float(repeat_penalty),
+                                                             1 if repeat_on_prompt else 0, int(seed) & 0xFFFFFFFFFFFFFFFF),
+                    "adam_b200_decoder_set_sampling")
 
     def prefill(self, n_tokens: int):
         """Consume the next ``n_tokens`` prompt tokens of every sequence, many positions per pass
@@ -229,6 +239,10 @@ class ADAMEngine:
         (engine.py:3760-3805)."""
         if config.is_greedy() and config.repeat_penalty == 1.0:
             return "gpu_matvec_argmax"
+        # LM head + top-k with repeat penalty + nucleus + draw, all on the device (the reference's
+        # 'gpu_fused_topk', engine.py:3403-3512): for up to SAMPLE_TOPK_MAX candidates
+        if config.is_greedy() or 0 < config.top_k <= SAMPLE_TOPK_MAX:
+            return "gpu_fused_topk"
         return "cpu"
 
     @staticmethod
@@ -366,9 +380,15 @@ class ADAMEngine:
                         finished[b] = True
 
             depth = max(1, int(sync_every))
+            fused = mode == "gpu_fused_topk"
+            if fused:
+                seed = config.seed if config.seed is not None else int.from_bytes(__import__("os").urandom(8), "little")
+                greedy = config.is_greedy()
+                self.set_sampling(1 if greedy else config.top_k, config.top_p, 0.0 if greedy else config.temperature,
+                                  config.repeat_penalty, config.repeat_on_prompt, seed)
             with g.batch():
                 while steps_done < n_steps and not all(finished):
-                    self.step(1, lm_head=True)
+                    self.step(1, lm_head=True, sample=fused)
                     slot = _ct.c_uint32(0)
                     self._check(self._lib.adam_b200_decoder_tokens_async(self._dec, _ct.byref(slot)), "adam_b200_decoder_tokens_async")
                     pending.append((steps_done, int(slot.value)))

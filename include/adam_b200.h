@@ -146,6 +146,14 @@ int map_topk_dev(uint32_t map, uint32_t src_h, uint32_t idx_dst_h, uint32_t val_
 int map_topp_dev(uint32_t map, uint32_t src_h, uint32_t dst_h, uint32_t n, float temperature, float top_p);
 int map_sample_categorical_dev(uint32_t map, uint32_t idx_h, uint32_t prob_h, uint32_t rand_h, uint32_t dst_h, uint32_t n);
 int map_repeat_penalty_dev(uint32_t map, uint32_t src_h, uint32_t token_ids_h, uint32_t n_ids, float penalty);
+/* adamah.c:9727-9832: per group of rows_per_group rows the k (<= 64) largest W[n,:] . x after the repeat
+ * penalty, (row as float32, value) at locs_idx_dst / locs_val_dst [group * k + r]; _dev uses 256 rows. */
+int map_matvec_topk_t_xq4_ex_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h, uint32_t b_h, uint32_t penalty_ids_h,
+                                 uint32_t idx_dst_h, uint32_t val_dst_h, uint32_t K, uint32_t N, uint32_t k,
+                                 uint32_t n_penalty, float repeat_penalty, uint32_t rows_per_group);
+int map_matvec_topk_t_xq4_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h, uint32_t b_h, uint32_t penalty_ids_h,
+                              uint32_t idx_dst_h, uint32_t val_dst_h, uint32_t K, uint32_t N, uint32_t k,
+                              uint32_t n_penalty, float repeat_penalty);
 int map_matvec_argmax_t_xq4_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h, uint32_t b_h,
                                 uint32_t idx_tmp_h, uint32_t val_tmp_h, uint32_t dst_h,
                                 uint32_t K, uint32_t N, uint32_t rows_per_group);
@@ -364,6 +372,11 @@ int adam_b200_decoder_token_trace(uint32_t id, uint32_t layer, long long* out, u
  * microseconds; the waits run out, the kernel records error bit 2 (adam_b200_device_error), sets the decoder's
  * sticky word and returns.  Later steps return at once until decoder_begin / decoder_continue. */
 int adam_b200_decoder_test_wait_expiry(uint32_t id, uint32_t wait_us);
+/* Sampling on the device (role of GenerationConfig + ADAMEngine._sample, adam/models/engine.py:24-29, :3711-3729):
+ * steps with flag bit4 (16) replace the arg-max token by a draw -- repeat penalty on the last 64 history ids,
+ * temperature, top_k (1..64), soft-max, nucleus top_p, counter-based generator keyed by (seed, sequence, position). */
+int adam_b200_decoder_set_sampling(uint32_t id, uint32_t top_k, float top_p, float temperature, float repeat_penalty,
+                                   uint32_t repeat_on_prompt, uint64_t seed);
 /* Device address / size of a decoder buffer: 0 projection output [batch][n_embd] f32,
  * 1 current token ids [max_batch] i32, 2 their logit values [max_batch] f32, 3 positions. */
 int adam_b200_decoder_buffer_ptr(uint32_t id, uint32_t which, uint64_t* ptr_out, uint64_t* bytes_out);

@@ -209,7 +209,7 @@ def test_host_sampling_mode(gpu):
     tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=44)
     f32 = dequant_model(tensors)
     prompt = [int(t) for t in synth.random_prompt(cfg.n_vocab, 7, seed=9)]
-    gen = GenerationConfig(max_tokens=12, temperature=0.9, top_k=5, top_p=0.95, repeat_penalty=1.3, seed=123, eos_token_ids=())
+    gen = GenerationConfig(max_tokens=12, temperature=0.9, top_k=100, top_p=0.95, repeat_penalty=1.3, seed=123, eos_token_ids=())   # more than 64 candidates: host
     eng = ADAMEngine(gpu, cfg, tensors, kv_cap=32, kv_dtype="f32")
     try:
         ids, st = eng.generate(prompt, gen)
@@ -224,7 +224,7 @@ def test_host_sampling_mode(gpu):
                 lg = logits.copy()
                 for h in set(seq[len(prompt):i + 1][-64:]):
                     lg[h] = lg[h] / 1.3 if lg[h] > 0 else lg[h] * 1.3
-                assert seq[i + 1] in set(np.argsort(-lg)[:5].tolist())
+                assert seq[i + 1] in set(np.argsort(-lg)[:100].tolist())
         # a nucleus that keeps one candidate is arg-max of the penalised logits
         one, _ = eng.generate(prompt, GenerationConfig(max_tokens=6, temperature=0.7, top_k=40, top_p=1e-6, repeat_penalty=1.0, seed=1,
                                                        eos_token_ids=()))
@@ -338,6 +338,88 @@ def test_bounded_wait_runs_out_and_the_kernel_returns(gpu):
         gpu.device_error()
         again, _ = eng.generate(prompt, GenerationConfig(max_tokens=8, **GREEDY))    # begin() clears the word
         assert again == good
+        assert gpu.device_error() == 0
+    finally:
+        eng.close()
+
+
+def _splitmix_uniform(seed, seq, pos):
+    """The device generator of sampled steps: splitmix64 of (seed, sequence, position), top 24 bits."""
+    m = (1 << 64) - 1
+    z = (seed + 0x9E3779B97F4A7C15 * (((seq << 32) | pos) + 1)) & m
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+    z ^= z >> 31
+    return np.float32(z >> 40) * np.float32(1.0 / 16777216.0)
+
+
+def test_device_sampling_mode(gpu):
+    """Repeat penalty, top-k, nucleus and the draw on the device ('gpu_fused_topk', engine.py:3403-3512; rule of
+    `_sample`, :3711-3729): the ids are reproduced on the host from the device's own logits by the same rule and
+    the same counter-based uniform numbers; 4 bytes come back per token; greedy with a penalty takes the best
+    penalised logit."""
+    cfg = _cfg(dict(n_layer=2))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=45, tied=False)
+    prompt = [int(t) for t in synth.random_prompt(cfg.n_vocab, 7, seed=9)]
+    T, K, P, PEN, SEED = 0.9, 5, 0.9, 1.3, 123
+    gen = GenerationConfig(max_tokens=14, temperature=T, top_k=K, top_p=P, repeat_penalty=PEN, seed=SEED, eos_token_ids=())
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=40, kv_dtype="f32")
+    try:
+        ids, st = eng.generate(prompt, gen)
+        assert st["sampling_mode"] == "gpu_fused_topk" and len(ids) == 14 and st["d2h_bytes"] == 4 * 14
+        ids2, _ = eng.generate(prompt, gen)
+        assert ids2 == ids
+        other, _ = eng.generate(prompt, GenerationConfig(max_tokens=14, temperature=T, top_k=K, top_p=P, repeat_penalty=PEN, seed=7, eos_token_ids=()))
+        assert other != ids                                  # another seed, another draw
+        logits = eng.logits_trace(prompt + ids[:-1])
+        f32 = np.float32
+
+        def penalised(lg, hist):
+            lg = lg.copy()
+            for t in set(hist[-64:]):
+                lg[t] = lg[t] / f32(PEN) if lg[t] > 0 else lg[t] * f32(PEN)
+            return lg
+
+        for i in range(len(ids)):
+            lg = penalised(logits[len(prompt) - 1 + i], ids[:i])
+            order = np.lexsort((np.arange(lg.size), -lg))[:K]         # value descending, ties to the lower id
+            l = lg[order]
+            p = np.exp(((l - l[0]) / f32(T)).astype(f32)).astype(f32)
+            tot = f32(0)
+            for v in p:
+                tot = f32(tot + v)
+            keep, cs = K, f32(0)
+            for r in range(K):
+                cs = f32(cs + f32(p[r] / tot))
+                if cs >= f32(P):
+                    keep = r + 1
+                    break
+            ks = f32(0)
+            for r in range(keep):
+                ks = f32(ks + p[r])
+            target = f32(_splitmix_uniform(SEED, 0, len(prompt) + i) * ks)
+            acc, chosen, margin = f32(0), keep - 1, 1.0
+            for r in range(keep):
+                acc = f32(acc + p[r])
+                margin = min(margin, abs(float(target) - float(acc)))
+                if target < acc:
+                    chosen = r
+                    break
+            if margin > 1e-5:                                 # (a draw that lands on a boundary may round either way)
+                assert ids[i] == int(order[chosen]), f"step {i}"
+        # greedy with a repeat penalty: the best penalised logit, still on the device
+        gid, st = eng.generate(prompt, GenerationConfig(max_tokens=10, top_k=1, temperature=0.0, repeat_penalty=PEN, eos_token_ids=()))
+        assert st["sampling_mode"] == "gpu_fused_topk"
+        glog = eng.logits_trace(prompt + gid[:-1])
+        for i in range(len(gid)):
+            assert gid[i] == int(np.argmax(penalised(glog[len(prompt) - 1 + i], gid[:i])))
+        # repeat_on_prompt widens the history to the prompt
+        pid, _ = eng.generate(prompt, GenerationConfig(max_tokens=4, top_k=1, temperature=0.0, repeat_penalty=3.0, repeat_on_prompt=True, eos_token_ids=()))
+        plog = eng.logits_trace(prompt + pid[:-1])
+        lg0 = plog[len(prompt) - 1].copy()
+        for t in set(prompt[-64:]):
+            lg0[t] = lg0[t] / f32(3.0) if lg0[t] > 0 else lg0[t] * f32(3.0)
+        assert pid[0] == int(np.argmax(lg0))
         assert gpu.device_error() == 0
     finally:
         eng.close()

@@ -404,3 +404,55 @@ def test_native_stats_count_launches(gpu):
     gpu.batch_end()
     st = gpu.get_native_stats()
     assert st["dispatch_count"] == 5 and st["submit_count"] == 1 and st["scheduler_mode_name"] == "level_batched"
+
+
+def test_matvec_topk_reference_vector(gpu):
+    """tests/test_decode_primitives.py:260-301: rows diag(1,2,3,4) in a Q4 map, x = ones, row 3 penalised by 2:
+    the two best are row 2 (3.0) and one of rows 1 / 3 (2.0)."""
+    gpu.map_create_typed(13, A.DTYPE_Q4, 1, 16, 32)
+    gpu.set_qparams(13, np.array([4.0 / 15.0], np.float32), np.array([0.0], np.float32))
+    gpu.scatter(13, np.arange(16, dtype=np.uint32), np.diag([1.0, 2.0, 3.0, 4.0]).astype(np.float32).reshape(-1))
+    _f32map(gpu, 14, 16, [1.0, 1.0, 1.0, 1.0])
+    a_h, b_h, pen = _h(gpu, [0]), _h(gpu, [0]), _h(gpu, [3])
+    idx, val = _h(gpu, [4, 5]), _h(gpu, [8, 9])
+    gpu.batch_begin()
+    gpu.map_matvec_topk_t_xq4_dev(14, 13, a_h, b_h, pen, idx, val, 4, 4, 2, 1, 2.0)
+    gpu.batch_end()
+    got_i = _read(gpu, 14, [4, 5]).astype(np.int32)
+    assert got_i[0] == 2 and got_i[1] in (1, 3)
+    assert np.allclose(_read(gpu, 14, [8, 9]), [3.0, 2.0], atol=0.15)
+    assert gpu._lib.map_matvec_topk_t_xq4_dev(14, 13, a_h, b_h, pen, idx, val, 4, 4, 65, 1, 2.0) == -3      # k beyond 64
+
+
+def test_matvec_topk_groups_match_numpy_on_gguf_blocks(gpu):
+    """Partial top-k per group of rows over a GGUF Q4_0 matrix (tensor-core GEMV underneath): every group's list
+    equals numpy's on the product of the decoded weights after the penalty; groups that hold fewer than k rows
+    are padded with (0, -FLT_MAX) as the reference shader does."""
+    from adam_b200 import gguf_blocks as gb
+    rng = np.random.default_rng(17)
+    N, K, k, rpg = 1000, 256, 7, 96
+    raw = gb.random_q4_0_blocks(rng, N, K)
+    gpu.map_create_typed(13, A.DTYPE_GGUF_Q4_0, 1, N * K)
+    gpu.upload_gguf_blocks(13, 2, 0, raw)
+    x = rng.standard_normal(K).astype(np.float32)
+    groups = (N + rpg - 1) // rpg
+    _f32map(gpu, 14, K + 2 * groups * k + 8, x)
+    pen_ids = [5, 97, 500, 999]
+    a_h, b_h, pen = _h(gpu, [0]), _h(gpu, [0]), _h(gpu, pen_ids)
+    il, vl = K + np.arange(groups * k), K + groups * k + np.arange(groups * k)
+    gpu.batch_begin()
+    gpu.map_matvec_topk_t_xq4_ex_dev(14, 13, a_h, b_h, pen, _h(gpu, il), _h(gpu, vl), K, N, k, len(pen_ids), 1.7, rpg)
+    gpu.batch_end()
+    got_i = _read(gpu, 14, il).astype(np.int64).reshape(groups, k)
+    got_v = _read(gpu, 14, vl).reshape(groups, k)
+    y = (q4_blocks.dequant(raw.reshape(-1), 2, N, K).astype(np.float64) @ x).astype(np.float32)
+    for t in pen_ids:
+        y[t] = y[t] / np.float32(1.7) if y[t] > 0 else y[t] * np.float32(1.7)
+    for g_ in range(groups):
+        r0, r1 = g_ * rpg, min(N, (g_ + 1) * rpg)
+        order = r0 + np.argsort(-y[r0:r1], kind="stable")[:k]
+        n = len(order)
+        assert got_i[g_, :n].tolist() == order.tolist()
+        assert np.allclose(got_v[g_, :n], y[order], rtol=1e-4, atol=1e-5)
+        assert (got_i[g_, n:] == 0).all() and (got_v[g_, n:] < -3e38).all()
+    assert gpu.device_error() == 0
