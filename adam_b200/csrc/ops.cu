@@ -277,24 +277,33 @@ __global__ void k_argmax(float* __restrict__ m, uint64_t n_el, const uint32_t* _
 // candidates after top-k), one CTA each. ----
 
 // The k largest of n values with their indices into the loc list, largest first, ties to the
-// lower index, NaN as -FLT_MAX; index stored as float32.  k <= 64.
-__global__ void k_topk(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ ls, const uint32_t* __restrict__ li,
-                       const uint32_t* __restrict__ lv, uint32_t n, uint32_t k, uint32_t* err) {
+// lower index, NaN as -FLT_MAX; index stored as float32.  k <= 64.  Every thread keeps the best of the
+// entries it owns that are still free (a bit per entry in shared memory marks the taken ones), a round is one
+// block-wide arg-max, and only the thread that owned the winner rescans its entries.
+constexpr uint32_t TOPK_BITMAP_WORDS = 4096;                 // entries 0 .. 131071 can be marked
+__global__ void __launch_bounds__(1024) k_topk(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ ls, const uint32_t* __restrict__ li,
+                                                const uint32_t* __restrict__ lv, uint32_t n, uint32_t k, uint32_t* err) {
     __shared__ float sv[32];
     __shared__ int si[32];
-    __shared__ int top[64];
-    for (uint32_t out = 0; out < k; ++out) {
-        float bv = -3.402823466e+38f; int bi = -1;
+    __shared__ uint32_t taken[TOPK_BITMAP_WORDS];
+    __shared__ int s_win;
+    for (uint32_t i = threadIdx.x; i < (n + 31) / 32; i += blockDim.x) taken[i] = 0u;
+    __syncthreads();
+    auto rescan = [&](float& bv, int& bi) {
+        bv = -3.402823466e+38f; bi = -1;
         for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-            bool taken = false;
-            for (uint32_t j = 0; j < out; ++j) taken |= (top[j] == (int)i);
-            if (taken) continue;
+            if (taken[i >> 5] & (1u << (i & 31))) continue;
             const uint64_t a = ls[i];
             if (a >= n_el) { atomicOr(err, DEVERR_OOB_MAP); continue; }
             float v = m[a];
             if (!(v == v)) v = -3.402823466e+38f;
             if (better(v, (int)i, bv, bi)) { bv = v; bi = (int)i; }
         }
+    };
+    float my_v; int my_i;
+    rescan(my_v, my_i);
+    for (uint32_t out = 0; out < k; ++out) {
+        float bv = my_v; int bi = my_i;
         for (int o = 16; o > 0; o >>= 1) {
             float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
@@ -303,77 +312,110 @@ __global__ void k_topk(float* __restrict__ m, uint64_t n_el, const uint32_t* __r
         __syncthreads();
         if (threadIdx.x == 0) {
             for (uint32_t w = 1; w < (blockDim.x >> 5); ++w) if (better(sv[w], si[w], bv, bi)) { bv = sv[w]; bi = si[w]; }
-            top[out] = bi;
+            s_win = bi;
+            if (bi >= 0) taken[bi >> 5] |= 1u << (bi & 31);
             const uint64_t di = li[out], dv = lv[out];
             if (di >= n_el || dv >= n_el) atomicOr(err, DEVERR_OOB_MAP);
             else { m[di] = (float)(bi < 0 ? 0 : bi); m[dv] = bi < 0 ? -3.402823466e+38f : bv; }
         }
         __syncthreads();
+        if (s_win >= 0 && s_win == my_i) rescan(my_v, my_i);       // only the winner's owner lost its candidate
+        __syncthreads();
     }
 }
 
-// Soft-max with temperature over n <= 64 candidates (already sorted by the caller), nucleus cut at
-// top_p, renormalised; the rest gets probability 0.  Serial, like the shader.
-__global__ void k_topp(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ ls, const uint32_t* __restrict__ ld,
-                       uint32_t n, float temperature, float top_p, uint32_t* err) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+// Soft-max with temperature over n <= 64 candidates (already sorted by the caller), nucleus cut at top_p,
+// renormalised; the rest gets probability 0 (map_topp.comp).  One warp, two candidates per lane: loads,
+// exponentials and the maximum run in parallel; the sums are formed in candidate order (each term fetched from
+// its lane by a shuffle), so the results equal a sequential pass bit for bit.
+__global__ void __launch_bounds__(32) k_topp(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ ls, const uint32_t* __restrict__ ld,
+                                              uint32_t n, float temperature, float top_p, uint32_t* err) {
     const float NEG = -3.402823466e+38f;
-    float lg[64], pr[64];
-    for (uint32_t i = 0; i < n; ++i) {
-        const uint64_t a = ls[i];
-        if (a >= n_el || ld[i] >= n_el) { atomicOr(err, DEVERR_OOB_MAP); return; }
-        float v = m[a];
-        if (!(v == v) || isinf(v)) v = NEG;
-        lg[i] = v;
+    const uint32_t lane = threadIdx.x;
+    float lg[2], pr[2];
+    bool bad = false;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t i = lane + 32 * h;
+        lg[h] = NEG;
+        if (i < n) {
+            if (ls[i] >= n_el || ld[i] >= n_el) bad = true;
+            else { float v = m[ls[i]]; lg[h] = (!(v == v) || isinf(v)) ? NEG : v; }
+        }
     }
+    if (__any_sync(0xffffffffu, bad)) { if (lane == 0) atomicOr(err, DEVERR_OOB_MAP); return; }
+    auto at = [&](const float (&x)[2], uint32_t i) { return __shfl_sync(0xffffffffu, x[i >> 5], i & 31); };
     const float temp = fmaxf(temperature, 1e-6f);
     const float keep_p = fminf(fmaxf(top_p, 0.f), 1.f);
-    float mx = NEG;
-    for (uint32_t i = 0; i < n; ++i) if (lg[i] > mx) mx = lg[i];
-    if (mx == NEG) { for (uint32_t i = 0; i < n; ++i) m[ld[i]] = 0.f; return; }
-    float sum = 0.f;
-    for (uint32_t i = 0; i < n; ++i) {
-        if (lg[i] == NEG) { pr[i] = 0.f; continue; }
-        pr[i] = expf(__fdiv_rn(lg[i] - mx, temp));
-        sum += pr[i];
+    const float mx = warp_max(fmaxf(lg[0], lg[1]));
+    if (mx == NEG) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) if (lane + 32 * h < n) m[ld[lane + 32 * h]] = 0.f;
+        return;
     }
-    if (sum <= 0.f) { for (uint32_t i = 0; i < n; ++i) m[ld[i]] = (i == 0) ? 1.f : 0.f; return; }
-    for (uint32_t i = 0; i < n; ++i) pr[i] = __fdiv_rn(pr[i], sum);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) pr[h] = (lane + 32 * h < n && lg[h] != NEG) ? expf(__fdiv_rn(lg[h] - mx, temp)) : 0.f;
+    float sum = 0.f;
+    for (uint32_t i = 0; i < n; ++i) sum += at(pr, i);
+    if (sum <= 0.f) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) if (lane + 32 * h < n) m[ld[lane + 32 * h]] = (lane + 32 * h == 0) ? 1.f : 0.f;
+        return;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) pr[h] = __fdiv_rn(pr[h], sum);
     uint32_t keep = 0;
     float csum = 0.f;
     for (uint32_t i = 0; i < n; ++i) {
-        csum += pr[i];
+        csum += at(pr, i);
         keep = i + 1;
         if (keep_p >= 0.999999f || csum >= keep_p) break;
     }
     if (keep == 0 && n > 0) keep = 1;
     float ks = 0.f;
-    for (uint32_t i = 0; i < keep; ++i) ks += pr[i];
+    for (uint32_t i = 0; i < keep; ++i) ks += at(pr, i);
     if (ks <= 0.f) ks = 1.f;
-    for (uint32_t i = 0; i < n; ++i) m[ld[i]] = i < keep ? __fdiv_rn(pr[i], ks) : 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t i = lane + 32 * h;
+        if (i < n) m[ld[i]] = i < keep ? __fdiv_rn(pr[h], ks) : 0.f;
+    }
 }
 
-// Inverse-CDF draw: the first candidate whose running probability sum exceeds r * total.
-__global__ void k_sample_categorical(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ lidx, const uint32_t* __restrict__ lprob,
-                                     const uint32_t* __restrict__ lrand, const uint32_t* __restrict__ ldst, uint32_t n, uint32_t* err) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    if (lrand[0] >= n_el || ldst[0] >= n_el) { atomicOr(err, DEVERR_OOB_MAP); return; }
-    for (uint32_t i = 0; i < n; ++i) if (lidx[i] >= n_el || lprob[i] >= n_el) { atomicOr(err, DEVERR_OOB_MAP); return; }
-    auto prob = [&](uint32_t i) { float p = m[lprob[i]]; return (!(p == p) || isinf(p) || p < 0.f) ? 0.f : p; };
-    float total = 0.f;
-    for (uint32_t i = 0; i < n; ++i) total += prob(i);
-    if (!(total > 0.f)) { m[ldst[0]] = m[lidx[0]]; return; }
-    float r = m[lrand[0]];
-    if (!(r == r) || isinf(r)) r = 0.f;
-    r = fminf(fmaxf(r, 0.f), 0.99999994f);
-    const float target = r * total;
-    float acc = 0.f;
-    uint32_t chosen = n - 1;
-    for (uint32_t i = 0; i < n; ++i) {
-        acc += prob(i);
-        if (target < acc) { chosen = i; break; }
+// Inverse-CDF draw: the first candidate whose running probability sum exceeds r * total
+// (map_sample_categorical.comp).  One warp; probabilities are loaded in parallel, the running sums are formed in
+// candidate order as above.
+__global__ void __launch_bounds__(32) k_sample_categorical(float* __restrict__ m, uint64_t n_el, const uint32_t* __restrict__ lidx, const uint32_t* __restrict__ lprob,
+                                                            const uint32_t* __restrict__ lrand, const uint32_t* __restrict__ ldst, uint32_t n, uint32_t* err) {
+    const uint32_t lane = threadIdx.x;
+    bool bad = lrand[0] >= n_el || ldst[0] >= n_el;
+    float pr[2] = {0.f, 0.f};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t i = lane + 32 * h;
+        if (i < n) {
+            if (lidx[i] >= n_el || lprob[i] >= n_el) bad = true;
+            else { const float p = m[lprob[i]]; pr[h] = (!(p == p) || isinf(p) || p < 0.f) ? 0.f : p; }
+        }
     }
-    m[ldst[0]] = m[lidx[chosen]];
+    if (__any_sync(0xffffffffu, bad)) { if (lane == 0) atomicOr(err, DEVERR_OOB_MAP); return; }
+    auto at = [&](uint32_t i) { return __shfl_sync(0xffffffffu, pr[i >> 5], i & 31); };
+    float total = 0.f;
+    for (uint32_t i = 0; i < n; ++i) total += at(i);
+    uint32_t chosen = 0;
+    if (total > 0.f) {
+        float r = m[lrand[0]];
+        if (!(r == r) || isinf(r)) r = 0.f;
+        r = fminf(fmaxf(r, 0.f), 0.99999994f);
+        const float target = r * total;
+        float acc = 0.f;
+        chosen = n - 1;
+        for (uint32_t i = 0; i < n; ++i) {
+            acc += at(i);
+            if (target < acc) { chosen = i; break; }
+        }
+    }
+    if (lane == 0) m[ldst[0]] = m[lidx[chosen]];
 }
 
 // logit[tok] = logit > 0 ? logit / penalty : logit * penalty for each listed token id.
@@ -647,6 +689,7 @@ extern "C" int map_topk_dev(uint32_t map, uint32_t src_h, uint32_t idx_dst_h, ui
     if (!m) return ADAMAH_ERR_NOT_FOUND;
     if (!n || !k) return ADAMAH_OK;
     if (k > 64) return fail(ADAMAH_ERR_INVALID, "topk: k must be at most 64");
+    if (n > TOPK_BITMAP_WORDS * 32u) return fail(ADAMAH_ERR_INVALID, "topk: at most %u candidates", TOPK_BITMAP_WORDS * 32u);
     REQ_H(src_h, (uint64_t)n * 4); REQ_H(idx_dst_h, (uint64_t)k * 4); REQ_H(val_dst_h, (uint64_t)k * 4);
     k_topk<<<1, 1024, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(src_h), hlocs(idx_dst_h), hlocs(val_dst_h), n, k, g.dev_err);
     DONE("map_topk");
