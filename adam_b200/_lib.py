@@ -142,7 +142,10 @@ _SIGS = {
     "adam_b200_decoder_set_sampling": (c_int, [u32, u32, f32, f32, f32, u32, u64]),
     "map_matvec_topk_t_xq4_ex_dev": (c_int, [u32, u32, u32, u32, u32, u32, u32, u32, u32, u32, u32, f32, u32]),
     "map_matvec_topk_t_xq4_dev": (c_int, [u32, u32, u32, u32, u32, u32, u32, u32, u32, u32, u32, f32]),
+    "map_matmul_t_xq8_dev": (c_int, [u32, u32, u32, u32, u32, u32, u32, u32, u32]),
+    "map_row_gather_xq8_dev": (c_int, [u32, u32, u32, u32, u32, u32, f32]),
     "map_upload_gguf_blocks": (c_int, [u32, u32, u64, c_void_p, u64]),
+    "adam_b200_upload_gguf_file": (c_int, [u32, u32, u64, ctypes.c_char_p, u64, u64]),
     "map_dequant_gguf": (c_int, [u32, u64, c_void_p, u64]),
     "adam_b200_tensor_tile": (c_int, [u32, u64, u32, u32]),
     "adam_b200_quantize_q4_0_dev": (c_int, [c_void_p, u64, c_void_p]),
@@ -153,7 +156,7 @@ OFF_PATH_SYMBOLS = [
     "map_op1", "map_op2", "map_matmul", "map_softmax", "map_layernorm", "map_broadcast", "map_reduce",
     "map_matmul_dev", "map_softmax_dev", "map_softmax_abs_dev", "map_attn_softmax_abs_dev", "map_layernorm_dev",
     "map_reduce_dev", "map_fma_dev", "map_matmul_t_x_dev", "map_matmul_x_dev",
-    "map_matmul_xq4_dev", "map_matmul_t_xq8_dev", "map_matmul_xq8_dev", "map_row_gather_xq8_dev",
+    "map_matmul_xq4_dev", "map_matmul_xq8_dev",
 ]
 
 

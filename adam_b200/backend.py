@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes
+import os
 from typing import Dict, Optional
 
 import numpy as np
@@ -240,6 +241,17 @@ class Adamah:
         self._check(self._lib.map_matmul_t_xq4_dev(map_act, map_wt, locs_a_handle, locs_b_handle, locs_c_handle, M, K, N, n_ops),
                     "map_matmul_t_xq4_dev")
 
+    def map_matmul_t_xq8_dev(self, map_act, map_wt, locs_a_handle, locs_b_handle, locs_c_handle, M, K, N, n_ops=1):
+        """C = A @ B^T with B in a GGUF Q8_0 / Q5_0 block map (adamah-MAIN/adamah/__init__.py map_matmul_t_xq8_dev)."""
+        self._check(self._lib.map_matmul_t_xq8_dev(map_act, map_wt, locs_a_handle, locs_b_handle, locs_c_handle, M, K, N, n_ops),
+                    "map_matmul_t_xq8_dev")
+
+    def map_row_gather_xq8_dev(self, map_act, map_wt, src_base, dst_base, row_idx, row_size, scale=1.0):
+        """One decoded row of a Q8_0 / Q5_0 block map, times ``scale``, into the float32 map
+        (adamah-MAIN/adamah/__init__.py:1786-1798)."""
+        self._check(self._lib.map_row_gather_xq8_dev(map_act, map_wt, src_base, dst_base, row_idx, row_size, float(scale)),
+                    "map_row_gather_xq8_dev")
+
     def map_attn_softmax_value_dev(self, map_id, locs_scores_handle, locs_values_handle, locs_out_handle, n_ops, row_size, value_dim,
                                    scale=1.0, cap=0.0):
         self._check(self._lib.map_attn_softmax_value_dev(map_id, locs_scores_handle, locs_values_handle, locs_out_handle, n_ops,
@@ -427,6 +439,11 @@ class Adamah:
             a = np.ascontiguousarray(raw, dtype=np.uint8)
             ptr, nb = self._ptr(a), a.nbytes
         self._check(self._lib.map_upload_gguf_blocks(map_id, ggml_type, elem_off, ptr, nb), "map_upload_gguf_blocks")
+
+    def upload_gguf_file(self, map_id: int, ggml_type: int, elem_off: int, path: str, file_offset: int, n_bytes: int):
+        """Blocks of one tensor straight from a .gguf file (``n_bytes`` at ``file_offset``) into a GGUF-block map."""
+        self._check(self._lib.adam_b200_upload_gguf_file(map_id, ggml_type, elem_off, os.fsencode(path), file_offset, n_bytes),
+                    "adam_b200_upload_gguf_file")
 
     def tile_tensor(self, map_id: int, elem_off: int, rows: int, cols: int):
         """Register a row-tiled copy of a Q4_0 tensor so GEMVs on it use the tensor-core kernel."""

@@ -13,6 +13,8 @@ DTYPE_Q6 = 4
 # extensions: weights stored as GGUF blocks (18 B / 32 and 144 B / 256)
 DTYPE_GGUF_Q4_0 = 16
 DTYPE_GGUF_Q4_K = 17
+DTYPE_GGUF_Q8_0 = 18
+DTYPE_GGUF_Q5_0 = 19
 
 # status codes (adamah.c:23-28)
 ADAMAH_OK = 0
@@ -59,5 +61,10 @@ DECODE_OP_ROW_COPY_OFFSET = 24
 DECODE_OP_ATTN_SOFTMAX_VALUE = 25
 
 # ggml tensor types accepted by map_upload_gguf_blocks
+GGML_TYPE_F32 = 0
 GGML_TYPE_Q4_0 = 2
+GGML_TYPE_Q5_0 = 6
+GGML_TYPE_Q8_0 = 8
 GGML_TYPE_Q4_K = 12
+# map dtype that stores each block type as it is in the file
+GGUF_MAP_DTYPE = {GGML_TYPE_Q4_0: DTYPE_GGUF_Q4_0, GGML_TYPE_Q4_K: DTYPE_GGUF_Q4_K, GGML_TYPE_Q8_0: DTYPE_GGUF_Q8_0, GGML_TYPE_Q5_0: DTYPE_GGUF_Q5_0}

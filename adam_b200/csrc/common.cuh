@@ -31,11 +31,16 @@ struct Map {
     void*    buf;          // F32: float[n]; Q4: uint32[ceil(n/8)];
                            // GGUF_Q4_K: raw 144-byte superblocks;
                            // GGUF_Q4_0: quant plane (uint4 per block) then scale plane (half per block)
+                           // GGUF_Q8_0: quant plane (32 B per block) then scale plane
+                           // GGUF_Q5_0: nibble plane (16 B per block), high-bit plane (uint32 per block), scale plane
     size_t   bytes;
     float*   qparams;      // Q4 map: interleaved [scale, zero] per group
     uint32_t n_groups;
     uint4*   q40_qs;       // GGUF_Q4_0 planes (inside buf)
     __half*  q40_d;
+    uint4*    b8_q;        // GGUF_Q8_0 / GGUF_Q5_0 planes (inside buf)
+    uint32_t* b8_h;
+    __half*   b8_d;
 };
 
 struct Handle {

@@ -17,6 +17,7 @@
 #include "gemv_mma.cuh"
 #include "gemm_tc.cuh"
 #include "token.cuh"
+#include "blocks8.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -101,7 +102,21 @@ __global__ void k_embed(const WeightRef w, uint32_t n_embd, uint32_t n_vocab, fl
     int32_t tok = (p < prompt_len[b]) ? prompt_tok[(size_t)b * prompt_ld + p] : cur_tok[b];
     if (tok < 0 || (uint32_t)tok >= n_vocab) { if (threadIdx.x == 0) atomicOr(err, DEVERR_BAD_TOKEN); tok = 0; }
     float* out = h + (size_t)r * n_embd;
-    if (WT == WT_Q4_0) {
+    if (WT == WT_Q8_0 || WT == WT_Q5_0) {
+        // code * fp16 scale is exact in float32; the embedding multiplier rounds once (map_row_gather_xq8.comp)
+        const size_t b0 = (size_t)tok * (n_embd / 32);
+        for (uint32_t i = threadIdx.x; i < n_embd; i += blockDim.x) {
+            const size_t blk = b0 + (i >> 5);
+            const uint32_t j = i & 31;
+            int q;
+            if (WT == WT_Q8_0) q = (int)reinterpret_cast<const int8_t*>(w.q)[blk * 32 + j];
+            else {
+                const uint32_t byte = reinterpret_cast<const uint8_t*>(w.q)[blk * 16 + (j & 15)];
+                q = (int)((j < 16 ? (byte & 15u) : (byte >> 4)) | (((w.h[blk] >> j) & 1u) << 4)) - 16;
+            }
+            out[i] = __fmul_rn(__fmul_rn((float)q, __half2float(w.d[blk])), emb_scale);
+        }
+    } else if (WT == WT_Q4_0) {
         const uint32_t nblk = n_embd / 32;
         const uint8_t* q = reinterpret_cast<const uint8_t*>(w.q + (size_t)tok * nblk);
         const __half* d = w.d + (size_t)tok * nblk;
@@ -718,6 +733,23 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
     return ADAMAH_OK;
 }
 
+// The embedding kernel takes a full dependency on everything before it (no programmatic launch): later kernels
+// of the step rely on the previous step's position update and cache writes being complete before any of them starts.
+static void launch_embed(Decoder* D, uint32_t rows, const int32_t* row_seq, const int32_t* row_pos) {
+    const adam_b200_decoder_desc& d = D->d;
+    auto go = [&](auto kern) {
+        launch_k(kern, dim3(rows), dim3(256), 0, g.stream, false, D->embd.w, d.n_embd, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok,
+                 d.kv_cap, D->cur_tok, D->hbuf[0], row_seq, row_pos, g.dev_err);
+    };
+    switch (D->embd.wtype) {
+    case WT_Q4_0: go(k_embed<WT_Q4_0>); break;
+    case WT_Q4_K: go(k_embed<WT_Q4_K>); break;
+    case WT_Q8_0: go(k_embed<WT_Q8_0>); break;
+    default:      go(k_embed<WT_Q5_0>); break;
+    }
+    count_launch();
+}
+
 static int gemv(const Mat& m, const Mat* m2, GemvArgs a, int B, int epi) {
     a.w0 = m.w; if (m2) a.w1 = m2->w;
     a.N = (int)m.rows; a.K = (int)m.cols; a.B = B; a.epi = epi;
@@ -754,16 +786,7 @@ static int enqueue_part(Decoder* D, uint32_t batch, uint32_t part, bool with_lm,
     if (part < 2 * d.n_layer && !(part & 1u)) {
         const uint32_t L = part / 2;
         const Layer& ly = D->layers[L];
-        // The embedding kernel takes a full dependency on everything before it (no programmatic
-        // launch): later kernels of the step rely on the previous step's position update and
-        // cache writes being complete before any of them starts.
-        if (L == 0) {
-            if (D->embd.wtype == WT_Q4_0)
-                launch_k(k_embed<WT_Q4_0>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], nullptr, nullptr, g.dev_err);
-            else
-                launch_k(k_embed<WT_Q4_K>, dim3(batch), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], nullptr, nullptr, g.dev_err);
-            count_launch();
-        }
+        if (L == 0) launch_embed(D, batch, nullptr, nullptr);
         const int cur = L == 0 ? 0 : 1;             // residual stream buffer on entry
         GemvArgs in = {};
         in.ldx = (int)E; in.eps = d.norm_eps; in.h_in = D->hbuf[cur]; in.w_pre = ly.norm[NORM_ATTN];
@@ -798,6 +821,16 @@ static int enqueue_part(Decoder* D, uint32_t batch, uint32_t part, bool with_lm,
     } else if (part == 2 * d.n_layer) {
         if (with_lm) {
             const Mat& lm = D->output.bound ? D->output : D->embd;
+            if (wt_is_b8(lm.wtype)) {
+                // Q8_0 / Q5_0 LM head: the norm chain, the products and the arg-max as three kernels; the products land
+                // in the logits buffer (soft-capped afterwards only when the caller wants them)
+                if ((rc = launch_chain_rows(D->hbuf[1], D->proj, D->layers[d.n_layer - 1].norm[NORM_POST_FFW], D->output_norm, D->hbuf[0], D->act,
+                                            (int)E, (int)batch, d.norm_eps, g.stream, g.pdl))) return rc;
+                if ((rc = launch_gemv_b8(lm.wtype, lm.w, D->act, (int)E, D->logits, (int)lm.rows, (int)lm.rows, (int)E, (int)batch, g.stream))) return rc;
+                if ((rc = launch_argmax_rows(D->logits, (int)lm.rows, (int)batch, d.final_softcap, want_logits, D->cur_tok, D->cur_val, nullptr, g.stream, false))) return rc;
+                D->h_final = 0;
+                return check_launch("decoder step");
+            }
             GemvArgs a = {};
             a.ldx = (int)E; a.eps = d.norm_eps; a.h_in = D->hbuf[1]; a.add_src = D->proj;
             a.w_post = D->layers[d.n_layer - 1].norm[NORM_POST_FFW]; a.w_pre = D->output_norm; a.h_out = D->hbuf[0];
@@ -883,6 +916,7 @@ static int prepare_token_kernel(Decoder* D) {
     if (E % 64 || q_dim % 64 || FF % 64 || E > (uint32_t)TK_MAX_E || q_dim > 2u * TK_THREADS * 4u) return ADAMAH_OK;
     const Mat& lm = D->output.bound ? D->output : D->embd;
     if (!lm.tiled || lm.rows % 16) return ADAMAH_OK;
+    if (wt_is_b8(D->embd.wtype) || wt_is_b8(lm.wtype)) return ADAMAH_OK;     // Q8_0 / Q5_0 tables run on the chain of kernels
     const int wt = lm.wtype;
     if (wt == WT_Q4_K && (E % 256 || q_dim % 256 || FF % 256)) return ADAMAH_OK;
     auto al16 = [](const void* p) { return ((uintptr_t)p & 15u) == 0; };
@@ -1091,10 +1125,12 @@ extern "C" int adam_b200_decoder_bind_matrix(uint32_t id, uint32_t layer, uint32
     int rc = weight_ref(m, elem_off, (uint64_t)rows * cols, &mt.wtype, &mt.w);
     if (rc) return rc;
     if (mt.wtype == WT_Q4_K && cols % 256) return fail(ADAMAH_ERR_INVALID, "bind_matrix: Q4_K needs cols %% 256 == 0");
+    if (wt_is_b8(mt.wtype) && ((kind != MAT_EMBD && kind != MAT_OUTPUT) || d.tp_size > 1 || d.n_ff < d.n_embd))
+        return fail(ADAMAH_ERR_INVALID, "bind_matrix: Q8_0 / Q5_0 blocks are accepted for token_embd and output, on one GPU, with n_ff >= n_embd");
     mt.rows = rows; mt.cols = cols; mt.bound = true; mt.map_id = map_wt; mt.elem_off = elem_off; mt.tiled = nullptr;
     // q, k, v get one combined tiled copy later (validate_bound); token_embd is tiled only as the LM head
     const bool solo = kind == MAT_O || kind == MAT_GATE || kind == MAT_UP || kind == MAT_DOWN || kind == MAT_OUTPUT || kind == MAT_EMBD;
-    if (D->use_tiles && solo && rows % 16 == 0 && cols % 64 == 0) {
+    if (D->use_tiles && solo && !wt_is_b8(mt.wtype) && rows % 16 == 0 && cols % 64 == 0) {
         if (tile_tensor(map_wt, elem_off, rows, cols) == ADAMAH_OK) mt.tiled = (const uint8_t*)find_tiled(map_wt, elem_off, rows, cols);
     }
     if (kind == MAT_EMBD) D->embd = mt; else if (kind == MAT_OUTPUT) D->output = mt; else D->layers[layer].m[kind] = mt;
@@ -1416,11 +1452,7 @@ static int enqueue_prefill_part(Decoder* D, uint32_t batch, uint32_t T, uint32_t
         if (L == 0) {
             k_prefill_rows<<<(rows + 63) / 64, 64, 0, g.stream>>>(D->pos, batch, T, D->row_seq, D->row_pos);
             count_launch();
-            if (D->embd.wtype == WT_Q4_0)
-                launch_k(k_embed<WT_Q4_0>, dim3(rows), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], (const int32_t*)D->row_seq, (const int32_t*)D->row_pos, g.dev_err);
-            else
-                launch_k(k_embed<WT_Q4_K>, dim3(rows), dim3(256), 0, g.stream, false, D->embd.w, E, D->embd.rows, d.emb_scale, D->pos, D->prompt_len, D->prompt_tok, d.kv_cap, D->cur_tok, D->hbuf[0], (const int32_t*)D->row_seq, (const int32_t*)D->row_pos, g.dev_err);
-            count_launch();
+            launch_embed(D, rows, (const int32_t*)D->row_seq, (const int32_t*)D->row_pos);
         }
         const int cur = L == 0 ? 0 : 1;
         GemvArgs in = {};

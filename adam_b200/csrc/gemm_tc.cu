@@ -534,6 +534,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) k_gemm_tc(const GemvArgs a, con
 
 // ---- host ----------------------------------------------------------------------------------------
 bool gemm_tc_supports(int wtype, const GemvArgs& a) {
+    if (wtype != WT_Q4_0 && wtype != WT_Q4_K) return false;
     if (g_tc_policy < 0) g_tc_policy = getenv("ADAM_B200_TC") ? atoi(getenv("ADAM_B200_TC")) : 1;
     if (g_tc_policy == 0 || !g_tc.ok) return false;
     if (a.B < TC_MIN_ROWS || a.B > TC_COLS) return false;

@@ -59,6 +59,7 @@ static void choose_shape(int units, int n_slots, int sm_count, int* L_out, int* 
 
 int launch_gemv(int wtype, GemvArgs a, cudaStream_t stream) {
     if (a.N <= 0 || a.K <= 0 || a.B <= 0) return fail(ADAMAH_ERR_INVALID, "gemv: empty shape");
+    if (wtype != WT_Q4_0 && wtype != WT_Q4_K) return fail(ADAMAH_ERR_INVALID, "gemv: this kernel reads Q4_0 / Q4_K blocks only");
     if (wtype == WT_Q4_0 ? (a.K % 32) : (a.K % 256)) return fail(ADAMAH_ERR_INVALID, "gemv: K=%d is not a whole number of blocks", a.K);
     if (!a.h_in && (((uintptr_t)a.x & 15) || (a.ldx & 3))) return fail(ADAMAH_ERR_INVALID, "gemv: activations must be 16-byte aligned");
     if (a.h_in && a.h_out == a.h_in) return fail(ADAMAH_ERR_INVALID, "gemv: h_out must not alias h_in");

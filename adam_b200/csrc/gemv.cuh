@@ -38,7 +38,7 @@
 
 namespace ab {
 
-enum { WT_Q4_0 = 0, WT_Q4_K = 1 };
+enum { WT_Q4_0 = 0, WT_Q4_K = 1, WT_Q8_0 = 2, WT_Q5_0 = 3 };   // the last two: blocks8.cuh (own kernels, not the ones below)
 enum { EPI_STORE = 0, EPI_GEGLU = 1, EPI_SWIGLU = 2, EPI_ARGMAX = 3 };
 
 template <int WT> struct Geo;
@@ -49,6 +49,7 @@ struct WeightRef {          // a [N,K] tensor inside a GGUF-block map
     const uint4*  q;        // Q4_0: first unit of the tensor in the quant plane
                             // Q4_K: first superblock (9 uint4 each)
     const __half* d;        // Q4_0: first block scale; unused for Q4_K
+    const uint32_t* h;      // Q5_0 only: first word of the high-bit plane (Q8_0 / Q5_0: q = quant plane, d = scale plane)
 };
 
 struct GemvArgs {

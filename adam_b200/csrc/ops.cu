@@ -7,6 +7,7 @@
 #include "gemv.cuh"
 #include "gemv_mma.cuh"
 #include "gemm_tc.cuh"
+#include "blocks8.cuh"
 
 #include <cstring>
 
@@ -487,6 +488,8 @@ static int* s_part_idx = nullptr;
 static unsigned int* s_ticket = nullptr;
 static int* s_tok = nullptr;
 
+int logits_scratch(size_t n, float** out);      // sample.cu
+
 int argmax_scratch(float** pv, int** pi, unsigned int** tk) {
     if (!s_part_val) {
         // per-CTA partial winners for up to 64 batch rows of one launch (16 row groups of 4), one ticket per group
@@ -513,12 +516,30 @@ int weight_ref(const Map* m, uint64_t off, uint64_t n_elems, int* wtype, WeightR
         *wtype = WT_Q4_K; w->q = (const uint4*)((const uint8_t*)m->buf + off / 256 * 144); w->d = nullptr;
         return ADAMAH_OK;
     }
+    if (m->dtype == ADAMAH_DTYPE_GGUF_Q8_0 || m->dtype == ADAMAH_DTYPE_GGUF_Q5_0) {
+        if (off % 32) return fail(ADAMAH_ERR_INVALID, "Q8_0 / Q5_0 tensor offset must be a multiple of 32");
+        const bool q8 = m->dtype == ADAMAH_DTYPE_GGUF_Q8_0;
+        *wtype = q8 ? WT_Q8_0 : WT_Q5_0;
+        w->q = m->b8_q + off / 32 * (q8 ? 2 : 1); w->d = m->b8_d + off / 32; w->h = q8 ? nullptr : m->b8_h + off / 32;
+        return ADAMAH_OK;
+    }
     return fail(ADAMAH_ERR_INVALID, "map does not hold GGUF blocks");
 }
 
 // Run a GEMV on the tensor at (map, off): the tensor-core kernel when a row-tiled
 // copy of exactly this tensor is registered and the shape fits, the generic one otherwise.
 int run_gemv(uint32_t map_id, uint64_t off, int wtype, GemvArgs& ga) {
+    if (wt_is_b8(wtype)) {
+        // Q8_0 / Q5_0: plain products from their own kernel; an arg-max is a second small kernel over the logits
+        if (ga.h_in || ga.epi == EPI_GEGLU || ga.epi == EPI_SWIGLU) return fail(ADAMAH_ERR_INVALID, "Q8_0 / Q5_0 tensors take plain products and arg-max only");
+        float* y = ga.y;
+        if (ga.epi == EPI_ARGMAX && !y) { int rc = logits_scratch((size_t)ga.B * ga.N, &y); if (rc) return rc; }
+        const int ldy = ga.y ? ga.ldy : ga.N;
+        int rc = launch_gemv_b8(wtype, ga.w0, ga.x, ga.ldx, y, ldy, ga.N, ga.K, ga.B, g.stream);
+        if (rc || ga.epi != EPI_ARGMAX) return rc;
+        if (ldy != ga.N) return fail(ADAMAH_ERR_INVALID, "arg-max over Q8_0 / Q5_0 products needs densely stored logits");
+        return launch_argmax_rows(y, ga.N, ga.B, ga.softcap, ga.y != nullptr, ga.out_tok, ga.out_val, ga.out_tok_f32, g.stream, false);
+    }
     if (ga.B >= TC_MIN_ROWS) {
         // many rows: the tcgen05 GEMM (its workspace is allocated on first use, never inside a capture)
         cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -795,7 +816,7 @@ extern "C" int map_matvec_argmax_t_xq4_dev(uint32_t map_act, uint32_t map_wt, ui
     uint32_t ab_, bb, db;
     if (!hfirst(a_h, &ab_) || !hfirst(b_h, &bb) || !hfirst(dst_h, &db)) return ADAMAH_ERR_NOT_FOUND;
     if ((uint64_t)ab_ + K > a->n_elems || db >= a->n_elems) return fail(ADAMAH_ERR_INVALID, "matvec_argmax: activation range beyond map");
-    if (w->dtype != ADAMAH_DTYPE_GGUF_Q4_0 && w->dtype != ADAMAH_DTYPE_GGUF_Q4_K)
+    if (w->dtype != ADAMAH_DTYPE_GGUF_Q4_0 && w->dtype != ADAMAH_DTYPE_GGUF_Q4_K && w->dtype != ADAMAH_DTYPE_GGUF_Q8_0 && w->dtype != ADAMAH_DTYPE_GGUF_Q5_0)
         return fail(ADAMAH_ERR_INVALID, "matvec_argmax: weights must be in a GGUF-block map");
     int wtype; GemvArgs ga = {};
     int rc = weight_ref(w, bb, (uint64_t)N * K, &wtype, &ga.w0);
@@ -808,6 +829,44 @@ extern "C" int map_matvec_argmax_t_xq4_dev(uint32_t map_act, uint32_t map_wt, ui
     rc = run_gemv(map_wt, bb, wtype, ga);
     if (rc) return rc;
     rc = check_launch("map_matvec_argmax_t_xq4");
+    end_of_op();
+    return rc;
+}
+
+// The reference's 8-bit weight operators (adamah.c:9834 map_matmul_t_xq8_dev, :10189 map_row_gather_xq8_dev; shaders
+// map_matvec_t_xq8.comp / map_matmul_t_xq8.comp / map_row_gather_xq8.comp).  There the weight map holds bytes plus a
+// (scale, zero) pair per 32; here it is a GGUF-block map of Q8_0 or Q5_0 blocks as they are in the file, which is
+// what the reference derives its bytes and pairs from (adam/models/engine.py:1142-1182).
+extern "C" int map_matmul_t_xq8_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h, uint32_t b_h, uint32_t c_h,
+                                    uint32_t M, uint32_t K, uint32_t N, uint32_t n_ops) {
+    REQ_READY();
+    Map* w = get_map(map_wt);
+    if (!w) return ADAMAH_ERR_NOT_FOUND;
+    if (n_ops == 0) return ADAMAH_OK;                                        // adamah.c:9856
+    if (w->dtype != ADAMAH_DTYPE_GGUF_Q8_0 && w->dtype != ADAMAH_DTYPE_GGUF_Q5_0)
+        return fail(ADAMAH_ERR_INVALID, "matmul_t_xq8: map %u does not hold Q8_0 / Q5_0 blocks", map_wt);
+    return map_matmul_t_xq4_dev(map_act, map_wt, a_h, b_h, c_h, M, K, N, n_ops);   // same contract; the map's type picks the kernel
+}
+
+// map_act[dst_base + i] = decode(map_wt[src_base + row_idx * row_size + i]) * scale, i < row_size: the token-embedding
+// row fetch (adam/models/engine.py:2409-2413 for the Q4 map; the Q8 twin is used for Q8_0 / Q5_0 embeddings).
+// Bases and the row index are immediates, as in the reference.
+extern "C" int map_row_gather_xq8_dev(uint32_t map_act, uint32_t map_wt, uint32_t src_base, uint32_t dst_base, uint32_t row_idx,
+                                      uint32_t row_size, float scale) {
+    REQ_READY();
+    Map* a = f32_map(map_act, "row_gather_xq8");
+    Map* w = get_map(map_wt);
+    if (!a || !w) return ADAMAH_ERR_NOT_FOUND;
+    if (row_size == 0) return ADAMAH_OK;                                     // adamah.c:10196
+    const uint64_t src = (uint64_t)src_base + (uint64_t)row_idx * row_size;
+    if (row_size % 32 || src % 32) return fail(ADAMAH_ERR_INVALID, "row_gather_xq8: rows must be whole blocks of 32");
+    if ((uint64_t)dst_base + row_size > a->n_elems) return fail(ADAMAH_ERR_INVALID, "row_gather_xq8: destination beyond map %u", map_act);
+    int wtype; WeightRef wr = {};
+    int rc = weight_ref(w, src, row_size, &wtype, &wr);
+    if (rc) return rc;
+    if (!wt_is_b8(wtype)) return fail(ADAMAH_ERR_INVALID, "row_gather_xq8: map %u does not hold Q8_0 / Q5_0 blocks", map_wt);
+    launch_dequant_b8(wtype, wr, row_size, (float*)a->buf + dst_base, scale, true, g.stream);
+    rc = check_launch("map_row_gather_xq8");
     end_of_op();
     return rc;
 }
@@ -897,6 +956,4 @@ OFFPATH(map_fma_dev, u32, u32, u32, u32, u32, u32)
 OFFPATH(map_matmul_t_x_dev, u32, u32, u32, u32, u32, u32, u32, u32, u32)
 OFFPATH(map_matmul_x_dev, u32, u32, u32, u32, u32, u32, u32, u32, u32)
 OFFPATH(map_matmul_xq4_dev, u32, u32, u32, u32, u32, u32, u32, u32, u32)
-OFFPATH(map_matmul_t_xq8_dev, u32, u32, u32, u32, u32, u32, u32, u32, u32)
 OFFPATH(map_matmul_xq8_dev, u32, u32, u32, u32, u32, u32, u32, u32, u32)
-OFFPATH(map_row_gather_xq8_dev, u32, u32, u32, u32, u32, u32, u32)

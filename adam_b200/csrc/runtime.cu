@@ -7,6 +7,7 @@
 // array, a loc handle a small device array, a batch a section of one in-order
 // stream closed by a single synchronisation.
 #include "common.cuh"
+#include "blocks8.cuh"
 
 #include <cstdarg>
 #include <cstdio>
@@ -244,7 +245,7 @@ extern "C" int adamah_init_ex(uint64_t, uint64_t) {
 }
 extern "C" int adamah_init(void) { return adamah_init_ex(0, 0); }
 
-namespace ab { void decoder_destroy_all(); void plans_clear_all(); void tiled_drop_map(uint32_t map_id); void ar_destroy_all(); void gemm_tc_release(); void sample_free_all(); }
+namespace ab { void decoder_destroy_all(); void plans_clear_all(); void tiled_drop_map(uint32_t map_id); void ar_destroy_all(); void gemm_tc_release(); void sample_free_all(); void file_stage_release(); }
 
 extern "C" void adamah_shutdown(void) {
     if (!g.inited) return;
@@ -253,6 +254,7 @@ extern "C" void adamah_shutdown(void) {
     ar_destroy_all();
     decoder_destroy_all();
     sample_free_all();
+    file_stage_release();
     gemm_tc_release();
     plans_clear_all();
     tiled_drop_map(0xFFFFFFFFu);
@@ -301,7 +303,8 @@ extern "C" uint32_t adam_b200_device_error(void) {
 
 extern "C" int adamah_set_dtype(uint32_t dtype) {
     if (!ready()) return ADAMAH_ERR_INVALID;
-    if (dtype != ADAMAH_DTYPE_F32 && dtype != ADAMAH_DTYPE_Q4 && dtype != ADAMAH_DTYPE_GGUF_Q4_0 && dtype != ADAMAH_DTYPE_GGUF_Q4_K)
+    if (dtype != ADAMAH_DTYPE_F32 && dtype != ADAMAH_DTYPE_Q4 && dtype != ADAMAH_DTYPE_GGUF_Q4_0 && dtype != ADAMAH_DTYPE_GGUF_Q4_K &&
+        dtype != ADAMAH_DTYPE_GGUF_Q8_0 && dtype != ADAMAH_DTYPE_GGUF_Q5_0)
         return fail(ADAMAH_ERR_INVALID, "dtype %u is not on the decode path (f32, q4 and GGUF block maps only)", dtype);
     g.active_dtype = dtype;
     return ADAMAH_OK;
@@ -344,6 +347,12 @@ extern "C" int map_init_dtype(uint32_t id, uint32_t dtype, uint32_t pack_size, u
     case ADAMAH_DTYPE_GGUF_Q4_K:
         if (m.n_elems % 256) return fail(ADAMAH_ERR_INVALID, "Q4_K map size must be a multiple of 256");
         m.bytes = m.n_elems / 256 * 144; break;
+    case ADAMAH_DTYPE_GGUF_Q8_0:
+        if (m.n_elems % 32) return fail(ADAMAH_ERR_INVALID, "Q8_0 map size must be a multiple of 32");
+        m.bytes = m.n_elems / 32 * 34; break;
+    case ADAMAH_DTYPE_GGUF_Q5_0:
+        if (m.n_elems % 32) return fail(ADAMAH_ERR_INVALID, "Q5_0 map size must be a multiple of 32");
+        m.bytes = m.n_elems / 32 * 22; break;
     default: return fail(ADAMAH_ERR_INVALID, "dtype %u is not on the decode path", dtype);
     }
     size_t alloc = (m.bytes + 255) & ~(size_t)255;
@@ -356,6 +365,15 @@ extern "C" int map_init_dtype(uint32_t id, uint32_t dtype, uint32_t pack_size, u
     if (dtype == ADAMAH_DTYPE_GGUF_Q4_0) {
         m.q40_qs = (uint4*)m.buf;
         m.q40_d = (__half*)((char*)m.buf + m.n_elems / 32 * 16);
+    }
+    if (dtype == ADAMAH_DTYPE_GGUF_Q8_0) {
+        m.b8_q = (uint4*)m.buf;
+        m.b8_d = (__half*)((char*)m.buf + m.n_elems / 32 * 32);
+    }
+    if (dtype == ADAMAH_DTYPE_GGUF_Q5_0) {
+        m.b8_q = (uint4*)m.buf;
+        m.b8_h = (uint32_t*)((char*)m.buf + m.n_elems / 32 * 16);
+        m.b8_d = (__half*)((char*)m.buf + m.n_elems / 32 * 20);
     }
     m.used = true;
     g.maps[id] = m;
@@ -611,39 +629,69 @@ extern "C" void adamah_stats_get(uint64_t* dispatch, uint64_t* submit, uint64_t*
 
 // ---- GGUF block maps -------------------------------------------------------
 
+namespace ab {
+static const BlockKind BLOCK_KINDS[] = {
+    {2, ADAMAH_DTYPE_GGUF_Q4_0, 32, 18, "Q4_0"}, {12, ADAMAH_DTYPE_GGUF_Q4_K, 256, 144, "Q4_K"},
+    {8, ADAMAH_DTYPE_GGUF_Q8_0, 32, 34, "Q8_0"}, {6, ADAMAH_DTYPE_GGUF_Q5_0, 32, 22, "Q5_0"}};
+const BlockKind* block_kind(uint32_t ggml_type) {
+    for (const BlockKind& k : BLOCK_KINDS) if (k.ggml_type == ggml_type) return &k;
+    return nullptr;
+}
+static WeightRef b8_ref(const Map* m, uint64_t first_block) {
+    WeightRef w = {};
+    w.q = m->b8_q + first_block * (m->dtype == ADAMAH_DTYPE_GGUF_Q8_0 ? 2 : 1);
+    w.d = m->b8_d + first_block;
+    w.h = m->b8_h ? m->b8_h + first_block : nullptr;
+    return w;
+}
+// Enqueue the placement of n_bytes of file blocks, already on the device at `dev_src` (2-byte aligned), at
+// element offset elem_off of map m.  Q4_K keeps the file layout (a copy); the 32-weight types go into planes.
+int place_blocks_from_device(Map* m, const BlockKind& k, uint64_t elem_off, const void* dev_src, uint64_t n_bytes) {
+    const uint64_t nb = n_bytes / k.bytes, b0 = elem_off / k.elems;
+    if (k.ggml_type == 12) {
+        CU(cudaMemcpyAsync((uint8_t*)m->buf + b0 * 144, dev_src, n_bytes, cudaMemcpyDeviceToDevice, g.stream));
+        return ADAMAH_OK;
+    }
+    if ((uintptr_t)dev_src & 1) return fail(ADAMAH_ERR_INVALID, "device block source must be 2-byte aligned");
+    if (k.ggml_type == 2) {
+        k_repack_q4_0<<<blocks_for(nb, 256), 256, 0, g.stream>>>((const uint16_t*)dev_src, m->q40_qs + b0, m->q40_d + b0, nb);
+        count_launch();
+        return ADAMAH_OK;
+    }
+    return launch_repack_b8(k.ggml_type == 8 ? WT_Q8_0 : WT_Q5_0, dev_src, b8_ref(m, b0), nb, g.stream);
+}
+int check_block_range(const Map* m, uint32_t id, const BlockKind* k, uint32_t ggml_type, uint64_t elem_off, uint64_t n_bytes) {
+    if (!k || m->dtype != k->dtype) return fail(ADAMAH_ERR_INVALID, "ggml type %u does not match the storage of map %u", ggml_type, id);
+    if (elem_off % k->elems || n_bytes % k->bytes) return fail(ADAMAH_ERR_INVALID, "%s upload must cover whole %u-byte blocks", k->name, k->bytes);
+    if (elem_off + n_bytes / k->bytes * k->elems > m->n_elems) return fail(ADAMAH_ERR_INVALID, "%s upload beyond map %u", k->name, id);
+    return ADAMAH_OK;
+}
+}  // namespace ab
+
 extern "C" int map_upload_gguf_blocks(uint32_t id, uint32_t ggml_type, uint64_t elem_off, const void* raw, uint64_t n_bytes) {
     Map* m = get_map(id);
     if (!m) return ADAMAH_ERR_NOT_FOUND;
     if (!raw || n_bytes == 0) return fail(ADAMAH_ERR_INVALID, "map_upload_gguf_blocks: empty input");
-    if (ggml_type == 2 && m->dtype == ADAMAH_DTYPE_GGUF_Q4_0) {
-        if (elem_off % 32 || n_bytes % 18) return fail(ADAMAH_ERR_INVALID, "Q4_0 upload must cover whole 18-byte blocks");
-        uint64_t nb = n_bytes / 18, b0 = elem_off / 32;
-        if (elem_off + nb * 32 > m->n_elems) return fail(ADAMAH_ERR_INVALID, "Q4_0 upload beyond map %u", id);
-        cudaPointerAttributes at;
-        bool on_dev = cudaPointerGetAttributes(&at, raw) == cudaSuccess && at.type == cudaMemoryTypeDevice;
-        cudaGetLastError();
-        const uint16_t* src = (const uint16_t*)raw;
-        void* tmp = nullptr;
-        if (!on_dev) {
-            CU(cudaMallocAsync(&tmp, n_bytes, g.stream));
-            CU(cudaMemcpyAsync(tmp, raw, n_bytes, cudaMemcpyHostToDevice, g.stream));
-            src = (const uint16_t*)tmp;
-        } else if ((uintptr_t)raw & 1) return fail(ADAMAH_ERR_INVALID, "device Q4_0 source must be 2-byte aligned");
-        k_repack_q4_0<<<blocks_for(nb, 256), 256, 0, g.stream>>>(src, m->q40_qs + b0, m->q40_d + b0, nb);
-        count_launch();
-        if (tmp) CU(cudaFreeAsync(tmp, g.stream));
-        CU(cudaStreamSynchronize(g.stream));
-        return check_launch("map_upload_gguf_blocks");
-    }
-    if (ggml_type == 12 && m->dtype == ADAMAH_DTYPE_GGUF_Q4_K) {
-        if (elem_off % 256 || n_bytes % 144) return fail(ADAMAH_ERR_INVALID, "Q4_K upload must cover whole 144-byte superblocks");
-        uint64_t nsb = n_bytes / 144;
-        if (elem_off + nsb * 256 > m->n_elems) return fail(ADAMAH_ERR_INVALID, "Q4_K upload beyond map %u", id);
-        CU(cudaMemcpyAsync((uint8_t*)m->buf + elem_off / 256 * 144, raw, n_bytes, cudaMemcpyDefault, g.stream));
+    const BlockKind* k = block_kind(ggml_type);
+    int rc = check_block_range(m, id, k, ggml_type, elem_off, n_bytes);
+    if (rc) return rc;
+    cudaPointerAttributes at;
+    const bool on_dev = cudaPointerGetAttributes(&at, raw) == cudaSuccess && at.type == cudaMemoryTypeDevice;
+    cudaGetLastError();
+    if (ggml_type == 12 && !on_dev) {          // file layout kept: straight to its place
+        CU(cudaMemcpyAsync((uint8_t*)m->buf + elem_off / 256 * 144, raw, n_bytes, cudaMemcpyHostToDevice, g.stream));
         CU(cudaStreamSynchronize(g.stream));
         return ADAMAH_OK;
     }
-    return fail(ADAMAH_ERR_INVALID, "ggml type %u does not match the storage of map %u", ggml_type, id);
+    void* tmp = nullptr;
+    if (!on_dev) {
+        CU(cudaMallocAsync(&tmp, n_bytes, g.stream));
+        CU(cudaMemcpyAsync(tmp, raw, n_bytes, cudaMemcpyHostToDevice, g.stream));
+    }
+    rc = place_blocks_from_device(m, *k, elem_off, tmp ? tmp : raw, n_bytes);
+    if (tmp) cudaFreeAsync(tmp, g.stream);
+    CU(cudaStreamSynchronize(g.stream));
+    return rc ? rc : check_launch("map_upload_gguf_blocks");
 }
 
 extern "C" int map_dequant_gguf(uint32_t id, uint64_t elem_off, float* out, uint64_t n_elems) {
@@ -652,6 +700,7 @@ extern "C" int map_dequant_gguf(uint32_t id, uint64_t elem_off, float* out, uint
     if (!out || n_elems == 0) return fail(ADAMAH_ERR_INVALID, "map_dequant_gguf: empty output");
     if (elem_off + n_elems > m->n_elems) return fail(ADAMAH_ERR_INVALID, "map_dequant_gguf: range beyond map %u", id);
     float* tmp = nullptr;
+    bool counted = false;
     if (m->dtype == ADAMAH_DTYPE_GGUF_Q4_0) {
         if (elem_off % 32 || n_elems % 32) return fail(ADAMAH_ERR_INVALID, "Q4_0 decode must cover whole blocks");
         CU(cudaMallocAsync((void**)&tmp, n_elems * 4, g.stream));
@@ -660,8 +709,13 @@ extern "C" int map_dequant_gguf(uint32_t id, uint64_t elem_off, float* out, uint
         if (elem_off % 256 || n_elems % 256) return fail(ADAMAH_ERR_INVALID, "Q4_K decode must cover whole superblocks");
         CU(cudaMallocAsync((void**)&tmp, n_elems * 4, g.stream));
         k_dequant_q4_k<<<blocks_for(n_elems / 2, 256), 256, 0, g.stream>>>((const uint8_t*)m->buf, elem_off / 256, tmp, n_elems / 256);
+    } else if (m->dtype == ADAMAH_DTYPE_GGUF_Q8_0 || m->dtype == ADAMAH_DTYPE_GGUF_Q5_0) {
+        if (elem_off % 32 || n_elems % 32) return fail(ADAMAH_ERR_INVALID, "Q8_0 / Q5_0 decode must cover whole blocks");
+        CU(cudaMallocAsync((void**)&tmp, n_elems * 4, g.stream));
+        launch_dequant_b8(m->dtype == ADAMAH_DTYPE_GGUF_Q8_0 ? WT_Q8_0 : WT_Q5_0, b8_ref(m, elem_off / 32), n_elems, tmp, 1.f, false, g.stream);
+        counted = true;
     } else return fail(ADAMAH_ERR_INVALID, "map %u does not hold GGUF blocks", id);
-    count_launch();
+    if (!counted) count_launch();
     CU(cudaMemcpyAsync(out, tmp, n_elems * 4, cudaMemcpyDeviceToHost, g.stream));
     CU(cudaFreeAsync(tmp, g.stream));
     CU(cudaStreamSynchronize(g.stream));

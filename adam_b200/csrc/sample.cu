@@ -255,7 +255,7 @@ int launch_sample(const float* logits, uint32_t V, uint32_t batch, uint32_t k, f
 }
 
 static float* s_logits = nullptr; static size_t s_logits_n = 0;
-static int logits_scratch(size_t n, float** out) {
+int logits_scratch(size_t n, float** out) {
     if (s_logits_n < n) {
         if (s_logits) { cudaStreamSynchronize(g.stream); cudaFree(s_logits); s_logits = nullptr; s_logits_n = 0; }
         if (cudaMalloc((void**)&s_logits, n * 4) != cudaSuccess) { cudaGetLastError(); return fail(ADAMAH_ERR_MEMORY, "out of device memory for %zu logits", n); }

@@ -90,6 +90,24 @@ class ADAMEngine:
                                                              self._kv_cap, cfg.head_dim // 2), "adam_b200_decoder_set_rope")
         self._closed = False
 
+    @classmethod
+    def from_gguf(cls, gpu, path: str, verbose: bool = False, **kw) -> "ADAMEngine":
+        """Engine over a .gguf file (role of adam/models/engine.py:118-170 with a streaming ``GGUFLoader``): the
+        header, key/value table and tensor table are parsed on the host, the configuration comes from the
+        metadata and the tensor shapes, and every matrix goes from the file to the GPU as raw blocks through
+        pinned staging (``adam_b200_upload_gguf_file``) -- no host-side decode or re-quantization."""
+        from .gguf_file import GGUFLoader
+        loader = GGUFLoader(path).load(verbose=verbose)
+        try:
+            cfg = loader.model_config(verbose=verbose)
+            kw.setdefault("kv_cap", min(int(cfg.n_ctx), 4096))
+            eng = cls(gpu, cfg, loader.model_tensors(), verbose=verbose, **kw)
+            eng.tensors = {}                 # views of the file mapping: not needed once the blocks are on the device
+            eng.metadata = loader.metadata
+        finally:
+            loader.close()
+        return eng
+
     # ---- helpers ---------------------------------------------------------------------
     def _check(self, rc: int, name: str):
         if rc != 0:
@@ -104,29 +122,40 @@ class ADAMEngine:
         t0 = time.perf_counter()
         self._mat_loc: Dict[str, tuple] = {}
         self._norm_loc: Dict[str, tuple] = {}
-        wtypes = {t.ggml_type for t in self.tensors.values() if isinstance(t, QTensor)}
-        if len(wtypes) != 1:
-            raise ValueError("all matrices must share one GGUF block type")
-        self._ggml_type = wtypes.pop()
-        dt = C.DTYPE_GGUF_Q4_0 if self._ggml_type == C.GGML_TYPE_Q4_0 else C.DTYPE_GGUF_Q4_K
+        layer_types = {t.ggml_type for n, t in self.tensors.items() if isinstance(t, QTensor) and n.startswith("blk.")}
+        if len(layer_types) != 1 or not layer_types <= {C.GGML_TYPE_Q4_0, C.GGML_TYPE_Q4_K}:
+            raise ValueError("the layers' matrices must share one block type, Q4_0 or Q4_K")
+        self._ggml_type = layer_types.pop()
         next_map = self.FIRST_WT_MAP
 
         def put(map_id, names):
+            """One GGUF-block map holding the named tensors back to back (they share a block type)."""
+            kinds = {self.tensors[n].ggml_type for n in names}
+            if len(kinds) != 1 or next(iter(kinds)) not in C.GGUF_MAP_DTYPE:
+                raise ValueError(f"tensors {names} must share one supported block type (Q4_0, Q4_K, Q8_0, Q5_0)")
             total = sum(self.tensors[n].rows * self.tensors[n].cols for n in names)
-            g.map_create_typed(map_id, dt, 1, total)
+            g.map_create_typed(map_id, C.GGUF_MAP_DTYPE[next(iter(kinds))], 1, total)
             off = 0
             for n in names:
                 t = self.tensors[n]
                 if hasattr(t.raw, "data_ptr"):          # CUDA tensor: blocks already on the device
                     g.upload_gguf_blocks(map_id, t.ggml_type, off, int(t.raw.data_ptr()), int(t.raw.numel()))
+                elif getattr(t, "file", None) is not None:   # blocks still in a GGUF file: streamed through pinned staging
+                    g.upload_gguf_file(map_id, t.ggml_type, off, t.file[0], t.file[1], t.nbytes)
                 else:
                     g.upload_gguf_blocks(map_id, t.ggml_type, off, t.raw)
                 self._mat_loc[n] = (map_id, off, t.rows, t.cols)
                 off += t.rows * t.cols
 
+        # token_embd (Q8_0 / Q5_0 in many real files) and output.weight share a map only when their types agree
         head = ["token_embd.weight"] + ([] if self._tied else ["output.weight"])
-        put(next_map, head)
-        next_map += 1
+        if len({self.tensors[n].ggml_type for n in head}) == 1:
+            put(next_map, head)
+            next_map += 1
+        else:
+            for n in head:
+                put(next_map, [n])
+                next_map += 1
         for L in range(c.n_layer):
             put(next_map, [f"blk.{L}.{m}.weight" for m in LAYER_MATS])
             next_map += 1

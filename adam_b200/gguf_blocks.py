@@ -1,9 +1,10 @@
-"""Host-side encoders and synthetic generators for GGUF Q4_0 / Q4_K blocks.
+"""Host-side encoders and synthetic generators for GGUF Q4_0 / Q4_K / Q8_0 / Q5_0 blocks.
 
 These build *inputs* (model files in memory): they are load-time host logic, not
 part of the decode path, and they never decode blocks — decoding happens only in
 the CUDA kernels.  Formats follow the GGUF block layouts the reference loader
-reads (adam/loaders/gguf.py:24-33 QUANT_INFO, :290-299 Q4_0, :312-337 Q4_K).
+reads (adam/loaders/gguf.py:24-33 QUANT_INFO, :290-299 Q4_0, :312-337 Q4_K,
+:282-288 Q8_0, :301-310 Q5_0).
 """
 from __future__ import annotations
 
@@ -11,10 +12,14 @@ import numpy as np
 
 GGML_TYPE_F32 = 0
 GGML_TYPE_Q4_0 = 2
+GGML_TYPE_Q5_0 = 6
+GGML_TYPE_Q8_0 = 8
 GGML_TYPE_Q4_K = 12
 
 Q4_0_BLOCK, Q4_0_BYTES = 32, 18
 Q4_K_BLOCK, Q4_K_BYTES = 256, 144
+Q8_0_BLOCK, Q8_0_BYTES = 32, 34
+Q5_0_BLOCK, Q5_0_BYTES = 32, 22
 
 
 def block_geometry(ggml_type: int) -> tuple[int, int]:
@@ -23,6 +28,10 @@ def block_geometry(ggml_type: int) -> tuple[int, int]:
         return Q4_0_BLOCK, Q4_0_BYTES
     if ggml_type == GGML_TYPE_Q4_K:
         return Q4_K_BLOCK, Q4_K_BYTES
+    if ggml_type == GGML_TYPE_Q8_0:
+        return Q8_0_BLOCK, Q8_0_BYTES
+    if ggml_type == GGML_TYPE_Q5_0:
+        return Q5_0_BLOCK, Q5_0_BYTES
     raise ValueError(f"unsupported ggml type {ggml_type}")
 
 
@@ -59,6 +68,57 @@ def quantize_q4_0(w: np.ndarray) -> np.ndarray:
     d16 = d.astype(np.float16).view(np.uint8).reshape(-1, 2)
     out = np.concatenate([d16, packed], axis=1)
     return out.reshape(lead + (w.shape[-1] // Q4_0_BLOCK * Q4_0_BYTES,))
+
+
+def _round_half_away(x: np.ndarray) -> np.ndarray:
+    """C ``roundf``: halves go away from zero (numpy's ``rint`` sends them to even)."""
+    a = np.abs(x)
+    f = np.floor(a)
+    return np.sign(x) * (f + np.floor(np.float32(2) * (a - f)))
+
+
+def quantize_q8_0(w: np.ndarray) -> np.ndarray:
+    """float32 ``[..., K]`` -> Q8_0 raw bytes ``[..., K/32*34]``.
+
+    The published ggml/gguf-py Q8_0 rule: per block of 32, ``d = max|x| / 127``,
+    codes ``roundf(x * (1/d))`` (0 when d is 0) as int8, ``d`` stored as fp16.
+    All arithmetic in float32."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    if w.shape[-1] % Q8_0_BLOCK:
+        raise ValueError("last dimension must be a multiple of 32")
+    lead = w.shape[:-1]
+    b = w.reshape(-1, Q8_0_BLOCK)
+    d = np.abs(b).max(axis=-1, keepdims=True) / np.float32(127)
+    with np.errstate(divide="ignore"):
+        inv = np.where(d == 0, np.float32(0), np.float32(1) / d).astype(np.float32)
+    q = _round_half_away(b * inv).astype(np.int8)
+    out = np.concatenate([d.astype(np.float16).view(np.uint8).reshape(-1, 2), q.view(np.uint8)], axis=1)
+    return out.reshape(lead + (w.shape[-1] // Q8_0_BLOCK * Q8_0_BYTES,))
+
+
+def quantize_q5_0(w: np.ndarray) -> np.ndarray:
+    """float32 ``[..., K]`` -> Q5_0 raw bytes ``[..., K/32*22]``.
+
+    The published ggml/gguf-py Q5_0 rule: per block of 32 take the element of largest
+    magnitude (first on ties) with its sign, ``d = that / -16``; codes are
+    ``trunc(x * (1/d) + 16.5)`` clipped to 0..31; byte j packs the low four bits of
+    code j (low nibble) and of code j+16 (high nibble); bit j of the little-endian
+    uint32 ``qh`` is bit 4 of code j; ``d`` stored as fp16."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    if w.shape[-1] % Q5_0_BLOCK:
+        raise ValueError("last dimension must be a multiple of 32")
+    lead = w.shape[:-1]
+    b = w.reshape(-1, Q5_0_BLOCK)
+    imax = np.abs(b).argmax(axis=-1)[:, None]
+    vmax = np.take_along_axis(b, imax, axis=-1)
+    d = vmax / np.float32(-16)
+    with np.errstate(divide="ignore"):
+        inv = np.where(d == 0, np.float32(0), np.float32(1) / d).astype(np.float32)
+    q = np.clip(np.trunc(b * inv + np.float32(16.5)), 0, 31).astype(np.uint8)
+    ql = (q[:, :16] & 0x0F) | ((q[:, 16:] & 0x0F) << np.uint8(4))
+    qh = (((q >> 4) & 1).astype(np.uint32) << np.arange(32, dtype=np.uint32)[None, :]).sum(axis=1, dtype=np.uint32)
+    out = np.concatenate([d.astype(np.float16).view(np.uint8).reshape(-1, 2), qh.astype("<u4").view(np.uint8).reshape(-1, 4), ql], axis=1)
+    return out.reshape(lead + (w.shape[-1] // Q5_0_BLOCK * Q5_0_BYTES,))
 
 
 def pack_q4_k_scales(sc: np.ndarray, mn: np.ndarray) -> np.ndarray:
@@ -138,3 +198,26 @@ def random_q4_k_blocks(rng: np.random.Generator, rows: int, cols: int) -> np.nda
     out[:, 0:4] = dd.view(np.uint8).reshape(nb, 4)
     out[:, 4:] = rng.integers(0, 256, size=(nb, 140), dtype=np.uint8)
     return out.reshape(rows, cols // Q4_K_BLOCK * Q4_K_BYTES)
+
+
+def random_q8_0_blocks(rng: np.random.Generator, rows: int, cols: int) -> np.ndarray:
+    """Seeded synthetic Q8_0 matrix: per block ``d = fp16(|N(0,0.02)|/127)`` and 32 uniform
+    random bytes (codes uniform -128..127).  Returns ``[rows, cols/32*34]``."""
+    nb = rows * cols // Q8_0_BLOCK
+    d = (np.abs(rng.standard_normal(nb, dtype=np.float32)) * np.float32(0.02) / np.float32(127)).astype(np.float16)
+    out = np.empty((nb, Q8_0_BYTES), np.uint8)
+    out[:, :2] = d.view(np.uint8).reshape(nb, 2)
+    out[:, 2:] = rng.integers(0, 256, size=(nb, 32), dtype=np.uint8)
+    return out.reshape(rows, cols // Q8_0_BLOCK * Q8_0_BYTES)
+
+
+def random_q5_0_blocks(rng: np.random.Generator, rows: int, cols: int) -> np.ndarray:
+    """Seeded synthetic Q5_0 matrix: per block ``d = fp16(+-|N(0,0.02)|/16)`` (either sign, as
+    the encoder produces), 4 uniform high-bit bytes and 16 uniform nibble bytes.
+    Returns ``[rows, cols/32*22]``."""
+    nb = rows * cols // Q5_0_BLOCK
+    d = (rng.standard_normal(nb, dtype=np.float32) * np.float32(0.02) / np.float32(16)).astype(np.float16)
+    out = np.empty((nb, Q5_0_BYTES), np.uint8)
+    out[:, :2] = d.view(np.uint8).reshape(nb, 2)
+    out[:, 2:] = rng.integers(0, 256, size=(nb, 20), dtype=np.uint8)
+    return out.reshape(rows, cols // Q5_0_BLOCK * Q5_0_BYTES)

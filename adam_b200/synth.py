@@ -8,7 +8,7 @@ ids.  Tensor names follow the GGUF names the reference engine looks up
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Union
+from typing import Dict, Optional, Union
 
 import numpy as np
 
@@ -23,6 +23,7 @@ class QTensor:
     rows: int
     cols: int
     raw: np.ndarray            # uint8, rows * cols/block * block_bytes
+    file: Optional[tuple] = None   # (path, byte offset) when the blocks still lie in a GGUF file (raw is a view of its mapping)
 
     @property
     def shape(self):
@@ -56,7 +57,8 @@ _QUANT_CHUNK_ROWS = 4096
 def _quantize(w: np.ndarray, ggml_type: int) -> QTensor:
     """Encode a matrix; large ones in row chunks on a thread pool (the encoders are
     row-independent numpy code that releases the GIL, so the bytes do not depend on the split)."""
-    enc = gb.quantize_q4_0 if ggml_type == gb.GGML_TYPE_Q4_0 else gb.quantize_q4_k
+    enc = {gb.GGML_TYPE_Q4_0: gb.quantize_q4_0, gb.GGML_TYPE_Q4_K: gb.quantize_q4_k,
+           gb.GGML_TYPE_Q8_0: gb.quantize_q8_0, gb.GGML_TYPE_Q5_0: gb.quantize_q5_0}[ggml_type]
     rows = w.shape[0]
     if rows <= _QUANT_CHUNK_ROWS:
         raw = enc(w)
@@ -72,22 +74,23 @@ def _quantize(w: np.ndarray, ggml_type: int) -> QTensor:
 
 def build_model(cfg: ModelConfig, ggml_type: int = gb.GGML_TYPE_Q4_0, seed: int = 0,
                 tied: bool = True, norm_noise: float = 0.1, qk_norm: bool = True,
-                post_norms: bool = True) -> Dict[str, Tensor]:
+                post_norms: bool = True, embd_type: Optional[int] = None) -> Dict[str, Tensor]:
     """Random-init model on the host: N(0, 0.02) matrices quantized to
-    ``ggml_type``, norm weights ``1 + norm_noise * N(0,1)``."""
+    ``ggml_type``, norm weights ``1 + norm_noise * N(0,1)``.  ``embd_type`` stores
+    token_embd (and output.weight) in another block type, as real files do (Q8_0, Q5_0)."""
     rng = np.random.default_rng(seed)
 
-    def mat(rows, cols):
+    def mat(rows, cols, kind=None):
         w = rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02)
-        return _quantize(w, ggml_type)
+        return _quantize(w, ggml_type if kind is None else kind)
 
     def norm(n):
         return (np.float32(1) + np.float32(norm_noise) * rng.standard_normal(n, dtype=np.float32)).astype(np.float32)
 
     t: Dict[str, Tensor] = {}
-    t["token_embd.weight"] = mat(cfg.n_vocab, cfg.n_embd)
+    t["token_embd.weight"] = mat(cfg.n_vocab, cfg.n_embd, embd_type)
     if not tied:
-        t["output.weight"] = mat(cfg.n_vocab, cfg.n_embd)
+        t["output.weight"] = mat(cfg.n_vocab, cfg.n_embd, embd_type)
     t["output_norm.weight"] = norm(cfg.n_embd)
     shapes = mat_shapes(cfg)
     for L in range(cfg.n_layer):

@@ -169,20 +169,22 @@ def threads_used():
 # ---- GEMV bandwidth (the metric's second half; configs 1 and 4) ------------------------------------------
 
 GEMV_SWEEP = [(2, 6912, 1152, 1), (2, 1152, 6912, 1), (12, 5376, 5376, 1), (12, 21504, 5376, 1), (12, 5376, 21504, 1),
-              (12, 262144, 5376, 1), (12, 5376, 5376, 8), (12, 21504, 5376, 8), (12, 5376, 21504, 8), (12, 262144, 5376, 8)]
+              (12, 262144, 5376, 1), (12, 5376, 5376, 8), (12, 21504, 5376, 8), (12, 5376, 21504, 8), (12, 262144, 5376, 8),
+              (8, 262144, 1152, 1), (6, 262144, 1152, 1)]      # Q8_0 / Q5_0: the token-embedding / LM-head table of the 1B shape
+_BLOCK_NAME = {2: "Q4_0", 12: "Q4_K", 8: "Q8_0", 6: "Q5_0"}
 
 
 def _gemv_weights(gpu, A, t, N, K, copies, tile):
     from adam_b200 import gguf_blocks as gb
-    dt = A.DTYPE_GGUF_Q4_0 if t == 2 else A.DTYPE_GGUF_Q4_K
+    dt = A.GGUF_MAP_DTYPE[t]
     rng = np.random.default_rng(0)
     ru = min(N, 4096)
-    raw_u = (gb.random_q4_0_blocks if t == 2 else gb.random_q4_k_blocks)(rng, ru, K)
+    raw_u = {2: gb.random_q4_0_blocks, 12: gb.random_q4_k_blocks, 8: gb.random_q8_0_blocks, 6: gb.random_q5_0_blocks}[t](rng, ru, K)
     raw = np.tile(raw_u, (N // ru + 1, 1))[:N]
     gpu.map_create_typed(1, dt, 1, copies * N * K)
     for c in range(copies):
         gpu.upload_gguf_blocks(1, t, c * N * K, raw)
-        if tile and N % 16 == 0 and K % (64 if t == 2 else 256) == 0:
+        if tile and t in (2, 12) and N % 16 == 0 and K % (64 if t == 2 else 256) == 0:
             gpu.tile_tensor(1, c * N * K, N, K)
     return rng
 
@@ -191,7 +193,8 @@ def gemv_shape(gpu, A, t, N, K, B=1, target_bytes=600e6, reps=5, tile=True):
     """Cold-HBM bandwidth of y = W x for one shape: a CUDA graph whose launches walk over enough distinct
     copies of W to exceed L2, timed with CUDA events on the library stream (best of ``reps``); plus the warm
     (L2-resident) per-launch latency.  Algorithmic bytes = GGUF block bytes + fp32 x + fp32 y."""
-    wbytes = N * K * 0.5625
+    be, bb = {2: (32, 18), 12: (256, 144), 8: (32, 34), 6: (32, 22)}[t]
+    wbytes = N * K // be * bb
     copies = int(min(160, max(1, np.ceil(target_bytes / wbytes))))
     rng = _gemv_weights(gpu, A, t, N, K, copies, tile)
     gpu.map_create_typed(0, A.DTYPE_F32, 1, B * K + B * N + 8)
@@ -220,7 +223,8 @@ def gemv_shape(gpu, A, t, N, K, B=1, target_bytes=600e6, reps=5, tile=True):
     gpu.graph_launch(gid2, 2)
     gpu.batch_begin(); gpu.timer_begin(); gpu.graph_launch(gid2, 1); ms2 = gpu.timer_end(); gpu.batch_end()
     peak, _ = measured_peaks()
-    out = dict(type="Q4_0" if t == 2 else "Q4_K", kernel="tcgen05 GEMM" if tc_path else ("tensor-core GEMV (tiled)" if tile else "CUDA-core GEMV"),
+    kernel = "tcgen05 GEMM" if tc_path else ("CUDA-core GEMV (planes)" if t in (8, 6) else "tensor-core GEMV (tiled)" if tile else "CUDA-core GEMV")
+    out = dict(type=_BLOCK_NAME[t], kernel=kernel,
                N=N, K=K, B=B, copies=copies, bytes_per_launch=int(alg), us_per_launch=round(best * 1e3 / copies, 3), GBs=round(gbs, 1),
                frac_of_measured=round(gbs / peak, 3), frac_of_8TBs=round(gbs / 8000, 3), warm_us_per_launch=round(ms2 * 1e3 / 20, 3))
     gpu.graph_destroy(gid); gpu.graph_destroy(gid2)

@@ -41,6 +41,8 @@ extern "C" {
 #define ADAMAH_DTYPE_Q4        3    /* nibbles, 8 per uint32, + f32 (scale,zero) per group */
 #define ADAMAH_DTYPE_GGUF_Q4_0 16   /* extension: 18-byte GGUF blocks of 32 */
 #define ADAMAH_DTYPE_GGUF_Q4_K 17   /* extension: 144-byte GGUF superblocks of 256 */
+#define ADAMAH_DTYPE_GGUF_Q8_0 18   /* extension: 34-byte GGUF blocks of 32 (int8 codes) */
+#define ADAMAH_DTYPE_GGUF_Q5_0 19   /* extension: 22-byte GGUF blocks of 32 (5-bit codes) */
 
 /* ======================= Part 1: reference-compatible ====================== */
 
@@ -158,6 +160,16 @@ int map_matvec_argmax_t_xq4_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h,
                                 uint32_t idx_tmp_h, uint32_t val_tmp_h, uint32_t dst_h,
                                 uint32_t K, uint32_t N, uint32_t rows_per_group);
 
+/* 8-bit weight operators: adamah.c:9834 (map_matmul_t_xq8_dev), :10189 (map_row_gather_xq8_dev).  The weight map is a
+ * GGUF-block map of Q8_0 or Q5_0 blocks (ADAMAH_DTYPE_GGUF_Q8_0 / _Q5_0) instead of the reference's byte map with a
+ * (scale, zero) pair per 32.  map_matmul_t_xq8_dev: C[M,N] = A[M,K] * W[N,K]^T.  map_row_gather_xq8_dev: the row
+ * row_idx of length row_size starting at element src_base of the weight map, decoded and multiplied by scale, to
+ * element dst_base of the activation map (bases and row index are immediates). */
+int map_matmul_t_xq8_dev(uint32_t map_act, uint32_t map_wt, uint32_t a_h, uint32_t b_h, uint32_t c_h,
+                         uint32_t M, uint32_t K, uint32_t N, uint32_t n_ops);
+int map_row_gather_xq8_dev(uint32_t map_act, uint32_t map_wt, uint32_t src_base, uint32_t dst_base,
+                           uint32_t row_idx, uint32_t row_size, float scale);
+
 /* decode plan: adamah.c:175-194 (struct), :10341, :10367, :10361 */
 typedef struct AdamahDecodePlanOp {
     uint32_t kind, map_id, map_id2, op_code;
@@ -172,7 +184,7 @@ int  adamah_decode_step(uint32_t plan_id, uint32_t pos, uint32_t seq_len);
 void adamah_clear_decode_plan(uint32_t plan_id);
 
 /* Symbols the reference binding resolves without a guard but which lie off the
- * decode path (generic tensor ops, Q8 storage).  They exist so the binding
+ * decode path (generic tensor ops, untransposed 8-bit products).  They exist so the binding
  * loads, and return ADAMAH_ERR_INVALID.  adamah-MAIN/adamah/__init__.py:530-960. */
 int map_op1(uint32_t, uint32_t, const uint32_t*, const uint32_t*, uint32_t);
 int map_op2(uint32_t, uint32_t, const uint32_t*, const uint32_t*, const uint32_t*, uint32_t);
@@ -191,9 +203,7 @@ int map_fma_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
 int map_matmul_t_x_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
 int map_matmul_x_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
 int map_matmul_xq4_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
-int map_matmul_t_xq8_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
 int map_matmul_xq8_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
-int map_row_gather_xq8_dev(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t);
 
 /* ============================ Part 2: extensions =========================== */
 
@@ -224,19 +234,25 @@ int adam_b200_capture_end(uint32_t* graph_id);
 int adam_b200_graph_launch(uint32_t graph_id, uint32_t times);
 int adam_b200_graph_destroy(uint32_t graph_id);
 
-/* Copy raw GGUF blocks (ggml_type 2 = Q4_0, 12 = Q4_K) into a GGUF-block map at
+/* Copy raw GGUF blocks (ggml_type 2 = Q4_0, 12 = Q4_K, 8 = Q8_0, 6 = Q5_0) into a GGUF-block map of the matching dtype at
  * element offset elem_off (a multiple of the block size).  `raw` may be a host
  * or a device pointer.  Replaces the reference's Python re-quantization at load
  * (adam/models/engine.py:974-1116); op signatures are unchanged -- weight handles
  * still carry element offsets. */
 int map_upload_gguf_blocks(uint32_t map_wt, uint32_t ggml_type, uint64_t elem_off, const void* raw, uint64_t n_bytes);
+/* The same placement with the blocks read from a file: n_bytes starting at file_offset of `path` (a tensor's
+ * data inside a .gguf file) stream through two pinned 32 MB buffers, one cudaMemcpyAsync per chunk, the read of
+ * the next chunk overlapping the copy of the current one.  Replaces adam/loaders/gguf.py:196-253
+ * (load_tensor_raw / iter_tensor_chunks) + the upload loops of adam/models/engine.py:929-1116. */
+int adam_b200_upload_gguf_file(uint32_t map_wt, uint32_t ggml_type, uint64_t elem_off, const char* path,
+                               uint64_t file_offset, uint64_t n_bytes);
 /* Build and register a row-tiled copy of the [rows, cols] Q4_0 tensor at elem_off of a
  * GGUF Q4_0 map (rows % 16 == 0, cols % 64 == 0).  Later GEMV / arg-max calls on exactly
  * that tensor run the tensor-core kernel on the copy; results stay within the same
  * tolerance.  Costs one extra copy of the tensor's bytes; freed with the map. */
 int adam_b200_tensor_tile(uint32_t map_wt, uint64_t elem_off, uint32_t rows, uint32_t cols);
 /* Decode n_elems weights starting at elem_off of a GGUF-block or Q4 map to
- * float32 (host pointer `out`); bit-exact w.r.t. adam/loaders/gguf.py:290-337. */
+ * float32 (host pointer `out`); bit-exact w.r.t. adam/loaders/gguf.py:282-337. */
 int map_dequant_gguf(uint32_t map_wt, uint64_t elem_off, float* out, uint64_t n_elems);
 /* Quantize float32 rows (device pointer, n_elems multiple of 32) to raw Q4_0
  * blocks (device pointer) with the ggml rule; load-time helper for synthetic

@@ -36,7 +36,7 @@ def lib():
 def dequant(raw: np.ndarray, ggml_type: int, rows: int, cols: int) -> np.ndarray:
     """Threaded block decode, bit-identical to ``oracle.q4_blocks.dequant``."""
     raw = np.ascontiguousarray(raw, np.uint8).reshape(-1)
-    be, bb = (32, 18) if ggml_type == 2 else (256, 144)
+    be, bb = {2: (32, 18), 12: (256, 144), 8: (32, 34), 6: (32, 22)}[ggml_type]
     nb = rows * cols // be
     assert raw.size == nb * bb
     out = np.empty(rows * cols, np.float32)

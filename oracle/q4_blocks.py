@@ -15,6 +15,10 @@ Q4_0_BLOCK = 32
 Q4_0_BYTES = 18
 Q4_K_BLOCK = 256
 Q4_K_BYTES = 144
+Q8_0_BLOCK = 32
+Q8_0_BYTES = 34
+Q5_0_BLOCK = 32
+Q5_0_BYTES = 22
 
 
 def _as_u8(raw) -> np.ndarray:
@@ -97,12 +101,59 @@ def dequant_q4_k(raw, n_elems: int | None = None) -> np.ndarray:
     return out
 
 
+def dequant_q8_0(raw, n_elems: int | None = None) -> np.ndarray:
+    """GGUF Q8_0 -> float32, flat, logical order.
+
+    Restates ``GGUFLoader._dq8`` (adam/loaders/gguf.py:282-288): a 34-byte block
+    is an fp16 scale ``d`` followed by 32 int8 codes; element ``j`` is
+    ``float32(q_j) * float32(d)`` (exact in float32: 8 + 11 significant bits).
+    """
+    a = _as_u8(raw)
+    if a.size % Q8_0_BYTES:
+        raise ValueError("Q8_0 byte count must be a multiple of 34")
+    blk = a.reshape(-1, Q8_0_BYTES)
+    d = blk[:, :2].copy().view(np.float16).astype(np.float32)          # [nb,1]
+    q = blk[:, 2:].view(np.int8).astype(np.float32)
+    out = (q * d).reshape(-1)
+    if n_elems is not None and n_elems != out.size:
+        raise ValueError("n_elems does not match the block count")
+    return out
+
+
+def dequant_q5_0(raw, n_elems: int | None = None) -> np.ndarray:
+    """GGUF Q5_0 -> float32, flat, logical order.
+
+    Restates ``GGUFLoader._dq5_0`` (adam/loaders/gguf.py:301-310): a 22-byte
+    block is an fp16 scale ``d``, a little-endian uint32 ``qh`` and 16 nibble
+    bytes; element ``j`` has the low nibble of byte ``j`` (j < 16) or the high
+    nibble of byte ``j-16`` as its low four bits and bit ``j`` of ``qh`` as bit 4;
+    value = ``d * (code - 16)`` (exact in float32).
+    """
+    a = _as_u8(raw)
+    if a.size % Q5_0_BYTES:
+        raise ValueError("Q5_0 byte count must be a multiple of 22")
+    blk = a.reshape(-1, Q5_0_BYTES)
+    d = blk[:, :2].copy().view(np.float16).astype(np.float32)          # [nb,1]
+    qh = blk[:, 2:6].copy().view("<u4")                                 # [nb,1]
+    ql = blk[:, 6:]
+    lo = np.concatenate([ql & 0x0F, (ql >> 4) & 0x0F], axis=1).astype(np.int32)
+    hi = ((qh >> np.arange(32, dtype=np.uint32)[None, :]) & 1).astype(np.int32)
+    out = (d * ((lo | (hi << 4)) - 16).astype(np.float32)).reshape(-1)
+    if n_elems is not None and n_elems != out.size:
+        raise ValueError("n_elems does not match the block count")
+    return out
+
+
 def dequant(raw, ggml_type: int, rows: int, cols: int) -> np.ndarray:
-    """Decode a ``[rows, cols]`` tensor stored as GGUF blocks (type 2 or 12)."""
+    """Decode a ``[rows, cols]`` tensor stored as GGUF blocks (type 2, 12, 8 or 6)."""
     if ggml_type == 2:
         return dequant_q4_0(raw, rows * cols).reshape(rows, cols)
     if ggml_type == 12:
         return dequant_q4_k(raw, rows * cols).reshape(rows, cols)
+    if ggml_type == 8:
+        return dequant_q8_0(raw, rows * cols).reshape(rows, cols)
+    if ggml_type == 6:
+        return dequant_q5_0(raw, rows * cols).reshape(rows, cols)
     raise ValueError(f"unsupported ggml type {ggml_type}")
 
 

@@ -1,10 +1,12 @@
 /*
- * Plain-C restatement of the reference's GGUF Q4_0 / Q4_K block decode and of the
- * mat-vec built on it.  TEST INFRASTRUCTURE: used only by tests/, the smoke check
+ * Plain-C restatement of the reference's GGUF Q4_0 / Q4_K / Q8_0 / Q5_0 block decode and
+ * of the mat-vec built on it.  TEST INFRASTRUCTURE: used only by tests/, the smoke check
  * and the CPU-baseline legs of bench.py (see oracle/__init__.py).
  *
  * q4_0: adam/loaders/gguf.py:290-299 (GGUFLoader._dq4_0)
  * q4_k: adam/loaders/gguf.py:312-337 (GGUFLoader._dq4k), scale unpack :325-328
+ * q8_0: adam/loaders/gguf.py:282-288 (GGUFLoader._dq8)
+ * q5_0: adam/loaders/gguf.py:301-310 (GGUFLoader._dq5_0)
  * gemv: y = W x with W decoded to float32 first and a float32 dot product per row,
  *       as the reference's numpy decoder does after pre-decoding the weights
  *       (tests/diagnostics/diag_inference.py:966-969, :985-987).
@@ -108,32 +110,65 @@ static void dq4_k_block(const uint8_t* b, float* out) {
     }
 }
 
-typedef struct { const uint8_t* raw; int type; float* out; } deq_ctx;
-static void deq_range(int64_t lo, int64_t hi, void* p) {
-    deq_ctx* c = (deq_ctx*)p;
-    if (c->type == 2) for (int64_t i = lo; i < hi; ++i) dq4_0_block(c->raw + i * 18, c->out + i * 32);
-    else for (int64_t i = lo; i < hi; ++i) dq4_k_block(c->raw + i * 144, c->out + i * 256);
+/* GGUFLoader._dq8 (adam/loaders/gguf.py:282-288): fp16 d, 32 int8 codes; value = q * d. */
+static void dq8_0_block(const uint8_t* b, float* out) {
+    uint16_t h;
+    memcpy(&h, b, 2);
+    const float d = half_to_float(h);
+    for (int j = 0; j < 32; ++j) out[j] = (float)(int8_t)b[2 + j] * d;
 }
 
-/* Decode n_blocks blocks of ggml type 2 (Q4_0) or 12 (Q4_K) to float32. */
+/* GGUFLoader._dq5_0 (adam/loaders/gguf.py:301-310): fp16 d, uint32 qh, 16 nibble bytes;
+ * code j = nibble | bit j of qh << 4; value = d * (code - 16). */
+static void dq5_0_block(const uint8_t* b, float* out) {
+    uint16_t h;
+    uint32_t qh;
+    memcpy(&h, b, 2);
+    memcpy(&qh, b + 2, 4);
+    const float d = half_to_float(h);
+    for (int j = 0; j < 32; ++j) {
+        const int lo = j < 16 ? (b[6 + j] & 0x0F) : (b[6 + j - 16] >> 4);
+        const int hi = (int)((qh >> j) & 1u);
+        out[j] = d * (float)((lo | (hi << 4)) - 16);
+    }
+}
+
+/* Block geometry and decoder of a ggml type: 2 Q4_0, 12 Q4_K, 8 Q8_0, 6 Q5_0. */
+typedef void (*block_fn)(const uint8_t*, float*);
+static int block_kind(int type, int64_t* elems, int64_t* bytes, block_fn* fn) {
+    switch (type) {
+    case 2:  *elems = 32;  *bytes = 18;  *fn = dq4_0_block; return 0;
+    case 12: *elems = 256; *bytes = 144; *fn = dq4_k_block; return 0;
+    case 8:  *elems = 32;  *bytes = 34;  *fn = dq8_0_block; return 0;
+    case 6:  *elems = 32;  *bytes = 22;  *fn = dq5_0_block; return 0;
+    default: return -1;
+    }
+}
+
+typedef struct { const uint8_t* raw; int64_t be, bb; block_fn fn; float* out; } deq_ctx;
+static void deq_range(int64_t lo, int64_t hi, void* p) {
+    deq_ctx* c = (deq_ctx*)p;
+    for (int64_t i = lo; i < hi; ++i) c->fn(c->raw + i * c->bb, c->out + i * c->be);
+}
+
+/* Decode n_blocks blocks of a supported ggml type to float32. */
 int q4_dequant(const uint8_t* raw, int ggml_type, int64_t n_blocks, float* out) {
-    if (ggml_type != 2 && ggml_type != 12) return -1;
-    deq_ctx c = {raw, ggml_type, out};
+    deq_ctx c = {raw, 0, 0, NULL, out};
+    if (block_kind(ggml_type, &c.be, &c.bb, &c.fn)) return -1;
     parallel_for(n_blocks, deq_range, &c);
     return 0;
 }
 
-typedef struct { const uint8_t* raw; int type; int64_t N, K, B; const float* x; float* y; } gemv_ctx;
+typedef struct { const uint8_t* raw; int64_t be, bb; block_fn fn; int64_t N, K, B; const float* x; float* y; double* y64; } gemv_ctx;
 static void gemv_range(int64_t lo, int64_t hi, void* p) {
     gemv_ctx* c = (gemv_ctx*)p;
-    const int64_t be = c->type == 2 ? 32 : 256, bb = c->type == 2 ? 18 : 144, nb = c->K / be;
+    const int64_t be = c->be, nb = c->K / be;
     for (int64_t n = lo; n < hi; ++n) {
         float acc[64];
         float w[256];
         for (int64_t b = 0; b < c->B; ++b) acc[b] = 0.0f;
         for (int64_t i = 0; i < nb; ++i) {
-            const uint8_t* blk = c->raw + (n * nb + i) * bb;
-            if (c->type == 2) dq4_0_block(blk, w); else dq4_k_block(blk, w);
+            c->fn(c->raw + (n * nb + i) * c->bb, w);
             for (int64_t b = 0; b < c->B; ++b) {
                 const float* xb = c->x + b * c->K + i * be;
                 float s = acc[b];
@@ -147,17 +182,15 @@ static void gemv_range(int64_t lo, int64_t hi, void* p) {
 
 /* The same product with every term and the sum in double: a reference whose own rounding
  * error is negligible beside the 1e-3 tolerance, for long rows (K of tens of thousands). */
-typedef struct { const uint8_t* raw; int type; int64_t N, K, B; const float* x; double* y; } gemv64_ctx;
 static void gemv64_range(int64_t lo, int64_t hi, void* p) {
-    gemv64_ctx* c = (gemv64_ctx*)p;
-    const int64_t be = c->type == 2 ? 32 : 256, bb = c->type == 2 ? 18 : 144, nb = c->K / be;
+    gemv_ctx* c = (gemv_ctx*)p;
+    const int64_t be = c->be, nb = c->K / be;
     for (int64_t n = lo; n < hi; ++n) {
         double acc[64];
         float w[256];
         for (int64_t b = 0; b < c->B; ++b) acc[b] = 0.0;
         for (int64_t i = 0; i < nb; ++i) {
-            const uint8_t* blk = c->raw + (n * nb + i) * bb;
-            if (c->type == 2) dq4_0_block(blk, w); else dq4_k_block(blk, w);
+            c->fn(c->raw + (n * nb + i) * c->bb, w);
             for (int64_t b = 0; b < c->B; ++b) {
                 const float* xb = c->x + b * c->K + i * be;
                 double s = acc[b];
@@ -165,13 +198,12 @@ static void gemv64_range(int64_t lo, int64_t hi, void* p) {
                 acc[b] = s;
             }
         }
-        for (int64_t b = 0; b < c->B; ++b) c->y[b * c->N + n] = acc[b];
+        for (int64_t b = 0; b < c->B; ++b) c->y64[b * c->N + n] = acc[b];
     }
 }
 int q4_gemv_f64(const uint8_t* raw, int ggml_type, int64_t N, int64_t K, const float* x, int64_t B, double* y) {
-    const int64_t be = ggml_type == 2 ? 32 : 256;
-    if ((ggml_type != 2 && ggml_type != 12) || K % be || B < 1 || B > 64) return -1;
-    gemv64_ctx c = {raw, ggml_type, N, K, B, x, y};
+    gemv_ctx c = {raw, 0, 0, NULL, N, K, B, x, NULL, y};
+    if (block_kind(ggml_type, &c.be, &c.bb, &c.fn) || K % c.be || B < 1 || B > 64) return -1;
     parallel_for(N, gemv64_range, &c);
     return 0;
 }
@@ -179,9 +211,8 @@ int q4_gemv_f64(const uint8_t* raw, int ggml_type, int64_t N, int64_t K, const f
 /* y[b][n] = sum_k W[n][k] x[b][k], rows decoded on the fly, float32 accumulation in
  * index order.  x is [B][K], y is [B][N], B <= 64. */
 int q4_gemv(const uint8_t* raw, int ggml_type, int64_t N, int64_t K, const float* x, int64_t B, float* y) {
-    const int64_t be = ggml_type == 2 ? 32 : 256;
-    if ((ggml_type != 2 && ggml_type != 12) || K % be || B < 1 || B > 64) return -1;
-    gemv_ctx c = {raw, ggml_type, N, K, B, x, y};
+    gemv_ctx c = {raw, 0, 0, NULL, N, K, B, x, y, NULL};
+    if (block_kind(ggml_type, &c.be, &c.bb, &c.fn) || K % c.be || B < 1 || B > 64) return -1;
     parallel_for(N, gemv_range, &c);
     return 0;
 }

@@ -29,6 +29,16 @@ reference tree is not needed when the tests run.  What each file pins:
                           file records the smallest gap between the best and the second-best logit
                           along the decoded path (from the numpy restatement, whose ids must equal the
                           reference's), so a reader can see how well-conditioned the arg-max is.
+``q8_q5_blocks.npz``      (``--blocks8``) raw Q8_0 / Q5_0 blocks (seeded, plus edge-case scales and codes)
+                          with the float32 output of ``GGUFLoader._dq8`` / ``_dq5_0``
+                          (adam/loaders/gguf.py:282-288, :301-310), asserted equal to ``gguf.dequantize``;
+                          and float32 rows with the bytes ``gguf.quants.quantize`` makes of them, pinning
+                          ``adam_b200.gguf_blocks.quantize_q8_0`` / ``quantize_q5_0``.
+``tiny.gguf``,            (``--gguf``) a small Gemma-3-shaped model file written with ``gguf.GGUFWriter``
+``gguf_file.npz``         (Q4_0 layers, Q8_0 token_embd, float32 norms) and what the reference's
+                          ``GGUFLoader.load`` and ``ModelConfig.from_gguf_metadata`` read from it
+                          (adam/loaders/gguf.py:58-133, adam/models/engine.py:56-111): metadata, tensor
+                          names, types, shapes, offsets, the data offset and the configuration.
 """
 import argparse
 import hashlib
@@ -58,6 +68,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("ADAM_REFERENCE_DIR", ""))
     ap.add_argument("--full-size", action="store_true", help="write decode_1b.npz (1B-shape model) instead of the small fixtures")
+    ap.add_argument("--blocks8", action="store_true", help="write q8_q5_blocks.npz only")
+    ap.add_argument("--gguf", action="store_true", help="write tiny.gguf and gguf_file.npz only")
     args = ap.parse_args()
     ref = args.reference
     if not ref or not os.path.isdir(ref):
@@ -77,6 +89,10 @@ def main():
 
     if args.full_size:
         return full_size(ref, gguf, T, RefModelConfig)
+    if args.blocks8:
+        return blocks8(gguf, T, GGUFLoader)
+    if args.gguf:
+        return gguf_file(gguf, T, GGUFLoader, RefModelConfig)
 
     loader = GGUFLoader.__new__(GGUFLoader)
     rng = np.random.default_rng(20240601)
@@ -166,6 +182,110 @@ def main():
         out[f"{name}_sha256"] = np.frombuffer(h.digest(), np.uint8)
     np.savez_compressed(os.path.join(HERE, "decode_tiny.npz"), **out)
     print("fixtures written to", HERE)
+
+
+def blocks8(gguf, T, GGUFLoader):
+    """Q8_0 / Q5_0: the reference loader's own decode of seeded blocks, and gguf's encoders."""
+    from adam_b200 import gguf_blocks as gb
+    loader = GGUFLoader.__new__(GGUFLoader)
+    rng = np.random.default_rng(20240602)
+    edge = [0x0000, 0x8000, 0x0001, 0x83FF, 0x7BFF, 0xFBFF, 0x3C00, 0xBC00]     # zero, -0, subnormals, largest finite, +-1
+    q8 = gb.random_q8_0_blocks(rng, 16, 128).reshape(-1, 34).copy()
+    q5 = gb.random_q5_0_blocks(rng, 16, 128).reshape(-1, 22).copy()
+    for i, bits in enumerate(edge):
+        q8[i, 0], q8[i, 1] = bits & 0xFF, bits >> 8
+        q5[i, 0], q5[i, 1] = bits & 0xFF, bits >> 8
+    q8[8, 2:] = 0x80; q8[9, 2:] = 0x7F; q8[10, 2:] = 0x00; q8[11, 2:] = 0xFF          # codes -128, 127, 0, -1
+    q5[8, 2:] = 0x00; q5[9, 2:] = 0xFF; q5[10, 2:6] = 0xFF; q5[10, 6:] = 0x00; q5[11, 2:6] = 0x00; q5[11, 6:] = 0xFF
+    q8_out = loader._dq8(q8.tobytes(), q8.shape[0] * 32)
+    q5_out = loader._dq5_0(q5.tobytes(), q5.shape[0] * 32)
+    for raw, out, t in ((q8, q8_out, T.Q8_0), (q5, q5_out, T.Q5_0)):
+        lib = gguf.dequantize(raw.reshape(1, -1), t).reshape(-1)
+        assert np.array_equal(out.view(np.uint32), lib.view(np.uint32)), t
+    w = (rng.standard_normal((24, 128), dtype=np.float32) * np.float32(0.02))
+    w[0, :32] = 0.0                                   # all-zero block (d == 0)
+    w[1, :32] = np.float32(0.01)                      # constant block
+    w[2, 5] = np.float32(-0.3)                        # negative extreme
+    w[3, 7] = np.float32(0.3); w[3, 9] = np.float32(-0.3)      # tie in magnitude: the first wins
+    w[4, :32] = np.float32(0.005) * (np.arange(32, dtype=np.float32) - np.float32(15.5))   # codes on .5 boundaries
+    raw8 = gguf.quants.quantize(w, T.Q8_0)
+    raw5 = gguf.quants.quantize(w, T.Q5_0)
+    assert np.array_equal(gb.quantize_q8_0(w), raw8) and np.array_equal(gb.quantize_q5_0(w), raw5)
+    np.savez_compressed(os.path.join(HERE, "q8_q5_blocks.npz"), q8_0_raw=q8, q8_0_out=q8_out, q5_0_raw=q5, q5_0_out=q5_out,
+                        w=w, q8_0_enc=raw8, q5_0_enc=raw5)
+    print("q8_q5_blocks.npz written")
+
+
+# the model of tiny.gguf: adam_b200.synth.build_model(GGUF_FILE_CFG(), Q4_0, embd_type=Q8_0, **GGUF_FILE_BUILD)
+GGUF_FILE_BUILD = dict(seed=31, tied=True)
+
+
+def GGUF_FILE_CFG():
+    from adam_b200.config import tiny_gemma3
+    return tiny_gemma3(n_layer=2, n_embd=64, n_head=2, n_head_kv=1, head_dim=32, n_ff=128, n_vocab=96, sliding_window=16)
+
+
+def write_model_gguf(path, cfg, tensors, gguf, extra_kv=None):
+    """Write ``tensors`` (QTensor / float32 arrays, GGUF names) and the metadata the reference reads as a .gguf
+    file with ``gguf.GGUFWriter``."""
+    w = gguf.GGUFWriter(path, cfg.arch)
+    w.add_name("tiny synthetic model")
+    w.add_context_length(cfg.n_ctx)
+    w.add_block_count(cfg.n_layer)
+    w.add_embedding_length(cfg.n_embd)
+    w.add_feed_forward_length(cfg.n_ff)
+    w.add_head_count(cfg.n_head)
+    w.add_head_count_kv(cfg.n_head_kv)
+    w.add_layer_norm_rms_eps(cfg.norm_eps)
+    w.add_vocab_size(cfg.n_vocab)
+    w.add_sliding_window(cfg.sliding_window)
+    w.add_rope_freq_base(cfg.rope_base_global)
+    w.add_float32(f"{cfg.arch}.rope.local_freq_base", cfg.rope_base_local)
+    w.add_key_length(cfg.head_dim)
+    w.add_value_length(cfg.head_dim_kv)
+    w.add_token_list([f"<t{i}>" for i in range(cfg.n_vocab)])
+    w.add_token_scores([float(-i) for i in range(cfg.n_vocab)])
+    w.add_bos_token_id(2)
+    w.add_eos_token_id(1)
+    for k, v in (extra_kv or {}).items():
+        w.add_string(k, v) if isinstance(v, str) else w.add_uint32(k, v)
+    for name, t in tensors.items():
+        if isinstance(t, np.ndarray):
+            w.add_tensor(name, np.ascontiguousarray(t, np.float32))
+        else:
+            w.add_tensor(name, np.ascontiguousarray(t.raw).reshape(t.rows, -1), raw_dtype=gguf.GGMLQuantizationType(t.ggml_type))
+    w.write_header_to_file()
+    w.write_kv_data_to_file()
+    w.write_tensors_to_file()
+    w.close()
+
+
+def gguf_file(gguf, T, GGUFLoader, RefModelConfig):
+    """tiny.gguf and what the reference's loader and configuration reader make of it."""
+    import json
+    from dataclasses import asdict
+    from adam_b200 import gguf_blocks as gb
+    from adam_b200 import synth
+    cfg = GGUF_FILE_CFG()
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, embd_type=gb.GGML_TYPE_Q8_0, **GGUF_FILE_BUILD)
+    path = os.path.join(HERE, "tiny.gguf")
+    write_model_gguf(path, cfg, tensors, gguf, extra_kv={"general.alignment": 32})
+    ld = GGUFLoader(path, keep_tensors=False, keep_raw_blocks=False)
+    with contextlib.redirect_stdout(io.StringIO()):
+        ld.load(verbose=False)
+        rcfg = RefModelConfig.from_gguf_metadata(ld.metadata, verbose=False)
+    names = [ti.name for ti in ld.tensor_infos]
+    raw0 = ld.load_tensor_raw("blk.1.ffn_down.weight")
+    np.savez_compressed(
+        os.path.join(HERE, "gguf_file.npz"),
+        metadata_json=np.array(json.dumps(ld.metadata, sort_keys=True)),
+        names=np.array(names), types=np.array([ti.dtype for ti in ld.tensor_infos], np.int64),
+        offsets=np.array([ti.offset for ti in ld.tensor_infos], np.int64),
+        shapes_json=np.array(json.dumps({n: list(ld.tensor_shapes[n]) for n in names})),
+        data_offset=np.int64(ld._data_offset), raw_bytes=np.int64(ld.estimate_raw_bytes()), f32_bytes=np.int64(ld.estimate_f32_bytes()),
+        ffn_down_1_sha256=np.frombuffer(hashlib.sha256(raw0).digest(), np.uint8),
+        config_json=np.array(json.dumps({k: v for k, v in asdict(rcfg).items()}, sort_keys=True)))
+    print("tiny.gguf", os.path.getsize(path), "bytes; gguf_file.npz written")
 
 
 # the full-size decode cases: (name, build kwargs, n_prompt, n_gen); the model is

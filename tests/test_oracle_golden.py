@@ -37,6 +37,24 @@ def test_q4_0_encoder_matches_gguf(golden_dir):
     assert np.array_equal(gb.quantize_q4_0(g["w"]), g["raw"])
 
 
+@pytest.mark.parametrize("kind", ["q8_0", "q5_0"])
+def test_q8_0_q5_0_decode_bit_exact(golden_dir, kind):
+    """adam/loaders/gguf.py:282-288 (_dq8), :301-310 (_dq5_0): numpy and C restatements against the reference's output."""
+    from oracle import cref
+    g = np.load(os.path.join(golden_dir, "q8_q5_blocks.npz"))
+    raw, want = g[f"{kind}_raw"], g[f"{kind}_out"]
+    dec = q4_blocks.dequant_q8_0 if kind == "q8_0" else q4_blocks.dequant_q5_0
+    with np.errstate(invalid="ignore", over="ignore"):
+        assert _bits_equal(dec(raw), want)
+        assert _bits_equal(cref.dequant(raw, 8 if kind == "q8_0" else 6, raw.shape[0], 32).reshape(-1), want)
+
+
+def test_q8_0_q5_0_encoders_match_gguf(golden_dir):
+    g = np.load(os.path.join(golden_dir, "q8_q5_blocks.npz"))
+    assert np.array_equal(gb.quantize_q8_0(g["w"]), g["q8_0_enc"])
+    assert np.array_equal(gb.quantize_q5_0(g["w"]), g["q5_0_enc"])
+
+
 def test_q4_k_scale_pack_roundtrip():
     rng = np.random.default_rng(3)
     sc = rng.integers(0, 64, (50, 8), dtype=np.uint8)
