@@ -145,6 +145,7 @@ _SIGS = {
     "map_matmul_t_xq8_dev": (c_int, [u32, u32, u32, u32, u32, u32, u32, u32, u32]),
     "map_row_gather_xq8_dev": (c_int, [u32, u32, u32, u32, u32, u32, f32]),
     "map_upload_gguf_blocks": (c_int, [u32, u32, u64, c_void_p, u64]),
+    "adam_b200_decode_plan_info": (c_int, [u32, POINTER(u32)]),
     "adam_b200_upload_gguf_file": (c_int, [u32, u32, u64, ctypes.c_char_p, u64, u64]),
     "map_dequant_gguf": (c_int, [u32, u64, c_void_p, u64]),
     "adam_b200_tensor_tile": (c_int, [u32, u64, u32, u32]),

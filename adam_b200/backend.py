@@ -429,6 +429,14 @@ class Adamah:
     def decode_step(self, plan_id: int, pos: int, seq_len: int):
         self._check(self._lib.adamah_decode_step(plan_id, pos, seq_len), "adamah_decode_step")
 
+    def decode_plan_info(self, plan_id: int) -> dict:
+        """How a registered plan runs: as one CUDA graph with device-side pos / seq_len, or by host substitution."""
+        out = (ctypes.c_uint32 * 6)()
+        self._check(self._lib.adam_b200_decode_plan_info(plan_id, out), "adam_b200_decode_plan_info")
+        state = ctypes.c_int32(out[0]).value
+        return dict(state=state, runs_as_graph=state == 2, cap=int(out[1]), graph_kernels=int(out[2]), recordings=int(out[3]),
+                    graph_steps=int(out[4]), host_steps=int(out[5]))
+
     # ---- GGUF-block maps (extension) ---------------------------------------------------
     def upload_gguf_blocks(self, map_id: int, ggml_type: int, elem_off: int, raw, n_bytes: Optional[int] = None):
         """Raw GGUF blocks (numpy uint8 array, or a device pointer given as int

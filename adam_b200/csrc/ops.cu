@@ -10,19 +10,31 @@
 #include "blocks8.cuh"
 
 #include <cstring>
+#include <initializer_list>
 
 namespace ab {
 
 #define OOB(idx, n, err) if ((uint64_t)(idx) >= (n)) { atomicOr((err), DEVERR_OOB_MAP); return; }
+
+// Decode-plan runtime arguments.  While a registered plan is lowered to a CUDA graph, an argument that holds one of the
+// two sentinels (ADAMAH_DECODE_RUNTIME_POS / _SEQ_LEN) is handed to its kernel as it is, together with `rt`, the
+// device address of {pos, seq_len}; the kernel resolves it when it runs, so one instantiated graph serves every step.
+// rt == NULL: immediate call, values are what they say.
+__device__ __forceinline__ uint32_t rtv(uint32_t v, const uint32_t* __restrict__ rt) {
+    if (!rt) return v;
+    return v == ADAMAH_DECODE_RUNTIME_POS ? rt[0] : (v == ADAMAH_DECODE_RUNTIME_SEQ_LEN ? rt[1] : v);
+}
+__global__ void k_set_runtime(uint32_t* rt, uint32_t pos, uint32_t seq_len) { rt[0] = pos; rt[1] = seq_len; }
 
 // dst = (x / sqrt(mean(x^2) + eps)) * w  [+ resid]; one CTA per row.
 // map_rmsnorm.comp / map_rmsnorm_x.comp / map_rmsnorm_add.comp.
 __global__ void k_rmsnorm(float* __restrict__ act, uint64_t n_act, const float* __restrict__ wt, uint64_t n_wt,
                           const uint32_t* __restrict__ l_src, const uint32_t* __restrict__ l_wt,
                           const uint32_t* __restrict__ l_res, const uint32_t* __restrict__ l_dst,
-                          uint32_t dim, float eps, uint32_t* err) {
+                          uint32_t dim, float eps, uint32_t* err, uint32_t n_rows, const uint32_t* __restrict__ rt) {
     __shared__ float red[33];
     const uint32_t r = blockIdx.x;
+    if (r >= rtv(n_rows, rt)) return;
     const uint64_t sb = l_src[r], wb = l_wt[r], db = l_dst[r], rb = l_res ? l_res[r] : 0;
     if (sb + dim > n_act || db + dim > n_act || wb + dim > n_wt || (l_res && rb + dim > n_act)) {
         if (threadIdx.x == 0) atomicOr(err, DEVERR_OOB_MAP);
@@ -53,7 +65,9 @@ __device__ __forceinline__ void rope_cs(uint32_t pos, uint32_t i, uint32_t head_
 
 // map_rope.comp: rotate pairs (d, d+half) of every head of every token.
 __global__ void k_rope(float* __restrict__ m, uint64_t n, const uint32_t* __restrict__ l_src, const uint32_t* __restrict__ l_dst,
-                       uint32_t n_tokens, uint32_t n_heads, uint32_t head_dim, uint32_t pos_offset, float base, uint32_t* err) {
+                       uint32_t n_tokens, uint32_t n_heads, uint32_t head_dim, uint32_t pos_offset, float base, uint32_t* err,
+                       const uint32_t* __restrict__ rt) {
+    n_tokens = rtv(n_tokens, rt); pos_offset = rtv(pos_offset, rt);
     const uint32_t half = head_dim / 2;
     const uint32_t pair = blockIdx.x * blockDim.x + threadIdx.x;
     if (pair >= n_tokens * n_heads * half) return;
@@ -74,8 +88,9 @@ __global__ void k_qk_norm_rope(float* __restrict__ act, uint64_t n_act, const fl
                                const uint32_t* __restrict__ l_qs, const uint32_t* __restrict__ l_qw,
                                const uint32_t* __restrict__ l_ks, const uint32_t* __restrict__ l_kw,
                                const uint32_t* __restrict__ l_dst, uint32_t q_rows, uint32_t q_dim, uint32_t k_rows, uint32_t k_dim,
-                               uint32_t pos, float base, uint32_t* err) {
+                               uint32_t pos, float base, uint32_t* err, const uint32_t* __restrict__ rt) {
     __shared__ float red[33];
+    pos = rtv(pos, rt);
     const uint32_t row = blockIdx.x;
     const bool is_q = row < q_rows;
     const uint32_t lr = is_q ? row : row - q_rows, dim = is_q ? q_dim : k_dim, half = dim / 2;
@@ -99,7 +114,8 @@ __global__ void k_qk_norm_rope(float* __restrict__ act, uint64_t n_act, const fl
 
 // map_row_copy.comp: copy_spec holds [src_row, dst_row] pairs.
 __global__ void k_row_copy(float* __restrict__ m, uint64_t n, const uint32_t* __restrict__ spec, const uint32_t* __restrict__ src_base,
-                           uint32_t dst_row_offset, uint32_t n_copies, uint32_t row_size, uint32_t* err) {
+                           uint32_t dst_row_offset, uint32_t n_copies, uint32_t row_size, uint32_t* err, const uint32_t* __restrict__ rt) {
+    dst_row_offset = rtv(dst_row_offset, rt); n_copies = rtv(n_copies, rt);
     const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (tid >= (uint64_t)n_copies * row_size) return;
     const uint32_t ci = (uint32_t)(tid / row_size), ei = (uint32_t)(tid % row_size);
@@ -111,10 +127,11 @@ __global__ void k_row_copy(float* __restrict__ m, uint64_t n, const uint32_t* __
 
 // map_matmul_t.comp: C[op][row][col] = sum_k A[op][row][k] * B[op][col][k]; a warp per output.
 __global__ void k_matmul_t(float* __restrict__ m, uint64_t n, const uint32_t* __restrict__ la, const uint32_t* __restrict__ lb,
-                           const uint32_t* __restrict__ lc, uint32_t M, uint32_t K, uint32_t N, uint32_t* err) {
+                           const uint32_t* __restrict__ lc, uint32_t M, uint32_t K, uint32_t N, uint32_t* err, const uint32_t* __restrict__ rt) {
+    M = rtv(M, rt); K = rtv(K, rt); N = rtv(N, rt);
     const uint32_t op = blockIdx.z, row = blockIdx.y;
     const uint32_t col = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (col >= N) return;
+    if (col >= N || row >= M) return;
     const uint64_t ab_ = (uint64_t)la[op] + (uint64_t)row * K, bb = (uint64_t)lb[op] + (uint64_t)col * K;
     const uint64_t cb = (uint64_t)lc[op] + (uint64_t)row * N + col;
     if (ab_ + K > n || bb + K > n || cb >= n) { if (lane == 0) atomicOr(err, DEVERR_OOB_MAP); return; }
@@ -127,9 +144,11 @@ __global__ void k_matmul_t(float* __restrict__ m, uint64_t n, const uint32_t* __
 // map_attn_softmax_value.comp: p = softmax(cap*tanh(score*scale/cap)); out = p @ V.
 __global__ void k_attn_softmax_value(float* __restrict__ m, uint64_t n, const uint32_t* __restrict__ l_sc, const uint32_t* __restrict__ l_v,
                                      const uint32_t* __restrict__ l_out, uint32_t row_size, uint32_t value_dim, float scale, float cap,
-                                     uint32_t* err) {
+                                     uint32_t* err, uint32_t smem_rows, const uint32_t* __restrict__ rt) {
     extern __shared__ float prob[];
     __shared__ float red[33];
+    row_size = rtv(row_size, rt);
+    if (row_size > smem_rows) { if (threadIdx.x == 0) atomicOr(err, DEVERR_OOB_MAP); return; }      // beyond what the graph was sized for
     const uint32_t op = blockIdx.x;
     const uint64_t sb = l_sc[op], vb = l_v[op], ob = l_out[op];
     if (sb + row_size > n || vb + (uint64_t)row_size * value_dim > n || ob + value_dim > n) { if (threadIdx.x == 0) atomicOr(err, DEVERR_OOB_MAP); return; }
@@ -220,26 +239,26 @@ __device__ float op2_eval(uint32_t op, float a, float b) {
 }
 
 __global__ void k_op1(float* __restrict__ m, uint64_t n_el, uint32_t op, const uint32_t* __restrict__ ls, const uint32_t* __restrict__ ld,
-                      uint32_t n, uint32_t* err) {
+                      uint32_t n, uint32_t* err, const uint32_t* __restrict__ rt) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
+    if (i >= rtv(n, rt)) return;
     const uint64_t s = ls[i], d = ld[i];
     OOB(s, n_el, err); OOB(d, n_el, err);
     m[d] = op1_eval(op, m[s]);
 }
 __global__ void k_op2(float* __restrict__ m, uint64_t n_el, uint32_t op, const uint32_t* __restrict__ la, const uint32_t* __restrict__ lb,
-                      const uint32_t* __restrict__ ld, uint32_t n, uint32_t* err) {
+                      const uint32_t* __restrict__ ld, uint32_t n, uint32_t* err, const uint32_t* __restrict__ rt) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
+    if (i >= rtv(n, rt)) return;
     const uint64_t a = la[i], b = lb[i], d = ld[i];
     OOB(a, n_el, err); OOB(b, n_el, err); OOB(d, n_el, err);
     m[d] = op2_eval(op, m[a], m[b]);
 }
 // map_broadcast.comp: dst[i] = src[i] (op) scalar[i]
 __global__ void k_broadcast(float* __restrict__ m, uint64_t n_el, uint32_t op, const uint32_t* __restrict__ ls, const uint32_t* __restrict__ lsc,
-                            const uint32_t* __restrict__ ld, uint32_t n, uint32_t* err) {
+                            const uint32_t* __restrict__ ld, uint32_t n, uint32_t* err, const uint32_t* __restrict__ rt) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
+    if (i >= rtv(n, rt)) return;
     const uint64_t s = ls[i], c = lsc[i], d = ld[i];
     OOB(s, n_el, err); OOB(c, n_el, err); OOB(d, n_el, err);
     const float v = m[s], k = m[c];
@@ -561,15 +580,40 @@ using namespace ab;
 #define REQ_H(h, bytes) if (!handle_ok((h), (uint32_t)(bytes))) return ADAMAH_ERR_NOT_FOUND
 #define DONE(name) do { count_launch(); int rc__ = check_launch(name); end_of_op(); return rc__; } while (0)
 
+// ---- decode-plan lowering: host side of the runtime arguments ------------------------------------------------
+// Set while adamah_decode_step records a plan into a graph.  An operator that meets a sentinel in an argument it can
+// take at run time sizes its launch for an upper bound (what its loc handles hold, or `cap` positions) and passes the
+// sentinel on; a sentinel anywhere else makes the recording fail and the plan falls back to host-side substitution.
+namespace ab {
+struct PlanRecording { bool active; uint32_t cap; uint32_t* dev; bool unsupported; };
+static PlanRecording g_rec = {};
+static inline bool is_rt(uint32_t v) { return g_rec.active && (v == ADAMAH_DECODE_RUNTIME_POS || v == ADAMAH_DECODE_RUNTIME_SEQ_LEN); }
+static inline const uint32_t* rt_ptr() { return g_rec.active ? g_rec.dev : nullptr; }
+// arguments that have no run-time form: a sentinel there ends the recording
+static inline bool rt_refuse(std::initializer_list<uint32_t> vals) {
+    for (uint32_t v : vals) if (is_rt(v)) { g_rec.unsupported = true; return true; }
+    return false;
+}
+static inline uint32_t handle_locs(uint32_t h) { return h < MAX_HANDLES && g.handles[h].used ? g.handles[h].nbytes / 4 : 0; }
+static inline uint32_t min_locs(std::initializer_list<uint32_t> hs) {
+    uint32_t m = 0xFFFFFFFFu;
+    for (uint32_t h : hs) { const uint32_t n = handle_locs(h); if (n < m) m = n; }
+    return m;
+}
+}
+#define RT_REFUSE(...) if (rt_refuse({__VA_ARGS__})) return fail(ADAMAH_ERR_INVALID, "decode plan: this argument cannot be a run-time value")
+
 static int rmsnorm_impl(uint32_t map_act, uint32_t map_wt, uint32_t src_h, uint32_t wt_h, uint32_t res_h, uint32_t dst_h,
                         uint32_t n_rows, uint32_t dim, float eps) {
     Map* a = f32_map(map_act, "rmsnorm"); Map* w = f32_map(map_wt, "rmsnorm");
     if (!a || !w) return ADAMAH_ERR_NOT_FOUND;
-    if (n_rows == 0 || dim == 0) return fail(ADAMAH_ERR_INVALID, "rmsnorm: empty shape");
-    REQ_H(src_h, n_rows * 4); REQ_H(wt_h, n_rows * 4); REQ_H(dst_h, n_rows * 4);
-    if (res_h) REQ_H(res_h, n_rows * 4);
-    k_rmsnorm<<<n_rows, 256, 0, g.stream>>>((float*)a->buf, a->n_elems, (const float*)w->buf, w->n_elems, hlocs(src_h), hlocs(wt_h),
-                                            res_h ? hlocs(res_h) : nullptr, hlocs(dst_h), dim, eps, g.dev_err);
+    RT_REFUSE(dim);
+    const uint32_t rows_ub = is_rt(n_rows) ? (res_h ? min_locs({src_h, wt_h, dst_h, res_h}) : min_locs({src_h, wt_h, dst_h})) : n_rows;
+    if (rows_ub == 0 || dim == 0) return fail(ADAMAH_ERR_INVALID, "rmsnorm: empty shape");
+    REQ_H(src_h, rows_ub * 4); REQ_H(wt_h, rows_ub * 4); REQ_H(dst_h, rows_ub * 4);
+    if (res_h) REQ_H(res_h, rows_ub * 4);
+    k_rmsnorm<<<rows_ub, 256, 0, g.stream>>>((float*)a->buf, a->n_elems, (const float*)w->buf, w->n_elems, hlocs(src_h), hlocs(wt_h),
+                                             res_h ? hlocs(res_h) : nullptr, hlocs(dst_h), dim, eps, g.dev_err, n_rows, rt_ptr());
     DONE("map_rmsnorm");
 }
 
@@ -594,11 +638,13 @@ extern "C" int map_rope_dev(uint32_t map, uint32_t src_h, uint32_t dst_h, uint32
     REQ_READY();
     Map* m = f32_map(map, "rope");
     if (!m) return ADAMAH_ERR_NOT_FOUND;
-    if (!n_tokens || !n_heads || head_dim < 2 || (head_dim & 1)) return fail(ADAMAH_ERR_INVALID, "rope: bad shape");
-    REQ_H(src_h, n_tokens * 4); REQ_H(dst_h, n_tokens * 4);
-    const uint64_t pairs = (uint64_t)n_tokens * n_heads * (head_dim / 2);
+    RT_REFUSE(n_heads, head_dim);
+    const uint32_t tok_ub = is_rt(n_tokens) ? min_locs({src_h, dst_h}) : n_tokens;
+    if (!tok_ub || !n_heads || head_dim < 2 || (head_dim & 1)) return fail(ADAMAH_ERR_INVALID, "rope: bad shape");
+    REQ_H(src_h, tok_ub * 4); REQ_H(dst_h, tok_ub * 4);
+    const uint64_t pairs = (uint64_t)tok_ub * n_heads * (head_dim / 2);
     k_rope<<<nblk(pairs, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(src_h), hlocs(dst_h), n_tokens, n_heads, head_dim,
-                                                   pos_offset, freq_base, g.dev_err);
+                                                   pos_offset, freq_base, g.dev_err, rt_ptr());
     DONE("map_rope");
 }
 
@@ -608,6 +654,7 @@ extern "C" int map_qk_norm_rope_x_dev(uint32_t map_act, uint32_t map_wt, uint32_
     REQ_READY();
     Map* a = f32_map(map_act, "qk_norm_rope"); Map* w = f32_map(map_wt, "qk_norm_rope");
     if (!a || !w) return ADAMAH_ERR_NOT_FOUND;
+    RT_REFUSE(q_rows, q_dim, k_rows, k_dim);
     if (q_rows + k_rows == 0 || (q_rows && (q_dim < 2 || (q_dim & 1))) || (k_rows && (k_dim < 2 || (k_dim & 1))))
         return fail(ADAMAH_ERR_INVALID, "qk_norm_rope: bad shape");
     if (q_rows) { REQ_H(qsrc_h, q_rows * 4); REQ_H(qwt_h, q_rows * 4); }
@@ -615,7 +662,7 @@ extern "C" int map_qk_norm_rope_x_dev(uint32_t map_act, uint32_t map_wt, uint32_
     REQ_H(qkdst_h, 4);
     k_qk_norm_rope<<<q_rows + k_rows, 128, 0, g.stream>>>((float*)a->buf, a->n_elems, (const float*)w->buf, w->n_elems,
         q_rows ? hlocs(qsrc_h) : nullptr, q_rows ? hlocs(qwt_h) : nullptr, k_rows ? hlocs(ksrc_h) : nullptr, k_rows ? hlocs(kwt_h) : nullptr,
-        hlocs(qkdst_h), q_rows, q_dim, k_rows, k_dim, pos_offset, freq_base, g.dev_err);
+        hlocs(qkdst_h), q_rows, q_dim, k_rows, k_dim, pos_offset, freq_base, g.dev_err, rt_ptr());
     DONE("map_qk_norm_rope_x");
 }
 
@@ -624,10 +671,12 @@ extern "C" int map_row_copy_offset_dev(uint32_t map, uint32_t spec_h, uint32_t s
     REQ_READY();
     Map* m = f32_map(map, "row_copy");
     if (!m) return ADAMAH_ERR_NOT_FOUND;
-    if (!n_copies || !row_size) return fail(ADAMAH_ERR_INVALID, "row_copy: empty shape");
-    REQ_H(spec_h, n_copies * 8); REQ_H(src_base_h, 4);
-    k_row_copy<<<nblk((uint64_t)n_copies * row_size, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(spec_h), hlocs(src_base_h),
-                                                                               dst_row_offset, n_copies, row_size, g.dev_err);
+    RT_REFUSE(row_size);
+    const uint32_t copies_ub = is_rt(n_copies) ? handle_locs(spec_h) / 2 : n_copies;
+    if (!copies_ub || !row_size) return fail(ADAMAH_ERR_INVALID, "row_copy: empty shape");
+    REQ_H(spec_h, copies_ub * 8); REQ_H(src_base_h, 4);
+    k_row_copy<<<nblk((uint64_t)copies_ub * row_size, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(spec_h), hlocs(src_base_h),
+                                                                                dst_row_offset, n_copies, row_size, g.dev_err, rt_ptr());
     DONE("map_row_copy_offset");
 }
 extern "C" int map_row_copy_dev(uint32_t map, uint32_t spec_h, uint32_t src_base_h, uint32_t n_copies, uint32_t row_size) {
@@ -638,10 +687,12 @@ extern "C" int map_matmul_t_dev(uint32_t map, uint32_t a_h, uint32_t b_h, uint32
     REQ_READY();
     Map* m = f32_map(map, "matmul_t");
     if (!m) return ADAMAH_ERR_NOT_FOUND;
-    if (!M || !K || !N || !n_ops || M > 65535 || n_ops > 65535) return fail(ADAMAH_ERR_INVALID, "matmul_t: bad shape");
+    RT_REFUSE(n_ops);
+    const uint32_t M_ub = is_rt(M) ? g_rec.cap : M, N_ub = is_rt(N) ? g_rec.cap : N;      // K only bounds a loop
+    if (!M_ub || !K || !N_ub || !n_ops || M_ub > 65535 || n_ops > 65535) return fail(ADAMAH_ERR_INVALID, "matmul_t: bad shape");
     REQ_H(a_h, n_ops * 4); REQ_H(b_h, n_ops * 4); REQ_H(c_h, n_ops * 4);
-    dim3 grid(nblk(N, 8), M, n_ops);
-    k_matmul_t<<<grid, 256, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(a_h), hlocs(b_h), hlocs(c_h), M, K, N, g.dev_err);
+    dim3 grid(nblk(N_ub, 8), M_ub, n_ops);
+    k_matmul_t<<<grid, 256, 0, g.stream>>>((float*)m->buf, m->n_elems, hlocs(a_h), hlocs(b_h), hlocs(c_h), M, K, N, g.dev_err, rt_ptr());
     DONE("map_matmul_t");
 }
 
@@ -650,10 +701,12 @@ extern "C" int map_attn_softmax_value_dev(uint32_t map, uint32_t scores_h, uint3
     REQ_READY();
     Map* m = f32_map(map, "attn_softmax_value");
     if (!m) return ADAMAH_ERR_NOT_FOUND;
-    if (!n_ops || !row_size || !value_dim) return fail(ADAMAH_ERR_INVALID, "attn_softmax_value: empty shape");
-    if (row_size > 49152) return fail(ADAMAH_ERR_INVALID, "attn_softmax_value: row_size %u exceeds 49152", row_size);
+    RT_REFUSE(n_ops, value_dim);
+    const uint32_t rows_ub = is_rt(row_size) ? (g_rec.cap < 49152u ? g_rec.cap : 49152u) : row_size;
+    if (!n_ops || !rows_ub || !value_dim) return fail(ADAMAH_ERR_INVALID, "attn_softmax_value: empty shape");
+    if (rows_ub > 49152) return fail(ADAMAH_ERR_INVALID, "attn_softmax_value: row_size %u exceeds 49152", rows_ub);
     REQ_H(scores_h, n_ops * 4); REQ_H(values_h, n_ops * 4); REQ_H(out_h, n_ops * 4);
-    const size_t smem = (size_t)row_size * 4;
+    const size_t smem = (size_t)rows_ub * 4;
     static size_t raised = 48 * 1024;
     if (smem > raised) {
         if (cudaFuncSetAttribute(k_attn_softmax_value, cudaFuncAttributeMaxDynamicSharedMemorySize, 196608) != cudaSuccess)
@@ -661,7 +714,7 @@ extern "C" int map_attn_softmax_value_dev(uint32_t map, uint32_t scores_h, uint3
         raised = 196608;
     }
     k_attn_softmax_value<<<n_ops, 256, smem, g.stream>>>((float*)m->buf, m->n_elems, hlocs(scores_h), hlocs(values_h), hlocs(out_h),
-                                                         row_size, value_dim, scale, cap, g.dev_err);
+                                                         row_size, value_dim, scale, cap, g.dev_err, rows_ub, rt_ptr());
     DONE("map_attn_softmax_value");
 }
 
@@ -671,8 +724,9 @@ extern "C" int map_op1_dev(uint32_t map, uint32_t op, uint32_t src_h, uint32_t d
     if (!m) return ADAMAH_ERR_NOT_FOUND;
     if (!n) return ADAMAH_OK;
     if (op > 33) return fail(ADAMAH_ERR_INVALID, "op1: unknown op %u", op);
-    REQ_H(src_h, (uint64_t)n * 4); REQ_H(dst_h, (uint64_t)n * 4);
-    k_op1<<<nblk(n, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, op, hlocs(src_h), hlocs(dst_h), n, g.dev_err);
+    const uint32_t n_ub = is_rt(n) ? min_locs({src_h, dst_h}) : n;
+    REQ_H(src_h, (uint64_t)n_ub * 4); REQ_H(dst_h, (uint64_t)n_ub * 4);
+    k_op1<<<nblk(n_ub, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, op, hlocs(src_h), hlocs(dst_h), n, g.dev_err, rt_ptr());
     DONE("map_op1");
 }
 extern "C" int map_op2_dev(uint32_t map, uint32_t op, uint32_t a_h, uint32_t b_h, uint32_t dst_h, uint32_t n) {
@@ -681,8 +735,9 @@ extern "C" int map_op2_dev(uint32_t map, uint32_t op, uint32_t a_h, uint32_t b_h
     if (!m) return ADAMAH_ERR_NOT_FOUND;
     if (!n) return ADAMAH_OK;
     if (op > 17 && op != 34 && op != 35) return fail(ADAMAH_ERR_INVALID, "op2: unknown op %u", op);
-    REQ_H(a_h, (uint64_t)n * 4); REQ_H(b_h, (uint64_t)n * 4); REQ_H(dst_h, (uint64_t)n * 4);
-    k_op2<<<nblk(n, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, op, hlocs(a_h), hlocs(b_h), hlocs(dst_h), n, g.dev_err);
+    const uint32_t n_ub = is_rt(n) ? min_locs({a_h, b_h, dst_h}) : n;
+    REQ_H(a_h, (uint64_t)n_ub * 4); REQ_H(b_h, (uint64_t)n_ub * 4); REQ_H(dst_h, (uint64_t)n_ub * 4);
+    k_op2<<<nblk(n_ub, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, op, hlocs(a_h), hlocs(b_h), hlocs(dst_h), n, g.dev_err, rt_ptr());
     DONE("map_op2");
 }
 extern "C" int map_broadcast_dev(uint32_t map, uint32_t op, uint32_t src_h, uint32_t scalar_h, uint32_t dst_h, uint32_t n) {
@@ -691,8 +746,9 @@ extern "C" int map_broadcast_dev(uint32_t map, uint32_t op, uint32_t src_h, uint
     if (!m) return ADAMAH_ERR_NOT_FOUND;
     if (!n) return ADAMAH_OK;
     if (op > 3) return fail(ADAMAH_ERR_INVALID, "broadcast: unknown op %u", op);
-    REQ_H(src_h, (uint64_t)n * 4); REQ_H(scalar_h, (uint64_t)n * 4); REQ_H(dst_h, (uint64_t)n * 4);
-    k_broadcast<<<nblk(n, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, op, hlocs(src_h), hlocs(scalar_h), hlocs(dst_h), n, g.dev_err);
+    const uint32_t n_ub = is_rt(n) ? min_locs({src_h, scalar_h, dst_h}) : n;
+    REQ_H(src_h, (uint64_t)n_ub * 4); REQ_H(scalar_h, (uint64_t)n_ub * 4); REQ_H(dst_h, (uint64_t)n_ub * 4);
+    k_broadcast<<<nblk(n_ub, 256), 256, 0, g.stream>>>((float*)m->buf, m->n_elems, op, hlocs(src_h), hlocs(scalar_h), hlocs(dst_h), n, g.dev_err, rt_ptr());
     DONE("map_broadcast");
 }
 extern "C" int map_argmax_dev(uint32_t map, uint32_t src_h, uint32_t dst_h, uint32_t n) {
@@ -764,6 +820,7 @@ extern "C" int map_matmul_t_xq4_dev(uint32_t map_act, uint32_t map_wt, uint32_t 
     Map* a = f32_map(map_act, "matmul_t_xq4");
     Map* w = get_map(map_wt);
     if (!a || !w) return ADAMAH_ERR_NOT_FOUND;
+    RT_REFUSE(M, K, N, n_ops);
     if (!M || !K || !N || !n_ops) return fail(ADAMAH_ERR_INVALID, "matmul_t_xq4: empty shape");
     REQ_H(a_h, n_ops * 4); REQ_H(b_h, n_ops * 4); REQ_H(c_h, n_ops * 4);
     for (uint32_t op = 0; op < n_ops; ++op) {
@@ -872,52 +929,48 @@ extern "C" int map_row_gather_xq8_dev(uint32_t map_act, uint32_t map_wt, uint32_
 }
 
 // ---- decode plan (adamah.c:10253-10398) -------------------------------------
+// A registered plan is a flat list of operator calls whose arguments may hold the sentinels
+// ADAMAH_DECODE_RUNTIME_POS / _SEQ_LEN.  The reference replays the list through its public entry points every step
+// with the sentinels replaced on the host.  Here the list is lowered ONCE to a CUDA graph in which the sentinels stay
+// symbolic: kernels read {pos, seq_len} from two device words that a one-thread kernel sets before each launch of the
+// graph, so a step costs two launches whatever the length of the plan.  Launches that depend on a run-time size are
+// sized for an upper bound (the loc handles' length, or `cap` positions, doubled and re-recorded when a step outgrows
+// it).  The first step of a plan runs eagerly (operators create their scratch buffers then, not inside a capture);
+// a plan the recorder cannot express (a sentinel in an argument with no run-time form, a device-produced base handle)
+// keeps running by host-side substitution, as in the reference.
 
 namespace ab {
+bool capturing();                     // runtime.cu: inside adam_b200_capture_begin / _end
 constexpr uint32_t MAX_PLANS = 16, MAX_PLAN_OPS = 4096;
-struct Plan { AdamahDecodePlanOp* ops; uint32_t n; bool valid; };
+struct Plan {
+    AdamahDecodePlanOp* ops; uint32_t n; bool valid;
+    int state;                        // 0 = not run yet, 1 = warmed (eager step done), 2 = graph, -1 = host substitution only
+    cudaGraph_t graph; cudaGraphExec_t exec;
+    uint32_t cap, nodes, compiles, graph_steps, host_steps;
+};
 static Plan g_plans[MAX_PLANS];
-void plans_clear_all() { for (auto& p : g_plans) { free(p.ops); p = Plan{}; } }
-static inline uint32_t rt(uint32_t v, uint32_t pos, uint32_t seq) {
-    return v == ADAMAH_DECODE_RUNTIME_POS ? pos : (v == ADAMAH_DECODE_RUNTIME_SEQ_LEN ? seq : v);
+static uint32_t* g_rt_dev = nullptr;
+static void plan_drop_graph(Plan& p) {
+    if (p.exec) { cudaStreamSynchronize(g.stream); cudaGraphExecDestroy(p.exec); }
+    if (p.graph) cudaGraphDestroy(p.graph);
+    p.exec = nullptr; p.graph = nullptr; p.nodes = 0;
 }
+void plans_clear_all() {
+    for (auto& p : g_plans) { plan_drop_graph(p); free(p.ops); p = Plan{}; }
+    if (g_rt_dev) { cudaFree(g_rt_dev); g_rt_dev = nullptr; }
 }
 
-extern "C" int adamah_register_decode_plan(uint32_t plan_id, const AdamahDecodePlanOp* ops, uint32_t n_ops) {
-    REQ_READY();
-    if (plan_id >= MAX_PLANS || n_ops > MAX_PLAN_OPS || (n_ops && !ops)) return fail(ADAMAH_ERR_INVALID, "decode plan: bad arguments");
-    Plan& p = g_plans[plan_id];
-    free(p.ops);
-    p = Plan{};
-    if (n_ops) {
-        p.ops = (AdamahDecodePlanOp*)malloc(sizeof(AdamahDecodePlanOp) * n_ops);
-        if (!p.ops) return fail(ADAMAH_ERR_MEMORY, "decode plan: out of host memory");
-        memcpy(p.ops, ops, sizeof(AdamahDecodePlanOp) * n_ops);
-    }
-    p.n = n_ops; p.valid = true;
-    return ADAMAH_OK;
-}
-extern "C" void adamah_clear_decode_plan(uint32_t plan_id) {
-    if (plan_id >= MAX_PLANS) return;
-    free(g_plans[plan_id].ops);
-    g_plans[plan_id] = Plan{};
-}
-extern "C" int adamah_decode_step(uint32_t plan_id, uint32_t pos, uint32_t seq_len) {
-    REQ_READY();
-    if (plan_id >= MAX_PLANS) return fail(ADAMAH_ERR_INVALID, "decode plan id out of range");
-    Plan& p = g_plans[plan_id];
-    if (!p.valid) return fail(ADAMAH_ERR_NOT_FOUND, "decode plan %u is not registered", plan_id);
-    const bool opened = g.batch_depth == 0;
-    if (opened) batch_begin();
+// The operator calls of a plan, with u0..u4 as given (`symbolic`) or with the sentinels replaced by pos / seq_len.
+static int plan_replay(const Plan& p, bool symbolic, uint32_t pos, uint32_t seq_len) {
+    auto rt = [&](uint32_t v) { return symbolic ? v : (v == ADAMAH_DECODE_RUNTIME_POS ? pos : (v == ADAMAH_DECODE_RUNTIME_SEQ_LEN ? seq_len : v)); };
     int rc = ADAMAH_OK;
     for (uint32_t i = 0; i < p.n && rc == ADAMAH_OK; ++i) {
         const AdamahDecodePlanOp& o = p.ops[i];
-        const uint32_t u0 = rt(o.u0, pos, seq_len), u1 = rt(o.u1, pos, seq_len), u2 = rt(o.u2, pos, seq_len),
-                       u3 = rt(o.u3, pos, seq_len), u4 = rt(o.u4, pos, seq_len);
+        const uint32_t u0 = rt(o.u0), u1 = rt(o.u1), u2 = rt(o.u2), u3 = rt(o.u3), u4 = rt(o.u4);
         switch (o.kind) {
         case 0: break;
         case 1: rc = adamah_fusion_flush(); break;
-        case 2: adamah_fusion_enable((int)u0); break;
+        case 2: adamah_fusion_enable(u0 != 0); break;
         case 10: rc = map_op1_dev(o.map_id, o.op_code, o.h0, o.h1, u0); break;
         case 11: rc = map_op2_dev(o.map_id, o.op_code, o.h0, o.h1, o.h2, u0); break;
         case 12: rc = map_rmsnorm_dev(o.map_id, o.h0, o.h1, o.h2, u0, u1, o.f0); break;
@@ -932,8 +985,90 @@ extern "C" int adamah_decode_step(uint32_t plan_id, uint32_t pos, uint32_t seq_l
         default: rc = fail(ADAMAH_ERR_INVALID, "decode plan: op kind %u is not on the decode path", o.kind); break;
         }
     }
+    return rc;
+}
+
+// Record the plan into a graph sized for `cap` positions.  Leaves p.state = 2 on success, -1 otherwise.
+static void plan_record(Plan& p, uint32_t cap) {
+    plan_drop_graph(p);
+    p.state = -1;
+    if (!g_rt_dev && cudaMalloc((void**)&g_rt_dev, 8) != cudaSuccess) { cudaGetLastError(); return; }
+    // base handles that only exist on the device would be read back (a synchronisation) by the operators that need them
+    for (uint32_t i = 0; i < p.n; ++i)
+        if (p.ops[i].kind == 19)
+            for (uint32_t h : {p.ops[i].h0, p.ops[i].h1, p.ops[i].h2}) if (h >= MAX_HANDLES || !g.handles[h].used || !g.handles[h].shadow) return;
+    const uint64_t l0 = g.launches;
+    if (cudaStreamSynchronize(g.stream) != cudaSuccess || cudaStreamBeginCapture(g.stream, cudaStreamCaptureModeRelaxed) != cudaSuccess) { cudaGetLastError(); return; }
+    g_rec = PlanRecording{true, cap, g_rt_dev, false};
+    const int rc = plan_replay(p, true, 0, 0);
+    g_rec.active = false;
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(g.stream, &graph);
+    const uint32_t nodes = (uint32_t)(g.launches - l0);
+    g.launches = l0;
+    if (rc != ADAMAH_OK || e != cudaSuccess || !graph) { cudaGetLastError(); if (graph) cudaGraphDestroy(graph); return; }
+    if (cudaGraphInstantiate(&p.exec, graph, 0) != cudaSuccess) { cudaGetLastError(); cudaGraphDestroy(graph); p.exec = nullptr; return; }
+    p.graph = graph; p.cap = cap; p.nodes = nodes; p.compiles++; p.state = 2;
+}
+}  // namespace ab
+
+extern "C" int adamah_register_decode_plan(uint32_t plan_id, const AdamahDecodePlanOp* ops, uint32_t n_ops) {
+    REQ_READY();
+    if (plan_id >= MAX_PLANS || n_ops > MAX_PLAN_OPS || (n_ops && !ops)) return fail(ADAMAH_ERR_INVALID, "decode plan: bad arguments");
+    Plan& p = g_plans[plan_id];
+    plan_drop_graph(p);
+    free(p.ops);
+    p = Plan{};
+    if (n_ops) {
+        p.ops = (AdamahDecodePlanOp*)malloc(sizeof(AdamahDecodePlanOp) * n_ops);
+        if (!p.ops) return fail(ADAMAH_ERR_MEMORY, "decode plan: out of host memory");
+        memcpy(p.ops, ops, sizeof(AdamahDecodePlanOp) * n_ops);
+    }
+    p.n = n_ops; p.valid = true;
+    static const bool graphs = !(getenv("ADAM_B200_PLAN_GRAPH") && atoi(getenv("ADAM_B200_PLAN_GRAPH")) == 0);
+    if (!graphs) p.state = -1;
+    return ADAMAH_OK;
+}
+extern "C" void adamah_clear_decode_plan(uint32_t plan_id) {
+    if (plan_id >= MAX_PLANS) return;
+    plan_drop_graph(g_plans[plan_id]);
+    free(g_plans[plan_id].ops);
+    g_plans[plan_id] = Plan{};
+}
+extern "C" int adamah_decode_step(uint32_t plan_id, uint32_t pos, uint32_t seq_len) {
+    REQ_READY();
+    if (plan_id >= MAX_PLANS) return fail(ADAMAH_ERR_INVALID, "decode plan id out of range");
+    Plan& p = g_plans[plan_id];
+    if (!p.valid) return fail(ADAMAH_ERR_NOT_FOUND, "decode plan %u is not registered", plan_id);
+    const bool opened = g.batch_depth == 0;
+    if (opened) batch_begin();
+    int rc = ADAMAH_OK;
+    const uint32_t need = (pos >= seq_len ? pos + 1 : seq_len);
+    if (p.state == 1 || (p.state == 2 && need > p.cap)) {
+        if (capturing()) p.state = p.state == 2 ? 2 : 1;          // inside a caller's capture: not now
+        else { uint32_t cap = 256; while (cap < need && cap < (1u << 30)) cap <<= 1; plan_record(p, cap); }
+    }
+    if (p.state == 2 && need <= p.cap && !capturing()) {
+        k_set_runtime<<<1, 1, 0, g.stream>>>(g_rt_dev, pos, seq_len);
+        if (cudaGraphLaunch(p.exec, g.stream) != cudaSuccess) rc = fail(ADAMAH_ERR_BACKEND, "decode plan: graph launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+        count_launch(1 + p.nodes);
+        p.graph_steps++;
+    } else {
+        rc = plan_replay(p, false, pos, seq_len);
+        p.host_steps++;
+        if (p.state == 0 && rc == ADAMAH_OK) p.state = 1;
+    }
     if (opened) batch_end();
     return rc;
+}
+// out[0..5] = state (2 = runs as a graph, -1 = host substitution only, 0 / 1 = not recorded yet), positions the graph is
+// sized for, kernels in the graph, times recorded, steps run as a graph, steps run by host substitution.
+extern "C" int adam_b200_decode_plan_info(uint32_t plan_id, uint32_t* out) {
+    if (plan_id >= MAX_PLANS || !out) return fail(ADAMAH_ERR_INVALID, "decode plan id out of range");
+    const Plan& p = g_plans[plan_id];
+    if (!p.valid) return fail(ADAMAH_ERR_NOT_FOUND, "decode plan %u is not registered", plan_id);
+    out[0] = (uint32_t)p.state; out[1] = p.cap; out[2] = p.nodes; out[3] = p.compiles; out[4] = p.graph_steps; out[5] = p.host_steps;
+    return ADAMAH_OK;
 }
 
 // ---- symbols off the decode path (present so the reference binding loads) ----

@@ -182,6 +182,12 @@ typedef struct AdamahDecodePlanOp {
 int  adamah_register_decode_plan(uint32_t plan_id, const AdamahDecodePlanOp* ops, uint32_t n_ops);
 int  adamah_decode_step(uint32_t plan_id, uint32_t pos, uint32_t seq_len);
 void adamah_clear_decode_plan(uint32_t plan_id);
+/* How a registered plan runs (extension).  From its second step on a plan is one CUDA graph in which the run-time
+ * arguments stay symbolic (kernels read pos / seq_len from device words set by a one-thread kernel before each graph
+ * launch).  out[0..5] = state (2 = graph, -1 = host-side substitution as in the reference, 0 / 1 = not recorded yet),
+ * positions the graph is sized for, kernels in the graph, times recorded, steps run as a graph, steps run by host
+ * substitution. */
+int  adam_b200_decode_plan_info(uint32_t plan_id, uint32_t* out);
 
 /* Symbols the reference binding resolves without a guard but which lie off the
  * decode path (generic tensor ops, untransposed 8-bit products).  They exist so the binding
