@@ -236,7 +236,15 @@ class ADAMEngineTP(ADAMEngine):
                 dist.all_gather_into_tensor(ids, gid.contiguous(), group=self._group)
                 self._tok[:B].copy_(merge_argmax_pairs(vals.view(W, B), ids.view(W, B)))
 
-    def step(self, n_steps: int = 1, lm_head: bool = True, logits: bool = False, direct: bool = False):
+    def _select_sampling_mode(self, config) -> str:
+        """Greedy decoding stays on the devices (per-shard arg-max + merge); the device-side sampling step works on one
+        GPU's full logits, so every other rule samples on the host from the gathered logits."""
+        return "gpu_matvec_argmax" if config.is_greedy() and config.repeat_penalty == 1.0 else "cpu"
+
+    def step(self, n_steps: int = 1, lm_head: bool = True, logits: bool = False, direct: bool = False, chain: bool = False,
+             sample: bool = False):
+        if sample:
+            raise ValueError("device-side sampling is not available with tensor parallelism")
         torch = self._torch
         flags = (STEP_LM if lm_head else 0) | (STEP_LOGITS if logits else 0)
         key = (flags, self._batch)
