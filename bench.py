@@ -9,10 +9,13 @@ Prints ONE JSON line.  ``value`` is decode tok/s with everything resident in HBM
 same metric through ``ADAMEngine.generate`` with host prompt ids: generated tokens divided by
 the whole call's time, i.e. the host->device prompt copy, the chunked prefill, every decode step
 and one device->host token read per step are all inside the timed region.
-``roofline`` is the dominant kernel of the metric's second half (the dequant GEMV, measured on the
-LM-head shape, 262144 x 1152 Q4_0, whose 170 MB exceed L2) against the measured HBM copy
-bandwidth; ``gemv_sweep`` lists the other GEMV shapes of the benchmark configurations (cold HBM:
-each launch of a graph reads a different copy of the weights).  ``cpu_baseline`` is the numpy
+``roofline`` is the kernel that makes up the timed region: the single-launch token kernel (one
+launch per decoded token; its algorithmic bytes are the model's Q4_0 blocks, the norm vectors and the
+cached keys and values one token reads, its duration the CUDA-event time of the K launches divided by
+K) against the measured HBM copy bandwidth.  ``lm_head_gemv`` is the dequant GEMV operator alone on the
+stream (the metric's second half), measured on the LM-head shape, 262144 x 1152 Q4_0, whose 170 MB
+exceed L2; ``gemv_sweep`` lists the other GEMV shapes of the benchmark configurations (cold HBM: each
+launch of a graph reads a different copy of the weights).  ``cpu_baseline`` is the numpy
 restatement of the reference's CPU decoder timed on this box's host cores on a bounded sample
 (same weights, same prompt); its greedy ids are compared with the GPU arm's
 (``ids_equal_oracle``).  ``tp`` is the Gemma-3-27B-shaped Q4_K model (random blocks, all 62
@@ -28,6 +31,7 @@ Other modes (one JSON line per result; what the summaries under profiles/ were m
     python bench.py --mode batch --batch 32 --prompt 512 --steps 256                batched decode + chunked prefill, 1B shape
     python bench.py --mode tp [--layers L --batch B --allreduce p2p|nccl --shard-of N]   27B-shape tensor-parallel decode
     python bench.py --mode token-once [--layers L]                                  a few token-kernel steps (for ncu)
+    python bench.py --mode token-trace [--layers L]                                 per-phase times inside the token kernel (SM clock stamps)
 """
 from __future__ import annotations
 
@@ -51,6 +55,9 @@ FALLBACK_HBM_GBS = 6650.0
 # `bench.py --mode gemv-once --type 2 --n 262144 --k 1152` (same kernel and shape; that
 # entry point also stores the 1 MB of logits)
 LMHEAD_DRAM_TRAFFIC = 169_949_184 + 4_576_256
+# the same two counters for one launch of the token kernel (full 26-layer model, context 130), from an ncu
+# capture of `bench.py --mode token-once --steps 4`
+TOKEN_DRAM_TRAFFIC = 566_583_808 + 4_014_848
 
 
 def measured_peaks():
@@ -429,7 +436,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the GEMV sweep of the default mode")
     ap.add_argument("--no-tp", action="store_true", help="skip the 27B-shape tensor-parallel decode of the default mode")
-    ap.add_argument("--mode", default="decode", choices=["decode", "gemv", "gemv-once", "batch", "tp", "token-once"])
+    ap.add_argument("--mode", default="decode", choices=["decode", "gemv", "gemv-once", "batch", "tp", "token-once", "token-trace"])
     ap.add_argument("--type", type=int, default=0, help="gemv / tp modes: GGML block type (2 = Q4_0, 12 = Q4_K)")
     ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--k", type=int, default=0)
@@ -443,7 +450,7 @@ def main():
     ap.add_argument("--shard-of", type=int, default=0, help="tp mode, one process: rank 0's shard of an N-way split without collectives")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
-    if args.mode in ("gemv", "gemv-once", "batch", "token-once"):
+    if args.mode in ("gemv", "gemv-once", "batch", "token-once", "token-trace"):
         return other_modes(args)
     if args.gpus > 1 and world == 1:
         # not under torchrun: relaunch one rank per GPU on this node
@@ -580,6 +587,15 @@ def main():
     gemv_bytes = N * K * 18 // 32 + 4 * K + 4
     gemv_gbs = gemv_bytes / (best / reps * 1e-3) / 1e9
     step_bytes = synth.model_weight_elems(cfg) * 18 // 32
+    # what one decoded token reads besides the weight blocks: the float32 norm vectors, and per layer the cached keys
+    # and values of the positions it attends to (fp16; the sliding window on the local layers) plus the row it appends
+    norm_bytes = 4 * (cfg.n_embd * (4 * cfg.n_layer + 1) + 2 * cfg.head_dim * cfg.n_layer)
+    ctx_mean = PROMPT_LEN + warmup + steps / 2.0
+    kv_row = 2 * cfg.n_head_kv * cfg.head_dim * 2
+    kv_bytes = sum(kv_row * (min(ctx_mean, cfg.sliding_window) if (cfg.sliding_window and not cfg.is_global(L)) else ctx_mean) + kv_row
+                   for L in range(cfg.n_layer))
+    token_bytes = int(step_bytes + norm_bytes + kv_bytes)
+    token_kernel = launches == steps          # one launch per token: the single-launch kernel ran (else the chain of per-operation kernels)
 
     # ---- the other GEMV shapes of the benchmark configurations (rank 0 of a single-GPU run) ---------
     sweep = None
@@ -623,10 +639,17 @@ def main():
                     "decode_only_tok_s": st["decode_tps"]},
             "ids_equal_oracle": ids_equal_oracle, "ids_compared": (len(cpu_ids) if cpu else 0),
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
-                         "traffic": LMHEAD_DRAM_TRAFFIC, "kernel": "k_gemv_mma<4,false> (LM head %dx%d Q4_0 + arg-max, tensor-core path)" % (N, K),
-                         "bytes_per_launch": gemv_bytes, "us_per_launch": best / reps * 1e3, "peak_kind": peak_kind,
-                         "frac_of_8TBs": gemv_gbs / 8000.0},
+            "roofline": {"bound": "hbm", "achieved": token_bytes / (ms / steps * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": token_bytes / (ms / steps * 1e-3) / 1e9 / hbm_peak, "traffic": TOKEN_DRAM_TRAFFIC if token_kernel else None,
+                         "kernel": ("k_token<Q4_0, fp16 KV, head 256> (one launch per token: every layer, LM head, arg-max)" if token_kernel
+                                    else "the step's chain of per-operation kernels (%d launches per token)" % (launches // max(1, steps))),
+                         "bytes_per_launch": token_bytes if token_kernel else None, "us_per_launch": ms / steps * 1e3 if token_kernel else None,
+                         "launches_in_timed_region": int(launches), "peak_kind": peak_kind,
+                         "frac_of_8TBs": token_bytes / (ms / steps * 1e-3) / 1e9 / 8000.0,
+                         "note": "latency-bound: 26 layers x 5 dependent hand-overs between the SMs inside one launch; the bytes stream at this rate only on average"},
+            "lm_head_gemv": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
+                             "traffic": LMHEAD_DRAM_TRAFFIC, "kernel": "k_gemv_mma<4,false> (LM head %dx%d Q4_0 + arg-max, tensor-core path), alone on the stream" % (N, K),
+                             "bytes_per_launch": gemv_bytes, "us_per_launch": best / reps * 1e3, "frac_of_8TBs": gemv_gbs / 8000.0},
             "step_hbm": {"bytes_per_step": step_bytes, "achieved_GBs": step_bytes / (ms / steps * 1e-3) / 1e9,
                          "frac": step_bytes / (ms / steps * 1e-3) / 1e9 / hbm_peak},
             "clocks": clk.summary(), "prefill_tok_s": (PROMPT_LEN - 1) / prefill_s, "build_s": t_build,
@@ -646,6 +669,48 @@ def main():
         print(json.dumps(line))
 
 
+def token_trace(gpu, args):
+    """Where the time of one token-kernel launch goes: every CTA stamps its SM clock at the phase boundaries of one
+    layer and of the LM head (``adam_b200_decoder_token_trace``); the figures are means over the CTAs that take part,
+    in microseconds at the SM clock read beside them, plus the launch time with and without the single-launch kernel."""
+    from adam_b200 import synth
+    from adam_b200.config import gemma3_1b, with_layers
+    from adam_b200.engine import ADAMEngine
+    cfg = gemma3_1b()
+    if args.layers:
+        cfg = with_layers(cfg, args.layers)
+    tensors = synth.build_model_cuda(gpu, cfg, seed=0)
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=PROMPT_LEN + 200, kv_dtype="f16", window=True)
+    eng.begin([synth.random_prompt(cfg.n_vocab, PROMPT_LEN, seed=1)], [PROMPT_LEN + 190])
+    gpu.batch_begin(); eng.prefill(PROMPT_LEN - 1); eng.step(8, lm_head=True); gpu.batch_end()
+    try:
+        mhz = float(subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm", "--format=csv,noheader,nounits", "-i", "0"], capture_output=True, text=True).stdout.split()[0])
+    except Exception:
+        mhz = 1965.0
+    names = ["", "residual update + input norm", "QKV product", "attention (QK-norm, RoPE, append, soft-max, PV)", "o-proj input staged", "o-proj product",
+             "residual update + post-attention / FFN norms", "gate/up product + GeGLU", "down-proj input staged", "down-proj product",
+             "", "final norm chain", "LM head product + arg-max", "finish"]
+    layer = min(5, cfg.n_layer - 1)
+    eng.token_trace(layer=layer)
+    tr = eng.token_trace(layer=layer).astype(np.float64)
+    phases = {}
+    for i in list(range(1, 10)) + [11, 12, 13]:
+        ok = (tr[:, i] > 0) & (tr[:, i - 1] > 0)
+        if ok.any():
+            d = (tr[ok, i] - tr[ok, i - 1]) / mhz
+            phases[names[i]] = {"mean_us": round(float(d.mean()), 2), "max_us": round(float(d.max()), 2), "ctas": int(ok.sum())}
+    ok = (tr[:, 9] > 0) & (tr[:, 0] > 0)
+    layer_us = float(((tr[ok, 9] - tr[ok, 0]) / mhz).mean()) if ok.any() else None
+    out = {"n_cta": int(tr.shape[0]), "traced_layer": layer, "sm_mhz": mhz, "layer_us": layer_us, "phases": phases}
+    for chain in (False, True):
+        gpu.batch_begin(); eng.step(8, lm_head=True, chain=chain); gpu.batch_end()
+        gpu.batch_begin(); gpu.timer_begin(); eng.step(64, lm_head=True, chain=chain); ms = gpu.timer_end(); gpu.batch_end()
+        out["ms_per_token_chain_of_kernels" if chain else "ms_per_token_single_launch"] = ms / 64
+    out["device_error"] = gpu.device_error()
+    eng.close()
+    return out
+
+
 def other_modes(args):
     """Single-GPU modes besides the decode benchmark (see the module docstring)."""
     if args.mode == "batch":
@@ -662,6 +727,8 @@ def other_modes(args):
             shapes = [(args.type, args.n, args.k, args.batch or 1)] if args.type and args.n and args.k else GEMV_SWEEP
             for sh in shapes:
                 print(json.dumps(gemv_shape(gpu, A, *sh, tile=not args.no_tile)), flush=True)
+        elif args.mode == "token-trace":
+            print(json.dumps(token_trace(gpu, args)))
         else:       # token-once: prompt, then a few single-launch token steps
             from adam_b200 import synth
             from adam_b200.config import gemma3_1b, with_layers
