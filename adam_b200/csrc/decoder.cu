@@ -74,7 +74,7 @@ struct Decoder {
 };
 
 constexpr uint32_t MAX_DECODERS = 8;
-constexpr uint32_t ATTN_SPLIT = 256;       // fewest tokens an attention CTA takes before another CTA is added
+constexpr uint32_t ATTN_SPLIT = 64;        // fewest tokens an attention CTA takes before another CTA is added
 constexpr uint32_t ATTN_MAX_SPLITS = 64;   // attention CTAs per (sequence, kv head)
 constexpr uint32_t PREFILL_ROWS = 64;      // rows (sequences x tokens) of one prefill chunk
 static Decoder* g_dec[MAX_DECODERS];
@@ -176,7 +176,8 @@ __global__ void k_embed(const WeightRef w, uint32_t n_embd, uint32_t n_vocab, fl
 // (max, sum, o) are merged across warps in shared memory, then across CTAs by the
 // CTA that finishes last.
 constexpr int ATTN_CP = 8;
-constexpr uint32_t ATTN_CHUNKS_PER_CTA = 32;   // chunks a CTA takes (4 per warp) before another CTA joins
+constexpr uint32_t ATTN_CHUNKS_PER_CTA = 32;   // chunks a CTA takes (4 per warp) before another CTA joins, when the grid is already large;
+                                               // launches with few (sequence, head) pairs pass a smaller number in the upper half of `hpc`
 
 template <typename T, int GS_MAX, int HD>
 __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv, uint32_t qkv_ld,
@@ -191,6 +192,8 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     // row_seq / row_pos != NULL: chunked prefill.  Row b of qkv/out belongs to sequence row_seq[b] at position
     // row_pos[b], and the keys and values of the whole chunk are already in the cache (k_kv_append ran before).
     const bool appended = row_pos != nullptr;
+    const uint32_t cpc_min = (hpc >> 16) ? (hpc >> 16) : ATTN_CHUNKS_PER_CTA;     // chunks per CTA before another CTA joins
+    hpc &= 0xFFFFu;
     T* __restrict__ kv_pool = reinterpret_cast<T*>(kv_pool_v);
     constexpr int DPL = HD / 32;                // dims per lane
     constexpr int CP = ATTN_CP;                 // positions per chunk
@@ -247,7 +250,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     const uint32_t seq = (uint32_t)p + 1;
     const uint32_t start = (window > 0 && seq > window) ? seq - window : 0;
     const uint32_t c_first = start / CP, n_chunks = (seq - 1) / CP - c_first + 1;
-    const uint32_t n_act = min((uint32_t)gridDim.x, (n_chunks + ATTN_CHUNKS_PER_CTA - 1) / ATTN_CHUNKS_PER_CTA);
+    const uint32_t n_act = min((uint32_t)gridDim.x, (n_chunks + cpc_min - 1) / cpc_min);
     if (split >= n_act) return;
     const uint32_t cpc = (n_chunks + n_act - 1) / n_act;
     const uint32_t c0 = min(c_first + split * cpc, c_first + n_chunks), c1 = min(c_first + n_chunks, c0 + cpc);
@@ -721,13 +724,19 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
     const Layer& ly = D->layers[L];
     const uint32_t qkv_ld = (d.n_head + 2 * d.n_head_kv) * d.head_dim;
     dim3 grid(D->n_splits, d.n_head_kv * (gs / hpc), batch);
+    // Chunks of 8 positions a CTA takes before another CTA joins: with few (sequence, head) pairs the SMs are idle and a
+    // CTA's chain of dependent chunk loads is the attention's whole time, so the positions are spread thinly (one chunk
+    // per warp); with many pairs the grid is full anyway and every extra CTA only repeats the query prologue.
+    static const uint32_t cpc_env = getenv("ADAM_B200_ATTN_CPC") ? (uint32_t)atoi(getenv("ADAM_B200_ATTN_CPC")) : 0u;
+    const uint32_t pairs = grid.y * grid.z;
+    const uint32_t cpc = cpc_env ? cpc_env : (pairs <= 8u ? 8u : ATTN_CHUNKS_PER_CTA);
     AttnKernel kern = hpc <= 1 ? pick_attn_hd<T, 1>(d.head_dim) : hpc <= 2 ? pick_attn_hd<T, 2>(d.head_dim)
                     : hpc <= 4 ? pick_attn_hd<T, 4>(d.head_dim) : pick_attn_hd<T, 8>(d.head_dim);
     if (smem > 48 * 1024) DCU(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_k(kern, grid, dim3(256), smem, g.stream, g.pdl, D->qkv, qkv_ld, ly.norm[NORM_Q], ly.norm[NORM_K], d.norm_eps,
              D->rope_cos[which], D->rope_sin[which], D->rope_pos[which],
              D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
-             d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, hpc,
+             d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, hpc | (cpc << 16),
              prefill ? D->row_seq : nullptr, prefill ? D->row_pos : nullptr, g.dev_err);
     count_launch();
     return ADAMAH_OK;

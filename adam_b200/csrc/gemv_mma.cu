@@ -1,6 +1,9 @@
 // Host-side launch logic of the tensor-core Q4_0 GEMV (kernel in gemv_mma.cuh).
 #include "gemv_mma.cuh"
 
+#include <cstdio>
+#include <cstdlib>
+
 namespace ab {
 
 constexpr int MMA_SMEM_LIMIT = 200 * 1024;
@@ -101,6 +104,16 @@ int launch_gemv_mma(int wt, const uint8_t* t0, const uint8_t* t1, GemvArgs a, cu
                 const double busy = (double)resident * nw * 16.0;
                 const double cost = (double)passes * (slice * nm + 3.0 + 0.25 * c) * (busy > 300.0 ? busy : 300.0);
                 if (cost < best_cost * 0.999) { best_cost = cost; n_warps = nw; KS = c; best_per_sm = per_sm; }
+            }
+        }
+        {   // tuning aid: ADAM_B200_MMA_SHAPE="warps,k_slices" overrides the estimate (warps 8 / 12 / 16, k_slices a divisor)
+            static const char* force = getenv("ADAM_B200_MMA_SHAPE");
+            int fw = 0, fk = 0;
+            if (force && sscanf(force, "%d,%d", &fw, &fk) == 2 && (fw == 8 || fw == 12 || fw == 16) && fw >= nw_min && fk >= 1 && fw % fk == 0 && fk <= pairs &&
+                x_bytes(units, ncol) + ring_bytes(wt, fw) <= (size_t)MMA_SMEM_LIMIT) {
+                n_warps = fw; KS = fk;
+                cudaOccupancyMaxActiveBlocksPerMultiprocessor(&best_per_sm, k, fw * 32, x_bytes(units, ncol) + ring_bytes(wt, fw));
+                if (best_per_sm < 1) best_per_sm = 1;
             }
         }
         const size_t smem = x_bytes(units, ncol) + ring_bytes(wt, n_warps);

@@ -9,10 +9,11 @@ Prints ONE JSON line.  ``value`` is decode tok/s with everything resident in HBM
 same metric through ``ADAMEngine.generate`` with host prompt ids: generated tokens divided by
 the whole call's time, i.e. the host->device prompt copy, the chunked prefill, every decode step
 and one device->host token read per step are all inside the timed region.
-``roofline`` is the kernel that makes up the timed region: the single-launch token kernel (one
-launch per decoded token; its algorithmic bytes are the model's Q4_0 blocks, the norm vectors and the
-cached keys and values one token reads, its duration the CUDA-event time of the K launches divided by
-K) against the measured HBM copy bandwidth.  ``lm_head_gemv`` is the dequant GEMV operator alone on the
+``roofline`` covers the timed region as a whole: the bytes one decoded token has to read (the model's
+Q4_0 blocks, the norm vectors, the cached keys and values) over the CUDA-event time of a step, against the
+measured HBM copy bandwidth.  A step is a CUDA graph of 133 per-operation kernels by default, or one launch
+of the persistent token kernel (``ADAM_B200_SINGLE_LAUNCH=1``); the line carries the other path's time as
+``other_step_path``.  ``lm_head_gemv`` is the dequant GEMV operator alone on the
 stream (the metric's second half), measured on the LM-head shape, 262144 x 1152 Q4_0, whose 170 MB
 exceed L2; ``gemv_sweep`` lists the other GEMV shapes of the benchmark configurations (cold HBM: each
 launch of a graph reads a different copy of the weights).  ``cpu_baseline`` is the numpy
@@ -30,7 +31,7 @@ Other modes (one JSON line per result; what the summaries under profiles/ were m
     python bench.py --mode gemv-once --type 2 --n 262144 --k 1152 --reps 4          a few launches (for ncu)
     python bench.py --mode batch --batch 32 --prompt 512 --steps 256                batched decode + chunked prefill, 1B shape
     python bench.py --mode tp [--layers L --batch B --allreduce p2p|nccl --shard-of N]   27B-shape tensor-parallel decode
-    python bench.py --mode token-once [--layers L]                                  a few token-kernel steps (for ncu)
+    python bench.py --mode token-once [--layers L] [--chain]                        a few token steps (for ncu): token kernel, or the graph of kernels
     python bench.py --mode token-trace [--layers L]                                 per-phase times inside the token kernel (SM clock stamps)
 """
 from __future__ import annotations
@@ -447,6 +448,7 @@ def main():
     ap.add_argument("--token-prefill", action="store_true", help="batch / tp modes: consume the prompt one position per step")
     ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"], help="tp mode: library peer-memory all-reduce or NCCL")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--chain", action="store_true", help="token-once mode: the CUDA graph of per-operation kernels instead of the token kernel")
     ap.add_argument("--shard-of", type=int, default=0, help="tp mode, one process: rank 0's shard of an N-way split without collectives")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
@@ -554,6 +556,16 @@ def main():
     barrier()
     launches = gpu.get_native_stats()["dispatch_count"]
     tokens_kernel = eng.read_log(0, PROMPT_LEN + warmup, steps)
+    # the other way to run a one-sequence step, for the record: every token as one launch of the persistent token kernel
+    other = None
+    if world == 1:
+        eng.begin([prompt], [kv_cap - 4])
+        gpu.batch_begin(); eng.prefill(PROMPT_LEN - 1); eng.step(warmup, lm_head=True, chain=eng.single_launch); gpu.batch_end()
+        gpu.reset_native_stats()
+        gpu.batch_begin(); gpu.timer_begin(); eng.step(steps, lm_head=True, chain=eng.single_launch); ms_o = gpu.timer_end(); gpu.batch_end()
+        other = {"path": "CUDA graph of per-operation kernels" if eng.single_launch else "single-launch token kernel (k_token)",
+                 "ms_per_step": ms_o / steps, "tok_s": steps / (ms_o * 1e-3), "gpu_launches": int(gpu.get_native_stats()["dispatch_count"]),
+                 "ids_equal": [int(t) for t in eng.read_log(0, PROMPT_LEN + warmup, steps)] == [int(t) for t in tokens_kernel]}
 
     # ---- end to end through the public API: host prompt in, one token read back per step ----
     gen_cfg = GenerationConfig(max_tokens=warmup + steps, top_k=1, temperature=0.0, repeat_penalty=1.0, eos_token_ids=())
@@ -642,11 +654,12 @@ def main():
             "roofline": {"bound": "hbm", "achieved": token_bytes / (ms / steps * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
                          "frac": token_bytes / (ms / steps * 1e-3) / 1e9 / hbm_peak, "traffic": TOKEN_DRAM_TRAFFIC if token_kernel else None,
                          "kernel": ("k_token<Q4_0, fp16 KV, head 256> (one launch per token: every layer, LM head, arg-max)" if token_kernel
-                                    else "the step's chain of per-operation kernels (%d launches per token)" % (launches // max(1, steps))),
+                                    else "all %d kernels of a token step together (CUDA graph: 105 k_gemv_mma, 26 k_attention, embed, advance); "
+                                         "the largest single kernel is under lm_head_gemv" % (launches // max(1, steps))),
                          "bytes_per_launch": token_bytes if token_kernel else None, "us_per_launch": ms / steps * 1e3 if token_kernel else None,
                          "launches_in_timed_region": int(launches), "peak_kind": peak_kind,
                          "frac_of_8TBs": token_bytes / (ms / steps * 1e-3) / 1e9 / 8000.0,
-                         "note": "latency-bound: 26 layers x 5 dependent hand-overs between the SMs inside one launch; the bytes stream at this rate only on average"},
+                         "note": "latency-bound: 26 layers x 5 dependent kernels (or hand-overs between SMs inside the single launch); the bytes stream at this rate only on average"},
             "lm_head_gemv": {"bound": "hbm", "achieved": gemv_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": gemv_gbs / hbm_peak,
                              "traffic": LMHEAD_DRAM_TRAFFIC, "kernel": "k_gemv_mma<4,false> (LM head %dx%d Q4_0 + arg-max, tensor-core path), alone on the stream" % (N, K),
                              "bytes_per_launch": gemv_bytes, "us_per_launch": best / reps * 1e3, "frac_of_8TBs": gemv_gbs / 8000.0},
@@ -654,6 +667,8 @@ def main():
                          "frac": step_bytes / (ms / steps * 1e-3) / 1e9 / hbm_peak},
             "clocks": clk.summary(), "prefill_tok_s": (PROMPT_LEN - 1) / prefill_s, "build_s": t_build,
         }
+        if other is not None:
+            line["other_step_path"] = other
         if sweep is not None:
             line["gemv_sweep"] = sweep
         if tp is not None:
@@ -737,7 +752,7 @@ def other_modes(args):
             if args.layers:
                 cfg = with_layers(cfg, args.layers)
             tensors = synth.build_model_cuda(gpu, cfg, seed=0)
-            eng = ADAMEngine(gpu, cfg, tensors, kv_cap=PROMPT_LEN + 64, kv_dtype="f16", window=True)
+            eng = ADAMEngine(gpu, cfg, tensors, kv_cap=PROMPT_LEN + 64, kv_dtype="f16", window=True, single_launch=not args.chain)
             eng.begin([synth.random_prompt(cfg.n_vocab, PROMPT_LEN, seed=1)], [PROMPT_LEN + 60])
             gpu.batch_begin(); eng.prefill(PROMPT_LEN - 1); eng.step(max(1, min(args.steps, 32)), lm_head=True); gpu.batch_end()
             print(json.dumps({"ok": gpu.device_error() == 0}))

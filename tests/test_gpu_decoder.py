@@ -281,8 +281,8 @@ def test_graph_replay_equals_direct_launches(gpu):
         # the single-launch token kernel: one launch per token, same ids
         eng.begin([prompt], [30])
         gpu.reset_native_stats()
-        eng.step(5, lm_head=False)
-        eng.step(10, lm_head=True)
+        eng.step(5, lm_head=False, chain=False)
+        eng.step(10, lm_head=True, chain=False)
         c = eng.read_log(0, 6, 10)
         assert np.array_equal(a, c)
         assert gpu.get_native_stats()["dispatch_count"] == 15
@@ -317,7 +317,7 @@ def test_bounded_wait_runs_out_and_the_kernel_returns(gpu):
     cfg = _cfg(dict(n_layer=3))
     tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=41, tied=False)
     prompt = synth.random_prompt(cfg.n_vocab, 6, seed=9)
-    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=48)
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=48, single_launch=True)
     try:
         good, _ = eng.generate(prompt, GenerationConfig(max_tokens=8, **GREEDY))
         eng.begin([prompt], [40])

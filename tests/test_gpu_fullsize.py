@@ -86,6 +86,15 @@ def test_1b_shape_128_prompt_128_greedy_tokens(gpu, golden_dir, case):
         assert gpu.device_error() == 0
     finally:
         eng.close()
+    # (c) the same configuration with every token as ONE kernel launch (the persistent token kernel)
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=kv_cap, kv_dtype="f16", window=True, single_launch=True)
+    try:
+        gpu.reset_native_stats()
+        got, _ = eng.generate(prompt, GenerationConfig(max_tokens=n_gen, **GREEDY))
+        assert got == want
+        assert gpu.device_error() == 0
+    finally:
+        eng.close()
         del f32, dec, tensors
         gc.collect()
 
