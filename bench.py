@@ -59,6 +59,9 @@ LMHEAD_DRAM_TRAFFIC = 169_949_184 + 4_576_256
 # the same two counters for one launch of the token kernel (full 26-layer model, context 130), from an ncu
 # capture of `bench.py --mode token-once --steps 4`
 TOKEN_DRAM_TRAFFIC = 566_583_808 + 4_014_848
+# and summed over the 133 kernels of one step of the CUDA-graph path, from an ncu capture of
+# `bench.py --mode token-once --chain --steps 3` (metrics gpu__time_duration, dram__bytes_read, dram__bytes_write)
+CHAIN_DRAM_TRAFFIC = 576_993_536 + 123_989
 
 
 def measured_peaks():
@@ -652,11 +655,11 @@ def main():
             "ids_equal_oracle": ids_equal_oracle, "ids_compared": (len(cpu_ids) if cpu else 0),
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": token_bytes / (ms / steps * 1e-3) / 1e9, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": token_bytes / (ms / steps * 1e-3) / 1e9 / hbm_peak, "traffic": TOKEN_DRAM_TRAFFIC if token_kernel else None,
+                         "frac": token_bytes / (ms / steps * 1e-3) / 1e9 / hbm_peak, "traffic": TOKEN_DRAM_TRAFFIC if token_kernel else CHAIN_DRAM_TRAFFIC,
                          "kernel": ("k_token<Q4_0, fp16 KV, head 256> (one launch per token: every layer, LM head, arg-max)" if token_kernel
                                     else "all %d kernels of a token step together (CUDA graph: 105 k_gemv_mma, 26 k_attention, embed, advance); "
                                          "the largest single kernel is under lm_head_gemv" % (launches // max(1, steps))),
-                         "bytes_per_launch": token_bytes if token_kernel else None, "us_per_launch": ms / steps * 1e3 if token_kernel else None,
+                         "bytes_per_step": token_bytes, "us_per_step": ms / steps * 1e3,
                          "launches_in_timed_region": int(launches), "peak_kind": peak_kind,
                          "frac_of_8TBs": token_bytes / (ms / steps * 1e-3) / 1e9 / 8000.0,
                          "note": "latency-bound: 26 layers x 5 dependent kernels (or hand-overs between SMs inside the single launch); the bytes stream at this rate only on average"},
