@@ -717,7 +717,13 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
     const uint32_t gs = d.n_head / d.n_head_kv;
     // Query heads per CTA: one while that still leaves SMs idle (lowest latency; the CTAs
     // of a kv head re-read its rows from L2), the whole group once the grid is large.
-    const uint32_t hpc = (batch * d.n_head <= 2u * (uint32_t)g.sm_count) ? 1u : gs;
+    // Measured at the 1B shape (4 query heads on 1 kv head): one sequence is fastest with a CTA per query head, eight
+    // sequences with two heads per CTA, 32 sequences and prefill chunks with the whole group per CTA (the rows of a kv
+    // head are then read once instead of once per query head).
+    static const uint32_t hpc_env = getenv("ADAM_B200_ATTN_HPC") ? (uint32_t)atoi(getenv("ADAM_B200_ATTN_HPC")) : 0u;
+    const uint32_t work = batch * d.n_head;                    // CTAs per position split with one head each
+    const uint32_t hpc_auto = work <= 8u ? 1u : (work <= 64u ? (gs >= 2u ? 2u : 1u) : gs);
+    const uint32_t hpc = (hpc_env && gs % hpc_env == 0 && hpc_env <= 8u) ? hpc_env : hpc_auto;
     const uint32_t window = ((d.flags & 1u) && d.sliding_window > 0 && !is_global_layer(d, L)) ? d.sliding_window : 0;
     const size_t smem = ((size_t)hpc * d.head_dim + 2 * (size_t)d.head_dim + (size_t)8 * hpc * d.head_dim) * 4;
     const int which = is_global_layer(d, L) ? 1 : 0;
@@ -729,7 +735,8 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
     // per warp); with many pairs the grid is full anyway and every extra CTA only repeats the query prologue.
     static const uint32_t cpc_env = getenv("ADAM_B200_ATTN_CPC") ? (uint32_t)atoi(getenv("ADAM_B200_ATTN_CPC")) : 0u;
     const uint32_t pairs = grid.y * grid.z;
-    const uint32_t cpc = cpc_env ? cpc_env : (pairs <= 8u ? 8u : ATTN_CHUNKS_PER_CTA);
+    const uint32_t cpc = cpc_env ? cpc_env : (work <= 64u ? 8u : ATTN_CHUNKS_PER_CTA);
+    (void)pairs;
     AttnKernel kern = hpc <= 1 ? pick_attn_hd<T, 1>(d.head_dim) : hpc <= 2 ? pick_attn_hd<T, 2>(d.head_dim)
                     : hpc <= 4 ? pick_attn_hd<T, 4>(d.head_dim) : pick_attn_hd<T, 8>(d.head_dim);
     if (smem > 48 * 1024) DCU(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
