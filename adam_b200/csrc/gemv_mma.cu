@@ -44,7 +44,13 @@ int launch_gemv_mma(int wt, const uint8_t* t0, const uint8_t* t1, GemvArgs a, cu
     if (pair && !t1) return fail(ADAMAH_ERR_INVALID, "gemv_mma: second matrix missing");
     const int units = a.K / 32, pairs = a.K / 64, n_rg = a.N / 16;
     // batch rows per pass: as many of 4, 2, 1 as shared memory allows
-    int nb_max = 4;
+    // Batch rows per pass.  The passes of a launch run side by side (gridDim.x), each re-reading the weights from L2.
+    // Matrices of a few MB are bound by latency, not by bytes: there more, thinner passes (more CTAs in flight) win --
+    // measured at the 1B shape: 4 rows as 4 passes of one (0.94 against 1.41 ms per step), 8..32 rows as passes of two
+    // (batch 8: 1.21 against 1.48 ms).  Large matrices (27B shapes, LM heads) and prefill chunks keep four rows per pass.
+    static const int nb_env = getenv("ADAM_B200_MMA_ROWS") ? atoi(getenv("ADAM_B200_MMA_ROWS")) : 0;
+    const double w_bytes = (double)a.N * a.K * 0.5625 * (pair ? 2 : 1);
+    int nb_max = (nb_env == 1 || nb_env == 2 || nb_env == 4) ? nb_env : (w_bytes > 16.0e6 ? 4 : (a.B <= 4 ? 1 : (a.B <= 32 ? 2 : 4)));
     const int nw_min = chain_min_warps(a) <= 8 ? 8 : (chain_min_warps(a) <= 12 ? 12 : 16);
     while (nb_max > 1 && x_bytes(units, 4 * nb_max) + ring_bytes(wt, nw_min) > (size_t)MMA_SMEM_LIMIT) nb_max >>= 1;
     // One launch covers up to MMA_MAX_PASSES groups of nb_max batch rows (gridDim.y); more rows take more launches.
