@@ -718,11 +718,11 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
     // Query heads per CTA: one while that still leaves SMs idle (lowest latency; the CTAs
     // of a kv head re-read its rows from L2), the whole group once the grid is large.
     // Measured at the 1B shape (4 query heads on 1 kv head): one sequence is fastest with a CTA per query head, eight
-    // sequences with two heads per CTA, 32 sequences and prefill chunks with the whole group per CTA (the rows of a kv
+    // sequences with two heads per CTA, 16 or more sequences and prefill chunks with the whole group per CTA (the rows of a kv
     // head are then read once instead of once per query head).
     static const uint32_t hpc_env = getenv("ADAM_B200_ATTN_HPC") ? (uint32_t)atoi(getenv("ADAM_B200_ATTN_HPC")) : 0u;
     const uint32_t work = batch * d.n_head;                    // CTAs per position split with one head each
-    const uint32_t hpc_auto = work <= 8u ? 1u : (work <= 64u ? (gs >= 2u ? 2u : 1u) : gs);
+    const uint32_t hpc_auto = work <= 8u ? 1u : (work <= 32u ? (gs >= 2u ? 2u : 1u) : gs);
     const uint32_t hpc = (hpc_env && gs % hpc_env == 0 && hpc_env <= 8u) ? hpc_env : hpc_auto;
     const uint32_t window = ((d.flags & 1u) && d.sliding_window > 0 && !is_global_layer(d, L)) ? d.sliding_window : 0;
     const size_t smem = ((size_t)hpc * d.head_dim + 2 * (size_t)d.head_dim + (size_t)8 * hpc * d.head_dim) * 4;
