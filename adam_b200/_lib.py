@@ -138,6 +138,7 @@ _SIGS = {
     "adam_b200_decoder_read_logits": (c_int, [u32, u32, c_void_p]),
     "adam_b200_decoder_read_buffer": (c_int, [u32, u32, u32, c_void_p, u32]),
     "adam_b200_decoder_token_trace": (c_int, [u32, u32, c_void_p, c_void_p]),
+    "adam_b200_decoder_step_trace": (c_int, [u32, u32, c_void_p, u32]),
     "adam_b200_decoder_test_wait_expiry": (c_int, [u32, u32]),
     "adam_b200_decoder_set_sampling": (c_int, [u32, u32, f32, f32, f32, u32, u64]),
     "map_matvec_topk_t_xq4_ex_dev": (c_int, [u32, u32, u32, u32, u32, u32, u32, u32, u32, u32, u32, f32, u32]),

@@ -12,6 +12,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libadam_b200.so")
 OBJ_DIR = os.path.join(HERE, "build")
+TRACE_LIB = os.path.join(HERE, "libadam_b200_trace.so")
+TRACE_OBJ_DIR = os.path.join(HERE, "build", "trace")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -35,9 +37,12 @@ def _deps_mtime() -> float:
     return max(os.path.getmtime(f) for f in files)
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, step_trace: bool = False) -> str:
     """Compile and link; returns the library path.  Skips work when the library
-    is newer than every source."""
+    is newer than every source.  ``step_trace`` builds the diagnostics variant ``libadam_b200_trace.so``
+    (kernels of the decode step stamp their phase boundaries; select it with ``ADAM_B200_LIB_PATH``)."""
+    LIB = TRACE_LIB if step_trace else globals()["LIB"]
+    OBJ_DIR = TRACE_OBJ_DIR if step_trace else globals()["OBJ_DIR"]
     if not force and os.path.exists(LIB) and os.path.getmtime(LIB) >= _deps_mtime():
         return LIB
     os.makedirs(OBJ_DIR, exist_ok=True)
@@ -50,7 +55,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_time):
             return obj
         cmd = [nvcc, *[f for f in NVCC_FLAGS if f != "--use_fast_math=false"], *os.environ.get("ADAM_B200_NVCC_EXTRA", "").split(),
-               "-c", src, "-o", obj]
+               *(["-DADAM_B200_STEP_TRACE"] if step_trace else []), "-c", src, "-o", obj]
         if ptxas_info:
             cmd[1:1] = ["-Xptxas", "-v"]
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -79,5 +84,6 @@ if __name__ == "__main__":
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--ptxas", action="store_true", help="print registers / spills / shared memory per kernel")
+    ap.add_argument("--step-trace", action="store_true", help="build the diagnostics variant libadam_b200_trace.so (-DADAM_B200_STEP_TRACE)")
     a = ap.parse_args()
-    print(build(force=a.force, verbose=a.verbose, ptxas_info=a.ptxas))
+    print(build(force=a.force, verbose=a.verbose, ptxas_info=a.ptxas, step_trace=a.step_trace))

@@ -102,6 +102,21 @@ inline cudaError_t launch_k(void (*k)(KArgs...), dim3 grid, dim3 block, size_t s
     return cudaLaunchKernelEx(&cfg, k, KArgs(args)...);
 }
 
+
+// ---- step trace (diagnostics build only: -DADAM_B200_STEP_TRACE, `python -m adam_b200.build --step-trace`) ----
+// Kernels of the decode step stamp the global nanosecond timer at their phase boundaries into a buffer the host
+// reads back (adam_b200_decoder_step_trace).  The regular build compiles none of it: no field, no parameter, no test.
+#ifdef ADAM_B200_STEP_TRACE
+#define STEP_TRACE_PARAM , long long* trace
+#define STEP_TRACE_ARG(x) , (x)
+__device__ __forceinline__ long long step_trace_now() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define STEP_STAMP(buf, index) do { if (buf) (buf)[index] = step_trace_now(); } while (0)
+#else
+#define STEP_TRACE_PARAM
+#define STEP_TRACE_ARG(x)
+#define STEP_STAMP(buf, index) do { } while (0)
+#endif
+
 // ---- device helpers --------------------------------------------------------
 
 // Programmatic dependent launch: let the next kernel in the stream start its

@@ -86,6 +86,10 @@ static Decoder* get_dec(uint32_t id) {
 }
 
 // ---- kernels ---------------------------------------------------------------
+#ifdef ADAM_B200_STEP_TRACE
+// step trace: [4 products][8 CTAs][8 stamps] then [32 attention CTAs][8 stamps] of layer g_step_trace_layer
+static long long* g_step_trace = nullptr; static uint32_t g_step_trace_layer = 0; static int g_step_trace_slot = -1;
+#endif
 
 // h[b] = dequant(token_embd[row tok]) * emb_scale   (diag_inference.py:975-977)
 template <int WT>
@@ -188,7 +192,13 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
                                                    uint32_t n_head, uint32_t layer, uint32_t window, float scale, float cap,
                                                    float* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                                                    unsigned int* __restrict__ ticket, uint32_t n_splits_max, uint32_t hpc,
-                                                   const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_pos, uint32_t* err) {
+                                                   const int32_t* __restrict__ row_seq, const int32_t* __restrict__ row_pos, uint32_t* err STEP_TRACE_PARAM) {
+#ifdef ADAM_B200_STEP_TRACE
+#define AT_STAMP(slot) do { if (threadIdx.x == 0 && blockIdx.z == 0 && (blockIdx.y * gridDim.x + blockIdx.x) < 32) STEP_STAMP(trace, (blockIdx.y * gridDim.x + blockIdx.x) * 8 + (slot)); } while (0)
+#else
+#define AT_STAMP(slot) do { } while (0)
+#endif
+    AT_STAMP(0);
     // row_seq / row_pos != NULL: chunked prefill.  Row b of qkv/out belongs to sequence row_seq[b] at position
     // row_pos[b], and the keys and values of the whole chunk are already in the cache (k_kv_append ran before).
     const bool appended = row_pos != nullptr;
@@ -311,7 +321,9 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         cs[j] = i < half ? ct[i] : 1.f;
         sn[j] = i < half ? st[i] : 0.f;
     }
+    AT_STAMP(1);
     if (!appended) { pdl_launch_dependents(); pdl_wait(); }     // this step's q/k/v rows come from the previous kernel
+    AT_STAMP(2);
     const float* row_q = qkv + (size_t)b * qkv_ld + (size_t)head0 * hd;
     const float* row_k = qkv + (size_t)b * qkv_ld + (size_t)n_head * hd + (size_t)kvh * hd;
     const float* row_v = row_k + (size_t)geo.n_kv * hd;
@@ -375,6 +387,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         }
     }
     __syncthreads();
+    AT_STAMP(3);
 
     // ---- this warp's chunks: scores, online soft-max, P@V ----
     float q[GS_MAX][DPL], o[GS_MAX][DPL], m_run[VPL], l_run[VPL];
@@ -466,6 +479,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         process(c, kr, vr);
         if constexpr (DB) { if (c + 8 < c1) process(c + 8, kr2, vr2); }
     }
+    AT_STAMP(4);
     // ---- merge the warps ----
     {
         float* so = s_o + (size_t)warp * gs * hd + lane * DPL;
@@ -520,11 +534,13 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         }
     }
     if (n_act == 1) return;
+    AT_STAMP(5);
     __threadfence();
     __syncthreads();
     unsigned int* tkt = ticket + slot_y;
     if (tid == 0) s_last = (atomicAdd(tkt, 1u) == n_act - 1);
     __syncthreads();
+    AT_STAMP(6);
     if (!s_last) return;
     __threadfence();
     // ---- merge the splits (last CTA to arrive): all loads of a batch of 4 splits are
@@ -561,6 +577,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
         }
         reinterpret_cast<float4*>(orow)[i4] = make_float4(num.x / den, num.y / den, num.z / den, num.w / den);
     }
+    AT_STAMP(7);
     if (tid == 0) *tkt = 0u;
 }
 
@@ -698,7 +715,7 @@ static size_t kv_elem_size(const adam_b200_decoder_desc& d) { return d.kv_dtype 
 
 typedef void (*AttnKernel)(const float*, uint32_t, const float*, const float*, float, const float*, const float*, uint32_t, void*, KvGeom,
                            const int32_t*, const int32_t*, uint32_t, uint32_t, uint32_t, float, float, float*, float*, float*,
-                           unsigned int*, uint32_t, uint32_t, const int32_t*, const int32_t*, uint32_t*);
+                           unsigned int*, uint32_t, uint32_t, const int32_t*, const int32_t*, uint32_t* STEP_TRACE_PARAM);
 
 template <typename T, int GS>
 static AttnKernel pick_attn_hd(uint32_t hd) {
@@ -744,7 +761,7 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
              D->rope_cos[which], D->rope_sin[which], D->rope_pos[which],
              D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
              d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, D->n_splits, hpc | (cpc << 16),
-             prefill ? D->row_seq : nullptr, prefill ? D->row_pos : nullptr, g.dev_err);
+             prefill ? D->row_seq : nullptr, prefill ? D->row_pos : nullptr, g.dev_err STEP_TRACE_ARG((g_step_trace && L == g_step_trace_layer && !prefill) ? g_step_trace + 4 * 64 : nullptr));
     count_launch();
     return ADAMAH_OK;
 }
@@ -767,6 +784,9 @@ static void launch_embed(Decoder* D, uint32_t rows, const int32_t* row_seq, cons
 }
 
 static int gemv(const Mat& m, const Mat* m2, GemvArgs a, int B, int epi) {
+#ifdef ADAM_B200_STEP_TRACE
+    if (g_step_trace && g_step_trace_slot >= 0) { a.trace = g_step_trace + 64 * g_step_trace_slot; g_step_trace_slot = -1; }
+#endif
     a.w0 = m.w; if (m2) a.w1 = m2->w;
     a.N = (int)m.rows; a.K = (int)m.cols; a.B = B; a.epi = epi;
     if (B >= TC_MIN_ROWS && (!m2 || m2->wtype == m.wtype) && gemm_tc_supports(m.wtype, a)) return launch_gemm_tc(m.wtype, a, g.stream);
@@ -810,6 +830,9 @@ static int enqueue_part(Decoder* D, uint32_t batch, uint32_t part, bool with_lm,
         in.y = D->qkv; in.ldy = (int)qkv_ld;
         if (ly.qkv_contiguous) {
             Mat qkv = ly.m[MAT_Q]; qkv.rows = qkv_ld; qkv.tiled = ly.qkv_tiled;
+#ifdef ADAM_B200_STEP_TRACE
+            if (L == g_step_trace_layer) g_step_trace_slot = 0;
+#endif
             if ((rc = gemv(qkv, nullptr, in, batch, EPI_STORE))) return rc;
         } else {
             if ((rc = gemv(ly.m[MAT_Q], nullptr, in, batch, EPI_STORE))) return rc;
@@ -823,6 +846,9 @@ static int enqueue_part(Decoder* D, uint32_t batch, uint32_t part, bool with_lm,
         if (rc) return rc;
         GemvArgs o = {};
         o.x = D->attn_out; o.ldx = (int)q_dim; o.y = D->proj; o.ldy = (int)E;
+#ifdef ADAM_B200_STEP_TRACE
+        if (L == g_step_trace_layer) g_step_trace_slot = 1;
+#endif
         if ((rc = gemv(ly.m[MAT_O], nullptr, o, batch, EPI_STORE))) return rc;
     } else if (part < 2 * d.n_layer) {
         const Layer& ly = D->layers[part / 2];
@@ -830,9 +856,15 @@ static int enqueue_part(Decoder* D, uint32_t batch, uint32_t part, bool with_lm,
         GemvArgs gu = {};
         gu.ldx = (int)E; gu.eps = d.norm_eps; gu.h_in = D->hbuf[0]; gu.add_src = D->proj; gu.w_post = ly.norm[NORM_POST_ATTN];
         gu.w_pre = ly.norm[NORM_FFN]; gu.h_out = D->hbuf[1]; gu.y = D->act; gu.ldy = (int)d.n_ff;
+#ifdef ADAM_B200_STEP_TRACE
+        if (part / 2 == g_step_trace_layer) g_step_trace_slot = 2;
+#endif
         if ((rc = gemv(ly.m[MAT_GATE], &ly.m[MAT_UP], gu, batch, d.ffn_act == 0 ? EPI_GEGLU : EPI_SWIGLU))) return rc;
         GemvArgs dn = {};
         dn.x = D->act; dn.ldx = (int)d.n_ff; dn.y = D->proj; dn.ldy = (int)E;
+#ifdef ADAM_B200_STEP_TRACE
+        if (part / 2 == g_step_trace_layer) g_step_trace_slot = 3;
+#endif
         if ((rc = gemv(ly.m[MAT_DOWN], nullptr, dn, batch, EPI_STORE))) return rc;
     } else if (part == 2 * d.n_layer) {
         if (with_lm) {
@@ -1558,6 +1590,35 @@ extern "C" int adam_b200_decoder_prefill(uint32_t id, uint32_t n_tokens) {
     if (rc == ADAMAH_OK) for (uint32_t& hp : D->hpos) hp += n_tokens;
     end_of_op();
     return rc;
+}
+
+// Where the time of a one-sequence step on the graph of per-operation kernels goes (diagnostics build only):
+// out == NULL arms the trace for `layer` (the step graphs are recorded again with the trace buffer attached);
+// a later call with a buffer waits for the stream and copies 512 stamps of the most recent step: the four
+// products of the layer (QKV, o-proj, gate/up, down) as [product][CTA 0..7][8] and its attention launch as
+// [CTA 0..31][8], nanoseconds of the GPU's global timer (slot meanings: adam_b200.h).
+extern "C" int adam_b200_decoder_step_trace(uint32_t id, uint32_t layer, long long* out, uint32_t n_words) {
+    Decoder* D = get_dec(id);
+    if (!D) return ADAMAH_ERR_NOT_FOUND;
+#ifdef ADAM_B200_STEP_TRACE
+    const size_t words = 4 * 64 + 32 * 8;
+    if (!out) {
+        if (layer >= D->d.n_layer) return fail(ADAMAH_ERR_INVALID, "decoder_step_trace: layer %u of %u", layer, D->d.n_layer);
+        DCU(cudaStreamSynchronize(g.stream));
+        if (!g_step_trace) DCU(cudaMalloc(&g_step_trace, words * 8));
+        DCU(cudaMemset(g_step_trace, 0, words * 8));
+        g_step_trace_layer = layer;
+        free_graphs(D);
+        return ADAMAH_OK;
+    }
+    if (!g_step_trace) return fail(ADAMAH_ERR_INVALID, "decoder_step_trace: not armed");
+    DCU(cudaStreamSynchronize(g.stream));
+    DCU(cudaMemcpy(out, g_step_trace, (n_words < words ? n_words : words) * 8, cudaMemcpyDeviceToHost));
+    return ADAMAH_OK;
+#else
+    (void)layer; (void)out; (void)n_words;
+    return fail(ADAMAH_ERR_INVALID, "decoder_step_trace: this library was built without ADAM_B200_STEP_TRACE (python -m adam_b200.build --step-trace)");
+#endif
 }
 
 // One part of a token step, enqueued directly on the stream (no graph): see enqueue_part.

@@ -75,6 +75,9 @@ struct GemvArgs {
     float softcap;                  // applied to stored logits only (monotone)
     int max_grid;                   // 0 = launcher's choice; otherwise an upper bound on the CTAs launched
     uint32_t* err;                  // device error word (set by launch_gemv_mma)
+#ifdef ADAM_B200_STEP_TRACE
+    long long* trace;               // 8 stamps per CTA for the first 8 CTAs of the first batch group (NULL = off)
+#endif
 };
 
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }

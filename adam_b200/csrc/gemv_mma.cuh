@@ -100,6 +100,74 @@ __device__ __forceinline__ void block_sum_max(float& sv, float& mv, float* red) 
     sv = a; mv = m;
 }
 
+// CTA-wide reductions with ONE barrier each: warp results go to `buf` (32 floats that no other reduction in
+// flight uses), every warp then folds them itself.
+__device__ __forceinline__ float cta_sum1(float v, float* buf) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (lane == 0) buf[warp] = v;
+    __syncthreads();
+    return warp_sum(lane < nw ? buf[lane] : 0.f);
+}
+__device__ __forceinline__ float cta_max1(float v, float* buf) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    if (lane == 0) buf[warp] = v;
+    __syncthreads();
+    return warp_max(lane < nw ? buf[lane] : -3.402823466e+38f);
+}
+__device__ __forceinline__ void cta_sum_max1(float& sv, float& mv, float* bs, float* bm) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sv += __shfl_xor_sync(0xffffffffu, sv, o);
+        mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, o));
+    }
+    if (lane == 0) { bs[warp] = sv; bm[warp] = mv; }
+    __syncthreads();
+    sv = lane < nw ? bs[lane] : 0.f; mv = lane < nw ? bm[lane] : -3.402823466e+38f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sv += __shfl_xor_sync(0xffffffffu, sv, o);
+        mv = fmaxf(mv, __shfl_xor_sync(0xffffffffu, mv, o));
+    }
+}
+
+// put_x4 plus the block's pre-summed columns: the eight lanes that hold the 32 activations of one block add
+// their bytes and lane 0 of the eight stores sxf * (256 * sum(hi) + sum(mid)) and sxf * 256 * sum(lo), the two
+// values the MMA lanes of batch row b subtract (s_sx[u * NCOL/2 + 2b], [.. + 2b + 1]).  Called by whole warps
+// (k0 = 4 * (float4 index), consecutive over the lanes); `active` is uniform over each group of eight lanes.
+template <int NCOL>
+__device__ __forceinline__ void put_x4_sums(signed char* xb, float* s_sx, int k0, int b, float4 v, bool active, float sxf) {
+    const float f[4] = {v.x, v.y, v.z, v.w};
+    uint32_t wh = 0, wm = 0, wl = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int xi = active ? __float2int_rn(f[i]) : 0;
+        const int lo = ((xi + 128) & 0xFF) - 128;
+        const int r = (xi - lo) >> 8;
+        const int mid = ((r + 128) & 0xFF) - 128;
+        const int hi = (r - mid) >> 8;
+        wh |= (uint32_t)(hi & 0xFF) << (8 * i); wm |= (uint32_t)(mid & 0xFF) << (8 * i); wl |= (uint32_t)(lo & 0xFF) << (8 * i);
+    }
+    if (active) {
+        const int i0 = xb_index<NCOL>(k0, 4 * b);
+        *reinterpret_cast<uint32_t*>(xb + i0) = wh;
+        *reinterpret_cast<uint32_t*>(xb + i0 + 32) = wm;
+        *reinterpret_cast<uint32_t*>(xb + i0 + 64) = wl;
+        *reinterpret_cast<uint32_t*>(xb + i0 + 96) = 0u;
+    }
+    int sh = __dp4a((int)wh, 0x01010101, 0), sm = __dp4a((int)wm, 0x01010101, 0), sl = __dp4a((int)wl, 0x01010101, 0);
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        sh += __shfl_xor_sync(0xffffffffu, sh, o);
+        sm += __shfl_xor_sync(0xffffffffu, sm, o);
+        sl += __shfl_xor_sync(0xffffffffu, sl, o);
+    }
+    if (active && (threadIdx.x & 7) == 0)
+        *reinterpret_cast<float2*>(s_sx + (size_t)(k0 >> 5) * (NCOL / 2) + 2 * b) = make_float2(sxf * (float)(sh * 256 + sm), sxf * (float)(sl * 256));
+}
+
 // ---- bulk-copy pipeline primitives (cp.async.bulk + mbarrier, all waits bounded) ----
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -136,6 +204,11 @@ template <bool PAIR, int WT> struct MmaGeo {
 };
 constexpr int mma_ring_bytes_per_warp(int wt) { return MMA_NSTAGE * (wt == WT_Q4_0 ? 6 * 576 : 4 * 640); }
 
+#ifdef ADAM_B200_STEP_TRACE
+#define GM_STAMP(slot) do { if (threadIdx.x == 0 && blockIdx.y < 8 && blockIdx.x == 0) STEP_STAMP(a_in.trace, blockIdx.y * 8 + (slot)); } while (0)
+#else
+#define GM_STAMP(slot) do { } while (0)
+#endif
 template <int NCOL, bool PAIR, int WT>
 __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const uint8_t* __restrict__ t0, const uint8_t* __restrict__ t1, int KS) {
     constexpr int NI = NCOL == 16 ? 2 : 1;      // MMAs per block
@@ -145,6 +218,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
     // SMs busy where one group alone is bound by latency, and because the group index is the fast
     // grid dimension the CTAs that stream the same tiles are scheduled together, so all groups but
     // the first find them in L2.
+    GM_STAMP(0);
     const uint32_t bx = blockIdx.y, gx = gridDim.y, grp = blockIdx.x;
     GemvArgs a = a_in;
     {
@@ -172,7 +246,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
     __shared__ float s_red[2][MMA_MAX_WARPS][NM][NI][16][2];
     __shared__ __align__(8) uint64_t s_bar[MMA_MAX_WARPS][MMA_NSTAGE];
     __shared__ float s_inv[4];
-    __shared__ float red[66];
+    __shared__ float s_rd[2][3][32];            // scratch of the CTA-wide reductions of the staging (alternating per batch row)
     __shared__ float s_bv[MMA_MAX_WARPS * 4];
     __shared__ int   s_bi[MMA_MAX_WARPS * 4];
     __shared__ bool  s_last;
@@ -234,13 +308,19 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
     }
     // Everything above touches only read-only weights; the activations come from the
     // previous kernel.
+    GM_STAMP(1);
     pdl_launch_dependents();
     pdl_wait();
-    // ---- stage activations as signed bytes (hi, mid | lo) in MMA operand order ----
+    GM_STAMP(2);
+    // ---- stage activations as signed bytes (hi, mid | lo) in MMA operand order, with the per-block sums the
+    // MMA lanes subtract (in the units of the lane that uses them: 256 * first column + second column, times
+    // the offset factor).  One barrier per CTA-wide reduction; loop bodies that hold no element are skipped. ----
     {
         const int n4 = a.K >> 2;
+        const int nj = (n4 + (int)blockDim.x - 1) / (int)blockDim.x;          // float4 per thread
         for (int b = 0; b < NBR && b < a.B; ++b) {
             const size_t row = (size_t)b * a.ldx;
+            float (*rd)[32] = s_rd[b & 1];
             if (a.h_in && n4 <= 3 * (int)blockDim.x) {
                 const float* hp = a.h_in + row;
                 const float* ap = a.add_src ? a.add_src + row : nullptr;
@@ -249,7 +329,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
 #pragma unroll
                 for (int j = 0; j < 3; ++j) {
                     const int i = threadIdx.x + j * blockDim.x;
-                    const bool in = i < n4;
+                    const bool in = j < nj && i < n4;
                     vh[j] = in ? reinterpret_cast<const float4*>(hp)[i] : z4;
                     va[j] = (in && ap) ? reinterpret_cast<const float4*>(ap)[i] : z4;
                 }
@@ -257,8 +337,9 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
                 if (ap && a.w_post) {
                     float ss = 0.f;
 #pragma unroll
-                    for (int j = 0; j < 3; ++j) { ss = fmaf(va[j].x, va[j].x, ss); ss = fmaf(va[j].y, va[j].y, ss); ss = fmaf(va[j].z, va[j].z, ss); ss = fmaf(va[j].w, va[j].w, ss); }
-                    ss = block_sum(ss, red);
+                    for (int j = 0; j < 3; ++j)
+                        if (j < nj) { ss = fmaf(va[j].x, va[j].x, ss); ss = fmaf(va[j].y, va[j].y, ss); ss = fmaf(va[j].z, va[j].z, ss); ss = fmaf(va[j].w, va[j].w, ss); }
+                    ss = cta_sum1(ss, rd[0]);
                     rms_a = sqrtf(ss / (float)a.K + a.eps);
                 }
                 const float rcp_a = __frcp_rn(rms_a);
@@ -266,18 +347,20 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
                 float ss = 0.f, am = 0.f;
 #pragma unroll
                 for (int j = 0; j < 3; ++j) {
-                    if (ap) {
-                        if (a.w_post) {
-                            vh[j].x += div_by(va[j].x, rms_a, rcp_a) * vp[j].x; vh[j].y += div_by(va[j].y, rms_a, rcp_a) * vp[j].y;
-                            vh[j].z += div_by(va[j].z, rms_a, rcp_a) * vp[j].z; vh[j].w += div_by(va[j].w, rms_a, rcp_a) * vp[j].w;
-                        } else { vh[j].x += va[j].x; vh[j].y += va[j].y; vh[j].z += va[j].z; vh[j].w += va[j].w; }
+                    if (j < nj) {
+                        if (ap) {
+                            if (a.w_post) {
+                                vh[j].x += div_by(va[j].x, rms_a, rcp_a) * vp[j].x; vh[j].y += div_by(va[j].y, rms_a, rcp_a) * vp[j].y;
+                                vh[j].z += div_by(va[j].z, rms_a, rcp_a) * vp[j].z; vh[j].w += div_by(va[j].w, rms_a, rcp_a) * vp[j].w;
+                            } else { vh[j].x += va[j].x; vh[j].y += va[j].y; vh[j].z += va[j].z; vh[j].w += va[j].w; }
+                        }
+                        ss = fmaf(vh[j].x, vh[j].x, ss); ss = fmaf(vh[j].y, vh[j].y, ss); ss = fmaf(vh[j].z, vh[j].z, ss); ss = fmaf(vh[j].w, vh[j].w, ss);
+                        am = fmaxf(am, fmaxf(fmaxf(fabsf(vh[j].x * vw[j].x), fabsf(vh[j].y * vw[j].y)), fmaxf(fabsf(vh[j].z * vw[j].z), fabsf(vh[j].w * vw[j].w))));
+                        const int i = threadIdx.x + j * blockDim.x;
+                        if (i < n4 && a.h_out && bx == 0) reinterpret_cast<float4*>(a.h_out + row)[i] = vh[j];
                     }
-                    ss = fmaf(vh[j].x, vh[j].x, ss); ss = fmaf(vh[j].y, vh[j].y, ss); ss = fmaf(vh[j].z, vh[j].z, ss); ss = fmaf(vh[j].w, vh[j].w, ss);
-                    am = fmaxf(am, fmaxf(fmaxf(fabsf(vh[j].x * vw[j].x), fabsf(vh[j].y * vw[j].y)), fmaxf(fabsf(vh[j].z * vw[j].z), fabsf(vh[j].w * vw[j].w))));
-                    const int i = threadIdx.x + j * blockDim.x;
-                    if (i < n4 && a.h_out && bx == 0) reinterpret_cast<float4*>(a.h_out + row)[i] = vh[j];
                 }
-                block_sum_max(ss, am, red);
+                cta_sum_max1(ss, am, rd[1], rd[2]);
                 float rms = 1.f;
                 if (a.w_pre) {
                     rms = sqrtf(ss / (float)a.K + a.eps);
@@ -285,8 +368,10 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
                     am = am * rcp * 1.000001f;             // bound on max |x| (the scale has a factor 2 to spare)
 #pragma unroll
                     for (int j = 0; j < 3; ++j) {
-                        vh[j].x = div_by(vh[j].x, rms, rcp) * vw[j].x; vh[j].y = div_by(vh[j].y, rms, rcp) * vw[j].y;
-                        vh[j].z = div_by(vh[j].z, rms, rcp) * vw[j].z; vh[j].w = div_by(vh[j].w, rms, rcp) * vw[j].w;
+                        if (j < nj) {
+                            vh[j].x = div_by(vh[j].x, rms, rcp) * vw[j].x; vh[j].y = div_by(vh[j].y, rms, rcp) * vw[j].y;
+                            vh[j].z = div_by(vh[j].z, rms, rcp) * vw[j].z; vh[j].w = div_by(vh[j].w, rms, rcp) * vw[j].w;
+                        }
                     }
                 }
                 float s, inv;
@@ -294,8 +379,10 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
                 if (threadIdx.x == 0) s_inv[b] = inv;
 #pragma unroll
                 for (int j = 0; j < 3; ++j) {
-                    const int i = threadIdx.x + j * blockDim.x;
-                    if (i < n4) put_x4<NCOL>(xb, 4 * i, b, make_float4(vh[j].x * s, vh[j].y * s, vh[j].z * s, vh[j].w * s));
+                    if (j < nj) {
+                        const int i = threadIdx.x + j * blockDim.x;
+                        put_x4_sums<NCOL>(xb, s_sx, 4 * i, b, make_float4(vh[j].x * s, vh[j].y * s, vh[j].z * s, vh[j].w * s), i < n4, SXF);
+                    }
                 }
             } else {
                 // plain activations: read once into registers when they fit (K <= 8192), scale, pack
@@ -307,16 +394,19 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int i = threadIdx.x + j * blockDim.x;
-                        v[j] = i < n4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                        v[j] = (j < nj && i < n4) ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) am = fmaxf(am, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
-                    am = block_max(am, red);
+                    for (int j = 0; j < 8; ++j)
+                        if (j < nj) am = fmaxf(am, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+                    am = cta_max1(am, rd[0]);
                     pow2_scale(am, s, inv);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        const int i = threadIdx.x + j * blockDim.x;
-                        if (i < n4) put_x4<NCOL>(xb, 4 * i, b, make_float4(v[j].x * s, v[j].y * s, v[j].z * s, v[j].w * s));
+                        if (j < nj) {
+                            const int i = threadIdx.x + j * blockDim.x;
+                            put_x4_sums<NCOL>(xb, s_sx, 4 * i, b, make_float4(v[j].x * s, v[j].y * s, v[j].z * s, v[j].w * s), i < n4, SXF);
+                        }
                     }
                 } else {
 #pragma unroll 4
@@ -324,36 +414,24 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
                         const float4 v = src[i];
                         am = fmaxf(am, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
                     }
-                    am = block_max(am, red);
+                    am = cta_max1(am, rd[0]);
                     pow2_scale(am, s, inv);
-#pragma unroll 4
-                    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-                        const float4 v = src[i];
-                        put_x4<NCOL>(xb, 4 * i, b, make_float4(v.x * s, v.y * s, v.z * s, v.w * s));
+                    for (int j = 0; j < nj; ++j) {
+                        const int i = threadIdx.x + j * blockDim.x;
+                        const float4 v = i < n4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                        put_x4_sums<NCOL>(xb, s_sx, 4 * i, b, make_float4(v.x * s, v.y * s, v.z * s, v.w * s), i < n4, SXF);
                     }
                 }
                 if (threadIdx.x == 0) s_inv[b] = inv;
             }
         }
+        // batch rows of this pass that the call does not have: their pre-summed entries are read, never used
+        if (a.B < NBR) {
+            for (int i = threadIdx.x; i < units * NPR; i += blockDim.x) if (((i % NPR) >> 1) >= a.B) s_sx[i] = 0.f;
+        }
         __syncthreads();
     }
-
-    // per-block, per-column-pair sums of the integer activations, in the units of the
-    // lane that uses them (256 * first column + second column) and already times -8
-    for (int i = threadIdx.x; i < units * NPR; i += blockDim.x) {
-        const int u = i / NPR, pr = i % NPR;
-        float v = 0.f;
-        if ((pr >> 1) < a.B) {
-            const int* c0 = reinterpret_cast<const int*>(xb + (size_t)(u * NCOL + 2 * pr) * 32);
-            const int* c1 = c0 + 8;
-            int s0 = 0, s1 = 0;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) { s0 = __dp4a(c0[e], 0x01010101, s0); s1 = __dp4a(c1[e], 0x01010101, s1); }
-            v = SXF * (float)(s0 * 256 + s1);
-        }
-        s_sx[i] = v;
-    }
-    __syncthreads();
+    GM_STAMP(3);
     float best_v[NI]; int best_i[NI];                       // arg-max candidates of batch rows 2i + t/2
     float acc[NM][NI][2];
 #pragma unroll
@@ -522,6 +600,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
             }
         }
     }
+    GM_STAMP(4);
     if (timed_out) {
         // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
         for (int s2 = 0; s2 < MMA_NSTAGE; ++s2) { mbar_wait(&s_bar[warp][s2], 0u); mbar_wait(&s_bar[warp][s2], 1u); }

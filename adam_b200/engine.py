@@ -259,6 +259,17 @@ class ADAMEngine:
         self._check(self._lib.adam_b200_decoder_token_trace(self._dec, int(layer) | (int(phase) << 16), out.ctypes.data, ctypes.byref(n)), "adam_b200_decoder_token_trace")
         return out[:int(n.value)]
 
+    def step_trace(self, layer: Optional[int] = None):
+        """Diagnostics build only (``python -m adam_b200.build --step-trace``).  ``step_trace(layer)`` arms the trace
+        for one layer of the default one-sequence step; ``step_trace()`` returns the stamps of the latest step in
+        nanoseconds: ``(products[4, 8, 8], attention[32, 8])`` (slot meanings: ``adam_b200_decoder_step_trace``)."""
+        if layer is not None:
+            self._check(self._lib.adam_b200_decoder_step_trace(self._dec, int(layer), None, 0), "adam_b200_decoder_step_trace")
+            return None
+        out = np.zeros(512, np.int64)
+        self._check(self._lib.adam_b200_decoder_step_trace(self._dec, 0, out.ctypes.data, 512), "adam_b200_decoder_step_trace")
+        return out[:256].reshape(4, 8, 8), out[256:512].reshape(32, 8)
+
     def logits_trace(self, tokens: Sequence[int], direct: bool = True) -> np.ndarray:
         """Teacher-forced pass over ``tokens``: the soft-capped logits after every
         position, ``[len(tokens), n_vocab]`` (for parity checks)."""

@@ -33,6 +33,8 @@ Other modes (one JSON line per result; what the summaries under profiles/ were m
     python bench.py --mode tp [--layers L --batch B --allreduce p2p|nccl --shard-of N]   27B-shape tensor-parallel decode
     python bench.py --mode token-once [--layers L] [--chain]                        a few token steps (for ncu): token kernel, or the graph of kernels
     python bench.py --mode token-trace [--layers L]                                 per-phase times inside the token kernel (SM clock stamps)
+    ADAM_B200_LIB_PATH=adam_b200/libadam_b200_trace.so python bench.py --mode step-trace   phase times of one layer's five kernels in the default step
+                                                                                    (needs `python -m adam_b200.build --step-trace`)
 """
 from __future__ import annotations
 
@@ -440,7 +442,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the GEMV sweep of the default mode")
     ap.add_argument("--no-tp", action="store_true", help="skip the 27B-shape tensor-parallel decode of the default mode")
-    ap.add_argument("--mode", default="decode", choices=["decode", "gemv", "gemv-once", "batch", "tp", "token-once", "token-trace"])
+    ap.add_argument("--mode", default="decode", choices=["decode", "gemv", "gemv-once", "batch", "tp", "token-once", "token-trace", "step-trace"])
     ap.add_argument("--type", type=int, default=0, help="gemv / tp modes: GGML block type (2 = Q4_0, 12 = Q4_K)")
     ap.add_argument("--n", type=int, default=0)
     ap.add_argument("--k", type=int, default=0)
@@ -455,7 +457,7 @@ def main():
     ap.add_argument("--shard-of", type=int, default=0, help="tp mode, one process: rank 0's shard of an N-way split without collectives")
     args = ap.parse_args()
     rank, local_rank, world = dist_env()
-    if args.mode in ("gemv", "gemv-once", "batch", "token-once", "token-trace"):
+    if args.mode in ("gemv", "gemv-once", "batch", "token-once", "token-trace", "step-trace"):
         return other_modes(args)
     if args.gpus > 1 and world == 1:
         # not under torchrun: relaunch one rank per GPU on this node
@@ -729,6 +731,47 @@ def token_trace(gpu, args):
     return out
 
 
+def step_trace(gpu, args):
+    """Where the time of one layer goes in the default one-sequence step (CUDA graph of per-operation kernels): the four
+    products and the attention launch of one layer stamp the GPU's nanosecond timer at their phase boundaries
+    (``adam_b200_decoder_step_trace``; needs the diagnostics library, see the module docstring).  The stamps are those of
+    the last of ``--steps`` back-to-back steps, so clocks and caches are those of the benchmark's timed loop."""
+    from adam_b200 import synth
+    from adam_b200.config import gemma3_1b, with_layers
+    from adam_b200.engine import ADAMEngine
+    cfg = gemma3_1b()
+    if args.layers:
+        cfg = with_layers(cfg, args.layers)
+    steps = max(args.steps, 64)
+    tensors = synth.build_model_cuda(gpu, cfg, seed=0)
+    eng = ADAMEngine(gpu, cfg, tensors, kv_cap=PROMPT_LEN + steps + 32, kv_dtype="f16", window=True)
+    eng.begin([synth.random_prompt(cfg.n_vocab, PROMPT_LEN, seed=1)], [PROMPT_LEN + steps + 24])
+    layer = min(5, cfg.n_layer - 1)
+    eng.step_trace(layer)
+    gpu.batch_begin(); eng.prefill(PROMPT_LEN - 1); eng.step(8, lm_head=True); gpu.batch_end()
+    gpu.batch_begin(); gpu.timer_begin(); eng.step(steps, lm_head=True); ms = gpu.timer_end(); gpu.batch_end()
+    prod, att = eng.step_trace()
+    t0 = int(prod[0, 0, 2])                     # the moment the layer's first kernel may read its input
+    names = ["qkv", "o_proj", "gate_up", "down"]
+    out = {"traced_layer": layer, "context": PROMPT_LEN + 8 + steps, "ms_per_token": ms / steps, "unit": "us since the QKV kernel's dependency wait ended (CTA 0)", "kernels": {}}
+    for k, nm in enumerate(names):
+        r = prod[k, 0].astype(np.int64)
+        out["kernels"][nm] = {"started": (r[0] - t0) / 1e3, "prologue_done": (r[1] - t0) / 1e3, "wait_over": (r[2] - t0) / 1e3,
+                              "input_staged": (r[3] - t0) / 1e3, "products_done": (r[4] - t0) / 1e3}
+    live = att[(att[:, 4] > 0)]
+    if len(live):
+        last = att[att[:, 7] > 0]
+        out["kernels"]["attention"] = {
+            "ctas_with_positions": int(len(live)), "started": float((live[:, 0].min() - t0) / 1e3), "rows_requested": float((live[:, 1].max() - t0) / 1e3),
+            "wait_over": float((live[:, 2].max() - t0) / 1e3), "rows_normed_rotated": float((live[:, 3].max() - t0) / 1e3),
+            "positions_done": float((live[:, 4].max() - t0) / 1e3), "partial_stored": float((live[:, 5].max() - t0) / 1e3) if (live[:, 5] > 0).any() else None,
+            "ticket_taken": float((live[:, 6].max() - t0) / 1e3) if (live[:, 6] > 0).any() else None,
+            "splits_merged": float((last[:, 7].max() - t0) / 1e3) if len(last) else None}
+    out["device_error"] = gpu.device_error()
+    eng.close()
+    return out
+
+
 def other_modes(args):
     """Single-GPU modes besides the decode benchmark (see the module docstring)."""
     if args.mode == "batch":
@@ -747,6 +790,8 @@ def other_modes(args):
                 print(json.dumps(gemv_shape(gpu, A, *sh, tile=not args.no_tile)), flush=True)
         elif args.mode == "token-trace":
             print(json.dumps(token_trace(gpu, args)))
+        elif args.mode == "step-trace":
+            print(json.dumps(step_trace(gpu, args)))
         else:       # token-once: prompt, then a few single-launch token steps
             from adam_b200 import synth
             from adam_b200.config import gemma3_1b, with_layers

@@ -389,6 +389,15 @@ int adam_b200_decoder_prefill_part(uint32_t id, uint32_t n_tokens, uint32_t part
  * (layer & 0xFFFF), 10..13 LM head, 16..22 inside product (layer >> 16) of that layer; out[cta * 32 + slot],
  * out holds 32 * 256 values. */
 int adam_b200_decoder_token_trace(uint32_t id, uint32_t layer, long long* out, uint32_t* n_cta_out);
+/* Diagnostics of the default one-sequence step (the CUDA graph of per-operation kernels; no counterpart in the
+ * reference).  Only a library built with -DADAM_B200_STEP_TRACE (`python -m adam_b200.build --step-trace`) records
+ * anything; the regular build returns ADAMAH_ERR_INVALID.  out == NULL arms the trace for `layer`; after some steps a
+ * call with out (512 values) returns the stamps of the latest step in nanoseconds of the GPU's global timer:
+ *   out[(p * 8 + cta) * 8 + slot], p = 0 QKV, 1 o-proj, 2 gate/up, 3 down, cta = 0..7, slots: 0 kernel start,
+ *     1 prologue done (weight copies requested), 2 dependency wait over, 3 input staged, 4 products done;
+ *   out[256 + cta * 8 + slot], attention CTAs 0..31, slots: 0 start, 1 cached rows requested, 2 wait over, 3 query /
+ *     key rows normed and rotated, 4 positions done, 5 partial result stored, 6 ticket taken, 7 splits merged (last CTA). */
+int adam_b200_decoder_step_trace(uint32_t id, uint32_t layer, long long* out, uint32_t n_words);
 /* Test hook for the bounded device-side waits (no counterpart in the reference): launches one token step of the
  * single active sequence on the token kernel with its last CTA left out and every wait limited to wait_us
  * microseconds; the waits run out, the kernel records error bit 2 (adam_b200_device_error), sets the decoder's
