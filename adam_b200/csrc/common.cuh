@@ -103,6 +103,20 @@ inline cudaError_t launch_k(void (*k)(KArgs...), dim3 grid, dim3 block, size_t s
 }
 
 
+// The same with the CTAs of a launch grouped into thread-block clusters of `cluster_x` along x (gridDim.x a multiple of it).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k_cluster(void (*k)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, unsigned cluster_x, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = cluster_x; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, k, KArgs(args)...);
+}
+
 // ---- step trace (diagnostics build only: -DADAM_B200_STEP_TRACE, `python -m adam_b200.build --step-trace`) ----
 // Kernels of the decode step stamp the global nanosecond timer at their phase boundaries into a buffer the host
 // reads back (adam_b200_decoder_step_trace).  The regular build compiles none of it: no field, no parameter, no test.

@@ -159,6 +159,23 @@ __global__ void k_embed(const WeightRef w, uint32_t n_embd, uint32_t n_vocab, fl
     }
 }
 
+// Cluster primitives of the attention launch whose position splits form one thread-block cluster: the splits'
+// partial results go to the first CTA's shared memory and meet at the hardware cluster barrier (every thread of
+// every CTA arrives exactly once per phase; a CTA may exit after its last arrive).
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+__device__ __forceinline__ uint32_t dsmem_addr_rank0(const void* p) {          // address of `p` in the cluster's CTA 0
+    uint32_t r;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(p)), "r"(0));
+    return r;
+}
+__device__ __forceinline__ void st_dsmem4(uint32_t addr, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" :: "r"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_dsmem2(uint32_t addr, float2 v) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" :: "r"(addr), "f"(v.x), "f"(v.y) : "memory");
+}
+
 // Decode attention for one (split, kv head, sequence), all query heads that share
 // the kv head, with the steps that precede it folded in:
 //   * per-head RMSNorm + half-split RoPE of the query rows (map_qk_norm_rope_x.comp),
@@ -199,6 +216,10 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
 #define AT_STAMP(slot) do { } while (0)
 #endif
     AT_STAMP(0);
+    // n_splits_max == 0: the gridDim.x splits of a (sequence, head group) are one thread-block cluster and merge
+    // through CTA 0's shared memory instead of global memory, a ticket and the last CTA to arrive.
+    const bool cmerge = n_splits_max == 0;
+    if (cmerge) cluster_arrive();               // "this CTA runs": waited for before the first store into CTA 0
     // row_seq / row_pos != NULL: chunked prefill.  Row b of qkv/out belongs to sequence row_seq[b] at position
     // row_pos[b], and the keys and values of the whole chunk are already in the cache (k_kv_append ran before).
     const bool appended = row_pos != nullptr;
@@ -261,7 +282,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     const uint32_t start = (window > 0 && seq > window) ? seq - window : 0;
     const uint32_t c_first = start / CP, n_chunks = (seq - 1) / CP - c_first + 1;
     const uint32_t n_act = min((uint32_t)gridDim.x, (n_chunks + cpc_min - 1) / cpc_min);
-    if (split >= n_act) return;
+    if (split >= n_act) { if (cmerge) { cluster_wait(); cluster_arrive(); } return; }
     const uint32_t cpc = (n_chunks + n_act - 1) / n_act;
     const uint32_t c0 = min(c_first + split * cpc, c_first + n_chunks), c1 = min(c_first + n_chunks, c0 + cpc);
     const uint32_t c_new = appended ? 0xFFFFFFFFu : (uint32_t)p / CP;      // chunk whose newest row comes from this step's q/k/v
@@ -270,6 +291,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     float* s_kn = s_q + gs * hd;                // [hd] newest key (as stored)
     float* s_vn = s_kn + hd;                    // [hd] newest value (as stored)
     float* s_o = s_vn + hd;                     // [8 warps][gs][hd]
+    float* s_cp = s_o + 8 * gs * hd;            // cluster merge, CTA 0 only: [split][gs * hd + 4 * gs] (16-byte aligned rows)
     const bool page8 = (geo.page % CP) == 0;
 
     // Rows of chunk c.  Every load is unconditional (a predicated load would have to be
@@ -516,6 +538,7 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
     float* po = part_o + ((size_t)slot_y * n_splits_max + split) * gs * hd;
     float* pml = part_ml + ((size_t)slot_y * n_splits_max + split) * gs * 2;
     float* orow = out + ((size_t)b * n_head + head0) * hd;
+    if (cmerge && n_act > 1 && split != 0) cluster_wait();      // CTA 0 of the cluster is running: its shared memory can be written
     for (uint32_t i4 = tid; i4 < n_out4; i4 += blockDim.x) {
         const uint32_t g = (i4 * 4) / hd;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -528,10 +551,45 @@ __global__ void __launch_bounds__(256) k_attention(const float* __restrict__ qkv
             L = fmaf(ww, s_l[w][g], L);
         }
         if (n_act == 1) { v.x /= L; v.y /= L; v.z /= L; v.w /= L; reinterpret_cast<float4*>(orow)[i4] = v; }
-        else {
+        else if (cmerge) {
+            float* mine = s_cp + (size_t)split * (gs * hd + 4 * gs);
+            if (split == 0) {
+                reinterpret_cast<float4*>(mine)[i4] = v;
+                if ((i4 * 4) % hd == 0) *reinterpret_cast<float2*>(mine + gs * hd + g * 2) = make_float2(s_M[g], L);
+            } else {
+                st_dsmem4(dsmem_addr_rank0(mine + i4 * 4), v);
+                if ((i4 * 4) % hd == 0) st_dsmem2(dsmem_addr_rank0(mine + gs * hd + g * 2), make_float2(s_M[g], L));
+            }
+        } else {
             reinterpret_cast<float4*>(po)[i4] = v;
             if ((i4 * 4) % hd == 0) *reinterpret_cast<float2*>(pml + g * 2) = make_float2(s_M[g], L);
         }
+    }
+    if (cmerge) {
+        // every thread is here exactly once, whatever n_act is
+        if (n_act == 1) { cluster_wait(); cluster_arrive(); return; }
+        if (split != 0) { cluster_arrive(); return; }
+        cluster_wait();
+        cluster_arrive();
+        cluster_wait();                         // ---- every split's partial result is in this CTA's shared memory ----
+        const uint32_t pstride = gs * hd + 4 * gs;
+        for (uint32_t i4 = tid; i4 < n_out4; i4 += blockDim.x) {
+            const uint32_t g = (i4 * 4) / hd;
+            float M = NEG;
+            for (uint32_t s0 = 0; s0 < n_act; ++s0) M = fmaxf(M, s_cp[(size_t)s0 * pstride + gs * hd + g * 2]);
+            float den = 0.f;
+            float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (uint32_t s0 = 0; s0 < n_act; ++s0) {
+                const float* ps = s_cp + (size_t)s0 * pstride;
+                const float w = expf(ps[gs * hd + g * 2] - M);
+                const float4 x = reinterpret_cast<const float4*>(ps)[i4];
+                num.x = fmaf(w, x.x, num.x); num.y = fmaf(w, x.y, num.y); num.z = fmaf(w, x.z, num.z); num.w = fmaf(w, x.w, num.w);
+                den = fmaf(w, ps[gs * hd + g * 2 + 1], den);
+            }
+            reinterpret_cast<float4*>(orow)[i4] = make_float4(num.x / den, num.y / den, num.z / den, num.w / den);
+        }
+        AT_STAMP(7);
+        return;
     }
     if (n_act == 1) return;
     AT_STAMP(5);
@@ -756,6 +814,50 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
     (void)pairs;
     AttnKernel kern = hpc <= 1 ? pick_attn_hd<T, 1>(d.head_dim) : hpc <= 2 ? pick_attn_hd<T, 2>(d.head_dim)
                     : hpc <= 4 ? pick_attn_hd<T, 4>(d.head_dim) : pick_attn_hd<T, 8>(d.head_dim);
+    // Few (sequence, head) pairs in flight: the position splits of a pair form one thread-block cluster of 8 CTAs and merge
+    // through shared memory (no partial results in global memory, no ticket, no last-CTA pass: 3 us less per launch at the
+    // 1B shape).  A cluster covers any context, its CTAs taking more chunks each, so layers that may attend to more than
+    // 2048 positions keep the wider grid of independent splits.  (Clusters of 16 were measured slower: they start later,
+    // and so does every kernel behind them.)  ADAM_B200_ATTN_CLUSTER=0 turns the path off, =16 allows clusters of 16.
+    static const int cluster_env = getenv("ADAM_B200_ATTN_CLUSTER") ? atoi(getenv("ADAM_B200_ATTN_CLUSTER")) : 8;
+    static const uint32_t cluster_work = getenv("ADAM_B200_ATTN_CLUSTER_WORK") ? (uint32_t)atoi(getenv("ADAM_B200_ATTN_CLUSTER_WORK")) : 8u;
+    const uint32_t reach = window ? (window < d.kv_cap ? window : d.kv_cap) : d.kv_cap;
+    if (cluster_env != 0 && !prefill && work <= cluster_work && reach <= 2048u) {
+        struct Known { AttnKernel k; unsigned cs; };
+        static Known known[16]; static int n_known = 0;
+        int cs = -1;
+        for (int i = 0; i < n_known; ++i) if (known[i].k == kern) cs = (int)known[i].cs;
+        const auto smem_for = [&](unsigned c) { return smem + (size_t)c * hpc * (d.head_dim + 4) * 4; };
+        if (cs < 0) {
+            cs = 0;
+            const unsigned c_max = cluster_env == 16 ? 16u : 8u;
+            if (c_max > 8 && cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) cudaGetLastError();
+            for (unsigned c = c_max; c >= 8 && !cs; c >>= 1) {
+                if (cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_for(c)) != cudaSuccess) { cudaGetLastError(); continue; }
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(c, grid.y, 1); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem_for(c);
+                cudaLaunchAttribute at[1];
+                at[0].id = cudaLaunchAttributeClusterDimension;
+                at[0].val.clusterDim.x = c; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+                cfg.attrs = at; cfg.numAttrs = 1;
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, (const void*)kern, &cfg) != cudaSuccess) { cudaGetLastError(); continue; }
+                if (n >= (int)(grid.y * grid.z)) cs = (int)c;
+            }
+            if (n_known < 16) { known[n_known].k = kern; known[n_known].cs = (unsigned)cs; ++n_known; }
+        }
+        if (cs > 0) {
+            grid.x = (unsigned)cs;
+            if (launch_k_cluster(kern, grid, dim3(256), smem_for((unsigned)cs), g.stream, g.pdl, (unsigned)cs, D->qkv, qkv_ld, ly.norm[NORM_Q], ly.norm[NORM_K], d.norm_eps,
+                                 D->rope_cos[which], D->rope_sin[which], D->rope_pos[which],
+                                 D->kv_pool, geo, D->block_table, D->pos, d.n_head, L, window, d.attn_scale,
+                                 d.attn_softcap, D->attn_out, D->part_o, D->part_ml, D->attn_ticket, 0u, hpc | (cpc << 16),
+                                 (const int32_t*)nullptr, (const int32_t*)nullptr, g.dev_err STEP_TRACE_ARG((g_step_trace && L == g_step_trace_layer) ? g_step_trace + 4 * 64 : nullptr)) != cudaSuccess)
+                return fail(ADAMAH_ERR_BACKEND, "attention: cluster launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+            count_launch();
+            return ADAMAH_OK;
+        }
+    }
     if (smem > 48 * 1024) DCU(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     launch_k(kern, grid, dim3(256), smem, g.stream, g.pdl, D->qkv, qkv_ld, ly.norm[NORM_Q], ly.norm[NORM_K], d.norm_eps,
              D->rope_cos[which], D->rope_sin[which], D->rope_pos[which],

@@ -152,19 +152,15 @@ def test_plan_with_an_argument_that_has_no_runtime_form_falls_back_to_host_subst
         gpu.clear_decode_plan(4)
 
 
-@pytest.mark.gpu
-def test_step_trace_needs_the_diagnostics_build():
+def test_step_trace_needs_the_diagnostics_build(gpu):
     """The regular library compiles no trace stamps: the diagnostics entry point says so instead of returning zeros."""
-    import adam_b200 as A
     from adam_b200 import synth
     from adam_b200.config import tiny_gemma3
     from adam_b200.engine import ADAMEngine
-    gpu = A.init()
+    cfg = tiny_gemma3(n_layer=2)
+    eng = ADAMEngine(gpu, cfg, synth.build_model(cfg, seed=3), kv_cap=64)
     try:
-        cfg = tiny_gemma3(n_layer=2)
-        eng = ADAMEngine(gpu, cfg, synth.build_model(cfg, seed=3), kv_cap=64)
         with pytest.raises(RuntimeError, match="STEP_TRACE"):
             eng.step_trace(0)
-        eng.close()
     finally:
-        gpu.shutdown()
+        eng.close()
