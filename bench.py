@@ -63,7 +63,7 @@ LMHEAD_DRAM_TRAFFIC = 169_949_184 + 4_576_256
 TOKEN_DRAM_TRAFFIC = 566_583_808 + 4_014_848
 # and summed over the 133 kernels of one step of the CUDA-graph path, from an ncu capture of
 # `bench.py --mode token-once --chain --steps 3` (metrics gpu__time_duration, dram__bytes_read, dram__bytes_write)
-CHAIN_DRAM_TRAFFIC = 576_993_536 + 123_989
+CHAIN_DRAM_TRAFFIC = 576_930_645 + 333_824
 
 
 def measured_peaks():
