@@ -50,22 +50,27 @@ __device__ __forceinline__ int xb_index(int k, int col) {
     return ((u * NCOL + col) * 4 + ((w & 15) >> 2)) * 8 + (w >> 4) * 4 + (w & 3);
 }
 
+// Four scaled activations (integers of at most 23 bits after rounding) as three words of signed bytes: x = hi * 65536 +
+// mid * 256 + lo with mid, lo in [-128, 127].  Adding 0x808080 makes every digit of the base-256 representation its value
+// plus 128 (the carries of the signed digits are those of the addition); flipping bit 7 of each byte turns that into the
+// two's-complement byte.  Then a 4 x 3 byte transpose.
+__device__ __forceinline__ void split_x4(const float (&f)[4], bool active, uint32_t& wh, uint32_t& wm, uint32_t& wl) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = active ? (((uint32_t)__float2int_rn(f[i]) + 0x00808080u) ^ 0x00808080u) : 0u;
+    wl = __byte_perm(__byte_perm(w[0], w[1], 0x0040), __byte_perm(w[2], w[3], 0x0040), 0x5410);
+    wm = __byte_perm(__byte_perm(w[0], w[1], 0x0051), __byte_perm(w[2], w[3], 0x0051), 0x5410);
+    wh = __byte_perm(__byte_perm(w[0], w[1], 0x0062), __byte_perm(w[2], w[3], 0x0062), 0x5410);
+}
+
 // Four consecutive scaled activations (k0 a multiple of 4) of batch row b: round to
 // integers, split into three signed bytes each, and store one 32-bit word into each
 // of the row's four columns (hi, mid, lo, zero).
 template <int NCOL>
 __device__ __forceinline__ void put_x4(signed char* xb, int k0, int b, float4 v) {
     const float f[4] = {v.x, v.y, v.z, v.w};
-    uint32_t wh = 0, wm = 0, wl = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int xi = __float2int_rn(f[i]);
-        const int lo = ((xi + 128) & 0xFF) - 128;
-        const int r = (xi - lo) >> 8;
-        const int mid = ((r + 128) & 0xFF) - 128;
-        const int hi = (r - mid) >> 8;
-        wh |= (uint32_t)(hi & 0xFF) << (8 * i); wm |= (uint32_t)(mid & 0xFF) << (8 * i); wl |= (uint32_t)(lo & 0xFF) << (8 * i);
-    }
+    uint32_t wh, wm, wl;
+    split_x4(f, true, wh, wm, wl);
     const int c0 = 4 * b;
     const int i0 = xb_index<NCOL>(k0, c0);          // columns of one block are 32 bytes apart
     *reinterpret_cast<uint32_t*>(xb + i0) = wh;
@@ -140,16 +145,8 @@ __device__ __forceinline__ void cta_sum_max1(float& sv, float& mv, float* bs, fl
 template <int NCOL>
 __device__ __forceinline__ void put_x4_sums(signed char* xb, float* s_sx, int k0, int b, float4 v, bool active, float sxf) {
     const float f[4] = {v.x, v.y, v.z, v.w};
-    uint32_t wh = 0, wm = 0, wl = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int xi = active ? __float2int_rn(f[i]) : 0;
-        const int lo = ((xi + 128) & 0xFF) - 128;
-        const int r = (xi - lo) >> 8;
-        const int mid = ((r + 128) & 0xFF) - 128;
-        const int hi = (r - mid) >> 8;
-        wh |= (uint32_t)(hi & 0xFF) << (8 * i); wm |= (uint32_t)(mid & 0xFF) << (8 * i); wl |= (uint32_t)(lo & 0xFF) << (8 * i);
-    }
+    uint32_t wh, wm, wl;
+    split_x4(f, active, wh, wm, wl);
     if (active) {
         const int i0 = xb_index<NCOL>(k0, 4 * b);
         *reinterpret_cast<uint32_t*>(xb + i0) = wh;
@@ -195,21 +192,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 // bytes per tile pair (16 rows x 64 weights): 512 nibble bytes + 32 fp16 scales (Q4_0), or
 // + 64 bytes of 6-bit scales/mins as bytes + 64 bytes of fp16 (d, dmin) per row (Q4_K)
 constexpr int mma_tile_bytes(int wt) { return wt == WT_Q4_0 ? 576 : 640; }
-constexpr int MMA_NSTAGE = 3;              // ring stages per warp
+constexpr int MMA_NSTAGE = 3;              // ring stages per warp (2 in the instance for long activation vectors, which leave less shared memory)
 constexpr int MMA_MAX_WARPS = 16;
 template <bool PAIR, int WT> struct MmaGeo {
     static constexpr int TILE = mma_tile_bytes(WT);
     static constexpr int CH = WT == WT_Q4_0 ? (PAIR ? 3 : 6) : (PAIR ? 2 : 4);   // tile pairs per stage and matrix
     static constexpr int STAGE_BYTES = CH * TILE * (PAIR ? 2 : 1);               // 3456 (Q4_0), 2560 (Q4_K)
 };
-constexpr int mma_ring_bytes_per_warp(int wt) { return MMA_NSTAGE * (wt == WT_Q4_0 ? 6 * 576 : 4 * 640); }
+constexpr int mma_ring_bytes_per_warp(int wt, int n_stage = MMA_NSTAGE) { return n_stage * (wt == WT_Q4_0 ? 6 * 576 : 4 * 640); }
 
 #ifdef ADAM_B200_STEP_TRACE
 #define GM_STAMP(slot) do { if (threadIdx.x == 0 && blockIdx.y < 8 && blockIdx.x == 0) STEP_STAMP(a_in.trace, blockIdx.y * 8 + (slot)); } while (0)
 #else
 #define GM_STAMP(slot) do { } while (0)
 #endif
-template <int NCOL, bool PAIR, int WT>
+template <int NCOL, bool PAIR, int WT, int NST = MMA_NSTAGE>      // NST: ring stages per warp
 __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const uint8_t* __restrict__ t0, const uint8_t* __restrict__ t1, int KS) {
     constexpr int NI = NCOL == 16 ? 2 : 1;      // MMAs per block
     constexpr int NBR = NCOL / 4;               // batch rows staged
@@ -244,7 +241,9 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
     constexpr float SXF = WT == WT_Q4_0 ? -8.0f : -1.0f;    // Q4_0: d*(q-8); Q4_K: (d*sc)*q - (dmin*m)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ float s_red[2][MMA_MAX_WARPS][NM][NI][16][2];
-    __shared__ __align__(8) uint64_t s_bar[MMA_MAX_WARPS][MMA_NSTAGE];
+    __shared__ __align__(8) uint64_t s_bar[MMA_MAX_WARPS][NST];
+    __shared__ __align__(8) uint64_t s_xbar;                // bulk copy of a long activation vector
+    bool x_timed_out = false;
     __shared__ float s_inv[4];
     __shared__ float s_rd[2][3][32];            // scratch of the CTA-wide reductions of the staging (alternating per batch row)
     __shared__ float s_bv[MMA_MAX_WARPS * 4];
@@ -264,12 +263,13 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
     // one cp.async.bulk per matrix, completion counted on the stage's mbarrier.
     signed char* xb = reinterpret_cast<signed char*>(smem_raw);                            // [units][NCOL][32]
     float* s_sx = reinterpret_cast<float*>(smem_raw + (size_t)units * NCOL * 32);          // [units][NPR], already times -8
-    unsigned char* ring = smem_raw + (((size_t)units * (NCOL * 32 + NPR * 4) + 127) & ~(size_t)127) + (size_t)warp * MMA_NSTAGE * STAGE_BYTES;
+    unsigned char* ring = smem_raw + (((size_t)units * (NCOL * 32 + NPR * 4) + 127) & ~(size_t)127) + (size_t)warp * NST * STAGE_BYTES;
     const int nch = (np + CH - 1) / CH;                     // chunks per row group for this warp
     const int n_chunks = my_sets * nch;
     if (lane == 0) {
 #pragma unroll
-        for (int st = 0; st < MMA_NSTAGE; ++st) mbar_init(&s_bar[warp][st], 1);
+        for (int st = 0; st < NST; ++st) mbar_init(&s_bar[warp][st], 1);
+        if (NST == 2 && warp == 0) mbar_init(&s_xbar, 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -285,12 +285,12 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
         bulk_g2s(dst, t0 + off, (uint32_t)(n * MMA_TILE), &s_bar[warp][i_st]);
         if (PAIR) bulk_g2s(dst + CH * MMA_TILE, t1 + off, (uint32_t)(n * MMA_TILE), &s_bar[warp][i_st]);
         ++i_c;
-        if (++i_st == MMA_NSTAGE) i_st = 0;
+        if (++i_st == NST) i_st = 0;
         if (++i_j == nch) { i_j = 0; i_rg += (int)gx * RG; }
     };
     if (lane == 0) {
 #pragma unroll
-        for (int c = 0; c < MMA_NSTAGE; ++c) if (i_c < n_chunks) issue_next();
+        for (int c = 0; c < NST; ++c) if (i_c < n_chunks) issue_next();
     }
     // Norm weights of the input chain (read-only, like the matrix): fetched ahead of the wait.
     float4 vp[3], vw[3];
@@ -409,17 +409,70 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
                         }
                     }
                 } else {
+                    // Long vectors.  With one batch row per pass the staged form of 32 activations takes the same 128 bytes
+                    // as the floats themselves: a bulk copy parks the floats where their bytes will go, one pass over
+                    // shared memory finds the maximum, a second one splits them in place.  The eight lanes
+                    // that share a block read their floats before any of them stores bytes.  With more rows per pass the
+                    // second pass reads global memory again.
+                    float4* park = reinterpret_cast<float4*>(xb);
+                    if constexpr (NCOL == 4 && NST == 2) {       // the instance the launcher picks for long plain vectors
+                        // the whole vector in one bulk copy: one memory round trip however long it is
+                        __syncthreads();                        // s_xbar was initialised by thread 0
+                        if (threadIdx.x == 0) {
+                            mbar_expect_tx(&s_xbar, (uint32_t)n4 * 16u);
+                            bulk_g2s(park, src, (uint32_t)n4 * 16u, &s_xbar);
+                        }
+                        if (!mbar_wait(&s_xbar, 0u)) { x_timed_out = true; if (threadIdx.x == 0) atomicOr(a.err, DEVERR_WAIT); }
+                        GM_STAMP(5);
 #pragma unroll 4
-                    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-                        const float4 v = src[i];
-                        am = fmaxf(am, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                    }
-                    am = cta_max1(am, rd[0]);
-                    pow2_scale(am, s, inv);
-                    for (int j = 0; j < nj; ++j) {
-                        const int i = threadIdx.x + j * blockDim.x;
-                        const float4 v = i < n4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-                        put_x4_sums<NCOL>(xb, s_sx, 4 * i, b, make_float4(v.x * s, v.y * s, v.z * s, v.w * s), i < n4, SXF);
+                        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+                            const float4 v = park[i];
+                            am = fmaxf(am, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                        }
+                        am = cta_max1(am, rd[0]);
+                        GM_STAMP(6);
+                        pow2_scale(am, s, inv);
+                        // four blocks per lane at a time, so that their shuffle chains overlap
+                        for (int j0 = 0; j0 < nj; j0 += 4) {
+                            float4 v4[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const int i = threadIdx.x + (j0 + u) * blockDim.x;
+                                v4[u] = (j0 + u < nj && i < n4) ? park[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                if (j0 + u < nj) {
+                                    const int i = threadIdx.x + (j0 + u) * blockDim.x;
+                                    put_x4_sums<NCOL>(xb, s_sx, 4 * i, b, make_float4(v4[u].x * s, v4[u].y * s, v4[u].z * s, v4[u].w * s), i < n4, SXF);
+                                }
+                            }
+                        }
+                    } else {
+#pragma unroll 4
+                        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+                            const float4 v = src[i];
+                            am = fmaxf(am, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                        }
+                        am = cta_max1(am, rd[0]);
+                        pow2_scale(am, s, inv);
+                        // second pass in groups of four: the loads of a group are all requested before the first is used
+                        for (int j0 = 0; j0 < nj; j0 += 4) {
+                            float4 v4[4];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                const int i = threadIdx.x + (j0 + u) * blockDim.x;
+                                v4[u] = (j0 + u < nj && i < n4) ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                if (j0 + u < nj) {
+                                    const int i = threadIdx.x + (j0 + u) * blockDim.x;
+                                    put_x4_sums<NCOL>(xb, s_sx, 4 * i, b, make_float4(v4[u].x * s, v4[u].y * s, v4[u].z * s, v4[u].w * s), i < n4, SXF);
+                                }
+                            }
+                        }
                     }
                 }
                 if (threadIdx.x == 0) s_inv[b] = inv;
@@ -531,7 +584,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
             __syncwarp();                                   // every lane is done with this stage
             if (lane == 0 && i_c < n_chunks) issue_next();
         }
-        if (++st == MMA_NSTAGE) { st = 0; ph ^= 1u; }
+        if (++st == NST) { st = 0; ph ^= 1u; }
         if (++j == nch) {
             // ---- end of this warp's K slice for the row group ----
             const int rg = c_rg;
@@ -601,9 +654,10 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
         }
     }
     GM_STAMP(4);
+    if (x_timed_out) mbar_wait(&s_xbar, 0u);
     if (timed_out) {
         // give the copies still in flight a bounded chance to land before the CTA's shared memory is released
-        for (int s2 = 0; s2 < MMA_NSTAGE; ++s2) { mbar_wait(&s_bar[warp][s2], 0u); mbar_wait(&s_bar[warp][s2], 1u); }
+        for (int s2 = 0; s2 < NST; ++s2) { mbar_wait(&s_bar[warp][s2], 0u); mbar_wait(&s_bar[warp][s2], 1u); }
     }
 
     if (a.epi != EPI_ARGMAX) return;

@@ -453,6 +453,7 @@ def main():
     ap.add_argument("--token-prefill", action="store_true", help="batch / tp modes: consume the prompt one position per step")
     ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"], help="tp mode: library peer-memory all-reduce or NCCL")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--shape", default="1b", choices=["1b", "27b"], help="step-trace mode: model shape (27b: Q4_0 blocks, give --layers)")
     ap.add_argument("--chain", action="store_true", help="token-once mode: the CUDA graph of per-operation kernels instead of the token kernel")
     ap.add_argument("--shard-of", type=int, default=0, help="tp mode, one process: rank 0's shard of an N-way split without collectives")
     args = ap.parse_args()
@@ -739,7 +740,8 @@ def step_trace(gpu, args):
     from adam_b200 import synth
     from adam_b200.config import gemma3_1b, with_layers
     from adam_b200.engine import ADAMEngine
-    cfg = gemma3_1b()
+    from adam_b200.config import gemma3_27b
+    cfg = gemma3_27b() if args.shape == "27b" else gemma3_1b()
     if args.layers:
         cfg = with_layers(cfg, args.layers)
     steps = max(args.steps, 64)
@@ -753,11 +755,13 @@ def step_trace(gpu, args):
     prod, att = eng.step_trace()
     t0 = int(prod[0, 0, 2])                     # the moment the layer's first kernel may read its input
     names = ["qkv", "o_proj", "gate_up", "down"]
-    out = {"traced_layer": layer, "context": PROMPT_LEN + 8 + steps, "ms_per_token": ms / steps, "unit": "us since the QKV kernel's dependency wait ended (CTA 0)", "kernels": {}}
+    out = {"shape": args.shape, "n_layer": cfg.n_layer, "traced_layer": layer, "context": PROMPT_LEN + 8 + steps, "ms_per_token": ms / steps, "unit": "us since the QKV kernel's dependency wait ended (CTA 0)", "kernels": {}}
     for k, nm in enumerate(names):
         r = prod[k, 0].astype(np.int64)
         out["kernels"][nm] = {"started": (r[0] - t0) / 1e3, "prologue_done": (r[1] - t0) / 1e3, "wait_over": (r[2] - t0) / 1e3,
                               "input_staged": (r[3] - t0) / 1e3, "products_done": (r[4] - t0) / 1e3}
+        if r[5] > 0:                            # long input vectors only: bulk copy landed, maximum known
+            out["kernels"][nm].update({"vector_in_shared_memory": (r[5] - t0) / 1e3, "maximum_known": (r[6] - t0) / 1e3})
     live = att[(att[:, 4] > 0)]
     if len(live):
         last = att[att[:, 7] > 0]
