@@ -342,6 +342,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
                     ss = cta_sum1(ss, rd[0]);
                     rms_a = sqrtf(ss / (float)a.K + a.eps);
                 }
+                GM_STAMP(5);
                 const float rcp_a = __frcp_rn(rms_a);
                 // h' and, in the same reduction, its sum of squares and max |h' * w_pre|
                 float ss = 0.f, am = 0.f;
@@ -361,6 +362,7 @@ __global__ void __launch_bounds__(512, 1) k_gemv_mma(const GemvArgs a_in, const 
                     }
                 }
                 cta_sum_max1(ss, am, rd[1], rd[2]);
+                GM_STAMP(6);
                 float rms = 1.f;
                 if (a.w_pre) {
                     rms = sqrtf(ss / (float)a.K + a.eps);

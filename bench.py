@@ -760,8 +760,8 @@ def step_trace(gpu, args):
         r = prod[k, 0].astype(np.int64)
         out["kernels"][nm] = {"started": (r[0] - t0) / 1e3, "prologue_done": (r[1] - t0) / 1e3, "wait_over": (r[2] - t0) / 1e3,
                               "input_staged": (r[3] - t0) / 1e3, "products_done": (r[4] - t0) / 1e3}
-        if r[5] > 0:                            # long input vectors only: bulk copy landed, maximum known
-            out["kernels"][nm].update({"vector_in_shared_memory": (r[5] - t0) / 1e3, "maximum_known": (r[6] - t0) / 1e3})
+        if r[5] > 0:        # inside the staging: norm chain -- branch RMS known, stream RMS and maximum known; long plain vector -- bulk copy landed, maximum known
+            out["kernels"][nm].update({"staging_mark_1": (r[5] - t0) / 1e3, "staging_mark_2": (r[6] - t0) / 1e3})
     live = att[(att[:, 4] > 0)]
     if len(live):
         last = att[att[:, 7] > 0]
