@@ -135,6 +135,33 @@ def test_long_context_uses_several_attention_splits_and_pages(gpu):
         eng.close()
 
 
+def test_clustered_and_independent_attention_splits_agree(gpu):
+    """One sequence: a cache of at most 2048 positions runs the position splits of a head as one thread-block cluster that
+    merges through shared memory, a larger one as independent CTAs that merge through global memory.  Same prompt, same
+    weights: both match the oracle, and each other's ids."""
+    cfg = _cfg(dict(n_layer=2, n_head=4, n_head_kv=2, head_dim=64))
+    tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=35, tied=True)
+    n = 300                                               # several splits of 64 positions
+    toks = synth.random_prompt(cfg.n_vocab, n, seed=7)
+    dec = OracleDecoder(cfg, dequant_model(tensors), kv_cap=n + 40)
+    for i, t in enumerate(toks):
+        ref = dec.forward(int(t), i, want_logits=(i == n - 1))
+    ids = []
+    for kv_cap in (n + 40, 4096):
+        eng = ADAMEngine(gpu, cfg, tensors, kv_cap=kv_cap, kv_dtype="f32")
+        try:
+            eng.begin([toks], [n + 32])
+            eng.step(n - 1, lm_head=False)
+            eng.step(1, lm_head=True, logits=True)
+            assert _rel(eng.read_logits(0), ref) < 1e-4
+            eng.step(24, lm_head=True)
+            ids.append(eng.read_log(0, n, 25))
+            assert gpu.device_error() == 0
+        finally:
+            eng.close()
+    assert np.array_equal(ids[0], ids[1]) and (ids[0] >= 0).all()
+
+
 def test_batch_of_ragged_prompts_equals_single_sequence_runs(gpu):
     cfg = _cfg(dict(n_layer=3))
     tensors = synth.build_model(cfg, gb.GGML_TYPE_Q4_0, seed=35, tied=False)
