@@ -822,7 +822,10 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
     static const int cluster_env = getenv("ADAM_B200_ATTN_CLUSTER") ? atoi(getenv("ADAM_B200_ATTN_CLUSTER")) : 8;
     static const uint32_t cluster_work = getenv("ADAM_B200_ATTN_CLUSTER_WORK") ? (uint32_t)atoi(getenv("ADAM_B200_ATTN_CLUSTER_WORK")) : 8u;
     const uint32_t reach = window ? (window < d.kv_cap ? window : d.kv_cap) : d.kv_cap;
-    if (cluster_env != 0 && !prefill && work <= cluster_work && reach <= 2048u) {
+    // The kernels behind a cluster launch start later (their prologues no longer overlap it); that costs more than the merge
+    // saves once the o-proj behind it has more than about a megabyte of tiles to request (27B shape, 4-way shard: 2 % slower).
+    const size_t o_bytes = (size_t)ly.m[MAT_O].rows * ly.m[MAT_O].cols * 9 / 16;
+    if (cluster_env != 0 && !prefill && work <= cluster_work && reach <= 2048u && o_bytes <= (1u << 20)) {
         struct Known { AttnKernel k; unsigned cs; };
         static Known known[16]; static int n_known = 0;
         int cs = -1;
