@@ -792,12 +792,12 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
     const uint32_t gs = d.n_head / d.n_head_kv;
     // Query heads per CTA: one while that still leaves SMs idle (lowest latency; the CTAs
     // of a kv head re-read its rows from L2), the whole group once the grid is large.
-    // Measured at the 1B shape (4 query heads on 1 kv head): one sequence is fastest with a CTA per query head, eight
+    // Measured at the 1B shape (4 query heads on 1 kv head): up to three sequences are fastest with a CTA per query head, eight
     // sequences with two heads per CTA, 16 or more sequences and prefill chunks with the whole group per CTA (the rows of a kv
     // head are then read once instead of once per query head).
     static const uint32_t hpc_env = getenv("ADAM_B200_ATTN_HPC") ? (uint32_t)atoi(getenv("ADAM_B200_ATTN_HPC")) : 0u;
     const uint32_t work = batch * d.n_head;                    // CTAs per position split with one head each
-    const uint32_t hpc_auto = work <= 8u ? 1u : (work <= 32u ? (gs >= 2u ? 2u : 1u) : gs);
+    const uint32_t hpc_auto = work <= 12u ? 1u : (work <= 32u ? (gs >= 2u ? 2u : 1u) : gs);
     const uint32_t hpc = (hpc_env && gs % hpc_env == 0 && hpc_env <= 8u) ? hpc_env : hpc_auto;
     const uint32_t window = ((d.flags & 1u) && d.sliding_window > 0 && !is_global_layer(d, L)) ? d.sliding_window : 0;
     const size_t smem = ((size_t)hpc * d.head_dim + 2 * (size_t)d.head_dim + (size_t)8 * hpc * d.head_dim) * 4;
@@ -814,13 +814,13 @@ static int launch_attn_t(Decoder* D, uint32_t L, uint32_t batch, bool prefill = 
     (void)pairs;
     AttnKernel kern = hpc <= 1 ? pick_attn_hd<T, 1>(d.head_dim) : hpc <= 2 ? pick_attn_hd<T, 2>(d.head_dim)
                     : hpc <= 4 ? pick_attn_hd<T, 4>(d.head_dim) : pick_attn_hd<T, 8>(d.head_dim);
-    // Few (sequence, head) pairs in flight: the position splits of a pair form one thread-block cluster of 8 CTAs and merge
+    // Few (sequence, head) pairs in flight (at most 12): the position splits of a pair form one thread-block cluster of 8 CTAs and merge
     // through shared memory (no partial results in global memory, no ticket, no last-CTA pass: 3 us less per launch at the
     // 1B shape).  A cluster covers any context, its CTAs taking more chunks each, so layers that may attend to more than
     // 2048 positions keep the wider grid of independent splits.  (Clusters of 16 were measured slower: they start later,
     // and so does every kernel behind them.)  ADAM_B200_ATTN_CLUSTER=0 turns the path off, =16 allows clusters of 16.
     static const int cluster_env = getenv("ADAM_B200_ATTN_CLUSTER") ? atoi(getenv("ADAM_B200_ATTN_CLUSTER")) : 8;
-    static const uint32_t cluster_work = getenv("ADAM_B200_ATTN_CLUSTER_WORK") ? (uint32_t)atoi(getenv("ADAM_B200_ATTN_CLUSTER_WORK")) : 8u;
+    static const uint32_t cluster_work = getenv("ADAM_B200_ATTN_CLUSTER_WORK") ? (uint32_t)atoi(getenv("ADAM_B200_ATTN_CLUSTER_WORK")) : 12u;
     const uint32_t reach = window ? (window < d.kv_cap ? window : d.kv_cap) : d.kv_cap;
     // The kernels behind a cluster launch start later (their prologues no longer overlap it); that costs more than the merge
     // saves once the o-proj behind it has more than about a megabyte of tiles to request (27B shape, 4-way shard: 2 % slower).
